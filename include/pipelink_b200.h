@@ -1,0 +1,133 @@
+/* pipelink_b200 — C ABI of the sm_100a stage kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its work on the
+ * given CUDA stream (a cudaStream_t passed as void*; NULL = the legacy default
+ * stream), and returns 0 (PLB_OK) or a PLB_E_* code. No entry point synchronises,
+ * allocates device memory, or throws. Device-side failures (a bounded wait that ran
+ * out, a schedule that does not fit its capacity) are written to the caller's
+ * plb_status record, which the caller zeroes before a sequence of calls and reads
+ * after synchronising the stream.
+ *
+ * Each declaration names the reference interface it stands in for, by path inside
+ * the PipeLink tree.
+ */
+#ifndef PIPELINK_B200_H
+#define PIPELINK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PLB_ABI_VERSION 1
+
+/* Return codes. 1..7 mirror PLK_E_* of the provider ABI
+ * (pipec/src/pipec2/host/include/pipelink_host_abi_v2.h:21-28). */
+enum {
+  PLB_OK = 0,
+  PLB_E_VERSION = 1,
+  PLB_E_CAPACITY = 2,
+  PLB_E_ARGUMENT = 3,
+  PLB_E_CONTRACT = 4,
+  PLB_E_RESOURCE = 5,
+  PLB_E_BUILD = 6,
+  PLB_E_RELEASE = 7,
+  PLB_E_CUDA = 8 /* a CUDA runtime/driver call failed; see plb_last_cuda_error() */
+};
+
+/* Device-written status record (32 bytes, device memory, 4-byte aligned).
+ * code: 0 healthy; 1 full-barrier timeout; 2 empty-barrier timeout; 3/4 accumulator
+ * barrier timeouts; 5 readiness-counter timeout; 6 bad argument found on the device
+ * (e.g. schedule larger than capacity); 7 drain timeout. */
+typedef struct plb_status {
+  int32_t code;
+  int32_t who;      /* CTA that recorded the failure */
+  int32_t what;     /* kernel-specific location */
+  uint32_t observed;
+  uint32_t expected;
+  int32_t reserved[3];
+} plb_status;
+
+int plb_abi_version(void);
+const char* plb_error_string(int code);
+int plb_last_cuda_error(void);
+
+/* ------------------------------------------------------------------ MXFP8
+ * ops.mxfp8_quantize(tensor, normal, transposed) as used at
+ * campaigns/mok/host/mok_port_host.py:122. src is bf16 [rows, cols], rows and cols
+ * multiples of 128. dst_fp8 is u8 [rows, cols]; dst_sc is u8
+ * [rows/128, cols/128, 32, 16] (campaigns/mok/host/resources.py:62-68). The
+ * transposed outputs are [cols, rows] with blocks of 32 along the source rows.
+ * Either pair of outputs may be NULL. */
+int plb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,
+                       void* dst_sc, void* dst_t_fp8, void* dst_t_sc, void* stream);
+
+/* Inverse of the above for checking: fp32 [rows, cols]. (No reference counterpart on
+ * the host; mirrors mxfp8::dequantize_single_block,
+ * campaigns/mok/port/act_gptoss/swiglu.cuh:395-396.) */
+int plb_mxfp8_dequantize(const void* src_fp8, const void* src_sc, int64_t rows, int64_t cols,
+                         float* dst_f32, void* stream);
+
+/* ------------------------------------------------------------------ MoE routing schedule
+ * ops.schedule_out (campaigns/mok/host/mok_port_host.py:59-69). routes is i32
+ * [world, tokens, topk] (the all-gathered top-k ids); this rank owns experts
+ * [expert_base, expert_base + num_local_experts). Every expert segment is padded to a
+ * multiple of `padding` rows (a multiple of 128; the reference's EXPERT_PADDING,
+ * campaigns/mok/port/framework/interp_fwd.cu:324). Outputs: peer_rank / peer_token_idx /
+ * dest_row i32 [capacity]; num_tokens i32 [1] (padded rows in use); tokens_per_expert
+ * i32 [num_local_experts]; expert_offsets i32 [num_local_experts + 1]; block_expert
+ * i32 [capacity/128]. scratch holds plb_moe_schedule_scratch_bytes() bytes. */
+size_t plb_moe_schedule_scratch_bytes(int world, int tokens, int topk, int num_local_experts);
+int plb_moe_schedule(const int32_t* routes, int world, int tokens, int topk, int expert_base,
+                     int num_local_experts, int capacity, int padding, int32_t* peer_rank,
+                     int32_t* peer_token_idx, int32_t* dest_row, int32_t* num_tokens,
+                     int32_t* tokens_per_expert, int32_t* expert_offsets, int32_t* block_expert,
+                     void* scratch, size_t scratch_bytes, plb_status* status, void* stream);
+
+/* ------------------------------------------------------------------ MoE dispatch
+ * dispatch_kernel (campaigns/mok/port/comm/comm.cu:105-123): for every scheduled row p,
+ * x_routed[p] = quantise(x_peers[peer_rank[p]][peer_token_idx[p]]); padding rows become
+ * zeros. x_peers is a device array of `world` device pointers to bf16 [tokens, hidden]
+ * buffers (peer-mapped for other ranks). Rows at or beyond *num_tokens are not written. */
+int plb_moe_dispatch(const void* const* x_peers, const int32_t* peer_rank,
+                     const int32_t* peer_token_idx, const int32_t* num_tokens, int64_t capacity,
+                     int64_t hidden, void* x_routed_fp8, void* x_routed_sc, void* stream);
+
+/* Interleave reference-layout gate and up weights ([experts, inter, hidden] fp8 +
+ * scales, campaigns/mok/host/resources.py:69) into the [experts, 2*inter, hidden]
+ * operand of plb_moe_gemm_gate_up: per expert, 64 gate rows then the 64 up rows of
+ * the same hidden indices, repeated. Pure data movement. */
+int plb_moe_pack_gate_up(const void* gate_fp8, const void* gate_sc, const void* up_fp8,
+                         const void* up_sc, int experts, int inter, int hidden, void* w13_fp8,
+                         void* w13_sc, void* stream);
+
+/* FWD_ROUTED_GATE + FWD_ROUTED_UP (campaigns/mok/port/gemm/gemm.cu:150-157) fused with
+ * mok_act_fwd (campaigns/mok/port/act/act.cu:100-178): hidden = silu(gate) * up,
+ * rounded to bf16, quantised to MXFP8 along the intermediate dimension. */
+int plb_moe_gemm_gate_up(const void* x_routed_fp8, const void* x_routed_sc, const void* w13_fp8,
+                         const void* w13_sc, const int32_t* block_expert,
+                         const int32_t* num_tokens, int64_t capacity, int experts, int inter,
+                         int hidden, void* hidden_fp8, void* hidden_sc, plb_status* status,
+                         void* stream);
+
+/* FWD_ROUTED_DOWN (gemm.cu:158-162) with the combine stage's row placement
+ * (combine_kernel, campaigns/mok/port/comm/comm.cu:124-129): row p of the product is
+ * written as bf16 to combine[dest_row[p]], skipped where dest_row[p] < 0. */
+int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
+                      const void* w2_sc, const int32_t* block_expert, const int32_t* num_tokens,
+                      const int32_t* dest_row, int64_t capacity, int experts, int inter, int hidden,
+                      void* combine_bf16, plb_status* status, void* stream);
+
+/* ops.fwd_epilogue (campaigns/mok/host/mok_port_host.py:204):
+ * out[t] = y_shared[t] + sum_j router_weights[t, j] * combine[t * topk + j], j ascending,
+ * fp32, every operation rounded separately. y_shared may be NULL. */
+int plb_moe_fwd_epilogue(const void* y_shared_bf16, const void* combine_bf16,
+                         const float* router_weights, int64_t tokens, int topk, int64_t hidden,
+                         void* out_bf16, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PIPELINK_B200_H */

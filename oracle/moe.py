@@ -1,0 +1,148 @@
+"""CPU oracle for the MXFP8 MoE FFN forward — TEST INFRASTRUCTURE, never on the product path.
+
+Only tests, ``__graft_entry__.smoke()`` and the CPU-baseline legs of ``bench.py`` may
+import this module.
+
+Follows the data flow of the reference's forward pass: dispatch quantises each scheduled
+token row (campaigns/mok/port/comm/comm.cu:105-123); gate and up projections produce bf16
+(campaigns/mok/port/gemm/gemm.cu:150-157); ``hidden = silu(gate) * up`` rounded to bf16 and
+requantised along the intermediate dimension (campaigns/mok/port/act/act.cu:100-178); the down
+projection writes bf16 rows that the combine stage places at ``token * k + slot``
+(gemm.cu:158-162, comm.cu:124-129); the epilogue forms
+``out = y_shared + sum_j w[t, j] * combine[t * k + j]`` (campaigns/mok/host/mok_port_host.py:204).
+
+PARITY UNPINNED for tolerances and quantisation arithmetic (``tests.utils.MXFP8_TOLERANCE``,
+``run_forward_reference_bf16`` and ``mxfp8.cuh`` are in absent submodules). Metrics follow
+``error_stats`` (mok_port_host.py:292-306): abs-mean, abs-max, relative = sum|err| / sum|ref|.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import mxfp8
+
+
+def _mm(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """fp32 a @ b.T on the host cores."""
+    return torch.matmul(torch.from_numpy(np.ascontiguousarray(a)),
+                        torch.from_numpy(np.ascontiguousarray(b)).T).numpy()
+
+
+def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    g = gate.astype(np.float32)
+    s = (g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))).astype(np.float32)
+    return (s * up.astype(np.float32)).astype(np.float32)
+
+
+def quantize_weights(w_gate, w_up, w_down):
+    """bf16-representable fp32 [E, I, H] / [E, I, H] / [E, H, I] -> per-expert (fp8, sc) lists."""
+    out = {}
+    for name, w in (("gate", w_gate), ("up", w_up), ("down", w_down)):
+        E, R, C = w.shape
+        q, sc = mxfp8.quantize(w.reshape(E * R, C))
+        out[name] = (q.reshape(E, R, C), sc)
+    return out
+
+
+def pack_gate_up(gate_q, gate_sc, up_q, up_sc):
+    """Row interleave used by the fused gate/up GEMM: per expert 64 gate rows, 64 up rows, ..."""
+    E, I, H = gate_q.shape
+    g_s = mxfp8.unpack_scales(gate_sc, E * I, H).reshape(E, I // 64, 64, H // 32)
+    u_s = mxfp8.unpack_scales(up_sc, E * I, H).reshape(E, I // 64, 64, H // 32)
+    q = np.stack([gate_q.reshape(E, I // 64, 64, H), up_q.reshape(E, I // 64, 64, H)], axis=2)
+    s = np.stack([g_s, u_s], axis=2)
+    return q.reshape(E, 2 * I, H), mxfp8.pack_scales(s.reshape(E * 2 * I, H // 32))
+
+
+def dispatch(x_by_rank, sched):
+    """Gather + quantise the scheduled rows. x_by_rank: list of fp32 [tokens, H] (bf16 values)."""
+    total = int(sched["num_tokens"][0])
+    H = x_by_rank[0].shape[1]
+    rows = np.zeros((total, H), dtype=np.float32)
+    pr, pt = sched["peer_rank"][:total], sched["peer_token_idx"][:total]
+    for r, x in enumerate(x_by_rank):
+        sel = pr == r
+        rows[sel] = x[pt[sel]]
+    q, sc = mxfp8.quantize(rows)
+    return q, sc
+
+
+def expert_ffn(xq, xsc, weights, sched, round_gate_up=True):
+    """Rows [total, H] quantised -> (hidden_q, hidden_sc, y bf16-valued fp32 [total, H])."""
+    total, H = xq.shape
+    gate_q, gate_sc = weights["gate"]
+    up_q, up_sc = weights["up"]
+    down_q, down_sc = weights["down"]
+    E, I, _ = gate_q.shape
+    x = mxfp8.dequantize(xq, xsc)
+    wg = mxfp8.dequantize(gate_q.reshape(E * I, H), gate_sc).reshape(E, I, H)
+    wu = mxfp8.dequantize(up_q.reshape(E * I, H), up_sc).reshape(E, I, H)
+    wd = mxfp8.dequantize(down_q.reshape(E * H, I), down_sc).reshape(E, H, I)
+    off = sched["expert_offsets"]
+    hidden = np.zeros((total, I), dtype=np.float32)
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi == lo:
+            continue
+        g = _mm(x[lo:hi], wg[e])
+        u = _mm(x[lo:hi], wu[e])
+        if round_gate_up:
+            g, u = mxfp8.bf16_round(g), mxfp8.bf16_round(u)
+        hidden[lo:hi] = mxfp8.bf16_round(silu_mul(g, u))
+    hq, hsc = mxfp8.quantize(hidden)
+    hd = mxfp8.dequantize(hq, hsc)
+    y = np.zeros((total, H), dtype=np.float32)
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            y[lo:hi] = mxfp8.bf16_round(_mm(hd[lo:hi], wd[e]))
+    return hq, hsc, y
+
+
+def combine(y, sched, rank, tokens, topk):
+    """Place rows owned by `rank` at token * k + slot (rows from other ranks are ignored)."""
+    total = int(sched["num_tokens"][0])
+    H = y.shape[1]
+    buf = np.zeros((tokens * topk, H), dtype=np.float32)
+    pr, dr = sched["peer_rank"][:total], sched["dest_row"][:total]
+    sel = pr == rank
+    buf[dr[sel]] = y[:total][sel]
+    return buf
+
+
+def fwd_epilogue(combine_buf, router_w, y_shared=None):
+    """out[t] = y_shared[t] + sum_j w[t, j] * combine[t*k + j]; separate fp32 roundings, j ascending."""
+    tokens, topk = router_w.shape
+    H = combine_buf.shape[1]
+    c = combine_buf.reshape(tokens, topk, H).astype(np.float32)
+    acc = np.zeros((tokens, H), dtype=np.float32) if y_shared is None else y_shared.astype(np.float32).copy()
+    for j in range(topk):
+        prod = (router_w[:, j:j + 1].astype(np.float32) * c[:, j]).astype(np.float32)
+        acc = (acc + prod).astype(np.float32)
+    return mxfp8.bf16_round(acc)
+
+
+def forward_single_rank(x, routes, router_w, weights, padding=128, capacity=None):
+    """Whole forward on one rank. x fp32 (bf16 values) [T, H]; routes i32 [T, k]."""
+    from . import routing
+    T, k = routes.shape
+    E = weights["gate"][0].shape[0]
+    if capacity is None:
+        capacity = ((T * k + E * (padding - 1)) + 127) // 128 * 128
+    sched = routing.build_schedule(routes[None], 0, E, capacity, padding)
+    xq, xsc = dispatch([x], sched)
+    hq, hsc, y = expert_ffn(xq, xsc, weights, sched)
+    buf = combine(y, sched, 0, T, k)
+    out = fwd_epilogue(buf, router_w)
+    return dict(schedule=sched, x_routed=(xq, xsc), hidden=(hq, hsc), y=y, combine=buf, output=out)
+
+
+def error_stats(expected, actual):
+    """abs-mean, abs-max, relative (= sum|err| / sum|ref|), and relative L2."""
+    e = np.asarray(expected, dtype=np.float64).reshape(-1)
+    a = np.asarray(actual, dtype=np.float64).reshape(-1)
+    d = np.abs(e - a)
+    return dict(abs_mean=float(d.mean()), abs_max=float(d.max()),
+                relative=float(d.sum() / max(np.abs(e).sum(), 1e-300)),
+                rel_l2=float(np.sqrt((d * d).sum() / max((e * e).sum(), 1e-300))))

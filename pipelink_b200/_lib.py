@@ -1,0 +1,85 @@
+"""ctypes binding of ``libpipelink_b200.so`` (declarations: ``include/pipelink_b200.h``).
+
+Loading fails loudly: there is no CPU or library fallback for any stage. The library is
+looked for in-tree (``pipelink_b200/_native``) and is produced by ``pipelink_b200.build``.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p, POINTER, c_float
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "_native" / "libpipelink_b200.so"
+
+STATUS_BYTES = 32
+STATUS_NAMES = {
+    0: "ok", 1: "full-barrier timeout", 2: "empty-barrier timeout", 3: "accumulator-full timeout",
+    4: "accumulator-empty timeout", 5: "readiness-counter timeout", 6: "bad argument on device",
+    7: "drain timeout",
+}
+
+# name -> (restype, argtypes); must list every symbol include/pipelink_b200.h declares.
+PROTOTYPES = {
+    "plb_abi_version": (c_int, []),
+    "plb_error_string": (c_char_p, [c_int]),
+    "plb_last_cuda_error": (c_int, []),
+    "plb_mxfp8_quantize": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p]),
+    "plb_mxfp8_dequantize": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "plb_moe_schedule_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "plb_moe_schedule": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "plb_moe_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                 c_void_p, c_void_p, c_void_p]),
+    "plb_moe_pack_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                     c_void_p, c_void_p, c_void_p]),
+    "plb_moe_gemm_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                     c_void_p]),
+    "plb_moe_gemm_down": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_void_p]),
+    "plb_moe_fwd_epilogue": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64,
+                                     c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+class PlbError(RuntimeError):
+    def __init__(self, fn: str, code: int, detail: str = ""):
+        self.fn, self.code = fn, code
+        super().__init__(f"{fn} failed: {code} ({detail})")
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise NativeLibraryMissing(
+                f"{LIB_PATH} not found: run `python -m pipelink_b200.build` (needs nvcc). "
+                "There is no fallback path.")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (restype, argtypes) in PROTOTYPES.items():
+            fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+            fn.restype, fn.argtypes = restype, argtypes
+        if lib.plb_abi_version() != 1:
+            raise NativeLibraryMissing("libpipelink_b200.so ABI version mismatch; rebuild")
+        _lib = lib
+    return _lib
+
+
+def call(name: str, *args) -> None:
+    """Call an int-returning entry point and raise PlbError on a non-zero code."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        detail = lib.plb_error_string(rc).decode()
+        if rc == 8:
+            detail += f", cudaError {lib.plb_last_cuda_error()}"
+        raise PlbError(name, rc, detail)

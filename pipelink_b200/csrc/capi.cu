@@ -1,0 +1,222 @@
+// extern "C" layer: argument checks, then one launcher call per entry point.
+// Declarations and their reference counterparts are in include/pipelink_b200.h.
+#include "../../include/pipelink_b200.h"
+
+#include "kernels.h"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int from_cuda(cudaError_t err) {
+  if (err == cudaSuccess) return PLB_OK;
+  g_last_cuda_error = static_cast<int>(err);
+  return err == cudaErrorInvalidValue ? PLB_E_ARGUMENT : PLB_E_CUDA;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int sm_count() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  return sms;
+}
+
+}  // namespace
+
+extern "C" {
+
+int plb_abi_version(void) { return PLB_ABI_VERSION; }
+
+const char* plb_error_string(int code) {
+  switch (code) {
+    case PLB_OK: return "ok";
+    case PLB_E_VERSION: return "ABI version mismatch";
+    case PLB_E_CAPACITY: return "capacity exceeded";
+    case PLB_E_ARGUMENT: return "bad argument";
+    case PLB_E_CONTRACT: return "contract violated";
+    case PLB_E_RESOURCE: return "resource unavailable";
+    case PLB_E_BUILD: return "build failed";
+    case PLB_E_RELEASE: return "release failed";
+    case PLB_E_CUDA: return "CUDA call failed";
+    default: return "unknown error";
+  }
+}
+
+int plb_last_cuda_error(void) { return g_last_cuda_error; }
+
+int plb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,
+                       void* dst_sc, void* dst_t_fp8, void* dst_t_sc, void* stream) {
+  if (rows < 0 || cols < 0 || rows % 128 || cols % 128) return PLB_E_ARGUMENT;
+  if (src_bf16 == nullptr || !aligned16(src_bf16)) return PLB_E_ARGUMENT;
+  if ((dst_fp8 == nullptr) != (dst_sc == nullptr)) return PLB_E_ARGUMENT;
+  if ((dst_t_fp8 == nullptr) != (dst_t_sc == nullptr)) return PLB_E_ARGUMENT;
+  if (!aligned16(dst_fp8) || !aligned16(dst_sc) || !aligned16(dst_t_fp8) || !aligned16(dst_t_sc))
+    return PLB_E_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dst_fp8 != nullptr) {
+    const int rc = from_cuda(plb::launch_quantize_plain(src_bf16, rows, cols, dst_fp8, dst_sc, s));
+    if (rc != PLB_OK) return rc;
+  }
+  if (dst_t_fp8 != nullptr) {
+    const int rc =
+        from_cuda(plb::launch_quantize_transposed(src_bf16, rows, cols, dst_t_fp8, dst_t_sc, s));
+    if (rc != PLB_OK) return rc;
+  }
+  return PLB_OK;
+}
+
+int plb_mxfp8_dequantize(const void* src_fp8, const void* src_sc, int64_t rows, int64_t cols,
+                         float* dst_f32, void* stream) {
+  if (rows < 0 || cols < 0 || rows % 128 || cols % 128) return PLB_E_ARGUMENT;
+  if (src_fp8 == nullptr || src_sc == nullptr || dst_f32 == nullptr) return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_dequantize(src_fp8, src_sc, rows, cols, dst_f32,
+                                          static_cast<cudaStream_t>(stream)));
+}
+
+size_t plb_moe_schedule_scratch_bytes(int world, int tokens, int topk, int num_local_experts) {
+  const int64_t entries = static_cast<int64_t>(world) * tokens * topk;
+  return static_cast<size_t>(plb::schedule_scratch_ints(entries, num_local_experts)) * sizeof(int);
+}
+
+int plb_moe_schedule(const int32_t* routes, int world, int tokens, int topk, int expert_base,
+                     int num_local_experts, int capacity, int padding, int32_t* peer_rank,
+                     int32_t* peer_token_idx, int32_t* dest_row, int32_t* num_tokens,
+                     int32_t* tokens_per_expert, int32_t* expert_offsets, int32_t* block_expert,
+                     void* scratch, size_t scratch_bytes, plb_status* status, void* stream) {
+  if (world < 1 || tokens < 0 || topk < 1 || num_local_experts < 1 || num_local_experts > 8192)
+    return PLB_E_ARGUMENT;
+  if (capacity < 0 || capacity % 128 || padding < 128 || padding % 128) return PLB_E_ARGUMENT;
+  if (!routes || !peer_rank || !peer_token_idx || !dest_row || !num_tokens || !tokens_per_expert ||
+      !expert_offsets || !block_expert || !status)
+    return PLB_E_ARGUMENT;
+  const size_t need = plb_moe_schedule_scratch_bytes(world, tokens, topk, num_local_experts);
+  if (need > 0 && (scratch == nullptr || scratch_bytes < need)) return PLB_E_CAPACITY;
+  plb::ScheduleArgs a;
+  a.routes = routes;
+  a.world = world;
+  a.tokens = tokens;
+  a.topk = topk;
+  a.expert_base = expert_base;
+  a.num_local_experts = num_local_experts;
+  a.capacity = capacity;
+  a.padding = padding;
+  a.peer_rank = peer_rank;
+  a.peer_token_idx = peer_token_idx;
+  a.dest_row = dest_row;
+  a.num_tokens = num_tokens;
+  a.tokens_per_expert = tokens_per_expert;
+  a.expert_offsets = expert_offsets;
+  a.block_expert = block_expert;
+  a.scratch = static_cast<int*>(scratch);
+  a.status = reinterpret_cast<plb::Status*>(status);
+  return from_cuda(plb::launch_schedule(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_dispatch(const void* const* x_peers, const int32_t* peer_rank,
+                     const int32_t* peer_token_idx, const int32_t* num_tokens, int64_t capacity,
+                     int64_t hidden, void* x_routed_fp8, void* x_routed_sc, void* stream) {
+  if (capacity < 0 || capacity % 128 || hidden <= 0 || hidden % 128) return PLB_E_ARGUMENT;
+  if (!x_peers || !peer_rank || !peer_token_idx || !num_tokens || !x_routed_fp8 || !x_routed_sc)
+    return PLB_E_ARGUMENT;
+  if (!aligned16(x_routed_fp8) || !aligned16(x_routed_sc)) return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_quantize_rows(x_peers, peer_rank, peer_token_idx, num_tokens,
+                                             capacity, hidden, x_routed_fp8, x_routed_sc,
+                                             static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_pack_gate_up(const void* gate_fp8, const void* gate_sc, const void* up_fp8,
+                         const void* up_sc, int experts, int inter, int hidden, void* w13_fp8,
+                         void* w13_sc, void* stream) {
+  if (experts < 1 || inter < 128 || inter % 128 || hidden < 128 || hidden % 128)
+    return PLB_E_ARGUMENT;
+  if (!gate_fp8 || !gate_sc || !up_fp8 || !up_sc || !w13_fp8 || !w13_sc) return PLB_E_ARGUMENT;
+  if (!aligned16(gate_fp8) || !aligned16(up_fp8) || !aligned16(w13_fp8)) return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_pack_gate_up(gate_fp8, gate_sc, up_fp8, up_sc, experts, inter,
+                                            hidden, w13_fp8, w13_sc,
+                                            static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_gemm_gate_up(const void* x_routed_fp8, const void* x_routed_sc, const void* w13_fp8,
+                         const void* w13_sc, const int32_t* block_expert,
+                         const int32_t* num_tokens, int64_t capacity, int experts, int inter,
+                         int hidden, void* hidden_fp8, void* hidden_sc, plb_status* status,
+                         void* stream) {
+  if (capacity < 0 || capacity % 128 || experts < 1 || inter < 128 || inter % 128 ||
+      hidden < 128 || hidden % 128)
+    return PLB_E_ARGUMENT;
+  if (!x_routed_fp8 || !x_routed_sc || !w13_fp8 || !w13_sc || !block_expert || !num_tokens ||
+      !hidden_fp8 || !hidden_sc || !status)
+    return PLB_E_ARGUMENT;
+  if (!aligned16(x_routed_fp8) || !aligned16(x_routed_sc) || !aligned16(w13_fp8) ||
+      !aligned16(w13_sc) || !aligned16(hidden_fp8) || !aligned16(hidden_sc))
+    return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.a_fp8 = x_routed_fp8;
+  a.a_sc = x_routed_sc;
+  a.b_fp8 = w13_fp8;
+  a.b_sc = w13_sc;
+  a.rows_capacity = capacity;
+  a.experts = experts;
+  a.n_rows = 2 * inter;
+  a.K = hidden;
+  a.block_expert = block_expert;
+  a.num_rows_dev = num_tokens;
+  a.mode = 0;
+  a.out = hidden_fp8;
+  a.out_sc = hidden_sc;
+  a.dest_row = nullptr;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(plb::launch_grouped_gemm(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
+                      const void* w2_sc, const int32_t* block_expert, const int32_t* num_tokens,
+                      const int32_t* dest_row, int64_t capacity, int experts, int inter, int hidden,
+                      void* combine_bf16, plb_status* status, void* stream) {
+  if (capacity < 0 || capacity % 128 || experts < 1 || inter < 128 || inter % 128 ||
+      hidden < 128 || hidden % 128)
+    return PLB_E_ARGUMENT;
+  if (!hidden_fp8 || !hidden_sc || !w2_fp8 || !w2_sc || !block_expert || !num_tokens ||
+      !dest_row || !combine_bf16 || !status)
+    return PLB_E_ARGUMENT;
+  if (!aligned16(hidden_fp8) || !aligned16(hidden_sc) || !aligned16(w2_fp8) ||
+      !aligned16(w2_sc) || !aligned16(combine_bf16))
+    return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.a_fp8 = hidden_fp8;
+  a.a_sc = hidden_sc;
+  a.b_fp8 = w2_fp8;
+  a.b_sc = w2_sc;
+  a.rows_capacity = capacity;
+  a.experts = experts;
+  a.n_rows = hidden;
+  a.K = inter;
+  a.block_expert = block_expert;
+  a.num_rows_dev = num_tokens;
+  a.mode = 1;
+  a.out = combine_bf16;
+  a.out_sc = nullptr;
+  a.dest_row = dest_row;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(plb::launch_grouped_gemm(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_fwd_epilogue(const void* y_shared_bf16, const void* combine_bf16,
+                         const float* router_weights, int64_t tokens, int topk, int64_t hidden,
+                         void* out_bf16, void* stream) {
+  if (tokens < 0 || topk < 1 || hidden <= 0 || hidden % 8) return PLB_E_ARGUMENT;
+  if (!combine_bf16 || !router_weights || !out_bf16) return PLB_E_ARGUMENT;
+  if (!aligned16(combine_bf16) || !aligned16(out_bf16) || !aligned16(y_shared_bf16))
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_weighted_combine(combine_bf16, router_weights, y_shared_bf16,
+                                                tokens, topk, hidden, out_bf16,
+                                                static_cast<cudaStream_t>(stream)));
+}
+
+}  // extern "C"

@@ -1,0 +1,78 @@
+// Internal launcher declarations shared by the kernel translation units and the
+// C-ABI layer. Every launcher enqueues work on `stream` and returns a cudaError_t
+// from the launch; none synchronises or allocates.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace plb {
+
+// ---- MXFP8 quantisation (quant.cu)
+cudaError_t launch_quantize_rows(const void* const* src_peers, const int* peer_rank,
+                                 const int* peer_token_idx, const int* num_rows_dev,
+                                 int64_t rows, int64_t cols, void* dst_fp8, void* dst_sc,
+                                 cudaStream_t stream);
+cudaError_t launch_quantize_plain(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,
+                                  void* dst_sc, cudaStream_t stream);
+cudaError_t launch_quantize_transposed(const void* src_bf16, int64_t rows, int64_t cols,
+                                       void* dst_t_fp8, void* dst_t_sc, cudaStream_t stream);
+cudaError_t launch_dequantize(const void* src_fp8, const void* src_sc, int64_t rows, int64_t cols,
+                              float* dst, cudaStream_t stream);
+cudaError_t launch_pack_gate_up(const void* gate_fp8, const void* gate_sc, const void* up_fp8,
+                                const void* up_sc, int experts, int inter, int hidden,
+                                void* w13_fp8, void* w13_sc, cudaStream_t stream);
+cudaError_t launch_weighted_combine(const void* combine_bf16, const float* router_weights,
+                                    const void* y_shared_bf16, int64_t tokens, int topk,
+                                    int64_t hidden, void* out_bf16, cudaStream_t stream);
+
+// ---- routing schedule (schedule.cu)
+struct ScheduleArgs {
+  const int* routes;      // [world * tokens * topk] global expert ids
+  int world, tokens, topk;
+  int expert_base;        // first global expert id owned by this rank
+  int num_local_experts;
+  int capacity;           // rows available in the schedule arrays (multiple of 128)
+  int padding;            // every expert segment is padded to a multiple of this (multiple of 128)
+  int* peer_rank;         // [capacity] source rank, -1 on padding rows
+  int* peer_token_idx;    // [capacity] token index on the source rank
+  int* dest_row;          // [capacity] token * topk + slot on the source rank, -1 on padding
+  int* num_tokens;        // [1] padded rows in use
+  int* tokens_per_expert; // [num_local_experts] unpadded counts
+  int* expert_offsets;    // [num_local_experts + 1] first row of each segment
+  int* block_expert;      // [capacity / 128] local expert of each 128-row block, -1 if unused
+  int* scratch;           // [schedule_scratch_ints(...)]
+  Status* status;
+};
+constexpr int kScheduleChunk = 1024;
+inline int64_t schedule_scratch_ints(int64_t entries, int num_local_experts) {
+  return ((entries + kScheduleChunk - 1) / kScheduleChunk) * num_local_experts;
+}
+cudaError_t launch_schedule(const ScheduleArgs& a, cudaStream_t stream);
+
+// ---- grouped MXFP8 GEMM (grouped_gemm.cu)
+struct GroupedGemmArgs {
+  const void* a_fp8;      // [rows_capacity, K]
+  const void* a_sc;       // [rows_capacity/128, K/128, 32, 16]
+  const void* b_fp8;      // [experts * n_rows, K]
+  const void* b_sc;       // [experts * n_rows/128, K/128, 32, 16]
+  int64_t rows_capacity;  // multiple of 128
+  int experts;
+  int n_rows;             // weight rows per expert (multiple of 128)
+  int K;                  // multiple of 128
+  const int* block_expert;
+  const int* num_rows_dev;
+  // mode 0: tile columns [0,64) are gate, [64,128) are up -> hidden (fp8 + scales), [rows, n_rows/2]
+  // mode 1: tile columns are output columns -> bf16 rows scattered through dest_row, [*, n_rows]
+  int mode;
+  void* out;
+  void* out_sc;
+  const int* dest_row;
+  int num_sms;
+  Status* status;
+};
+cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);
+int grouped_gemm_smem_bytes();
+
+}  // namespace plb

@@ -1,0 +1,289 @@
+// HBM-bound byte/element kernels either side of the grouped GEMM:
+//   * MXFP8 quantisation of bf16 rows, optionally gathered through the routing
+//     schedule from peer-addressable token buffers (the dispatch stage,
+//     campaigns/mok/port/comm/comm.cu:105-123: x_routed[p] = quant(x_buffer[peer_rank[p]][peer_token_idx[p]])),
+//   * the transposed orientation (scales along the original row dimension) that the
+//     backward GEMMs contract over (campaigns/mok/host/resources.py:62-77),
+//   * dequantisation (checker use), gate/up weight interleave, and the weighted
+//     top-k reduction  out = y_shared + sum_j w[t,j] * combine[t*k+j]
+//     (ops.fwd_epilogue, campaigns/mok/host/mok_port_host.py:204).
+// All are sized as grid-stride loops over 16-byte vectors with a grid that is a
+// multiple of the SM count.
+#include "kernels.h"
+#include "mxfp8.cuh"
+
+namespace plb {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// One thread owns 8 consecutive elements; 4 adjacent lanes own one 32-element block.
+template <bool GATHER>
+__global__ void __launch_bounds__(kThreads)
+quantize_rows_kernel(const void* const* __restrict__ src_peers, const uint4* __restrict__ src_plain,
+                     const int* __restrict__ peer_rank, const int* __restrict__ peer_token_idx,
+                     const int* __restrict__ num_rows_dev, int64_t rows, int64_t cols,
+                     uint2* __restrict__ dst_fp8, uint8_t* __restrict__ dst_sc) {
+  const int64_t vec_per_row = cols >> 3;
+  int64_t nrows = rows;
+  if (num_rows_dev != nullptr) {
+    const int64_t live = *num_rows_dev;
+    nrows = live < rows ? live : rows;
+  }
+  const int64_t total = nrows * vec_per_row;               // multiple of 16
+  const int64_t total_warp = (total + 31) & ~int64_t(31);  // keep whole warps in the loop
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t col_blocks = cols >> 7;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total_warp;
+       v += stride) {
+    const bool active = v < total;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    int64_t row = 0, j = 0;
+    if (active) {
+      row = v / vec_per_row;
+      j = v - row * vec_per_row;
+      if (GATHER) {
+        const int pr = peer_rank[row];
+        if (pr >= 0) {
+          const uint4* base = static_cast<const uint4*>(src_peers[pr]);
+          raw = base[static_cast<int64_t>(peer_token_idx[row]) * vec_per_row + j];
+        }
+      } else {
+        raw = src_plain[v];
+      }
+    }
+    float f[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
+                  bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const uint32_t e = e8m0_from_amax(amax);
+    const float inv = e8m0_inverse(e);
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t base_lane = lane & ~15u;
+    uint32_t word = __shfl_sync(0xFFFFFFFFu, e, base_lane);
+    word |= __shfl_sync(0xFFFFFFFFu, e, base_lane + 4) << 8;
+    word |= __shfl_sync(0xFFFFFFFFu, e, base_lane + 8) << 16;
+    word |= __shfl_sync(0xFFFFFFFFu, e, base_lane + 12) << 24;
+    if (active) {
+      uint2 out;
+      out.x = cvt_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+      out.y = cvt_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+      dst_fp8[v] = out;
+      if ((lane & 15u) == 0u) {
+        const size_t off = scale_offset(row, j >> 2, col_blocks);
+        *reinterpret_cast<uint32_t*>(dst_sc + off) = word;
+      }
+    }
+  }
+}
+
+// Transposed orientation: dst_t[c, r] = quant(src[r, c]) with blocks of 32 along r.
+// One thread owns two adjacent source columns and one 32-row block.
+__global__ void __launch_bounds__(kThreads)
+quantize_transposed_kernel(const uint32_t* __restrict__ src, int64_t rows, int64_t cols,
+                           uint8_t* __restrict__ dst_fp8, uint8_t* __restrict__ dst_sc) {
+  const int64_t col_pairs = cols >> 1;
+  const int64_t row_blocks = rows >> 5;
+  const int64_t total = col_pairs * row_blocks;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t dst_col_blocks = rows >> 7;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total;
+       v += stride) {
+    const int64_t rb = v / col_pairs;
+    const int64_t cp = v - rb * col_pairs;
+    float lo[32], hi[32];
+    float amax_lo = 0.0f, amax_hi = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t w = src[(rb * 32 + i) * col_pairs + cp];
+      lo[i] = bf16_lo(w);
+      hi[i] = bf16_hi(w);
+      amax_lo = fmaxf(amax_lo, fabsf(lo[i]));
+      amax_hi = fmaxf(amax_hi, fabsf(hi[i]));
+    }
+    const uint32_t e_lo = e8m0_from_amax(amax_lo), e_hi = e8m0_from_amax(amax_hi);
+    const float inv_lo = e8m0_inverse(e_lo), inv_hi = e8m0_inverse(e_hi);
+    uint4* out_lo = reinterpret_cast<uint4*>(dst_fp8 + (2 * cp) * rows + rb * 32);
+    uint4* out_hi = reinterpret_cast<uint4*>(dst_fp8 + (2 * cp + 1) * rows + rb * 32);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      uint4 a, b;
+      a.x = cvt_e4m3x4(lo[q * 16 + 0] * inv_lo, lo[q * 16 + 1] * inv_lo, lo[q * 16 + 2] * inv_lo, lo[q * 16 + 3] * inv_lo);
+      a.y = cvt_e4m3x4(lo[q * 16 + 4] * inv_lo, lo[q * 16 + 5] * inv_lo, lo[q * 16 + 6] * inv_lo, lo[q * 16 + 7] * inv_lo);
+      a.z = cvt_e4m3x4(lo[q * 16 + 8] * inv_lo, lo[q * 16 + 9] * inv_lo, lo[q * 16 + 10] * inv_lo, lo[q * 16 + 11] * inv_lo);
+      a.w = cvt_e4m3x4(lo[q * 16 + 12] * inv_lo, lo[q * 16 + 13] * inv_lo, lo[q * 16 + 14] * inv_lo, lo[q * 16 + 15] * inv_lo);
+      b.x = cvt_e4m3x4(hi[q * 16 + 0] * inv_hi, hi[q * 16 + 1] * inv_hi, hi[q * 16 + 2] * inv_hi, hi[q * 16 + 3] * inv_hi);
+      b.y = cvt_e4m3x4(hi[q * 16 + 4] * inv_hi, hi[q * 16 + 5] * inv_hi, hi[q * 16 + 6] * inv_hi, hi[q * 16 + 7] * inv_hi);
+      b.z = cvt_e4m3x4(hi[q * 16 + 8] * inv_hi, hi[q * 16 + 9] * inv_hi, hi[q * 16 + 10] * inv_hi, hi[q * 16 + 11] * inv_hi);
+      b.w = cvt_e4m3x4(hi[q * 16 + 12] * inv_hi, hi[q * 16 + 13] * inv_hi, hi[q * 16 + 14] * inv_hi, hi[q * 16 + 15] * inv_hi);
+      out_lo[q] = a;
+      out_hi[q] = b;
+    }
+    dst_sc[scale_offset(2 * cp, rb, dst_col_blocks)] = static_cast<uint8_t>(e_lo);
+    dst_sc[scale_offset(2 * cp + 1, rb, dst_col_blocks)] = static_cast<uint8_t>(e_hi);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+dequantize_kernel(const uint8_t* __restrict__ src, const uint8_t* __restrict__ sc, int64_t rows,
+                  int64_t cols, float* __restrict__ dst) {
+  const int64_t total = rows * cols;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t col_blocks = cols >> 7;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const uint32_t s = sc[scale_offset(r, c >> 5, col_blocks)];
+    dst[i] = e4m3_to_float(src[i]) * e8m0_value(s);
+  }
+}
+
+// w13 row order per expert: [gate 0..63 | up 0..63 | gate 64..127 | up 64..127 | ...]
+// so that one 128-row weight tile yields 64 gate and 64 up columns of the same
+// hidden index range and its scale block is one ordinary 512-byte block.
+__global__ void __launch_bounds__(kThreads)
+pack_gate_up_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ gate_sc,
+                    const uint8_t* __restrict__ up, const uint8_t* __restrict__ up_sc, int experts,
+                    int inter, int hidden, uint8_t* __restrict__ w13, uint8_t* __restrict__ w13_sc) {
+  const int64_t vec_per_row = hidden >> 4;  // 16-byte vectors
+  const int64_t dst_rows = static_cast<int64_t>(experts) * 2 * inter;
+  const int64_t total = dst_rows * vec_per_row;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t col_blocks = hidden >> 7;
+  const int64_t groups = hidden >> 5;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total;
+       v += stride) {
+    const int64_t dr = v / vec_per_row, j = v - dr * vec_per_row;
+    const int64_t e = dr / (2 * inter), within = dr - e * 2 * inter;
+    const int64_t tile = within >> 7, r = within & 127;
+    const bool is_up = r >= 64;
+    const int64_t sr = e * inter + tile * 64 + (r & 63);
+    const uint8_t* src = is_up ? up : gate;
+    reinterpret_cast<uint4*>(w13)[v] = reinterpret_cast<const uint4*>(src)[sr * vec_per_row + j];
+    // this thread also moves the scale bytes of the 32-column groups it starts
+    if ((j & 1) == 0) {
+      const int64_t g = j >> 1;
+      if (g < groups) {
+        const uint8_t* ssrc = is_up ? up_sc : gate_sc;
+        w13_sc[scale_offset(dr, g, col_blocks)] = ssrc[scale_offset(sr, g, col_blocks)];
+      }
+    }
+  }
+}
+
+// out[t, c] = bf16( (y_shared ? y_shared[t,c] : 0) + sum_{j<k} w[t,j] * combine[t*k+j, c] )
+// with every multiply and add rounded separately in fp32 and j ascending, so the
+// result is a pure function of its inputs (deterministic combine order).
+__global__ void __launch_bounds__(kThreads)
+weighted_combine_kernel(const uint4* __restrict__ combine, const float* __restrict__ w,
+                        const uint4* __restrict__ y_shared, int64_t tokens, int topk,
+                        int64_t hidden, uint4* __restrict__ out) {
+  const int64_t vec_per_row = hidden >> 3;
+  const int64_t total = tokens * vec_per_row;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total;
+       v += stride) {
+    const int64_t t = v / vec_per_row, j = v - t * vec_per_row;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (y_shared != nullptr) {
+      const uint4 y = y_shared[v];
+      acc[0] = bf16_lo(y.x); acc[1] = bf16_hi(y.x); acc[2] = bf16_lo(y.y); acc[3] = bf16_hi(y.y);
+      acc[4] = bf16_lo(y.z); acc[5] = bf16_hi(y.z); acc[6] = bf16_lo(y.w); acc[7] = bf16_hi(y.w);
+    }
+    for (int s = 0; s < topk; ++s) {
+      const float ws = w[t * topk + s];
+      const uint4 c = combine[(t * topk + s) * vec_per_row + j];
+      const float f[8] = {bf16_lo(c.x), bf16_hi(c.x), bf16_lo(c.y), bf16_hi(c.y),
+                          bf16_lo(c.z), bf16_hi(c.z), bf16_lo(c.w), bf16_hi(c.w)};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(ws, f[i]));
+    }
+    uint4 o;
+    __nv_bfloat162 p;
+    p = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&p);
+    p = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&p);
+    p = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&p);
+    p = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&p);
+    out[v] = o;
+  }
+}
+
+int grid_for(int64_t work_items) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t want = (work_items + kThreads - 1) / kThreads;
+  const int64_t cap = static_cast<int64_t>(sms) * 8;
+  int64_t g = want < cap ? want : cap;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+}  // namespace
+
+cudaError_t launch_quantize_rows(const void* const* src_peers, const int* peer_rank,
+                                 const int* peer_token_idx, const int* num_rows_dev, int64_t rows,
+                                 int64_t cols, void* dst_fp8, void* dst_sc, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  quantize_rows_kernel<true><<<grid_for(rows * (cols >> 3)), kThreads, 0, stream>>>(
+      src_peers, nullptr, peer_rank, peer_token_idx, num_rows_dev, rows, cols,
+      static_cast<uint2*>(dst_fp8), static_cast<uint8_t*>(dst_sc));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_plain(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,
+                                  void* dst_sc, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  quantize_rows_kernel<false><<<grid_for(rows * (cols >> 3)), kThreads, 0, stream>>>(
+      nullptr, static_cast<const uint4*>(src_bf16), nullptr, nullptr, nullptr, rows, cols,
+      static_cast<uint2*>(dst_fp8), static_cast<uint8_t*>(dst_sc));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_transposed(const void* src_bf16, int64_t rows, int64_t cols,
+                                       void* dst_t_fp8, void* dst_t_sc, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  quantize_transposed_kernel<<<grid_for((rows >> 5) * (cols >> 1)), kThreads, 0, stream>>>(
+      static_cast<const uint32_t*>(src_bf16), rows, cols, static_cast<uint8_t*>(dst_t_fp8),
+      static_cast<uint8_t*>(dst_t_sc));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dequantize(const void* src_fp8, const void* src_sc, int64_t rows, int64_t cols,
+                              float* dst, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  dequantize_kernel<<<grid_for(rows * cols), kThreads, 0, stream>>>(
+      static_cast<const uint8_t*>(src_fp8), static_cast<const uint8_t*>(src_sc), rows, cols, dst);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_gate_up(const void* gate_fp8, const void* gate_sc, const void* up_fp8,
+                                const void* up_sc, int experts, int inter, int hidden,
+                                void* w13_fp8, void* w13_sc, cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(experts) * 2 * inter * (hidden >> 4);
+  pack_gate_up_kernel<<<grid_for(total), kThreads, 0, stream>>>(
+      static_cast<const uint8_t*>(gate_fp8), static_cast<const uint8_t*>(gate_sc),
+      static_cast<const uint8_t*>(up_fp8), static_cast<const uint8_t*>(up_sc), experts, inter,
+      hidden, static_cast<uint8_t*>(w13_fp8), static_cast<uint8_t*>(w13_sc));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_weighted_combine(const void* combine_bf16, const float* router_weights,
+                                    const void* y_shared_bf16, int64_t tokens, int topk,
+                                    int64_t hidden, void* out_bf16, cudaStream_t stream) {
+  if (tokens == 0) return cudaSuccess;
+  weighted_combine_kernel<<<grid_for(tokens * (hidden >> 3)), kThreads, 0, stream>>>(
+      static_cast<const uint4*>(combine_bf16), router_weights,
+      static_cast<const uint4*>(y_shared_bf16), tokens, topk, hidden,
+      static_cast<uint4*>(out_bf16));
+  return cudaGetLastError();
+}
+
+}  // namespace plb

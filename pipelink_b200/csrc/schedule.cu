@@ -1,0 +1,152 @@
+// Routing schedule: turns the all-gathered top-k expert ids of every rank into the
+// padded, expert-sorted row list one rank's grouped GEMMs run over. It stands in for
+// the reference's host-launched ops.schedule_out (campaigns/mok/host/mok_port_host.py:59-69),
+// whose outputs are peer_rank / peer_token_idx / num_tokens / tokens_per_expert
+// (compared bitwise there, :356-363) with every expert segment padded to
+// EXPERT_PADDING rows and padding rows marked peer_rank = -1 (:93-96).
+//
+// Row order inside an expert segment is ascending (source rank, token, slot), i.e.
+// ascending position in the gathered routes array. Three launches, no atomics on
+// global memory, so the result is a pure function of the routes:
+//   count : per 1024-entry chunk, per local expert, how many entries route to it
+//   scan  : per expert exclusive scan over chunks, padded segment offsets,
+//           block -> expert map, totals
+//   fill  : per chunk, thread e walks the chunk in order and emits its rows
+#include "kernels.h"
+
+namespace plb {
+
+namespace {
+
+__global__ void schedule_count_kernel(const int* __restrict__ routes, int64_t entries,
+                                      int expert_base, int num_local_experts,
+                                      int* __restrict__ chunk_counts) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int64_t begin = static_cast<int64_t>(blockIdx.x) * kScheduleChunk;
+  for (int i = threadIdx.x; i < kScheduleChunk; i += blockDim.x) {
+    const int64_t idx = begin + i;
+    if (idx < entries) {
+      const int e = routes[idx] - expert_base;
+      if (e >= 0 && e < num_local_experts) atomicAdd(&hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x)
+    chunk_counts[static_cast<int64_t>(blockIdx.x) * num_local_experts + e] = hist[e];
+}
+
+__global__ void schedule_scan_kernel(ScheduleArgs a, int chunks) {
+  extern __shared__ int padded[];  // [num_local_experts + 1]
+  const int E = a.num_local_experts;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int running = 0;
+    for (int c = 0; c < chunks; ++c) {
+      const int64_t at = static_cast<int64_t>(c) * E + e;
+      const int n = a.scratch[at];
+      a.scratch[at] = running;
+      running += n;
+    }
+    a.tokens_per_expert[e] = running;
+    padded[e] = (running + a.padding - 1) / a.padding * a.padding;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int64_t off = 0;
+    for (int e = 0; e < E; ++e) {
+      const int n = padded[e];
+      padded[e] = static_cast<int>(off);
+      off += n;
+    }
+    if (off > a.capacity) {
+      report_failure(a.status, ST_BAD_ARGUMENT, 100, static_cast<unsigned>(off),
+                     static_cast<unsigned>(a.capacity));
+      // leave an empty schedule behind so downstream stages do nothing
+      for (int e = 0; e <= E; ++e) padded[e] = 0;
+      off = 0;
+    }
+    padded[E] = static_cast<int>(off);
+    *a.num_tokens = static_cast<int>(off);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) a.expert_offsets[e] = padded[e];
+  const int blocks = a.capacity >> 7;
+  for (int b = threadIdx.x; b < blocks; b += blockDim.x) {
+    const int row = b << 7;
+    int owner = -1;
+    if (row < padded[E]) {
+      int lo = 0, hi = E;  // last e with padded[e] <= row
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (padded[mid] <= row) lo = mid; else hi = mid;
+      }
+      owner = lo;
+    }
+    a.block_expert[b] = owner;
+  }
+}
+
+__global__ void schedule_fill_kernel(ScheduleArgs a, int64_t entries) {
+  __shared__ int ids[kScheduleChunk];
+  const int64_t begin = static_cast<int64_t>(blockIdx.x) * kScheduleChunk;
+  for (int i = threadIdx.x; i < kScheduleChunk; i += blockDim.x) {
+    const int64_t idx = begin + i;
+    ids[i] = idx < entries ? a.routes[idx] - a.expert_base : -1;
+  }
+  __syncthreads();
+  const int E = a.num_local_experts;
+  const int total = a.expert_offsets[E];
+  const int64_t per_rank = static_cast<int64_t>(a.tokens) * a.topk;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int seg = a.expert_offsets[e];
+    if (total == 0) continue;
+    int pos = seg + a.scratch[static_cast<int64_t>(blockIdx.x) * E + e];
+    for (int i = 0; i < kScheduleChunk; ++i) {
+      if (ids[i] == e) {
+        const int64_t idx = begin + i;
+        const int src = static_cast<int>(idx / per_rank);
+        const int rem = static_cast<int>(idx - src * per_rank);
+        a.peer_rank[pos] = src;
+        a.peer_token_idx[pos] = rem / a.topk;
+        a.dest_row[pos] = rem;
+        ++pos;
+      }
+    }
+    if (blockIdx.x == 0) {
+      const int live_end = seg + a.tokens_per_expert[e];
+      const int seg_end = a.expert_offsets[e + 1];
+      for (int p = live_end; p < seg_end; ++p) {
+        a.peer_rank[p] = -1;
+        a.peer_token_idx[p] = 0;
+        a.dest_row[p] = -1;
+      }
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_schedule(const ScheduleArgs& a, cudaStream_t stream) {
+  const int64_t entries = static_cast<int64_t>(a.world) * a.tokens * a.topk;
+  const int chunks = static_cast<int>((entries + kScheduleChunk - 1) / kScheduleChunk);
+  const int E = a.num_local_experts;
+  int threads = ((E + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  if (chunks > 0) {
+    schedule_count_kernel<<<chunks, 256, E * sizeof(int), stream>>>(a.routes, entries,
+                                                                    a.expert_base, E, a.scratch);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+  }
+  schedule_scan_kernel<<<1, 1024, (E + 1) * sizeof(int), stream>>>(a, chunks);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  if (chunks > 0) {
+    schedule_fill_kernel<<<chunks, threads, 0, stream>>>(a, entries);
+    err = cudaGetLastError();
+  }
+  return err;
+}
+
+}  // namespace plb

@@ -1,0 +1,264 @@
+"""Host side of the MXFP8 MoE forward path (single rank or one rank of an expert-parallel group).
+
+Mirrors the reference's session object ``MoKHost`` (campaigns/mok/host/mok_port_host.py:72-239):
+same ``Shape`` / ``Inputs`` records, the same step order for ``forward`` (schedule -> dispatch ->
+gate/up GEMM + SwiGLU -> down GEMM + combine placement -> weighted epilogue), the same names for
+the forward-context tensors it returns, and ``ops.mxfp8_quantize`` for weights. All device work
+goes through the C ABI in ``include/pipelink_b200.h``; torch only owns the memory and the stream.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+EXPERT_PADDING = 128  # rows; one grouped-GEMM tile (the reference pads to its 256-row tile)
+
+
+@dataclass(frozen=True)
+class Shape:
+    name: str
+    experts: int
+    hidden: int
+    intermediate: int
+    topk: int
+    tokens: int
+
+
+SANITY = Shape("sanity", 4, 256, 256, 1, 512)
+CONFIG2 = Shape("moe-ffn-fwd", 64, 4096, 2048, 8, 16384)
+
+
+@dataclass(frozen=True)
+class Inputs:
+    x: torch.Tensor        # bf16 [tokens, hidden]
+    experts: torch.Tensor  # int [tokens, topk]
+    router: torch.Tensor   # fp32 [tokens, topk]
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def schedule_capacity(tokens_total: int, num_local_experts: int, padding: int = EXPERT_PADDING) -> int:
+    """Rows that always suffice: every routed row plus worst-case padding, rounded to 128."""
+    need = tokens_total + num_local_experts * (padding - 1)
+    return (need + 127) // 128 * 128
+
+
+def mxfp8_quantize(t: torch.Tensor, normal: bool = True, transposed: bool = False):
+    """``ops.mxfp8_quantize(tensor, normal, transposed)`` (mok_port_host.py:122).
+
+    ``t`` is bf16 ``[..., rows, cols]`` on the device; leading dims are folded into rows.
+    Returns ``(fp8, sc, fp8_t, sc_t)`` with ``None`` for the orientation not requested; fp8
+    tensors are uint8, scales are uint8 ``[rows/128, cols/128, 32, 16]``.
+    """
+    if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous():
+        raise ValueError("mxfp8_quantize wants a contiguous CUDA bf16 tensor")
+    cols = t.shape[-1]
+    rows = t.numel() // cols
+    if rows % 128 or cols % 128:
+        raise ValueError("rows and cols must be multiples of 128")
+    dev = t.device
+    q = sc = qt = sct = None
+    if normal:
+        q = torch.empty(t.shape, dtype=torch.uint8, device=dev)
+        sc = torch.empty((rows // 128, cols // 128, 32, 16), dtype=torch.uint8, device=dev)
+    if transposed:
+        if t.dim() != 2:
+            raise ValueError("the transposed orientation is defined for 2-D tensors")
+        qt = torch.empty((cols, rows), dtype=torch.uint8, device=dev)
+        sct = torch.empty((cols // 128, rows // 128, 32, 16), dtype=torch.uint8, device=dev)
+    _lib.call("plb_mxfp8_quantize", t.data_ptr(), rows, cols, _ptr(q), _ptr(sc), _ptr(qt),
+              _ptr(sct), _stream())
+    return q, sc, qt, sct
+
+
+def mxfp8_dequantize(q: torch.Tensor, sc: torch.Tensor) -> torch.Tensor:
+    cols = q.shape[-1]
+    rows = q.numel() // cols
+    out = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    _lib.call("plb_mxfp8_dequantize", q.data_ptr(), sc.data_ptr(), rows, cols, out.data_ptr(),
+              _stream())
+    return out
+
+
+class DeviceStatus:
+    """The 32-byte status record the kernels write on a bounded-wait failure."""
+
+    def __init__(self, device):
+        self.buf = torch.zeros(8, dtype=torch.int32, device=device)
+
+    def reset(self):
+        self.buf.zero_()
+
+    def check(self, where: str = ""):
+        """Synchronises, then raises if a kernel recorded a failure."""
+        vals = self.buf.cpu().tolist()
+        if vals[0] != 0:
+            name = _lib.STATUS_NAMES.get(vals[0], "unknown")
+            raise RuntimeError(f"device status {vals[0]} ({name}) {where}: cta={vals[1]} what={vals[2]} "
+                               f"observed={vals[3] & 0xFFFFFFFF} expected={vals[4] & 0xFFFFFFFF}")
+
+
+class Schedule:
+    """Device arrays written by ``plb_moe_schedule`` (fields of upstream's schedule object)."""
+
+    def __init__(self, world, tokens, topk, num_local_experts, capacity, device):
+        i32 = dict(dtype=torch.int32, device=device)
+        self.capacity = capacity
+        self.peer_rank = torch.empty(capacity, **i32)
+        self.peer_token_idx = torch.empty(capacity, **i32)
+        self.dest_row = torch.empty(capacity, **i32)
+        self.num_tokens = torch.zeros(1, **i32)
+        self.tokens_per_expert = torch.zeros(num_local_experts, **i32)
+        self.expert_offsets = torch.zeros(num_local_experts + 1, **i32)
+        self.block_expert = torch.empty(capacity // 128, **i32)
+        nbytes = _lib.load().plb_moe_schedule_scratch_bytes(world, tokens, topk, num_local_experts)
+        self.scratch = torch.empty(max(nbytes, 4) // 4, **i32)
+
+
+class MoKHost:
+    """One rank's persistent forward session."""
+
+    def __init__(self, shape: Shape, *, device="cuda", rank: int = 0, world: int = 1,
+                 padding: int = EXPERT_PADDING, capacity: int | None = None):
+        if shape.experts % world:
+            raise ValueError("shape/process group disagrees: experts % world != 0")
+        _lib.load()
+        self.shape, self.rank, self.world, self.padding = shape, rank, world, padding
+        self.device = torch.device(device)
+        E = shape.experts // world
+        L, H, I, k = shape.tokens, shape.hidden, shape.intermediate, shape.topk
+        self.num_local_experts = E
+        self.capacity = capacity or schedule_capacity(world * L * k, E, padding)
+        P = self.capacity
+        u8 = dict(dtype=torch.uint8, device=self.device)
+        self.status = DeviceStatus(self.device)
+        self.schedule = Schedule(world, L, k, E, P, self.device)
+        self.routes_i32 = torch.empty((world, L, k), dtype=torch.int32, device=self.device)
+        self.x_buffer = torch.empty((L, H), dtype=torch.bfloat16, device=self.device)
+        self.router_weight_buffer = torch.empty((L, k), dtype=torch.float32, device=self.device)
+        self.x_peers = torch.tensor([self.x_buffer.data_ptr()] * world, dtype=torch.int64,
+                                    device=self.device)
+        self.buffers = {
+            "x_routed_fp8": torch.empty((P, H), **u8),
+            "x_routed_sc": torch.empty((P // 128, H // 128, 32, 16), **u8),
+            "hidden_routed_fp8": torch.empty((P, I), **u8),
+            "hidden_routed_sc": torch.empty((P // 128, I // 128, 32, 16), **u8),
+            "combine_buffer": torch.empty((L * k, H), dtype=torch.bfloat16, device=self.device),
+            "output": torch.empty((L, H), dtype=torch.bfloat16, device=self.device),
+        }
+        self.weights = None
+
+    # ------------------------------------------------------------------ weights
+    def load_weights(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                     keep_unpacked: bool = True):
+        """bf16 [E, I, H], [E, I, H], [E, H, I] for this rank's experts."""
+        E, I, H = self.num_local_experts, self.shape.intermediate, self.shape.hidden
+        if tuple(w_gate.shape) != (E, I, H) or tuple(w_up.shape) != (E, I, H) or tuple(w_down.shape) != (E, H, I):
+            raise ValueError("weight shapes disagree with the session shape")
+        gq, gsc, _, _ = mxfp8_quantize(w_gate.contiguous())
+        uq, usc, _, _ = mxfp8_quantize(w_up.contiguous())
+        dq, dsc, _, _ = mxfp8_quantize(w_down.contiguous())
+        self.load_quantized_weights(gq, gsc, uq, usc, dq, dsc, keep_unpacked=keep_unpacked)
+
+    def load_quantized_weights(self, gq, gsc, uq, usc, dq, dsc, keep_unpacked: bool = True):
+        E, I, H = self.num_local_experts, self.shape.intermediate, self.shape.hidden
+        w13 = torch.empty((E, 2 * I, H), dtype=torch.uint8, device=self.device)
+        w13_sc = torch.empty((E * 2 * I // 128, H // 128, 32, 16), dtype=torch.uint8, device=self.device)
+        _lib.call("plb_moe_pack_gate_up", gq.data_ptr(), gsc.data_ptr(), uq.data_ptr(), usc.data_ptr(),
+                  E, I, H, w13.data_ptr(), w13_sc.data_ptr(), _stream())
+        torch.cuda.current_stream().synchronize()
+        self.weights = dict(w13_fp8=w13, w13_sc=w13_sc, w_routed_down_fp8=dq, w_routed_down_sc=dsc)
+        if keep_unpacked:
+            self.weights.update(w_routed_gate_fp8=gq, w_routed_gate_sc=gsc, w_routed_up_fp8=uq,
+                                w_routed_up_sc=usc)
+
+    # ------------------------------------------------------------------ steps
+    def schedule_into(self, routes_all_ranks: torch.Tensor):
+        """routes: int [world, tokens, topk] (already gathered over the group)."""
+        s, sh = self.schedule, self.shape
+        self.routes_i32.copy_(routes_all_ranks.reshape(self.routes_i32.shape))
+        _lib.call("plb_moe_schedule", self.routes_i32.data_ptr(), self.world, sh.tokens, sh.topk,
+                  self.rank * self.num_local_experts, self.num_local_experts, self.capacity,
+                  self.padding, s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
+                  s.dest_row.data_ptr(), s.num_tokens.data_ptr(), s.tokens_per_expert.data_ptr(),
+                  s.expert_offsets.data_ptr(), s.block_expert.data_ptr(), s.scratch.data_ptr(),
+                  s.scratch.numel() * 4, self.status.buf.data_ptr(), _stream())
+        return s
+
+    def dispatch(self):
+        s, b, sh = self.schedule, self.buffers, self.shape
+        _lib.call("plb_moe_dispatch", self.x_peers.data_ptr(), s.peer_rank.data_ptr(),
+                  s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(), self.capacity, sh.hidden,
+                  b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(), _stream())
+
+    def gemm_gate_up(self):
+        s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        _lib.call("plb_moe_gemm_gate_up", b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
+                  w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(), s.block_expert.data_ptr(),
+                  s.num_tokens.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate,
+                  sh.hidden, b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(),
+                  self.status.buf.data_ptr(), _stream())
+
+    def gemm_down(self):
+        s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        _lib.call("plb_moe_gemm_down", b["hidden_routed_fp8"].data_ptr(),
+                  b["hidden_routed_sc"].data_ptr(), w["w_routed_down_fp8"].data_ptr(),
+                  w["w_routed_down_sc"].data_ptr(), s.block_expert.data_ptr(),
+                  s.num_tokens.data_ptr(), s.dest_row.data_ptr(), self.capacity,
+                  self.num_local_experts, sh.intermediate, sh.hidden,
+                  b["combine_buffer"].data_ptr(), self.status.buf.data_ptr(), _stream())
+
+    def fwd_epilogue(self, y_shared=None):
+        b, sh = self.buffers, self.shape
+        _lib.call("plb_moe_fwd_epilogue", _ptr(y_shared), b["combine_buffer"].data_ptr(),
+                  self.router_weight_buffer.data_ptr(), sh.tokens, sh.topk, sh.hidden,
+                  b["output"].data_ptr(), _stream())
+        return b["output"]
+
+    def megakernel(self):
+        """The device part between the barriers of the reference's forward (mok_port_host.py:203)."""
+        self.dispatch()
+        self.gemm_gate_up()
+        self.gemm_down()
+
+    def forward(self, inputs: Inputs, *, check: bool = True):
+        """Single-rank forward: every token of ``inputs`` is local and every expert is local."""
+        if self.world != 1:
+            raise ValueError("forward() drives one rank; use pipelink_b200.ep for a group")
+        if self.weights is None:
+            raise RuntimeError("load_weights() first")
+        self.status.reset()
+        self.schedule_into(inputs.experts[None])
+        self.x_buffer.copy_(inputs.x)
+        self.router_weight_buffer.copy_(inputs.router)
+        self.megakernel()
+        out = self.fwd_epilogue()
+        if check:
+            self.status.check("after MoE forward")
+        return {"output": out, **self.context_tensors()}
+
+    def context_tensors(self):
+        b = self.buffers
+        return {"x_routed_data": b["x_routed_fp8"], "x_routed_scale": b["x_routed_sc"],
+                "hidden_routed_data": b["hidden_routed_fp8"], "hidden_routed_scale": b["hidden_routed_sc"],
+                "combine_buffer": b["combine_buffer"]}
+
+    @staticmethod
+    def new_inputs(shape: Shape, generation: int, device, rank: int = 0, world: int = 1) -> Inputs:
+        """Seeded inputs with the reference harness's recipe (mok_port_host.py:273-282)."""
+        gen = torch.Generator(device=device).manual_seed(1234 + rank + generation * world)
+        logits = torch.randn(shape.tokens, shape.experts, generator=gen, device=device)
+        values, experts = torch.topk(logits, shape.topk, dim=1)
+        if generation % 3 == 0:
+            experts.copy_(torch.arange(shape.topk, device=device).expand(shape.tokens, -1))
+        x = torch.randn(shape.tokens, shape.hidden, generator=gen, device=device, dtype=torch.bfloat16)
+        return Inputs(x, experts, torch.softmax(values.float(), dim=-1))
