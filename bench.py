@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""Headline benchmark: MXFP8 MoE FFN forward (BASELINE.json configs[1]) on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 20 --warmup 3
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference        # the CPU port of the reference path, host cores
+
+A step is one forward pass over one synthetic batch: routing schedule -> dispatch (gather +
+MXFP8 quantise) -> gate/up grouped GEMM with fused SwiGLU + requantise -> down grouped GEMM with
+combine placement -> weighted top-k epilogue. Weights are quantised once before timing (as the
+reference does at session start). Work counted: 6*T*k*H*I FLOP per step (padding rows excluded).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "mxfp8_moe_ffn_fwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--tokens", type=int, default=None, help="tokens per rank (default: config)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference path on the host cores, on a bounded sample
+# ---------------------------------------------------------------------------------------------
+def cpu_sample(hidden, inter, steps=1, warmup=0):
+    """Forward of a bounded sample (8 experts, 2048 tokens x top-8 => 16384 rows) on the host."""
+    import numpy as np
+    import torch
+
+    from oracle import moe as omoe
+    from oracle import mxfp8 as omx
+    from oracle import routing as oroute
+
+    E, T, k = 8, 2048, 8
+    rng = np.random.default_rng(0)
+    w = [omx.bf16_round(rng.standard_normal(s, dtype=np.float32) * np.float32(0.02))
+         for s in ((E, inter, hidden), (E, inter, hidden), (E, hidden, inter))]
+    weights = omoe.quantize_weights(*w)
+    x = omx.bf16_round(rng.standard_normal((T, hidden), dtype=np.float32))
+    ids, rw = oroute.route_topk(rng.standard_normal((T, E), dtype=np.float32), k)
+    flop = 6.0 * T * k * hidden * inter
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        omoe.forward_single_rank(x, ids, rw, weights)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return dict(value=flop / sec / 1e12, unit=UNIT, cores=torch.get_num_threads(), kind="port",
+                sample=f"{E} experts x {T} tokens x top-{k} ({T * k} rows) at H={hidden}, I={inter}; "
+                       f"{sec:.2f} s per pass; oracle port (numpy quantise + torch fp32 matmul)"), sec
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from pipelink_b200 import mok
+    shape = mok.CONFIG2
+    base, sec = cpu_sample(shape.hidden, shape.intermediate, steps=max(1, min(args.steps, 3)),
+                           warmup=min(args.warmup, 1))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU port of the e4m3/ue8m0 path)",
+            "data": "synthetic", "config": {"workload": shape.name, "sample": base["sample"]},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# native arm
+# ---------------------------------------------------------------------------------------------
+def run_native(args):
+    import torch
+    import torch.distributed as dist
+
+    from pipelink_b200 import mok
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    pk = peaks()
+    base = mok.CONFIG2
+    if world == 1:
+        shape = base if args.tokens is None else mok.Shape(base.name, base.experts, base.hidden,
+                                                           base.intermediate, base.topk, args.tokens)
+        session = SingleRank(shape, dev)
+    else:
+        from pipelink_b200 import ep
+        tokens = args.tokens or 8192
+        shape = mok.Shape("moe-ffn-fwd-ep", base.experts, base.hidden, base.intermediate, base.topk, tokens)
+        session = ep.BenchSession(shape, dev, rank, world)
+
+    flop_per_rank = 6.0 * shape.tokens * shape.topk * shape.hidden * shape.intermediate
+    for _ in range(max(args.warmup, 3)):
+        session.step()
+    session.check()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    session.kernel_events = []
+    ev[0].record()
+    for _ in range(args.steps):
+        session.step(record=True)
+    ev[1].record()
+    torch.cuda.synchronize()
+    ms_local = ev[0].elapsed_time(ev[1])
+    t = torch.tensor([ms_local], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    session.check()
+
+    ms_step = ms_total / args.steps
+    value = flop_per_rank * world / (ms_step * 1e-3) / 1e12
+
+    # dominant kernel: the fused gate/up GEMM (2/3 of the FLOPs)
+    k_ms = statistics.mean(a.elapsed_time(b) for a, b in session.kernel_events) if session.kernel_events else None
+    fp8_peak = 2.0 * pk["bf16_sustained"]
+    roof = None
+    if k_ms:
+        achieved = (4.0 * shape.tokens * shape.topk * shape.hidden * shape.intermediate) / (k_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": "grouped_gemm_kernel<0> (gate/up + SwiGLU + requantise)",
+                "achieved": achieved, "peak": fp8_peak, "unit": UNIT, "frac": achieved / fp8_peak,
+                "traffic": session.traffic_per_launch(),
+                "peak_source": f"2 x bf16_tflops_sustained of {pk['source']} peaks (dense FP8 = 2 x bf16 rate; "
+                               "the peaks file holds no FP8 figure)",
+                "ms_per_launch": k_ms}
+
+    e2e = None
+    if not args.no_e2e:
+        e2e_ms, h2d, d2h = session.e2e(max(3, min(args.steps, 10)))
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e = {"value": flop_per_rank * world / (float(t.item()) * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": float(t.item())}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu, _ = cpu_sample(shape.hidden, shape.intermediate)
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 (ue8m0 block scales), bf16 out",
+                "data": "synthetic",
+                "config": {"workload": shape.name, "tokens_per_rank": shape.tokens, "hidden": shape.hidden,
+                           "experts": shape.experts, "topk": shape.topk, "intermediate": shape.intermediate,
+                           "l2": "inputs larger than L2 (weights 1.5 GB, activations > 1 GB per step)",
+                           "expert_padding": mok.EXPERT_PADDING},
+                "clocks": clocks, "e2e": e2e, "gpu_launches": session.launches_per_step * args.steps,
+                "roofline": roof, "cpu_baseline": cpu,
+                "frac_of_fp8_peak_whole_step": value / world / fp8_peak}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+class SingleRank:
+    """configs[1]: every token and every expert on one GPU."""
+
+    launches_per_step = 7  # schedule x3, dispatch, gate/up GEMM, down GEMM, epilogue
+
+    def __init__(self, shape, dev):
+        import torch
+
+        from pipelink_b200 import mok
+        self.torch, self.mok, self.shape, self.dev = torch, mok, shape, dev
+        torch.manual_seed(0)
+        E, H, I = shape.experts, shape.hidden, shape.intermediate
+        self.host = mok.MoKHost(shape, device=dev)
+        # quantise expert weights in slices to bound the bf16 staging memory
+        q = {}
+        for name, rows, cols in (("gate", I, H), ("up", I, H), ("down", H, I)):
+            fp8 = torch.empty((E, rows, cols), dtype=torch.uint8, device=dev)
+            sc = torch.empty((E * rows // 128, cols // 128, 32, 16), dtype=torch.uint8, device=dev)
+            for e in range(E):
+                w = (torch.randn(rows, cols, device=dev) * 0.02).to(torch.bfloat16)
+                a, b, _, _ = mok.mxfp8_quantize(w)
+                fp8[e].copy_(a)
+                sc[e * rows // 128:(e + 1) * rows // 128].copy_(b)
+            q[name] = (fp8, sc)
+        self.host.load_quantized_weights(*q["gate"], *q["up"], *q["down"], keep_unpacked=False)
+        del q
+        logits = torch.randn(shape.tokens, E, device=dev)
+        values, experts = torch.topk(logits, shape.topk, dim=1)
+        self.inputs = mok.Inputs((torch.randn(shape.tokens, H, device=dev)).to(torch.bfloat16), experts,
+                                 torch.softmax(values.float(), dim=-1))
+        self.routes = experts.to(torch.int32)[None].contiguous()
+        self.host.x_buffer.copy_(self.inputs.x)
+        self.host.router_weight_buffer.copy_(self.inputs.router)
+        self.kernel_events = []
+        # pinned host copies for the end-to-end leg
+        self.h_x = self.inputs.x.cpu().pin_memory()
+        self.h_routes = self.routes.cpu().pin_memory()
+        self.h_router = self.inputs.router.cpu().pin_memory()
+        self.h_out = torch.empty((shape.tokens, H), dtype=torch.bfloat16).pin_memory()
+        torch.cuda.synchronize()
+
+    def step(self, record=False):
+        h, torch = self.host, self.torch
+        h.schedule_into(self.routes)
+        h.dispatch()
+        if record:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            h.gemm_gate_up()
+            b.record()
+            self.kernel_events.append((a, b))
+        else:
+            h.gemm_gate_up()
+        h.gemm_down()
+        h.fwd_epilogue()
+
+    def check(self):
+        self.host.status.check("bench")
+
+    def traffic_per_launch(self):
+        return None  # filled from the ncu capture recorded under profiles/
+
+    def e2e(self, steps):
+        """Host buffers in, host buffer out, through the public session API."""
+        torch, h = self.torch, self.host
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            h.x_buffer.copy_(self.h_x, non_blocking=True)
+            h.routes_i32.copy_(self.h_routes, non_blocking=True)
+            h.router_weight_buffer.copy_(self.h_router, non_blocking=True)
+            h.schedule_into(h.routes_i32)
+            h.megakernel()
+            out = h.fwd_epilogue()
+            self.h_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        b.record()
+        torch.cuda.synchronize()
+        h2d = self.h_x.numel() * 2 + self.h_routes.numel() * 4 + self.h_router.numel() * 4
+        return a.elapsed_time(b) / steps, h2d, self.h_out.numel() * 2
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()
