@@ -86,6 +86,31 @@ int plb_moe_schedule(const int32_t* routes, int world, int tokens, int topk, int
                      int32_t* tokens_per_expert, int32_t* expert_offsets, int32_t* block_expert,
                      void* scratch, size_t scratch_bytes, plb_status* status, void* stream);
 
+/* The same schedule for callers that cannot provide scratch memory and cannot call
+ * cudaMalloc themselves: a plugin that is handed only input and output pointers, a
+ * stage built behind a broker that owns every workspace (the provider ABI gives a
+ * stage no allocator), or a serving loop where an allocation would stall the whole
+ * device. It has no counterpart in the reference. The chunk counts live in a 1 MiB
+ * static device array inside the library (held by every GPU that loads the library
+ * until the process exits), so:
+ *   - problems whose plb_moe_schedule_scratch_bytes() exceeds
+ *     plb_moe_schedule_noalloc_max_scratch_bytes() are refused with PLB_E_CAPACITY;
+ *   - the first call on each device looks up the array's device address (no
+ *     allocation); make that first call outside any stream capture;
+ *   - all calls on a device share the array: two calls whose kernels can overlap on
+ *     the GPU (different streams) race. Calls ordered on one stream are safe, and
+ *     nothing in the array needs clearing between calls, because every count a call
+ *     reads is first written by that call.
+ * It never calls cudaMalloc, cudaFree or any allocating routine. Results are
+ * identical to plb_moe_schedule. */
+size_t plb_moe_schedule_noalloc_max_scratch_bytes(void);
+int plb_moe_schedule_noalloc(const int32_t* routes, int world, int tokens, int topk,
+                             int expert_base, int num_local_experts, int capacity, int padding,
+                             int32_t* peer_rank, int32_t* peer_token_idx, int32_t* dest_row,
+                             int32_t* num_tokens, int32_t* tokens_per_expert,
+                             int32_t* expert_offsets, int32_t* block_expert, plb_status* status,
+                             void* stream);
+
 /* ------------------------------------------------------------------ MoE dispatch
  * dispatch_kernel (campaigns/mok/port/comm/comm.cu:105-123): for every scheduled row p,
  * x_routed[p] = quantise(x_peers[peer_rank[p]][peer_token_idx[p]]); padding rows become

@@ -30,6 +30,10 @@ PROTOTYPES = {
     "plb_moe_schedule": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "plb_moe_schedule_noalloc_max_scratch_bytes": (c_size_t, []),
+    "plb_moe_schedule_noalloc": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_void_p]),
     "plb_moe_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                  c_void_p, c_void_p, c_void_p]),
     "plb_moe_pack_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,

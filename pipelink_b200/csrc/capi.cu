@@ -114,6 +114,47 @@ int plb_moe_schedule(const int32_t* routes, int world, int tokens, int topk, int
   return from_cuda(plb::launch_schedule(a, static_cast<cudaStream_t>(stream)));
 }
 
+size_t plb_moe_schedule_noalloc_max_scratch_bytes(void) {
+  return static_cast<size_t>(plb::schedule_static_scratch_ints()) * sizeof(int);
+}
+
+int plb_moe_schedule_noalloc(const int32_t* routes, int world, int tokens, int topk,
+                             int expert_base, int num_local_experts, int capacity, int padding,
+                             int32_t* peer_rank, int32_t* peer_token_idx, int32_t* dest_row,
+                             int32_t* num_tokens, int32_t* tokens_per_expert,
+                             int32_t* expert_offsets, int32_t* block_expert, plb_status* status,
+                             void* stream) {
+  if (world < 1 || tokens < 0 || topk < 1 || num_local_experts < 1 || num_local_experts > 8192)
+    return PLB_E_ARGUMENT;
+  if (capacity < 0 || capacity % 128 || padding < 128 || padding % 128) return PLB_E_ARGUMENT;
+  if (!routes || !peer_rank || !peer_token_idx || !dest_row || !num_tokens || !tokens_per_expert ||
+      !expert_offsets || !block_expert || !status)
+    return PLB_E_ARGUMENT;
+  // the built-in scratch has a fixed size: refuse anything that would not fit
+  if (plb_moe_schedule_scratch_bytes(world, tokens, topk, num_local_experts) >
+      plb_moe_schedule_noalloc_max_scratch_bytes())
+    return PLB_E_CAPACITY;
+  plb::ScheduleArgs a;
+  a.routes = routes;
+  a.world = world;
+  a.tokens = tokens;
+  a.topk = topk;
+  a.expert_base = expert_base;
+  a.num_local_experts = num_local_experts;
+  a.capacity = capacity;
+  a.padding = padding;
+  a.peer_rank = peer_rank;
+  a.peer_token_idx = peer_token_idx;
+  a.dest_row = dest_row;
+  a.num_tokens = num_tokens;
+  a.tokens_per_expert = tokens_per_expert;
+  a.expert_offsets = expert_offsets;
+  a.block_expert = block_expert;
+  a.scratch = nullptr;
+  a.status = reinterpret_cast<plb::Status*>(status);
+  return from_cuda(plb::launch_schedule_static(a, static_cast<cudaStream_t>(stream)));
+}
+
 int plb_moe_dispatch(const void* const* x_peers, const int32_t* peer_rank,
                      const int32_t* peer_token_idx, const int32_t* num_tokens, int64_t capacity,
                      int64_t hidden, void* x_routed_fp8, void* x_routed_sc, void* stream) {

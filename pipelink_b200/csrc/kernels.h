@@ -50,6 +50,11 @@ inline int64_t schedule_scratch_ints(int64_t entries, int num_local_experts) {
   return ((entries + kScheduleChunk - 1) / kScheduleChunk) * num_local_experts;
 }
 cudaError_t launch_schedule(const ScheduleArgs& a, cudaStream_t stream);
+// Same schedule with the chunk counts kept in a library-owned static device array
+// (a.scratch is ignored). cudaErrorInvalidValue if the problem needs more than
+// schedule_static_scratch_ints() ints.
+cudaError_t launch_schedule_static(const ScheduleArgs& a, cudaStream_t stream);
+int64_t schedule_static_scratch_ints();
 
 // ---- grouped MXFP8 GEMM (grouped_gemm.cu)
 struct GroupedGemmArgs {

@@ -125,7 +125,41 @@ __global__ void schedule_fill_kernel(ScheduleArgs a, int64_t entries) {
   }
 }
 
+// Scratch for launch_schedule_static: chunk counts for callers that hand over no
+// workspace. 1 MiB, resident on every device that loads this library until the
+// process exits. Its name is only a host-side handle here; the device address is
+// looked up once per device below.
+constexpr int64_t kStaticScratchInts = 262144;
+static __device__ __align__(256) int g_schedule_scratch[kStaticScratchInts];
+
+constexpr int kMaxDevices = 64;
+int* g_static_scratch_ptr[kMaxDevices] = {};
+
 }  // namespace
+
+int64_t schedule_static_scratch_ints() { return kStaticScratchInts; }
+
+cudaError_t launch_schedule_static(const ScheduleArgs& args, cudaStream_t stream) {
+  const int64_t entries = static_cast<int64_t>(args.world) * args.tokens * args.topk;
+  if (schedule_scratch_ints(entries, args.num_local_experts) > kStaticScratchInts)
+    return cudaErrorInvalidValue;
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    // one-time set-up for this device (it is the current device): resolve the
+    // device address of the array; host code must never pass the symbol itself
+    int* ptr = nullptr;
+    err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_schedule_scratch);
+    if (err != cudaSuccess) return err;
+    if (ptr == nullptr) return cudaErrorInvalidSymbol;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  ScheduleArgs a = args;
+  a.scratch = g_static_scratch_ptr[dev];
+  return launch_schedule(a, stream);
+}
 
 cudaError_t launch_schedule(const ScheduleArgs& a, cudaStream_t stream) {
   const int64_t entries = static_cast<int64_t>(a.world) * a.tokens * a.topk;
