@@ -145,6 +145,55 @@ int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void*
                       const int32_t* dest_row, int64_t capacity, int experts, int inter, int hidden,
                       void* combine_bf16, plb_status* status, void* stream);
 
+/* ------------------------------------------------------------------ expert parallelism
+ * One process per GPU; every rank owns tokens [tokens, hidden] and experts/world experts.
+ * Peer-visible buffers are plain device allocations shared through CUDA IPC; "*_peers"
+ * arguments are device arrays of `world` device pointers (entry `rank` = the local
+ * buffer), the counterpart of the provider ABI's peer_addresses[world]
+ * (pipec/src/pipec2/host/include/pipelink_host_abi_v2.h:162-180). */
+
+/* Set-up helpers (these DO allocate / map memory and synchronise; not for the hot loop).
+ * plb_sym_alloc: zero-filled device allocation that can be exported.
+ * plb_ipc_export / import: 64-byte cudaIpcMemHandle_t out / in; import enables peer access. */
+int plb_sym_alloc(size_t bytes, void** out);
+int plb_sym_free(void* p);
+int plb_ipc_export(void* p, void* handle64);
+int plb_ipc_import(const void* handle64, void** out);
+int plb_ipc_close(void* p);
+
+/* Flag barrier over the group, the stand-in for ops.barrier_all
+ * (campaigns/mok/host/mok_port_host.py:178-180): every rank adds 1 to flags[rank] on every
+ * peer (fence.acq_rel.sys + red.release.sys) and waits (ld.acquire.sys, bounded) until its
+ * own flags[i] reach the generation kept in state[0], which the kernel then advances.
+ * flags: u32 [world] per rank, zero at start, never reset. state: u32 [1] local, zero at start.
+ * All ranks must launch it in the same order; one CTA, so it cannot starve its peers. */
+int plb_ep_barrier(void* const* flags_peers, void* state, int rank, int world, plb_status* status,
+                   void* stream);
+
+/* ops.all_gather_top_experts (mok_port_host.py:59-62): copy `bytes` (multiple of 16) from src
+ * into slot `rank` of every peer's gather buffer (dst_peers[p] + rank * bytes). Follow with
+ * plb_ep_barrier before reading the gathered buffer. */
+int plb_ep_publish(const void* src, int64_t bytes, void* const* dst_peers, int rank, int world,
+                   void* stream);
+
+/* dispatch_kernel over NVLink (campaigns/mok/port/comm/comm.cu:105-123) on pre-quantised
+ * tokens: x_routed[p] = xq_peers[peer_rank[p]][peer_token_idx[p]] (E4M3 bytes and the row's
+ * scale words); padding rows become zeros. xq is u8 [tokens, hidden], xsc its
+ * [tokens/128, hidden/128, 32, 16] scales, both produced by plb_mxfp8_quantize at home. */
+int plb_ep_pull_rows(const void* const* xq_peers, const void* const* xsc_peers,
+                     const int32_t* peer_rank, const int32_t* peer_token_idx,
+                     const int32_t* num_tokens, int64_t capacity, int64_t hidden,
+                     void* x_routed_fp8, void* x_routed_sc, void* stream);
+
+/* plb_moe_gemm_down with the combine push (combine_kernel, comm.cu:124-129,327): row p is
+ * stored to combine_peers[peer_rank[p]][dest_row[p]] from the GEMM epilogue. */
+int plb_moe_gemm_down_push(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
+                           const void* w2_sc, const int32_t* block_expert,
+                           const int32_t* num_tokens, const int32_t* dest_row,
+                           const int32_t* peer_rank, int64_t capacity, int experts, int inter,
+                           int hidden, void* const* combine_peers, plb_status* status,
+                           void* stream);
+
 /* ops.fwd_epilogue (campaigns/mok/host/mok_port_host.py:204):
  * out[t] = y_shared[t] + sum_j router_weights[t, j] * combine[t * topk + j], j ascending,
  * fp32, every operation rounded separately. y_shared may be NULL. */

@@ -146,3 +146,37 @@ def error_stats(expected, actual):
     return dict(abs_mean=float(d.mean()), abs_max=float(d.max()),
                 relative=float(d.sum() / max(np.abs(e).sum(), 1e-300)),
                 rel_l2=float(np.sqrt((d * d).sum() / max((e * e).sum(), 1e-300))))
+
+
+def forward_multi_rank(xs, routes, router_ws, weights, world, padding=128):
+    """Expert-parallel forward: xs[r] fp32 [T, H], routes[r] i32 [T, k] (global expert ids),
+    router_ws[r] fp32 [T, k]; `weights` holds all experts, rank r owns a contiguous slice.
+    Returns per-rank outputs plus the per-rank schedules and combine buffers."""
+    from . import routing
+    T, k = routes[0].shape
+    E = weights["gate"][0].shape[0]
+    El = E // world
+    gathered = np.stack(routes).astype(np.int32)
+    combine_bufs = [np.zeros((T * k, xs[0].shape[1]), dtype=np.float32) for _ in range(world)]
+    scheds, hiddens = [], []
+    for r in range(world):
+        cap = ((world * T * k + El * (padding - 1)) + 127) // 128 * 128
+        sched = routing.build_schedule(gathered, r * El, El, cap, padding)
+        local = {}
+        for name in ("gate", "up", "down"):
+            q, sc = weights[name]
+            rows, cols = q.shape[1], q.shape[2]
+            sc_rg = mxfp8.unpack_scales(sc, E * rows, cols).reshape(E, rows, cols // 32)
+            local[name] = (q[r * El:(r + 1) * El],
+                           mxfp8.pack_scales(sc_rg[r * El:(r + 1) * El].reshape(El * rows, cols // 32)))
+        xq, xsc = dispatch(xs, sched)
+        hq, hsc, y = expert_ffn(xq, xsc, local, sched)
+        total = int(sched["num_tokens"][0])
+        pr, dr = sched["peer_rank"][:total], sched["dest_row"][:total]
+        for home in range(world):
+            sel = pr == home
+            combine_bufs[home][dr[sel]] = y[:total][sel]
+        scheds.append(sched)
+        hiddens.append((hq, hsc))
+    outs = [fwd_epilogue(combine_bufs[r], router_ws[r]) for r in range(world)]
+    return dict(outputs=outs, schedules=scheds, combine=combine_bufs, hidden=hiddens)

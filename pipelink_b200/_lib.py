@@ -44,6 +44,18 @@ PROTOTYPES = {
     "plb_moe_gemm_down": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_void_p]),
+    "plb_moe_gemm_down_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p,
+                                       c_void_p, c_void_p]),
+    "plb_ep_barrier": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "plb_ep_publish": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
+    "plb_ep_pull_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                 c_void_p, c_void_p, c_void_p]),
+    "plb_sym_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
+    "plb_sym_free": (c_int, [c_void_p]),
+    "plb_ipc_export": (c_int, [c_void_p, c_void_p]),
+    "plb_ipc_import": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "plb_ipc_close": (c_int, [c_void_p]),
     "plb_moe_fwd_epilogue": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64,
                                      c_void_p, c_void_p]),
 }

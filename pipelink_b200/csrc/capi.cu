@@ -2,6 +2,8 @@
 // Declarations and their reference counterparts are in include/pipelink_b200.h.
 #include "../../include/pipelink_b200.h"
 
+#include <string.h>
+
 #include "kernels.h"
 
 namespace {
@@ -214,10 +216,12 @@ int plb_moe_gemm_gate_up(const void* x_routed_fp8, const void* x_routed_sc, cons
   return from_cuda(plb::launch_grouped_gemm(a, static_cast<cudaStream_t>(stream)));
 }
 
-int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
-                      const void* w2_sc, const int32_t* block_expert, const int32_t* num_tokens,
-                      const int32_t* dest_row, int64_t capacity, int experts, int inter, int hidden,
-                      void* combine_bf16, plb_status* status, void* stream) {
+static int gemm_down_impl(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
+                          const void* w2_sc, const int32_t* block_expert,
+                          const int32_t* num_tokens, const int32_t* dest_row, int64_t capacity,
+                          int experts, int inter, int hidden, void* combine_bf16,
+                          void* const* combine_peers, const int32_t* peer_rank, plb_status* status,
+                          void* stream) {
   if (capacity < 0 || capacity % 128 || experts < 1 || inter < 128 || inter % 128 ||
       hidden < 128 || hidden % 128)
     return PLB_E_ARGUMENT;
@@ -242,11 +246,100 @@ int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void*
   a.out = combine_bf16;
   a.out_sc = nullptr;
   a.dest_row = dest_row;
+  a.out_peers = combine_peers;
+  a.peer_rank = peer_rank;
   a.num_sms = sm_count();
   a.status = reinterpret_cast<plb::Status*>(status);
   if (a.num_sms <= 0) return PLB_E_CUDA;
   return from_cuda(plb::launch_grouped_gemm(a, static_cast<cudaStream_t>(stream)));
 }
+
+int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
+                      const void* w2_sc, const int32_t* block_expert, const int32_t* num_tokens,
+                      const int32_t* dest_row, int64_t capacity, int experts, int inter, int hidden,
+                      void* combine_bf16, plb_status* status, void* stream) {
+  return gemm_down_impl(hidden_fp8, hidden_sc, w2_fp8, w2_sc, block_expert, num_tokens, dest_row,
+                        capacity, experts, inter, hidden, combine_bf16, nullptr, nullptr, status,
+                        stream);
+}
+
+int plb_moe_gemm_down_push(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
+                           const void* w2_sc, const int32_t* block_expert,
+                           const int32_t* num_tokens, const int32_t* dest_row,
+                           const int32_t* peer_rank, int64_t capacity, int experts, int inter,
+                           int hidden, void* const* combine_peers, plb_status* status,
+                           void* stream) {
+  if (!combine_peers || !peer_rank) return PLB_E_ARGUMENT;
+  // the local base is only a non-null placeholder; every row is addressed through the table
+  return gemm_down_impl(hidden_fp8, hidden_sc, w2_fp8, w2_sc, block_expert, num_tokens, dest_row,
+                        capacity, experts, inter, hidden, const_cast<void**>(combine_peers),
+                        combine_peers, peer_rank, status, stream);
+}
+
+int plb_ep_barrier(void* const* flags_peers, void* state, int rank, int world, plb_status* status,
+                   void* stream) {
+  if (!flags_peers || !state || !status || world < 1 || world > 32 || rank < 0 || rank >= world)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_ep_barrier(reinterpret_cast<unsigned* const*>(flags_peers),
+                                          static_cast<unsigned*>(state), rank, world,
+                                          reinterpret_cast<plb::Status*>(status),
+                                          static_cast<cudaStream_t>(stream)));
+}
+
+int plb_ep_publish(const void* src, int64_t bytes, void* const* dst_peers, int rank, int world,
+                   void* stream) {
+  if (!src || !dst_peers || bytes < 0 || bytes % 16 || !aligned16(src) || world < 1 || rank < 0 ||
+      rank >= world)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_ep_publish(src, bytes, dst_peers, rank, world,
+                                          static_cast<cudaStream_t>(stream)));
+}
+
+int plb_ep_pull_rows(const void* const* xq_peers, const void* const* xsc_peers,
+                     const int32_t* peer_rank, const int32_t* peer_token_idx,
+                     const int32_t* num_tokens, int64_t capacity, int64_t hidden,
+                     void* x_routed_fp8, void* x_routed_sc, void* stream) {
+  if (capacity < 0 || capacity % 128 || hidden <= 0 || hidden % 128) return PLB_E_ARGUMENT;
+  if (!xq_peers || !xsc_peers || !peer_rank || !peer_token_idx || !num_tokens || !x_routed_fp8 ||
+      !x_routed_sc)
+    return PLB_E_ARGUMENT;
+  if (!aligned16(x_routed_fp8) || !aligned16(x_routed_sc)) return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_ep_pull_rows(xq_peers, xsc_peers, peer_rank, peer_token_idx,
+                                            num_tokens, capacity, static_cast<int>(hidden),
+                                            x_routed_fp8, x_routed_sc,
+                                            static_cast<cudaStream_t>(stream)));
+}
+
+int plb_sym_alloc(size_t bytes, void** out) {
+  if (!out || bytes == 0) return PLB_E_ARGUMENT;
+  void* p = nullptr;
+  cudaError_t err = cudaMalloc(&p, bytes);
+  if (err != cudaSuccess) return from_cuda(err);
+  err = cudaMemset(p, 0, bytes);
+  if (err != cudaSuccess) {
+    cudaFree(p);
+    return from_cuda(err);
+  }
+  *out = p;
+  return PLB_OK;
+}
+
+int plb_sym_free(void* p) { return p ? from_cuda(cudaFree(p)) : PLB_OK; }
+
+int plb_ipc_export(void* p, void* handle64) {
+  if (!p || !handle64) return PLB_E_ARGUMENT;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  return from_cuda(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), p));
+}
+
+int plb_ipc_import(const void* handle64, void** out) {
+  if (!handle64 || !out) return PLB_E_ARGUMENT;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return from_cuda(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int plb_ipc_close(void* p) { return p ? from_cuda(cudaIpcCloseMemHandle(p)) : PLB_OK; }
 
 int plb_moe_fwd_epilogue(const void* y_shared_bf16, const void* combine_bf16,
                          const float* router_weights, int64_t tokens, int topk, int64_t hidden,

@@ -1,0 +1,168 @@
+// Expert-parallel plumbing over peer-mapped memory (NVLink / NVSwitch): symmetric
+// allocation export/import, a flag barrier whose waits are bounded, the routes
+// all-gather, and the dispatch pull of pre-quantised token rows.
+//
+// The reference exchanges token rows with comm CTAs that read peers' x_buffer and
+// write peers' combine_buffer (campaigns/mok/port/comm/comm.cu:105-129,326-335) and
+// brackets the kernel with barrier_all launches (campaigns/mok/host/mok_port_host.py:198-205).
+// Here every rank quantises its own tokens once, peers pull E4M3 rows plus their scale
+// words (half the NVLink bytes of pulling bf16, and bit-identical because MXFP8 blocks
+// run along the hidden dimension of a single row), and the combine push happens inside
+// the down GEMM's epilogue. No TMA touches peer memory: all peer traffic is plain
+// 16-byte loads and stores.
+//
+// Counter protocol (examples/comm-overlap/comm/push_gather.cuh:16-150): flags are never
+// reset; a launch generation kept in device memory gives each barrier its target value;
+// signal = fence.acq_rel.sys + red.release.sys.add; wait = ld.acquire.sys with a
+// wrap-safe signed compare and a cycle budget.
+#include "kernels.h"
+
+namespace plb {
+
+namespace {
+
+__device__ __forceinline__ void red_release_sys_add(unsigned* addr, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* addr) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_acq_rel_sys() {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+}
+
+// One CTA. Thread i < world signals peer i's flag[rank] and waits for its own flag[i].
+// state[0] is this rank's barrier generation (advanced by the kernel itself).
+__global__ void ep_barrier_kernel(unsigned* const* flags_peers, unsigned* state, int rank, int world,
+                                  Status* status) {
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  const unsigned target = state[0] + 1u;
+  const int i = threadIdx.x;
+  if (i < world) {
+    fence_acq_rel_sys();
+    red_release_sys_add(flags_peers[i] + rank, 1u);
+    const unsigned* mine = flags_peers[rank] + i;
+    const long long t0 = clock64();
+    for (unsigned it = 0;; ++it) {
+      const unsigned v = ld_acquire_sys(mine);
+      if (static_cast<int>(v - target) >= 0) break;
+      if ((it & 255u) == 255u) {
+        if (clock64() - t0 > kWaitBudgetCycles) {
+          report_failure(status, ST_TIMEOUT_COUNTER, 200 + i, v, target);
+          failed = 1;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // advance even after a failure so later barriers compare against fresh targets
+    state[0] = target;
+    __threadfence();
+  }
+}
+
+// dst_peers[p] + rank * count .. : this rank's slice of every peer's gather buffer.
+__global__ void ep_publish_kernel(const uint4* __restrict__ src, int64_t vecs,
+                                  uint4* const* dst_peers, int rank, int world) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int p = 0; p < world; ++p) {
+    uint4* dst = dst_peers[p] + static_cast<int64_t>(rank) * vecs;
+    for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs;
+         v += stride)
+      dst[v] = src[v];
+  }
+}
+
+// One warp per scheduled row: copy H bytes of E4M3 and H/128 scale words from the
+// owning rank's quantised token buffer into this rank's routed buffers.
+__global__ void __launch_bounds__(256)
+ep_pull_rows_kernel(const uint8_t* const* __restrict__ xq_peers,
+                    const uint8_t* const* __restrict__ xsc_peers, const int* __restrict__ peer_rank,
+                    const int* __restrict__ peer_token_idx, const int* __restrict__ num_rows_dev,
+                    int64_t capacity, int hidden, uint8_t* __restrict__ x_routed_fp8,
+                    uint8_t* __restrict__ x_routed_sc) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  int64_t rows = *num_rows_dev;
+  if (rows > capacity) rows = capacity;
+  const int vec_per_row = hidden >> 4;
+  const int col_blocks = hidden >> 7;
+  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < rows;
+       p += warps) {
+    const int src_rank = peer_rank[p];
+    uint4* dst = reinterpret_cast<uint4*>(x_routed_fp8 + p * hidden);
+    const size_t dst_sc_row = static_cast<size_t>(p >> 7) * col_blocks * 512 + (p & 31) * 16 +
+                              ((p & 127) >> 5) * 4;
+    if (src_rank < 0) {
+      for (int v = lane; v < vec_per_row; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+      for (int c = lane; c < col_blocks; c += 32)
+        *reinterpret_cast<uint32_t*>(x_routed_sc + dst_sc_row + static_cast<size_t>(c) * 512) = 0u;
+      continue;
+    }
+    const int64_t t = peer_token_idx[p];
+    const uint4* src = reinterpret_cast<const uint4*>(xq_peers[src_rank] + t * hidden);
+    const uint8_t* src_sc = xsc_peers[src_rank] + static_cast<size_t>(t >> 7) * col_blocks * 512 +
+                            (t & 31) * 16 + ((t & 127) >> 5) * 4;
+    // loads first, then stores, so several NVLink reads are in flight per lane
+    for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
+      uint4 tmp[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + u * 32 + lane;
+        if (v < vec_per_row) tmp[u] = src[v];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + u * 32 + lane;
+        if (v < vec_per_row) dst[v] = tmp[u];
+      }
+    }
+    for (int c = lane; c < col_blocks; c += 32) {
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(src_sc + static_cast<size_t>(c) * 512);
+      *reinterpret_cast<uint32_t*>(x_routed_sc + dst_sc_row + static_cast<size_t>(c) * 512) = w;
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_ep_barrier(unsigned* const* flags_peers, unsigned* state, int rank, int world,
+                              Status* status, cudaStream_t stream) {
+  ep_barrier_kernel<<<1, 32, 0, stream>>>(flags_peers, state, rank, world, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_publish(const void* src, int64_t bytes, void* const* dst_peers, int rank,
+                              int world, cudaStream_t stream) {
+  const int64_t vecs = bytes >> 4;
+  if (vecs == 0) return cudaSuccess;
+  int64_t blocks = (vecs + 255) / 256;
+  if (blocks > 64) blocks = 64;
+  ep_publish_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+      static_cast<const uint4*>(src), vecs, reinterpret_cast<uint4* const*>(dst_peers), rank, world);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_pull_rows(const void* const* xq_peers, const void* const* xsc_peers,
+                                const int* peer_rank, const int* peer_token_idx,
+                                const int* num_rows_dev, int64_t capacity, int hidden,
+                                void* x_routed_fp8, void* x_routed_sc, cudaStream_t stream) {
+  if (capacity == 0) return cudaSuccess;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  ep_pull_rows_kernel<<<sms * 8, 256, 0, stream>>>(
+      reinterpret_cast<const uint8_t* const*>(xq_peers),
+      reinterpret_cast<const uint8_t* const*>(xsc_peers), peer_rank, peer_token_idx, num_rows_dev,
+      capacity, hidden, static_cast<uint8_t*>(x_routed_fp8), static_cast<uint8_t*>(x_routed_sc));
+  return cudaGetLastError();
+}
+
+}  // namespace plb

@@ -67,6 +67,8 @@ struct KernelParams {
   uint8_t* out;
   uint8_t* out_sc;
   const int* dest_row;
+  uint8_t* const* out_peers;  // mode 1, optional: output base per source rank (peer-mapped)
+  const int* peer_rank;       // mode 1 with out_peers: which base row p goes to
   Status* status;
 };
 
@@ -270,6 +272,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         *reinterpret_cast<uint16_t*>(p.out_sc + off) = static_cast<uint16_t>(scale_pair);
       } else {
         const int dest = p.dest_row[row];
+        // combine push: the row goes to its home rank's buffer (plain stores over NVLink)
+        uint8_t* out_base = p.out;
+        if (p.out_peers != nullptr && dest >= 0) out_base = p.out_peers[p.peer_rank[row]];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
@@ -277,7 +282,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           tc_wait_ld();
           if (dest >= 0) {
             uint4* dst = reinterpret_cast<uint4*>(
-                p.out + (static_cast<size_t>(dest) * p.out_cols + n_blk * BN + c * 32) * 2);
+                out_base + (static_cast<size_t>(dest) * p.out_cols + n_blk * BN + c * 32) * 2);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               uint4 o;
@@ -366,6 +371,8 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
   p.out = static_cast<uint8_t*>(a.out);
   p.out_sc = static_cast<uint8_t*>(a.out_sc);
   p.dest_row = a.dest_row;
+  p.out_peers = reinterpret_cast<uint8_t* const*>(a.out_peers);
+  p.peer_rank = a.peer_rank;
   p.status = a.status;
   static bool attr_set[2] = {false, false};
   cudaError_t err;

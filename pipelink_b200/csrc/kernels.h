@@ -74,10 +74,22 @@ struct GroupedGemmArgs {
   void* out;
   void* out_sc;
   const int* dest_row;
+  void* const* out_peers = nullptr;  // mode 1: per-source-rank output bases (device array), or null
+  const int* peer_rank = nullptr;    // mode 1 with out_peers
   int num_sms;
   Status* status;
 };
 cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);
 int grouped_gemm_smem_bytes();
+
+// ---- expert-parallel plumbing (ep.cu)
+cudaError_t launch_ep_barrier(unsigned* const* flags_peers, unsigned* state, int rank, int world,
+                              Status* status, cudaStream_t stream);
+cudaError_t launch_ep_publish(const void* src, int64_t bytes, void* const* dst_peers, int rank,
+                              int world, cudaStream_t stream);
+cudaError_t launch_ep_pull_rows(const void* const* xq_peers, const void* const* xsc_peers,
+                                const int* peer_rank, const int* peer_token_idx,
+                                const int* num_rows_dev, int64_t capacity, int hidden,
+                                void* x_routed_fp8, void* x_routed_sc, cudaStream_t stream);
 
 }  // namespace plb

@@ -1,0 +1,304 @@
+"""Expert-parallel MXFP8 MoE forward: one rank per GPU, experts sharded, tokens stay home.
+
+Host-side counterpart of the reference's EP session (campaigns/mok/host/mok_port_host.py:198-205:
+build schedule -> copy x / router weights into symmetric buffers -> barrier -> megakernel ->
+barrier -> fwd_epilogue) with the collectives replaced by this library's in-kernel peer-memory
+stages: every rank quantises its tokens once, publishes its routes into every peer's gather
+buffer, peers pull E4M3 rows over NVLink (``plb_ep_pull_rows``), and the down GEMM's epilogue
+pushes result rows into the home rank's combine buffer (``plb_moe_gemm_down_push``).
+``torch.distributed`` is used only to exchange the CUDA IPC handles of the symmetric slabs.
+
+Two ways to form a group:
+  * ``LocalGroup``  - all ranks live in this process on one device (tests on a single GPU;
+    phases run rank after rank on one stream, so no flag barrier is needed or launched);
+  * ``IpcGroup``    - one process per GPU; slabs are shared through CUDA IPC handles.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib, mok
+
+
+def _align(n, a=256):
+    return (n + a - 1) // a * a
+
+
+class SlabLayout:
+    """Offsets of the peer-visible buffers inside one rank's symmetric slab."""
+
+    def __init__(self, shape: mok.Shape, world: int):
+        L, H, k = shape.tokens, shape.hidden, shape.topk
+        if L % 128:
+            raise ValueError("tokens per rank must be a multiple of 128")
+        off = 0
+        self.flags = off; off += _align(4 * 32)
+        self.xq = off; off += _align(L * H)
+        self.xsc = off; off += _align(L // 128 * (H // 128) * 512)
+        self.routes_all = off; off += _align(world * L * k * 4)
+        self.combine = off; off += _align(L * k * H * 2)
+        self.nbytes = off
+
+
+class _RawTensor:
+    """Expose a raw device pointer to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    if dtype == torch.bfloat16:
+        t = torch.as_tensor(_RawTensor(ptr, shape, "<i2"), device=device)
+        return t.view(torch.bfloat16)
+    typestr = {torch.uint8: "|u1", torch.int32: "<i4", torch.float32: "<f4"}[dtype]
+    return torch.as_tensor(_RawTensor(ptr, shape, typestr), device=device)
+
+
+def sym_alloc(nbytes: int) -> int:
+    out = ctypes.c_void_p()
+    _lib.call("plb_sym_alloc", nbytes, ctypes.byref(out))
+    return out.value
+
+
+class LocalGroup:
+    """`world` ranks emulated in one process: every slab is an allocation on the current device."""
+
+    def __init__(self, shape: mok.Shape, world: int, device):
+        self.world, self.device, self.distributed = world, torch.device(device), False
+        self.layout = SlabLayout(shape, world)
+        self.slabs = [sym_alloc(self.layout.nbytes) for _ in range(world)]
+
+    def ptrs_for(self, rank: int):
+        return list(self.slabs)
+
+    def close(self):
+        for p in self.slabs:
+            _lib.call("plb_sym_free", p)
+        self.slabs = []
+
+
+class IpcGroup:
+    """One process per GPU; handles travel through ``torch.distributed`` (bootstrap only)."""
+
+    def __init__(self, shape: mok.Shape, rank: int, world: int, device, group=None):
+        import torch.distributed as dist
+        self.world, self.rank, self.device, self.distributed = world, rank, torch.device(device), True
+        self.layout = SlabLayout(shape, world)
+        self.local = sym_alloc(self.layout.nbytes)
+        handle = (ctypes.c_ubyte * 64)()
+        _lib.call("plb_ipc_export", self.local, handle)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, bytes(handle), group=group)
+        self.peer_ptrs = []
+        for r, h in enumerate(gathered):
+            if r == rank:
+                self.peer_ptrs.append(self.local)
+            else:
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                out = ctypes.c_void_p()
+                _lib.call("plb_ipc_import", buf, ctypes.byref(out))
+                self.peer_ptrs.append(out.value)
+        dist.barrier(group=group)
+
+    def ptrs_for(self, rank: int):
+        assert rank == self.rank
+        return list(self.peer_ptrs)
+
+    def close(self):
+        torch.cuda.synchronize()
+        for r, p in enumerate(self.peer_ptrs):
+            if r != self.rank:
+                _lib.call("plb_ipc_close", p)
+        _lib.call("plb_sym_free", self.local)
+        self.peer_ptrs = []
+
+
+class EpMoKHost(mok.MoKHost):
+    """One rank of the group. ``shape.tokens`` is tokens per rank, ``shape.experts`` the global count."""
+
+    def __init__(self, shape: mok.Shape, rank: int, group, padding: int = mok.EXPERT_PADDING):
+        super().__init__(shape, device=group.device, rank=rank, world=group.world, padding=padding)
+        self.group, lay = group, group.layout
+        ptrs = group.ptrs_for(rank)
+        dev, L, H, k, W = self.device, shape.tokens, shape.hidden, shape.topk, group.world
+        table = lambda off: torch.tensor([p + off for p in ptrs], dtype=torch.int64, device=dev)
+        self.flags_peers, self.xq_peers, self.xsc_peers = table(lay.flags), table(lay.xq), table(lay.xsc)
+        self.routes_peers, self.combine_peers = table(lay.routes_all), table(lay.combine)
+        me = ptrs[rank]
+        self.xq = tensor_from_ptr(me + lay.xq, (L, H), torch.uint8, dev)
+        self.xsc = tensor_from_ptr(me + lay.xsc, (L // 128, H // 128, 32, 16), torch.uint8, dev)
+        self.routes_all = tensor_from_ptr(me + lay.routes_all, (W, L, k), torch.int32, dev)
+        self.buffers["combine_buffer"] = tensor_from_ptr(me + lay.combine, (L * k, H), torch.bfloat16, dev)
+        self.routes_local = torch.empty((L, k), dtype=torch.int32, device=dev)
+        self.barrier_state = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    # ---- steps, in the order forward() issues them
+    def stage_inputs(self, inputs: mok.Inputs):
+        self.x_buffer.copy_(inputs.x)
+        self.router_weight_buffer.copy_(inputs.router)
+        self.routes_local.copy_(inputs.experts)
+        self.quantize_tokens()
+
+    def quantize_tokens(self):
+        sh = self.shape
+        _lib.call("plb_mxfp8_quantize", self.x_buffer.data_ptr(), sh.tokens, sh.hidden, self.xq.data_ptr(),
+                  self.xsc.data_ptr(), None, None, mok._stream())
+
+    def publish_routes(self):
+        _lib.call("plb_ep_publish", self.routes_local.data_ptr(), self.routes_local.numel() * 4,
+                  self.routes_peers.data_ptr(), self.rank, self.world, mok._stream())
+
+    def barrier(self):
+        if self.group.distributed:
+            _lib.call("plb_ep_barrier", self.flags_peers.data_ptr(), self.barrier_state.data_ptr(), self.rank,
+                      self.world, self.status.buf.data_ptr(), mok._stream())
+
+    def build_schedule(self):
+        s, sh = self.schedule, self.shape
+        _lib.call("plb_moe_schedule", self.routes_all.data_ptr(), self.world, sh.tokens, sh.topk,
+                  self.rank * self.num_local_experts, self.num_local_experts, self.capacity, self.padding,
+                  s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.dest_row.data_ptr(),
+                  s.num_tokens.data_ptr(), s.tokens_per_expert.data_ptr(), s.expert_offsets.data_ptr(),
+                  s.block_expert.data_ptr(), s.scratch.data_ptr(), s.scratch.numel() * 4,
+                  self.status.buf.data_ptr(), mok._stream())
+
+    def pull(self):
+        s, b, sh = self.schedule, self.buffers, self.shape
+        _lib.call("plb_ep_pull_rows", self.xq_peers.data_ptr(), self.xsc_peers.data_ptr(),
+                  s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),
+                  self.capacity, sh.hidden, b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
+                  mok._stream())
+
+    def gemm_down_push(self):
+        s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        _lib.call("plb_moe_gemm_down_push", b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(),
+                  w["w_routed_down_fp8"].data_ptr(), w["w_routed_down_sc"].data_ptr(),
+                  s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(),
+                  s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
+                  self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
+
+    def device_step(self):
+        """Everything after the inputs sit in x_buffer / routes_local / router_weight_buffer."""
+        self.quantize_tokens()
+        self.publish_routes()
+        self.barrier()          # routes gathered, every rank's quantised tokens readable
+        self.build_schedule()
+        self.pull()
+        self.gemm_gate_up()
+        self.gemm_down_push()
+        self.barrier()          # every rank's rows have landed in my combine buffer
+        return self.fwd_epilogue()
+
+    def forward(self, inputs: mok.Inputs, *, check: bool = True):
+        if not self.group.distributed:
+            raise ValueError("ranks of a LocalGroup are stepped together: use forward_local_group()")
+        self.status.reset()
+        self.x_buffer.copy_(inputs.x)
+        self.router_weight_buffer.copy_(inputs.router)
+        self.routes_local.copy_(inputs.experts)
+        out = self.device_step()
+        if check:
+            self.status.check("after EP forward")
+        return {"output": out, **self.context_tensors()}
+
+
+def forward_local_group(hosts, inputs_per_rank):
+    """Run every rank of a LocalGroup phase by phase on the current stream."""
+    for h, inp in zip(hosts, inputs_per_rank):
+        h.status.reset()
+        h.stage_inputs(inp)
+        h.publish_routes()
+    for h in hosts:
+        h.build_schedule()
+        h.pull()
+        h.gemm_gate_up()
+    for h in hosts:
+        h.gemm_down_push()
+    outs = [h.fwd_epilogue() for h in hosts]
+    for h in hosts:
+        h.status.check("after local-group forward")
+    return outs
+
+
+class BenchSession:
+    """bench.py's N > 1 arm: one rank of an IpcGroup at BASELINE config 4's per-rank shape."""
+
+    launches_per_step = 11  # quantise, publish, barrier x2, schedule x3, pull, 2 GEMMs, epilogue
+
+    def __init__(self, shape: mok.Shape, dev, rank: int, world: int):
+        self.shape, self.dev = shape, dev
+        self.group = IpcGroup(shape, rank, world, dev)
+        self.host = EpMoKHost(shape, rank, self.group)
+        torch.manual_seed(1234 + rank)
+        E, H, I = self.host.num_local_experts, shape.hidden, shape.intermediate
+        q = {}
+        for name, rows, cols in (("gate", I, H), ("up", I, H), ("down", H, I)):
+            fp8 = torch.empty((E, rows, cols), dtype=torch.uint8, device=dev)
+            sc = torch.empty((E * rows // 128, cols // 128, 32, 16), dtype=torch.uint8, device=dev)
+            for e in range(E):
+                w = (torch.randn(rows, cols, device=dev) * 0.02).to(torch.bfloat16)
+                a, b, _, _ = mok.mxfp8_quantize(w)
+                fp8[e].copy_(a)
+                sc[e * rows // 128:(e + 1) * rows // 128].copy_(b)
+            q[name] = (fp8, sc)
+        self.host.load_quantized_weights(*q["gate"], *q["up"], *q["down"], keep_unpacked=False)
+        logits = torch.randn(shape.tokens, shape.experts, device=dev)
+        values, experts = torch.topk(logits, shape.topk, dim=1)
+        x = torch.randn(shape.tokens, H, device=dev).to(torch.bfloat16)
+        self.inputs = mok.Inputs(x, experts, torch.softmax(values.float(), dim=-1))
+        h = self.host
+        h.x_buffer.copy_(x)
+        h.router_weight_buffer.copy_(self.inputs.router)
+        h.routes_local.copy_(experts)
+        self.kernel_events = []
+        self.h_x = x.cpu().pin_memory()
+        self.h_routes = experts.to(torch.int32).cpu().pin_memory()
+        self.h_router = self.inputs.router.cpu().pin_memory()
+        self.h_out = torch.empty((shape.tokens, H), dtype=torch.bfloat16).pin_memory()
+        torch.cuda.synchronize()
+
+    def step(self, record=False):
+        h = self.host
+        h.quantize_tokens()
+        h.publish_routes()
+        h.barrier()
+        h.build_schedule()
+        h.pull()
+        if record:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            h.gemm_gate_up()
+            b.record()
+            self.kernel_events.append((a, b))
+        else:
+            h.gemm_gate_up()
+        h.gemm_down_push()
+        h.barrier()
+        h.fwd_epilogue()
+
+    def check(self):
+        self.host.status.check("bench (EP)")
+
+    def traffic_per_launch(self):
+        return None
+
+    def e2e(self, steps):
+        h = self.host
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            h.x_buffer.copy_(self.h_x, non_blocking=True)
+            h.routes_local.copy_(self.h_routes, non_blocking=True)
+            h.router_weight_buffer.copy_(self.h_router, non_blocking=True)
+            out = h.device_step()
+            self.h_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        b.record()
+        torch.cuda.synchronize()
+        h2d = self.h_x.numel() * 2 + self.h_routes.numel() * 4 + self.h_router.numel() * 4
+        return a.elapsed_time(b) / steps, h2d, self.h_out.numel() * 2
