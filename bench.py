@@ -217,7 +217,7 @@ def run_native(args):
     roof = None
     if k_ms:
         achieved = (4.0 * shape.tokens * shape.topk * shape.hidden * shape.intermediate) / (k_ms * 1e-3) / 1e12
-        roof = {"bound": "tensor", "kernel": "grouped_gemm_kernel<0> (gate/up + SwiGLU + requantise)",
+        roof = {"bound": "tensor", "kernel": "grouped gate/up GEMM + SwiGLU + requantise",
                 "achieved": achieved, "peak": fp8_peak, "unit": UNIT, "frac": achieved / fp8_peak,
                 "traffic": session.traffic_per_launch(),
                 "peak_source": f"2 x bf16_tflops_sustained of {pk['source']} peaks (dense FP8 = 2 x bf16 rate; "
@@ -245,7 +245,7 @@ def run_native(args):
                 "config": {"workload": shape.name, "tokens_per_rank": shape.tokens, "hidden": shape.hidden,
                            "experts": shape.experts, "topk": shape.topk, "intermediate": shape.intermediate,
                            "l2": "inputs larger than L2 (weights 1.5 GB, activations > 1 GB per step)",
-                           "expert_padding": mok.EXPERT_PADDING},
+                           "expert_padding": mok.expert_padding(), "gemm_variant": "cta-pair 256x256" if mok.expert_padding() == 256 else "single-cta 128x128"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": session.launches_per_step * args.steps,
                 "roofline": roof, "cpu_baseline": cpu,
                 "frac_of_fp8_peak_whole_step": value / world / fp8_peak}

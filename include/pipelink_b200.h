@@ -54,6 +54,16 @@ int plb_abi_version(void);
 const char* plb_error_string(int code);
 int plb_last_cuda_error(void);
 
+/* Grouped-GEMM tiling variant, process-wide: 2 (default) = CTA pairs on 256x256 tiles
+ * (cta_group::2, the reference's geometry, campaigns/mok/port/gemm/gemm.cu:26-36);
+ * 1 = one CTA per 128x128 tile. plb_moe_tile_rows() is the row granularity the current
+ * variant needs: `padding` of the schedule, `capacity`, `inter` and `hidden` must be
+ * multiples of it, and plb_moe_pack_gate_up interleaves in blocks of half of it. Choose the
+ * variant before packing weights. */
+int plb_moe_set_gemm_variant(int variant);
+int plb_moe_gemm_variant(void);
+int plb_moe_tile_rows(void);
+
 /* ------------------------------------------------------------------ MXFP8
  * ops.mxfp8_quantize(tensor, normal, transposed) as used at
  * campaigns/mok/host/mok_port_host.py:122. src is bf16 [rows, cols], rows and cols
@@ -122,8 +132,8 @@ int plb_moe_dispatch(const void* const* x_peers, const int32_t* peer_rank,
 
 /* Interleave reference-layout gate and up weights ([experts, inter, hidden] fp8 +
  * scales, campaigns/mok/host/resources.py:69) into the [experts, 2*inter, hidden]
- * operand of plb_moe_gemm_gate_up: per expert, 64 gate rows then the 64 up rows of
- * the same hidden indices, repeated. Pure data movement. */
+ * operand of plb_moe_gemm_gate_up: per expert, B gate rows then the B up rows of the
+ * same hidden indices, repeated, with B = plb_moe_tile_rows() / 2. Pure data movement. */
 int plb_moe_pack_gate_up(const void* gate_fp8, const void* gate_sc, const void* up_fp8,
                          const void* up_sc, int experts, int inter, int hidden, void* w13_fp8,
                          void* w13_sc, void* stream);

@@ -45,12 +45,13 @@ def quantize_weights(w_gate, w_up, w_down):
     return out
 
 
-def pack_gate_up(gate_q, gate_sc, up_q, up_sc):
-    """Row interleave used by the fused gate/up GEMM: per expert 64 gate rows, 64 up rows, ..."""
+def pack_gate_up(gate_q, gate_sc, up_q, up_sc, block=128):
+    """Row interleave used by the fused gate/up GEMM: per expert `block` gate rows, `block` up rows, ..."""
     E, I, H = gate_q.shape
-    g_s = mxfp8.unpack_scales(gate_sc, E * I, H).reshape(E, I // 64, 64, H // 32)
-    u_s = mxfp8.unpack_scales(up_sc, E * I, H).reshape(E, I // 64, 64, H // 32)
-    q = np.stack([gate_q.reshape(E, I // 64, 64, H), up_q.reshape(E, I // 64, 64, H)], axis=2)
+    B = block
+    g_s = mxfp8.unpack_scales(gate_sc, E * I, H).reshape(E, I // B, B, H // 32)
+    u_s = mxfp8.unpack_scales(up_sc, E * I, H).reshape(E, I // B, B, H // 32)
+    q = np.stack([gate_q.reshape(E, I // B, B, H), up_q.reshape(E, I // B, B, H)], axis=2)
     s = np.stack([g_s, u_s], axis=2)
     return q.reshape(E, 2 * I, H), mxfp8.pack_scales(s.reshape(E * 2 * I, H // 32))
 

@@ -23,6 +23,9 @@ PROTOTYPES = {
     "plb_abi_version": (c_int, []),
     "plb_error_string": (c_char_p, [c_int]),
     "plb_last_cuda_error": (c_int, []),
+    "plb_moe_set_gemm_variant": (c_int, [c_int]),
+    "plb_moe_gemm_variant": (c_int, []),
+    "plb_moe_tile_rows": (c_int, []),
     "plb_mxfp8_quantize": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p]),
     "plb_mxfp8_dequantize": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),

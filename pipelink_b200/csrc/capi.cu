@@ -10,6 +10,13 @@ namespace {
 
 thread_local int g_last_cuda_error = 0;
 
+// 1 = one CTA per 128x128 tile (grouped_gemm.cu), 2 = CTA pair per 256x256 tile (grouped_gemm2.cu)
+int g_gemm_variant = 2;
+
+cudaError_t run_gemm(const plb::GroupedGemmArgs& a, cudaStream_t s) {
+  return g_gemm_variant == 2 ? plb::launch_grouped_gemm_pair(a, s) : plb::launch_grouped_gemm(a, s);
+}
+
 int from_cuda(cudaError_t err) {
   if (err == cudaSuccess) return PLB_OK;
   g_last_cuda_error = static_cast<int>(err);
@@ -47,6 +54,14 @@ const char* plb_error_string(int code) {
 }
 
 int plb_last_cuda_error(void) { return g_last_cuda_error; }
+
+int plb_moe_set_gemm_variant(int variant) {
+  if (variant != 1 && variant != 2) return PLB_E_ARGUMENT;
+  g_gemm_variant = variant;
+  return PLB_OK;
+}
+int plb_moe_gemm_variant(void) { return g_gemm_variant; }
+int plb_moe_tile_rows(void) { return g_gemm_variant == 2 ? 256 : 128; }
 
 int plb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,
                        void* dst_sc, void* dst_t_fp8, void* dst_t_sc, void* stream) {
@@ -176,8 +191,9 @@ int plb_moe_pack_gate_up(const void* gate_fp8, const void* gate_sc, const void* 
     return PLB_E_ARGUMENT;
   if (!gate_fp8 || !gate_sc || !up_fp8 || !up_sc || !w13_fp8 || !w13_sc) return PLB_E_ARGUMENT;
   if (!aligned16(gate_fp8) || !aligned16(up_fp8) || !aligned16(w13_fp8)) return PLB_E_ARGUMENT;
+  if (inter % plb_moe_tile_rows()) return PLB_E_ARGUMENT;
   return from_cuda(plb::launch_pack_gate_up(gate_fp8, gate_sc, up_fp8, up_sc, experts, inter,
-                                            hidden, w13_fp8, w13_sc,
+                                            hidden, plb_moe_tile_rows() / 2, w13_fp8, w13_sc,
                                             static_cast<cudaStream_t>(stream)));
 }
 
@@ -213,7 +229,7 @@ int plb_moe_gemm_gate_up(const void* x_routed_fp8, const void* x_routed_sc, cons
   a.num_sms = sm_count();
   a.status = reinterpret_cast<plb::Status*>(status);
   if (a.num_sms <= 0) return PLB_E_CUDA;
-  return from_cuda(plb::launch_grouped_gemm(a, static_cast<cudaStream_t>(stream)));
+  return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
 }
 
 static int gemm_down_impl(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
@@ -251,7 +267,7 @@ static int gemm_down_impl(const void* hidden_fp8, const void* hidden_sc, const v
   a.num_sms = sm_count();
   a.status = reinterpret_cast<plb::Status*>(status);
   if (a.num_sms <= 0) return PLB_E_CUDA;
-  return from_cuda(plb::launch_grouped_gemm(a, static_cast<cudaStream_t>(stream)));
+  return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
 }
 
 int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,

@@ -1,0 +1,456 @@
+// Grouped MXFP8 GEMM on CTA pairs: tcgen05.mma.cta_group::2, 256x256 output tiles.
+//
+// Same contract as grouped_gemm.cu (the reference's FWD_ROUTED_GATE/UP fused with its
+// SwiGLU stage, and FWD_ROUTED_DOWN with the combine placement:
+// campaigns/mok/port/gemm/gemm.cu:150-162, campaigns/mok/port/act/act.cu:100-178,
+// campaigns/mok/port/comm/comm.cu:124-129) and the reference's own tile geometry
+// (cluster of 2, M256 x N256, gemm.cu:26-36), chosen here because a 128x128 single-CTA
+// tile moves ~260 B/clk/SM through shared memory and stalls the tensor pipe below 40 %;
+// the paired tile stages half as many bytes per MMA cycle.
+//
+// Cluster (2,1,1), 384 threads per CTA:
+//   warp 0      TMA producer (both CTAs): own 128 rows of A, own 128 weight rows of B
+//               (the pair's MMA reads N = 256 across the two CTAs), own 512-byte A-scale
+//               block and both 512-byte B-scale blocks; completion bytes of both CTAs are
+//               credited to the leader CTA's full barrier
+//   warp 1      MMA issuer (leader CTA only): scale blocks -> tensor memory, four K=32
+//               MMAs per 128-byte K step, commits to both CTAs' empty barriers and, per
+//               tile, to both CTAs' accumulator-full barriers
+//   warp 2      tensor-memory alloc / free (both CTAs)
+//   warps 4-11  epilogue (both CTAs): two warps per 32-lane quadrant, each drains 128
+//               accumulator columns into registers, releases the accumulator at once so
+//               the next tile's MMAs overlap the epilogue math, then stores
+// One 256-column fp32 accumulator per CTA (columns 0-255), scale columns behind it.
+//
+// Mode 0: weight rows per 256-row tile are [128 gate | 128 up] of the same hidden
+// indices; out = MXFP8(bf16(silu(bf16 gate) * bf16 up)).
+// Mode 1: bf16 rows to out_base[dest_row], staged through shared memory so every
+// store instruction writes two 256-byte row segments (NVLink-friendly for the push).
+#include "kernels.h"
+#include "mxfp8.cuh"
+
+namespace plb {
+
+namespace {
+
+constexpr int kStages = 5;
+constexpr int kTileBytes = 128 * 128;                  // one CTA's A or B tile per K step
+constexpr int kSfBytes = 512;
+constexpr int kSfStageBytes = 3 * kSfBytes;            // A scales, B scales rows 0-127, 128-255
+constexpr uint32_t kStageTx = 2 * kTileBytes + kSfStageBytes;  // per CTA per stage
+constexpr int kOffA = 0;
+constexpr int kOffB = kStages * kTileBytes;
+constexpr int kOffSf = 2 * kStages * kTileBytes;
+constexpr int kOffStaging = kOffSf + kStages * kSfStageBytes;  // 8 warps x 4 KB
+constexpr int kStagingBytes = 8 * 4096;
+constexpr int kOffBars = kOffStaging + kStagingBytes;
+constexpr int kBarrierBytes = 256;
+constexpr int kSmemBytes2 = kOffBars + kBarrierBytes + 1024;
+static_assert(kOffSf % 1024 == 0 && kOffStaging % 16 == 0, "shared memory layout");
+constexpr int kThreads2 = 384;
+constexpr int kEpilogueWarps = 8;
+constexpr int kTmemCols = 512;
+constexpr int kSfColBase = 256;
+constexpr int kSfColsPerStage = 16;  // 4 (A) + 8 (B) used
+constexpr uint32_t kIdescPair = idesc_mxf8(256, 256);
+
+struct Barriers2 {
+  uint64_t full[kStages];   // used in the leader CTA: 2 arrivals + both CTAs' bytes
+  uint64_t empty[kStages];  // per CTA: 1 arrival (leader's commit)
+  uint64_t acc_full;        // per CTA: 1 arrival (leader's commit)
+  uint64_t acc_empty;       // used in the leader CTA: one arrival per epilogue warp of the pair
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+static_assert(sizeof(Barriers2) <= kBarrierBytes, "barrier block too large");
+
+struct Params2 {
+  const int* block_expert;  // per 128-row block
+  const int* num_rows_dev;
+  int max_m_tiles;          // capacity / 256
+  int k_steps;
+  int n_tiles;              // weight rows per expert / 256
+  int out_cols;             // mode 0: I, mode 1: H
+  uint8_t* out;
+  uint8_t* out_sc;
+  const int* dest_row;
+  uint8_t* const* out_peers;
+  const int* peer_rank;
+  Status* status;
+};
+
+__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ uint32_t pack_bf16(uint32_t a_bits, uint32_t b_bits) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(a_bits), __uint_as_float(b_bits));
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// 32 gate + 32 up accumulator values -> 32 E4M3 bytes (two uint4) and the block's scale byte.
+__device__ __forceinline__ uint32_t swiglu_quant32(const uint32_t* g, const uint32_t* u, uint4& q0,
+                                                   uint4& q1) {
+  float h[32];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float gf = bf16r(__uint_as_float(g[i]));
+    const float uf = bf16r(__uint_as_float(u[i]));
+    const float s = __fdividef(gf, 1.0f + __expf(-gf));
+    h[i] = bf16r(s * uf);
+    amax = fmaxf(amax, fabsf(h[i]));
+  }
+  const uint32_t e = e8m0_from_amax(amax);
+  const float inv = e8m0_inverse(e);
+  q0.x = cvt_e4m3x4(h[0] * inv, h[1] * inv, h[2] * inv, h[3] * inv);
+  q0.y = cvt_e4m3x4(h[4] * inv, h[5] * inv, h[6] * inv, h[7] * inv);
+  q0.z = cvt_e4m3x4(h[8] * inv, h[9] * inv, h[10] * inv, h[11] * inv);
+  q0.w = cvt_e4m3x4(h[12] * inv, h[13] * inv, h[14] * inv, h[15] * inv);
+  q1.x = cvt_e4m3x4(h[16] * inv, h[17] * inv, h[18] * inv, h[19] * inv);
+  q1.y = cvt_e4m3x4(h[20] * inv, h[21] * inv, h[22] * inv, h[23] * inv);
+  q1.z = cvt_e4m3x4(h[24] * inv, h[25] * inv, h[26] * inv, h[27] * inv);
+  q1.w = cvt_e4m3x4(h[28] * inv, h[29] * inv, h[30] * inv, h[31] * inv);
+  return e;
+}
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
+grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
+                     const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_sfa,
+                     const __grid_constant__ CUtensorMap map_sfb, const Params2 p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+  Barriers2* bars = reinterpret_cast<Barriers2*>(smem + kOffBars);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  int m_tiles = *p.num_rows_dev >> 8;
+  if (m_tiles > p.max_m_tiles) m_tiles = p.max_m_tiles;
+  const int total_tiles = m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 2);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bars->acc_full), 1);
+    mbar_init(smem_u32(&bars->acc_empty), 2 * kEpilogueWarps);
+    mbar_init(smem_u32(&bars->drain), 1);
+    fence_mbar_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    prefetch_tensormap(&map_sfa);
+    prefetch_tensormap(&map_sfb);
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(smem_u32(&bars->tmem_base), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp < 4) {
+    setmaxnreg_dec<56>();
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------- TMA producer (both CTAs)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
+        const int m_tile = tile / p.n_tiles;
+        const int n_tile = tile - m_tile * p.n_tiles;
+        const int expert = p.block_expert[m_tile * 2];
+        const int a_blk = m_tile * 2 + static_cast<int>(cta_rank);             // 128-row block of A
+        const int b_blk0 = (expert * p.n_tiles + n_tile) * 2;                  // first 128-row block of B
+        const int b_blk = b_blk0 + static_cast<int>(cta_rank);
+        for (int kb = 0; kb < p.k_steps; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY,
+                         stage)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = mapa_shared(smem_u32(&bars->full[stage]), 0);
+          mbar_arrive_expect_tx_cluster(full, kStageTx);
+          const uint32_t sf = smem_base + kOffSf + stage * kSfStageBytes;
+          tma_load_2d_pair(smem_base + kOffA + stage * kTileBytes, &map_a, full, kb * 128,
+                           a_blk * 128);
+          tma_load_2d_pair(smem_base + kOffB + stage * kTileBytes, &map_b, full, kb * 128,
+                           b_blk * 128);
+          tma_load_2d_pair(sf, &map_sfa, full, 0, a_blk * p.k_steps + kb);
+          tma_load_2d_pair(sf + kSfBytes, &map_sfb, full, 0, b_blk0 * p.k_steps + kb);
+          tma_load_2d_pair(sf + 2 * kSfBytes, &map_sfb, full, 0, (b_blk0 + 1) * p.k_steps + kb);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before this CTA can exit
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000LL) {
+        }
+      }
+    } else if (warp == 1 && lane == 0 && leader) {
+      // ---------------------------------------------------------- MMA issuer (leader CTA)
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      const uint32_t acc_full_own = smem_u32(&bars->acc_full);
+      const uint32_t acc_full_peer = mapa_shared(acc_full_own, 1);
+      for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY,
+                       0)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int kb = 0; kb < p.k_steps; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->full[stage]), phase, p.status, ST_TIMEOUT_FULL, stage)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sf = smem_base + kOffSf + stage * kSfStageBytes;
+          const uint32_t sfa_t = tmem_base + kSfColBase + stage * kSfColsPerStage;
+          const uint32_t sfb_t = sfa_t + 4;
+          tc_cp_32x128b_warpx4_pair(sfa_t, smem_desc(sf, kDescScale));
+          tc_cp_32x128b_warpx4_pair(sfb_t, smem_desc(sf + kSfBytes, kDescScale));
+          tc_cp_32x128b_warpx4_pair(sfb_t + 4, smem_desc(sf + 2 * kSfBytes, kDescScale));
+          const uint64_t adesc = smem_desc(smem_base + kOffA + stage * kTileBytes, kDescSw128KMajor);
+          const uint64_t bdesc = smem_desc(smem_base + kOffB + stage * kTileBytes, kDescSw128KMajor);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            tc_mma_mxf8_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(kIdescPair, k),
+                             sfa_t, sfb_t, (kb | k) != 0 ? 1u : 0u);
+          }
+          const uint32_t empty_own = smem_u32(&bars->empty[stage]);
+          tc_commit_pair(empty_own);
+          tc_commit_pair(mapa_shared(empty_own, 1));
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit_pair(acc_full_own);
+        tc_commit_pair(acc_full_peer);
+        acc_phase ^= 1u;
+      }
+      if (!ok) {
+        tc_commit_pair(smem_u32(&bars->drain));
+        const long long t0 = clock64();
+        while (!mbar_try_wait(smem_u32(&bars->drain), 0)) {
+          if (clock64() - t0 > 20000000LL) break;
+        }
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue (both CTAs)
+    setmaxnreg_inc<224>();
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+    const int ch = (warp - 4) >> 2;       // which half of the accumulator columns
+    const uint32_t acc_empty_leader = mapa_shared(smem_u32(&bars->acc_empty), 0);
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const uint32_t stage_base = smem_base + kOffStaging + (warp - 4) * 4096;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
+      const int m_tile = tile / p.n_tiles;
+      const int n_tile = tile - m_tile * p.n_tiles;
+      if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, p.status, ST_TIMEOUT_TMEM_FULL, 0))
+        ok = false;
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row = static_cast<int64_t>(m_tile) * 256 + cta_rank * 128 + quad * 32 + lane;
+      if (MODE == 0) {
+        uint32_t g0[32], g1[32], u0[32], u1[32];
+        tc_ld_32x32b_x32(taddr + ch * 64, g0);
+        tc_ld_32x32b_x32(taddr + ch * 64 + 32, g1);
+        tc_ld_32x32b_x32(taddr + 128 + ch * 64, u0);
+        tc_ld_32x32b_x32(taddr + 128 + ch * 64 + 32, u1);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        uint4 q0, q1, q2, q3;
+        const uint32_t e0 = swiglu_quant32(g0, u0, q0, q1);
+        const uint32_t e1 = swiglu_quant32(g1, u1, q2, q3);
+        uint4* dst = reinterpret_cast<uint4*>(p.out + row * p.out_cols + n_tile * 128 + ch * 64);
+        dst[0] = q0;
+        dst[1] = q1;
+        dst[2] = q2;
+        dst[3] = q3;
+        const size_t off = scale_offset(row, n_tile * 4 + ch * 2, p.out_cols >> 7);
+        *reinterpret_cast<uint16_t*>(p.out_sc + off) = static_cast<uint16_t>(e0 | (e1 << 8));
+      } else {
+        uint32_t v0[32], v1[32], v2[32], v3[32];
+        tc_ld_32x32b_x32(taddr + ch * 128, v0);
+        tc_ld_32x32b_x32(taddr + ch * 128 + 32, v1);
+        tc_ld_32x32b_x32(taddr + ch * 128 + 64, v2);
+        tc_ld_32x32b_x32(taddr + ch * 128 + 96, v3);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        // 128 fp32 -> 64 packed bf16 pairs = 16 chunks of 16 bytes
+        uint32_t w[64];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          w[i] = pack_bf16(v0[2 * i], v0[2 * i + 1]);
+          w[16 + i] = pack_bf16(v1[2 * i], v1[2 * i + 1]);
+          w[32 + i] = pack_bf16(v2[2 * i], v2[2 * i + 1]);
+          w[48 + i] = pack_bf16(v3[2 * i], v3[2 * i + 1]);
+        }
+        const int dest = p.dest_row[row];
+        const int pr = (p.out_peers != nullptr && dest >= 0) ? p.peer_rank[row] : 0;
+        const size_t col_byte = (static_cast<size_t>(n_tile) * 256 + ch * 128) * 2;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if ((lane >> 4) == h) {
+            const uint32_t r16 = lane & 15;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t addr = stage_base + r16 * 256 + ((static_cast<uint32_t>(j) ^ r16) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]),
+                           "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                           : "memory");
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t rr = i * 2 + (lane >> 4);
+            const uint32_t c = lane & 15;
+            const int src_lane = h * 16 + static_cast<int>(rr);
+            const int d = __shfl_sync(0xFFFFFFFFu, dest, src_lane);
+            const int prr = __shfl_sync(0xFFFFFFFFu, pr, src_lane);
+            uint4 val;
+            const uint32_t addr = stage_base + rr * 256 + ((c ^ rr) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                         : "r"(addr)
+                         : "memory");
+            if (d >= 0) {
+              uint8_t* base = p.out_peers != nullptr ? p.out_peers[prr] : p.out;
+              *reinterpret_cast<uint4*>(base + static_cast<size_t>(d) * p.out_cols * 2 + col_byte +
+                                        c * 16) = val;
+            }
+          }
+          __syncwarp();
+        }
+      }
+      acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn2() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+bool encode_operand(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k) {
+  EncodeTiledFn fn = encode_fn2();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {k, rows};
+  const cuuint64_t strides[1] = {k};
+  const cuuint32_t box[2] = {128, 128};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Scale tensor seen as [blocks, 128] u32: one row per 512-byte scale block.
+bool encode_scales(CUtensorMap* map, const void* base, uint64_t blocks) {
+  EncodeTiledFn fn = encode_fn2();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {128, blocks};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {128, 1};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
+            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// Requirements beyond launch_grouped_gemm: rows_capacity, every expert segment and
+// n_rows are multiples of 256; mode 0 weights are interleaved in blocks of 128 rows.
+cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stream) {
+  if (a.rows_capacity % 256 || a.n_rows % 256 || a.K % 128 || a.K <= 0 || a.n_rows <= 0)
+    return cudaErrorInvalidValue;
+  if (a.rows_capacity == 0 || a.experts == 0) return cudaSuccess;
+  CUtensorMap map_a, map_b, map_sfa, map_sfb;
+  const uint64_t k_steps = a.K / 128;
+  if (!encode_operand(&map_a, a.a_fp8, static_cast<uint64_t>(a.rows_capacity), a.K) ||
+      !encode_operand(&map_b, a.b_fp8, static_cast<uint64_t>(a.experts) * a.n_rows, a.K) ||
+      !encode_scales(&map_sfa, a.a_sc, static_cast<uint64_t>(a.rows_capacity / 128) * k_steps) ||
+      !encode_scales(&map_sfb, a.b_sc,
+                     static_cast<uint64_t>(a.experts) * (a.n_rows / 128) * k_steps))
+    return cudaErrorInvalidValue;
+  Params2 p;
+  p.block_expert = a.block_expert;
+  p.num_rows_dev = a.num_rows_dev;
+  p.max_m_tiles = static_cast<int>(a.rows_capacity / 256);
+  p.k_steps = static_cast<int>(k_steps);
+  p.n_tiles = a.n_rows / 256;
+  p.out_cols = a.mode == 0 ? a.n_rows / 2 : a.n_rows;
+  p.out = static_cast<uint8_t*>(a.out);
+  p.out_sc = static_cast<uint8_t*>(a.out_sc);
+  p.dest_row = a.dest_row;
+  p.out_peers = reinterpret_cast<uint8_t* const*>(a.out_peers);
+  p.peer_rank = a.peer_rank;
+  p.status = a.status;
+  const int grid = a.num_sms & ~1;
+  if (grid < 2) return cudaErrorInvalidValue;
+  cudaError_t err;
+  if (a.mode == 0) {
+    err = cudaFuncSetAttribute(grouped_gemm2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kSmemBytes2);
+    if (err != cudaSuccess) return err;
+    grouped_gemm2_kernel<0><<<grid, kThreads2, kSmemBytes2, stream>>>(map_a, map_b, map_sfa,
+                                                                     map_sfb, p);
+  } else {
+    err = cudaFuncSetAttribute(grouped_gemm2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kSmemBytes2);
+    if (err != cudaSuccess) return err;
+    grouped_gemm2_kernel<1><<<grid, kThreads2, kSmemBytes2, stream>>>(map_a, map_b, map_sfa,
+                                                                     map_sfb, p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace plb

@@ -21,7 +21,7 @@ cudaError_t launch_quantize_transposed(const void* src_bf16, int64_t rows, int64
 cudaError_t launch_dequantize(const void* src_fp8, const void* src_sc, int64_t rows, int64_t cols,
                               float* dst, cudaStream_t stream);
 cudaError_t launch_pack_gate_up(const void* gate_fp8, const void* gate_sc, const void* up_fp8,
-                                const void* up_sc, int experts, int inter, int hidden,
+                                const void* up_sc, int experts, int inter, int hidden, int block,
                                 void* w13_fp8, void* w13_sc, cudaStream_t stream);
 cudaError_t launch_weighted_combine(const void* combine_bf16, const float* router_weights,
                                     const void* y_shared_bf16, int64_t tokens, int topk,
@@ -80,6 +80,8 @@ struct GroupedGemmArgs {
   Status* status;
 };
 cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);
+// CTA-pair variant (grouped_gemm2.cu): 256-row tiles, mode 0 weights interleaved per 128 rows.
+cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stream);
 int grouped_gemm_smem_bytes();
 
 // ---- expert-parallel plumbing (ep.cu)

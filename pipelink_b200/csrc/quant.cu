@@ -145,13 +145,15 @@ dequantize_kernel(const uint8_t* __restrict__ src, const uint8_t* __restrict__ s
   }
 }
 
-// w13 row order per expert: [gate 0..63 | up 0..63 | gate 64..127 | up 64..127 | ...]
-// so that one 128-row weight tile yields 64 gate and 64 up columns of the same
-// hidden index range and its scale block is one ordinary 512-byte block.
+// w13 row order per expert, for interleave block B (64 or 128):
+// [gate 0..B-1 | up 0..B-1 | gate B..2B-1 | up B..2B-1 | ...] so that one 2B-row weight
+// tile yields B gate and B up columns of the same hidden index range and its scale
+// blocks are ordinary 512-byte blocks.
 __global__ void __launch_bounds__(kThreads)
 pack_gate_up_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ gate_sc,
                     const uint8_t* __restrict__ up, const uint8_t* __restrict__ up_sc, int experts,
-                    int inter, int hidden, uint8_t* __restrict__ w13, uint8_t* __restrict__ w13_sc) {
+                    int inter, int hidden, int block, uint8_t* __restrict__ w13,
+                    uint8_t* __restrict__ w13_sc) {
   const int64_t vec_per_row = hidden >> 4;  // 16-byte vectors
   const int64_t dst_rows = static_cast<int64_t>(experts) * 2 * inter;
   const int64_t total = dst_rows * vec_per_row;
@@ -162,9 +164,9 @@ pack_gate_up_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict_
        v += stride) {
     const int64_t dr = v / vec_per_row, j = v - dr * vec_per_row;
     const int64_t e = dr / (2 * inter), within = dr - e * 2 * inter;
-    const int64_t tile = within >> 7, r = within & 127;
-    const bool is_up = r >= 64;
-    const int64_t sr = e * inter + tile * 64 + (r & 63);
+    const int64_t tile = within / (2 * block), r = within - tile * 2 * block;
+    const bool is_up = r >= block;
+    const int64_t sr = e * inter + tile * block + (is_up ? r - block : r);
     const uint8_t* src = is_up ? up : gate;
     reinterpret_cast<uint4*>(w13)[v] = reinterpret_cast<const uint4*>(src)[sr * vec_per_row + j];
     // this thread also moves the scale bytes of the 32-column groups it starts
@@ -265,13 +267,13 @@ cudaError_t launch_dequantize(const void* src_fp8, const void* src_sc, int64_t r
 }
 
 cudaError_t launch_pack_gate_up(const void* gate_fp8, const void* gate_sc, const void* up_fp8,
-                                const void* up_sc, int experts, int inter, int hidden,
+                                const void* up_sc, int experts, int inter, int hidden, int block,
                                 void* w13_fp8, void* w13_sc, cudaStream_t stream) {
   const int64_t total = static_cast<int64_t>(experts) * 2 * inter * (hidden >> 4);
   pack_gate_up_kernel<<<grid_for(total), kThreads, 0, stream>>>(
       static_cast<const uint8_t*>(gate_fp8), static_cast<const uint8_t*>(gate_sc),
       static_cast<const uint8_t*>(up_fp8), static_cast<const uint8_t*>(up_sc), experts, inter,
-      hidden, static_cast<uint8_t*>(w13_fp8), static_cast<uint8_t*>(w13_sc));
+      hidden, block, static_cast<uint8_t*>(w13_fp8), static_cast<uint8_t*>(w13_sc));
   return cudaGetLastError();
 }
 

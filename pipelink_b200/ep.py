@@ -120,7 +120,7 @@ class IpcGroup:
 class EpMoKHost(mok.MoKHost):
     """One rank of the group. ``shape.tokens`` is tokens per rank, ``shape.experts`` the global count."""
 
-    def __init__(self, shape: mok.Shape, rank: int, group, padding: int = mok.EXPERT_PADDING):
+    def __init__(self, shape: mok.Shape, rank: int, group, padding: int | None = None):
         super().__init__(shape, device=group.device, rank=rank, world=group.world, padding=padding)
         self.group, lay = group, group.layout
         ptrs = group.ptrs_for(rank)

@@ -14,7 +14,16 @@ import torch
 
 from . import _lib
 
-EXPERT_PADDING = 128  # rows; one grouped-GEMM tile (the reference pads to its 256-row tile)
+def expert_padding() -> int:
+    """Rows every expert segment is padded to: one grouped-GEMM tile (256 for the CTA-pair
+    variant, as in the reference, campaigns/mok/port/framework/interp_fwd.cu:324; 128 for the
+    single-CTA variant)."""
+    return _lib.load().plb_moe_tile_rows()
+
+
+def set_gemm_variant(variant: int) -> None:
+    """1 = one CTA per 128x128 tile, 2 = CTA pair per 256x256 tile. Choose before loading weights."""
+    _lib.call("plb_moe_set_gemm_variant", variant)
 
 
 @dataclass(frozen=True)
@@ -46,10 +55,11 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def schedule_capacity(tokens_total: int, num_local_experts: int, padding: int = EXPERT_PADDING) -> int:
-    """Rows that always suffice: every routed row plus worst-case padding, rounded to 128."""
+def schedule_capacity(tokens_total: int, num_local_experts: int, padding: int | None = None) -> int:
+    """Rows that always suffice: every routed row plus worst-case padding, rounded to a tile."""
+    padding = padding or expert_padding()
     need = tokens_total + num_local_experts * (padding - 1)
-    return (need + 127) // 128 * 128
+    return (need + padding - 1) // padding * padding
 
 
 def mxfp8_quantize(t: torch.Tensor, normal: bool = True, transposed: bool = False):
@@ -128,10 +138,13 @@ class MoKHost:
     """One rank's persistent forward session."""
 
     def __init__(self, shape: Shape, *, device="cuda", rank: int = 0, world: int = 1,
-                 padding: int = EXPERT_PADDING, capacity: int | None = None):
+                 padding: int | None = None, capacity: int | None = None):
         if shape.experts % world:
             raise ValueError("shape/process group disagrees: experts % world != 0")
         _lib.load()
+        padding = padding or expert_padding()
+        if shape.hidden % expert_padding() or shape.intermediate % expert_padding():
+            raise ValueError(f"hidden and intermediate must be multiples of {expert_padding()}")
         self.shape, self.rank, self.world, self.padding = shape, rank, world, padding
         self.device = torch.device(device)
         E = shape.experts // world

@@ -26,10 +26,17 @@ def _bf16_np(t):
     return t.detach().float().cpu().numpy()
 
 
-@pytest.fixture(scope="module")
-def mok(native_lib):
+@pytest.fixture(scope="module", params=[2, 1], ids=["cta-pair", "single-cta"])
+def mok(native_lib, request):
+    """The host module with the grouped-GEMM variant under test selected (restored afterwards)."""
     from pipelink_b200 import mok
-    return mok
+    mok.set_gemm_variant(request.param)
+    yield mok
+    mok.set_gemm_variant(2)
+
+
+def _tile(mok):
+    return mok.expert_padding()
 
 
 def _status(mok, dev="cuda"):
@@ -160,19 +167,20 @@ def _explain(got, ref):
 
 def test_gemm_ones(mok):
     """All-ones operands with unit scales: every output equals K. Checks the MMA plumbing alone."""
-    rows, K, N = 128, 256, 128
+    rows, K, N = _tile(mok), 256, _tile(mok)
     a_q = torch.full((rows, K), 0x38, dtype=torch.uint8, device="cuda")  # 1.0 in E4M3
     b_q = torch.full((N, K), 0x38, dtype=torch.uint8, device="cuda")
     a_sc = torch.full((rows // 128, K // 128, 32, 16), 127, dtype=torch.uint8, device="cuda")
     b_sc = torch.full((N // 128, K // 128, 32, 16), 127, dtype=torch.uint8, device="cuda")
-    out = _gemm_down_raw(mok, a_q, a_sc, b_q, b_sc, _identity_schedule(mok, rows, [0]), rows, 1, K, N)
+    out = _gemm_down_raw(mok, a_q, a_sc, b_q, b_sc, _identity_schedule(mok, rows, [0] * (rows // 128)), rows, 1, K, N)
     got = _bf16_np(out)
     assert np.array_equal(got, np.full((rows, N), float(K), dtype=np.float32)), _explain(got, np.full((rows, N), float(K)))
 
 
 @pytest.mark.parametrize("random_scales", [False, True])
-@pytest.mark.parametrize("rows,K,N,experts", [(128, 128, 128, 1), (256, 512, 256, 2), (384, 1024, 384, 3)])
-def test_gemm_down_vs_oracle(mok, rows, K, N, experts, random_scales):
+@pytest.mark.parametrize("tiles_m,K,tiles_n,experts", [(1, 128, 1, 1), (2, 512, 2, 2), (3, 1024, 3, 3), (5, 2048, 1, 2)])
+def test_gemm_down_vs_oracle(mok, tiles_m, K, tiles_n, experts, random_scales):
+    rows, N = tiles_m * _tile(mok), tiles_n * _tile(mok)
     rng = np.random.default_rng(rows + K + N + random_scales)
     a = omx.bf16_round(rng.standard_normal((rows, K)).astype(np.float32))
     b = omx.bf16_round(rng.standard_normal((experts * N, K)).astype(np.float32) * 0.05)
@@ -187,7 +195,8 @@ def test_gemm_down_vs_oracle(mok, rows, K, N, experts, random_scales):
         a_sc[:] = 127
         b_sc[:] = 127
     blocks = rows // 128
-    owner = [i % experts for i in range(blocks)]
+    per_tile = _tile(mok) // 128
+    owner = [(i // per_tile) % experts for i in range(blocks)]   # whole tiles belong to one expert
     out = _gemm_down_raw(mok, _t(a_q), _t(a_sc), _t(b_q), _t(b_sc), _identity_schedule(mok, rows, owner),
                          rows, experts, K, N)
     ad, bd = omx.dequantize(a_q, a_sc), omx.dequantize(b_q, b_sc).reshape(experts, N, K)
@@ -200,11 +209,11 @@ def test_gemm_down_vs_oracle(mok, rows, K, N, experts, random_scales):
 
 def test_gemm_down_scatter_and_padding(mok):
     """dest_row permutes rows and negative entries are skipped (left as the poison value)."""
-    rows, K, N = 256, 256, 128
+    rows, K, N = 2 * _tile(mok), 256, _tile(mok)
     rng = np.random.default_rng(5)
     a_q, a_sc = omx.quantize(omx.bf16_round(rng.standard_normal((rows, K)).astype(np.float32)))
     b_q, b_sc = omx.quantize(omx.bf16_round(rng.standard_normal((N, K)).astype(np.float32) * 0.05))
-    sched = _identity_schedule(mok, rows, [0, 0])
+    sched = _identity_schedule(mok, rows, [0] * (rows // 128))
     perm = rng.permutation(rows).astype(np.int32)
     perm[::7] = -1
     sched["dest_row"] = _t(perm)
@@ -247,7 +256,7 @@ def test_forward_vs_oracle(mok, shape_args, generation):
     # weight quantisation on the device is bit-exact
     assert np.array_equal(_np(host.weights["w_routed_gate_fp8"]), weights["gate"][0])
     assert np.array_equal(_np(host.weights["w_routed_down_sc"]), weights["down"][1])
-    w13_q, w13_sc = omoe.pack_gate_up(*weights["gate"], *weights["up"])
+    w13_q, w13_sc = omoe.pack_gate_up(*weights["gate"], *weights["up"], block=_tile(mok) // 2)
     assert np.array_equal(_np(host.weights["w13_fp8"]), w13_q)
     assert np.array_equal(_np(host.weights["w13_sc"]), w13_sc)
 
