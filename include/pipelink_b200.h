@@ -63,6 +63,9 @@ int plb_last_cuda_error(void);
 int plb_moe_set_gemm_variant(int variant);
 int plb_moe_gemm_variant(void);
 int plb_moe_tile_rows(void);
+/* Diagnostics: a device buffer of [grid, 16] int64 that profiling builds of the library
+ * (-DPLB_GEMM_PROFILE) fill with per-role cycle counters; ignored by regular builds. */
+int plb_debug_set_profile_buffer(void* device_i64_grid_by_16);
 
 /* ------------------------------------------------------------------ MXFP8
  * ops.mxfp8_quantize(tensor, normal, transposed) as used at

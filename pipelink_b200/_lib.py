@@ -26,6 +26,7 @@ PROTOTYPES = {
     "plb_moe_set_gemm_variant": (c_int, [c_int]),
     "plb_moe_gemm_variant": (c_int, []),
     "plb_moe_tile_rows": (c_int, []),
+    "plb_debug_set_profile_buffer": (c_int, [c_void_p]),
     "plb_mxfp8_quantize": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p]),
     "plb_mxfp8_dequantize": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),

@@ -13,7 +13,10 @@ thread_local int g_last_cuda_error = 0;
 // 1 = one CTA per 128x128 tile (grouped_gemm.cu), 2 = CTA pair per 256x256 tile (grouped_gemm2.cu)
 int g_gemm_variant = 2;
 
-cudaError_t run_gemm(const plb::GroupedGemmArgs& a, cudaStream_t s) {
+void* g_profile_buffer = nullptr;
+
+cudaError_t run_gemm(plb::GroupedGemmArgs& a, cudaStream_t s) {
+  a.profile = g_profile_buffer;
   return g_gemm_variant == 2 ? plb::launch_grouped_gemm_pair(a, s) : plb::launch_grouped_gemm(a, s);
 }
 
@@ -61,6 +64,10 @@ int plb_moe_set_gemm_variant(int variant) {
   return PLB_OK;
 }
 int plb_moe_gemm_variant(void) { return g_gemm_variant; }
+int plb_debug_set_profile_buffer(void* device_i64_grid_by_16) {
+  g_profile_buffer = device_i64_grid_by_16;
+  return PLB_OK;
+}
 int plb_moe_tile_rows(void) { return g_gemm_variant == 2 ? 256 : 128; }
 
 int plb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,

@@ -274,7 +274,9 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr,
                                                               uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
+  // relaxed: the producer publishes no data of its own through this arrival (the copies
+  // complete on the barrier themselves), and a cluster-scope release would cost a fence
+  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
                    cluster_addr),
                "r"(bytes)
                : "memory");

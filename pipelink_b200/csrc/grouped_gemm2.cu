@@ -33,16 +33,28 @@ namespace plb {
 
 namespace {
 
+#ifdef PLB_EXP_STAGES
+constexpr int kStages = PLB_EXP_STAGES;
+#else
 constexpr int kStages = 5;
+#endif
 constexpr int kTileBytes = 128 * 128;                  // one CTA's A or B tile per K step
 constexpr int kSfBytes = 512;
 constexpr int kSfStageBytes = 3 * kSfBytes;            // A scales, B scales rows 0-127, 128-255
+#ifdef PLB_EXP_NOSF
+constexpr uint32_t kStageTx = 2 * kTileBytes;
+#else
 constexpr uint32_t kStageTx = 2 * kTileBytes + kSfStageBytes;  // per CTA per stage
+#endif
 constexpr int kOffA = 0;
 constexpr int kOffB = kStages * kTileBytes;
 constexpr int kOffSf = 2 * kStages * kTileBytes;
 constexpr int kOffStaging = kOffSf + kStages * kSfStageBytes;  // 8 warps x 4 KB
+#ifdef PLB_EXP_NOSTAGING
+constexpr int kStagingBytes = 0;
+#else
 constexpr int kStagingBytes = 8 * 4096;
+#endif
 constexpr int kOffBars = kOffStaging + kStagingBytes;
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes2 = kOffBars + kBarrierBytes + 1024;
@@ -65,7 +77,21 @@ struct Barriers2 {
 };
 static_assert(sizeof(Barriers2) <= kBarrierBytes, "barrier block too large");
 
+#ifdef PLB_GEMM_PROFILE
+#define PROF_DECL(x) long long x = 0
+#define PROF_T0(x) const long long x = clock64()
+#define PROF_ADD(acc, t0) acc += clock64() - (t0)
+#define PROF_WRITE(slot, v) \
+  if (p.prof != nullptr) p.prof[static_cast<size_t>(blockIdx.x) * 16 + (slot)] = (v)
+#else
+#define PROF_DECL(x)
+#define PROF_T0(x)
+#define PROF_ADD(acc, t0)
+#define PROF_WRITE(slot, v)
+#endif
+
 struct Params2 {
+  long long* prof;          // per-CTA cycle counters; only written by profiling builds
   const int* block_expert;  // per 128-row block
   const int* num_rows_dev;
   int max_m_tiles;          // capacity / 256
@@ -168,6 +194,8 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      PROF_DECL(t_empty);
+      PROF_T0(t_begin);
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
         const int m_tile = tile / p.n_tiles;
         const int n_tile = tile - m_tile * p.n_tiles;
@@ -176,11 +204,13 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         const int b_blk0 = (expert * p.n_tiles + n_tile) * 2;                  // first 128-row block of B
         const int b_blk = b_blk0 + static_cast<int>(cta_rank);
         for (int kb = 0; kb < p.k_steps; ++kb) {
+          PROF_T0(t0);
           if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY,
                          stage)) {
             ok = false;
             break;
           }
+          PROF_ADD(t_empty, t0);
           const uint32_t full = mapa_shared(smem_u32(&bars->full[stage]), 0);
           mbar_arrive_expect_tx_cluster(full, kStageTx);
           const uint32_t sf = smem_base + kOffSf + stage * kSfStageBytes;
@@ -188,12 +218,16 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
                            a_blk * 128);
           tma_load_2d_pair(smem_base + kOffB + stage * kTileBytes, &map_b, full, kb * 128,
                            b_blk * 128);
+#ifndef PLB_EXP_NOSF
           tma_load_2d_pair(sf, &map_sfa, full, 0, a_blk * p.k_steps + kb);
           tma_load_2d_pair(sf + kSfBytes, &map_sfb, full, 0, b_blk0 * p.k_steps + kb);
           tma_load_2d_pair(sf + 2 * kSfBytes, &map_sfb, full, 0, (b_blk0 + 1) * p.k_steps + kb);
+#endif
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      PROF_WRITE(0, t_empty);
+      PROF_WRITE(1, clock64() - t_begin);
       if (!ok) {
         // give copies already in flight time to land before this CTA can exit
         const long long t0 = clock64();
@@ -208,18 +242,25 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       bool ok = true;
       const uint32_t acc_full_own = smem_u32(&bars->acc_full);
       const uint32_t acc_full_peer = mapa_shared(acc_full_own, 1);
+      PROF_DECL(t_acc);
+      PROF_DECL(t_full);
+      PROF_T0(t_begin);
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
+        PROF_T0(ta);
         if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY,
                        0)) {
           ok = false;
           break;
         }
+        PROF_ADD(t_acc, ta);
         tc_fence_after();
         for (int kb = 0; kb < p.k_steps; ++kb) {
+          PROF_T0(tf);
           if (!mbar_wait(smem_u32(&bars->full[stage]), phase, p.status, ST_TIMEOUT_FULL, stage)) {
             ok = false;
             break;
           }
+          PROF_ADD(t_full, tf);
           tc_fence_after();
           const uint32_t sf = smem_base + kOffSf + stage * kSfStageBytes;
           const uint32_t sfa_t = tmem_base + kSfColBase + stage * kSfColsPerStage;
@@ -244,6 +285,9 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         tc_commit_pair(acc_full_peer);
         acc_phase ^= 1u;
       }
+      PROF_WRITE(2, t_acc);
+      PROF_WRITE(3, t_full);
+      PROF_WRITE(4, clock64() - t_begin);
       if (!ok) {
         tc_commit_pair(smem_u32(&bars->drain));
         const long long t0 = clock64();
@@ -262,13 +306,19 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint32_t stage_base = smem_base + kOffStaging + (warp - 4) * 4096;
     uint32_t acc_phase = 0;
     bool ok = true;
+    PROF_DECL(t_wait);
+    PROF_DECL(t_drain);
+    PROF_DECL(t_work);
     for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
       const int m_tile = tile / p.n_tiles;
       const int n_tile = tile - m_tile * p.n_tiles;
+      PROF_T0(tw);
       if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, p.status, ST_TIMEOUT_TMEM_FULL, 0))
         ok = false;
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
+      PROF_ADD(t_wait, tw);
+      PROF_T0(td);
       tc_fence_after();
       const int64_t row = static_cast<int64_t>(m_tile) * 256 + cta_rank * 128 + quad * 32 + lane;
       if (MODE == 0) {
@@ -281,6 +331,8 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        PROF_ADD(t_drain, td);
+        PROF_T0(tm);
         uint4 q0, q1, q2, q3;
         const uint32_t e0 = swiglu_quant32(g0, u0, q0, q1);
         const uint32_t e1 = swiglu_quant32(g1, u1, q2, q3);
@@ -291,6 +343,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         dst[3] = q3;
         const size_t off = scale_offset(row, n_tile * 4 + ch * 2, p.out_cols >> 7);
         *reinterpret_cast<uint16_t*>(p.out_sc + off) = static_cast<uint16_t>(e0 | (e1 << 8));
+        PROF_ADD(t_work, tm);
       } else {
         uint32_t v0[32], v1[32], v2[32], v3[32];
         tc_ld_32x32b_x32(taddr + ch * 128, v0);
@@ -301,6 +354,8 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        PROF_ADD(t_drain, td);
+        PROF_T0(tm);
         // 128 fp32 -> 64 packed bf16 pairs = 16 chunks of 16 bytes
         uint32_t w[64];
 #pragma unroll
@@ -347,8 +402,14 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           __syncwarp();
         }
+        PROF_ADD(t_work, tm);
       }
       acc_phase ^= 1u;
+    }
+    if (warp == 4 && lane == 0) {
+      PROF_WRITE(5, t_wait);
+      PROF_WRITE(6, t_drain);
+      PROF_WRITE(7, t_work);
     }
   }
 
@@ -422,6 +483,7 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
                      static_cast<uint64_t>(a.experts) * (a.n_rows / 128) * k_steps))
     return cudaErrorInvalidValue;
   Params2 p;
+  p.prof = static_cast<long long*>(a.profile);
   p.block_expert = a.block_expert;
   p.num_rows_dev = a.num_rows_dev;
   p.max_m_tiles = static_cast<int>(a.rows_capacity / 256);

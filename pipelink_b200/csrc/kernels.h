@@ -78,6 +78,7 @@ struct GroupedGemmArgs {
   const int* peer_rank = nullptr;    // mode 1 with out_peers
   int num_sms;
   Status* status;
+  void* profile = nullptr;  // cycle counters [grid, 16] i64, written only by profiling builds
 };
 cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);
 // CTA-pair variant (grouped_gemm2.cu): 256-row tiles, mode 0 weights interleaved per 128 rows.

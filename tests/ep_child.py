@@ -36,7 +36,8 @@ def main():
         out = _f(host.forward(inputs[rank])["output"])
         weights = omoe.quantize_weights(_f(wg), _f(wu), _f(wd))
         ref = omoe.forward_multi_rank([_f(i.x) for i in inputs], [i.experts.cpu().numpy().astype(np.int32) for i in inputs],
-                                      [i.router.cpu().numpy() for i in inputs], weights, world)
+                                      [i.router.cpu().numpy() for i in inputs], weights, world,
+                                      padding=mok.expert_padding())
         s = omoe.error_stats(ref["outputs"][rank], out)
         assert np.isfinite(out).all() and s["relative"] <= 2e-2, (rank, generation, s)
     torch.cuda.synchronize()

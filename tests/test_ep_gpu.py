@@ -47,7 +47,8 @@ def test_local_group_forward_vs_oracle(native_lib, world, shape_args):
         weights = omoe.quantize_weights(_f(wg), _f(wu), _f(wd))
         ref = omoe.forward_multi_rank([_f(i.x) for i in inputs],
                                       [i.experts.cpu().numpy().astype(np.int32) for i in inputs],
-                                      [i.router.cpu().numpy() for i in inputs], weights, world)
+                                      [i.router.cpu().numpy() for i in inputs], weights, world,
+                                      padding=mok.expert_padding())
         for r, h in enumerate(hosts):
             sched = ref["schedules"][r]
             total = int(sched["num_tokens"][0])
