@@ -40,16 +40,27 @@ __global__ void schedule_count_kernel(const int* __restrict__ routes, int64_t en
 __global__ void schedule_scan_kernel(ScheduleArgs a, int chunks) {
   extern __shared__ int padded[];  // [num_local_experts + 1]
   const int E = a.num_local_experts;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int running = 0;
-    for (int c = 0; c < chunks; ++c) {
+  // one warp per expert (strided): lanes scan 32 chunks at a time with a running carry
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += warps) {
+    int carry = 0;
+    for (int base = 0; base < chunks; base += 32) {
+      const int c = base + lane;
       const int64_t at = static_cast<int64_t>(c) * E + e;
-      const int n = a.scratch[at];
-      a.scratch[at] = running;
-      running += n;
+      const int n = c < chunks ? a.scratch[at] : 0;
+      int incl = n;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= d) incl += up;
+      }
+      if (c < chunks) a.scratch[at] = carry + incl - n;
+      carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
     }
-    a.tokens_per_expert[e] = running;
-    padded[e] = (running + a.padding - 1) / a.padding * a.padding;
+    if (lane == 0) {
+      a.tokens_per_expert[e] = carry;
+      padded[e] = (carry + a.padding - 1) / a.padding * a.padding;
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {

@@ -143,11 +143,6 @@ class EpMoKHost(mok.MoKHost):
         self.routes_local.copy_(inputs.experts)
         self.quantize_tokens()
 
-    def quantize_tokens(self):
-        sh = self.shape
-        _lib.call("plb_mxfp8_quantize", self.x_buffer.data_ptr(), sh.tokens, sh.hidden, self.xq.data_ptr(),
-                  self.xsc.data_ptr(), None, None, mok._stream())
-
     def publish_routes(self):
         _lib.call("plb_ep_publish", self.routes_local.data_ptr(), self.routes_local.numel() * 4,
                   self.routes_peers.data_ptr(), self.rank, self.world, mok._stream())
@@ -165,13 +160,6 @@ class EpMoKHost(mok.MoKHost):
                   s.num_tokens.data_ptr(), s.tokens_per_expert.data_ptr(), s.expert_offsets.data_ptr(),
                   s.block_expert.data_ptr(), s.scratch.data_ptr(), s.scratch.numel() * 4,
                   self.status.buf.data_ptr(), mok._stream())
-
-    def pull(self):
-        s, b, sh = self.schedule, self.buffers, self.shape
-        _lib.call("plb_ep_pull_rows", self.xq_peers.data_ptr(), self.xsc_peers.data_ptr(),
-                  s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),
-                  self.capacity, sh.hidden, b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
-                  mok._stream())
 
     def gemm_down_push(self):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape

@@ -156,10 +156,16 @@ class MoKHost:
         self.status = DeviceStatus(self.device)
         self.schedule = Schedule(world, L, k, E, P, self.device)
         self.routes_i32 = torch.empty((world, L, k), dtype=torch.int32, device=self.device)
-        self.x_buffer = torch.empty((L, H), dtype=torch.bfloat16, device=self.device)
+        # tokens are quantised once at home (rows padded to a whole 128-row scale block), then
+        # dispatch gathers E4M3 rows + scale words; identical bytes to quantising gathered rows
+        L_pad = (L + 127) // 128 * 128
+        self._x_storage = torch.zeros((L_pad, H), dtype=torch.bfloat16, device=self.device)
+        self.x_buffer = self._x_storage[:L]
         self.router_weight_buffer = torch.empty((L, k), dtype=torch.float32, device=self.device)
-        self.x_peers = torch.tensor([self.x_buffer.data_ptr()] * world, dtype=torch.int64,
-                                    device=self.device)
+        self.xq = torch.empty((L_pad, H), **u8)
+        self.xsc = torch.empty((L_pad // 128, H // 128, 32, 16), **u8)
+        self.xq_peers = torch.tensor([self.xq.data_ptr()] * world, dtype=torch.int64, device=self.device)
+        self.xsc_peers = torch.tensor([self.xsc.data_ptr()] * world, dtype=torch.int64, device=self.device)
         self.buffers = {
             "x_routed_fp8": torch.empty((P, H), **u8),
             "x_routed_sc": torch.empty((P // 128, H // 128, 32, 16), **u8),
@@ -207,11 +213,23 @@ class MoKHost:
                   s.scratch.numel() * 4, self.status.buf.data_ptr(), _stream())
         return s
 
-    def dispatch(self):
+    def quantize_tokens(self):
+        """x_buffer (bf16) -> xq / xsc, the buffers dispatch pulls rows from."""
+        rows = self._x_storage.shape[0]
+        _lib.call("plb_mxfp8_quantize", self._x_storage.data_ptr(), rows, self.shape.hidden,
+                  self.xq.data_ptr(), self.xsc.data_ptr(), None, None, _stream())
+
+    def pull(self):
+        """Dispatch: gather every scheduled row's E4M3 bytes and scale words (comm.cu:105-123)."""
         s, b, sh = self.schedule, self.buffers, self.shape
-        _lib.call("plb_moe_dispatch", self.x_peers.data_ptr(), s.peer_rank.data_ptr(),
-                  s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(), self.capacity, sh.hidden,
-                  b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(), _stream())
+        _lib.call("plb_ep_pull_rows", self.xq_peers.data_ptr(), self.xsc_peers.data_ptr(),
+                  s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),
+                  self.capacity, sh.hidden, b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
+                  _stream())
+
+    def dispatch(self):
+        self.quantize_tokens()
+        self.pull()
 
     def gemm_gate_up(self):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape

@@ -133,6 +133,45 @@ def test_schedule_overflow_sets_status(mok):
     assert int(s.num_tokens.item()) == 0
 
 
+# ------------------------------------------------------------------ dispatch (two routes, same bytes)
+def test_dispatch_paths_bit_exact(mok):
+    """Gather-then-quantise (plb_moe_dispatch) and quantise-then-gather (plb_ep_pull_rows) both
+    reproduce the oracle's routed rows byte for byte, padding rows included."""
+    from pipelink_b200 import _lib
+    rng = np.random.default_rng(3)
+    tokens, topk, experts, H = 333, 2, 4, 512
+    routes = np.stack([rng.permutation(experts)[:topk] for _ in range(tokens)])[None]
+    s, st, cap = _run_schedule(mok, routes, 0, experts, _tile(mok))
+    st.check()
+    x = (torch.randn(tokens, H, device="cuda") * 2).to(torch.bfloat16)
+    ref = oroute.build_schedule(routes, 0, experts, cap, _tile(mok))
+    total = int(ref["num_tokens"][0])
+    rq, rsc = omoe.dispatch([_bf16_np(x)], ref)
+    u8 = dict(dtype=torch.uint8, device="cuda")
+    # route 1: gather bf16 rows, quantise
+    q1 = torch.full((cap, H), 255, **u8)
+    sc1 = torch.full((cap // 128, H // 128, 32, 16), 255, **u8)
+    table = torch.tensor([x.data_ptr()], dtype=torch.int64, device="cuda")
+    _lib.call("plb_moe_dispatch", table.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
+              s.num_tokens.data_ptr(), cap, H, q1.data_ptr(), sc1.data_ptr(), None)
+    # route 2: quantise at home (rows padded to 128), gather bytes + scale words
+    pad = (tokens + 127) // 128 * 128
+    xp = torch.zeros(pad, H, dtype=torch.bfloat16, device="cuda")
+    xp[:tokens] = x
+    xq, xsc, _, _ = mok.mxfp8_quantize(xp)
+    q2 = torch.full((cap, H), 255, **u8)
+    sc2 = torch.full((cap // 128, H // 128, 32, 16), 255, **u8)
+    tq = torch.tensor([xq.data_ptr()], dtype=torch.int64, device="cuda")
+    ts = torch.tensor([xsc.data_ptr()], dtype=torch.int64, device="cuda")
+    _lib.call("plb_ep_pull_rows", tq.data_ptr(), ts.data_ptr(), s.peer_rank.data_ptr(),
+              s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(), cap, H, q2.data_ptr(), sc2.data_ptr(), None)
+    torch.cuda.synchronize()
+    for q, sc in ((q1, sc1), (q2, sc2)):
+        assert np.array_equal(_np(q)[:total], rq)
+        assert np.array_equal(_np(sc)[: total // 128], rsc)
+        assert (_np(q)[total:] == 255).all()      # rows beyond the live schedule are untouched
+
+
 # ------------------------------------------------------------------ grouped GEMM building blocks
 def _identity_schedule(mok, rows, experts_of_block):
     """A schedule whose row p maps to combine row p; block b belongs to experts_of_block[b]."""
