@@ -109,7 +109,7 @@ int plb_moe_schedule(const int32_t* routes, int world, int tokens, int topk, int
                      int32_t* peer_token_idx, int32_t* dest_row, int32_t* num_tokens,
                      int32_t* tokens_per_expert, int32_t* expert_offsets, int32_t* block_expert,
                      void* scratch, size_t scratch_bytes, plb_status* status, void* stream) {
-  if (world < 1 || tokens < 0 || topk < 1 || num_local_experts < 1 || num_local_experts > 8192)
+  if (world < 1 || tokens < 0 || topk < 1 || num_local_experts < 1 || num_local_experts > 1024)
     return PLB_E_ARGUMENT;
   if (capacity < 0 || capacity % 128 || padding < 128 || padding % 128) return PLB_E_ARGUMENT;
   if (!routes || !peer_rank || !peer_token_idx || !dest_row || !num_tokens || !tokens_per_expert ||
@@ -148,7 +148,7 @@ int plb_moe_schedule_noalloc(const int32_t* routes, int world, int tokens, int t
                              int32_t* num_tokens, int32_t* tokens_per_expert,
                              int32_t* expert_offsets, int32_t* block_expert, plb_status* status,
                              void* stream) {
-  if (world < 1 || tokens < 0 || topk < 1 || num_local_experts < 1 || num_local_experts > 8192)
+  if (world < 1 || tokens < 0 || topk < 1 || num_local_experts < 1 || num_local_experts > 1024)
     return PLB_E_ARGUMENT;
   if (capacity < 0 || capacity % 128 || padding < 128 || padding % 128) return PLB_E_ARGUMENT;
   if (!routes || !peer_rank || !peer_token_idx || !dest_row || !num_tokens || !tokens_per_expert ||

@@ -183,10 +183,12 @@ pack_gate_up_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict_
 // out[t, c] = bf16( (y_shared ? y_shared[t,c] : 0) + sum_{j<k} w[t,j] * combine[t*k+j, c] )
 // with every multiply and add rounded separately in fp32 and j ascending, so the
 // result is a pure function of its inputs (deterministic combine order).
+template <int TOPK>  // 0 = runtime top-k; otherwise the loads of all slots are issued together
 __global__ void __launch_bounds__(kThreads)
 weighted_combine_kernel(const uint4* __restrict__ combine, const float* __restrict__ w,
-                        const uint4* __restrict__ y_shared, int64_t tokens, int topk,
+                        const uint4* __restrict__ y_shared, int64_t tokens, int topk_rt,
                         int64_t hidden, uint4* __restrict__ out) {
+  const int topk = TOPK > 0 ? TOPK : topk_rt;
   const int64_t vec_per_row = hidden >> 3;
   const int64_t total = tokens * vec_per_row;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -199,6 +201,22 @@ weighted_combine_kernel(const uint4* __restrict__ combine, const float* __restri
       acc[0] = bf16_lo(y.x); acc[1] = bf16_hi(y.x); acc[2] = bf16_lo(y.y); acc[3] = bf16_hi(y.y);
       acc[4] = bf16_lo(y.z); acc[5] = bf16_hi(y.z); acc[6] = bf16_lo(y.w); acc[7] = bf16_hi(y.w);
     }
+    if (TOPK > 0) {
+      uint4 c[TOPK > 0 ? TOPK : 1];
+      float ws[TOPK > 0 ? TOPK : 1];
+#pragma unroll
+      for (int s = 0; s < TOPK; ++s) {
+        ws[s] = w[t * TOPK + s];
+        c[s] = combine[(t * TOPK + s) * vec_per_row + j];
+      }
+#pragma unroll
+      for (int s = 0; s < TOPK; ++s) {
+        const float f[8] = {bf16_lo(c[s].x), bf16_hi(c[s].x), bf16_lo(c[s].y), bf16_hi(c[s].y),
+                            bf16_lo(c[s].z), bf16_hi(c[s].z), bf16_lo(c[s].w), bf16_hi(c[s].w)};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(ws[s], f[i]));
+      }
+    } else
     for (int s = 0; s < topk; ++s) {
       const float ws = w[t * topk + s];
       const uint4 c = combine[(t * topk + s) * vec_per_row + j];
@@ -281,10 +299,21 @@ cudaError_t launch_weighted_combine(const void* combine_bf16, const float* route
                                     const void* y_shared_bf16, int64_t tokens, int topk,
                                     int64_t hidden, void* out_bf16, cudaStream_t stream) {
   if (tokens == 0) return cudaSuccess;
-  weighted_combine_kernel<<<grid_for(tokens * (hidden >> 3)), kThreads, 0, stream>>>(
-      static_cast<const uint4*>(combine_bf16), router_weights,
-      static_cast<const uint4*>(y_shared_bf16), tokens, topk, hidden,
-      static_cast<uint4*>(out_bf16));
+  const int grid = grid_for(tokens * (hidden >> 3));
+  const uint4* c = static_cast<const uint4*>(combine_bf16);
+  const uint4* y = static_cast<const uint4*>(y_shared_bf16);
+  uint4* o = static_cast<uint4*>(out_bf16);
+#define PLB_COMBINE(K) \
+  weighted_combine_kernel<K><<<grid, kThreads, 0, stream>>>(c, router_weights, y, tokens, topk, hidden, o)
+  switch (topk) {
+    case 1: PLB_COMBINE(1); break;
+    case 2: PLB_COMBINE(2); break;
+    case 4: PLB_COMBINE(4); break;
+    case 6: PLB_COMBINE(6); break;
+    case 8: PLB_COMBINE(8); break;
+    default: PLB_COMBINE(0); break;
+  }
+#undef PLB_COMBINE
   return cudaGetLastError();
 }
 

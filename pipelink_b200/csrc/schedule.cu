@@ -11,7 +11,8 @@
 //   count : per 1024-entry chunk, per local expert, how many entries route to it
 //   scan  : per expert exclusive scan over chunks, padded segment offsets,
 //           block -> expert map, totals
-//   fill  : per chunk, thread e walks the chunk in order and emits its rows
+//   fill  : per chunk, entries are ranked among same-expert entries with warp match masks
+//           and per-warp counts, 256 entries per round, and written to their rows
 #include "kernels.h"
 
 namespace plb {
@@ -98,34 +99,57 @@ __global__ void schedule_scan_kernel(ScheduleArgs a, int chunks) {
   }
 }
 
-__global__ void schedule_fill_kernel(ScheduleArgs a, int64_t entries) {
-  __shared__ int ids[kScheduleChunk];
-  const int64_t begin = static_cast<int64_t>(blockIdx.x) * kScheduleChunk;
-  for (int i = threadIdx.x; i < kScheduleChunk; i += blockDim.x) {
-    const int64_t idx = begin + i;
-    ids[i] = idx < entries ? a.routes[idx] - a.expert_base : -1;
-  }
-  __syncthreads();
+// Stable placement of one 1024-entry chunk, 256 entries per round: an entry's row is
+// (rows of its expert placed by earlier chunks and rounds) + (same-expert entries in
+// earlier warps of this round) + (same-expert entries in earlier lanes of its warp).
+// smem: run[E] running row per expert, wcnt[8][E] per-warp counts of the current round.
+__global__ void __launch_bounds__(256)
+schedule_fill_kernel(ScheduleArgs a, int64_t entries) {
+  extern __shared__ int fill_smem[];
   const int E = a.num_local_experts;
+  int* run = fill_smem;
+  int* wcnt = fill_smem + E;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total = a.expert_offsets[E];
+  if (total == 0) return;  // empty (or overflowed) schedule: nothing to place
+  const int64_t begin = static_cast<int64_t>(blockIdx.x) * kScheduleChunk;
   const int64_t per_rank = static_cast<int64_t>(a.tokens) * a.topk;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    const int seg = a.expert_offsets[e];
-    if (total == 0) continue;
-    int pos = seg + a.scratch[static_cast<int64_t>(blockIdx.x) * E + e];
-    for (int i = 0; i < kScheduleChunk; ++i) {
-      if (ids[i] == e) {
-        const int64_t idx = begin + i;
-        const int src = static_cast<int>(idx / per_rank);
-        const int rem = static_cast<int>(idx - src * per_rank);
-        a.peer_rank[pos] = src;
-        a.peer_token_idx[pos] = rem / a.topk;
-        a.dest_row[pos] = rem;
-        ++pos;
-      }
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    run[e] = a.expert_offsets[e] + a.scratch[static_cast<int64_t>(blockIdx.x) * E + e];
+  for (int round = 0; round < kScheduleChunk / 256; ++round) {
+    for (int i = threadIdx.x; i < 8 * E; i += blockDim.x) wcnt[i] = 0;
+    __syncthreads();
+    const int64_t idx = begin + round * 256 + threadIdx.x;
+    int e = -1;
+    if (idx < entries) {
+      e = a.routes[idx] - a.expert_base;
+      if (e < 0 || e >= E) e = -1;
     }
-    if (blockIdx.x == 0) {
-      const int live_end = seg + a.tokens_per_expert[e];
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+    const int before = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && before == 0) wcnt[warp * E + e] = __popc(peers);
+    __syncthreads();
+    if (e >= 0) {
+      int pos = run[e] + before;
+      for (int w = 0; w < warp; ++w) pos += wcnt[w * E + e];
+      const int src = static_cast<int>(idx / per_rank);
+      const int rem = static_cast<int>(idx - src * per_rank);
+      a.peer_rank[pos] = src;
+      a.peer_token_idx[pos] = rem / a.topk;
+      a.dest_row[pos] = rem;
+    }
+    __syncthreads();
+    for (int x = threadIdx.x; x < E; x += blockDim.x) {
+      int add = 0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) add += wcnt[w * E + x];
+      run[x] += add;
+    }
+    __syncthreads();
+  }
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      const int live_end = a.expert_offsets[e] + a.tokens_per_expert[e];
       const int seg_end = a.expert_offsets[e + 1];
       for (int p = live_end; p < seg_end; ++p) {
         a.peer_rank[p] = -1;
@@ -176,8 +200,6 @@ cudaError_t launch_schedule(const ScheduleArgs& a, cudaStream_t stream) {
   const int64_t entries = static_cast<int64_t>(a.world) * a.tokens * a.topk;
   const int chunks = static_cast<int>((entries + kScheduleChunk - 1) / kScheduleChunk);
   const int E = a.num_local_experts;
-  int threads = ((E + 31) / 32) * 32;
-  if (threads > 1024) threads = 1024;
   if (chunks > 0) {
     schedule_count_kernel<<<chunks, 256, E * sizeof(int), stream>>>(a.routes, entries,
                                                                     a.expert_base, E, a.scratch);
@@ -188,7 +210,7 @@ cudaError_t launch_schedule(const ScheduleArgs& a, cudaStream_t stream) {
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
   if (chunks > 0) {
-    schedule_fill_kernel<<<chunks, threads, 0, stream>>>(a, entries);
+    schedule_fill_kernel<<<chunks, 256, 9 * E * sizeof(int), stream>>>(a, entries);
     err = cudaGetLastError();
   }
   return err;
