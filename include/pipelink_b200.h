@@ -214,6 +214,48 @@ int plb_moe_fwd_epilogue(const void* y_shared_bf16, const void* combine_bf16,
                          const float* router_weights, int64_t tokens, int topk, int64_t hidden,
                          void* out_bf16, void* stream);
 
+/* ------------------------------------------------------------------ batch-1 decode
+ * One launch decodes one token of a Llama-shaped model (hidden 2048, 32 query / 8 KV heads,
+ * head_dim 64, FFN 8192) as a persistent interpreter over per-SM instruction streams: the
+ * stand-in for the reference's decode megakernel and its provider arguments
+ * (campaigns/megakernel/host/mk_host_abi.h:35-85, MkProviderArgs). All pointers are device
+ * addresses. Tensor layouts follow that header: qkv_w [layers,3072,2048], o_w
+ * [layers,2048,2048], up_w / gate_w [layers,8192,2048], down_w [layers,2048,8192], norms
+ * [layers,2048], lm_head [vocab,2048] (tied embedding table), k_cache / v_cache
+ * [layers,max_seq_len,8,64], instructions i32 [num_sms,num_instructions,32]; rope tables are
+ * f32 [rows,32] (one entry per rotated pair, interleaved-pair RoPE,
+ * campaigns/megakernel/host/export_inputs.py:229-240). Instruction words: 0 opcode, 1 layer,
+ * 2-5 operands, 6 counter to wait on (-1 none), 7 its target, 8 counter to bump (-1 none).
+ * Opcodes 1-7 as campaigns/megakernel/host/export_inputs.py:49-58; 8 = greedy sample
+ * (argmax with ties to the lower id, token_out[pos+1], next embedding row into hidden,
+ * *pos_dev += 1). The call zeroes `bars` (num_bars counters) on the stream, then launches
+ * cooperatively with num_sms CTAs. */
+typedef struct plb_decode_args {
+  const void *qkv_w, *o_w, *up_w, *gate_w, *down_w, *attn_norm, *mlp_norm, *lm_norm, *lm_head;
+  void *k_cache, *v_cache;
+  const float *rope_cos, *rope_sin;
+  void *hidden, *q_post_rope, *attn_out, *silu_out, *logits;
+  float *attn_out_partial, *attn_lse_partial, *argmax_val;
+  int32_t* argmax_idx;
+  uint32_t* bars;
+  const int32_t* instructions;
+  int32_t* pos_dev;
+  int32_t* token_out;
+  plb_status* status;
+  int32_t num_instructions, max_seq_len, max_parts, vocab;
+  float attn_scale, eps;
+  int32_t num_bars, reserved;
+} plb_decode_args;
+int plb_decode_step(const plb_decode_args* args, int num_sms, void* stream);
+
+/* The partial-attention op alone, in the harness layout of the reference's checker
+ * (campaigns/megakernel/host/check_cute_attention.cu:16-45): q bf16 [32,64], k / v bf16
+ * [length,8,64], out f32 [(kv_head*partitions+part)*4+h, 64] normalised, lse f32 (base 2);
+ * an empty partition yields zeros and -inf. */
+int plb_decode_attention_partial(const void* q, const void* k, const void* v, float* out,
+                                 float* lse, int length, int partitions, float scale,
+                                 void* stream);
+
 #ifdef __cplusplus
 }
 #endif

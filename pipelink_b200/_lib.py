@@ -60,6 +60,9 @@ PROTOTYPES = {
     "plb_ipc_export": (c_int, [c_void_p, c_void_p]),
     "plb_ipc_import": (c_int, [c_void_p, POINTER(c_void_p)]),
     "plb_ipc_close": (c_int, [c_void_p]),
+    "plb_decode_step": (c_int, [c_void_p, c_int, c_void_p]),
+    "plb_decode_attention_partial": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                             c_float, c_void_p]),
     "plb_moe_fwd_epilogue": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64,
                                      c_void_p, c_void_p]),
 }

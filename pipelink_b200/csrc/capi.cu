@@ -4,6 +4,7 @@
 
 #include <string.h>
 
+#include "decode.h"
 #include "kernels.h"
 
 namespace {
@@ -374,6 +375,28 @@ int plb_moe_fwd_epilogue(const void* y_shared_bf16, const void* combine_bf16,
   return from_cuda(plb::launch_weighted_combine(combine_bf16, router_weights, y_shared_bf16,
                                                 tokens, topk, hidden, out_bf16,
                                                 static_cast<cudaStream_t>(stream)));
+}
+
+int plb_decode_step(const plb_decode_args* args, int num_sms, void* stream) {
+  static_assert(sizeof(plb_decode_args) == sizeof(plb::DecodeGlobals), "decode argument blocks differ");
+  if (!args || num_sms < 1) return PLB_E_ARGUMENT;
+  if (!args->qkv_w || !args->hidden || !args->instructions || !args->bars || !args->pos_dev ||
+      !args->status || args->num_instructions < 1 || args->num_bars < 1 || args->max_parts < 1)
+    return PLB_E_ARGUMENT;
+  plb::DecodeGlobals g;
+  memcpy(&g, args, sizeof(g));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err = cudaMemsetAsync(args->bars, 0, sizeof(uint32_t) * args->num_bars, s);
+  if (err != cudaSuccess) return from_cuda(err);
+  return from_cuda(plb::launch_decode_step(g, num_sms, s));
+}
+
+int plb_decode_attention_partial(const void* q, const void* k, const void* v, float* out,
+                                 float* lse, int length, int partitions, float scale,
+                                 void* stream) {
+  if (!q || !k || !v || !out || !lse || length < 0 || partitions < 1) return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_attention_partial(q, k, v, out, lse, length, partitions, scale,
+                                                 static_cast<cudaStream_t>(stream)));
 }
 
 }  // extern "C"

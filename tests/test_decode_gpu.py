@@ -1,0 +1,117 @@
+"""GPU parity for the decode path through the C ABI: the partial-attention op against the
+float64 oracle on the reference checker's own lengths x partitions grid and predicate, and whole
+decode steps against the CPU restatement with the reference's allclose gate."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import decode as od
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = (1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 129, 1026, 4098)
+PARTITIONS = (1, 2, 3, 8, 24)
+
+
+def _f(t):
+    return t.detach().float().cpu().numpy()
+
+
+def test_attention_partial_reference_grid(native_lib):
+    from pipelink_b200 import _lib
+    g = torch.Generator(device="cuda").manual_seed(20261007)
+    q = (torch.randn(32, 64, generator=g, device="cuda") * 0.7).to(torch.bfloat16)
+    k = (torch.randn(4098, 8, 64, generator=g, device="cuda") * 0.7).to(torch.bfloat16)
+    v = (torch.randn(4098, 8, 64, generator=g, device="cuda") * 0.7).to(torch.bfloat16)
+    qn, kn, vn = _f(q), _f(k), _f(v)
+    cases = failures = 0
+    for length in LENGTHS:
+        for parts in PARTITIONS:
+            n = 8 * parts * 4
+            out = torch.full((n, 64), float("nan"), dtype=torch.float32, device="cuda")
+            lse = torch.full((n,), float("nan"), dtype=torch.float32, device="cuda")
+            _lib.call("plb_decode_attention_partial", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                      lse.data_ptr(), length, parts, 0.125, None)
+            torch.cuda.synchronize()
+            ref, ref_lse = od.attention_partial_f64(qn, kn, vn, length, parts)
+            bad = od.attention_gate(ref, ref_lse, out.cpu().numpy().astype(np.float64), lse.cpu().numpy().astype(np.float64))
+            assert bad == 0, (length, parts, bad)
+            cases += 1
+            failures += bad
+    assert cases == 70 and failures == 0
+
+
+def _make_session(layers, vocab, max_seq, seed=0, partitions=None):
+    from pipelink_b200 import decode as hd
+    torch.manual_seed(seed)
+    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.02).to(torch.bfloat16)
+    w = dict(qkv_w=mk(layers, hd.QKV_ROWS, hd.HIDDEN), o_w=mk(layers, hd.HIDDEN, hd.HIDDEN),
+             up_w=mk(layers, hd.FFN, hd.HIDDEN), gate_w=mk(layers, hd.FFN, hd.HIDDEN),
+             down_w=mk(layers, hd.HIDDEN, hd.FFN),
+             attn_norm=(1 + 0.1 * torch.randn(layers, hd.HIDDEN, device="cuda")).to(torch.bfloat16),
+             mlp_norm=(1 + 0.1 * torch.randn(layers, hd.HIDDEN, device="cuda")).to(torch.bfloat16),
+             lm_norm=torch.ones(hd.HIDDEN, device="cuda", dtype=torch.bfloat16), lm_head=mk(vocab, hd.HIDDEN))
+    s = hd.DecodeSession(w, max_seq_len=max_seq, partitions=partitions)
+    model = {k: _f(v) for k, v in w.items()}
+    return s, model
+
+
+def _check_step(s, model, kc, vc, hidden_in, pos, cos, sin):
+    ref = od.decode_step(model, kc, vc, hidden_in, pos, cos, sin)
+    for name, got in (("hidden_states", None), ("logits", s.logits), ("q_last", s.q_post_rope),
+                      ("attn_out", s.attn_out), ("silu_out", s.silu_out)):
+        if got is None:
+            continue
+        bad, worst = od.gate(ref[name], _f(got))
+        assert bad == 0, (name, pos, bad, worst)
+    L = s.layers
+    for name, cache in (("k_row", s.k_cache), ("v_row", s.v_cache)):
+        bad, worst = od.gate(ref[name], _f(cache[L - 1, pos]).reshape(-1))
+        assert bad == 0, (name, pos, bad, worst)
+    logits = _f(s.logits)
+    token = int(s.token_out[pos + 1].item())
+    assert token == int(np.argmax(logits)), "greedy choice must be the first maximum of the stored logits"
+    assert int(s.pos.item()) == pos + 1
+    # the kernel leaves the chosen token's embedding in the residual stream for the next step
+    assert np.array_equal(_f(s.hidden), model["lm_head"][token])
+    return ref, token
+
+
+@pytest.mark.parametrize("layers,vocab,prefill,partitions", [(2, 1024, 0, 1), (2, 2048, 37, 3), (3, 4096, 300, None)])
+def test_decode_steps_vs_oracle(native_lib, layers, vocab, prefill, partitions):
+    max_seq = prefill + 8
+    s, model = _make_session(layers, vocab, max_seq, seed=layers, partitions=partitions)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    if prefill:
+        s.k_cache[:, :prefill] = torch.randn(layers, prefill, 8, 64, generator=g, device="cuda").to(torch.bfloat16)
+        s.v_cache[:, :prefill] = torch.randn(layers, prefill, 8, 64, generator=g, device="cuda").to(torch.bfloat16)
+    # rows at and beyond the sequence hold poison, as in the reference's bundles
+    s.k_cache[:, prefill:] = 100.0
+    s.v_cache[:, prefill:] = 100.0
+    kc, vc = _f(s.k_cache), _f(s.v_cache)
+    cos, sin = od.rope_tables(max_seq)
+    token = 3
+    s.start(token, prefill)
+    for step in range(3):
+        pos = prefill + step
+        hidden_in = model["lm_head"][token]
+        s.step()
+        s.status.check(f"decode step {step}")
+        _, token = _check_step(s, model, kc, vc, hidden_in, pos, cos, sin)
+
+
+def test_decode_full_size_one_step(native_lib):
+    """The benchmark's shape: 16 layers, vocab 128256, KV cache pre-filled to 4096 tokens."""
+    layers, vocab, prefill = 16, 128256, 4096
+    s, model = _make_session(layers, vocab, prefill + 4, seed=1)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    s.k_cache[:, :prefill] = torch.randn(layers, prefill, 8, 64, generator=g, device="cuda").to(torch.bfloat16)
+    s.v_cache[:, :prefill] = torch.randn(layers, prefill, 8, 64, generator=g, device="cuda").to(torch.bfloat16)
+    kc, vc = _f(s.k_cache), _f(s.v_cache)
+    cos, sin = od.rope_tables(prefill + 4)
+    s.start(12345, prefill)
+    s.step()
+    s.status.check("full-size decode")
+    _check_step(s, model, kc, vc, model["lm_head"][12345], prefill, cos, sin)
