@@ -40,6 +40,7 @@ def parse():
     ap.add_argument("--tokens", type=int, default=None, help="tokens per rank (default: config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the Llama-1B decode ms/token leg")
     return ap.parse_args()
 
 
@@ -181,6 +182,7 @@ def run_native(args):
         session = ep.BenchSession(shape, dev, rank, world)
 
     flop_per_rank = 6.0 * shape.tokens * shape.topk * shape.hidden * shape.intermediate
+    launches_per_step = session.launches_per_step
     for _ in range(max(args.warmup, 3)):
         session.step()
     session.check()
@@ -233,6 +235,13 @@ def run_native(args):
         e2e = {"value": flop_per_rank * world / (float(t.item()) * 1e-3) / 1e12, "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": float(t.item())}
 
+    decode = None
+    if rank == 0 and world == 1 and not args.no_decode and args.tokens is None:
+        del session
+        torch.cuda.empty_cache()
+        decode = decode_leg(dev, pk)
+        session = None
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu, _ = cpu_sample(shape.hidden, shape.intermediate)
@@ -246,12 +255,48 @@ def run_native(args):
                            "experts": shape.experts, "topk": shape.topk, "intermediate": shape.intermediate,
                            "l2": "inputs larger than L2 (weights 1.5 GB, activations > 1 GB per step)",
                            "expert_padding": mok.expert_padding(), "gemm_variant": "cta-pair 256x256" if mok.expert_padding() == 256 else "single-cta 128x128"},
-                "clocks": clocks, "e2e": e2e, "gpu_launches": session.launches_per_step * args.steps,
-                "roofline": roof, "cpu_baseline": cpu,
+                "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+                "roofline": roof, "cpu_baseline": cpu, "decode": decode,
                 "frac_of_fp8_peak_whole_step": value / world / fp8_peak}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def decode_leg(dev, pk, steps=128, prefill=4096):
+    """BASELINE.json configs[2]: Llama-1B-shaped batch-1 greedy decode, KV pre-filled to 4096,
+    128 steps, one cooperative launch per token. Replicas only: the path does not shard."""
+    import torch
+
+    from pipelink_b200 import decode as hd
+    torch.manual_seed(0)
+    L, V = 16, 128256
+    mk = lambda *s: (torch.randn(*s, device=dev) * 0.02).to(torch.bfloat16)
+    w = dict(qkv_w=mk(L, hd.QKV_ROWS, hd.HIDDEN), o_w=mk(L, hd.HIDDEN, hd.HIDDEN), up_w=mk(L, hd.FFN, hd.HIDDEN),
+             gate_w=mk(L, hd.FFN, hd.HIDDEN), down_w=mk(L, hd.HIDDEN, hd.FFN),
+             attn_norm=torch.ones(L, hd.HIDDEN, device=dev), mlp_norm=torch.ones(L, hd.HIDDEN, device=dev),
+             lm_norm=torch.ones(hd.HIDDEN, device=dev), lm_head=mk(V, hd.HIDDEN))
+    s = hd.DecodeSession(w, max_seq_len=prefill + steps + 8, device=dev)
+    s.k_cache[:, :prefill].normal_()
+    s.v_cache[:, :prefill].normal_()
+    s.start(1, prefill)
+    s.decode(8)                      # warm-up tokens
+    s.start(1, prefill)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    s.decode(steps, check=False)
+    b.record()
+    torch.cuda.synchronize()
+    s.status.check("decode leg")
+    ms = a.elapsed_time(b) / steps
+    nbytes = sum(s.bytes_per_token(prefill + i) for i in range(steps)) / steps
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"metric": "llama1b_decode_ms_per_token", "value": ms, "unit": "ms/token", "steps": steps,
+            "prefill": prefill, "higher_is_better": False, "dtype": "bf16", "launches_per_token": 1,
+            "tokens": s.token_out[prefill + 1: prefill + 5].tolist(),
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                         "bytes_per_token": nbytes, "peak_source": f"hbm_gbs of {pk['source']} peaks"}}
 
 
 class SingleRank:

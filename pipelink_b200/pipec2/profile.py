@@ -1,0 +1,27 @@
+"""Target profile: resource domains and limits of sm_100a
+(pipec/src/pipec2/profile.py:107-151: same capacities as the reference's sm_103a/sm_100a)."""
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class Domain:
+    unit: str
+    capacity: int
+    lowest: int
+    granularity: int
+    physical: str      # domains sharing a physical resource must not overlap each other
+    scale: int         # units -> physical units (an mbarrier slot is 16 bytes of shared memory)
+
+
+SM_100A = {
+    "name": "sm_100a", "lto_arch": "lto_100a", "gencode": ("compute_100a", "lto_100a"), "sm": "sm_100a",
+    "param_limit_bytes": 32764, "param_align": 64, "max_threads": 1024,
+    "domains": {
+        "smem": Domain("bytes", 232448, 0, 1, "smem", 1),
+        "mbarrier": Domain("16-byte slots", 232448 // 16, 0, 1, "smem", 16),
+        "tmem": Domain("columns", 512, 0, 32, "tmem", 1),
+        "named_barrier": Domain("IDs", 16, 1, 1, "named_barrier", 1),
+        "warp": Domain("launch warps", 32, 0, 1, "warp", 1),
+    },
+}
+PROFILES = {"sm_100a": SM_100A}

@@ -1,0 +1,152 @@
+"""Link-time resource solve with Z3: ring depths, claim bases per domain, warp tiling.
+
+Same problem statement as the reference's solver (pipec/src/pipec2/solve.py:815-1007; objective
+order docs/reference/pack-and-link.md:131-141): one integer per bindable depth handle (from its
+candidate values) and one per claim base; claims in domains that share a physical resource must
+not overlap (an mbarrier slot occupies 16 bytes of shared memory); bases respect alignment,
+granularity, absolute placement and the domain capacity; role warp claims tile ``[0, warps)``
+exactly. Objective, lexicographic: maximise depths in priority order, then minimise the
+high-water mark of each physical domain. Unsatisfiable problems are reported with the clause
+whose constraints were in the unsat core, by the reference's precedence
+``L-OVERLAP > L-HANDLE > L-TOPO > L-ALIGN`` (solve.py:494,603-627).
+"""
+from __future__ import annotations
+
+import z3
+
+from .model import ClauseFailure, PipeLinkError
+
+PRECEDENCE = ("L-BUDGET", "L-OVERLAP", "L-HANDLE", "L-TOPO", "L-ALIGN")
+
+
+def _extent_expr(extent, depth_vars):
+    e = extent.get("const", 0)
+    for handle, coef in extent.get("per", {}).items():
+        e = e + coef * depth_vars[handle]
+    return e
+
+
+def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forced=None, total_warps=None):
+    """claims: handle -> unified claim record. Returns (bindings, intervals, tiers)."""
+    forced = forced or {}
+    opt = z3.Optimize()
+    opt.set(priority="lex")
+    tracked = []  # (bool, clause, path) for diagnostics through a parallel Solver
+    cons = []
+
+    def add(expr, clause, path):
+        cons.append((expr, clause, path))
+
+    depth_vars = {}
+    for name, h in handles.items():
+        if h["class"] != "depth":
+            continue
+        v = z3.Int(name)
+        depth_vars[name] = v
+        values = [forced[name]] if name in forced else h["values"]
+        if name in forced and forced[name] not in h["values"]:
+            raise PipeLinkError(ClauseFailure("L-HANDLE", f"pipeline.forced_bindings.{name}",
+                                              f"{forced[name]} is not a candidate value", {"values": h["values"]}))
+        add(z3.Or([v == x for x in values]), "L-HANDLE", f"handles.{name}.values")
+
+    base_vars, ext_exprs = {}, {}
+    domains = profile["domains"]
+    for name, cl in claims.items():
+        dom = domains[cl["domain"]]
+        b = z3.Int(name)
+        base_vars[name] = b
+        ext = _extent_expr(cl["extent"], depth_vars)
+        gran = max(dom.granularity, 1)
+        # extents are rounded up to the domain granularity (TMEM columns come in 32s)
+        ext_g = ext if gran == 1 else ((ext + gran - 1) / gran) * gran
+        ext_exprs[name] = ext_g
+        add(b >= dom.lowest, "L-BUDGET", f"claims.{name}.base")
+        add(b + ext_g <= dom.capacity + dom.lowest, "L-BUDGET", f"claims.{name}.extent")
+        align = max(cl.get("align", 1), gran)
+        if align > 1:
+            add(b % align == 0, "L-ALIGN", f"claims.{name}.align")
+        if "absolute_base" in cl:
+            add(b == cl["absolute_base"], "L-ALIGN", f"claims.{name}.absolute_base")
+        if name in forced:
+            add(b == forced[name], "L-HANDLE", f"pipeline.forced_bindings.{name}")
+
+    # non-overlap inside every physical resource (kernel-lifetime claims only in this build)
+    names = sorted(claims)
+    for i, a in enumerate(names):
+        for bname in names[i + 1:]:
+            da, db = domains[claims[a]["domain"]], domains[claims[bname]["domain"]]
+            if da.physical != db.physical:
+                continue
+            lo_a, hi_a = base_vars[a] * da.scale, (base_vars[a] + ext_exprs[a]) * da.scale
+            lo_b, hi_b = base_vars[bname] * db.scale, (base_vars[bname] + ext_exprs[bname]) * db.scale
+            add(z3.Or(hi_a <= lo_b, hi_b <= lo_a), "L-OVERLAP", f"claims.{a}~{bname}")
+
+    # warp claims tile [0, total) exactly
+    warp_claims = [n for n in names if claims[n]["domain"] == "warp"]
+    if warp_claims:
+        total = sum(claims[n]["extent"]["const"] for n in warp_claims)
+        for n in warp_claims:
+            add(base_vars[n] + claims[n]["extent"]["const"] <= total, "L-TOPO", f"claims.{n}.warp_tiling")
+        if total > domains["warp"].capacity:
+            raise PipeLinkError(ClauseFailure("L-TOPO", "topology.warps", f"{total} warps exceed the launch limit"))
+
+    for expr, _, _ in cons:
+        opt.add(expr)
+
+    tiers = []
+    for name in depth_priority:
+        if name in depth_vars:
+            opt.maximize(depth_vars[name])
+            tiers.append({"name": f"max {name}"})
+    for name in sorted(depth_vars):
+        if name not in depth_priority:
+            opt.maximize(depth_vars[name])
+            tiers.append({"name": f"max {name}"})
+    highwater = {}
+    for phys in sorted({d.physical for d in domains.values()}):
+        members = [n for n in names if domains[claims[n]["domain"]].physical == phys]
+        if not members:
+            continue
+        hw = z3.Int(f"__hw_{phys}")
+        for n in members:
+            opt.add(hw >= (base_vars[n] + ext_exprs[n]) * domains[claims[n]["domain"]].scale)
+        highwater[phys] = hw
+        opt.minimize(hw)
+        tiers.append({"name": f"min high-water {phys}"})
+    # finally prefer low bases so layouts are deterministic
+    for n in names:
+        opt.minimize(base_vars[n])
+
+    if opt.check() != z3.sat:
+        _diagnose(cons)
+    model = opt.model()
+    val = lambda e: model.eval(e, model_completion=True).as_long()
+    bindings = {n: [val(v), "forced" if n in forced else "solved"] for n, v in depth_vars.items()}
+    intervals = {}
+    for n in names:
+        lo = val(base_vars[n])
+        hi = lo + val(ext_exprs[n])
+        bindings[n] = [lo, "forced" if n in forced else "solved"]
+        intervals.setdefault(claims[n]["domain"], []).append(
+            {"handle": n, "lo": lo, "hi": hi, "phase": claims[n].get("lifetime", "kernel")})
+    for tier in tiers:
+        tier["status"] = "optimal"
+    hw_vals = {phys: val(hw) for phys, hw in highwater.items()}
+    return bindings, intervals, {"tiers": tiers, "high_water": hw_vals, "engine": f"z3 {z3.get_version_string()} Optimize(lex)"}
+
+
+def _diagnose(cons):
+    """Map an unsatisfiable problem to clause failures through a tracked unsat core."""
+    s = z3.Solver()
+    labels = {}
+    for i, (expr, clause, path) in enumerate(cons):
+        p = z3.Bool(f"c{i}")
+        labels[str(p)] = (clause, path)
+        s.assert_and_track(expr, p)
+    failures = [ClauseFailure("L-BUDGET", "solve", "no assignment satisfies the resource constraints")]
+    if s.check() == z3.unsat:
+        core = [labels[str(c)] for c in s.unsat_core()]
+        best = min((PRECEDENCE.index(c) if c in PRECEDENCE else 99) for c, _ in core)
+        clause = PRECEDENCE[best] if best < len(PRECEDENCE) else core[0][0]
+        failures = [ClauseFailure(clause, path, "constraint is part of the unsatisfiable core") for c, path in core if c == clause]
+    raise PipeLinkError(failures)

@@ -1,0 +1,31 @@
+// Stage gemm.mma: one elected lane issues block-scaled tcgen05 MMAs into tensor memory.
+#include "gemm3.cuh"
+
+extern "C" __device__ void gemm3_mma_role(const void* raw_params, unsigned) {
+  using namespace gemm3;
+  const Gemm3MmaParams& p = *static_cast<const Gemm3MmaParams*>(raw_params);
+  extern __shared__ __align__(1024) unsigned char pl_smem[];
+  if ((threadIdx.x & 31) != 0) return;
+  const uint32_t smem = plb::smem_u32(pl_smem);
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(pl_smem + pipelink_tmem_slot());
+  const int depth = pipelink_gemm_depth();
+  const int k_steps = p.K / TileK;
+  const uint32_t d_tmem = tmem + pipelink_gemm_acc();
+  constexpr uint32_t idesc = plb::idesc_mxf8(TileM, TileN);
+  for (int k = 0; k < k_steps; ++k) {
+    const int slot = k % depth;
+    if (!wait(barrier_addr(smem, pipelink_gemm_full(), slot), (k / depth) & 1)) return;
+    plb::tc_fence_after();
+    const uint32_t base = smem + pipelink_gemm_operands() + slot * SlotBytes;
+    const uint32_t sfa = tmem + pipelink_gemm_sf() + slot * ScaleColsPerSlot, sfb = sfa + 4;
+    plb::tc_cp_32x128b_warpx4(sfa, plb::smem_desc(base + 2 * OperandBytes, plb::kDescScale));
+    plb::tc_cp_32x128b_warpx4(sfb, plb::smem_desc(base + 2 * OperandBytes + ScaleBytes, plb::kDescScale));
+    const uint64_t adesc = plb::smem_desc(base, plb::kDescSw128KMajor);
+    const uint64_t bdesc = plb::smem_desc(base + OperandBytes, plb::kDescSw128KMajor);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      plb::tc_mma_mxf8(d_tmem, adesc + 2 * j, bdesc + 2 * j, plb::idesc_with_sf(idesc, j), sfa, sfb, (k | j) != 0 ? 1u : 0u);
+    plb::tc_commit(barrier_addr(smem, pipelink_gemm_empty(), slot));
+  }
+  plb::tc_commit(barrier_addr(smem, pipelink_gemm_acc_ready()));
+}
