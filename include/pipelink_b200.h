@@ -256,6 +256,24 @@ int plb_decode_attention_partial(const void* q, const void* k, const void* v, fl
                                  float* lse, int length, int partitions, float scale,
                                  void* stream);
 
+/* ------------------------------------------------------------------ linked images
+ * Load and launch a linked pipeline image (`pipeline.cubin` + `link.json` of the link driver):
+ * the roles of CudaBackend in the reference (pipec/src/pipec2/host/cuda.py:123-286: module load,
+ * one launch with the block size, dynamic shared memory and params image the link recorded;
+ * stream-only work, so a launch can be captured into a CUDA graph). params_image points to host
+ * memory holding link.json's params.total_bytes bytes (stage blobs at their recorded offsets). */
+int plb_image_load(const void* image, const char* symbol, int dyn_smem_bytes, void** library,
+                   void** kernel);
+int plb_image_launch(void* kernel, int grid_x, int grid_y, int grid_z, int threads,
+                     int dyn_smem_bytes, const void* params_image, void* stream);
+int plb_image_unload(void* library);
+
+/* Encode a 2-D byte tensor map (what an owner's provider writes into its residue,
+ * examples/hopper-gemm-split/host/owner/provider.cpp:13-48): [rows, row_bytes] row-major, box
+ * box_rows x box_bytes, optional 128-byte swizzle; out128 receives the 128-byte CUtensorMap. */
+int plb_tensor_map_2d_u8(void* out128, const void* base, uint64_t rows, uint64_t row_bytes,
+                         uint32_t box_rows, uint32_t box_bytes, int swizzle128);
+
 #ifdef __cplusplus
 }
 #endif

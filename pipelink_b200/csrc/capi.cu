@@ -399,4 +399,66 @@ int plb_decode_attention_partial(const void* q, const void* k, const void* v, fl
                                                  static_cast<cudaStream_t>(stream)));
 }
 
+// ---- linked-image launcher (cudaLibrary API) and tensor-map helper for stage providers
+int plb_image_load(const void* image, const char* symbol, int dyn_smem_bytes, void** library,
+                   void** kernel) {
+  if (!image || !symbol || !library || !kernel) return PLB_E_ARGUMENT;
+  cudaLibrary_t lib = nullptr;
+  cudaError_t err = cudaLibraryLoadData(&lib, image, nullptr, nullptr, 0, nullptr, nullptr, 0);
+  if (err != cudaSuccess) return from_cuda(err);
+  cudaKernel_t k = nullptr;
+  err = cudaLibraryGetKernel(&k, lib, symbol);
+  if (err == cudaSuccess && dyn_smem_bytes > 0)
+    err = cudaFuncSetAttribute(reinterpret_cast<const void*>(k),
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem_bytes);
+  if (err != cudaSuccess) {
+    cudaLibraryUnload(lib);
+    return from_cuda(err);
+  }
+  *library = lib;
+  *kernel = k;
+  return PLB_OK;
+}
+
+int plb_image_launch(void* kernel, int grid_x, int grid_y, int grid_z, int threads,
+                     int dyn_smem_bytes, const void* params_image, void* stream) {
+  if (!kernel || !params_image || grid_x < 1 || grid_y < 1 || grid_z < 1 || threads < 32)
+    return PLB_E_ARGUMENT;
+  void* args[] = {const_cast<void*>(params_image)};
+  return from_cuda(cudaLaunchKernel(kernel, dim3(grid_x, grid_y, grid_z), dim3(threads), args,
+                                    dyn_smem_bytes, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_image_unload(void* library) {
+  return library ? from_cuda(cudaLibraryUnload(static_cast<cudaLibrary_t>(library))) : PLB_OK;
+}
+
+int plb_tensor_map_2d_u8(void* out128, const void* base, uint64_t rows, uint64_t row_bytes,
+                         uint32_t box_rows, uint32_t box_bytes, int swizzle128) {
+  if (!out128 || !base || rows == 0 || row_bytes == 0 || row_bytes % 16 || box_bytes > 256 ||
+      box_rows > 256)
+    return PLB_E_ARGUMENT;
+  typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                         const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                         CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                         CUtensorMapFloatOOBfill);
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return PLB_E_RESOURCE;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {box_bytes, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult rc = reinterpret_cast<Fn>(sym)(
+      &map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return PLB_E_BUILD;
+  memcpy(out128, &map, sizeof(map));
+  return PLB_OK;
+}
+
 }  // extern "C"

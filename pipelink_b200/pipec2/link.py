@@ -1,0 +1,158 @@
+"""``pipec2 link``: packages + pipeline description -> ``pipeline.cubin`` + ``link.json``.
+
+Phase order of the reference's driver (pipec/src/pipec2/link.py:1614-1861): load and validate ->
+pair channels -> layout identity -> protocol expansion -> unify claims -> params layout -> solve
+-> generate stub + dispatch -> LTO link -> receipt.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import tempfile
+from pathlib import Path
+
+from . import canonjson, codegen, container, contracts, jitlink, schema
+from .model import ClauseFailure, LinkResult, PipeLinkError
+from .profile import PROFILES
+from .solve import solve
+
+TMEM_SLOT_HANDLE = "pipelink_tmem_slot"
+
+
+def _unify_claims(manifests, handles):
+    """Several owners may state the same claim; the statements must agree (L-OWNER)."""
+    claims, failures = {}, []
+    for m in manifests:
+        for cl in m.get("claims", []):
+            rec = {k: v for k, v in cl.items() if k != "roles"}
+            h = cl["handle"]
+            if h in claims:
+                if claims[h]["rec"] != rec:
+                    failures.append(ClauseFailure("L-OWNER", f"claims.{h}", "owners disagree about the claim",
+                                                  {"first": claims[h]["stage"], "second": m["stage"]["id"]}))
+                claims[h]["roles"] += [(m["stage"]["id"], r) for r in cl.get("roles", [])]
+            else:
+                claims[h] = {"rec": rec, "stage": m["stage"]["id"],
+                             "roles": [(m["stage"]["id"], r) for r in cl.get("roles", [])]}
+            if h not in handles:
+                failures.append(ClauseFailure("L-HANDLE", f"claims.{h}", "claim handle is not declared by the pipeline"))
+            elif handles[h]["class"] != "base":
+                failures.append(ClauseFailure("L-HANDLE", f"claims.{h}", "a claim needs a base-class handle"))
+            for dep in cl.get("extent", {}).get("per", {}):
+                if handles.get(dep, {}).get("class") != "depth":
+                    failures.append(ClauseFailure("L-HANDLE", f"claims.{h}.extent.per.{dep}", "extent refers to an undeclared depth handle"))
+    if failures:
+        raise PipeLinkError(failures)
+    return claims
+
+
+def _params_layout(manifests, profile):
+    entries, off = [], 0
+    for m in manifests:
+        p = m.get("params", {"bytes": 0, "align": 1})
+        align = max(p.get("align", 1), 1)
+        off = (off + align - 1) // align * align
+        entries.append([m["stage"]["id"], off, p.get("bytes", 0), align])
+        off += p.get("bytes", 0)
+    total = (off + profile["param_align"] - 1) // profile["param_align"] * profile["param_align"]
+    if total > profile["param_limit_bytes"]:
+        raise PipeLinkError(ClauseFailure("L-PARAMS", "params.total_bytes", f"{total} bytes exceed the {profile['param_limit_bytes']}-byte limit"))
+    return {"total_bytes": total, "align": profile["param_align"], "entries": entries}
+
+
+def link(pipeline_path, out_dir, *, device_link=True):
+    pipeline_path, out_dir = Path(pipeline_path), Path(out_dir)
+    spec = json.loads(pipeline_path.read_text())
+    schema.validate_pipeline(spec)
+    pipe = spec["pipeline"]
+    manifests, payloads, input_hashes = [], [], {}
+    for st in pipe["stages"]:
+        path = (pipeline_path.parent / st["artifact_path"]).resolve()
+        m, payload = container.read(path)
+        schema.validate_manifest(m, where=m["stage"].get("id", str(path)))
+        if m["stage"]["id"] != st["stage_id"]:
+            raise PipeLinkError(ClauseFailure("L-LINK", f"pipeline.stages.{st['stage_id']}", f"package holds stage {m['stage']['id']!r}"))
+        manifests.append(m)
+        payloads.append(payload)
+        input_hashes[st["stage_id"]] = hashlib.sha256(path.read_bytes()).hexdigest()
+    profiles = {m["pipelink_abi"]["target"]["profile"] for m in manifests}
+    if len(profiles) != 1:
+        raise PipeLinkError(ClauseFailure("L-LINK", "pipelink_abi.target.profile", f"stages target different profiles: {sorted(profiles)}"))
+    maths = {json.dumps(m["pipelink_abi"]["target"].get("math"), sort_keys=True) for m in manifests}
+    if len(maths) != 1:
+        raise PipeLinkError(ClauseFailure("L-LINK", "pipelink_abi.target.math", "one floating-point code generation mode per image"))
+    profile = PROFILES[profiles.pop()]
+    handles = dict(pipe.get("handles", {}))
+
+    channels = contracts.pair_channels(manifests)
+    contracts.check_compatibility(channels)
+    expansions = contracts.expand_protocols(channels, manifests)
+    for e in expansions:
+        d = e.get("depth")
+        if isinstance(d, dict) and "handle" in d and handles.get(d["handle"], {}).get("class") != "depth":
+            raise PipeLinkError(ClauseFailure("L-HANDLE", f"channels.{e['channel']}.ring.depth", "ring depth handle is not declared"))
+
+    claims = _unify_claims(manifests, handles)
+    uses_tmem = any(c["rec"]["domain"] == "tmem" for c in claims.values())
+    if uses_tmem:  # the dispatch kernel owns the slot it publishes the allocation base through
+        handles[TMEM_SLOT_HANDLE] = {"class": "base", "binding": "bind", "domain": "smem", "owner": f"claim:{TMEM_SLOT_HANDLE}"}
+        claims[TMEM_SLOT_HANDLE] = {"rec": {"handle": TMEM_SLOT_HANDLE, "domain": "smem", "extent": {"const": 16, "per": {}}, "align": 16},
+                                    "stage": "pipec2.dispatch", "roles": []}
+    params = _params_layout(manifests, profile)
+    bindings, intervals, solver = solve({h: c["rec"] for h, c in claims.items()}, handles, profile,
+                                        depth_priority=pipe.get("depth_priority", []),
+                                        forced=pipe.get("forced_bindings", {}))
+
+    # roles: warp interval from the role's warp claim, params offset from the layout
+    offsets = {e[0]: e[1] for e in params["entries"]}
+    roles, covered = [], 0
+    for m in manifests:
+        for rname, r in m["stage"]["roles"].items():
+            claim = [h for h, c in claims.items() if c["rec"]["domain"] == "warp" and (m["stage"]["id"], rname) in c["roles"]]
+            if len(claim) != 1:
+                raise PipeLinkError(ClauseFailure("L-TOPO", f"{m['stage']['id']}.roles.{rname}", "a role needs exactly one warp claim"))
+            lo = bindings[claim[0]][0]
+            if claims[claim[0]]["rec"]["extent"]["const"] != r["warps"]:
+                raise PipeLinkError(ClauseFailure("L-TOPO", f"{m['stage']['id']}.roles.{rname}", "warp claim extent differs from the role's warp count"))
+            roles.append({"stage": m["stage"]["id"], "role": rname, "entry": r["entry"], "warp_lo": lo,
+                          "warp_hi": lo + r["warps"], "params_offset": offsets[m["stage"]["id"]], "variant": 0})
+            covered += r["warps"]
+    roles.sort(key=lambda r: r["warp_lo"])
+    threads = 32 * covered
+    tmem_cols = 0
+    if uses_tmem:
+        hw = max(iv["hi"] for iv in intervals["tmem"])
+        tmem_cols = 32
+        while tmem_cols < hw:
+            tmem_cols *= 2
+    smem_hw = solver["high_water"].get("smem", 0)
+    generated = {
+        "binding_stub.cu": codegen.binding_stub(bindings),
+        "dispatch.cu": codegen.dispatch(threads=threads, params_total=params["total_bytes"], roles=roles,
+                                        expansions=expansions, bindings=bindings, tmem_columns=tmem_cols,
+                                        tmem_slot=bindings.get(TMEM_SLOT_HANDLE, [0])[0], tmem_warp=roles[0]["warp_lo"]),
+    }
+    out_dir.mkdir(parents=True, exist_ok=True)
+    gen_dir = out_dir / "generated"
+    gen_dir.mkdir(exist_ok=True)
+    for name, text in generated.items():
+        (gen_dir / name).write_text(text)
+    observed = (-1, -1, -1)
+    if device_link:
+        objects = [(m["stage"]["id"], p) for m, p in zip(manifests, payloads)]
+        with tempfile.TemporaryDirectory() as tmp:
+            for name in generated:
+                obj = Path(tmp) / (name + ".o")
+                jitlink.compile_lto(str(gen_dir / name), str(obj), profile)
+                objects.append((name, obj.read_bytes()))
+        cubin, info = jitlink.link(objects, profile["sm"])
+        (out_dir / "pipeline.cubin").write_bytes(cubin)
+        (out_dir / "nvjitlink.log").write_text(info)
+    result = LinkResult(
+        kernel_symbol="pipelink_kernel", threads=threads, regs_cap=min(255, 65536 // max(threads, 1) // 8 * 8),
+        dyn_smem_bytes=smem_hw, cluster=(1, 1, 1), params=params, bindings=bindings, variants={},
+        intervals=intervals, protocol_expansions=expansions, observed=observed, input_hashes=input_hashes,
+        generated_hashes={k: hashlib.sha256(v.encode()).hexdigest() for k, v in generated.items()},
+        solver=solver, roles=roles, tmem_columns=tmem_cols)
+    (out_dir / "link.json").write_text(canonjson.dumps(result.to_json_obj()))
+    return result

@@ -58,7 +58,7 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         ext = _extent_expr(cl["extent"], depth_vars)
         gran = max(dom.granularity, 1)
         # extents are rounded up to the domain granularity (TMEM columns come in 32s)
-        ext_g = ext if gran == 1 else ((ext + gran - 1) / gran) * gran
+        ext_g = ext if gran == 1 else (((ext + gran - 1) // gran) * gran if isinstance(ext, int) else ((ext + gran - 1) / gran) * gran)
         ext_exprs[name] = ext_g
         add(b >= dom.lowest, "L-BUDGET", f"claims.{name}.base")
         add(b + ext_g <= dom.capacity + dom.lowest, "L-BUDGET", f"claims.{name}.extent")
@@ -120,7 +120,7 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
     if opt.check() != z3.sat:
         _diagnose(cons)
     model = opt.model()
-    val = lambda e: model.eval(e, model_completion=True).as_long()
+    val = lambda e: e if isinstance(e, int) else model.eval(e, model_completion=True).as_long()
     bindings = {n: [val(v), "forced" if n in forced else "solved"] for n, v in depth_vars.items()}
     intervals = {}
     for n in names:

@@ -3,7 +3,7 @@
 
 #include "gemm3.cuh"
 
-extern "C" __device__ void gemm3_epilogue_role(const void* raw_params, unsigned) {
+extern "C" __device__ void gemm_epilogue_bias_silu_role(const void* raw_params, unsigned) {
   using namespace gemm3;
   const Gemm3EpilogueParams& p = *static_cast<const Gemm3EpilogueParams*>(raw_params);
   extern __shared__ __align__(1024) unsigned char pl_smem[];

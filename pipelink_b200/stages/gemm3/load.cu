@@ -1,7 +1,7 @@
 // Stage gemm.load: one elected lane feeds the operands ring with TMA.
 #include "gemm3.cuh"
 
-extern "C" __device__ void gemm3_load_role(const void* raw_params, unsigned) {
+extern "C" __device__ void gemm_load_role(const void* raw_params, unsigned) {
   using namespace gemm3;
   const Gemm3LoadParams& p = *static_cast<const Gemm3LoadParams*>(raw_params);
   extern __shared__ __align__(1024) unsigned char pl_smem[];

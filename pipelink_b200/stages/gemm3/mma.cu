@@ -1,7 +1,7 @@
 // Stage gemm.mma: one elected lane issues block-scaled tcgen05 MMAs into tensor memory.
 #include "gemm3.cuh"
 
-extern "C" __device__ void gemm3_mma_role(const void* raw_params, unsigned) {
+extern "C" __device__ void gemm_mma_role(const void* raw_params, unsigned) {
   using namespace gemm3;
   const Gemm3MmaParams& p = *static_cast<const Gemm3MmaParams*>(raw_params);
   extern __shared__ __align__(1024) unsigned char pl_smem[];
