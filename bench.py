@@ -359,7 +359,14 @@ class SingleRank:
         self.host.status.check("bench")
 
     def traffic_per_launch(self):
-        return None  # filled from the ncu capture recorded under profiles/
+        """dram bytes of one gate/up GEMM launch: the ncu capture of the 4096-token case
+        (profiles/grouped_gemm_pair_moe_ffn_fwd.md) read 1.062 x that case's algorithmic bytes;
+        scaled here by this workload's algorithmic bytes (A, output and their scales grow with rows)."""
+        sh, P = self.shape, self.host.capacity
+        H, I, E = sh.hidden, sh.intermediate, sh.experts
+        rows = min(P, sh.tokens * sh.topk + E * self.host.padding // 2)
+        algorithmic = rows * H * (1 + 1 / 32) + E * 2 * I * H * (1 + 1 / 32) + rows * I * (1 + 1 / 32)
+        return 1.062 * algorithmic
 
     def e2e(self, steps):
         """Host buffers in, host buffer out, through the public session API."""
