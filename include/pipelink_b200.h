@@ -256,6 +256,41 @@ int plb_decode_attention_partial(const void* q, const void* k, const void* v, fl
                                  float* lse, int length, int partitions, float scale,
                                  void* stream);
 
+/* ------------------------------------------------------------------ prefill attention
+ * Causal flash-attention forward, bf16, head_dim 128 (the reference's sm90 core,
+ * campaigns/attention/src/sm90/role_core.cuh + role_load.cuh + role_epilogue.cuh). Q / O are
+ * [q_rows, q_heads, 128], K / V [kv_rows, kv_heads, 128], LSE f32 [batch * q_heads, seq_q]
+ * (natural log of the sum of exp of the scaled scores, campaigns/attention/src/slot/family.cuh:156-229).
+ * The caller supplies the work list, one record per 128-query tile and head, the counterpart of
+ * WorkDesc (campaigns/attention/src/sm90/README.md:107-122); heavy tiles first balances a causal
+ * mask. `ready` (optional) holds one counter per 128-key block of K / V: a block is read only once
+ * (int32)(ready[block] - ready_target) >= 0, the context-parallel acquire of
+ * campaigns/attention/src/sm90/cp_load.cuh:124-137. */
+typedef struct plb_attn_work {
+  int32_t q_row0;    /* first row of the tile in Q / O */
+  int32_t q_pos0;    /* global sequence position of that query */
+  int32_t kv_row0;   /* row of key block 0 in K / V */
+  int32_t kv_pos0;   /* global sequence position of that key */
+  int32_t kv_blocks; /* 128-key blocks to visit */
+  int32_t head;
+  int32_t batch;
+  int32_t reserved;
+} plb_attn_work;
+int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
+                      const plb_attn_work* work, int num_work, int q_heads, int kv_heads, int seq_q,
+                      uint64_t q_rows, uint64_t kv_rows, float scale, const uint32_t* ready,
+                      uint32_t ready_target, plb_status* status, void* stream);
+
+/* Context-parallel K/V exchange (kv_gather_role_gather, campaigns/attention/src/sm90/stage_kv_gather.cu:16-78):
+ * rank r holds chunks r and 2*world-1-r of the sequence (zigzag) as k_local / v_local
+ * [2 * chunk_blocks * 128, kv_heads * 128]; every 128-token block (block_bytes bytes of K, same of
+ * V) is stored into the gathered global-order buffers of each rank that needs it (early chunk:
+ * all ranks; late chunk: ranks <= r), then that rank's ready[global block] is bumped by 1 with
+ * fence.acq_rel.sys + red.release.sys. Counters are never reset: launch n makes them n. */
+int plb_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks, int64_t block_bytes,
+                   int rank, int world, void* const* k_gather_peers, void* const* v_gather_peers,
+                   void* const* ready_peers, int ctas, void* stream);
+
 /* ------------------------------------------------------------------ linked images
  * Load and launch a linked pipeline image (`pipeline.cubin` + `link.json` of the link driver):
  * the roles of CudaBackend in the reference (pipec/src/pipec2/host/cuda.py:123-286: module load,

@@ -1,0 +1,140 @@
+"""Host side of causal prefill attention and its context-parallel composition.
+
+Single GPU: ``attention_fwd(q, k, v)`` builds the work list (one record per 128-query tile and
+head, heavy tiles first) and calls ``plb_attention_fwd``.
+
+Context parallel (the reference's ``cp`` composition, campaigns/attention/README.md:216-262):
+the sequence is cut into 2W chunks, rank r owns chunks r and 2W-1-r (zigzag); queries never
+move; every rank pushes its K/V blocks into the gathered, global-order buffers of the ranks that
+need them (``plb_cp_push_kv``) and bumps one readiness counter per 128-token block; the attention
+kernel's load lane acquires a block's counter right before its first TMA of that block. A step is
+[group barrier] -> push -> attention, all on one stream: the push never waits on peers, so no two
+kernels on one GPU wait on each other.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from .mok import DeviceStatus, _stream
+
+BLK, D = 128, 128
+
+
+def causal_work(batch: int, seq: int, q_heads: int) -> np.ndarray:
+    """i32 [n, 8]: (q_row0, q_pos0, kv_row0, kv_pos0, kv_blocks, head, batch, 0), longest tiles first."""
+    rows = []
+    for qb in range(seq // BLK - 1, -1, -1):
+        for b in range(batch):
+            for h in range(q_heads):
+                rows.append((b * seq + qb * BLK, qb * BLK, b * seq, 0, qb + 1, h, b, 0))
+    return np.asarray(rows, dtype=np.int32).reshape(-1, 8)
+
+
+def zigzag_work(seq: int, world: int, rank: int, q_heads: int) -> np.ndarray:
+    """Work list of one rank (batch 1): local tile t covers global positions s*C + (128 t mod C),
+    s = rank for the early chunk and 2W-1-rank for the late one (src/sm90/README.md:202-209)."""
+    C = seq // (2 * world)
+    items = []
+    for t in range(2 * C // BLK):
+        s = rank if t * BLK < C else 2 * world - 1 - rank
+        pos = s * C + (t * BLK) % C
+        items.append((pos, t))
+    rows = []
+    for pos, t in sorted(items, reverse=True):
+        for h in range(q_heads):
+            rows.append((t * BLK, pos, 0, 0, pos // BLK + 1, h, 0, 0))
+    return np.asarray(rows, dtype=np.int32).reshape(-1, 8)
+
+
+def _launch(q, k, v, out, lse, work, seq_q, ready, ready_target, status):
+    q_rows, q_heads = q.shape[0], q.shape[1]
+    kv_rows, kv_heads = k.shape[0], k.shape[1]
+    _lib.call("plb_attention_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+              work.data_ptr(), work.shape[0], q_heads, kv_heads, seq_q, q_rows, kv_rows, 1.0 / math.sqrt(D),
+              0 if ready is None else ready.data_ptr(), ready_target, status.buf.data_ptr(), _stream())
+
+
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, check: bool = True):
+    """q [B, S, Hq, 128], k / v [B, S, Hkv, 128] bf16 CUDA. Returns (O like q, LSE f32 [B*Hq, S])."""
+    B, S, Hq, d = q.shape
+    if d != D or S % BLK or q.dtype != torch.bfloat16:
+        raise ValueError("attention_fwd wants bf16, head_dim 128 and a sequence that is a multiple of 128")
+    Hkv = k.shape[2]
+    out = torch.empty_like(q)
+    lse = torch.empty((B * Hq, S), dtype=torch.float32, device=q.device)
+    work = torch.from_numpy(causal_work(B, S, Hq)).to(q.device)
+    status = DeviceStatus(q.device)
+    _launch(q.reshape(B * S, Hq, D), k.reshape(B * S, Hkv, D), v.reshape(B * S, Hkv, D), out.reshape(B * S, Hq, D),
+            lse, work, S, None, 0, status)
+    if check:
+        status.check("attention_fwd")
+    return out, lse
+
+
+class CpRank:
+    """One rank of a context-parallel group (batch 1). Buffers peers write into (`k_gather`,
+    `v_gather`, `ready`, barrier `flags`) live in a slab that is shared through CUDA IPC
+    (``ep.IpcGroup``-style) or, for single-GPU tests, allocated side by side in one process."""
+
+    def __init__(self, seq: int, q_heads: int, kv_heads: int, rank: int, world: int, slab_ptrs, layout, device):
+        from .ep import tensor_from_ptr
+        self.seq, self.rank, self.world, self.device = seq, rank, world, torch.device(device)
+        self.C = seq // (2 * world)
+        if self.C % BLK:
+            raise ValueError("sequence / (2 * world) must be a multiple of 128")
+        self.q_heads, self.kv_heads = q_heads, kv_heads
+        dev = self.device
+        me = slab_ptrs[rank]
+        self.k_gather = tensor_from_ptr(me + layout["k"], (seq, kv_heads, D), torch.bfloat16, dev)
+        self.v_gather = tensor_from_ptr(me + layout["v"], (seq, kv_heads, D), torch.bfloat16, dev)
+        self.ready = tensor_from_ptr(me + layout["ready"], (seq // BLK,), torch.int32, dev)
+        table = lambda off: torch.tensor([p + off for p in slab_ptrs], dtype=torch.int64, device=dev)
+        self.k_peers, self.v_peers = table(layout["k"]), table(layout["v"])
+        self.ready_peers, self.flags_peers = table(layout["ready"]), table(layout["flags"])
+        self.work = torch.from_numpy(zigzag_work(seq, world, rank, q_heads)).to(dev)
+        self.barrier_state = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = DeviceStatus(dev)
+        self.generation = 0
+        self.out = torch.empty((2 * self.C, q_heads, D), dtype=torch.bfloat16, device=dev)
+        self.lse = torch.empty((q_heads, 2 * self.C), dtype=torch.float32, device=dev)
+
+    @staticmethod
+    def slab_layout(seq: int, kv_heads: int):
+        kv = seq * kv_heads * D * 2
+        lay = {"flags": 0, "ready": 256, "k": 256 + (seq // BLK * 4 + 255) // 256 * 256}
+        lay["v"] = lay["k"] + kv
+        lay["nbytes"] = lay["v"] + kv
+        return lay
+
+    def barrier(self):
+        _lib.call("plb_ep_barrier", self.flags_peers.data_ptr(), self.barrier_state.data_ptr(), self.rank, self.world,
+                  self.status.buf.data_ptr(), _stream())
+
+    def push(self, k_local: torch.Tensor, v_local: torch.Tensor, ctas: int = 32):
+        """k_local / v_local bf16 [2C, kv_heads, 128]: this rank's early chunk then its late chunk."""
+        self.generation += 1
+        _lib.call("plb_cp_push_kv", k_local.data_ptr(), v_local.data_ptr(), self.C // BLK, BLK * self.kv_heads * D * 2,
+                  self.rank, self.world, self.k_peers.data_ptr(), self.v_peers.data_ptr(), self.ready_peers.data_ptr(),
+                  ctas, _stream())
+
+    def attend(self, q_local: torch.Tensor):
+        _launch(q_local, self.k_gather, self.v_gather, self.out, self.lse, self.work, 2 * self.C, self.ready,
+                self.generation, self.status)
+        return self.out, self.lse
+
+    def step(self, q_local, k_local, v_local, distributed: bool = True):
+        if distributed:
+            self.barrier()       # every rank has finished reading the previous step's gathered K/V
+        self.push(k_local, v_local)
+        return self.attend(q_local)
+
+
+def shard_zigzag(t: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """[S, ...] -> this rank's [2C, ...] (early chunk then late chunk)."""
+    C = t.shape[0] // (2 * world)
+    return torch.cat([t[rank * C:(rank + 1) * C], t[(2 * world - 1 - rank) * C:(2 * world - rank) * C]]).contiguous()

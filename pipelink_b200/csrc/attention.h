@@ -1,0 +1,56 @@
+// Work descriptors and arguments of the prefill attention kernel (attention.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+
+namespace plb {
+
+// One 128-query tile of one head. Mirrored by plb_attn_work in include/pipelink_b200.h.
+struct AttnWork {
+  int q_row0;     // first row of the tile in the [batch*seq_q, q_heads*128] view of Q / O
+  int q_pos0;     // global sequence position of that row (differs from the row under context parallelism)
+  int kv_row0;    // row of key block 0 in the [kv_rows, kv_heads*128] view of K / V
+  int kv_pos0;    // global sequence position of that key
+  int kv_blocks;  // 128-key blocks to visit (causal: q_pos0 / 128 + 1 when kv_pos0 = 0)
+  int head;       // query head
+  int batch;
+  int reserved;
+};
+
+struct AttnParams {
+  const AttnWork* work;
+  int num_work;
+  int q_heads;
+  int q_per_kv;
+  int seq_q;
+  __nv_bfloat16* out;
+  float* lse;
+  float scale_log2;
+  unsigned ready_target;
+  const unsigned* ready;  // per 128-key block readiness counters (context parallel), or null
+  Status* status;
+};
+
+struct AttnArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse;
+  const AttnWork* work;
+  int num_work;
+  int q_heads, kv_heads;
+  int seq_q;
+  uint64_t q_rows, kv_rows;
+  float scale;
+  const unsigned* ready;
+  unsigned ready_target;
+  int num_sms;
+  Status* status;
+};
+
+cudaError_t launch_attention_fwd(const AttnArgs& a, cudaStream_t stream);
+
+}  // namespace plb

@@ -4,6 +4,7 @@
 
 #include <string.h>
 
+#include "attention.h"
 #include "decode.h"
 #include "kernels.h"
 
@@ -397,6 +398,43 @@ int plb_decode_attention_partial(const void* q, const void* k, const void* v, fl
   if (!q || !k || !v || !out || !lse || length < 0 || partitions < 1) return PLB_E_ARGUMENT;
   return from_cuda(plb::launch_attention_partial(q, k, v, out, lse, length, partitions, scale,
                                                  static_cast<cudaStream_t>(stream)));
+}
+
+int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
+                      const plb_attn_work* work, int num_work, int q_heads, int kv_heads, int seq_q,
+                      uint64_t q_rows, uint64_t kv_rows, float scale, const uint32_t* ready,
+                      uint32_t ready_target, plb_status* status, void* stream) {
+  static_assert(sizeof(plb_attn_work) == sizeof(plb::AttnWork), "work descriptor layouts differ");
+  if (!q || !k || !v || !out || !lse || !work || !status || num_work < 0) return PLB_E_ARGUMENT;
+  if (q_heads < 1 || kv_heads < 1 || q_heads % kv_heads || seq_q < 128 || seq_q % 128 ||
+      q_rows % 128 || kv_rows % 128)
+    return PLB_E_ARGUMENT;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return PLB_E_ARGUMENT;
+  plb::AttnArgs a;
+  a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
+  a.work = reinterpret_cast<const plb::AttnWork*>(work);
+  a.num_work = num_work;
+  a.q_heads = q_heads; a.kv_heads = kv_heads; a.seq_q = seq_q;
+  a.q_rows = q_rows; a.kv_rows = kv_rows;
+  a.scale = scale;
+  a.ready = ready; a.ready_target = ready_target;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(plb::launch_attention_fwd(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks, int64_t block_bytes,
+                   int rank, int world, void* const* k_gather_peers, void* const* v_gather_peers,
+                   void* const* ready_peers, int ctas, void* stream) {
+  if (!k_local || !v_local || !k_gather_peers || !v_gather_peers || !ready_peers) return PLB_E_ARGUMENT;
+  if (chunk_blocks < 0 || block_bytes <= 0 || block_bytes % 16 || world < 1 || rank < 0 ||
+      rank >= world || ctas < 1)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_cp_push_kv(k_local, v_local, chunk_blocks, block_bytes, rank, world,
+                                          k_gather_peers, v_gather_peers,
+                                          reinterpret_cast<unsigned* const*>(ready_peers), ctas,
+                                          static_cast<cudaStream_t>(stream)));
 }
 
 // ---- linked-image launcher (cudaLibrary API) and tensor-map helper for stage providers

@@ -117,11 +117,20 @@ __device__ void stage_vector(const __nv_bfloat16* __restrict__ src,
                              const __nv_bfloat16* __restrict__ norm_w, int n, float eps,
                              float* x, float* red) {
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    // plain (coherent) load: these activations were written by other SMs in this launch
-    const float v = ld_bf16_coherent(src + i);
-    x[i] = v;
-    ss += v * v;
+  // coherent 16-byte loads: these activations were written by other SMs in this launch
+  for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+    uint4 raw;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                 : "l"(src + i)
+                 : "memory");
+    const float f[8] = {blo(raw.x), bhi(raw.x), blo(raw.y), bhi(raw.y),
+                        blo(raw.z), bhi(raw.z), blo(raw.w), bhi(raw.w)};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      x[i + j] = f[j];
+      ss += f[j] * f[j];
+    }
   }
   if (norm_w == nullptr) {
     __syncthreads();
@@ -271,6 +280,33 @@ __device__ __forceinline__ void partition_range(int length, int partitions, int 
   if (begin > end) begin = end;
 }
 
+// L2 prefetch of the weight rows an instruction will stream.
+__device__ void prefetch_weights(const DecodeGlobals& g, const int* in) {
+  const int op = in[0], layer = in[1], a0 = in[2], a1 = in[3];
+  const __nv_bfloat16* wbase = nullptr;
+  const __nv_bfloat16* wbase2 = nullptr;
+  size_t wbytes = 0;
+  if (op == 1) { wbase = g.qkv_w + (static_cast<size_t>(layer) * kQkvRows + a0) * kHidden; wbytes = static_cast<size_t>(a1) * kHidden * 2; }
+  if (op == 4) { wbase = g.o_w + (static_cast<size_t>(layer) * kHidden + a0) * kHidden; wbytes = static_cast<size_t>(a1) * kHidden * 2; }
+  if (op == 5) {
+    wbase = g.gate_w + (static_cast<size_t>(layer) * kFfn + a0) * kHidden;
+    wbase2 = g.up_w + (static_cast<size_t>(layer) * kFfn + a0) * kHidden;
+    wbytes = static_cast<size_t>(a1) * kHidden * 2;
+  }
+  if (op == 6) { wbase = g.down_w + (static_cast<size_t>(layer) * kHidden + a0) * kFfn; wbytes = static_cast<size_t>(a1) * kFfn * 2; }
+  if (op == 7) {  // the LM head (525 MB) exceeds L2: only its first 512 KB per SM is worth prefetching
+    wbase = g.lm_head + static_cast<size_t>(a0) * kHidden;
+    wbytes = static_cast<size_t>(a1) * kHidden * 2;
+    if (wbytes > (512u << 10)) wbytes = 512u << 10;
+  }
+  if (wbase == nullptr) return;
+  const char* pa = reinterpret_cast<const char*>(wbase);
+  for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < wbytes; off += kDecThreads * 128) {
+    prefetch_l2(pa + off);
+    if (wbase2 != nullptr) prefetch_l2(reinterpret_cast<const char*>(wbase2) + off);
+  }
+}
+
 // ---------------------------------------------------------------- the interpreter
 __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const DecodeGlobals g) {
   extern __shared__ __align__(16) float dsm[];
@@ -289,24 +325,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const DecodeGlob
     const int dep = in[6], sig = in[8];
     const unsigned dep_target = static_cast<unsigned>(in[7]);
 
-    // which weight rows this instruction will stream (for the L2 prefetch while waiting)
-    const __nv_bfloat16* wbase = nullptr;
-    size_t wbytes = 0;
-    if (op == 1) { wbase = g.qkv_w + (static_cast<size_t>(layer) * kQkvRows + a0) * kHidden; wbytes = static_cast<size_t>(a1) * kHidden * 2; }
-    if (op == 4) { wbase = g.o_w + (static_cast<size_t>(layer) * kHidden + a0) * kHidden; wbytes = static_cast<size_t>(a1) * kHidden * 2; }
-    if (op == 5) { wbase = g.gate_w + (static_cast<size_t>(layer) * kFfn + a0) * kHidden; wbytes = static_cast<size_t>(a1) * kHidden * 2; }
-    if (op == 6) { wbase = g.down_w + (static_cast<size_t>(layer) * kHidden + a0) * kFfn; wbytes = static_cast<size_t>(a1) * kFfn * 2; }
-    if (op == 7) { wbase = g.lm_head + static_cast<size_t>(a0) * kHidden; wbytes = static_cast<size_t>(a1) * kHidden * 2; if (wbytes > (1u << 20)) wbytes = 1u << 20; }
-    if (wbase != nullptr) {
-      const char* pb = reinterpret_cast<const char*>(wbase);
-      for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < wbytes; off += kDecThreads * 128)
-        prefetch_l2(pb + off);
-      if (op == 5) {
-        const char* pu = reinterpret_cast<const char*>(g.up_w + (static_cast<size_t>(layer) * kFfn + a0) * kHidden);
-        for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < wbytes; off += kDecThreads * 128)
-          prefetch_l2(pu + off);
-      }
-    }
+    // Keep HBM busy across the dependency stalls: the first instruction prefetches its own
+    // weight rows into L2, every instruction prefetches the rows of the next one before it
+    // starts computing, so a matvec mostly reads L2 while HBM streams the following slice.
+    if (ip == 0) prefetch_weights(g, in);
+    if (ip + 1 < g.num_instructions) prefetch_weights(g, in + 32);
     if (dep >= 0) {
       if (!wait_counter(g.bars + dep, dep_target, g.status, op * 100 + layer)) return;
     }

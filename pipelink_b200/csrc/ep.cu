@@ -131,7 +131,76 @@ ep_pull_rows_kernel(const uint8_t* const* __restrict__ xq_peers,
   }
 }
 
+// Context-parallel K/V exchange: push this rank's 128-token K and V blocks into every
+// consumer's gathered (global-order) buffers and publish one counter per block.
+// Stand-in for kv_gather_role_gather (campaigns/attention/src/sm90/stage_kv_gather.cu:16-78)
+// with the primitives of examples/comm-overlap/comm/push_gather.cuh:80-103: all lanes copy with
+// 16-byte generic stores (loads batched before stores), then fence.acq_rel.sys and one
+// red.release.sys on the consumer's counter. Zigzag ownership (campaigns/attention/README.md:222-228):
+// rank r holds chunks r and 2W-1-r of 2W; the early chunk is needed by every rank, the late
+// chunk only by ranks <= r (causality), so tasks are (block, consumer) pairs in that set,
+// visited in descending global position (the blocks consumers wait for first).
+__global__ void __launch_bounds__(256)
+cp_push_kv_kernel(const uint4* __restrict__ k_local, const uint4* __restrict__ v_local,
+                  int chunk_blocks, int vec_per_block, int rank, int world,
+                  uint4* const* __restrict__ k_peers, uint4* const* __restrict__ v_peers,
+                  unsigned* const* __restrict__ ready_peers) {
+  // task order: late chunk (consumers 0..rank) first, then early chunk (all consumers)
+  const int late_tasks = chunk_blocks * (rank + 1);
+  const int total = late_tasks + chunk_blocks * world;
+  for (int t = blockIdx.x; t < total; t += gridDim.x) {
+    int local_block, consumer, global_block;
+    if (t < late_tasks) {
+      const int b = chunk_blocks - 1 - t / (rank + 1);  // descending position
+      consumer = t % (rank + 1);
+      local_block = chunk_blocks + b;
+      global_block = (2 * world - 1 - rank) * chunk_blocks + b;
+    } else {
+      const int u = t - late_tasks;
+      const int b = chunk_blocks - 1 - u / world;
+      consumer = u % world;
+      local_block = b;
+      global_block = rank * chunk_blocks + b;
+    }
+    const uint4* ks = k_local + static_cast<size_t>(local_block) * vec_per_block;
+    const uint4* vs = v_local + static_cast<size_t>(local_block) * vec_per_block;
+    uint4* kd = k_peers[consumer] + static_cast<size_t>(global_block) * vec_per_block;
+    uint4* vd = v_peers[consumer] + static_cast<size_t>(global_block) * vec_per_block;
+    for (int i0 = threadIdx.x; i0 < vec_per_block; i0 += blockDim.x * 4) {
+      uint4 a[4], b[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < vec_per_block) { a[u] = ks[i]; b[u] = vs[i]; }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < vec_per_block) { kd[i] = a[u]; vd[i] = b[u]; }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      fence_acq_rel_sys();
+      red_release_sys_add(ready_peers[consumer] + global_block, 1u);
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks,
+                              int64_t block_bytes, int rank, int world, void* const* k_peers,
+                              void* const* v_peers, unsigned* const* ready_peers, int ctas,
+                              cudaStream_t stream) {
+  if (chunk_blocks == 0) return cudaSuccess;
+  cp_push_kv_kernel<<<ctas, 256, 0, stream>>>(
+      static_cast<const uint4*>(k_local), static_cast<const uint4*>(v_local), chunk_blocks,
+      static_cast<int>(block_bytes >> 4), rank, world, reinterpret_cast<uint4* const*>(k_peers),
+      reinterpret_cast<uint4* const*>(v_peers), ready_peers);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_ep_barrier(unsigned* const* flags_peers, unsigned* state, int rank, int world,
                               Status* status, cudaStream_t stream) {

@@ -90,6 +90,10 @@ cudaError_t launch_ep_barrier(unsigned* const* flags_peers, unsigned* state, int
                               Status* status, cudaStream_t stream);
 cudaError_t launch_ep_publish(const void* src, int64_t bytes, void* const* dst_peers, int rank,
                               int world, cudaStream_t stream);
+cudaError_t launch_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks,
+                              int64_t block_bytes, int rank, int world, void* const* k_peers,
+                              void* const* v_peers, unsigned* const* ready_peers, int ctas,
+                              cudaStream_t stream);
 cudaError_t launch_ep_pull_rows(const void* const* xq_peers, const void* const* xsc_peers,
                                 const int* peer_rank, const int* peer_token_idx,
                                 const int* num_rows_dev, int64_t capacity, int hidden,

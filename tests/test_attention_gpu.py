@@ -1,0 +1,77 @@
+"""GPU parity for causal prefill attention (tcgen05) and its context-parallel composition.
+
+Inputs are the reference's Philox fixtures (U[-2,2) rounded to bf16); the oracle evaluates full
+visible keys for sampled rows (all rows for short sequences); the predicate is the reference's
+``|a - r| <= 0.02 + 0.02 |r|`` for O and LSE. Context parallel runs W ranks in one process on one
+GPU (all pushes, then each rank's attention) and must reproduce the single-GPU result bitwise."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oa
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(S, Hq, Hkv, case=0):
+    q = oa.philox_bf16(S * Hq * 128, case, 1).reshape(S, Hq, 128)
+    k = oa.philox_bf16(S * Hkv * 128, case, 2).reshape(S, Hkv, 128)
+    v = oa.philox_bf16(S * Hkv * 128, case, 3).reshape(S, Hkv, 128)
+    dev = lambda a: torch.from_numpy(a).to(torch.bfloat16).cuda()
+    return (q, k, v), (dev(q), dev(k), dev(v))
+
+
+@pytest.mark.parametrize("S,Hq,Hkv,rows", [(128, 1, 1, None), (256, 4, 1, None), (512, 8, 2, None), (1024, 4, 4, "boundary"),
+                                           (4096, 8, 2, "boundary")])
+def test_attention_vs_oracle(native_lib, S, Hq, Hkv, rows):
+    from pipelink_b200 import attention as att
+    (q, k, v), (dq, dk, dv) = _inputs(S, Hq, Hkv, case=S)
+    out, lse = att.attention_fwd(dq[None], dk[None], dv[None])
+    torch.cuda.synchronize()
+    sel = list(range(S)) if rows is None else oa.boundary_rows(S, extra=(S // 2 + 3, S - 130))
+    ref_o, ref_lse = oa.reference_rows(q, k, v, sel, 1.0 / np.sqrt(128.0))
+    got_o = out[0].float().cpu().numpy()[sel]
+    got_lse = lse.cpu().numpy()[:, sel]
+    assert np.isfinite(got_o).all()
+    assert oa.matches(got_o, ref_o) == 0, np.abs(got_o - ref_o).max()
+    assert oa.matches(got_lse, ref_lse) == 0, np.abs(got_lse - ref_lse).max()
+
+
+def test_attention_deterministic(native_lib):
+    from pipelink_b200 import attention as att
+    _, (dq, dk, dv) = _inputs(1024, 8, 2, case=7)
+    a, la = att.attention_fwd(dq[None], dk[None], dv[None])
+    b, lb = att.attention_fwd(dq[None], dk[None], dv[None])
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16)) and torch.equal(la, lb)
+
+
+@pytest.mark.parametrize("world,S", [(2, 1024), (4, 2048)])
+def test_context_parallel_matches_single_gpu(native_lib, world, S):
+    from pipelink_b200 import attention as att, ep
+    Hq, Hkv = 8, 2
+    (q, k, v), (dq, dk, dv) = _inputs(S, Hq, Hkv, case=world)
+    full_o, full_lse = att.attention_fwd(dq[None], dk[None], dv[None])
+    torch.cuda.synchronize()
+    layout = att.CpRank.slab_layout(S, Hkv)
+    slabs = [ep.sym_alloc(layout["nbytes"]) for _ in range(world)]
+    try:
+        ranks = [att.CpRank(S, Hq, Hkv, r, world, slabs, layout, "cuda") for r in range(world)]
+        for rnk in ranks:   # poison the gathered buffers: a block that was not pushed cannot look right
+            rnk.k_gather.fill_(float("nan"))
+            rnk.v_gather.fill_(float("nan"))
+        for step in range(2):   # two steps: counters advance by one per step and are never reset
+            for r, rnk in enumerate(ranks):
+                rnk.push(att.shard_zigzag(dk, world, r), att.shard_zigzag(dv, world, r))
+            for r, rnk in enumerate(ranks):
+                o, lse = rnk.attend(att.shard_zigzag(dq, world, r))
+                torch.cuda.synchronize()
+                rnk.status.check(f"cp rank {r}")
+                pos = torch.from_numpy(oa.zigzag_rows(S, world, r)).cuda()
+                assert torch.equal(o.view(torch.int16), full_o[0][pos].view(torch.int16)), (world, r, step)
+                assert torch.equal(lse, full_lse[:, pos])
+                assert (rnk.ready.cpu().numpy()[: (2 * world - r) * (S // (2 * world)) // 128] == step + 1).all()
+    finally:
+        torch.cuda.synchronize()
+        from pipelink_b200 import _lib
+        for p in slabs:
+            _lib.call("plb_sym_free", p)
