@@ -158,6 +158,42 @@ int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void*
                       const int32_t* dest_row, int64_t capacity, int experts, int inter, int hidden,
                       void* combine_bf16, plb_status* status, void* stream);
 
+/* ------------------------------------------------------------------ MoE backward
+ * plb_moe_gemm_gate_up_train: plb_moe_gemm_gate_up that also keeps what the backward pass reads,
+ * as the reference's forward does (gemm.cu:150-157 emits gate/up in bf16 and MXFP8; the act stage
+ * writes hidden in both orientations, act.cu:310-313): MXFP8 gate and up [capacity, inter] and the
+ * bf16 hidden that was quantised (its transposed quantisation is a plb_mxfp8_quantize call).
+ * plb_moe_bwd_dy: backward of the weighted combine for every scheduled row p = (t, slot):
+ *   d_y[p] = bf16(w[t, slot] * d_out[t]), d_w[t, slot] = <d_out[t], combine[t*k+slot]>; padding rows
+ *   and rows beyond *num_tokens become zeros (the whole capacity is defined afterwards).
+ * plb_moe_swiglu_bwd: swiglu_bwd_kernel (campaigns/mok/port/act_gptoss/swiglu.cuh:219-558, default
+ *   silu(g)*u math): d_gate_up bf16 [capacity, 2*inter] = [d_gate | d_up] from the saved MXFP8
+ *   gate / up and bf16 d_hidden.
+ * plb_moe_gather_rows: bf16 rows in schedule order (operand of the gate/up weight gradient).
+ * plb_moe_gemm_wgrad: the wgrad cases of expert_grouped_gemm_kernel (gemm.cu:166-243): for every
+ *   expert e, d_w[e] = A_t[:, rows of e] . B_t[:, rows of e]^T with both operands quantised along
+ *   the schedule-row dimension ([m_rows, capacity] and [n_rows, capacity]); an expert without rows
+ *   gets zeros (zero_empty_routed_wgrads, mok_port_host.py:218-220). d_w is bf16 [experts, m_rows, n_rows].
+ * The data gradients are plb_moe_gemm_down calls on transposed-quantised weights
+ * (d_hidden = d_y . W_down: inter := hidden, hidden := inter; d_x = d_gate_up . [W_gate; W_up]). */
+int plb_moe_gemm_gate_up_train(const void* x_routed_fp8, const void* x_routed_sc, const void* w13_fp8,
+                               const void* w13_sc, const int32_t* block_expert, const int32_t* num_tokens,
+                               int64_t capacity, int experts, int inter, int hidden, void* hidden_fp8,
+                               void* hidden_sc, void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc,
+                               void* hidden_bf16, plb_status* status, void* stream);
+int plb_moe_bwd_dy(const void* d_out_bf16, const void* combine_bf16, const float* router_weights,
+                   const int32_t* peer_rank, const int32_t* peer_token_idx, const int32_t* dest_row,
+                   const int32_t* num_tokens, int64_t capacity, int hidden, int topk, void* d_y_bf16,
+                   float* d_router_weights, void* stream);
+int plb_moe_swiglu_bwd(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                       const void* d_hidden_bf16, const int32_t* num_tokens, int64_t capacity, int inter,
+                       void* d_gate_up_bf16, void* stream);
+int plb_moe_gather_rows(const void* src_bf16, const int32_t* peer_rank, const int32_t* peer_token_idx,
+                        const int32_t* num_tokens, int64_t capacity, int cols, void* dst_bf16, void* stream);
+int plb_moe_gemm_wgrad(const void* a_t_fp8, const void* a_t_sc, const void* b_t_fp8, const void* b_t_sc,
+                       const int32_t* expert_offsets, int64_t capacity, int experts, int m_rows, int n_rows,
+                       void* d_w_bf16, plb_status* status, void* stream);
+
 /* ------------------------------------------------------------------ expert parallelism
  * One process per GPU; every rank owns tokens [tokens, hidden] and experts/world experts.
  * Peer-visible buffers are plain device allocations shared through CUDA IPC; "*_peers"

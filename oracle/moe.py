@@ -69,8 +69,9 @@ def dispatch(x_by_rank, sched):
     return q, sc
 
 
-def expert_ffn(xq, xsc, weights, sched, round_gate_up=True):
-    """Rows [total, H] quantised -> (hidden_q, hidden_sc, y bf16-valued fp32 [total, H])."""
+def expert_ffn(xq, xsc, weights, sched, round_gate_up=True, context=None):
+    """Rows [total, H] quantised -> (hidden_q, hidden_sc, y bf16-valued fp32 [total, H]).
+    `context` (a dict) receives the bf16 gate / up / hidden the backward pass differentiates through."""
     total, H = xq.shape
     gate_q, gate_sc = weights["gate"]
     up_q, up_sc = weights["up"]
@@ -82,6 +83,7 @@ def expert_ffn(xq, xsc, weights, sched, round_gate_up=True):
     wd = mxfp8.dequantize(down_q.reshape(E * H, I), down_sc).reshape(E, H, I)
     off = sched["expert_offsets"]
     hidden = np.zeros((total, I), dtype=np.float32)
+    gate_all, up_all = np.zeros((total, I), dtype=np.float32), np.zeros((total, I), dtype=np.float32)
     for e in range(E):
         lo, hi = int(off[e]), int(off[e + 1])
         if hi == lo:
@@ -90,7 +92,10 @@ def expert_ffn(xq, xsc, weights, sched, round_gate_up=True):
         u = _mm(x[lo:hi], wu[e])
         if round_gate_up:
             g, u = mxfp8.bf16_round(g), mxfp8.bf16_round(u)
+        gate_all[lo:hi], up_all[lo:hi] = g, u
         hidden[lo:hi] = mxfp8.bf16_round(silu_mul(g, u))
+    if context is not None:
+        context.update(gate=gate_all, up=up_all, hidden=hidden.copy())
     hq, hsc = mxfp8.quantize(hidden)
     hd = mxfp8.dequantize(hq, hsc)
     y = np.zeros((total, H), dtype=np.float32)
@@ -124,7 +129,7 @@ def fwd_epilogue(combine_buf, router_w, y_shared=None):
     return mxfp8.bf16_round(acc)
 
 
-def forward_single_rank(x, routes, router_w, weights, padding=128, capacity=None):
+def forward_single_rank(x, routes, router_w, weights, padding=128, capacity=None, context=None):
     """Whole forward on one rank. x fp32 (bf16 values) [T, H]; routes i32 [T, k]."""
     from . import routing
     T, k = routes.shape
@@ -133,7 +138,7 @@ def forward_single_rank(x, routes, router_w, weights, padding=128, capacity=None
         capacity = ((T * k + E * (padding - 1)) + 127) // 128 * 128
     sched = routing.build_schedule(routes[None], 0, E, capacity, padding)
     xq, xsc = dispatch([x], sched)
-    hq, hsc, y = expert_ffn(xq, xsc, weights, sched)
+    hq, hsc, y = expert_ffn(xq, xsc, weights, sched, context=context)
     buf = combine(y, sched, 0, T, k)
     out = fwd_epilogue(buf, router_w)
     return dict(schedule=sched, x_routed=(xq, xsc), hidden=(hq, hsc), y=y, combine=buf, output=out)
@@ -181,3 +186,59 @@ def forward_multi_rank(xs, routes, router_ws, weights, world, padding=128):
         hiddens.append((hq, hsc))
     outs = [fwd_epilogue(combine_bufs[r], router_ws[r]) for r in range(world)]
     return dict(outputs=outs, schedules=scheds, combine=combine_bufs, hidden=hiddens)
+
+
+def _deq_t(a):
+    """Transposed quantisation of a [R, C] -> dequantised [C, R]."""
+    return mxfp8.dequantize(*mxfp8.quantize_transposed(a))
+
+
+def backward_single_rank(x, router_w, w_gate, w_up, w_down, fwd, ctx, d_out):
+    """Backward of forward_single_rank with the same quantisation points as the device path:
+    d_y, d_hidden and [d_gate | d_up] are bf16 tensors quantised along the contraction dimension of
+    each GEMM that consumes them (normal orientation for data gradients, transposed for weight
+    gradients); weights enter the data gradients transposed-quantised
+    (campaigns/mok/port/gemm/gemm.cu:166-243, campaigns/mok/host/resources.py:62-77).
+    x, d_out fp32 [T, H]; w_* bf16-valued fp32; fwd / ctx from forward_single_rank(context=ctx)."""
+    sched = fwd["schedule"]
+    total = int(sched["num_tokens"][0])
+    off, pr, pt, dr = sched["expert_offsets"], sched["peer_rank"][:total], sched["peer_token_idx"][:total], sched["dest_row"][:total]
+    T, k = router_w.shape
+    E, I, H = w_gate.shape
+    live = pr >= 0
+    wflat = router_w.reshape(-1).astype(np.float32)
+    dy = np.zeros((total, H), np.float32)
+    dy[live] = mxfp8.bf16_round((wflat[dr[live]][:, None] * d_out[pt[live]]).astype(np.float32))
+    d_router = np.zeros(T * k, np.float32)
+    d_router[dr[live]] = (d_out[pt[live]].astype(np.float64) * fwd["combine"][dr[live]].astype(np.float64)).sum(axis=1)
+    dyd = mxfp8.dequantize(*mxfp8.quantize(dy))
+    dy_t, hid_t = _deq_t(dy), _deq_t(ctx["hidden"])
+    d_hidden = np.zeros((total, I), np.float32)
+    d_w_down = np.zeros((E, H, I), np.float32)
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            d_hidden[lo:hi] = mxfp8.bf16_round(_mm(dyd[lo:hi], _deq_t(w_down[e])))          # [rows, H] x [I, H]^T
+            d_w_down[e] = mxfp8.bf16_round(_mm(dy_t[:, lo:hi], hid_t[:, lo:hi]))            # [H, rows] x [I, rows]^T
+    g = mxfp8.dequantize(*mxfp8.quantize(ctx["gate"]))
+    u = mxfp8.dequantize(*mxfp8.quantize(ctx["up"]))
+    sg = (np.float32(1.0) / (np.float32(1.0) + np.exp(-g))).astype(np.float32)
+    d_up = d_hidden * (g * sg)
+    d_gate = d_hidden * u * sg * (np.float32(1.0) + g * (np.float32(1.0) - sg))
+    dgu = mxfp8.bf16_round(np.concatenate([d_gate, d_up], axis=1).astype(np.float32))
+    dgud = mxfp8.dequantize(*mxfp8.quantize(dgu))
+    rows = np.zeros((total, H), np.float32)
+    rows[live] = x[pt[live]]
+    dgu_t, x_t = _deq_t(dgu), _deq_t(rows)
+    d_x_buf = np.zeros((T * k, H), np.float32)
+    d_w_cat = np.zeros((E, 2 * I, H), np.float32)
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            dxr = mxfp8.bf16_round(_mm(dgud[lo:hi], _deq_t(np.concatenate([w_gate[e], w_up[e]]))))   # [rows, 2I] x [H, 2I]^T
+            sel = pr[lo:hi] >= 0
+            d_x_buf[dr[lo:hi][sel]] = dxr[sel]
+            d_w_cat[e] = mxfp8.bf16_round(_mm(dgu_t[:, lo:hi], x_t[:, lo:hi]))                       # [2I, rows] x [H, rows]^T
+    d_x = fwd_epilogue(d_x_buf, np.ones((T, k), np.float32))
+    return dict(d_x=d_x, d_router_weights=d_router.reshape(T, k), d_w_routed_gate=d_w_cat[:, :I], d_w_routed_up=d_w_cat[:, I:],
+                d_w_routed_down=d_w_down, d_hidden=d_hidden, d_gate_up=dgu, d_y=dy)

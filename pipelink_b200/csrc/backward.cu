@@ -1,0 +1,176 @@
+// HBM-bound stages of the MoE backward pass around the grouped GEMMs:
+//   * d_y rows: d_y[p] = w[t, slot] * d_out[t] for every scheduled row (the backward of the
+//     weighted combine, ops.bwd path of campaigns/mok/host/mok_port_host.py:207-219) and the
+//     router-weight gradient d_w[t, slot] = <d_out[t], y[t, slot]>;
+//   * SwiGLU backward (campaigns/mok/port/act_gptoss/swiglu.cuh:4-43,219-558, default variant
+//     silu(g) * u): dequantise the saved MXFP8 gate / up, d_up = d_h * silu(g),
+//     d_gate = d_h * u * sig(g) * (1 + g * (1 - sig(g))), written as bf16 [rows, 2I] = [d_gate | d_up];
+//   * row gather of bf16 tokens into schedule order (the operand of the gate/up weight gradient).
+// The quantisations these feed (both orientations) are plb_mxfp8_quantize calls on the host side.
+#include "kernels.h"
+#include "mxfp8.cuh"
+
+namespace plb {
+
+namespace {
+
+__device__ __forceinline__ float lo16(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi16(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// One warp per scheduled row.
+__global__ void __launch_bounds__(256)
+bwd_dy_kernel(const uint4* __restrict__ d_out, const uint4* __restrict__ y, const float* __restrict__ router_w,
+              const int* __restrict__ peer_rank, const int* __restrict__ peer_token_idx,
+              const int* __restrict__ dest_row, const int* __restrict__ num_rows_dev, int64_t capacity,
+              int hidden, int topk, uint4* __restrict__ dy, float* __restrict__ d_router_w) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  int64_t rows = *num_rows_dev;
+  if (rows > capacity) rows = capacity;
+  const int vecs = hidden >> 3;
+  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < rows; p += warps) {
+    uint4* dst = dy + p * vecs;
+    if (peer_rank[p] < 0) {
+      for (int v = lane; v < vecs; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const int64_t t = peer_token_idx[p];
+    const int64_t d = dest_row[p];
+    const float w = router_w[d];  // router weights are [tokens, topk] = indexed by token * topk + slot
+    const uint4* src = d_out + t * vecs;
+    const uint4* yr = y + d * vecs;
+    float dot = 0.0f;
+    for (int v = lane; v < vecs; v += 32) {
+      const uint4 g = src[v], yy = yr[v];
+      const float gf[8] = {lo16(g.x), hi16(g.x), lo16(g.y), hi16(g.y), lo16(g.z), hi16(g.z), lo16(g.w), hi16(g.w)};
+      const float yf[8] = {lo16(yy.x), hi16(yy.x), lo16(yy.y), hi16(yy.y), lo16(yy.z), hi16(yy.z), lo16(yy.w), hi16(yy.w)};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot = fmaf(gf[i], yf[i], dot);
+      uint4 o;
+      o.x = pack2(__fmul_rn(w, gf[0]), __fmul_rn(w, gf[1]));
+      o.y = pack2(__fmul_rn(w, gf[2]), __fmul_rn(w, gf[3]));
+      o.z = pack2(__fmul_rn(w, gf[4]), __fmul_rn(w, gf[5]));
+      o.w = pack2(__fmul_rn(w, gf[6]), __fmul_rn(w, gf[7]));
+      dst[v] = o;
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, s);
+    if (lane == 0) d_router_w[d] = dot;
+    (void)topk;
+  }
+}
+
+// One thread per 8 consecutive intermediate columns of one row.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ gate_sc,
+                  const uint8_t* __restrict__ up, const uint8_t* __restrict__ up_sc,
+                  const uint4* __restrict__ d_hidden, const int* __restrict__ num_rows_dev, int64_t capacity,
+                  int inter, uint4* __restrict__ dgu) {
+  int64_t rows = *num_rows_dev;
+  if (rows > capacity) rows = capacity;
+  const int vecs = inter >> 3;
+  const int64_t total = rows * vecs;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t col_blocks = inter >> 7;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total; v += stride) {
+    const int64_t r = v / vecs, j = v - r * vecs;
+    const size_t so = scale_offset(r, j >> 2, col_blocks);
+    const float gs = e8m0_value(gate_sc[so]), us = e8m0_value(up_sc[so]);
+    const uint2 gq = *reinterpret_cast<const uint2*>(gate + r * inter + j * 8);
+    const uint2 uq = *reinterpret_cast<const uint2*>(up + r * inter + j * 8);
+    const uint4 dh = d_hidden[v];
+    const float dhf[8] = {lo16(dh.x), hi16(dh.x), lo16(dh.y), hi16(dh.y), lo16(dh.z), hi16(dh.z), lo16(dh.w), hi16(dh.w)};
+    float dg[8], du[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t gb = ((i < 4 ? gq.x : gq.y) >> (8 * (i & 3))) & 0xFFu;
+      const uint32_t ub = ((i < 4 ? uq.x : uq.y) >> (8 * (i & 3))) & 0xFFu;
+      const float g = e4m3_to_float(gb) * gs, u = e4m3_to_float(ub) * us;
+      const float sg = 1.0f / (1.0f + __expf(-g));
+      du[i] = dhf[i] * (g * sg);
+      dg[i] = dhf[i] * u * sg * (1.0f + g * (1.0f - sg));
+    }
+    uint4 og, ou;
+    og.x = pack2(dg[0], dg[1]); og.y = pack2(dg[2], dg[3]); og.z = pack2(dg[4], dg[5]); og.w = pack2(dg[6], dg[7]);
+    ou.x = pack2(du[0], du[1]); ou.y = pack2(du[2], du[3]); ou.z = pack2(du[4], du[5]); ou.w = pack2(du[6], du[7]);
+    dgu[r * (2 * vecs) + j] = og;
+    dgu[r * (2 * vecs) + vecs + j] = ou;
+  }
+}
+
+// Rows beyond the live schedule are zero-filled so the transposed quantisation that follows
+// sees defined values over the whole capacity.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ peer_rank,
+                   const int* __restrict__ peer_token_idx, const int* __restrict__ num_rows_dev,
+                   int64_t capacity, int vecs, uint4* __restrict__ dst) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t rows = *num_rows_dev;
+  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < capacity; p += warps) {
+    const bool live = p < rows && peer_rank[p] >= 0;
+    const uint4* s = live ? src + static_cast<int64_t>(peer_token_idx[p]) * vecs : nullptr;
+    for (int v = lane; v < vecs; v += 32) dst[p * vecs + v] = live ? s[v] : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// Zero rows [*num_rows, capacity) of a bf16 [capacity, cols] tensor.
+__global__ void __launch_bounds__(256)
+zero_tail_kernel(uint4* __restrict__ t, const int* __restrict__ num_rows_dev, int64_t capacity, int vecs) {
+  const int64_t begin = static_cast<int64_t>(*num_rows_dev) * vecs, end = capacity * vecs;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < end; i += stride)
+    t[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+int sm_grid(int mult) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms * mult;
+}
+
+}  // namespace
+
+cudaError_t launch_bwd_dy(const void* d_out, const void* y, const float* router_w, const int* peer_rank,
+                          const int* peer_token_idx, const int* dest_row, const int* num_rows_dev,
+                          int64_t capacity, int hidden, int topk, void* dy, float* d_router_w,
+                          cudaStream_t stream) {
+  if (capacity == 0) return cudaSuccess;
+  bwd_dy_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const uint4*>(d_out), static_cast<const uint4*>(y),
+                                                router_w, peer_rank, peer_token_idx, dest_row, num_rows_dev,
+                                                capacity, hidden, topk, static_cast<uint4*>(dy), d_router_w);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  zero_tail_kernel<<<sm_grid(2), 256, 0, stream>>>(static_cast<uint4*>(dy), num_rows_dev, capacity, hidden >> 3);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_bwd(const void* gate, const void* gate_sc, const void* up, const void* up_sc,
+                              const void* d_hidden, const int* num_rows_dev, int64_t capacity, int inter,
+                              void* dgu, cudaStream_t stream) {
+  if (capacity == 0) return cudaSuccess;
+  swiglu_bwd_kernel<<<sm_grid(8), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(gate), static_cast<const uint8_t*>(gate_sc), static_cast<const uint8_t*>(up),
+      static_cast<const uint8_t*>(up_sc), static_cast<const uint4*>(d_hidden), num_rows_dev, capacity, inter,
+      static_cast<uint4*>(dgu));
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  zero_tail_kernel<<<sm_grid(2), 256, 0, stream>>>(static_cast<uint4*>(dgu), num_rows_dev, capacity, (2 * inter) >> 3);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const void* src, const int* peer_rank, const int* peer_token_idx,
+                               const int* num_rows_dev, int64_t capacity, int cols, void* dst,
+                               cudaStream_t stream) {
+  if (capacity == 0) return cudaSuccess;
+  gather_rows_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const uint4*>(src), peer_rank, peer_token_idx,
+                                                     num_rows_dev, capacity, cols >> 3, static_cast<uint4*>(dst));
+  return cudaGetLastError();
+}
+
+}  // namespace plb

@@ -400,6 +400,79 @@ int plb_decode_attention_partial(const void* q, const void* k, const void* v, fl
                                                  static_cast<cudaStream_t>(stream)));
 }
 
+int plb_moe_gemm_gate_up_train(const void* x_routed_fp8, const void* x_routed_sc, const void* w13_fp8,
+                               const void* w13_sc, const int32_t* block_expert, const int32_t* num_tokens,
+                               int64_t capacity, int experts, int inter, int hidden, void* hidden_fp8,
+                               void* hidden_sc, void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc,
+                               void* hidden_bf16, plb_status* status, void* stream) {
+  if (g_gemm_variant != 2) return PLB_E_CONTRACT;  // the saving epilogue exists in the CTA-pair kernel
+  if (capacity < 0 || capacity % 256 || experts < 1 || inter < 256 || inter % 256 || hidden < 256 || hidden % 256)
+    return PLB_E_ARGUMENT;
+  if (!x_routed_fp8 || !x_routed_sc || !w13_fp8 || !w13_sc || !block_expert || !num_tokens || !hidden_fp8 ||
+      !hidden_sc || !gate_fp8 || !gate_sc || !up_fp8 || !up_sc || !hidden_bf16 || !status)
+    return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.a_fp8 = x_routed_fp8; a.a_sc = x_routed_sc; a.b_fp8 = w13_fp8; a.b_sc = w13_sc;
+  a.rows_capacity = capacity; a.experts = experts; a.n_rows = 2 * inter; a.K = hidden;
+  a.block_expert = block_expert; a.num_rows_dev = num_tokens; a.mode = 0;
+  a.out = hidden_fp8; a.out_sc = hidden_sc; a.dest_row = nullptr;
+  a.save_gate = gate_fp8; a.save_gate_sc = gate_sc; a.save_up = up_fp8; a.save_up_sc = up_sc;
+  a.save_hidden = hidden_bf16;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_gemm_wgrad(const void* a_t_fp8, const void* a_t_sc, const void* b_t_fp8, const void* b_t_sc,
+                       const int32_t* expert_offsets, int64_t capacity, int experts, int m_rows, int n_rows,
+                       void* d_w_bf16, plb_status* status, void* stream) {
+  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
+  if (capacity < 0 || capacity % 256 || experts < 1 || m_rows < 256 || m_rows % 256 || n_rows < 256 || n_rows % 256)
+    return PLB_E_ARGUMENT;
+  if (!a_t_fp8 || !a_t_sc || !b_t_fp8 || !b_t_sc || !expert_offsets || !d_w_bf16 || !status) return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.a_fp8 = a_t_fp8; a.a_sc = a_t_sc; a.b_fp8 = b_t_fp8; a.b_sc = b_t_sc;
+  a.rows_capacity = capacity; a.experts = experts; a.n_rows = n_rows; a.m_rows = m_rows; a.K = 0;
+  a.block_expert = nullptr; a.num_rows_dev = nullptr; a.mode = 2;
+  a.out = d_w_bf16; a.out_sc = nullptr; a.dest_row = nullptr;
+  a.expert_offsets = expert_offsets;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(plb::launch_grouped_gemm_pair(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_bwd_dy(const void* d_out_bf16, const void* combine_bf16, const float* router_weights,
+                   const int32_t* peer_rank, const int32_t* peer_token_idx, const int32_t* dest_row,
+                   const int32_t* num_tokens, int64_t capacity, int hidden, int topk, void* d_y_bf16,
+                   float* d_router_weights, void* stream) {
+  if (!d_out_bf16 || !combine_bf16 || !router_weights || !peer_rank || !peer_token_idx || !dest_row ||
+      !num_tokens || !d_y_bf16 || !d_router_weights || capacity < 0 || hidden <= 0 || hidden % 8 || topk < 1)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_bwd_dy(d_out_bf16, combine_bf16, router_weights, peer_rank, peer_token_idx,
+                                      dest_row, num_tokens, capacity, hidden, topk, d_y_bf16, d_router_weights,
+                                      static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_swiglu_bwd(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                       const void* d_hidden_bf16, const int32_t* num_tokens, int64_t capacity, int inter,
+                       void* d_gate_up_bf16, void* stream) {
+  if (!gate_fp8 || !gate_sc || !up_fp8 || !up_sc || !d_hidden_bf16 || !num_tokens || !d_gate_up_bf16 ||
+      capacity < 0 || capacity % 128 || inter <= 0 || inter % 128)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_swiglu_bwd(gate_fp8, gate_sc, up_fp8, up_sc, d_hidden_bf16, num_tokens, capacity,
+                                          inter, d_gate_up_bf16, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_gather_rows(const void* src_bf16, const int32_t* peer_rank, const int32_t* peer_token_idx,
+                        const int32_t* num_tokens, int64_t capacity, int cols, void* dst_bf16, void* stream) {
+  if (!src_bf16 || !peer_rank || !peer_token_idx || !num_tokens || !dst_bf16 || capacity < 0 || cols <= 0 || cols % 8)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_gather_rows(src_bf16, peer_rank, peer_token_idx, num_tokens, capacity, cols,
+                                           dst_bf16, static_cast<cudaStream_t>(stream)));
+}
+
 int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
                       const plb_attn_work* work, int num_work, int q_heads, int kv_heads, int seq_q,
                       uint64_t q_rows, uint64_t kv_rows, float scale, const uint32_t* ready,

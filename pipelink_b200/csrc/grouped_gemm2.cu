@@ -104,7 +104,58 @@ struct Params2 {
   uint8_t* const* out_peers;
   const int* peer_rank;
   Status* status;
+  // mode 0, training: also keep what the backward pass reads (any of these may be null)
+  uint8_t* save_gate;      // E4M3 [rows, I]
+  uint8_t* save_gate_sc;
+  uint8_t* save_up;
+  uint8_t* save_up_sc;
+  __nv_bfloat16* save_hidden;  // bf16 [rows, I], the value that was quantised
+  // mode 2 (weight gradients): per expert e, out[e] = A[:, seg_e] . B[:, seg_e]^T with the
+  // contraction over that expert's rows of the schedule
+  const int* expert_offsets;  // [experts + 1]
+  int experts;
+  int m_tiles;                // A rows / 256
+  int k_blocks_total;         // contraction length of the whole tensors / 128
 };
+
+// What one tile means for the loads and the epilogue, identical for every role.
+struct Tile {
+  int a_blk;     // 128-row block of A loaded by this CTA
+  int b_blk0;    // first of the tile's two 128-row blocks of B
+  int k_blk0;    // first 128-byte K block
+  int k_steps;
+  int k_pitch;   // K blocks per row block in the scale tensors
+  int n_tile;    // output column tile
+  int64_t out_row0;  // first output row of the pair's tile (CTA adds rank*128 + quad*32 + lane)
+};
+
+template <int MODE>
+__device__ __forceinline__ Tile decode_tile(const Params2& p, int tile, int cta_rank) {
+  Tile t;
+  if (MODE == 2) {
+    const int per_expert = p.m_tiles * p.n_tiles;
+    const int e = tile / per_expert, r = tile - e * per_expert;
+    const int m_tile = r / p.n_tiles;
+    t.n_tile = r - m_tile * p.n_tiles;
+    t.a_blk = m_tile * 2 + cta_rank;
+    t.b_blk0 = t.n_tile * 2;
+    t.k_blk0 = p.expert_offsets[e] >> 7;
+    t.k_steps = (p.expert_offsets[e + 1] - p.expert_offsets[e]) >> 7;
+    t.k_pitch = p.k_blocks_total;
+    t.out_row0 = (static_cast<int64_t>(e) * p.m_tiles + m_tile) * 256;
+  } else {
+    const int m_tile = tile / p.n_tiles;
+    t.n_tile = tile - m_tile * p.n_tiles;
+    const int expert = p.block_expert[m_tile * 2];
+    t.a_blk = m_tile * 2 + cta_rank;
+    t.b_blk0 = (expert * p.n_tiles + t.n_tile) * 2;
+    t.k_blk0 = 0;
+    t.k_steps = p.k_steps;
+    t.k_pitch = p.k_steps;
+    t.out_row0 = static_cast<int64_t>(m_tile) * 256;
+  }
+  return t;
+}
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ uint32_t pack_bf16(uint32_t a_bits, uint32_t b_bits) {
@@ -123,6 +174,35 @@ __device__ __forceinline__ uint32_t swiglu_quant32(const uint32_t* g, const uint
     const float uf = bf16r(__uint_as_float(u[i]));
     const float s = __fdividef(gf, 1.0f + __expf(-gf));
     h[i] = bf16r(s * uf);
+    amax = fmaxf(amax, fabsf(h[i]));
+  }
+  const uint32_t e = e8m0_from_amax(amax);
+  const float inv = e8m0_inverse(e);
+  q0.x = cvt_e4m3x4(h[0] * inv, h[1] * inv, h[2] * inv, h[3] * inv);
+  q0.y = cvt_e4m3x4(h[4] * inv, h[5] * inv, h[6] * inv, h[7] * inv);
+  q0.z = cvt_e4m3x4(h[8] * inv, h[9] * inv, h[10] * inv, h[11] * inv);
+  q0.w = cvt_e4m3x4(h[12] * inv, h[13] * inv, h[14] * inv, h[15] * inv);
+  q1.x = cvt_e4m3x4(h[16] * inv, h[17] * inv, h[18] * inv, h[19] * inv);
+  q1.y = cvt_e4m3x4(h[20] * inv, h[21] * inv, h[22] * inv, h[23] * inv);
+  q1.z = cvt_e4m3x4(h[24] * inv, h[25] * inv, h[26] * inv, h[27] * inv);
+  q1.w = cvt_e4m3x4(h[28] * inv, h[29] * inv, h[30] * inv, h[31] * inv);
+  return e;
+}
+
+// hidden value of one element pair exactly as swiglu_quant32 computes it (bf16-valued float)
+__device__ __forceinline__ float swiglu_bf16(uint32_t g_bits, uint32_t u_bits) {
+  const float gf = bf16r(__uint_as_float(g_bits));
+  const float uf = bf16r(__uint_as_float(u_bits));
+  return bf16r(__fdividef(gf, 1.0f + __expf(-gf)) * uf);
+}
+
+// 32 accumulator values -> bf16 round -> MXFP8 block (two uint4 of E4M3 + scale byte)
+__device__ __forceinline__ uint32_t quant32_bf16(const uint32_t* a, uint4& q0, uint4& q1) {
+  float h[32];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    h[i] = bf16r(__uint_as_float(a[i]));
     amax = fmaxf(amax, fabsf(h[i]));
   }
   const uint32_t e = e8m0_from_amax(amax);
@@ -158,9 +238,14 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
-  int m_tiles = *p.num_rows_dev >> 8;
-  if (m_tiles > p.max_m_tiles) m_tiles = p.max_m_tiles;
-  const int total_tiles = m_tiles * p.n_tiles;
+  int total_tiles;
+  if (MODE == 2) {
+    total_tiles = p.experts * p.m_tiles * p.n_tiles;
+  } else {
+    int m_tiles = *p.num_rows_dev >> 8;
+    if (m_tiles > p.max_m_tiles) m_tiles = p.max_m_tiles;
+    total_tiles = m_tiles * p.n_tiles;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -197,13 +282,10 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       PROF_DECL(t_empty);
       PROF_T0(t_begin);
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-        const int m_tile = tile / p.n_tiles;
-        const int n_tile = tile - m_tile * p.n_tiles;
-        const int expert = p.block_expert[m_tile * 2];
-        const int a_blk = m_tile * 2 + static_cast<int>(cta_rank);             // 128-row block of A
-        const int b_blk0 = (expert * p.n_tiles + n_tile) * 2;                  // first 128-row block of B
+        const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank));
+        const int a_blk = t.a_blk, b_blk0 = t.b_blk0;
         const int b_blk = b_blk0 + static_cast<int>(cta_rank);
-        for (int kb = 0; kb < p.k_steps; ++kb) {
+        for (int kb = 0; kb < t.k_steps; ++kb) {
           PROF_T0(t0);
           if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY,
                          stage)) {
@@ -214,14 +296,15 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t full = mapa_shared(smem_u32(&bars->full[stage]), 0);
           mbar_arrive_expect_tx_cluster(full, kStageTx);
           const uint32_t sf = smem_base + kOffSf + stage * kSfStageBytes;
-          tma_load_2d_pair(smem_base + kOffA + stage * kTileBytes, &map_a, full, kb * 128,
+          const int kk = t.k_blk0 + kb;
+          tma_load_2d_pair(smem_base + kOffA + stage * kTileBytes, &map_a, full, kk * 128,
                            a_blk * 128);
-          tma_load_2d_pair(smem_base + kOffB + stage * kTileBytes, &map_b, full, kb * 128,
+          tma_load_2d_pair(smem_base + kOffB + stage * kTileBytes, &map_b, full, kk * 128,
                            b_blk * 128);
 #ifndef PLB_EXP_NOSF
-          tma_load_2d_pair(sf, &map_sfa, full, 0, a_blk * p.k_steps + kb);
-          tma_load_2d_pair(sf + kSfBytes, &map_sfb, full, 0, b_blk0 * p.k_steps + kb);
-          tma_load_2d_pair(sf + 2 * kSfBytes, &map_sfb, full, 0, (b_blk0 + 1) * p.k_steps + kb);
+          tma_load_2d_pair(sf, &map_sfa, full, 0, a_blk * t.k_pitch + kk);
+          tma_load_2d_pair(sf + kSfBytes, &map_sfb, full, 0, b_blk0 * t.k_pitch + kk);
+          tma_load_2d_pair(sf + 2 * kSfBytes, &map_sfb, full, 0, (b_blk0 + 1) * t.k_pitch + kk);
 #endif
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -246,6 +329,8 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       PROF_DECL(t_full);
       PROF_T0(t_begin);
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
+        const Tile t = decode_tile<MODE>(p, tile, 0);
+        if (t.k_steps == 0) continue;  // empty expert: the epilogue writes zeros on its own
         PROF_T0(ta);
         if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY,
                        0)) {
@@ -254,7 +339,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         PROF_ADD(t_acc, ta);
         tc_fence_after();
-        for (int kb = 0; kb < p.k_steps; ++kb) {
+        for (int kb = 0; kb < t.k_steps; ++kb) {
           PROF_T0(tf);
           if (!mbar_wait(smem_u32(&bars->full[stage]), phase, p.status, ST_TIMEOUT_FULL, stage)) {
             ok = false;
@@ -310,8 +395,16 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     PROF_DECL(t_drain);
     PROF_DECL(t_work);
     for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-      const int m_tile = tile / p.n_tiles;
-      const int n_tile = tile - m_tile * p.n_tiles;
+      const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank));
+      const int n_tile = t.n_tile;
+      const int64_t row = t.out_row0 + cta_rank * 128 + quad * 32 + lane;
+      if (MODE == 2 && t.k_steps == 0) {
+        // an expert with no rows: its weight gradient is zero; no accumulator was produced
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (row * p.out_cols + n_tile * 256 + ch * 128) * 2);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+        continue;
+      }
       PROF_T0(tw);
       if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, p.status, ST_TIMEOUT_TMEM_FULL, 0))
         ok = false;
@@ -320,7 +413,6 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       PROF_ADD(t_wait, tw);
       PROF_T0(td);
       tc_fence_after();
-      const int64_t row = static_cast<int64_t>(m_tile) * 256 + cta_rank * 128 + quad * 32 + lane;
       if (MODE == 0) {
         uint32_t g0[32], g1[32], u0[32], u1[32];
         tc_ld_32x32b_x32(taddr + ch * 64, g0);
@@ -333,6 +425,31 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         PROF_ADD(t_drain, td);
         PROF_T0(tm);
+        const size_t elem0 = static_cast<size_t>(row) * p.out_cols + n_tile * 128 + ch * 64;
+        const size_t sc_off = scale_offset(row, n_tile * 4 + ch * 2, p.out_cols >> 7);
+        if (p.save_gate != nullptr) {
+          // training: the bf16-rounded gate and up values the backward pass differentiates through,
+          // stored as MXFP8 (campaigns/mok/port/gemm/gemm.cu:150-157 emits the same tensors)
+          uint4 a0, a1, a2, a3;
+          const uint32_t sg0 = quant32_bf16(g0, a0, a1);
+          const uint32_t sg1 = quant32_bf16(g1, a2, a3);
+          uint4* gd = reinterpret_cast<uint4*>(p.save_gate + elem0);
+          gd[0] = a0; gd[1] = a1; gd[2] = a2; gd[3] = a3;
+          *reinterpret_cast<uint16_t*>(p.save_gate_sc + sc_off) = static_cast<uint16_t>(sg0 | (sg1 << 8));
+          const uint32_t su0 = quant32_bf16(u0, a0, a1);
+          const uint32_t su1 = quant32_bf16(u1, a2, a3);
+          uint4* ud = reinterpret_cast<uint4*>(p.save_up + elem0);
+          ud[0] = a0; ud[1] = a1; ud[2] = a2; ud[3] = a3;
+          *reinterpret_cast<uint16_t*>(p.save_up_sc + sc_off) = static_cast<uint16_t>(su0 | (su1 << 8));
+        }
+        if (p.save_hidden != nullptr) {
+          uint32_t* hd = reinterpret_cast<uint32_t*>(p.save_hidden + elem0);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            hd[i >> 1] = pack_bf16(__float_as_uint(swiglu_bf16(g0[i], u0[i])), __float_as_uint(swiglu_bf16(g0[i + 1], u0[i + 1])));
+            hd[16 + (i >> 1)] = pack_bf16(__float_as_uint(swiglu_bf16(g1[i], u1[i])), __float_as_uint(swiglu_bf16(g1[i + 1], u1[i + 1])));
+          }
+        }
         uint4 q0, q1, q2, q3;
         const uint32_t e0 = swiglu_quant32(g0, u0, q0, q1);
         const uint32_t e1 = swiglu_quant32(g1, u1, q2, q3);
@@ -365,7 +482,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
           w[32 + i] = pack_bf16(v2[2 * i], v2[2 * i + 1]);
           w[48 + i] = pack_bf16(v3[2 * i], v3[2 * i + 1]);
         }
-        const int dest = p.dest_row[row];
+        const int dest = MODE == 2 ? static_cast<int>(row) : p.dest_row[row];
         const int pr = (p.out_peers != nullptr && dest >= 0) ? p.peer_rank[row] : 0;
         const size_t col_byte = (static_cast<size_t>(n_tile) * 256 + ch * 128) * 2;
 #pragma unroll
@@ -470,17 +587,24 @@ bool encode_scales(CUtensorMap* map, const void* base, uint64_t blocks) {
 
 // Requirements beyond launch_grouped_gemm: rows_capacity, every expert segment and
 // n_rows are multiples of 256; mode 0 weights are interleaved in blocks of 128 rows.
+// Mode 2 (weight gradients): a_fp8 is [m_rows, rows_capacity] and b_fp8 [n_rows, rows_capacity],
+// both quantised along the schedule-row dimension; out is bf16 [experts, m_rows, n_rows].
 cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stream) {
-  if (a.rows_capacity % 256 || a.n_rows % 256 || a.K % 128 || a.K <= 0 || a.n_rows <= 0)
+  if (a.rows_capacity % 256 || a.n_rows % 256 || a.n_rows <= 0) return cudaErrorInvalidValue;
+  if (a.mode == 2) {
+    if (a.m_rows % 256 || a.m_rows <= 0 || a.expert_offsets == nullptr) return cudaErrorInvalidValue;
+  } else if (a.K % 128 || a.K <= 0) {
     return cudaErrorInvalidValue;
+  }
   if (a.rows_capacity == 0 || a.experts == 0) return cudaSuccess;
   CUtensorMap map_a, map_b, map_sfa, map_sfb;
-  const uint64_t k_steps = a.K / 128;
-  if (!encode_operand(&map_a, a.a_fp8, static_cast<uint64_t>(a.rows_capacity), a.K) ||
-      !encode_operand(&map_b, a.b_fp8, static_cast<uint64_t>(a.experts) * a.n_rows, a.K) ||
-      !encode_scales(&map_sfa, a.a_sc, static_cast<uint64_t>(a.rows_capacity / 128) * k_steps) ||
-      !encode_scales(&map_sfb, a.b_sc,
-                     static_cast<uint64_t>(a.experts) * (a.n_rows / 128) * k_steps))
+  const uint64_t k_len = a.mode == 2 ? static_cast<uint64_t>(a.rows_capacity) : static_cast<uint64_t>(a.K);
+  const uint64_t k_steps = k_len / 128;
+  const uint64_t a_rows = a.mode == 2 ? static_cast<uint64_t>(a.m_rows) : static_cast<uint64_t>(a.rows_capacity);
+  const uint64_t b_rows = a.mode == 2 ? static_cast<uint64_t>(a.n_rows) : static_cast<uint64_t>(a.experts) * a.n_rows;
+  if (!encode_operand(&map_a, a.a_fp8, a_rows, k_len) || !encode_operand(&map_b, a.b_fp8, b_rows, k_len) ||
+      !encode_scales(&map_sfa, a.a_sc, (a_rows / 128) * k_steps) ||
+      !encode_scales(&map_sfb, a.b_sc, (b_rows / 128) * k_steps))
     return cudaErrorInvalidValue;
   Params2 p;
   p.prof = static_cast<long long*>(a.profile);
@@ -496,22 +620,31 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
   p.out_peers = reinterpret_cast<uint8_t* const*>(a.out_peers);
   p.peer_rank = a.peer_rank;
   p.status = a.status;
+  p.save_gate = static_cast<uint8_t*>(a.save_gate);
+  p.save_gate_sc = static_cast<uint8_t*>(a.save_gate_sc);
+  p.save_up = static_cast<uint8_t*>(a.save_up);
+  p.save_up_sc = static_cast<uint8_t*>(a.save_up_sc);
+  p.save_hidden = static_cast<__nv_bfloat16*>(a.save_hidden);
+  p.expert_offsets = a.expert_offsets;
+  p.experts = a.experts;
+  p.m_tiles = a.mode == 2 ? a.m_rows / 256 : 0;
+  p.k_blocks_total = static_cast<int>(k_steps);
   const int grid = a.num_sms & ~1;
   if (grid < 2) return cudaErrorInvalidValue;
   cudaError_t err;
+#define PLB_LAUNCH_PAIR(M)                                                                              \
+  err = cudaFuncSetAttribute(grouped_gemm2_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                             kSmemBytes2);                                                              \
+  if (err != cudaSuccess) return err;                                                                   \
+  grouped_gemm2_kernel<M><<<grid, kThreads2, kSmemBytes2, stream>>>(map_a, map_b, map_sfa, map_sfb, p)
   if (a.mode == 0) {
-    err = cudaFuncSetAttribute(grouped_gemm2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               kSmemBytes2);
-    if (err != cudaSuccess) return err;
-    grouped_gemm2_kernel<0><<<grid, kThreads2, kSmemBytes2, stream>>>(map_a, map_b, map_sfa,
-                                                                     map_sfb, p);
+    PLB_LAUNCH_PAIR(0);
+  } else if (a.mode == 1) {
+    PLB_LAUNCH_PAIR(1);
   } else {
-    err = cudaFuncSetAttribute(grouped_gemm2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               kSmemBytes2);
-    if (err != cudaSuccess) return err;
-    grouped_gemm2_kernel<1><<<grid, kThreads2, kSmemBytes2, stream>>>(map_a, map_b, map_sfa,
-                                                                     map_sfb, p);
+    PLB_LAUNCH_PAIR(2);
   }
+#undef PLB_LAUNCH_PAIR
   return cudaGetLastError();
 }
 

@@ -79,11 +79,32 @@ struct GroupedGemmArgs {
   int num_sms;
   Status* status;
   void* profile = nullptr;  // cycle counters [grid, 16] i64, written only by profiling builds
+  // mode 0, training (pair variant): MXFP8 gate / up and bf16 hidden kept for the backward pass
+  void* save_gate = nullptr;
+  void* save_gate_sc = nullptr;
+  void* save_up = nullptr;
+  void* save_up_sc = nullptr;
+  void* save_hidden = nullptr;
+  // mode 2 (pair variant): weight gradients, contraction over each expert's schedule rows
+  const int* expert_offsets = nullptr;
+  int m_rows = 0;
 };
 cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);
 // CTA-pair variant (grouped_gemm2.cu): 256-row tiles, mode 0 weights interleaved per 128 rows.
 cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stream);
 int grouped_gemm_smem_bytes();
+
+// ---- backward-pass stages (backward.cu)
+cudaError_t launch_bwd_dy(const void* d_out, const void* y, const float* router_w, const int* peer_rank,
+                          const int* peer_token_idx, const int* dest_row, const int* num_rows_dev,
+                          int64_t capacity, int hidden, int topk, void* dy, float* d_router_w,
+                          cudaStream_t stream);
+cudaError_t launch_swiglu_bwd(const void* gate, const void* gate_sc, const void* up, const void* up_sc,
+                              const void* d_hidden, const int* num_rows_dev, int64_t capacity, int inter,
+                              void* dgu, cudaStream_t stream);
+cudaError_t launch_gather_rows(const void* src, const int* peer_rank, const int* peer_token_idx,
+                               const int* num_rows_dev, int64_t capacity, int cols, void* dst,
+                               cudaStream_t stream);
 
 // ---- expert-parallel plumbing (ep.cu)
 cudaError_t launch_ep_barrier(unsigned* const* flags_peers, unsigned* state, int rank, int world,

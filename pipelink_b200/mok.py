@@ -178,8 +178,10 @@ class MoKHost:
 
     # ------------------------------------------------------------------ weights
     def load_weights(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
-                     keep_unpacked: bool = True):
-        """bf16 [E, I, H], [E, I, H], [E, H, I] for this rank's experts."""
+                     keep_unpacked: bool = True, train: bool = False):
+        """bf16 [E, I, H], [E, I, H], [E, H, I] for this rank's experts. ``train=True`` also
+        prepares the transposed-quantised weights the data gradients contract with
+        (``w_routed_*_t`` of campaigns/mok/host/resources.py:75-77)."""
         E, I, H = self.num_local_experts, self.shape.intermediate, self.shape.hidden
         if tuple(w_gate.shape) != (E, I, H) or tuple(w_up.shape) != (E, I, H) or tuple(w_down.shape) != (E, H, I):
             raise ValueError("weight shapes disagree with the session shape")
@@ -187,6 +189,21 @@ class MoKHost:
         uq, usc, _, _ = mxfp8_quantize(w_up.contiguous())
         dq, dsc, _, _ = mxfp8_quantize(w_down.contiguous())
         self.load_quantized_weights(gq, gsc, uq, usc, dq, dsc, keep_unpacked=keep_unpacked)
+        if train:
+            u8 = dict(dtype=torch.uint8, device=self.device)
+            wdt = torch.empty((E, I, H), **u8)                       # W_down^T, blocks along H
+            wdt_sc = torch.empty((E * I // 128, H // 128, 32, 16), **u8)
+            wct = torch.empty((E, H, 2 * I), **u8)                   # [W_gate; W_up]^T, blocks along 2I
+            wct_sc = torch.empty((E * H // 128, 2 * I // 128, 32, 16), **u8)
+            for e in range(E):
+                _, _, t, tsc = mxfp8_quantize(w_down[e].contiguous(), False, True)
+                wdt[e].copy_(t)
+                wdt_sc[e * I // 128:(e + 1) * I // 128].copy_(tsc)
+                _, _, t, tsc = mxfp8_quantize(torch.cat([w_gate[e], w_up[e]]).contiguous(), False, True)
+                wct[e].copy_(t)
+                wct_sc[e * H // 128:(e + 1) * H // 128].copy_(tsc)
+            self.weights.update(w_down_t_fp8=wdt, w_down_t_sc=wdt_sc, w_cat_t_fp8=wct, w_cat_t_sc=wct_sc)
+            self._alloc_train_buffers()
 
     def load_quantized_weights(self, gq, gsc, uq, usc, dq, dsc, keep_unpacked: bool = True):
         E, I, H = self.num_local_experts, self.shape.intermediate, self.shape.hidden
@@ -255,14 +272,91 @@ class MoKHost:
                   b["output"].data_ptr(), _stream())
         return b["output"]
 
+    # ------------------------------------------------------------------ training
+    def _alloc_train_buffers(self):
+        P, sh, dev = self.capacity, self.shape, self.device
+        H, I, E, k, L = sh.hidden, sh.intermediate, self.num_local_experts, sh.topk, sh.tokens
+        u8 = dict(dtype=torch.uint8, device=dev)
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        sc = lambda r, c: torch.empty((r // 128, c // 128, 32, 16), **u8)
+        b = self.buffers
+        b.update(gate_routed_fp8=torch.empty((P, I), **u8), gate_routed_sc=sc(P, I),
+                 up_routed_fp8=torch.empty((P, I), **u8), up_routed_sc=sc(P, I),
+                 hidden_routed_bf16=torch.zeros((P, I), **bf),
+                 d_y_routed=torch.empty((P, H), **bf), d_hidden_routed=torch.zeros((P, I), **bf),
+                 d_gate_up_routed=torch.empty((P, 2 * I), **bf), x_routed_bf16=torch.empty((P, H), **bf),
+                 d_x_routed_buffer=torch.zeros((L * k, H), **bf), d_x=torch.empty((L, H), **bf),
+                 d_router_weights=torch.zeros((L, k), dtype=torch.float32, device=dev),
+                 d_w_routed_down=torch.empty((E, H, I), **bf), d_w_routed_gate_up=torch.empty((E, 2 * I, H), **bf))
+        self._ones = torch.ones((L, k), dtype=torch.float32, device=dev)
+        self._identity_rows = torch.arange(P, dtype=torch.int32, device=dev)
+
+    def gemm_gate_up_train(self):
+        s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        _lib.call("plb_moe_gemm_gate_up_train", b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
+                  w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(), s.block_expert.data_ptr(), s.num_tokens.data_ptr(),
+                  self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
+                  b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(),
+                  b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(),
+                  b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(),
+                  b["hidden_routed_bf16"].data_ptr(), self.status.buf.data_ptr(), _stream())
+
+    def _gemm_rows(self, a_q, a_sc, b_q, b_sc, K, N, out, dest_rows):
+        """bf16 out[dest_rows[p]] = A_q[p] . B_q[expert(p)]^T: plb_moe_gemm_down with K and N named freely."""
+        s = self.schedule
+        _lib.call("plb_moe_gemm_down", a_q.data_ptr(), a_sc.data_ptr(), b_q.data_ptr(), b_sc.data_ptr(),
+                  s.block_expert.data_ptr(), s.num_tokens.data_ptr(), dest_rows.data_ptr(), self.capacity,
+                  self.num_local_experts, K, N, out.data_ptr(), self.status.buf.data_ptr(), _stream())
+
+    def _wgrad(self, a_t, a_t_sc, b_t, b_t_sc, m_rows, n_rows, out):
+        _lib.call("plb_moe_gemm_wgrad", a_t.data_ptr(), a_t_sc.data_ptr(), b_t.data_ptr(), b_t_sc.data_ptr(),
+                  self.schedule.expert_offsets.data_ptr(), self.capacity, self.num_local_experts, m_rows, n_rows,
+                  out.data_ptr(), self.status.buf.data_ptr(), _stream())
+
+    def backward(self, d_out: torch.Tensor, *, check: bool = True):
+        """Backward of the last ``forward(train=True)`` (single rank). Returns the gradients the
+        reference reports (GRAD_NAMES, mok_port_host.py:29-30, routed part): d_x, d_router_weights,
+        d_w_routed_gate / up / down."""
+        s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        P, H, I, k = self.capacity, sh.hidden, sh.intermediate, sh.topk
+        nt = s.num_tokens.data_ptr()
+        # combine backward + router-weight gradient
+        _lib.call("plb_moe_bwd_dy", d_out.data_ptr(), b["combine_buffer"].data_ptr(), self.router_weight_buffer.data_ptr(),
+                  s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.dest_row.data_ptr(), nt, P, H, k,
+                  b["d_y_routed"].data_ptr(), b["d_router_weights"].data_ptr(), _stream())
+        dy_q, dy_sc, dy_t, dy_t_sc = mxfp8_quantize(b["d_y_routed"], True, True)
+        # down projection: data gradient, then weight gradient (contraction over each expert's rows)
+        self._gemm_rows(dy_q, dy_sc, w["w_down_t_fp8"], w["w_down_t_sc"], H, I, b["d_hidden_routed"], self._identity_rows)
+        _, _, h_t, h_t_sc = mxfp8_quantize(b["hidden_routed_bf16"], False, True)
+        self._wgrad(dy_t, dy_t_sc, h_t, h_t_sc, H, I, b["d_w_routed_down"])
+        # SwiGLU
+        _lib.call("plb_moe_swiglu_bwd", b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(),
+                  b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(), b["d_hidden_routed"].data_ptr(), nt, P, I,
+                  b["d_gate_up_routed"].data_ptr(), _stream())
+        dgu_q, dgu_sc, dgu_t, dgu_t_sc = mxfp8_quantize(b["d_gate_up_routed"], True, True)
+        # gate/up projections: data gradient scattered to (token, slot) rows, then summed per token
+        self._gemm_rows(dgu_q, dgu_sc, w["w_cat_t_fp8"], w["w_cat_t_sc"], 2 * I, H, b["d_x_routed_buffer"], s.dest_row)
+        _lib.call("plb_moe_fwd_epilogue", None, b["d_x_routed_buffer"].data_ptr(), self._ones.data_ptr(), sh.tokens, k, H,
+                  b["d_x"].data_ptr(), _stream())
+        _lib.call("plb_moe_gather_rows", self.x_buffer.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
+                  nt, P, H, b["x_routed_bf16"].data_ptr(), _stream())
+        _, _, x_t, x_t_sc = mxfp8_quantize(b["x_routed_bf16"], False, True)
+        self._wgrad(dgu_t, dgu_t_sc, x_t, x_t_sc, 2 * I, H, b["d_w_routed_gate_up"])
+        if check:
+            self.status.check("after MoE backward")
+        g = b["d_w_routed_gate_up"]
+        return {"d_x": b["d_x"], "d_router_weights": b["d_router_weights"], "d_w_routed_gate": g[:, :I],
+                "d_w_routed_up": g[:, I:], "d_w_routed_down": b["d_w_routed_down"]}
+
     def megakernel(self):
         """The device part between the barriers of the reference's forward (mok_port_host.py:203)."""
         self.dispatch()
         self.gemm_gate_up()
         self.gemm_down()
 
-    def forward(self, inputs: Inputs, *, check: bool = True):
-        """Single-rank forward: every token of ``inputs`` is local and every expert is local."""
+    def forward(self, inputs: Inputs, *, check: bool = True, train: bool = False):
+        """Single-rank forward: every token of ``inputs`` is local and every expert is local.
+        ``train=True`` keeps the forward context ``backward`` needs."""
         if self.world != 1:
             raise ValueError("forward() drives one rank; use pipelink_b200.ep for a group")
         if self.weights is None:
@@ -271,7 +365,14 @@ class MoKHost:
         self.schedule_into(inputs.experts[None])
         self.x_buffer.copy_(inputs.x)
         self.router_weight_buffer.copy_(inputs.router)
-        self.megakernel()
+        if train:
+            if "w_down_t_fp8" not in self.weights:
+                raise RuntimeError("load_weights(..., train=True) first")
+            self.dispatch()
+            self.gemm_gate_up_train()
+            self.gemm_down()
+        else:
+            self.megakernel()
         out = self.fwd_epilogue()
         if check:
             self.status.check("after MoE forward")
