@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-1B decode ms/token leg")
+    ap.add_argument("--no-attention", action="store_true", help="skip the causal prefill attention leg")
     return ap.parse_args()
 
 
@@ -235,6 +236,13 @@ def run_native(args):
         e2e = {"value": flop_per_rank * world / (float(t.item()) * 1e-3) / 1e12, "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": float(t.item())}
 
+    attention = None
+    if not args.no_attention and args.tokens is None:
+        if world == 1:
+            attention = attention_leg(dev, pk)
+        else:
+            attention = cp_attention_leg(dev, pk, rank, world)
+
     decode = None
     if rank == 0 and world == 1 and not args.no_decode and args.tokens is None:
         del session
@@ -256,11 +264,78 @@ def run_native(args):
                            "l2": "inputs larger than L2 (weights 1.5 GB, activations > 1 GB per step)",
                            "expert_padding": mok.expert_padding(), "gemm_variant": "cta-pair 256x256" if mok.expert_padding() == 256 else "single-cta 128x128"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
-                "roofline": roof, "cpu_baseline": cpu, "decode": decode,
+                "roofline": roof, "cpu_baseline": cpu, "decode": decode, "attention": attention,
                 "frac_of_fp8_peak_whole_step": value / world / fp8_peak}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def attention_leg(dev, pk, seq=32768, steps=3):
+    """Causal prefill attention, one GPU: batch 1, 32 query / 8 KV heads, head_dim 128 (the
+    reference's W1-32k cell, campaigns/attention/README.md:172). FLOP = 4 d Hq S (S+1) / 2."""
+    import torch
+
+    from pipelink_b200 import attention as att
+    torch.manual_seed(0)
+    Hq, Hkv = 32, 8
+    q = torch.randn(1, seq, Hq, 128, device=dev).to(torch.bfloat16)
+    k = torch.randn(1, seq, Hkv, 128, device=dev).to(torch.bfloat16)
+    v = torch.randn(1, seq, Hkv, 128, device=dev).to(torch.bfloat16)
+    att.attention_fwd(q, k, v)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(steps):
+        att.attention_fwd(q, k, v, check=False)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    tf = 4.0 * 128 * Hq * seq * (seq + 1) / 2 / (ms * 1e-3) / 1e12
+    return {"metric": "causal_prefill_attention_tflops", "value": tf, "unit": "TFLOP/s", "ms": ms, "seq": seq,
+            "heads": [Hq, Hkv], "dtype": "bf16",
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_sustained"], "unit": "TFLOP/s",
+                         "frac": tf / pk["bf16_sustained"], "peak_source": f"bf16_tflops_sustained of {pk['source']} peaks"}}
+
+
+def cp_attention_leg(dev, pk, rank, world, seq=131072, steps=2):
+    """BASELINE.json configs[4]: context-parallel causal prefill, S = 131072 split zigzag over the
+    ranks, K/V pushed over NVLink with per-block counters. Time = max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from pipelink_b200 import attention as att, ep
+    Hq, Hkv = 32, 8
+    C2 = seq // world
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q = torch.randn(C2, Hq, 128, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn(C2, Hkv, 128, generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn(C2, Hkv, 128, generator=g, device=dev).to(torch.bfloat16)
+    layout = att.CpRank.slab_layout(seq, Hkv)
+    slab = ep.IpcSlab(layout["nbytes"], rank, world)
+    r = att.CpRank(seq, Hq, Hkv, rank, world, slab.ptrs, layout, dev)
+    r.step(q, k, v)
+    torch.cuda.synchronize()
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        r.step(q, k, v)
+    b.record()
+    torch.cuda.synchronize()
+    r.status.check("cp attention leg")
+    t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    dist.barrier()
+    slab.close()
+    tf = 4.0 * 128 * Hq * seq * (seq + 1) / 2 / (ms * 1e-3) / 1e12
+    chunk = seq // (2 * world)
+    payload = 1.5 * world * (world - 1) * chunk * Hkv * 128 * 2 * 2   # K+V bytes that must cross NVLink, all ranks
+    return {"metric": "cp_causal_prefill_attention_tflops", "value": tf, "unit": "TFLOP/s", "ms": ms, "seq": seq,
+            "world": world, "nvlink_payload_bytes": payload, "scaling": "strong",
+            "roofline": {"bound": "tensor", "achieved": tf / world, "peak": pk["bf16_sustained"], "unit": "TFLOP/s per GPU",
+                         "frac": tf / world / pk["bf16_sustained"]}}
 
 
 def decode_leg(dev, pk, steps=128, prefill=4096):

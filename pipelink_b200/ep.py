@@ -81,39 +81,65 @@ class LocalGroup:
         self.slabs = []
 
 
-class IpcGroup:
-    """One process per GPU; handles travel through ``torch.distributed`` (bootstrap only)."""
+def exchange_handles(handle: bytes, world: int, group=None):
+    """Bootstrap step: every rank contributes its 64-byte IPC handle and receives all of them, in
+    rank order. The only use of ``torch.distributed`` on the expert-parallel path (any backend)."""
+    import torch.distributed as dist
+    if len(handle) != 64:
+        raise ValueError("a CUDA IPC memory handle is 64 bytes")
+    gathered = [None] * world
+    dist.all_gather_object(gathered, bytes(handle), group=group)
+    if any(h is None or len(h) != 64 for h in gathered):
+        raise RuntimeError("a rank did not contribute a handle")
+    return gathered
 
-    def __init__(self, shape: mok.Shape, rank: int, world: int, device, group=None):
+
+class IpcSlab:
+    """One zero-filled device allocation per rank, mapped into every rank through CUDA IPC.
+    ``ptrs[r]`` is rank r's slab as addressable from this process (``ptrs[rank]`` is local)."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, group=None):
         import torch.distributed as dist
-        self.world, self.rank, self.device, self.distributed = world, rank, torch.device(device), True
-        self.layout = SlabLayout(shape, world)
-        self.local = sym_alloc(self.layout.nbytes)
+        self.rank, self.world = rank, world
+        self.local = sym_alloc(nbytes)
         handle = (ctypes.c_ubyte * 64)()
         _lib.call("plb_ipc_export", self.local, handle)
-        gathered = [None] * world
-        dist.all_gather_object(gathered, bytes(handle), group=group)
-        self.peer_ptrs = []
+        gathered = exchange_handles(bytes(handle), world, group)
+        self.ptrs = []
         for r, h in enumerate(gathered):
             if r == rank:
-                self.peer_ptrs.append(self.local)
+                self.ptrs.append(self.local)
             else:
                 buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
                 out = ctypes.c_void_p()
                 _lib.call("plb_ipc_import", buf, ctypes.byref(out))
-                self.peer_ptrs.append(out.value)
+                self.ptrs.append(out.value)
         dist.barrier(group=group)
+
+    def close(self):
+        torch.cuda.synchronize()
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank:
+                _lib.call("plb_ipc_close", p)
+        _lib.call("plb_sym_free", self.local)
+        self.ptrs = []
+
+
+class IpcGroup:
+    """One process per GPU; handles travel through ``torch.distributed`` (bootstrap only)."""
+
+    def __init__(self, shape: mok.Shape, rank: int, world: int, device, group=None):
+        self.world, self.rank, self.device, self.distributed = world, rank, torch.device(device), True
+        self.layout = SlabLayout(shape, world)
+        self.slab = IpcSlab(self.layout.nbytes, rank, world, group)
+        self.peer_ptrs = self.slab.ptrs
 
     def ptrs_for(self, rank: int):
         assert rank == self.rank
         return list(self.peer_ptrs)
 
     def close(self):
-        torch.cuda.synchronize()
-        for r, p in enumerate(self.peer_ptrs):
-            if r != self.rank:
-                _lib.call("plb_ipc_close", p)
-        _lib.call("plb_sym_free", self.local)
+        self.slab.close()
         self.peer_ptrs = []
 
 

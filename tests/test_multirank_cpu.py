@@ -1,0 +1,80 @@
+"""The N > 1 host logic on CPU: two gloo ranks exchange handles and routes, build their schedules
+with the oracle, and the union must place every (rank, token, slot) exactly once; context-parallel
+work lists must tile the causal triangle exactly."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import routing
+        from pipelink_b200 import ep
+        # 1. handle exchange (bootstrap): rank r contributes 64 bytes of value r
+        handles = ep.exchange_handles(bytes([rank]) * 64, world)
+        assert [h[0] for h in handles] == list(range(world))
+        # 2. routes all-gather + per-rank schedule
+        tokens, topk, experts = 96, 2, 8
+        rng = np.random.default_rng(100 + rank)
+        mine = np.stack([rng.permutation(experts)[:topk] for _ in range(tokens)]).astype(np.int32)
+        bucket = [torch.zeros(tokens, topk, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(bucket, torch.from_numpy(mine))
+        routes = torch.stack(bucket).numpy()
+        assert np.array_equal(routes[rank], mine)
+        El = experts // world
+        sched = routing.build_schedule(routes, rank * El, El, 1024, 256)
+        total = int(sched["num_tokens"][0])
+        live = sched["peer_rank"][:total] >= 0
+        placed = np.stack([sched["peer_rank"][:total][live], sched["dest_row"][:total][live]], axis=1)
+        np.save(os.path.join(tmp, f"placed{rank}.npy"), placed)
+        np.save(os.path.join(tmp, f"routes{rank}.npy"), routes)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_schedule_every_route_once(tmp_path):
+    world, port = 2, _free_port()
+    mp.spawn(_rank_main, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    routes = np.load(tmp_path / "routes0.npy")
+    assert np.array_equal(routes, np.load(tmp_path / "routes1.npy"))
+    tokens, topk = routes.shape[1:]
+    seen = np.zeros((world, tokens * topk), int)
+    for r in range(world):
+        placed = np.load(tmp_path / f"placed{r}.npy")
+        for src, dest in placed:
+            seen[src, dest] += 1
+            assert routes[src, dest // topk, dest % topk] // 4 == r     # the row went to the owner of its expert
+    assert (seen == 1).all()
+
+
+@pytest.mark.parametrize("world,seq", [(2, 1024), (4, 4096), (8, 131072)])
+def test_zigzag_work_tiles_the_causal_triangle(world, seq):
+    from oracle import attention as oa
+    from pipelink_b200 import attention as att
+    covered = np.zeros(seq // 128, int)
+    total_blocks = 0
+    for r in range(world):
+        w = att.zigzag_work(seq, world, r, q_heads=1)
+        pos = oa.zigzag_rows(seq, world, r)
+        for q_row0, q_pos0, kv_row0, kv_pos0, kv_blocks, head, batch, _ in w:
+            assert pos[q_row0] == q_pos0 and kv_blocks == q_pos0 // 128 + 1 and kv_row0 == 0 and kv_pos0 == 0
+            covered[q_pos0 // 128] += 1
+            total_blocks += kv_blocks
+        per_rank = sum(row[4] for row in w)
+        # zigzag balances the causal work: every rank visits the same number of KV blocks
+        assert per_rank == (seq // 128) * (seq // 128 + 1) // 2 // world
+    assert (covered == 1).all() and total_blocks == (seq // 128) * (seq // 128 + 1) // 2
