@@ -308,12 +308,14 @@ typedef struct plb_attn_work {
   int32_t kv_row0;   /* row of key block 0 in K / V */
   int32_t kv_pos0;   /* global sequence position of that key */
   int32_t kv_blocks; /* 128-key blocks to visit */
-  int32_t head;
+  int32_t head;      /* query head; the first of two when heads_per_work is 2 */
   int32_t batch;
   int32_t reserved;
 } plb_attn_work;
+/* heads_per_work: 1 = one record per head; 2 = one record per pair of heads (head, head + 1) that
+ * share a KV head (q_heads / kv_heads must be even, head even): K / V are fetched once for both. */
 int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
-                      const plb_attn_work* work, int num_work, int q_heads, int kv_heads, int seq_q,
+                      const plb_attn_work* work, int num_work, int heads_per_work, int q_heads, int kv_heads, int seq_q,
                       uint64_t q_rows, uint64_t kv_rows, float scale, const uint32_t* ready,
                       uint32_t ready_target, plb_status* status, void* stream);
 

@@ -25,17 +25,24 @@ from .mok import DeviceStatus, _stream
 BLK, D = 128, 128
 
 
-def causal_work(batch: int, seq: int, q_heads: int) -> np.ndarray:
-    """i32 [n, 8]: (q_row0, q_pos0, kv_row0, kv_pos0, kv_blocks, head, batch, 0), longest tiles first."""
+def heads_per_work(q_heads: int, kv_heads: int) -> int:
+    """2 when consecutive query heads pair up inside one KV group (one record, one K/V fetch for
+    both), else 1."""
+    return 2 if (q_heads // kv_heads) % 2 == 0 else 1
+
+
+def causal_work(batch: int, seq: int, q_heads: int, step: int = 1) -> np.ndarray:
+    """i32 [n, 8]: (q_row0, q_pos0, kv_row0, kv_pos0, kv_blocks, head, batch, 0), longest tiles first;
+    one record per `step` consecutive heads."""
     rows = []
     for qb in range(seq // BLK - 1, -1, -1):
         for b in range(batch):
-            for h in range(q_heads):
+            for h in range(0, q_heads, step):
                 rows.append((b * seq + qb * BLK, qb * BLK, b * seq, 0, qb + 1, h, b, 0))
     return np.asarray(rows, dtype=np.int32).reshape(-1, 8)
 
 
-def zigzag_work(seq: int, world: int, rank: int, q_heads: int) -> np.ndarray:
+def zigzag_work(seq: int, world: int, rank: int, q_heads: int, step: int = 1) -> np.ndarray:
     """Work list of one rank (batch 1): local tile t covers global positions s*C + (128 t mod C),
     s = rank for the early chunk and 2W-1-rank for the late one (src/sm90/README.md:202-209)."""
     C = seq // (2 * world)
@@ -46,31 +53,33 @@ def zigzag_work(seq: int, world: int, rank: int, q_heads: int) -> np.ndarray:
         items.append((pos, t))
     rows = []
     for pos, t in sorted(items, reverse=True):
-        for h in range(q_heads):
+        for h in range(0, q_heads, step):
             rows.append((t * BLK, pos, 0, 0, pos // BLK + 1, h, 0, 0))
     return np.asarray(rows, dtype=np.int32).reshape(-1, 8)
 
 
-def _launch(q, k, v, out, lse, work, seq_q, ready, ready_target, status):
+def _launch(q, k, v, out, lse, work, step, seq_q, ready, ready_target, status):
     q_rows, q_heads = q.shape[0], q.shape[1]
     kv_rows, kv_heads = k.shape[0], k.shape[1]
     _lib.call("plb_attention_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-              work.data_ptr(), work.shape[0], q_heads, kv_heads, seq_q, q_rows, kv_rows, 1.0 / math.sqrt(D),
+              work.data_ptr(), work.shape[0], step, q_heads, kv_heads, seq_q, q_rows, kv_rows, 1.0 / math.sqrt(D),
               0 if ready is None else ready.data_ptr(), ready_target, status.buf.data_ptr(), _stream())
 
 
-def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, check: bool = True):
-    """q [B, S, Hq, 128], k / v [B, S, Hkv, 128] bf16 CUDA. Returns (O like q, LSE f32 [B*Hq, S])."""
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, check: bool = True, pair_heads: bool | None = None):
+    """q [B, S, Hq, 128], k / v [B, S, Hkv, 128] bf16 CUDA. Returns (O like q, LSE f32 [B*Hq, S]).
+    `pair_heads` None picks the two-heads-per-CTA kernel whenever Hq / Hkv is even."""
     B, S, Hq, d = q.shape
     if d != D or S % BLK or q.dtype != torch.bfloat16:
         raise ValueError("attention_fwd wants bf16, head_dim 128 and a sequence that is a multiple of 128")
     Hkv = k.shape[2]
     out = torch.empty_like(q)
     lse = torch.empty((B * Hq, S), dtype=torch.float32, device=q.device)
-    work = torch.from_numpy(causal_work(B, S, Hq)).to(q.device)
+    step = heads_per_work(Hq, Hkv) if pair_heads is None else (2 if pair_heads else 1)
+    work = torch.from_numpy(causal_work(B, S, Hq, step)).to(q.device)
     status = DeviceStatus(q.device)
     _launch(q.reshape(B * S, Hq, D), k.reshape(B * S, Hkv, D), v.reshape(B * S, Hkv, D), out.reshape(B * S, Hq, D),
-            lse, work, S, None, 0, status)
+            lse, work, step, S, None, 0, status)
     if check:
         status.check("attention_fwd")
     return out, lse
@@ -96,7 +105,8 @@ class CpRank:
         table = lambda off: torch.tensor([p + off for p in slab_ptrs], dtype=torch.int64, device=dev)
         self.k_peers, self.v_peers = table(layout["k"]), table(layout["v"])
         self.ready_peers, self.flags_peers = table(layout["ready"]), table(layout["flags"])
-        self.work = torch.from_numpy(zigzag_work(seq, world, rank, q_heads)).to(dev)
+        self.step_heads = heads_per_work(q_heads, kv_heads)
+        self.work = torch.from_numpy(zigzag_work(seq, world, rank, q_heads, self.step_heads)).to(dev)
         self.barrier_state = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = DeviceStatus(dev)
         self.generation = 0
@@ -123,7 +133,7 @@ class CpRank:
                   ctas, _stream())
 
     def attend(self, q_local: torch.Tensor):
-        _launch(q_local, self.k_gather, self.v_gather, self.out, self.lse, self.work, 2 * self.C, self.ready,
+        _launch(q_local, self.k_gather, self.v_gather, self.out, self.lse, self.work, self.step_heads, 2 * self.C, self.ready,
                 self.generation, self.status)
         return self.out, self.lse
 

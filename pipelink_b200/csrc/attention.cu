@@ -349,6 +349,377 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two query heads per CTA. When the number of query heads per KV head is even, one work record
+// covers heads h and h+1 of the same 128-query tile: both read the same K/V blocks under the
+// same mask, so every K/V tile is fetched once for two S/O tiles and the tensor pipe alternates
+// between them while the other tile's softmax runs.
+//
+// Per CTA (384 threads), persistent over the work list:
+//   warp 0     TMA: both Q tiles once per record; K and V blocks through two 2-deep rings
+//   warp 1     MMA: S_t = Q_t K^T into TMEM columns [128 t, 128 t + 128); O_t += P_t V with the A
+//              operand P_t read from TMEM (bf16, written over the first 64 columns of S_t by the
+//              softmax warps) and O_t accumulated in TMEM columns [256 + 128 t, +128) across all
+//              blocks of the record. Issue order per block: P0 V, Q0 K'^T, P1 V, Q1 K'^T (K' the
+//              next block), so each tile's next scores are queued right behind its P V.
+//   warps 4-7  softmax of tile 0, warps 8-11 of tile 1, one query row per thread: the running
+//              maximum is only advanced (and O_t, l rescaled in TMEM) when a block raises it by
+//              more than 2^8; otherwise exponentials stay relative to the older maximum, which
+//              fp32 sums and bf16 P tolerate. Final O_t / l and LSE.
+constexpr int kPairThreads = 384;  // warpgroup 0: TMA, MMA, two idle warps; warpgroups 1 and 2: softmax
+constexpr int kPOffQ = 0;                              // two Q tiles
+constexpr int kPOffK = 2 * kTileBytes;
+constexpr int kPOffV = kPOffK + kKvStages * kTileBytes;
+constexpr int kPOffBar = kPOffV + kKvStages * kTileBytes;
+constexpr int kPairSmem = kPOffBar + 256 + 1024;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+struct TrueTag { static constexpr bool value = true; };
+struct FalseTag { static constexpr bool value = false; };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct PairBars {
+  uint64_t q_full, q_empty;
+  uint64_t k_full[kKvStages], k_empty[kKvStages];
+  uint64_t v_full[kKvStages], v_empty[kKvStages];
+  uint64_t s_full[2], p_full[2];
+  uint64_t o_full[2], o_free[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+static_assert(sizeof(PairBars) <= 256, "barrier block");
+
+template <bool kUseCounters>
+__global__ void __launch_bounds__(kPairThreads, 1)
+attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                          const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t sb = raw_addr + pad;
+  PairBars* bars = reinterpret_cast<PairBars*>(smem + kPOffBar);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bars->q_full), 1);
+    mbar_init(smem_u32(&bars->q_empty), 1);
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(smem_u32(&bars->k_full[s]), 1);
+      mbar_init(smem_u32(&bars->k_empty[s]), 1);
+      mbar_init(smem_u32(&bars->v_full[s]), 1);
+      mbar_init(smem_u32(&bars->v_empty[s]), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&bars->s_full[t]), 1);
+      mbar_init(smem_u32(&bars->p_full[t]), 128);
+      mbar_init(smem_u32(&bars->o_full[t]), 1);
+      mbar_init(smem_u32(&bars->o_free[t]), 128);
+    }
+    mbar_init(smem_u32(&bars->drain), 1);
+    fence_mbar_init();
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&bars->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp < 4) {
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t q_phase = 0, k_it = 0, v_it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+        const AttnWork wk = p.work[w];
+        const int col = wk.head * kD;
+        const int kv_col = (wk.head / p.q_per_kv) * kD;
+        if (!mbar_wait(smem_u32(&bars->q_empty), q_phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, 10)) { ok = false; break; }
+        mbar_arrive_expect_tx(smem_u32(&bars->q_full), 2 * kTileBytes);
+#pragma unroll
+        for (int a = 0; a < 4; ++a)  // tile t = a / 2 (head + t), 64-column half a % 2
+          tma_load_2d(sb + kPOffQ + a * kAtomBytes, &map_q, smem_u32(&bars->q_full), col + a * 64, wk.q_row0);
+        q_phase ^= 1u;
+        for (int j = 0; j < wk.kv_blocks && ok; ++j) {
+          const int kv_row = wk.kv_row0 + j * kBlk;
+          if (kUseCounters && p.ready != nullptr) {
+            const unsigned* flag = p.ready + (wk.kv_row0 / kBlk + j);
+            const long long t0 = clock64();
+            while (static_cast<int>(ld_acquire_sys_u32(flag) - p.ready_target) < 0) {
+              if (clock64() - t0 > kWaitBudgetCycles || ld_volatile_i32(&p.status->code) != 0) {
+                report_failure(p.status, ST_TIMEOUT_COUNTER, 300, ld_acquire_sys_u32(flag), p.ready_target);
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
+          {
+            const int s = k_it % kKvStages;
+            if (!mbar_wait(smem_u32(&bars->k_empty[s]), ((k_it / kKvStages) & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, 11)) { ok = false; break; }
+            const uint32_t full = smem_u32(&bars->k_full[s]);
+            mbar_arrive_expect_tx(full, kTileBytes);
+            tma_load_2d(sb + kPOffK + s * kTileBytes, &map_k, full, kv_col, kv_row);
+            tma_load_2d(sb + kPOffK + s * kTileBytes + kAtomBytes, &map_k, full, kv_col + 64, kv_row);
+            ++k_it;
+          }
+          {
+            const int s = v_it % kKvStages;
+            if (!mbar_wait(smem_u32(&bars->v_empty[s]), ((v_it / kKvStages) & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, 12)) { ok = false; break; }
+            const uint32_t full = smem_u32(&bars->v_full[s]);
+            mbar_arrive_expect_tx(full, kTileBytes);
+            tma_load_2d(sb + kPOffV + s * kTileBytes, &map_v, full, kv_col, kv_row);
+            tma_load_2d(sb + kPOffV + s * kTileBytes + kAtomBytes, &map_v, full, kv_col + 64, kv_row);
+            ++v_it;
+          }
+        }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000LL) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t q_phase = 0, k_it = 0, v_it = 0, blk_it = 0, item_it = 0;
+      bool ok = true;
+      auto issue_qk = [&](int t, int ks) {
+        const uint32_t qa = sb + kPOffQ + t * kTileBytes, ka = sb + kPOffK + ks * kTileBytes;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+          tc_mma_f16(tmem + t * 128, smem_desc(qa + off, kDescSw128KMajor), smem_desc(ka + off, kDescSw128KMajor),
+                     kIdescQK, k != 0 ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&bars->s_full[t]));
+      };
+      for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+        const AttnWork wk = p.work[w];
+        const int n = wk.kv_blocks;
+        if (!mbar_wait(smem_u32(&bars->q_full), q_phase, p.status, ST_TIMEOUT_FULL, 22)) { ok = false; break; }
+        {
+          const int ks = k_it % kKvStages;
+          if (!mbar_wait(smem_u32(&bars->k_full[ks]), (k_it / kKvStages) & 1u, p.status, ST_TIMEOUT_FULL, 20)) { ok = false; break; }
+          tc_fence_after();
+          issue_qk(0, ks);
+          issue_qk(1, ks);
+          tc_commit(smem_u32(&bars->k_empty[ks]));
+          ++k_it;
+        }
+        for (int j = 0; j < n && ok; ++j) {
+          const bool have_next = j + 1 < n;
+          const int vs = v_it % kKvStages, ks = k_it % kKvStages;
+          if (!mbar_wait(smem_u32(&bars->v_full[vs]), (v_it / kKvStages) & 1u, p.status, ST_TIMEOUT_FULL, 23)) { ok = false; break; }
+          if (have_next &&
+              !mbar_wait(smem_u32(&bars->k_full[ks]), (k_it / kKvStages) & 1u, p.status, ST_TIMEOUT_FULL, 26)) { ok = false; break; }
+          const uint32_t va = sb + kPOffV + vs * kTileBytes;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (!mbar_wait(smem_u32(&bars->p_full[t]), blk_it & 1u, p.status, ST_TIMEOUT_FULL, 24)) { ok = false; break; }
+            // the first P V of a record overwrites O_t: the previous record's epilogue must have read it
+            if (j == 0 &&
+                !mbar_wait(smem_u32(&bars->o_free[t]), (item_it & 1u) ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, 25)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 8; ++k)  // 16 keys per step: 8 packed columns of P, 16 rows x 128 B of V
+              tc_mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + k * 8, smem_desc(va + k * 2048, kDescVMn), kIdescPV,
+                            (j != 0 || k != 0) ? 1u : 0u);
+            if (!have_next) tc_commit(smem_u32(&bars->o_full[t]));
+            if (have_next) issue_qk(t, ks);
+          }
+          if (!ok) break;
+          tc_commit(smem_u32(&bars->v_empty[vs]));
+          ++v_it;
+          if (have_next) {
+            tc_commit(smem_u32(&bars->k_empty[ks]));
+            ++k_it;
+          }
+          ++blk_it;
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&bars->q_empty));
+        q_phase ^= 1u;
+        ++item_it;
+      }
+      if (!ok) {
+        tc_commit(smem_u32(&bars->drain));
+        const long long t0 = clock64();
+        while (!mbar_try_wait(smem_u32(&bars->drain), 0)) {
+          if (clock64() - t0 > 20000000LL) break;
+        }
+      }
+    }
+  }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int t = (warp - 4) >> 2;     // tile (head offset) of this warp
+    const int quad = warp & 3;         // TMEM lane quadrant this warp may touch
+    const int row = quad * 32 + lane;  // query row inside the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t tmem_s = tmem + t * 128 + lane_addr;
+    const uint32_t tmem_o = tmem + 256 + t * 128 + lane_addr;
+    const float scale = p.scale_log2;
+    uint32_t blk_it = 0, item_it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+      const AttnWork wk = p.work[w];
+      const int head = wk.head + t;
+      const int q_pos = wk.q_pos0 + row;
+      float m_ref = -INFINITY, l = 0.0f;
+      for (int j = 0; j < wk.kv_blocks; ++j) {
+        if (!mbar_wait(smem_u32(&bars->s_full[t]), blk_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, 30)) ok = false;
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const int key0 = wk.kv_pos0 + j * kBlk;
+        const int valid = q_pos - key0 + 1;  // keys [0, valid) of this block are visible to the row
+        const bool diag = key0 + kBlk - 1 > wk.q_pos0;  // uniform per block: some row is masked
+        float bm = -INFINITY;
+        {
+          // pass 1: block maximum of the raw scores, two 32-column chunks in flight
+          float b0 = -INFINITY, b1 = -INFINITY;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t a[32], b[32];
+            tc_ld_32x32b_x32(tmem_s + h * 64, a);
+            tc_ld_32x32b_x32(tmem_s + h * 64 + 32, b);
+            tc_wait_ld();
+            if (diag) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (h * 64 + i < valid) b0 = fmaxf(b0, __uint_as_float(a[i]));
+                if (h * 64 + 32 + i < valid) b1 = fmaxf(b1, __uint_as_float(b[i]));
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                b0 = fmaxf(b0, __uint_as_float(a[i]));
+                b1 = fmaxf(b1, __uint_as_float(b[i]));
+              }
+            }
+          }
+          bm = fmaxf(b0, b1);
+        }
+        bm *= scale;  // scale > 0
+        const float m_new = fmaxf(m_ref, bm);
+        const bool need = m_new > m_ref && (m_ref == -INFINITY || m_new - m_ref > kRescaleThreshold);
+        if (__any_sync(0xFFFFFFFFu, need)) {
+          if (j > 0) {
+            // O_t holds the sum over blocks 0..j-1 (their P V completed before this block's scores)
+            const float alpha = m_new == m_ref ? 1.0f : ex2_approx(m_ref - m_new);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t ov[32];
+              tc_ld_32x32b_x32(tmem_o + c * 32, ov);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+              tc_st_32x32b_x32(tmem_o + c * 32, ov);
+            }
+            tc_wait_st();
+            l *= alpha;
+          }
+          m_ref = m_new;
+        }
+        const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+        // P = exp2(s * scale - m_ref) as bf16, two per 32-bit column, over the first 64 columns of S_t
+        // pass 2: scores are read again from TMEM (cheaper than holding 128 of them in registers);
+        // P of columns [64 h, 64 h + 64) lands on columns [32 h, 32 h + 32), all of them already read
+        float sum0 = 0.0f, sum1 = 0.0f;
+        auto half = [&](auto masked, int h) {
+          uint32_t a[32], b[32], pk[32];
+          tc_ld_32x32b_x32(tmem_s + h * 64, a);
+          tc_ld_32x32b_x32(tmem_s + h * 64 + 32, b);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float a0 = ex2_approx(fmaf(__uint_as_float(a[i]), scale, -m_use));
+            float a1 = ex2_approx(fmaf(__uint_as_float(a[i + 1]), scale, -m_use));
+            float c0 = ex2_approx(fmaf(__uint_as_float(b[i]), scale, -m_use));
+            float c1 = ex2_approx(fmaf(__uint_as_float(b[i + 1]), scale, -m_use));
+            if (decltype(masked)::value) {
+              if (h * 64 + i >= valid) a0 = 0.0f;
+              if (h * 64 + i + 1 >= valid) a1 = 0.0f;
+              if (h * 64 + 32 + i >= valid) c0 = 0.0f;
+              if (h * 64 + 32 + i + 1 >= valid) c1 = 0.0f;
+            }
+            sum0 += a0 + a1;
+            sum1 += c0 + c1;
+            __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pc = __floats2bfloat162_rn(c0, c1);
+            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&pa);
+            pk[16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&pc);
+          }
+          tc_st_32x32b_x32(tmem_s + h * 32, pk);
+        };
+        if (diag) {
+          half(TrueTag{}, 0);
+          half(TrueTag{}, 1);
+        } else {
+          half(FalseTag{}, 0);
+          half(FalseTag{}, 1);
+        }
+        tc_wait_st();
+        l += sum0 + sum1;
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bars->p_full[t]));
+        ++blk_it;
+      }
+      if (!ok) break;
+      // epilogue: O_t / l as bf16 and the natural-log LSE
+      if (!mbar_wait(smem_u32(&bars->o_full[t]), item_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, 32)) ok = false;
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      const size_t out_row = static_cast<size_t>(wk.q_row0 + row);
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (out_row * p.q_heads + head) * kD);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t ov[32];
+        tc_ld_32x32b_x32(tmem_o + c * 32, ov);
+        tc_wait_ld();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t wv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 tt = __floats2bfloat162_rn(__uint_as_float(ov[g * 8 + e * 2]) * inv,
+                                                      __uint_as_float(ov[g * 8 + e * 2 + 1]) * inv);
+            wv[e] = *reinterpret_cast<uint32_t*>(&tt);
+          }
+          dst[c * 4 + g] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars->o_free[t]));
+      ++item_it;
+      p.lse[(static_cast<size_t>(wk.batch) * p.q_heads + head) * p.seq_q + (wk.q_row0 - wk.batch * p.seq_q) + row] =
+          l > 0.0f ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -396,14 +767,17 @@ cudaError_t launch_attention_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.status = a.status;
   int grid = a.num_sms < a.num_work ? a.num_sms : a.num_work;
   cudaError_t err;
-  if (a.ready != nullptr) {
-    err = cudaFuncSetAttribute(attention_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+  if (a.heads_per_work == 2) {
+    if (p.q_per_kv % 2 != 0) return cudaErrorInvalidValue;
+    auto kern = a.ready != nullptr ? attention_fwd_pair_kernel<true> : attention_fwd_pair_kernel<false>;
+    err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
     if (err != cudaSuccess) return err;
-    attention_fwd_kernel<true><<<grid, kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, p);
+    kern<<<grid, kPairThreads, kPairSmem, stream>>>(mq, mk, mv, p);
   } else {
-    err = cudaFuncSetAttribute(attention_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+    auto kern = a.ready != nullptr ? attention_fwd_kernel<true> : attention_fwd_kernel<false>;
+    err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
     if (err != cudaSuccess) return err;
-    attention_fwd_kernel<false><<<grid, kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, p);
+    kern<<<grid, kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, p);
   }
   return cudaGetLastError();
 }

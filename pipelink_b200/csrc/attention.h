@@ -14,7 +14,7 @@ struct AttnWork {
   int kv_row0;    // row of key block 0 in the [kv_rows, kv_heads*128] view of K / V
   int kv_pos0;    // global sequence position of that key
   int kv_blocks;  // 128-key blocks to visit (causal: q_pos0 / 128 + 1 when kv_pos0 = 0)
-  int head;       // query head
+  int head;       // query head (the first of two when records cover head pairs)
   int batch;
   int reserved;
 };
@@ -41,6 +41,7 @@ struct AttnArgs {
   float* lse;
   const AttnWork* work;
   int num_work;
+  int heads_per_work;  // 1: one head per record; 2: records cover heads (head, head + 1) of one KV group
   int q_heads, kv_heads;
   int seq_q;
   uint64_t q_rows, kv_rows;

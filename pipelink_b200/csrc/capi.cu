@@ -474,7 +474,7 @@ int plb_moe_gather_rows(const void* src_bf16, const int32_t* peer_rank, const in
 }
 
 int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
-                      const plb_attn_work* work, int num_work, int q_heads, int kv_heads, int seq_q,
+                      const plb_attn_work* work, int num_work, int heads_per_work, int q_heads, int kv_heads, int seq_q,
                       uint64_t q_rows, uint64_t kv_rows, float scale, const uint32_t* ready,
                       uint32_t ready_target, plb_status* status, void* stream) {
   static_assert(sizeof(plb_attn_work) == sizeof(plb::AttnWork), "work descriptor layouts differ");
@@ -483,7 +483,9 @@ int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, fl
       q_rows % 128 || kv_rows % 128)
     return PLB_E_ARGUMENT;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return PLB_E_ARGUMENT;
+  if (heads_per_work != 1 && !(heads_per_work == 2 && (q_heads / kv_heads) % 2 == 0)) return PLB_E_ARGUMENT;
   plb::AttnArgs a;
+  a.heads_per_work = heads_per_work;
   a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
   a.work = reinterpret_cast<const plb::AttnWork*>(work);
   a.num_work = num_work;

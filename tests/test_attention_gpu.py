@@ -37,6 +37,28 @@ def test_attention_vs_oracle(native_lib, S, Hq, Hkv, rows):
     assert oa.matches(got_lse, ref_lse) == 0, np.abs(got_lse - ref_lse).max()
 
 
+@pytest.mark.parametrize("pair", [False, True])
+def test_attention_growing_scores_both_kernels(native_lib, pair):
+    """Keys grow with position, so the row maximum keeps rising by more than the two-head kernel's
+    rescale threshold: its deferred rescale of O in TMEM has to fire in late blocks; the one-head
+    kernel on the same inputs is the cross-check."""
+    from pipelink_b200 import attention as att
+    S, Hq, Hkv = 2048, 4, 2
+    (q, k, v), _ = _inputs(S, Hq, Hkv, case=11)
+    ramp = (1.0 + 5.0 * np.arange(S, dtype=np.float32) / S)[:, None, None]
+    k = torch.from_numpy(k * ramp).to(torch.bfloat16).float().numpy()
+    dev = lambda a: torch.from_numpy(a).to(torch.bfloat16).cuda()
+    out, lse = att.attention_fwd(dev(q)[None], dev(k)[None], dev(v)[None], pair_heads=pair)
+    torch.cuda.synchronize()
+    sel = oa.boundary_rows(S, extra=(S // 2 + 3, S - 130, 700, 1300))
+    ref_o, ref_lse = oa.reference_rows(q, k, v, sel, 1.0 / np.sqrt(128.0))
+    got_o = out[0].float().cpu().numpy()[sel]
+    got_lse = lse.cpu().numpy()[:, sel]
+    assert np.isfinite(got_o).all()
+    assert oa.matches(got_o, ref_o) == 0, np.abs(got_o - ref_o).max()
+    assert oa.matches(got_lse, ref_lse) == 0, np.abs(got_lse - ref_lse).max()
+
+
 def test_attention_deterministic(native_lib):
     from pipelink_b200 import attention as att
     _, (dq, dk, dv) = _inputs(1024, 8, 2, case=7)
