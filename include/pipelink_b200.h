@@ -262,7 +262,10 @@ int plb_moe_fwd_epilogue(const void* y_shared_bf16, const void* combine_bf16,
  * f32 [rows,32] (one entry per rotated pair, interleaved-pair RoPE,
  * campaigns/megakernel/host/export_inputs.py:229-240). Instruction words: 0 opcode, 1 layer,
  * 2-5 operands, 6 counter to wait on (-1 none), 7 its target, 8 counter to bump (-1 none).
- * Opcodes 1-7 as campaigns/megakernel/host/export_inputs.py:49-58; 8 = greedy sample
+ * Opcodes 1-7 as campaigns/megakernel/host/export_inputs.py:49-58; for opcode 2 a non-zero word
+ * 5 is 1 + the index of a counter on which the partitions of one KV head count themselves in:
+ * the last one to arrive also merges that head's partials (the work of opcode 3) and only it
+ * bumps the counter of word 8. 8 = greedy sample
  * (argmax with ties to the lower id, token_out[pos+1], next embedding row into hidden,
  * *pos_dev += 1). The call zeroes `bars` (num_bars counters) on the stream, then launches
  * cooperatively with num_sms CTAs. */
@@ -280,7 +283,7 @@ typedef struct plb_decode_args {
   plb_status* status;
   int32_t num_instructions, max_seq_len, max_parts, vocab;
   float attn_scale, eps;
-  int32_t num_bars, reserved;
+  int32_t num_bars, layers;
 } plb_decode_args;
 int plb_decode_step(const plb_decode_args* args, int num_sms, void* stream);
 

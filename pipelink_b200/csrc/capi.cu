@@ -68,6 +68,9 @@ int plb_moe_set_gemm_variant(int variant) {
 int plb_moe_gemm_variant(void) { return g_gemm_variant; }
 int plb_debug_set_profile_buffer(void* device_i64_grid_by_16) {
   g_profile_buffer = device_i64_grid_by_16;
+#ifdef PLB_DECODE_PROFILE
+  plb::set_decode_profile(device_i64_grid_by_16);
+#endif
   return PLB_OK;
 }
 int plb_moe_tile_rows(void) { return g_gemm_variant == 2 ? 256 : 128; }
@@ -382,7 +385,8 @@ int plb_decode_step(const plb_decode_args* args, int num_sms, void* stream) {
   static_assert(sizeof(plb_decode_args) == sizeof(plb::DecodeGlobals), "decode argument blocks differ");
   if (!args || num_sms < 1) return PLB_E_ARGUMENT;
   if (!args->qkv_w || !args->hidden || !args->instructions || !args->bars || !args->pos_dev ||
-      !args->status || args->num_instructions < 1 || args->num_bars < 1 || args->max_parts < 1)
+      !args->status || args->num_instructions < 1 || args->num_bars < 1 || args->max_parts < 1 ||
+      args->layers < 1 || !args->k_cache || !args->v_cache)
     return PLB_E_ARGUMENT;
   plb::DecodeGlobals g;
   memcpy(&g, args, sizeof(g));

@@ -17,10 +17,14 @@
 // 16-token KV blocks split as blocks_per_partition = ceil(ceil(len/16)/partitions).
 //
 // Decode at batch 1 streams 2.47 GB of weights per token and does ~2 FLOP per byte, so
-// every op is an HBM-bound matvec: one warp per pair of weight rows, 16-byte
-// non-allocating loads, eight in flight per lane (64 KB per SM), fp32 accumulation,
-// activations staged once per instruction in shared memory. While an instruction waits
-// for its producers it prefetches its weight rows into L2.
+// every matvec is HBM-bound. Weights never depend on activations, so each CTA runs one
+// producer warp that walks the CTA's instruction stream ahead of the consumers and streams the
+// weight rows of ops 1, 4, 5, 6, 7 into a ring of 32 KB shared-memory stages with untiled bulk
+// copies (mbarrier full/empty per stage): HBM stays busy while the 16 consumer warps wait for a
+// dependency counter. A stage is 16 warp tasks of 2 KB (1024 bf16 of one row); a lane keeps its
+// 32 activations in registers for the whole instruction, sums four 16-byte chunks per task,
+// and per-row partial sums meet in shared memory where the op's epilogue (RoPE + KV append,
+// residual add, SiLU * up, logits + argmax) runs once per block of rows.
 //
 // Every wait is bounded (cycle budget -> status record, all other waits give up).
 #include "kernels.h"
@@ -30,8 +34,13 @@ namespace plb {
 
 namespace {
 
-constexpr int kDecThreads = 512;
-constexpr int kDecWarps = kDecThreads / 32;
+constexpr int kConsumers = 512;              // 16 consumer warps
+constexpr int kDecWarps = kConsumers / 32;
+constexpr int kDecThreads = kConsumers + 32;  // + the producer warp
+constexpr int kStageBytes = 32768;
+constexpr int kStages = 6;
+constexpr int kTaskBytes = 2048;              // one warp task: 1024 bf16 of one weight row
+constexpr int kPartialFloats = 2048;          // per-row partial sums of one block of rows
 constexpr int kHidden = 2048;
 constexpr int kHeadDim = 64;
 constexpr int kQHeads = 32;
@@ -39,16 +48,6 @@ constexpr int kKvHeads = 8;
 constexpr int kFfn = 8192;
 constexpr int kQkvRows = (kQHeads + 2 * kKvHeads) * kHeadDim;  // 3072
 
-__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-__device__ __forceinline__ void prefetch_l2(const void* p) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-}
 __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
   unsigned v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -87,64 +86,106 @@ __device__ __forceinline__ float dot8(uint4 w, const float* x) {
   return s;
 }
 
-// Two weight rows (each `chunks` 16-byte vectors) against the staged fp32 vector.
-// chunks is a multiple of 128 (2048 or 8192 columns).
-__device__ __forceinline__ void warp_dot2(const uint4* __restrict__ row_a,
-                                          const uint4* __restrict__ row_b,
-                                          const float* __restrict__ x, int chunks, int lane,
-                                          float& sum_a, float& sum_b) {
-  float sa = 0.0f, sb = 0.0f;
-  for (int c0 = 0; c0 < chunks; c0 += 128) {
-    uint4 wa[4], wb[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      wa[u] = ldg_stream(row_a + c0 + u * 32 + lane);
-      wb[u] = ldg_stream(row_b + c0 + u * 32 + lane);
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float* xs = x + (c0 + u * 32 + lane) * 8;
-      sa += dot8(wa[u], xs);
-      sb += dot8(wb[u], xs);
-    }
-  }
-  sum_a = warp_sum(sa);
-  sum_b = warp_sum(sb);
+// All consumer threads (the producer warp never joins).
+__device__ __forceinline__ void consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
 }
 
-// Stage a bf16 vector of n elements into shared fp32; optionally RMS-normalise with weight.
-__device__ void stage_vector(const __nv_bfloat16* __restrict__ src,
-                             const __nv_bfloat16* __restrict__ norm_w, int n, float eps,
-                             float* x, float* red) {
-  float ss = 0.0f;
-  // coherent 16-byte loads: these activations were written by other SMs in this launch
-  for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
-    uint4 raw;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
-                 : "l"(src + i)
-                 : "memory");
-    const float f[8] = {blo(raw.x), bhi(raw.x), blo(raw.y), bhi(raw.y),
-                        blo(raw.z), bhi(raw.z), blo(raw.w), bhi(raw.w)};
+// 16-byte load of bf16 activations another SM wrote earlier in this launch.
+__device__ __forceinline__ uint4 ld_coherent_v4(const void* p) {
+  uint4 raw;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+               : "l"(p)
+               : "memory");
+  return raw;
+}
+__device__ __forceinline__ void unpack8(uint4 raw, float* f) {
+  f[0] = blo(raw.x); f[1] = bhi(raw.x); f[2] = blo(raw.y); f[3] = bhi(raw.y);
+  f[4] = blo(raw.z); f[5] = bhi(raw.z); f[6] = blo(raw.w); f[7] = bhi(raw.w);
+}
+__device__ __forceinline__ float dot8r(uint4 w, const float* x) {
+  float s = blo(w.x) * x[0];
+  s = fmaf(bhi(w.x), x[1], s);
+  s = fmaf(blo(w.y), x[2], s);
+  s = fmaf(bhi(w.y), x[3], s);
+  s = fmaf(blo(w.z), x[4], s);
+  s = fmaf(bhi(w.z), x[5], s);
+  s = fmaf(blo(w.w), x[6], s);
+  s = fmaf(bhi(w.w), x[7], s);
+  return s;
+}
+
+// The activations one lane multiplies for a whole instruction: section `sec` of the input vector
+// (1024 elements), chunks lane, lane + 32, lane + 64, lane + 96 of it. With `norm_w` the vector
+// (2048 long) is RMS-normalised first: every warp reads all of it once, computes the sum of
+// squares itself and keeps its own section.
+__device__ __forceinline__ void load_x(const __nv_bfloat16* __restrict__ src,
+                                       const __nv_bfloat16* __restrict__ norm_w, int sec, int lane,
+                                       float eps, float (&xr)[32]) {
+  if (norm_w != nullptr) {
+    uint4 raw[8], wn[4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) raw[j] = ld_coherent_v4(src + (lane + 32 * j) * 8);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wn[i] = *reinterpret_cast<const uint4*>(norm_w + sec * 1024 + (lane + 32 * i) * 8);
+    float ss = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      x[i + j] = f[j];
-      ss += f[j] * f[j];
-    }
-  }
-  if (norm_w == nullptr) {
-    __syncthreads();
-    return;
-  }
-  ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  float total = 0.0f;
+      float f[8];
+      unpack8(raw[j], f);
 #pragma unroll
-  for (int w = 0; w < kDecWarps; ++w) total += red[w];
-  const float inv = rsqrtf(total / static_cast<float>(n) + eps);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = x[i] * inv * __bfloat162float(norm_w[i]);
-  __syncthreads();
+      for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / static_cast<float>(kHidden) + eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 mine = sec == 0 ? raw[i] : raw[4 + i];
+      float f[8], w[8];
+      unpack8(mine, f);
+      unpack8(wn[i], w);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xr[i * 8 + e] = f[e] * inv * w[e];
+    }
+  } else {
+    uint4 raw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) raw[i] = ld_coherent_v4(src + sec * 1024 + (lane + 32 * i) * 8);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) unpack8(raw[i], &xr[i * 8]);
+  }
+}
+
+// Which weight rows an instruction streams: up to two matrices (gate, up) of `rows` rows of K.
+struct Plan {
+  const char* base[2];
+  int nmat;
+  int rows;
+  int K;
+};
+__device__ __forceinline__ Plan plan_of(const DecodeGlobals& g, const int* in) {
+  Plan p;
+  p.base[0] = p.base[1] = nullptr;
+  p.nmat = 0;
+  p.rows = 0;
+  p.K = kHidden;
+  const int op = in[0], layer = in[1], a0 = in[2], a1 = in[3];
+  if (op == 1) { p.base[0] = reinterpret_cast<const char*>(g.qkv_w + (static_cast<size_t>(layer) * kQkvRows + a0) * kHidden); p.nmat = 1; p.rows = a1; }
+  if (op == 4) { p.base[0] = reinterpret_cast<const char*>(g.o_w + (static_cast<size_t>(layer) * kHidden + a0) * kHidden); p.nmat = 1; p.rows = a1; }
+  if (op == 5) {
+    p.base[0] = reinterpret_cast<const char*>(g.gate_w + (static_cast<size_t>(layer) * kFfn + a0) * kHidden);
+    p.base[1] = reinterpret_cast<const char*>(g.up_w + (static_cast<size_t>(layer) * kFfn + a0) * kHidden);
+    p.nmat = 2;
+    p.rows = a1;
+  }
+  if (op == 6) { p.base[0] = reinterpret_cast<const char*>(g.down_w + (static_cast<size_t>(layer) * kHidden + a0) * kFfn); p.nmat = 1; p.rows = a1; p.K = kFfn; }
+  if (op == 7) { p.base[0] = reinterpret_cast<const char*>(g.lm_head + static_cast<size_t>(a0) * kHidden); p.nmat = 1; p.rows = a1; }
+  return p;
+}
+// Rows of one block: its partial sums (rows x matrices x warps per row) fit kPartialFloats.
+__device__ __forceinline__ int block_rows_of(const Plan& p) {
+  return kPartialFloats / ((p.K / 1024) * p.nmat);
 }
 
 // Bounded wait until counter >= target. Returns false after recording a failure.
@@ -166,14 +207,14 @@ __device__ bool wait_counter(const unsigned* counter, unsigned target, Status* s
     }
     ok_flag = ok;
   }
-  __syncthreads();
+  consumer_sync();
   const bool ok = ok_flag != 0;
-  __syncthreads();
+  consumer_sync();
   return ok;
 }
 
 __device__ __forceinline__ void signal_counter(unsigned* counter) {
-  __syncthreads();
+  consumer_sync();
   if (threadIdx.x == 0) {
     __threadfence();
     atomicAdd(counter, 1u);
@@ -181,75 +222,86 @@ __device__ __forceinline__ void signal_counter(unsigned* counter) {
 }
 
 // ---------------------------------------------------------------- partial attention
-// One CTA: 4 query heads of one KV head over tokens [begin, end). Warps take 32-token
-// tiles round-robin; a lane scores one token, then owns two output dims for the P.V sum.
-// q: bf16 [4][64] (this KV head's heads); k, v: first token's row of this KV head;
-// kv_stride: elements between consecutive tokens. Results: out [4][64] normalised, lse2 [4].
-__device__ void attention_partial(const __nv_bfloat16* __restrict__ q,
-                                  const __nv_bfloat16* __restrict__ k,
-                                  const __nv_bfloat16* __restrict__ v, int kv_stride, int begin,
-                                  int end, float scale_log2, float* smem, float* out,
-                                  float* lse) {
-  float* qs = smem;                         // [4][64]
+// One CTA: 4 query heads of one KV head over tokens [begin, end). A warp takes 32-token tiles;
+// a lane scores one token against the 4 heads, then owns two output dims for the P.V sum.
+// Results: out [4][64] normalised, lse2 [4] (base 2).
+struct AttnAcc {
+  float m[4], l[4], acc[4][2];
+};
+__device__ __forceinline__ void attn_init(AttnAcc& a) {
+#pragma unroll
+  for (int h = 0; h < 4; ++h) { a.m[h] = -INFINITY; a.l[h] = 0.0f; a.acc[h][0] = a.acc[h][1] = 0.0f; }
+}
+
+// One tile of n <= 32 tokens. kchunk(c): 16-byte chunk c (8 dims) of THIS lane's token's key row;
+// vword(j): dims 2*lane, 2*lane+1 of token j's value row. qs: [4][64] queries, pre-scaled, in
+// shared memory.
+template <class KChunk, class VWord>
+__device__ __forceinline__ void attn_tile(AttnAcc& a, const float* qs, int n, int lane, KChunk kchunk,
+                                          VWord vword) {
+  float s[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  if (lane < n) {
+#pragma unroll
+    for (int h = 0; h < 4; ++h) s[h] = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 kk = kchunk(c);
+#pragma unroll
+      for (int h = 0; h < 4; ++h) s[h] += dot8(kk, qs + h * 64 + c * 8);
+    }
+  }
+  float p[4];
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    const float tile_max = warp_max(s[h]);
+    const float new_m = fmaxf(a.m[h], tile_max);
+    const float corr = a.m[h] == -INFINITY ? 0.0f : exp2f(a.m[h] - new_m);
+    p[h] = lane < n ? exp2f(s[h] - new_m) : 0.0f;
+    a.l[h] = a.l[h] * corr + warp_sum(p[h]);
+    a.acc[h][0] *= corr;
+    a.acc[h][1] *= corr;
+    a.m[h] = new_m;
+  }
+  // the value rows are fetched as two batches of 16 independent loads so their latencies overlap
+#pragma unroll
+  for (int jb = 0; jb < 32; jb += 16) {
+    if (jb >= n) break;
+    uint32_t vv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) vv[j] = jb + j < n ? vword(jb + j) : 0u;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float v0 = blo(vv[j]), v1 = bhi(vv[j]);
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const float pj = __shfl_sync(0xFFFFFFFFu, p[h], jb + j);
+        a.acc[h][0] = fmaf(pj, v0, a.acc[h][0]);
+        a.acc[h][1] = fmaf(pj, v1, a.acc[h][1]);
+      }
+    }
+  }
+}
+
+// smem floats: qs [256] | part_m [warps*4] | part_l [warps*4] | part_o [warps*4*64]
+__device__ __forceinline__ void attn_stage_q(const __nv_bfloat16* __restrict__ q, float scale_log2, float* smem) {
+  for (int i = threadIdx.x; i < 256; i += kConsumers) smem[i] = ld_bf16_coherent(q + i) * scale_log2;
+  consumer_sync();
+}
+
+// Merge the 16 warps' states into out [4][64], lse [4].
+__device__ void attn_merge(const AttnAcc& a, float* smem, float* out, float* lse) {
   float* part_m = smem + 256;               // [warps][4]
   float* part_l = part_m + kDecWarps * 4;   // [warps][4]
   float* part_o = part_l + kDecWarps * 4;   // [warps][4][64]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < 256; i += blockDim.x)
-    qs[i] = ld_bf16_coherent(q + i) * scale_log2;
-  __syncthreads();
-  float m[4], l[4], acc[4][2];
-#pragma unroll
-  for (int h = 0; h < 4; ++h) { m[h] = -INFINITY; l[h] = 0.0f; acc[h][0] = acc[h][1] = 0.0f; }
-  for (int t0 = begin + warp * 32; t0 < end; t0 += kDecWarps * 32) {
-    const int t = t0 + lane;
-    float s[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    if (t < end) {
-      const uint4* krow = reinterpret_cast<const uint4*>(k + static_cast<size_t>(t) * kv_stride);
-      uint4 kk[8];
-#pragma unroll
-      for (int c = 0; c < 8; ++c) kk[c] = krow[c];
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        float d = 0.0f;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) d += dot8(kk[c], qs + h * 64 + c * 8);
-        s[h] = d;
-      }
-    }
-    float p[4];
-#pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      const float tile_max = warp_max(s[h]);
-      const float new_m = fmaxf(m[h], tile_max);
-      const float corr = m[h] == -INFINITY ? 0.0f : exp2f(m[h] - new_m);
-      p[h] = t < end ? exp2f(s[h] - new_m) : 0.0f;
-      l[h] = l[h] * corr + warp_sum(p[h]);
-      acc[h][0] *= corr;
-      acc[h][1] *= corr;
-      m[h] = new_m;
-    }
-    const int n = min(32, end - t0);
-    for (int j = 0; j < n; ++j) {
-      const uint32_t vv = *reinterpret_cast<const uint32_t*>(
-          v + static_cast<size_t>(t0 + j) * kv_stride + 2 * lane);
-      const float v0 = blo(vv), v1 = bhi(vv);
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        const float pj = __shfl_sync(0xFFFFFFFFu, p[h], j);
-        acc[h][0] = fmaf(pj, v0, acc[h][0]);
-        acc[h][1] = fmaf(pj, v1, acc[h][1]);
-      }
-    }
-  }
 #pragma unroll
   for (int h = 0; h < 4; ++h) {
-    if (lane == 0) { part_m[warp * 4 + h] = m[h]; part_l[warp * 4 + h] = l[h]; }
-    part_o[(warp * 4 + h) * 64 + 2 * lane] = acc[h][0];
-    part_o[(warp * 4 + h) * 64 + 2 * lane + 1] = acc[h][1];
+    if (lane == 0) { part_m[warp * 4 + h] = a.m[h]; part_l[warp * 4 + h] = a.l[h]; }
+    part_o[(warp * 4 + h) * 64 + 2 * lane] = a.acc[h][0];
+    part_o[(warp * 4 + h) * 64 + 2 * lane + 1] = a.acc[h][1];
   }
-  __syncthreads();
-  // merge the warps: thread (h, d) for h < 4, d < 64
+  consumer_sync();
+  // thread (h, d) for h < 4, d < 64
   if (threadIdx.x < 256) {
     const int h = threadIdx.x >> 6, d = threadIdx.x & 63;
     float mx = -INFINITY;
@@ -268,7 +320,40 @@ __device__ void attention_partial(const __nv_bfloat16* __restrict__ q,
     out[h * 64 + d] = denom > 0.0f ? val / denom : 0.0f;
     if (d == 0) lse[h] = denom > 0.0f ? mx + log2f(denom) : -INFINITY;
   }
-  __syncthreads();
+  consumer_sync();
+}
+
+// Tokens [begin, end) straight from global memory (coherent loads: rows may have been written
+// by other SMs earlier in this launch). k, v: first token's row of this KV head; kv_stride:
+// elements between consecutive tokens.
+__device__ __forceinline__ void attn_tiles_global(AttnAcc& a, const float* qs, const __nv_bfloat16* k,
+                                                  const __nv_bfloat16* v, int kv_stride, int begin, int end,
+                                                  int first_warp, int num_warps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < first_warp || warp >= first_warp + num_warps) return;
+  for (int t0 = begin + (warp - first_warp) * 32; t0 < end; t0 += num_warps * 32) {
+    const int n = min(32, end - t0);
+    const __nv_bfloat16* krow = k + static_cast<size_t>(t0 + min(lane, n - 1)) * kv_stride;
+    attn_tile(a, qs, n, lane,
+              [&](int c) { return ld_coherent_v4(krow + c * 8); },
+              [&](int j) {
+                uint32_t w;
+                asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(w) : "l"(v + static_cast<size_t>(t0 + j) * kv_stride + 2 * lane) : "memory");
+                return w;
+              });
+  }
+}
+
+__device__ void attention_partial(const __nv_bfloat16* __restrict__ q,
+                                  const __nv_bfloat16* __restrict__ k,
+                                  const __nv_bfloat16* __restrict__ v, int kv_stride, int begin,
+                                  int end, float scale_log2, float* smem, float* out,
+                                  float* lse) {
+  attn_stage_q(q, scale_log2, smem);
+  AttnAcc a;
+  attn_init(a);
+  attn_tiles_global(a, smem, k, v, kv_stride, begin, end, 0, kDecWarps);
+  attn_merge(a, smem, out, lse);
 }
 
 __device__ __forceinline__ void partition_range(int length, int partitions, int part, int& begin,
@@ -280,43 +365,155 @@ __device__ __forceinline__ void partition_range(int length, int partitions, int 
   if (begin > end) begin = end;
 }
 
-// L2 prefetch of the weight rows an instruction will stream.
-__device__ void prefetch_weights(const DecodeGlobals& g, const int* in) {
-  const int op = in[0], layer = in[1], a0 = in[2], a1 = in[3];
-  const __nv_bfloat16* wbase = nullptr;
-  const __nv_bfloat16* wbase2 = nullptr;
-  size_t wbytes = 0;
-  if (op == 1) { wbase = g.qkv_w + (static_cast<size_t>(layer) * kQkvRows + a0) * kHidden; wbytes = static_cast<size_t>(a1) * kHidden * 2; }
-  if (op == 4) { wbase = g.o_w + (static_cast<size_t>(layer) * kHidden + a0) * kHidden; wbytes = static_cast<size_t>(a1) * kHidden * 2; }
-  if (op == 5) {
-    wbase = g.gate_w + (static_cast<size_t>(layer) * kFfn + a0) * kHidden;
-    wbase2 = g.up_w + (static_cast<size_t>(layer) * kFfn + a0) * kHidden;
-    wbytes = static_cast<size_t>(a1) * kHidden * 2;
-  }
-  if (op == 6) { wbase = g.down_w + (static_cast<size_t>(layer) * kHidden + a0) * kFfn; wbytes = static_cast<size_t>(a1) * kFfn * 2; }
-  if (op == 7) {  // the LM head (525 MB) exceeds L2: only its first 512 KB per SM is worth prefetching
-    wbase = g.lm_head + static_cast<size_t>(a0) * kHidden;
-    wbytes = static_cast<size_t>(a1) * kHidden * 2;
-    if (wbytes > (512u << 10)) wbytes = 512u << 10;
-  }
-  if (wbase == nullptr) return;
-  const char* pa = reinterpret_cast<const char*>(wbase);
-  for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < wbytes; off += kDecThreads * 128) {
-    prefetch_l2(pa + off);
-    if (wbase2 != nullptr) prefetch_l2(reinterpret_cast<const char*>(wbase2) + off);
+#ifdef PLB_DECODE_PROFILE
+// Profiling builds: per CTA and opcode, cycles spent waiting for the dependency, working, and
+// signalling, accumulated by thread 0 into [grid][9][4] i64 (last slot: instruction count).
+__device__ long long* g_decode_profile = nullptr;
+#define DEC_PROF_T(var) const long long var = clock64()
+#define DEC_PROF_ADD(op, slot, cycles)                                                        \
+  if (threadIdx.x == 0 && g_decode_profile != nullptr)                                        \
+  g_decode_profile[(static_cast<size_t>(blockIdx.x) * 9 + (op)) * 4 + (slot)] += (cycles)
+#else
+#define DEC_PROF_T(var)
+#define DEC_PROF_ADD(op, slot, cycles)
+#endif
+
+// Op 3: merge the partials of heads [head0, head0 + nheads) over `parts` partitions. One warp
+// per (head, 16 output dims); lanes take partitions, so every load of the merge is issued at once.
+__device__ void merge_heads(const DecodeGlobals& g, int a0, int a1, int a2) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int task = warp; task < a1 * 4; task += kDecWarps) {
+    const int head = a0 + (task >> 2), d0 = (task & 3) * 16;
+    const volatile float* lse = g.attn_lse_partial + static_cast<size_t>(head) * g.max_parts;
+    float mx = -INFINITY;
+    for (int p = lane; p < a2; p += 32) mx = fmaxf(mx, lse[p]);
+    mx = warp_max(mx);
+    float sum = 0.0f, val[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) val[e] = 0.0f;
+    if (mx != -INFINITY) {
+      for (int p = lane; p < a2; p += 32) {
+        const float lp = lse[p];
+        const float w = lp == -INFINITY ? 0.0f : exp2f(lp - mx);
+        sum += w;
+        const float* src = g.attn_out_partial + (static_cast<size_t>(head) * g.max_parts + p) * 64 + d0;
+        float4 o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(o[q].x), "=f"(o[q].y), "=f"(o[q].z), "=f"(o[q].w)
+                       : "l"(src + q * 4)
+                       : "memory");
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          val[q * 4 + 0] = fmaf(w, o[q].x, val[q * 4 + 0]);
+          val[q * 4 + 1] = fmaf(w, o[q].y, val[q * 4 + 1]);
+          val[q * 4 + 2] = fmaf(w, o[q].z, val[q * 4 + 2]);
+          val[q * 4 + 3] = fmaf(w, o[q].w, val[q * 4 + 3]);
+        }
+      }
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) val[e] = warp_sum(val[e]);
+    if (lane < 16) {
+      float mine = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) mine = lane == e ? val[e] : mine;
+      g.attn_out[head * 64 + d0 + lane] = __float2bfloat16_rn(sum > 0.0f ? mine / sum : 0.0f);
+    }
   }
 }
 
+// Ring stages of a partial-attention instruction: tokens [begin, lim) of one KV head, 128 per
+// stage (16 KB of keys then 16 KB of values, rows of 128 bytes with the 128-byte swizzle). The
+// token being decoded (row `pos`, written earlier in this launch) never goes through the ring.
+struct AttnPlan {
+  int begin, end, lim, stages;
+};
+__device__ __forceinline__ AttnPlan attn_plan_of(const int* in, int pos) {
+  AttnPlan a;
+  partition_range(pos + 1, in[3], in[4], a.begin, a.end);
+  a.lim = min(a.end, pos);
+  a.stages = a.lim > a.begin ? (a.lim - a.begin + 127) / 128 : 0;
+  return a;
+}
+
+struct DecBars {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+};
+
 // ---------------------------------------------------------------- the interpreter
-__global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const DecodeGlobals g) {
-  extern __shared__ __align__(16) float dsm[];
-  float* x = dsm;                 // up to 8192 floats
-  float* red = dsm + kFfn;        // 64 floats
-  float* scratch = red + 64;      // attention workspace / argmax
+__global__ void __launch_bounds__(kDecThreads, 1)
+decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+  extern __shared__ __align__(1024) uint8_t dsm_raw[];
+  uint8_t* ring = dsm_raw;                                                   // kStages x 32 KB
+  DecBars* bars = reinterpret_cast<DecBars*>(dsm_raw + kStages * kStageBytes);
+  float* partial = reinterpret_cast<float*>(dsm_raw + kStages * kStageBytes + 128);
+  float* scratch = partial + kPartialFloats;                                 // attention workspace / argmax
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = *g.pos_dev;
   const int* my = g.instructions + static_cast<size_t>(blockIdx.x) * g.num_instructions * 32;
 
+  __shared__ int stage_failed;  // a consumer warp gave up on a stage: all leave together at the next barrier
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), kDecWarps);
+    }
+    stage_failed = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == kDecWarps) {
+    // ---------------------------------------------------------------- weight producer
+    if (lane != 0) return;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int ip = 0; ip < g.num_instructions && ok; ++ip) {
+      const int* in = my + ip * 32;
+      if (in[0] == 2) {
+        const AttnPlan ap = attn_plan_of(in, pos);
+        for (int st = 0; st < ap.stages; ++st, ++it) {
+          const int slot = it % kStages;
+          if (!mbar_wait(smem_u32(&bars->empty[slot]), ((it / kStages) & 1u) ^ 1u, g.status, ST_TIMEOUT_EMPTY, 902)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bars->full[slot]);
+          const uint32_t dst = smem_u32(ring + slot * kStageBytes);
+          mbar_arrive_expect_tx(full, kStageBytes);
+          tma_load_4d(dst, &map_k, full, 0, in[2], ap.begin + st * 128, in[1]);
+          tma_load_4d(dst + kStageBytes / 2, &map_v, full, 0, in[2], ap.begin + st * 128, in[1]);
+        }
+        continue;
+      }
+      const Plan pl = plan_of(g, in);
+      if (pl.nmat == 0) continue;
+      const int row_bytes = pl.K * 2, rps = kStageBytes / row_bytes, brows = block_rows_of(pl);
+      for (int b0 = 0; b0 < pl.rows && ok; b0 += brows) {
+        const int nb = min(brows, pl.rows - b0);
+        for (int m = 0; m < pl.nmat && ok; ++m) {
+          for (int r0 = 0; r0 < nb; r0 += rps, ++it) {
+            const int slot = it % kStages;
+            if (!mbar_wait(smem_u32(&bars->empty[slot]), ((it / kStages) & 1u) ^ 1u, g.status, ST_TIMEOUT_EMPTY, 900 + in[0])) { ok = false; break; }
+            const uint32_t bytes = static_cast<uint32_t>(min(rps, nb - r0)) * row_bytes;
+            const uint32_t full = smem_u32(&bars->full[slot]);
+            mbar_arrive_expect_tx(full, bytes);
+            bulk_load(smem_u32(ring + slot * kStageBytes), pl.base[m] + static_cast<size_t>(b0 + r0) * row_bytes, bytes, full);
+          }
+        }
+      }
+    }
+    if (!ok) {  // let copies in flight land before the CTA's shared memory is released
+      const long long t0 = clock64();
+      while (clock64() - t0 < 400000LL) {
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ consumers
+  uint32_t it = 0;
   for (int ip = 0; ip < g.num_instructions; ++ip) {
     const int* in = my + ip * 32;
     const int op = in[0];
@@ -324,163 +521,228 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const DecodeGlob
     const int layer = in[1], a0 = in[2], a1 = in[3], a2 = in[4];
     const int dep = in[6], sig = in[8];
     const unsigned dep_target = static_cast<unsigned>(in[7]);
-
-    // Keep HBM busy across the dependency stalls: the first instruction prefetches its own
-    // weight rows into L2, every instruction prefetches the rows of the next one before it
-    // starts computing, so a matvec mostly reads L2 while HBM streams the following slice.
-    if (ip == 0) prefetch_weights(g, in);
-    if (ip + 1 < g.num_instructions) prefetch_weights(g, in + 32);
+    DEC_PROF_T(t_start);
     if (dep >= 0) {
       if (!wait_counter(g.bars + dep, dep_target, g.status, op * 100 + layer)) return;
     }
+    DEC_PROF_T(t_dep);
 
-    if (op == 1) {
-      // RMSNorm(hidden) -> rows [a0, a0+a1) of W_qkv -> RoPE on q/k pairs -> q_post_rope / KV append
-      stage_vector(g.hidden, g.attn_norm + static_cast<size_t>(layer) * kHidden, kHidden, g.eps, x, red);
-      const uint4* W = reinterpret_cast<const uint4*>(g.qkv_w + static_cast<size_t>(layer) * kQkvRows * kHidden);
-      for (int pr = warp; pr < a1 / 2; pr += kDecWarps) {
-        const int r = a0 + 2 * pr;
-        float s0, s1;
-        warp_dot2(W + static_cast<size_t>(r) * (kHidden / 8), W + static_cast<size_t>(r + 1) * (kHidden / 8), x, kHidden / 8, lane, s0, s1);
-        if (lane == 0) {
-          const size_t cache_row = (static_cast<size_t>(layer) * g.max_seq_len + pos) * (kKvHeads * kHeadDim);
-          if (r < (kQHeads + kKvHeads) * kHeadDim) {
-            const int pair = (r & (kHeadDim - 1)) >> 1;
-            const float c = g.rope_cos[static_cast<size_t>(pos) * 32 + pair];
-            const float sn = g.rope_sin[static_cast<size_t>(pos) * 32 + pair];
-            const float o0 = s0 * c - s1 * sn, o1 = s1 * c + s0 * sn;
-            if (r < kQHeads * kHeadDim) {
-              g.q_post_rope[r] = __float2bfloat16_rn(o0);
-              g.q_post_rope[r + 1] = __float2bfloat16_rn(o1);
-            } else {
-              const int kr = r - kQHeads * kHeadDim;
-              g.k_cache[cache_row + kr] = __float2bfloat16_rn(o0);
-              g.k_cache[cache_row + kr + 1] = __float2bfloat16_rn(o1);
+    const Plan pl = plan_of(g, in);
+    if (pl.nmat != 0) {
+      // ---- matvec ops: partial sums of every row of the block, then the op's epilogue
+      const int wpr = pl.K / 1024;          // warps per row: 2 or 8
+      const int sec = warp % wpr, row_in_stage = warp / wpr;
+      const int rps = kStageBytes / (pl.K * 2), brows = block_rows_of(pl);
+      float xr[32];
+      if (op == 1) load_x(g.hidden, g.attn_norm + static_cast<size_t>(layer) * kHidden, sec, lane, g.eps, xr);
+      else if (op == 4) load_x(g.attn_out, nullptr, sec, lane, g.eps, xr);
+      else if (op == 5) load_x(g.hidden, g.mlp_norm + static_cast<size_t>(layer) * kHidden, sec, lane, g.eps, xr);
+      else if (op == 6) load_x(g.silu_out, nullptr, sec, lane, g.eps, xr);
+      else load_x(g.hidden, g.lm_norm, sec, lane, g.eps, xr);
+      float best = -INFINITY;
+      int best_idx = 0x7FFFFFFF;
+      for (int b0 = 0; b0 < pl.rows; b0 += brows) {
+        const int nb = min(brows, pl.rows - b0);
+        bool ok = true;
+        for (int m = 0; m < pl.nmat && ok; ++m) {
+          for (int r0 = 0; r0 < nb; r0 += rps, ++it) {
+            const int slot = it % kStages;
+            if (!mbar_wait(smem_u32(&bars->full[slot]), (it / kStages) & 1u, g.status, ST_TIMEOUT_FULL, 800 + op)) { ok = false; break; }
+            if (r0 + row_in_stage < nb) {
+              const uint4* src = reinterpret_cast<const uint4*>(ring + slot * kStageBytes + warp * kTaskBytes);
+              uint4 w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) w[i] = src[lane + 32 * i];
+              float acc = 0.0f;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) acc += dot8r(w[i], xr + i * 8);
+              acc = warp_sum(acc);
+              if (lane == 0) partial[(m * nb + r0 + row_in_stage) * wpr + sec] = acc;
             }
-          } else {
-            const int vr = r - (kQHeads + kKvHeads) * kHeadDim;
-            g.v_cache[cache_row + vr] = __float2bfloat16_rn(s0);
-            g.v_cache[cache_row + vr + 1] = __float2bfloat16_rn(s1);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->empty[slot]));
           }
+        }
+        // a failed wait has set the status word, so every other warp's wait gives up too and all
+        // 16 warps still meet at this barrier before leaving
+        if (!ok) *reinterpret_cast<volatile int*>(&stage_failed) = 1;
+        consumer_sync();
+        if (*reinterpret_cast<volatile int*>(&stage_failed) != 0) return;
+        // ---- epilogue of rows [b0, b0 + nb) of this instruction's slice
+        auto row_sum = [&](int idx) {
+          float v = 0.0f;
+          for (int q = 0; q < wpr; ++q) v += partial[idx * wpr + q];
+          return v;
+        };
+        if (op == 1) {
+          for (int pr = threadIdx.x; pr < nb / 2; pr += kConsumers) {
+            const int r = a0 + b0 + 2 * pr;
+            const float s0 = row_sum(2 * pr), s1 = row_sum(2 * pr + 1);
+            const size_t cache_row = (static_cast<size_t>(layer) * g.max_seq_len + pos) * (kKvHeads * kHeadDim);
+            if (r < (kQHeads + kKvHeads) * kHeadDim) {
+              const int pair = (r & (kHeadDim - 1)) >> 1;
+              const float c = g.rope_cos[static_cast<size_t>(pos) * 32 + pair];
+              const float sn = g.rope_sin[static_cast<size_t>(pos) * 32 + pair];
+              const float o0 = s0 * c - s1 * sn, o1 = s1 * c + s0 * sn;
+              if (r < kQHeads * kHeadDim) {
+                g.q_post_rope[r] = __float2bfloat16_rn(o0);
+                g.q_post_rope[r + 1] = __float2bfloat16_rn(o1);
+              } else {
+                const int kr = r - kQHeads * kHeadDim;
+                g.k_cache[cache_row + kr] = __float2bfloat16_rn(o0);
+                g.k_cache[cache_row + kr + 1] = __float2bfloat16_rn(o1);
+              }
+            } else {
+              const int vr = r - (kQHeads + kKvHeads) * kHeadDim;
+              g.v_cache[cache_row + vr] = __float2bfloat16_rn(s0);
+              g.v_cache[cache_row + vr + 1] = __float2bfloat16_rn(s1);
+            }
+          }
+        } else if (op == 4 || op == 6) {
+          for (int i = threadIdx.x; i < nb; i += kConsumers) {
+            const int r = a0 + b0 + i;
+            g.hidden[r] = __float2bfloat16_rn(ld_bf16_coherent(g.hidden + r) + row_sum(i));
+          }
+        } else if (op == 5) {
+          for (int i = threadIdx.x; i < nb; i += kConsumers) {
+            const float sg = row_sum(i), su = row_sum(nb + i);
+            g.silu_out[a0 + b0 + i] = __float2bfloat16_rn(sg / (1.0f + __expf(-sg)) * su);
+          }
+        } else {
+          for (int i = threadIdx.x; i < nb; i += kConsumers) {
+            const int r = a0 + b0 + i;
+            const __nv_bfloat16 bv16 = __float2bfloat16_rn(row_sum(i));
+            g.logits[r] = bv16;
+            const float f = __bfloat162float(bv16);
+            if (f > best || (f == best && r < best_idx)) { best = f; best_idx = r; }
+          }
+        }
+        consumer_sync();  // partial sums are free for the next block
+      }
+      if (op == 7) {
+        // lowest id among the maxima of this CTA's slice
+        const float wbest = warp_max(best);
+        int cand = best == wbest ? best_idx : 0x7FFFFFFF;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) cand = min(cand, __shfl_xor_sync(0xFFFFFFFFu, cand, d));
+        float* bv = scratch;
+        int* bi = reinterpret_cast<int*>(scratch + kDecWarps);
+        if (lane == 0) { bv[warp] = wbest; bi[warp] = cand; }
+        consumer_sync();
+        if (threadIdx.x == 0) {
+          float cb = bv[0];
+          int ci = bi[0];
+          for (int w = 1; w < kDecWarps; ++w)
+            if (bv[w] > cb || (bv[w] == cb && bi[w] < ci)) { cb = bv[w]; ci = bi[w]; }
+          g.argmax_val[blockIdx.x] = cb;
+          g.argmax_idx[blockIdx.x] = ci;
         }
       }
     } else if (op == 2) {
-      // a0 = kv head, a1 = partitions, a2 = partition index
-      int begin, end;
-      partition_range(pos + 1, a1, a2, begin, end);
+      // a0 = kv head, a1 = partitions, a2 = partition index, word 5 = 1 + arrival counter of this
+      // KV head when the last partition to finish also merges (op 3 folded in), else 0
+      const AttnPlan ap = attn_plan_of(in, pos);
       const size_t kv_base = static_cast<size_t>(layer) * g.max_seq_len * (kKvHeads * kHeadDim) + a0 * kHeadDim;
-      // partial layout: [head][part][64]; heads of this KV head are a0*4 .. a0*4+3
       float* tmp_out = scratch + 256 + kDecWarps * 8 + kDecWarps * 256;
       float* tmp_lse = tmp_out + 256;
-      attention_partial(g.q_post_rope + a0 * 4 * kHeadDim, g.k_cache + kv_base, g.v_cache + kv_base,
-                        kKvHeads * kHeadDim, begin, end, g.attn_scale * 1.4426950408889634f, scratch,
-                        tmp_out, tmp_lse);
+      attn_stage_q(g.q_post_rope + a0 * 4 * kHeadDim, g.attn_scale * 1.4426950408889634f, scratch);
+      AttnAcc acc;
+      attn_init(acc);
+      bool ok = true;
+      for (int st = 0; st < ap.stages; ++st, ++it) {
+        const int slot = it % kStages;
+        if (!mbar_wait(smem_u32(&bars->full[slot]), (it / kStages) & 1u, g.status, ST_TIMEOUT_FULL, 802)) { ok = false; break; }
+        if ((warp >> 2) == (st & 3)) {   // four warps per stage, rotating, so stages overlap
+          const int row0 = (warp & 3) * 32;
+          const int n = min(32, ap.lim - (ap.begin + st * 128 + row0));
+          if (n > 0) {
+            const uint8_t* kb = ring + slot * kStageBytes;
+            const uint8_t* vb = kb + kStageBytes / 2;
+            const int krow = row0 + lane;
+            attn_tile(acc, scratch, n, lane,
+                      [&](int c) { return *reinterpret_cast<const uint4*>(kb + krow * 128 + ((c ^ (krow & 7)) << 4)); },
+                      [&](int j) {
+                        const int r = row0 + j;
+                        return *reinterpret_cast<const uint32_t*>(vb + r * 128 + (((lane >> 2) ^ (r & 7)) << 4) + (lane & 3) * 4);
+                      });
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->empty[slot]));
+      }
+      // the token being decoded: its K/V row was written by the QKV op of this launch
+      if (pos >= ap.begin && pos < ap.end)
+        attn_tiles_global(acc, scratch, g.k_cache + kv_base, g.v_cache + kv_base, kKvHeads * kHeadDim, pos, pos + 1,
+                          kDecWarps - 1, 1);
+      if (!ok) *reinterpret_cast<volatile int*>(&stage_failed) = 1;
+      attn_merge(acc, scratch, tmp_out, tmp_lse);
+      if (*reinterpret_cast<volatile int*>(&stage_failed) != 0) return;
+      // partial layout: [head][part][64]; heads of this KV head are a0*4 .. a0*4+3
       if (threadIdx.x < 256) {
         const int h = threadIdx.x >> 6, d = threadIdx.x & 63;
         g.attn_out_partial[(static_cast<size_t>(a0 * 4 + h) * g.max_parts + a2) * 64 + d] = tmp_out[h * 64 + d];
         if (d == 0) g.attn_lse_partial[static_cast<size_t>(a0 * 4 + h) * g.max_parts + a2] = tmp_lse[h];
       }
+      if (in[5] > 0) {
+        // count this partition in; whoever completes the KV head merges its four heads and
+        // signals, everyone else moves on without signalling
+        __shared__ int is_last;
+        consumer_sync();
+        if (threadIdx.x == 0) {
+          __threadfence();
+          const unsigned before = atomicAdd(g.bars + (in[5] - 1), 1u);
+          __threadfence();
+          is_last = before + 1u == static_cast<unsigned>(a1);
+        }
+        consumer_sync();
+        const bool last = is_last != 0;
+        if (last) merge_heads(g, a0 * 4, 4, a1);
+        if (sig >= 0 && last) signal_counter(g.bars + sig);
+        consumer_sync();
+        continue;
+      }
     } else if (op == 3) {
-      // merge partials of heads [a0, a0+a1): a2 = partitions
-      for (int idx = threadIdx.x; idx < a1 * 64; idx += blockDim.x) {
-        const int head = a0 + idx / 64, d = idx & 63;
-        const volatile float* lse = g.attn_lse_partial + static_cast<size_t>(head) * g.max_parts;
-        float mx = -INFINITY;
-        for (int p = 0; p < a2; ++p) mx = fmaxf(mx, lse[p]);
-        float sum = 0.0f, val = 0.0f;
-        if (mx != -INFINITY) {
-          for (int p = 0; p < a2; ++p) {
-            const float lp = lse[p];
-            const float w = lp == -INFINITY ? 0.0f : exp2f(lp - mx);
-            sum += w;
-            val += w * *reinterpret_cast<const volatile float*>(
-                           g.attn_out_partial + (static_cast<size_t>(head) * g.max_parts + p) * 64 + d);
-          }
-        }
-        g.attn_out[head * 64 + d] = __float2bfloat16_rn(sum > 0.0f ? val / sum : 0.0f);
-      }
-    } else if (op == 4 || op == 6) {
-      // hidden[r] += W[r, :] . v   (v = attn_out for 4, silu_out for 6)
-      const int K = op == 4 ? kHidden : kFfn;
-      stage_vector(op == 4 ? g.attn_out : g.silu_out, nullptr, K, g.eps, x, red);
-      const __nv_bfloat16* Wb = op == 4 ? g.o_w + static_cast<size_t>(layer) * kHidden * kHidden
-                                        : g.down_w + static_cast<size_t>(layer) * kHidden * kFfn;
-      const uint4* W = reinterpret_cast<const uint4*>(Wb);
-      for (int pr = warp; pr < a1 / 2; pr += kDecWarps) {
-        const int r = a0 + 2 * pr;
-        float s0, s1;
-        warp_dot2(W + static_cast<size_t>(r) * (K / 8), W + static_cast<size_t>(r + 1) * (K / 8), x, K / 8, lane, s0, s1);
-        if (lane == 0) {
-          g.hidden[r] = __float2bfloat16_rn(ld_bf16_coherent(g.hidden + r) + s0);
-          g.hidden[r + 1] = __float2bfloat16_rn(ld_bf16_coherent(g.hidden + r + 1) + s1);
-        }
-      }
-    } else if (op == 5) {
-      stage_vector(g.hidden, g.mlp_norm + static_cast<size_t>(layer) * kHidden, kHidden, g.eps, x, red);
-      const uint4* G = reinterpret_cast<const uint4*>(g.gate_w + static_cast<size_t>(layer) * kFfn * kHidden);
-      const uint4* U = reinterpret_cast<const uint4*>(g.up_w + static_cast<size_t>(layer) * kFfn * kHidden);
-      for (int i = warp; i < a1; i += kDecWarps) {
-        const int r = a0 + i;
-        float sg, su;
-        warp_dot2(G + static_cast<size_t>(r) * (kHidden / 8), U + static_cast<size_t>(r) * (kHidden / 8), x, kHidden / 8, lane, sg, su);
-        if (lane == 0) g.silu_out[r] = __float2bfloat16_rn(sg / (1.0f + __expf(-sg)) * su);
-      }
-    } else if (op == 7) {
-      stage_vector(g.hidden, g.lm_norm, kHidden, g.eps, x, red);
-      const uint4* W = reinterpret_cast<const uint4*>(g.lm_head);
-      float best = -INFINITY;
-      int best_idx = 0x7FFFFFFF;
-      for (int pr = warp; pr < a1 / 2; pr += kDecWarps) {
-        const int r = a0 + 2 * pr;
-        float s0, s1;
-        warp_dot2(W + static_cast<size_t>(r) * (kHidden / 8), W + static_cast<size_t>(r + 1) * (kHidden / 8), x, kHidden / 8, lane, s0, s1);
-        if (lane == 0) {
-          const __nv_bfloat16 b0 = __float2bfloat16_rn(s0), b1 = __float2bfloat16_rn(s1);
-          g.logits[r] = b0;
-          g.logits[r + 1] = b1;
-          const float f0 = __bfloat162float(b0), f1 = __bfloat162float(b1);
-          if (f0 > best || (f0 == best && r < best_idx)) { best = f0; best_idx = r; }
-          if (f1 > best || (f1 == best && r + 1 < best_idx)) { best = f1; best_idx = r + 1; }
-        }
-      }
-      float* bv = scratch;
-      int* bi = reinterpret_cast<int*>(scratch + kDecWarps);
-      if (lane == 0) { bv[warp] = best; bi[warp] = best_idx; }
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        for (int w = 1; w < kDecWarps; ++w)
-          if (bv[w] > best || (bv[w] == best && bi[w] < best_idx)) { best = bv[w]; best_idx = bi[w]; }
-        g.argmax_val[blockIdx.x] = best;
-        g.argmax_idx[blockIdx.x] = best_idx;
-      }
+      merge_heads(g, a0, a1, a2);
     } else if (op == 8) {
       // greedy sample over the per-SM candidates (a0 = how many), next embedding row, position + 1
       __shared__ int token;
-      if (threadIdx.x == 0) {
+      if (warp == 0) {
         float best = -INFINITY;
         int best_idx = 0x7FFFFFFF;
-        for (int i = 0; i < a0; ++i) {
+        for (int i = lane; i < a0; i += 32) {
           const float v = *reinterpret_cast<const volatile float*>(g.argmax_val + i);
           const int id = *reinterpret_cast<const volatile int*>(g.argmax_idx + i);
           if (v > best || (v == best && id < best_idx)) { best = v; best_idx = id; }
         }
-        token = best_idx;
-        g.token_out[pos + 1] = best_idx;
-        *g.pos_dev = pos + 1;
+        const float wbest = warp_max(best);
+        int cand = best == wbest ? best_idx : 0x7FFFFFFF;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) cand = min(cand, __shfl_xor_sync(0xFFFFFFFFu, cand, d));
+        if (lane == 0) {
+          token = cand;
+          g.token_out[pos + 1] = cand;
+          *g.pos_dev = pos + 1;
+        }
       }
-      __syncthreads();
+      consumer_sync();
       const __nv_bfloat16* row = g.lm_head + static_cast<size_t>(token) * kHidden;
-      for (int i = threadIdx.x; i < kHidden; i += blockDim.x) g.hidden[i] = row[i];
+      for (int i = threadIdx.x; i < kHidden; i += kConsumers) g.hidden[i] = row[i];
     }
+    DEC_PROF_T(t_work);
     if (sig >= 0) signal_counter(g.bars + sig);
-    __syncthreads();
+    consumer_sync();
+    DEC_PROF_T(t_end);
+    DEC_PROF_ADD(op, 0, t_dep - t_start);
+    DEC_PROF_ADD(op, 1, t_work - t_dep);
+    DEC_PROF_ADD(op, 2, t_end - t_work);
+    DEC_PROF_ADD(op, 3, 1);
   }
 }
 
 // Standalone harness for op 2 with the layout of the reference's checker
 // (campaigns/megakernel/host/check_cute_attention.cu:16-45): grid = 8 * partitions CTAs,
 // q bf16 [32][64], k/v bf16 [length][8][64], out f32 [(head*partitions+part)*4 + h][64].
-__global__ void __launch_bounds__(kDecThreads, 1)
+__global__ void __launch_bounds__(kConsumers, 1)
 attention_partial_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                          float* out, float* lse, int length, int partitions, float scale) {
   extern __shared__ __align__(16) float dsm[];
@@ -500,17 +762,77 @@ attention_partial_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k, const _
   }
 }
 
-constexpr int kDecodeSmemFloats = kFfn + 64 + 256 + kDecWarps * 8 + kDecWarps * 256 + 256 + 8;
 constexpr int kAttnSmemFloats = 256 + kDecWarps * 8 + kDecWarps * 256 + 256 + 8;
+constexpr int kDecodeSmemBytes = kStages * kStageBytes + 128 + (kPartialFloats + kAttnSmemFloats) * 4;
+static_assert(sizeof(DecBars) <= 128, "barrier block");
+static_assert(kDecodeSmemBytes <= 227 * 1024, "shared memory budget");
+
+}  // namespace
+
+#ifdef PLB_DECODE_PROFILE
+cudaError_t set_decode_profile(void* buffer) {
+  long long* p = static_cast<long long*>(buffer);
+  return cudaMemcpyToSymbol(g_decode_profile, &p, sizeof(p));
+}
+#endif
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// KV cache [layers, max_seq_len, 8, 64] bf16 as a 4-D tensor; box = 128 tokens of one KV head
+// (rows of 128 bytes, 128-byte swizzle). Rows past max_seq_len read as zeros.
+bool encode_kv_map(CUtensorMap* map, const void* base, int layers, int max_seq_len) {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return false;
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(kKvHeads),
+                              static_cast<cuuint64_t>(max_seq_len), static_cast<cuuint64_t>(layers)};
+  const cuuint64_t strides[3] = {kHeadDim * 2, kKvHeads * kHeadDim * 2,
+                                 static_cast<cuuint64_t>(max_seq_len) * kKvHeads * kHeadDim * 2};
+  const cuuint32_t box[4] = {kHeadDim, 1, 128, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The maps depend only on (cache address, layers, max_seq_len): one decode session reuses them.
+struct KvMapCache {
+  const void* k = nullptr;
+  const void* v = nullptr;
+  int layers = 0, max_seq_len = 0;
+  CUtensorMap map_k, map_v;
+};
 
 }  // namespace
 
 cudaError_t launch_decode_step(const DecodeGlobals& g, int num_sms, cudaStream_t stream) {
-  const int smem = kDecodeSmemFloats * 4;
+  const int smem = kDecodeSmemBytes;
+  static thread_local KvMapCache cache;
+  if (cache.k != g.k_cache || cache.v != g.v_cache || cache.layers != g.layers || cache.max_seq_len != g.max_seq_len) {
+    if (g.layers < 1 || g.max_seq_len < 1 || !encode_kv_map(&cache.map_k, g.k_cache, g.layers, g.max_seq_len) ||
+        !encode_kv_map(&cache.map_v, g.v_cache, g.layers, g.max_seq_len)) {
+      cache.k = nullptr;
+      return cudaErrorInvalidValue;
+    }
+    cache.k = g.k_cache;
+    cache.v = g.v_cache;
+    cache.layers = g.layers;
+    cache.max_seq_len = g.max_seq_len;
+  }
   cudaError_t err = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess) return err;
   DecodeGlobals copy = g;
-  void* args[] = {&copy};
+  void* args[] = {&copy, &cache.map_k, &cache.map_v};
   // cooperative launch: every CTA of the grid is resident, which the counter waits rely on
   return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(decode_kernel), dim3(num_sms),
                                      dim3(kDecThreads), args, smem, stream);
@@ -523,7 +845,7 @@ cudaError_t launch_attention_partial(const void* q, const void* k, const void* v
   cudaError_t err = cudaFuncSetAttribute(attention_partial_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess) return err;
-  attention_partial_kernel<<<kKvHeads * partitions, kDecThreads, smem, stream>>>(
+  attention_partial_kernel<<<kKvHeads * partitions, kConsumers, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
       static_cast<const __nv_bfloat16*>(v), out, lse, length, partitions, scale);
   return cudaGetLastError();

@@ -32,7 +32,7 @@ class DecodeArgs(ctypes.Structure):
         "instructions", "pos_dev", "token_out", "status")] +
         [(n, ctypes.c_int32) for n in ("num_instructions", "max_seq_len", "max_parts", "vocab")] +
         [("attn_scale", ctypes.c_float), ("eps", ctypes.c_float), ("num_bars", ctypes.c_int32),
-         ("reserved", ctypes.c_int32)])
+         ("layers", ctypes.c_int32)])
 
 
 def split_even(units: int, parts: int):
@@ -47,16 +47,22 @@ def split_even(units: int, parts: int):
     return out
 
 
-def build_schedule(num_sms: int, layers: int, vocab: int, partitions: int):
-    """Returns (instructions i32 [num_sms, n, 32] as a CPU tensor, number of counters)."""
+def build_schedule(num_sms: int, layers: int, vocab: int, partitions: int, fuse_reduce: bool = True):
+    """Returns (instructions i32 [num_sms, n, 32] as a CPU tensor, number of counters).
+
+    With `fuse_reduce` the partitions of a KV head count themselves in on one extra counter per
+    (layer, KV head) and the last to arrive merges the head's partials, so opcode 3 is not
+    emitted and a layer has five dependent stages instead of six."""
     if vocab // 2 < num_sms:
         raise ValueError("vocab too small: every SM must own an LM-head slice")
     per_sm = [[] for _ in range(num_sms)]
     bar = lambda layer, op: layer * 8 + op
     rr = 0  # rotating start so small ops do not always land on SM 0
 
-    def emit(sm, op, layer, a0, a1, a2, dep, target, sig):
-        per_sm[sm].append([op, layer, a0, a1, a2, 0, dep, target, sig] + [0] * 23)
+    def emit(sm, op, layer, a0, a1, a2, dep, target, sig, a3=0):
+        per_sm[sm].append([op, layer, a0, a1, a2, a3, dep, target, sig] + [0] * 23)
+
+    arrive = lambda layer, kvh: (layers + 1) * 8 + layer * KV_HEADS + kvh
 
     n_down_prev = 0
     for l in range(layers):
@@ -65,13 +71,18 @@ def build_schedule(num_sms: int, layers: int, vocab: int, partitions: int):
         for sm, (s, n) in enumerate(qkv):
             emit(sm, OP_QKV, l, 2 * s, 2 * n, 0, dep, target, bar(l, OP_QKV))
         for t in range(KV_HEADS * partitions):
-            emit((rr + t) % num_sms, OP_ATTN, l, t // partitions, partitions, t % partitions,
-                 bar(l, OP_QKV), len(qkv), bar(l, OP_ATTN))
+            if fuse_reduce:
+                emit((rr + t) % num_sms, OP_ATTN, l, t // partitions, partitions, t % partitions,
+                     bar(l, OP_QKV), len(qkv), bar(l, OP_REDUCE), 1 + arrive(l, t // partitions))
+            else:
+                emit((rr + t) % num_sms, OP_ATTN, l, t // partitions, partitions, t % partitions,
+                     bar(l, OP_QKV), len(qkv), bar(l, OP_ATTN))
         rr = (rr + KV_HEADS * partitions) % num_sms
-        for kvh in range(KV_HEADS):
-            emit((rr + kvh) % num_sms, OP_REDUCE, l, kvh * 4, 4, partitions, bar(l, OP_ATTN),
-                 KV_HEADS * partitions, bar(l, OP_REDUCE))
-        rr = (rr + KV_HEADS) % num_sms
+        if not fuse_reduce:
+            for kvh in range(KV_HEADS):
+                emit((rr + kvh) % num_sms, OP_REDUCE, l, kvh * 4, 4, partitions, bar(l, OP_ATTN),
+                     KV_HEADS * partitions, bar(l, OP_REDUCE))
+            rr = (rr + KV_HEADS) % num_sms
         oproj = split_even(HIDDEN // 2, num_sms)
         for sm, (s, n) in enumerate(oproj):
             emit(sm, OP_OPROJ, l, 2 * s, 2 * n, 0, bar(l, OP_REDUCE), KV_HEADS, bar(l, OP_OPROJ))
@@ -91,7 +102,7 @@ def build_schedule(num_sms: int, layers: int, vocab: int, partitions: int):
     for sm, rows in enumerate(per_sm):
         if rows:
             inst[sm, : len(rows)] = torch.tensor(rows, dtype=torch.int32)
-    return inst, (layers + 1) * 8
+    return inst, (layers + 1) * 8 + layers * KV_HEADS
 
 
 def rope_tables(rows: int, theta=500000.0, factor=32.0, low=1.0, high=4.0, original=8192):
@@ -110,7 +121,7 @@ class DecodeSession:
     """Weights, caches, activations and the instruction stream for one model on one GPU."""
 
     def __init__(self, weights: dict, *, max_seq_len: int, device="cuda", partitions: int | None = None,
-                 num_sms: int | None = None):
+                 num_sms: int | None = None, fuse_reduce: bool = True):
         _lib.load()
         self.device = torch.device(device)
         dev = self.device
@@ -134,7 +145,7 @@ class DecodeSession:
         self.attn_lse_partial = torch.zeros((Q_HEADS, self.partitions), dtype=torch.float32, device=dev)
         self.argmax_val = torch.zeros(self.num_sms, dtype=torch.float32, device=dev)
         self.argmax_idx = torch.zeros(self.num_sms, dtype=torch.int32, device=dev)
-        inst, nbars = build_schedule(self.num_sms, self.layers, self.vocab, self.partitions)
+        inst, nbars = build_schedule(self.num_sms, self.layers, self.vocab, self.partitions, fuse_reduce)
         self.instructions = inst.to(dev).contiguous()
         self.bars = torch.zeros(nbars, dtype=torch.int32, device=dev)
         self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -150,7 +161,7 @@ class DecodeSession:
         a.pos_dev, a.status = self.pos.data_ptr(), self.status.buf.data_ptr()
         a.num_instructions, a.max_seq_len = self.instructions.shape[1], max_seq_len
         a.max_parts, a.vocab = self.partitions, self.vocab
-        a.attn_scale, a.eps, a.num_bars, a.reserved = 1.0 / math.sqrt(HEAD_DIM), 1e-5, nbars, 0
+        a.attn_scale, a.eps, a.num_bars, a.layers = 1.0 / math.sqrt(HEAD_DIM), 1e-5, nbars, self.layers
         self.args = a
 
     def start(self, token_id: int, pos: int):

@@ -48,17 +48,27 @@ def test_attention_oracle_partitions_merge_to_full():
     assert np.isinf(lse.reshape(8, 24, 4)[:, 2:]).all() and (out.reshape(8, 24, 4, 64)[:, 2:] == 0).all()
 
 
+@pytest.mark.parametrize("fuse", [True, False])
 @pytest.mark.parametrize("num_sms,layers,vocab,parts", [(148, 16, 128256, 18), (148, 2, 1024, 3), (8, 1, 64, 1)])
-def test_schedule_covers_every_row_once_and_counts_match(num_sms, layers, vocab, parts):
+def test_schedule_covers_every_row_once_and_counts_match(num_sms, layers, vocab, parts, fuse):
     from pipelink_b200 import decode as hd
-    inst, nbars = hd.build_schedule(num_sms, layers, vocab, parts)
-    assert inst.shape[0] == num_sms and inst.shape[2] == 32 and nbars == (layers + 1) * 8
+    inst, nbars = hd.build_schedule(num_sms, layers, vocab, parts, fuse_reduce=fuse)
+    assert inst.shape[0] == num_sms and inst.shape[2] == 32 and nbars == (layers + 1) * 8 + layers * 8
     rows = inst.reshape(-1, 32).numpy()
     rows = rows[rows[:, 0] != 0]
     signals = {}
+    arrivals = {}
     for r in rows:
-        if r[8] >= 0:
+        if r[0] == 2 and r[5] > 0:
+            # partitions count themselves in; only the last one bumps the counter of word 8
+            assert (layers + 1) * 8 <= r[5] - 1 < nbars
+            if r[5] not in arrivals:
+                signals[r[8]] = signals.get(r[8], 0) + 1
+            arrivals[r[5]] = arrivals.get(r[5], 0) + 1
+            assert r[3] == parts
+        elif r[8] >= 0:
             signals[r[8]] = signals.get(r[8], 0) + 1
+    assert all(n == parts for n in arrivals.values()) and len(arrivals) == (layers * 8 if fuse else 0)
     for r in rows:
         if r[6] >= 0:
             assert signals[r[6]] == r[7], "a wait target must equal the number of producers"
@@ -73,7 +83,7 @@ def test_schedule_covers_every_row_once_and_counts_match(num_sms, layers, vocab,
         att = rows[(rows[:, 0] == 2) & (rows[:, 1] == l)]
         assert sorted((r[2], r[4]) for r in att) == [(h, p) for h in range(8) for p in range(parts)]
         red = rows[(rows[:, 0] == 3) & (rows[:, 1] == l)]
-        assert sorted(r[2] for r in red) == list(range(0, 32, 4))
+        assert sorted(r[2] for r in red) == ([] if fuse else list(range(0, 32, 4)))
     lm = rows[rows[:, 0] == 7]
     cover = np.zeros(vocab, int)
     for r in lm:

@@ -43,7 +43,7 @@ def test_attention_partial_reference_grid(native_lib):
     assert cases == 70 and failures == 0
 
 
-def _make_session(layers, vocab, max_seq, seed=0, partitions=None):
+def _make_session(layers, vocab, max_seq, seed=0, partitions=None, fuse_reduce=True):
     from pipelink_b200 import decode as hd
     torch.manual_seed(seed)
     mk = lambda *s: (torch.randn(*s, device="cuda") * 0.02).to(torch.bfloat16)
@@ -53,7 +53,7 @@ def _make_session(layers, vocab, max_seq, seed=0, partitions=None):
              attn_norm=(1 + 0.1 * torch.randn(layers, hd.HIDDEN, device="cuda")).to(torch.bfloat16),
              mlp_norm=(1 + 0.1 * torch.randn(layers, hd.HIDDEN, device="cuda")).to(torch.bfloat16),
              lm_norm=torch.ones(hd.HIDDEN, device="cuda", dtype=torch.bfloat16), lm_head=mk(vocab, hd.HIDDEN))
-    s = hd.DecodeSession(w, max_seq_len=max_seq, partitions=partitions)
+    s = hd.DecodeSession(w, max_seq_len=max_seq, partitions=partitions, fuse_reduce=fuse_reduce)
     model = {k: _f(v) for k, v in w.items()}
     return s, model
 
@@ -97,10 +97,14 @@ def _check_step(s, model, kc, vc, hidden_in, pos, cos, sin, reported_fraction=2e
     return ref, token
 
 
-@pytest.mark.parametrize("layers,vocab,prefill,partitions", [(2, 1024, 0, 1), (2, 2048, 37, 3), (3, 4096, 300, None)])
-def test_decode_steps_vs_oracle(native_lib, layers, vocab, prefill, partitions):
+@pytest.mark.parametrize("layers,vocab,prefill,partitions,fuse", [
+    (2, 1024, 0, 1, True), (2, 2048, 37, 3, True), (3, 4096, 300, None, True), (2, 2048, 1100, 4, True),
+    (2, 2048, 37, 3, False), (2, 2048, 700, 2, False)])
+def test_decode_steps_vs_oracle(native_lib, layers, vocab, prefill, partitions, fuse):
+    """`fuse` False keeps the separate merge instruction (opcode 3). Prefills of 700 and 1100 with
+    few partitions make a partition span several 128-token ring stages."""
     max_seq = prefill + 8
-    s, model = _make_session(layers, vocab, max_seq, seed=layers, partitions=partitions)
+    s, model = _make_session(layers, vocab, max_seq, seed=layers, partitions=partitions, fuse_reduce=fuse)
     g = torch.Generator(device="cuda").manual_seed(7)
     if prefill:
         s.k_cache[:, :prefill] = torch.randn(layers, prefill, 8, 64, generator=g, device="cuda").to(torch.bfloat16)
