@@ -41,6 +41,21 @@ constexpr int kStageBytes = 32768;
 constexpr int kStages = 6;
 constexpr int kTaskBytes = 2048;              // one warp task: 1024 bf16 of one weight row
 constexpr int kPartialFloats = 2048;          // per-row partial sums of one block of rows
+constexpr int kAttnSmemFloats = 256 + kDecWarps * 8 + kDecWarps * 256 + 256 + 8;  // attention workspace
+constexpr int kInstWords = 12;                // words 0-8 of an instruction are used; kept 16-byte aligned
+constexpr int kInstSmemBytes = 6144;          // streams of up to 128 instructions are copied to shared memory
+#ifndef PLB_DEC_INFLIGHT
+#define PLB_DEC_INFLIGHT kStages
+#endif
+#ifndef PLB_DEC_L2_AHEAD
+#define PLB_DEC_L2_AHEAD 0
+#endif
+#ifndef PLB_DEC_EVICT_FIRST
+#define PLB_DEC_EVICT_FIRST 1
+#endif
+constexpr int kMaxInflight = PLB_DEC_INFLIGHT;   // ring copies issued but not yet landed
+constexpr int kL2Ahead = PLB_DEC_L2_AHEAD;       // stages beyond the ring that are prefetched into L2
+constexpr bool kEvictFirst = PLB_DEC_EVICT_FIRST != 0;  // ring copies mark their lines evict-first in L2
 constexpr int kHidden = 2048;
 constexpr int kHeadDim = 64;
 constexpr int kQHeads = 32;
@@ -120,33 +135,55 @@ __device__ __forceinline__ float dot8r(uint4 w, const float* x) {
 // (1024 elements), chunks lane, lane + 32, lane + 64, lane + 96 of it. With `norm_w` the vector
 // (2048 long) is RMS-normalised first: every warp reads all of it once, computes the sum of
 // squares itself and keeps its own section.
-__device__ __forceinline__ void load_x(const __nv_bfloat16* __restrict__ src,
-                                       const __nv_bfloat16* __restrict__ norm_w, int sec, int lane,
-                                       float eps, float (&xr)[32]) {
-  if (norm_w != nullptr) {
-    uint4 raw[8], wn[4];
+__device__ __forceinline__ void load_norm_w(const __nv_bfloat16* __restrict__ norm_w, int sec, int lane,
+                                            uint4 (&wn)[4]) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) raw[j] = ld_coherent_v4(src + (lane + 32 * j) * 8);
+  for (int i = 0; i < 4; ++i) wn[i] = *reinterpret_cast<const uint4*>(norm_w + sec * 1024 + (lane + 32 * i) * 8);
+}
+// `wn`: this lane's norm weights (load_norm_w; constants, so they are fetched before the
+// instruction's dependency wait), ignored when `normed` is false. A 2048-long input is read from
+// global memory once per CTA (256 threads, one 16-byte chunk each) and shared through `xs`
+// (4 KB + 8 floats): 16 warps each reading all of it from the same few L2 lines on every SM
+// made those lines a hot spot. An 8192-long input is read directly, every warp its own 2 KB.
+__device__ __forceinline__ void load_x(const __nv_bfloat16* __restrict__ src, int K, bool normed,
+                                       const uint4 (&wn)[4], int sec, int lane, float eps,
+                                       float* xs, float (&xr)[32]) {
+  if (K == kHidden) {
+    uint4* xs4 = reinterpret_cast<uint4*>(xs);
+    float* red = xs + 1024;
+    if (threadIdx.x < 256) {
+      const uint4 raw = ld_coherent_v4(src + threadIdx.x * 8);
+      xs4[threadIdx.x] = raw;
+      if (normed) {
+        float f[8], ss = 0.0f;
+        unpack8(raw, f);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) wn[i] = *reinterpret_cast<const uint4*>(norm_w + sec * 1024 + (lane + 32 * i) * 8);
-    float ss = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float f[8];
-      unpack8(raw[j], f);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+        for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) red[threadIdx.x >> 5] = ss;
+      }
     }
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / static_cast<float>(kHidden) + eps);
+    consumer_sync();
+    float inv = 1.0f;
+    if (normed) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) ss += red[w];
+      inv = rsqrtf(ss / static_cast<float>(kHidden) + eps);
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 mine = sec == 0 ? raw[i] : raw[4 + i];
-      float f[8], w[8];
-      unpack8(mine, f);
-      unpack8(wn[i], w);
+      float f[8];
+      unpack8(xs4[sec * 128 + lane + 32 * i], f);
+      if (normed) {
+        float w[8];
+        unpack8(wn[i], w);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) xr[i * 8 + e] = f[e] * inv * w[e];
+        for (int e = 0; e < 8; ++e) xr[i * 8 + e] = f[e] * inv * w[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xr[i * 8 + e] = f[e];
+      }
     }
   } else {
     uint4 raw[4];
@@ -196,6 +233,7 @@ __device__ bool wait_counter(const unsigned* counter, unsigned target, Status* s
     const long long t0 = clock64();
     for (unsigned it = 0;; ++it) {
       if (ld_acquire_gpu(counter) >= target) break;
+      __nanosleep(40);   // 148 CTAs poll one line: back off so the bumps get through
       if ((it & 63u) == 63u) {
         if (ld_volatile_i32(&st->code) != 0) { ok = 0; break; }
         if (clock64() - t0 > kWaitBudgetCycles) {
@@ -367,14 +405,16 @@ __device__ __forceinline__ void partition_range(int length, int partitions, int 
 
 #ifdef PLB_DECODE_PROFILE
 // Profiling builds: per CTA and opcode, cycles spent waiting for the dependency, working, and
-// signalling, accumulated by thread 0 into [grid][9][4] i64 (last slot: instruction count).
+// signalling, accumulated by thread 0 into [grid][9][8] i64 (slot 7: instruction count).
 __device__ long long* g_decode_profile = nullptr;
 #define DEC_PROF_T(var) const long long var = clock64()
+#define DEC_PROF_MARK(var) var = clock64()
 #define DEC_PROF_ADD(op, slot, cycles)                                                        \
   if (threadIdx.x == 0 && g_decode_profile != nullptr)                                        \
-  g_decode_profile[(static_cast<size_t>(blockIdx.x) * 9 + (op)) * 4 + (slot)] += (cycles)
+  g_decode_profile[(static_cast<size_t>(blockIdx.x) * 9 + (op)) * 8 + (slot)] += (cycles)
 #else
 #define DEC_PROF_T(var)
+#define DEC_PROF_MARK(var)
 #define DEC_PROF_ADD(op, slot, cycles)
 #endif
 
@@ -439,6 +479,56 @@ __device__ __forceinline__ AttnPlan attn_plan_of(const int* in, int pos) {
   return a;
 }
 
+// One ring stage as the producer sees it.
+struct StageDesc {
+  const char* src;   // weights: first byte
+  uint32_t bytes;    // bytes the stage's barrier expects
+  int attn;          // 1: K and V boxes of 128 tokens through the tensor maps
+  int head, token, layer;
+  int op;
+};
+
+// Enumerates the stages of a CTA's instruction stream in the order the consumers take them.
+struct StageCursor {
+  int ip, sub, b0, m, r0;
+  __device__ void reset() { ip = 0; sub = 0; b0 = 0; m = 0; r0 = 0; }
+  __device__ bool next(const DecodeGlobals& g, const int* my, int stride, int pos, StageDesc& d) {
+    for (; ip < g.num_instructions; ++ip, sub = 0, b0 = 0, m = 0, r0 = 0) {
+      const int* in = my + ip * stride;
+      d.op = in[0];
+      if (in[0] == 2) {
+        const AttnPlan ap = attn_plan_of(in, pos);
+        if (sub >= ap.stages) continue;
+        d.attn = 1;
+        d.bytes = kStageBytes;
+        d.head = in[2];
+        d.token = ap.begin + sub * 128;
+        d.layer = in[1];
+        d.src = nullptr;
+        ++sub;
+        return true;
+      }
+      const Plan pl = plan_of(g, in);
+      if (pl.nmat == 0 || b0 >= pl.rows) continue;
+      const int row_bytes = pl.K * 2, rps = kStageBytes / row_bytes, brows = block_rows_of(pl);
+      const int nb = min(brows, pl.rows - b0);
+      d.attn = 0;
+      d.bytes = static_cast<uint32_t>(min(rps, nb - r0)) * row_bytes;
+      d.src = pl.base[m] + static_cast<size_t>(b0 + r0) * row_bytes;
+      r0 += rps;
+      if (r0 >= nb) {
+        r0 = 0;
+        if (++m >= pl.nmat) {
+          m = 0;
+          b0 += brows;   // past the last block the next call moves on to the next instruction
+        }
+      }
+      return true;
+    }
+    return false;
+  }
+};
+
 struct DecBars {
   uint64_t full[kStages];
   uint64_t empty[kStages];
@@ -454,7 +544,18 @@ decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, 
   float* scratch = partial + kPartialFloats;                                 // attention workspace / argmax
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = *g.pos_dev;
+  // This CTA's instruction stream: a miss on an instruction word would cost the producer (and the
+  // consumers) a full memory latency per instruction, so the used words are copied to shared
+  // memory once; longer streams are read in place.
   const int* my = g.instructions + static_cast<size_t>(blockIdx.x) * g.num_instructions * 32;
+  int istride = 32;
+  if (g.num_instructions * kInstWords * 4 <= kInstSmemBytes) {
+    int* local = reinterpret_cast<int*>(scratch + kAttnSmemFloats);
+    for (int i = threadIdx.x; i < g.num_instructions * kInstWords; i += kDecThreads)
+      local[i] = my[(i / kInstWords) * 32 + i % kInstWords];
+    my = local;
+    istride = kInstWords;
+  }
 
   __shared__ int stage_failed;  // a consumer warp gave up on a stage: all leave together at the next barrier
   if (threadIdx.x == 0) {
@@ -468,41 +569,52 @@ decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, 
   __syncthreads();
 
   if (warp == kDecWarps) {
-    // ---------------------------------------------------------------- weight producer
+    // ---------------------------------------------------------------- producer
+    // Walks the stage sequence of this CTA's instructions with two cursors: one issues the copies
+    // into the ring, the other runs kL2Ahead stages further and only asks L2 to fetch, so that
+    // HBM keeps streaming while the ring is full and the consumers sit at a dependency.
     if (lane != 0) return;
-    uint32_t it = 0;
-    bool ok = true;
-    for (int ip = 0; ip < g.num_instructions && ok; ++ip) {
-      const int* in = my + ip * 32;
-      if (in[0] == 2) {
-        const AttnPlan ap = attn_plan_of(in, pos);
-        for (int st = 0; st < ap.stages; ++st, ++it) {
-          const int slot = it % kStages;
-          if (!mbar_wait(smem_u32(&bars->empty[slot]), ((it / kStages) & 1u) ^ 1u, g.status, ST_TIMEOUT_EMPTY, 902)) { ok = false; break; }
-          const uint32_t full = smem_u32(&bars->full[slot]);
-          const uint32_t dst = smem_u32(ring + slot * kStageBytes);
-          mbar_arrive_expect_tx(full, kStageBytes);
-          tma_load_4d(dst, &map_k, full, 0, in[2], ap.begin + st * 128, in[1]);
-          tma_load_4d(dst + kStageBytes / 2, &map_v, full, 0, in[2], ap.begin + st * 128, in[1]);
-        }
-        continue;
-      }
-      const Plan pl = plan_of(g, in);
-      if (pl.nmat == 0) continue;
-      const int row_bytes = pl.K * 2, rps = kStageBytes / row_bytes, brows = block_rows_of(pl);
-      for (int b0 = 0; b0 < pl.rows && ok; b0 += brows) {
-        const int nb = min(brows, pl.rows - b0);
-        for (int m = 0; m < pl.nmat && ok; ++m) {
-          for (int r0 = 0; r0 < nb; r0 += rps, ++it) {
-            const int slot = it % kStages;
-            if (!mbar_wait(smem_u32(&bars->empty[slot]), ((it / kStages) & 1u) ^ 1u, g.status, ST_TIMEOUT_EMPTY, 900 + in[0])) { ok = false; break; }
-            const uint32_t bytes = static_cast<uint32_t>(min(rps, nb - r0)) * row_bytes;
-            const uint32_t full = smem_u32(&bars->full[slot]);
-            mbar_arrive_expect_tx(full, bytes);
-            bulk_load(smem_u32(ring + slot * kStageBytes), pl.base[m] + static_cast<size_t>(b0 + r0) * row_bytes, bytes, full);
+    StageCursor load_c, ahead_c;
+    load_c.reset();
+    ahead_c.reset();
+    uint64_t policy = 0;
+    if (kEvictFirst) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    uint32_t it = 0, ahead = 0;
+    bool ok = true, more_ahead = true;
+    StageDesc d, pd;
+    while (ok && load_c.next(g, my, istride, pos, d)) {
+      while (kL2Ahead > 0 && more_ahead && ahead < it + kStages + kL2Ahead) {
+        more_ahead = ahead_c.next(g, my, istride, pos, pd);
+        if (!more_ahead) break;
+        if (ahead >= it + kStages) {
+          if (pd.attn) {
+            tma_prefetch_4d(&map_k, 0, pd.head, pd.token, pd.layer);
+            tma_prefetch_4d(&map_v, 0, pd.head, pd.token, pd.layer);
+          } else {
+            bulk_prefetch_l2(pd.src, pd.bytes);
           }
         }
+        ++ahead;
       }
+      const int slot = it % kStages;
+      if (!mbar_wait(smem_u32(&bars->empty[slot]), ((it / kStages) & 1u) ^ 1u, g.status, ST_TIMEOUT_EMPTY, 900 + d.op)) { ok = false; break; }
+      if (kMaxInflight < kStages && it >= static_cast<uint32_t>(kMaxInflight)) {
+        // bound the copies in flight: stage it - kMaxInflight must have landed
+        const uint32_t prev = it - kMaxInflight;
+        if (!mbar_wait(smem_u32(&bars->full[prev % kStages]), (prev / kStages) & 1u, g.status, ST_TIMEOUT_FULL, 950)) { ok = false; break; }
+      }
+      const uint32_t full = smem_u32(&bars->full[slot]);
+      const uint32_t dst = smem_u32(ring + slot * kStageBytes);
+      mbar_arrive_expect_tx(full, d.bytes);
+      if (d.attn) {
+        tma_load_4d(dst, &map_k, full, 0, d.head, d.token, d.layer);
+        tma_load_4d(dst + kStageBytes / 2, &map_v, full, 0, d.head, d.token, d.layer);
+      } else if (kEvictFirst) {
+        bulk_load_hint(dst, d.src, d.bytes, full, policy);
+      } else {
+        bulk_load(dst, d.src, d.bytes, full);
+      }
+      ++it;
     }
     if (!ok) {  // let copies in flight land before the CTA's shared memory is released
       const long long t0 = clock64();
@@ -515,30 +627,45 @@ decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, 
   // ------------------------------------------------------------------ consumers
   uint32_t it = 0;
   for (int ip = 0; ip < g.num_instructions; ++ip) {
-    const int* in = my + ip * 32;
+    const int* in = my + ip * istride;
     const int op = in[0];
     if (op == 0) continue;
     const int layer = in[1], a0 = in[2], a1 = in[3], a2 = in[4];
     const int dep = in[6], sig = in[8];
     const unsigned dep_target = static_cast<unsigned>(in[7]);
     DEC_PROF_T(t_start);
+    // constants of this instruction are fetched before the dependency wait
+    const Plan pl = plan_of(g, in);
+    const int wpr = pl.K / 1024;          // warps per row: 2 or 8
+    const int sec = warp % wpr, row_in_stage = warp / wpr;
+    uint4 wn[4] = {};
+    float rope_c = 0.0f, rope_s = 0.0f;
+    if (op == 1) {
+      load_norm_w(g.attn_norm + static_cast<size_t>(layer) * kHidden, sec, lane, wn);
+      const int r = a0 + 2 * static_cast<int>(threadIdx.x);   // the pair this thread finishes in block 0
+      if (2 * static_cast<int>(threadIdx.x) < a1 && r < (kQHeads + kKvHeads) * kHeadDim) {
+        rope_c = g.rope_cos[static_cast<size_t>(pos) * 32 + ((r & (kHeadDim - 1)) >> 1)];
+        rope_s = g.rope_sin[static_cast<size_t>(pos) * 32 + ((r & (kHeadDim - 1)) >> 1)];
+      }
+    } else if (op == 5) {
+      load_norm_w(g.mlp_norm + static_cast<size_t>(layer) * kHidden, sec, lane, wn);
+    } else if (op == 7) {
+      load_norm_w(g.lm_norm, sec, lane, wn);
+    }
     if (dep >= 0) {
       if (!wait_counter(g.bars + dep, dep_target, g.status, op * 100 + layer)) return;
     }
     DEC_PROF_T(t_dep);
+#ifdef PLB_DECODE_PROFILE
+    long long t_x = t_dep, t_st = t_dep, t_sy = t_dep;
+#endif
 
-    const Plan pl = plan_of(g, in);
     if (pl.nmat != 0) {
       // ---- matvec ops: partial sums of every row of the block, then the op's epilogue
-      const int wpr = pl.K / 1024;          // warps per row: 2 or 8
-      const int sec = warp % wpr, row_in_stage = warp / wpr;
       const int rps = kStageBytes / (pl.K * 2), brows = block_rows_of(pl);
       float xr[32];
-      if (op == 1) load_x(g.hidden, g.attn_norm + static_cast<size_t>(layer) * kHidden, sec, lane, g.eps, xr);
-      else if (op == 4) load_x(g.attn_out, nullptr, sec, lane, g.eps, xr);
-      else if (op == 5) load_x(g.hidden, g.mlp_norm + static_cast<size_t>(layer) * kHidden, sec, lane, g.eps, xr);
-      else if (op == 6) load_x(g.silu_out, nullptr, sec, lane, g.eps, xr);
-      else load_x(g.hidden, g.lm_norm, sec, lane, g.eps, xr);
+      load_x(op == 4 ? g.attn_out : op == 6 ? g.silu_out : g.hidden, pl.K, op != 4 && op != 6, wn, sec, lane, g.eps, scratch, xr);
+      DEC_PROF_MARK(t_x);
       float best = -INFINITY;
       int best_idx = 0x7FFFFFFF;
       for (int b0 = 0; b0 < pl.rows; b0 += brows) {
@@ -566,7 +693,9 @@ decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, 
         // a failed wait has set the status word, so every other warp's wait gives up too and all
         // 16 warps still meet at this barrier before leaving
         if (!ok) *reinterpret_cast<volatile int*>(&stage_failed) = 1;
+        DEC_PROF_MARK(t_st);
         consumer_sync();
+        DEC_PROF_MARK(t_sy);
         if (*reinterpret_cast<volatile int*>(&stage_failed) != 0) return;
         // ---- epilogue of rows [b0, b0 + nb) of this instruction's slice
         auto row_sum = [&](int idx) {
@@ -581,8 +710,9 @@ decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, 
             const size_t cache_row = (static_cast<size_t>(layer) * g.max_seq_len + pos) * (kKvHeads * kHeadDim);
             if (r < (kQHeads + kKvHeads) * kHeadDim) {
               const int pair = (r & (kHeadDim - 1)) >> 1;
-              const float c = g.rope_cos[static_cast<size_t>(pos) * 32 + pair];
-              const float sn = g.rope_sin[static_cast<size_t>(pos) * 32 + pair];
+              const bool early = b0 == 0 && pr == static_cast<int>(threadIdx.x);
+              const float c = early ? rope_c : g.rope_cos[static_cast<size_t>(pos) * 32 + pair];
+              const float sn = early ? rope_s : g.rope_sin[static_cast<size_t>(pos) * 32 + pair];
               const float o0 = s0 * c - s1 * sn, o1 = s1 * c + s0 * sn;
               if (r < kQHeads * kHeadDim) {
                 g.q_post_rope[r] = __float2bfloat16_rn(o0);
@@ -645,9 +775,23 @@ decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, 
       const size_t kv_base = static_cast<size_t>(layer) * g.max_seq_len * (kKvHeads * kHeadDim) + a0 * kHeadDim;
       float* tmp_out = scratch + 256 + kDecWarps * 8 + kDecWarps * 256;
       float* tmp_lse = tmp_out + 256;
+      // the token being decoded: its K/V row was written by the QKV op of this launch, so it is
+      // read directly (coherent loads, issued together with the query loads) by the last warp
+      const bool has_tail = pos >= ap.begin && pos < ap.end;
+      uint4 tail_k[8] = {};
+      uint32_t tail_v = 0;
+      if (has_tail && warp == kDecWarps - 1) {
+        const size_t at = kv_base + static_cast<size_t>(pos) * (kKvHeads * kHeadDim);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tail_k[c] = ld_coherent_v4(g.k_cache + at + c * 8);
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(tail_v) : "l"(g.v_cache + at + 2 * lane) : "memory");
+      }
       attn_stage_q(g.q_post_rope + a0 * 4 * kHeadDim, g.attn_scale * 1.4426950408889634f, scratch);
+      DEC_PROF_MARK(t_x);
       AttnAcc acc;
       attn_init(acc);
+      if (has_tail && warp == kDecWarps - 1)
+        attn_tile(acc, scratch, 1, lane, [&](int c) { return tail_k[c]; }, [&](int) { return tail_v; });
       bool ok = true;
       for (int st = 0; st < ap.stages; ++st, ++it) {
         const int slot = it % kStages;
@@ -670,12 +814,10 @@ decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, 
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars->empty[slot]));
       }
-      // the token being decoded: its K/V row was written by the QKV op of this launch
-      if (pos >= ap.begin && pos < ap.end)
-        attn_tiles_global(acc, scratch, g.k_cache + kv_base, g.v_cache + kv_base, kKvHeads * kHeadDim, pos, pos + 1,
-                          kDecWarps - 1, 1);
       if (!ok) *reinterpret_cast<volatile int*>(&stage_failed) = 1;
+      DEC_PROF_MARK(t_st);
       attn_merge(acc, scratch, tmp_out, tmp_lse);
+      DEC_PROF_MARK(t_sy);
       if (*reinterpret_cast<volatile int*>(&stage_failed) != 0) return;
       // partial layout: [head][part][64]; heads of this KV head are a0*4 .. a0*4+3
       if (threadIdx.x < 256) {
@@ -695,10 +837,21 @@ decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, 
           is_last = before + 1u == static_cast<unsigned>(a1);
         }
         consumer_sync();
+        DEC_PROF_T(t_arr);
         const bool last = is_last != 0;
         if (last) merge_heads(g, a0 * 4, 4, a1);
+        DEC_PROF_T(t_mrg);
         if (sig >= 0 && last) signal_counter(g.bars + sig);
         consumer_sync();
+        DEC_PROF_T(t_fin);
+        DEC_PROF_ADD(op, 0, t_dep - t_start);   // dependency wait
+        DEC_PROF_ADD(op, 1, t_x - t_dep);       // queries (and the current token's K/V) loaded
+        DEC_PROF_ADD(op, 2, t_st - t_x);        // ring stages
+        DEC_PROF_ADD(op, 3, t_sy - t_st);       // merge of the warps
+        DEC_PROF_ADD(op, 4, t_arr - t_sy);      // partial stored, partition counted in
+        DEC_PROF_ADD(op, 5, t_mrg - t_arr);     // last arriver: merge of the KV head
+        DEC_PROF_ADD(op, 6, t_fin - t_mrg);     // last arriver: signal
+        DEC_PROF_ADD(op, 7, 1);
         continue;
       }
     } else if (op == 3) {
@@ -730,12 +883,17 @@ decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, 
     }
     DEC_PROF_T(t_work);
     if (sig >= 0) signal_counter(g.bars + sig);
+    DEC_PROF_T(t_sig);
     consumer_sync();
     DEC_PROF_T(t_end);
-    DEC_PROF_ADD(op, 0, t_dep - t_start);
-    DEC_PROF_ADD(op, 1, t_work - t_dep);
-    DEC_PROF_ADD(op, 2, t_end - t_work);
-    DEC_PROF_ADD(op, 3, 1);
+    DEC_PROF_ADD(op, 0, t_dep - t_start);   // dependency wait
+    DEC_PROF_ADD(op, 1, t_x - t_dep);       // activations into registers
+    DEC_PROF_ADD(op, 2, t_st - t_x);        // thread 0's warp through its stages (last block)
+    DEC_PROF_ADD(op, 3, t_sy - t_st);       // waiting for the other warps
+    DEC_PROF_ADD(op, 4, t_work - t_sy);     // epilogue
+    DEC_PROF_ADD(op, 5, t_sig - t_work);    // barrier + fence + counter bump
+    DEC_PROF_ADD(op, 6, t_end - t_sig);
+    DEC_PROF_ADD(op, 7, 1);
   }
 }
 
@@ -762,10 +920,9 @@ attention_partial_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k, const _
   }
 }
 
-constexpr int kAttnSmemFloats = 256 + kDecWarps * 8 + kDecWarps * 256 + 256 + 8;
-constexpr int kDecodeSmemBytes = kStages * kStageBytes + 128 + (kPartialFloats + kAttnSmemFloats) * 4;
+constexpr int kDecodeSmemBytes = kStages * kStageBytes + 128 + (kPartialFloats + kAttnSmemFloats) * 4 + kInstSmemBytes;
 static_assert(sizeof(DecBars) <= 128, "barrier block");
-static_assert(kDecodeSmemBytes <= 227 * 1024, "shared memory budget");
+static_assert(kDecodeSmemBytes + 1024 <= 227 * 1024, "shared memory budget (1 KB of static shared memory and alignment)");
 
 }  // namespace
 

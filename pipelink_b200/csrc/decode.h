@@ -47,7 +47,7 @@ struct DecodeGlobals {
 };
 
 #ifdef PLB_DECODE_PROFILE
-cudaError_t set_decode_profile(void* buffer);  // profiling builds only: [grid][9][4] i64 cycle sums
+cudaError_t set_decode_profile(void* buffer);  // profiling builds only: [grid][9][8] i64 cycle sums
 #endif
 cudaError_t launch_decode_step(const DecodeGlobals& g, int num_sms, cudaStream_t stream);
 cudaError_t launch_attention_partial(const void* q, const void* k, const void* v, float* out,
