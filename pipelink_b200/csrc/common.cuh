@@ -146,15 +146,6 @@ __device__ __forceinline__ void bulk_load_hint(uint32_t dst, const void* src, ui
       "l"(src), "r"(bytes), "r"(bar), "l"(policy)
       : "memory");
 }
-// Ask L2 to fetch a byte range / a 4-D box; nothing lands in shared memory.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int x, int y, int z, int w) {
-  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global [%0, {%1, %2, %3, %4}];" ::"l"(map), "r"(x),
-               "r"(y), "r"(z), "r"(w)
-               : "memory");
-}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
