@@ -10,13 +10,16 @@ from __future__ import annotations
 
 from .model import ClauseFailure, PipeLinkError
 
-COMPAT_FIELDS = ("space", "scope", "proxy", "tile", "ring", "binds")
+COMPAT_FIELDS = ("space", "scope", "proxy", "tile", "binds")
 
 
 def canonical_layout(layout: dict | None):
-    """Flatten nested modes, drop unit modes and merge contiguous ones; keep the swizzle."""
+    """Flatten nested modes, drop unit modes and merge contiguous ones; keep the swizzle.
+    Tensor-memory layouts are `lanes` [start, stop) and `cols` (pipec/src/pipec2/layout.py:75-78)."""
     if layout is None:
         return None
+    if "lanes" in layout or "cols" in layout:   # tensor memory: a lane range and a column count
+        return {"elem_bits": layout.get("elem_bits"), "lanes": list(layout.get("lanes", ())), "cols": layout.get("cols")}
     shape = [s for mode in layout["shape"] for s in mode]
     stride = [s for mode in layout["stride"] for s in mode]
     modes = [(sh, st) for sh, st in zip(shape, stride) if sh != 1]
@@ -50,17 +53,35 @@ def pair_channels(manifests: list[dict]):
     return channels
 
 
+def physical_identity(ep: dict):
+    """What both ends of a channel must agree on byte for byte: the canonical layout and how far
+    apart ring stages are (the reference's `endpoint.physical_identity`, clause L8)."""
+    return {"layout": canonical_layout(ep.get("layout")), "stage_stride_bytes": (ep.get("ring") or {}).get("stage_stride_bytes")}
+
+
 def check_compatibility(channels) -> None:
     failures = []
     for name, ((ps, pe), (cs, ce)) in channels.items():
+        for stage, ep in ((ps, pe), (cs, ce)):
+            lay = ep.get("layout") or {}
+            if ep.get("space") == "tmem" and "lanes" in lay:
+                lanes = lay["lanes"][1] - lay["lanes"][0]
+                if [lanes, lay.get("cols")] != list(ep.get("tile", {}).get("shape", [])):
+                    failures.append(ClauseFailure("L8", f"endpoints.{name}.layout",
+                                                  "TMEM lane/column shape is not congruent with tile.shape", {"stage": stage}))
+        if failures:
+            continue
         for f in COMPAT_FIELDS:
             if pe.get(f) != ce.get(f):
                 failures.append(ClauseFailure("L-PAIR", f"channels.{name}.endpoint.{f}",
                                               f"endpoint compatibility field {f} differs",
                                               {"producer": ps, "consumer": cs}))
-        if canonical_layout(pe.get("layout")) != canonical_layout(ce.get("layout")):
+        if (pe.get("ring") or {}).get("depth") != (ce.get("ring") or {}).get("depth"):
+            failures.append(ClauseFailure("L-PAIR", f"channels.{name}.endpoint.ring", "ring depths differ",
+                                          {"producer": ps, "consumer": cs}))
+        if physical_identity(pe) != physical_identity(ce):
             failures.append(ClauseFailure("L8", f"channels.{name}.layout", "paired endpoints describe different physical layouts",
-                                          {"producer": canonical_layout(pe.get("layout")), "consumer": canonical_layout(ce.get("layout"))}))
+                                          {"producer": physical_identity(pe), "consumer": physical_identity(ce)}))
         if pe.get("protocol") != ce.get("protocol"):
             failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol", "endpoint protocols differ"))
     if failures:

@@ -8,6 +8,7 @@ annotations would register) and does the two remaining pack steps: compile the L
 """
 from __future__ import annotations
 
+import hashlib
 import json
 import tempfile
 from pathlib import Path
@@ -27,7 +28,11 @@ def pack_cu(source, manifest_path=None, out=None, profile="sm_100a", includes=()
         obj = Path(tmp) / "stage.o"
         jitlink.compile_lto(str(source), str(obj), PROFILES[profile], includes, defines)
         payload = obj.read_bytes()
-    manifest.setdefault("provenance", {})["source"] = source.name
+    # provenance as the reference records it (pipec/src/pipec2/schema.py:1015-1030): how the
+    # manifest came to be and the digests of what it was made from
+    manifest["provenance"] = {"mechanism": "declared-json",
+                              "inputs": {"tu": hashlib.sha256(source.read_bytes()).hexdigest(),
+                                         "manifest": hashlib.sha256(manifest_path.read_bytes()).hexdigest()}}
     data = container.pack(manifest, payload)
     out = Path(out) if out else source.with_suffix(".plink")
     out.write_bytes(data)

@@ -57,8 +57,9 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         base_vars[name] = b
         ext = _extent_expr(cl["extent"], depth_vars)
         gran = max(dom.granularity, 1)
-        # extents are rounded up to the domain granularity (TMEM columns come in 32s)
-        ext_g = ext if gran == 1 else (((ext + gran - 1) // gran) * gran if isinstance(ext, int) else ((ext + gran - 1) / gran) * gran)
+        # the domain granularity constrains where a claim may start, not how long it is (the
+        # reference places 24 scale columns at [128, 152), pipec/src/pipec2/solve.py)
+        ext_g = ext
         ext_exprs[name] = ext_g
         add(b >= dom.lowest, "L-BUDGET", f"claims.{name}.base")
         add(b + ext_g <= dom.capacity + dom.lowest, "L-BUDGET", f"claims.{name}.extent")

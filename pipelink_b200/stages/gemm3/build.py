@@ -39,12 +39,13 @@ def _operands(direction, role):
 def _accumulator(direction, role):
     return {"name": "accumulator", "direction": direction, "owner_role": role, "space": "tmem", "scope": "cta", "proxy": "async",
             "tile": {"dtype": "f32", "shape": [128, 128]},
-            "layout": {"encoding": "pl-layout-v2", "elem_bits": 32, "shape": [[128], [128]], "stride": [[65536], [1]], "swizzle": None},
-            "ring": {"depth": {"fixed": 1}, "stage_stride_bytes": 0},
+            "layout": {"encoding": "pl-layout-v2", "elem_bits": 32, "lanes": [0, 128], "cols": 128},
+            "ring": {"depth": {"fixed": 1}, "stage_stride_bytes": 65536},
             "protocol": {"kind": "mbarrier",
                          "full": {"slots": "pipelink_gemm_acc_ready", "arrive": {"count": 1, "by": "mma"}, "tx_bytes": 0},
-                         "empty": None, "init": {"owner": "mma", "phase": 0, "materializer": "dispatch"}, "release": "once"},
-            "binds": {"base": "pipelink_gemm_acc", "full": "pipelink_gemm_acc_ready"}}
+                         "empty": {"slots": "pipelink_gemm_acc_empty", "arrive": {"count": 4, "by": "epilogue"}, "tx_bytes": 0},
+                         "init": {"owner": "mma", "phase": 0, "materializer": "dispatch"}, "release": "once-per-acquire"},
+            "binds": {"base": "pipelink_gemm_acc", "full": "pipelink_gemm_acc_ready", "empty": "pipelink_gemm_acc_empty"}}
 
 
 OPERAND_CLAIMS = [
@@ -55,6 +56,7 @@ OPERAND_CLAIMS = [
 ACC_CLAIMS = [
     {"domain": "tmem", "handle": "pipelink_gemm_acc", "extent": {"const": 128, "per": {}}, "align": 32, "lifetime": "kernel"},
     {"domain": "mbarrier", "handle": "pipelink_gemm_acc_ready", "extent": {"const": 1, "per": {}}, "align": 1, "lifetime": "kernel"},
+    {"domain": "mbarrier", "handle": "pipelink_gemm_acc_empty", "extent": {"const": 1, "per": {}}, "align": 1, "lifetime": "kernel"},
 ]
 SF_CLAIM = {"domain": "tmem", "handle": "pipelink_gemm_sf", "extent": {"const": 0, "per": {"pipelink_gemm_depth": 8}}, "align": 32, "lifetime": "kernel"}
 
@@ -63,13 +65,26 @@ def _warp(handle, n, role, align=1):
     return {"domain": "warp", "handle": handle, "extent": {"const": n, "per": {}}, "align": align, "lifetime": "kernel", "roles": [role]}
 
 
+def _layout_probe(type_name: str) -> str:
+    """sha256 over the parameter struct's definition in gemm3.cuh (whitespace-normalised): the
+    manifest's `sha256_of_layout_probe`, which changes whenever a field, its type or order does."""
+    import hashlib
+    import re
+    text = (HERE / "gemm3.cuh").read_text()
+    m = re.search(r"struct\s+(alignas\(\d+\)\s+)?" + type_name + r"\s*\{.*?\};", text, re.S)
+    if m is None:
+        raise ValueError(f"{type_name} is not defined in gemm3.cuh")
+    return hashlib.sha256(" ".join(m.group(0).split()).encode()).hexdigest()
+
+
 def _manifest(stage_id, prefix, role, entry, warps, endpoints, claims, params, undefined):
+    params = dict(params, sha256_of_layout_probe=_layout_probe(params["type"]))
     return {"pipelink_abi": json.loads(json.dumps(ABI)),
             "stage": {"id": stage_id, "version": "1.0.0", "symbol_prefix": prefix, "entry_abi": "v2",
                       "roles": {role: {"entry": entry, "warps": warps}}, "exports": {}, "entry_signature": SIG,
                       "variants": [{"key": {}, "index": 0}]},
             "endpoints": endpoints, "claims": claims,
-            "topology": {"cta_group": {"fixed": 1}, "cluster": {"compiled": [1, 1, 1]}, "multicast": [], "persistent": False, "scheduler": "static"},
+            "topology": {"cta_group": {"fixed": 1}, "cluster": {"compiled": [1, 1, 1], "launch": {"x_multiple_of": 1, "max": [1, 1, 1]}}, "multicast": [], "persistent": False, "scheduler": "static"},
             "params": params, "hints": {},
             "symbols": {"mechanism": "declared", "defined_strong": [entry], "defined_weak": [], "undefined": {u: "function" for u in undefined}},
             "provenance": {}, "payload": {"file": "stage.o"}}
@@ -85,15 +100,15 @@ MANIFESTS = {
                      [_warp("pipelink_gemm_warp_mma", 1, "mma"), *OPERAND_CLAIMS, *ACC_CLAIMS, SF_CLAIM],
                      {"bytes": 16, "align": 16, "type": "Gemm3MmaParams"},
                      ["pipelink_gemm_depth", "pipelink_gemm_operands", "pipelink_gemm_full", "pipelink_gemm_empty",
-                      "pipelink_gemm_acc", "pipelink_gemm_sf", "pipelink_gemm_acc_ready", "pipelink_tmem_slot"]),
+                      "pipelink_gemm_acc", "pipelink_gemm_sf", "pipelink_gemm_acc_ready", "pipelink_gemm_acc_empty", "pipelink_tmem_slot"]),
     "epilogue_bias_silu": _manifest("gemm.epilogue.bias-silu", "gemm_epilogue_bias_silu_", "epilogue",
                                     "gemm_epilogue_bias_silu_role", 4, [_accumulator("consume", "epilogue")],
                                     [_warp("pipelink_gemm_warp_epilogue", 4, "epilogue", align=4), *ACC_CLAIMS],
                                     {"bytes": 32, "align": 16, "type": "Gemm3EpilogueParams"},
-                                    ["pipelink_gemm_acc", "pipelink_gemm_acc_ready", "pipelink_tmem_slot"]),
+                                    ["pipelink_gemm_acc", "pipelink_gemm_acc_ready", "pipelink_gemm_acc_empty", "pipelink_tmem_slot"]),
 }
 BASE_HANDLES = {"pipelink_gemm_operands": "smem", "pipelink_gemm_full": "mbarrier", "pipelink_gemm_empty": "mbarrier",
-                "pipelink_gemm_acc_ready": "mbarrier", "pipelink_gemm_acc": "tmem", "pipelink_gemm_sf": "tmem",
+                "pipelink_gemm_acc_ready": "mbarrier", "pipelink_gemm_acc_empty": "mbarrier", "pipelink_gemm_acc": "tmem", "pipelink_gemm_sf": "tmem",
                 "pipelink_gemm_warp_load": "warp", "pipelink_gemm_warp_mma": "warp", "pipelink_gemm_warp_epilogue": "warp"}
 
 

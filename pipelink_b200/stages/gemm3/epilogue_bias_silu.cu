@@ -41,4 +41,7 @@ extern "C" __device__ void gemm_epilogue_bias_silu_role(const void* raw_params, 
     }
   }
   plb::tc_fence_before();
+  // accumulator released: one arrival per epilogue warp on the channel's empty side
+  __syncwarp();
+  if (lane == 0) plb::mbar_arrive(barrier_addr(smem, pipelink_gemm_acc_empty()));
 }

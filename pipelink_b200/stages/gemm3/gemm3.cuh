@@ -48,6 +48,7 @@ extern "C" __device__ int pipelink_gemm_operands();    // smem byte offset of th
 extern "C" __device__ int pipelink_gemm_full();        // first mbarrier slot (16 bytes each)
 extern "C" __device__ int pipelink_gemm_empty();
 extern "C" __device__ int pipelink_gemm_acc_ready();   // mbarrier slot: accumulator complete
+extern "C" __device__ int pipelink_gemm_acc_empty();   // mbarrier slot: accumulator drained (one arrival per epilogue warp)
 extern "C" __device__ int pipelink_gemm_acc();         // first TMEM column of the accumulator
 extern "C" __device__ int pipelink_gemm_sf();          // first TMEM column of the scale slots
 extern "C" __device__ int pipelink_tmem_slot();        // smem byte offset where dispatch put the TMEM base

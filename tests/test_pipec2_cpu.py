@@ -169,3 +169,47 @@ def test_config0_oracle_is_finite_and_shaped():
     case = gemm3.make_case(256, 256, 256)
     ref = gemm3.expected(case)
     assert ref.shape == (256, 256) and gemm3.compare(ref, ref)["violations"] == 0
+
+
+# ---- held to the reference's own linker front end -------------------------------------------
+# tests/golden/gemm3_reference_linker.json records what pipec2 of the reference tree answers for
+# THIS repo's packages and pipeline variants (tests/golden/make_linker_golden.py made it).
+GOLDEN = json.loads((Path(__file__).parent / "golden" / "gemm3_reference_linker.json").read_text())
+
+
+@pytest.mark.parametrize("case", sorted(GOLDEN["solutions"]))
+def test_solution_tiers_equal_the_reference_linker(linked, tmp_path, case):
+    from tests.golden import linker_cases
+    out, _ = linked
+    stages = json.loads((out / "pipeline.json").read_text())["pipeline"]["stages"]
+    for s in stages:
+        s["artifact_path"] = str(out / s["artifact_path"])
+    spec = tmp_path / "pipeline.json"
+    spec.write_text(json.dumps(g3.pipeline_spec(stages, **linker_cases.SOLVE_CASES[case])))
+    r = linker.link(spec, tmp_path / "link", device_link=False)
+    want = GOLDEN["solutions"][case]
+    assert {h: r.bindings[h][0] for h in want["depths"]} == want["depths"]
+    assert r.threads == want["threads"] and list(r.cluster) == want["cluster"]
+    hw = {d: max(iv["hi"] for iv in ivs) for d, ivs in r.intervals.items()}
+    assert hw["tmem"] == want["high_water"]["tmem"] and hw["warp"] == want["high_water"]["warp"]
+    # this linker adds one 16-byte slot through which dispatch publishes the TMEM base; without it
+    # the shared-memory high-water mark is the reference's
+    slot = r.bindings[linker.TMEM_SLOT_HANDLE][0]
+    others = max(iv["hi"] * (16 if d == "mbarrier" else 1) for d in ("smem", "mbarrier") for iv in r.intervals[d]
+                 if iv["handle"] != linker.TMEM_SLOT_HANDLE)
+    assert others == want["dyn_smem_bytes"] and r.dyn_smem_bytes == max(others, slot + 16) <= want["dyn_smem_bytes"] + 16
+    roles = {x["role"]: [x["warp_lo"], x["warp_hi"]] for x in r.roles}
+    assert roles == want["warp_map"]
+    ext = {iv["handle"]: (iv["hi"] - iv["lo"]) * (16 if d == "mbarrier" else 1) for d, ivs in r.intervals.items() for iv in ivs}
+    for handle, n in want["extents"].items():
+        assert ext[handle] == n, handle
+
+
+@pytest.mark.parametrize("case", sorted(GOLDEN["negative"]))
+def test_negative_clause_ids_equal_the_reference_linker(case):
+    from tests.golden import linker_cases
+    ms = linker_cases.mutated(g3.MANIFESTS, case)
+    with pytest.raises(PipeLinkError) as e:
+        ch = _channels(ms)
+        contracts.expand_protocols(ch, ms)
+    assert sorted({f.clause_id for f in e.value.failures}) == GOLDEN["negative"][case], str(e.value)
