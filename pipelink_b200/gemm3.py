@@ -50,3 +50,38 @@ class Gemm3:
 
     def close(self):
         self.session.close()
+
+
+class Gemm3Hosted:
+    """The same GEMM opened through the host broker: the group's provider
+    (stages/gemm3/host/provider.cu) is asked what it needs and writes the three parameter blocks,
+    tensor maps included; this class only names the tensors. One open per set of tensors, any
+    number of launches (or one captured CUDA graph) after it."""
+
+    GROUP = Path(__file__).resolve().parent / "stages" / "gemm3" / "gemm3.host.json"
+
+    def __init__(self, aq, asc, bq, bsc, bias, out, link_dir=None, backend=None):
+        from .pipec2 import host
+        link_dir = Path(link_dir or ensure_built())
+        provider = link_dir.parent / "libgemm3_provider.so"
+        if not provider.exists():
+            from .stages.gemm3 import build
+            build.build_provider(link_dir.parent)
+        M, K = aq.shape
+        N = bq.shape[0]
+        R = host.Resource.of_tensor
+        self.tensors = (aq, asc, bq, bsc, bias, out)      # keep the allocations alive
+        self.session = host.open_host(
+            link_dir, self.GROUP, provider, struct.pack("<IIII", M, N, K, 0),
+            {"a": R(aq), "a_scales": R(asc), "b": R(bq), "b_scales": R(bsc), "bias": R(bias), "out": R(out, "write")},
+            backend=backend)
+
+    def run(self, stream=None):
+        self.session.launch(stream if stream is not None else torch.cuda.current_stream().cuda_stream)
+
+    def capture(self):
+        from .pipec2 import host
+        return host.CudaBackend.capture(self.session)
+
+    def close(self):
+        self.session.close()

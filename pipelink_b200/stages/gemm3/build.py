@@ -123,6 +123,22 @@ def pipeline_spec(stages, depth=None, values=(6, 5, 4, 3, 2)):
                          "topology": {"persistent": False, "scheduler": "static"}}}
 
 
+def build_provider(out: Path) -> Path:
+    """The group's params provider (host code): out/libgemm3_provider.so."""
+    out.mkdir(parents=True, exist_ok=True)
+    lib = out / "libgemm3_provider.so"
+    src = HERE / "host" / "provider.cu"
+    deps = [src, HERE / "gemm3.cuh", HERE.parents[2] / "include" / "pipelink_host_abi_v2.h"]
+    if lib.exists() and all(d.stat().st_mtime <= lib.stat().st_mtime for d in deps):
+        return lib
+    cmd = [jitlink.nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr",
+           "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(lib), str(src)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("provider build failed:\n" + proc.stderr[-3000:])
+    return lib
+
+
 def write_manifests():
     for name, m in MANIFESTS.items():
         (HERE / f"{name}.manifest.json").write_text(json.dumps(m, indent=1, sort_keys=True) + "\n")
@@ -139,6 +155,7 @@ def build(out: Path, depth=None, one_tu=True):
     spec = out / "pipeline.json"
     spec.write_text(json.dumps(pipeline_spec(stages, depth), indent=1))
     result = linker.link(spec, out / "link")
+    build_provider(out)
     if one_tu:
         # same-source single translation unit: the parity denominator for the linked image
         tu = out / "link" / "generated" / "one_tu.cu"

@@ -57,3 +57,32 @@ def test_linked_vs_one_tu_latency(images):
         times.append(best)
     print(f"linked {times[0] * 1e3:.2f} us, one-TU {times[1] * 1e3:.2f} us, ratio {times[0] / times[1]:.4f}")
     assert times[0] <= times[1] * 1.03 + 0.002
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1024, 1024, 1024)])
+def test_hosted_open_equals_hostless_and_replays_from_a_graph(images, M, N, K):
+    """The broker route: the group's provider is queried, builds the three parameter blocks (tensor
+    maps included) and the launch must be bitwise the host-less one; one captured CUDA graph
+    replays it onto fresh poison."""
+    from pipelink_b200 import gemm3
+    linked, _ = images
+    case = og.make_case(M, N, K, seed=1)
+    dev = {k: _t(case[k]) for k in ("aq", "asc", "bq", "bsc")}
+    bias = torch.from_numpy(case["bias"]).to(torch.bfloat16).cuda()
+    plain = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    linked.run(dev["aq"], dev["asc"], dev["bq"], dev["bsc"], bias, plain)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    hosted = gemm3.Gemm3Hosted(dev["aq"], dev["asc"], dev["bq"], dev["bsc"], bias, out)
+    try:
+        assert hosted.session.geometry[0] == (M // 128, N // 128, 1)
+        assert [t["ring_depth"] for t in hosted.session.transfers] == [hosted.session.link["bindings"]["pipelink_gemm_depth"][0]] * 2
+        hosted.run()
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), plain.view(torch.int16))
+        graph = hosted.capture()
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), plain.view(torch.int16))
+    finally:
+        hosted.close()
