@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-1B decode ms/token leg")
+    ap.add_argument("--no-train", action="store_true", help="skip the expert-parallel forward+backward leg (N > 1)")
     ap.add_argument("--no-attention", action="store_true", help="skip the causal prefill attention leg")
     return ap.parse_args()
 
@@ -243,6 +244,14 @@ def run_native(args):
         else:
             attention = cp_attention_leg(dev, pk, rank, world)
 
+    train = None
+    if world > 1 and not args.no_train and args.tokens is None:
+        session.group.close()
+        del session
+        torch.cuda.empty_cache()
+        session = None
+        train = ep_train_leg(shape, dev, rank, world, pk)
+
     decode = None
     if rank == 0 and world == 1 and not args.no_decode and args.tokens is None:
         del session
@@ -264,11 +273,48 @@ def run_native(args):
                            "l2": "inputs larger than L2 (weights 1.5 GB, activations > 1 GB per step)",
                            "expert_padding": mok.expert_padding(), "gemm_variant": "cta-pair 256x256" if mok.expert_padding() == 256 else "single-cta 128x128"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
-                "roofline": roof, "cpu_baseline": cpu, "decode": decode, "attention": attention,
+                "roofline": roof, "cpu_baseline": cpu, "decode": decode, "attention": attention, "ep_fwd_bwd": train,
                 "frac_of_fp8_peak_whole_step": value / world / fp8_peak}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def ep_train_leg(shape, dev, rank, world, pk, steps=5):
+    """Expert-parallel forward + backward at the same per-rank shape (the fwd+bwd case of the
+    expert-parallel configuration): 18 T k H I FLOP per rank and step (forward 6, both data
+    gradients 6, both weight gradients 6), device time, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from pipelink_b200 import ep
+    session = ep.BenchSession(shape, dev, rank, world, train=True)
+    for _ in range(3):
+        session.step()
+    session.check()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        session.step()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device=dev)
+    dist.barrier()
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    session.check()
+    ms = float(t.item())
+    flop = 18.0 * shape.tokens * shape.topk * shape.hidden * shape.intermediate
+    payload = shape.tokens * shape.topk * shape.hidden * (world - 1) / world
+    out = {"metric": "mxfp8_moe_ffn_fwd_bwd_tflops", "value": flop * world / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms,
+           "steps": steps, "tokens_per_rank": shape.tokens, "world": world, "scaling": "weak",
+           "gpu_launches": session.launches_per_step * steps,
+           "frac_of_fp8_peak": flop / (ms * 1e-3) / 1e12 / (2.0 * pk["bf16_sustained"]),
+           "nvlink_payload_bytes_per_rank": {"dispatch_e4m3": payload * (1 + 1 / 32), "combine_bf16": payload * 2,
+                                             "d_out_bf16": payload * 2, "x_bf16": payload * 2, "d_x_bf16": payload * 2}}
+    session.group.close()
+    return out
 
 
 def attention_leg(dev, pk, seq=32768, steps=3):

@@ -234,6 +234,25 @@ int plb_ep_pull_rows(const void* const* xq_peers, const void* const* xsc_peers,
                      const int32_t* num_tokens, int64_t capacity, int64_t hidden,
                      void* x_routed_fp8, void* x_routed_sc, void* stream);
 
+/* Expert-parallel backward, the mirror of dispatch and combine (mok_comm_bwd,
+ * campaigns/mok/port/comm/comm.cu:226-262): gradients of routed rows are pulled from the token's
+ * home rank and the input gradient rows are pushed back to it.
+ * plb_ep_bwd_dy: d_y[p] = router_w_peers[r][dest_row[p]] * d_out_peers[r][peer_token_idx[p]] with
+ *   r = peer_rank[p]; padding rows and rows past *num_tokens become zeros.
+ * plb_moe_router_grad: at the home rank, d_router_weights[t, j] = <d_out[t], combine[t * topk + j]>
+ *   (the same reduction order as plb_moe_bwd_dy, so both give the same bits).
+ * plb_ep_gather_rows: plb_moe_gather_rows with the source picked by peer_rank[p] (bf16 rows of x
+ *   for the gate/up weight gradient).
+ * The input gradient d_x is plb_moe_gemm_down_push on the transposed-quantised gate/up weights into
+ * every home rank's [tokens * topk, hidden] buffer, summed over the slots with plb_moe_fwd_epilogue. */
+int plb_ep_bwd_dy(const void* const* d_out_peers, const float* const* router_w_peers, const int32_t* peer_rank,
+                  const int32_t* peer_token_idx, const int32_t* dest_row, const int32_t* num_tokens, int64_t capacity,
+                  int hidden, void* d_y_bf16, void* stream);
+int plb_moe_router_grad(const void* d_out_bf16, const void* combine_bf16, int64_t tokens, int topk, int hidden,
+                        float* d_router_weights, void* stream);
+int plb_ep_gather_rows(const void* const* src_peers, const int32_t* peer_rank, const int32_t* peer_token_idx,
+                       const int32_t* num_tokens, int64_t capacity, int cols, void* dst_bf16, void* stream);
+
 /* plb_moe_gemm_down with the combine push (combine_kernel, comm.cu:124-129,327): row p is
  * stored to combine_peers[peer_rank[p]][dest_row[p]] from the GEMM epilogue. */
 int plb_moe_gemm_down_push(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,

@@ -118,6 +118,93 @@ gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ peer_r
   }
 }
 
+// Expert-parallel forms of the two kernels above: the row's source rank picks the base pointer.
+// d_y[p] = w_peers[r][dest_row[p]] * d_out_peers[r][token]; the router gradient is computed at
+// the token's home rank instead (router_grad_kernel), where the combine rows already are.
+__global__ void __launch_bounds__(256)
+ep_bwd_dy_kernel(const uint4* const* __restrict__ d_out_peers, const float* const* __restrict__ router_w_peers,
+                 const int* __restrict__ peer_rank, const int* __restrict__ peer_token_idx,
+                 const int* __restrict__ dest_row, const int* __restrict__ num_rows_dev, int64_t capacity,
+                 int hidden, uint4* __restrict__ dy) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  int64_t rows = *num_rows_dev;
+  if (rows > capacity) rows = capacity;
+  const int vecs = hidden >> 3;
+  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < capacity; p += warps) {
+    uint4* dst = dy + p * vecs;
+    const int r = p < rows ? peer_rank[p] : -1;
+    if (r < 0) {
+      for (int v = lane; v < vecs; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const float w = router_w_peers[r][dest_row[p]];
+    const uint4* src = d_out_peers[r] + static_cast<int64_t>(peer_token_idx[p]) * vecs;
+    for (int v0 = lane; v0 < vecs; v0 += 128) {   // four 16-byte loads in flight per lane
+      uint4 g[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * 32 < vecs) g[u] = src[v0 + u * 32];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (v0 + u * 32 >= vecs) break;
+        uint4 o;
+        o.x = pack2(__fmul_rn(w, lo16(g[u].x)), __fmul_rn(w, hi16(g[u].x)));
+        o.y = pack2(__fmul_rn(w, lo16(g[u].y)), __fmul_rn(w, hi16(g[u].y)));
+        o.z = pack2(__fmul_rn(w, lo16(g[u].z)), __fmul_rn(w, hi16(g[u].z)));
+        o.w = pack2(__fmul_rn(w, lo16(g[u].w)), __fmul_rn(w, hi16(g[u].w)));
+        dst[v0 + u * 32] = o;
+      }
+    }
+  }
+}
+
+// d_router_w[t * topk + j] = <d_out[t], combine[t * topk + j]>: one warp per (token, slot), the
+// same lane partition, fma order and shuffle tree as bwd_dy_kernel, so both give the same bits.
+__global__ void __launch_bounds__(256)
+router_grad_kernel(const uint4* __restrict__ d_out, const uint4* __restrict__ y, int64_t tokens, int topk, int hidden,
+                   float* __restrict__ d_router_w) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int vecs = hidden >> 3;
+  for (int64_t d = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; d < tokens * topk; d += warps) {
+    const uint4* src = d_out + (d / topk) * vecs;
+    const uint4* yr = y + d * vecs;
+    float dot = 0.0f;
+    for (int v = lane; v < vecs; v += 32) {
+      const uint4 g = src[v], yy = yr[v];
+      const float gf[8] = {lo16(g.x), hi16(g.x), lo16(g.y), hi16(g.y), lo16(g.z), hi16(g.z), lo16(g.w), hi16(g.w)};
+      const float yf[8] = {lo16(yy.x), hi16(yy.x), lo16(yy.y), hi16(yy.y), lo16(yy.z), hi16(yy.z), lo16(yy.w), hi16(yy.w)};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot = fmaf(gf[i], yf[i], dot);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, s);
+    if (lane == 0) d_router_w[d] = dot;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+ep_gather_rows_kernel(const uint4* const* __restrict__ src_peers, const int* __restrict__ peer_rank,
+                      const int* __restrict__ peer_token_idx, const int* __restrict__ num_rows_dev,
+                      int64_t capacity, int vecs, uint4* __restrict__ dst) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t rows = *num_rows_dev;
+  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < capacity; p += warps) {
+    const int r = p < rows ? peer_rank[p] : -1;
+    const uint4* s = r >= 0 ? src_peers[r] + static_cast<int64_t>(peer_token_idx[p]) * vecs : nullptr;
+    for (int v0 = lane; v0 < vecs; v0 += 128) {
+      uint4 g[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) g[u] = (r >= 0 && v0 + u * 32 < vecs) ? s[v0 + u * 32] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * 32 < vecs) dst[p * vecs + v0 + u * 32] = g[u];
+    }
+  }
+}
+
 // Zero rows [*num_rows, capacity) of a bf16 [capacity, cols] tensor.
 __global__ void __launch_bounds__(256)
 zero_tail_kernel(uint4* __restrict__ t, const int* __restrict__ num_rows_dev, int64_t capacity, int vecs) {
@@ -170,6 +257,33 @@ cudaError_t launch_gather_rows(const void* src, const int* peer_rank, const int*
   if (capacity == 0) return cudaSuccess;
   gather_rows_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const uint4*>(src), peer_rank, peer_token_idx,
                                                      num_rows_dev, capacity, cols >> 3, static_cast<uint4*>(dst));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_bwd_dy(const void* const* d_out_peers, const float* const* router_w_peers, const int* peer_rank,
+                             const int* peer_token_idx, const int* dest_row, const int* num_rows_dev, int64_t capacity,
+                             int hidden, void* dy, cudaStream_t stream) {
+  if (capacity == 0) return cudaSuccess;
+  ep_bwd_dy_kernel<<<sm_grid(8), 256, 0, stream>>>(reinterpret_cast<const uint4* const*>(d_out_peers), router_w_peers,
+                                                   peer_rank, peer_token_idx, dest_row, num_rows_dev, capacity, hidden,
+                                                   static_cast<uint4*>(dy));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_router_grad(const void* d_out, const void* combine, int64_t tokens, int topk, int hidden,
+                               float* d_router_w, cudaStream_t stream) {
+  if (tokens == 0) return cudaSuccess;
+  router_grad_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const uint4*>(d_out), static_cast<const uint4*>(combine),
+                                                     tokens, topk, hidden, d_router_w);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_gather_rows(const void* const* src_peers, const int* peer_rank, const int* peer_token_idx,
+                                  const int* num_rows_dev, int64_t capacity, int cols, void* dst, cudaStream_t stream) {
+  if (capacity == 0) return cudaSuccess;
+  ep_gather_rows_kernel<<<sm_grid(8), 256, 0, stream>>>(reinterpret_cast<const uint4* const*>(src_peers), peer_rank,
+                                                        peer_token_idx, num_rows_dev, capacity, cols >> 3,
+                                                        static_cast<uint4*>(dst));
   return cudaGetLastError();
 }
 

@@ -477,6 +477,32 @@ int plb_moe_gather_rows(const void* src_bf16, const int32_t* peer_rank, const in
                                            dst_bf16, static_cast<cudaStream_t>(stream)));
 }
 
+int plb_ep_bwd_dy(const void* const* d_out_peers, const float* const* router_w_peers, const int32_t* peer_rank,
+                  const int32_t* peer_token_idx, const int32_t* dest_row, const int32_t* num_tokens, int64_t capacity,
+                  int hidden, void* d_y_bf16, void* stream) {
+  if (!d_out_peers || !router_w_peers || !peer_rank || !peer_token_idx || !dest_row || !num_tokens || !d_y_bf16 ||
+      capacity < 0 || hidden <= 0 || hidden % 8)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_ep_bwd_dy(d_out_peers, router_w_peers, peer_rank, peer_token_idx, dest_row, num_tokens,
+                                         capacity, hidden, d_y_bf16, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_router_grad(const void* d_out_bf16, const void* combine_bf16, int64_t tokens, int topk, int hidden,
+                        float* d_router_weights, void* stream) {
+  if (!d_out_bf16 || !combine_bf16 || !d_router_weights || tokens < 0 || topk < 1 || hidden <= 0 || hidden % 8)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_router_grad(d_out_bf16, combine_bf16, tokens, topk, hidden, d_router_weights,
+                                           static_cast<cudaStream_t>(stream)));
+}
+
+int plb_ep_gather_rows(const void* const* src_peers, const int32_t* peer_rank, const int32_t* peer_token_idx,
+                       const int32_t* num_tokens, int64_t capacity, int cols, void* dst_bf16, void* stream) {
+  if (!src_peers || !peer_rank || !peer_token_idx || !num_tokens || !dst_bf16 || capacity < 0 || cols <= 0 || cols % 8)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_ep_gather_rows(src_peers, peer_rank, peer_token_idx, num_tokens, capacity, cols, dst_bf16,
+                                              static_cast<cudaStream_t>(stream)));
+}
+
 int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
                       const plb_attn_work* work, int num_work, int heads_per_work, int q_heads, int kv_heads, int seq_q,
                       uint64_t q_rows, uint64_t kv_rows, float scale, const uint32_t* ready,

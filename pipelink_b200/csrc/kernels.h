@@ -102,6 +102,13 @@ cudaError_t launch_bwd_dy(const void* d_out, const void* y, const float* router_
 cudaError_t launch_swiglu_bwd(const void* gate, const void* gate_sc, const void* up, const void* up_sc,
                               const void* d_hidden, const int* num_rows_dev, int64_t capacity, int inter,
                               void* dgu, cudaStream_t stream);
+cudaError_t launch_ep_bwd_dy(const void* const* d_out_peers, const float* const* router_w_peers, const int* peer_rank,
+                             const int* peer_token_idx, const int* dest_row, const int* num_rows_dev, int64_t capacity,
+                             int hidden, void* dy, cudaStream_t stream);
+cudaError_t launch_router_grad(const void* d_out, const void* combine, int64_t tokens, int topk, int hidden,
+                               float* d_router_w, cudaStream_t stream);
+cudaError_t launch_ep_gather_rows(const void* const* src_peers, const int* peer_rank, const int* peer_token_idx,
+                                  const int* num_rows_dev, int64_t capacity, int cols, void* dst, cudaStream_t stream);
 cudaError_t launch_gather_rows(const void* src, const int* peer_rank, const int* peer_token_idx,
                                const int* num_rows_dev, int64_t capacity, int cols, void* dst,
                                cudaStream_t stream);

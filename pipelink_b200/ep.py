@@ -29,7 +29,7 @@ def _align(n, a=256):
 class SlabLayout:
     """Offsets of the peer-visible buffers inside one rank's symmetric slab."""
 
-    def __init__(self, shape: mok.Shape, world: int):
+    def __init__(self, shape: mok.Shape, world: int, train: bool = False):
         L, H, k = shape.tokens, shape.hidden, shape.topk
         if L % 128:
             raise ValueError("tokens per rank must be a multiple of 128")
@@ -39,6 +39,12 @@ class SlabLayout:
         self.xsc = off; off += _align(L // 128 * (H // 128) * 512)
         self.routes_all = off; off += _align(world * L * k * 4)
         self.combine = off; off += _align(L * k * H * 2)
+        self.train = train
+        if train:   # what the backward pass reads from / writes to a token's home rank
+            self.x_bf16 = off; off += _align(L * H * 2)        # tokens, for the gate/up weight gradient
+            self.d_out = off; off += _align(L * H * 2)         # upstream gradient
+            self.router_w = off; off += _align(L * k * 4)      # router weights (d_y = w * d_out)
+            self.d_x_rows = off; off += _align(L * k * H * 2)  # input-gradient rows, one per (token, slot)
         self.nbytes = off
 
 
@@ -67,9 +73,9 @@ def sym_alloc(nbytes: int) -> int:
 class LocalGroup:
     """`world` ranks emulated in one process: every slab is an allocation on the current device."""
 
-    def __init__(self, shape: mok.Shape, world: int, device):
+    def __init__(self, shape: mok.Shape, world: int, device, train: bool = False):
         self.world, self.device, self.distributed = world, torch.device(device), False
-        self.layout = SlabLayout(shape, world)
+        self.layout = SlabLayout(shape, world, train)
         self.slabs = [sym_alloc(self.layout.nbytes) for _ in range(world)]
 
     def ptrs_for(self, rank: int):
@@ -128,9 +134,9 @@ class IpcSlab:
 class IpcGroup:
     """One process per GPU; handles travel through ``torch.distributed`` (bootstrap only)."""
 
-    def __init__(self, shape: mok.Shape, rank: int, world: int, device, group=None):
+    def __init__(self, shape: mok.Shape, rank: int, world: int, device, group=None, train: bool = False):
         self.world, self.rank, self.device, self.distributed = world, rank, torch.device(device), True
-        self.layout = SlabLayout(shape, world)
+        self.layout = SlabLayout(shape, world, train)
         self.slab = IpcSlab(self.layout.nbytes, rank, world, group)
         self.peer_ptrs = self.slab.ptrs
 
@@ -161,6 +167,20 @@ class EpMoKHost(mok.MoKHost):
         self.buffers["combine_buffer"] = tensor_from_ptr(me + lay.combine, (L * k, H), torch.bfloat16, dev)
         self.routes_local = torch.empty((L, k), dtype=torch.int32, device=dev)
         self.barrier_state = torch.zeros(1, dtype=torch.int32, device=dev)
+        if lay.train:
+            self.x_peers, self.d_out_peers = table(lay.x_bf16), table(lay.d_out)
+            self.router_w_peers, self.d_x_rows_peers = table(lay.router_w), table(lay.d_x_rows)
+            # the peer-visible copies replace the private buffers of the single-rank session
+            self.x_buffer = tensor_from_ptr(me + lay.x_bf16, (L, H), torch.bfloat16, dev)
+            self._x_storage = self.x_buffer     # tokens per rank is a multiple of 128: no padding rows
+            self.router_weight_buffer = tensor_from_ptr(me + lay.router_w, (L, k), torch.float32, dev)
+            self.d_out_buffer = tensor_from_ptr(me + lay.d_out, (L, H), torch.bfloat16, dev)
+            self._d_x_rows = tensor_from_ptr(me + lay.d_x_rows, (L * k, H), torch.bfloat16, dev)
+
+    def _alloc_train_buffers(self):
+        super()._alloc_train_buffers()
+        if self.group.layout.train:
+            self.buffers["d_x_routed_buffer"] = self._d_x_rows
 
     # ---- steps, in the order forward() issues them
     def stage_inputs(self, inputs: mok.Inputs):
@@ -195,32 +215,107 @@ class EpMoKHost(mok.MoKHost):
                   s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
                   self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
 
-    def device_step(self):
+    def device_step(self, train: bool = False):
         """Everything after the inputs sit in x_buffer / routes_local / router_weight_buffer."""
         self.quantize_tokens()
         self.publish_routes()
         self.barrier()          # routes gathered, every rank's quantised tokens readable
         self.build_schedule()
         self.pull()
-        self.gemm_gate_up()
+        if train:
+            self.gemm_gate_up_train()
+        else:
+            self.gemm_gate_up()
         self.gemm_down_push()
         self.barrier()          # every rank's rows have landed in my combine buffer
         return self.fwd_epilogue()
 
-    def forward(self, inputs: mok.Inputs, *, check: bool = True):
+    def forward(self, inputs: mok.Inputs, *, check: bool = True, train: bool = False):
         if not self.group.distributed:
             raise ValueError("ranks of a LocalGroup are stepped together: use forward_local_group()")
         self.status.reset()
         self.x_buffer.copy_(inputs.x)
         self.router_weight_buffer.copy_(inputs.router)
         self.routes_local.copy_(inputs.experts)
-        out = self.device_step()
+        out = self.device_step(train)
         if check:
             self.status.check("after EP forward")
         return {"output": out, **self.context_tensors()}
 
+    # ---- backward, in the order backward() issues the steps (mirror of dispatch / combine)
+    def bwd_expert_side(self):
+        """Everything this rank does for the rows of ITS experts: pull w * d_out from the tokens'
+        home ranks, both data gradients, SwiGLU backward, the three weight gradients, and the push
+        of the input-gradient rows back to the home ranks."""
+        s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        P, H, I = self.capacity, sh.hidden, sh.intermediate
+        nt = s.num_tokens.data_ptr()
+        _lib.call("plb_ep_bwd_dy", self.d_out_peers.data_ptr(), self.router_w_peers.data_ptr(), s.peer_rank.data_ptr(),
+                  s.peer_token_idx.data_ptr(), s.dest_row.data_ptr(), nt, P, H, b["d_y_routed"].data_ptr(), mok._stream())
+        dy_q, dy_sc, dy_t, dy_t_sc = mok.mxfp8_quantize(b["d_y_routed"], True, True)
+        self._gemm_rows(dy_q, dy_sc, w["w_down_t_fp8"], w["w_down_t_sc"], H, I, b["d_hidden_routed"], self._identity_rows)
+        _, _, h_t, h_t_sc = mok.mxfp8_quantize(b["hidden_routed_bf16"], False, True)
+        self._wgrad(dy_t, dy_t_sc, h_t, h_t_sc, H, I, b["d_w_routed_down"])
+        _lib.call("plb_moe_swiglu_bwd", b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(),
+                  b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(), b["d_hidden_routed"].data_ptr(), nt, P, I,
+                  b["d_gate_up_routed"].data_ptr(), mok._stream())
+        dgu_q, dgu_sc, dgu_t, dgu_t_sc = mok.mxfp8_quantize(b["d_gate_up_routed"], True, True)
+        # d_x rows go straight from the GEMM epilogue into the home rank's [tokens * topk, H] buffer
+        _lib.call("plb_moe_gemm_down_push", dgu_q.data_ptr(), dgu_sc.data_ptr(), w["w_cat_t_fp8"].data_ptr(),
+                  w["w_cat_t_sc"].data_ptr(), s.block_expert.data_ptr(), nt, s.dest_row.data_ptr(), s.peer_rank.data_ptr(),
+                  P, self.num_local_experts, 2 * I, H, self.d_x_rows_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
+        _lib.call("plb_ep_gather_rows", self.x_peers.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), nt, P, H,
+                  b["x_routed_bf16"].data_ptr(), mok._stream())
+        _, _, x_t, x_t_sc = mok.mxfp8_quantize(b["x_routed_bf16"], False, True)
+        self._wgrad(dgu_t, dgu_t_sc, x_t, x_t_sc, 2 * I, H, b["d_w_routed_gate_up"])
 
-def forward_local_group(hosts, inputs_per_rank):
+    def bwd_home_side_early(self):
+        """Needs only this rank's own tokens: the router-weight gradient."""
+        b, sh = self.buffers, self.shape
+        _lib.call("plb_moe_router_grad", self.d_out_buffer.data_ptr(), b["combine_buffer"].data_ptr(), sh.tokens, sh.topk,
+                  sh.hidden, b["d_router_weights"].data_ptr(), mok._stream())
+
+    def bwd_home_side_late(self):
+        """After every rank's input-gradient rows have landed: sum the slots of each token."""
+        b, sh = self.buffers, self.shape
+        _lib.call("plb_moe_fwd_epilogue", None, b["d_x_routed_buffer"].data_ptr(), self._ones.data_ptr(), sh.tokens,
+                  sh.topk, sh.hidden, b["d_x"].data_ptr(), mok._stream())
+
+    def gradients(self):
+        b, I = self.buffers, self.shape.intermediate
+        g = b["d_w_routed_gate_up"]
+        return {"d_x": b["d_x"], "d_router_weights": b["d_router_weights"], "d_w_routed_gate": g[:, :I],
+                "d_w_routed_up": g[:, I:], "d_w_routed_down": b["d_w_routed_down"]}
+
+    def backward(self, d_out: torch.Tensor, *, check: bool = True):
+        """Backward of the last ``forward(train=True)`` of a distributed group."""
+        if not self.group.distributed:
+            raise ValueError("ranks of a LocalGroup are stepped together: use backward_local_group()")
+        self.d_out_buffer.copy_(d_out)
+        self.barrier()          # every rank's d_out is readable; forward's combine rows are long in place
+        self.bwd_home_side_early()
+        self.bwd_expert_side()
+        self.barrier()          # every rank's d_x rows have landed here
+        self.bwd_home_side_late()
+        if check:
+            self.status.check("after EP backward")
+        return self.gradients()
+
+
+def backward_local_group(hosts, d_out_per_rank):
+    """Backward of forward_local_group(..., train=True), phase by phase on the current stream."""
+    for h, d in zip(hosts, d_out_per_rank):
+        h.d_out_buffer.copy_(d)
+    for h in hosts:
+        h.bwd_home_side_early()
+        h.bwd_expert_side()
+    for h in hosts:
+        h.bwd_home_side_late()
+        h.status.check("after local-group backward")
+    return [h.gradients() for h in hosts]
+
+
+def forward_local_group(hosts, inputs_per_rank, train: bool = False):
     """Run every rank of a LocalGroup phase by phase on the current stream."""
     for h, inp in zip(hosts, inputs_per_rank):
         h.status.reset()
@@ -229,7 +324,10 @@ def forward_local_group(hosts, inputs_per_rank):
     for h in hosts:
         h.build_schedule()
         h.pull()
-        h.gemm_gate_up()
+        if train:
+            h.gemm_gate_up_train()
+        else:
+            h.gemm_gate_up()
     for h in hosts:
         h.gemm_down_push()
     outs = [h.fwd_epilogue() for h in hosts]
@@ -242,24 +340,33 @@ class BenchSession:
     """bench.py's N > 1 arm: one rank of an IpcGroup at BASELINE config 4's per-rank shape."""
 
     launches_per_step = 11  # quantise, publish, barrier x2, schedule x3, pull, 2 GEMMs, epilogue
+    # backward adds: barrier x2, router grad, d_y pull, 5 quantise, 2 dgrad GEMMs, SwiGLU backward, x gather,
+    # 2 wgrad GEMMs, slot sum, 2 tail-zeroing launches
+    launches_per_step_train = 11 + 18
 
-    def __init__(self, shape: mok.Shape, dev, rank: int, world: int):
-        self.shape, self.dev = shape, dev
-        self.group = IpcGroup(shape, rank, world, dev)
+    def __init__(self, shape: mok.Shape, dev, rank: int, world: int, train: bool = False):
+        self.shape, self.dev, self.train = shape, dev, train
+        self.group = IpcGroup(shape, rank, world, dev, train=train)
         self.host = EpMoKHost(shape, rank, self.group)
         torch.manual_seed(1234 + rank)
         E, H, I = self.host.num_local_experts, shape.hidden, shape.intermediate
-        q = {}
-        for name, rows, cols in (("gate", I, H), ("up", I, H), ("down", H, I)):
-            fp8 = torch.empty((E, rows, cols), dtype=torch.uint8, device=dev)
-            sc = torch.empty((E * rows // 128, cols // 128, 32, 16), dtype=torch.uint8, device=dev)
-            for e in range(E):
-                w = (torch.randn(rows, cols, device=dev) * 0.02).to(torch.bfloat16)
-                a, b, _, _ = mok.mxfp8_quantize(w)
-                fp8[e].copy_(a)
-                sc[e * rows // 128:(e + 1) * rows // 128].copy_(b)
-            q[name] = (fp8, sc)
-        self.host.load_quantized_weights(*q["gate"], *q["up"], *q["down"], keep_unpacked=False)
+        if train:
+            mk = lambda *sh: (torch.randn(*sh, device=dev) * 0.02).to(torch.bfloat16)
+            self.host.load_weights(mk(E, I, H), mk(E, I, H), mk(E, H, I), keep_unpacked=False, train=True)
+            self.d_out = torch.randn(shape.tokens, H, device=dev).to(torch.bfloat16)
+            self.launches_per_step = self.launches_per_step_train
+        else:
+            q = {}
+            for name, rows, cols in (("gate", I, H), ("up", I, H), ("down", H, I)):
+                fp8 = torch.empty((E, rows, cols), dtype=torch.uint8, device=dev)
+                sc = torch.empty((E * rows // 128, cols // 128, 32, 16), dtype=torch.uint8, device=dev)
+                for e in range(E):
+                    w = (torch.randn(rows, cols, device=dev) * 0.02).to(torch.bfloat16)
+                    a, b, _, _ = mok.mxfp8_quantize(w)
+                    fp8[e].copy_(a)
+                    sc[e * rows // 128:(e + 1) * rows // 128].copy_(b)
+                q[name] = (fp8, sc)
+            self.host.load_quantized_weights(*q["gate"], *q["up"], *q["down"], keep_unpacked=False)
         logits = torch.randn(shape.tokens, shape.experts, device=dev)
         values, experts = torch.topk(logits, shape.topk, dim=1)
         x = torch.randn(shape.tokens, H, device=dev).to(torch.bfloat16)
@@ -282,17 +389,20 @@ class BenchSession:
         h.barrier()
         h.build_schedule()
         h.pull()
+        gate_up = h.gemm_gate_up_train if self.train else h.gemm_gate_up
         if record:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            h.gemm_gate_up()
+            gate_up()
             b.record()
             self.kernel_events.append((a, b))
         else:
-            h.gemm_gate_up()
+            gate_up()
         h.gemm_down_push()
         h.barrier()
         h.fwd_epilogue()
+        if self.train:
+            h.backward(self.d_out, check=False)
 
     def check(self):
         self.host.status.check("bench (EP)")

@@ -1,4 +1,5 @@
-"""torchrun child of tests/test_ep_gpu.py: a real IPC group, checked against the CPU oracle."""
+"""torchrun child of tests/test_ep_gpu.py: a real IPC group. The forward is checked against the
+CPU oracle; forward + backward against one rank holding every token and every expert (bitwise)."""
 import os
 import sys
 from pathlib import Path
@@ -40,6 +41,38 @@ def main():
                                       padding=mok.expert_padding())
         s = omoe.error_stats(ref["outputs"][rank], out)
         assert np.isfinite(out).all() and s["relative"] <= 2e-2, (rank, generation, s)
+    torch.cuda.synchronize()
+    dist.barrier()
+    group.close()
+
+    # ---- training: forward + backward across the group == the single-rank pass on the whole problem
+    mok.set_gemm_variant(2)
+    group = ep.IpcGroup(shape, rank, world, dev, train=True)
+    host = ep.EpMoKHost(shape, rank, group)
+    host.load_weights(wg[rank * El:(rank + 1) * El] * 2.5, wu[rank * El:(rank + 1) * El] * 2.5, wd[rank * El:(rank + 1) * El] * 2.5, train=True)
+    whole = mok.Shape("whole", E, H, I, shape.topk, shape.tokens * world)
+    single = mok.MoKHost(whole, device=dev)
+    single.load_weights(wg * 2.5, wu * 2.5, wd * 2.5, train=True)
+    L = shape.tokens
+    eq = lambda a, b: torch.equal(a.contiguous().view(torch.int16 if a.dtype == torch.bfloat16 else torch.int32),
+                                  b.contiguous().view(torch.int16 if b.dtype == torch.bfloat16 else torch.int32))
+    for generation in (1, 3):
+        inputs = [mok.MoKHost.new_inputs(shape, generation, dev, rank=r, world=world) for r in range(world)]
+        gen = torch.Generator(device=dev).manual_seed(77 + generation)
+        d_outs = [torch.randn(L, H, generator=gen, device=dev).to(torch.bfloat16) for _ in range(world)]
+        joined = mok.Inputs(torch.cat([i.x for i in inputs]), torch.cat([i.experts for i in inputs]), torch.cat([i.router for i in inputs]))
+        out_single = single.forward(joined, train=True)["output"].clone()
+        want = {k: v.clone() for k, v in single.backward(torch.cat(d_outs)).items()}
+        host.buffers["d_x_routed_buffer"].fill_(float("nan"))
+        out = host.forward(inputs[rank], train=True)["output"]
+        g = host.backward(d_outs[rank])
+        torch.cuda.synchronize()
+        assert eq(out, out_single[rank * L:(rank + 1) * L]), (rank, generation, "output")
+        assert torch.isfinite(g["d_x"].float()).all()
+        assert eq(g["d_x"], want["d_x"][rank * L:(rank + 1) * L]), (rank, generation, "d_x")
+        assert eq(g["d_router_weights"], want["d_router_weights"][rank * L:(rank + 1) * L]), (rank, generation, "d_router_weights")
+        for name in ("d_w_routed_gate", "d_w_routed_up", "d_w_routed_down"):
+            assert eq(g[name], want[name][rank * El:(rank + 1) * El]), (rank, generation, name)
     torch.cuda.synchronize()
     dist.barrier()
     group.close()

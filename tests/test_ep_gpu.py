@@ -71,6 +71,51 @@ def test_local_group_forward_vs_oracle(native_lib, world, shape_args):
         group.close()
 
 
+@pytest.mark.parametrize("world,shape_args", [(2, ("ep2b", 8, 512, 256, 2, 256)), (4, ("ep4b", 8, 256, 256, 4, 128))])
+def test_local_group_backward_equals_the_single_rank_backward(native_lib, world, shape_args):
+    """Forward + backward over a group must give, bit for bit, what one rank holding every token and
+    every expert computes: an expert's rows arrive in the same order on the rank that owns it, so
+    every quantisation block, GEMM and reduction sees the same operands. (The single-rank backward
+    is itself held to the CPU oracle in test_moe_backward_gpu.py.)"""
+    from pipelink_b200 import ep, mok
+    mok.set_gemm_variant(2)
+    shape = mok.Shape(*shape_args)
+    wg, wu, wd, inputs = make_group_case(mok, shape, world, seed=3)
+    wg, wu, wd = wg * 2.5, wu * 2.5, wd * 2.5
+    torch.manual_seed(11)
+    d_outs = [torch.randn(shape.tokens, shape.hidden, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    # one rank, all tokens, all experts
+    whole = mok.Shape("whole", shape.experts, shape.hidden, shape.intermediate, shape.topk, shape.tokens * world)
+    single = mok.MoKHost(whole)
+    single.load_weights(wg, wu, wd, train=True)
+    joined = mok.Inputs(torch.cat([i.x for i in inputs]), torch.cat([i.experts for i in inputs]), torch.cat([i.router for i in inputs]))
+    out_single = single.forward(joined, train=True)["output"].clone()
+    want = {k: v.clone() for k, v in single.backward(torch.cat(d_outs)).items()}
+    group = ep.LocalGroup(shape, world, "cuda", train=True)
+    try:
+        hosts = [ep.EpMoKHost(shape, r, group) for r in range(world)]
+        El, L = shape.experts // world, shape.tokens
+        for r, h in enumerate(hosts):
+            h.load_weights(wg[r * El:(r + 1) * El], wu[r * El:(r + 1) * El], wd[r * El:(r + 1) * El], train=True)
+            h.buffers["d_x_routed_buffer"].fill_(float("nan"))      # every (token, slot) row must be pushed by some rank
+        outs = ep.forward_local_group(hosts, inputs, train=True)
+        grads = ep.backward_local_group(hosts, d_outs)
+        torch.cuda.synchronize()
+        eq = lambda a, b: torch.equal(a.contiguous().view(torch.int16 if a.dtype == torch.bfloat16 else torch.int32),
+                                      b.contiguous().view(torch.int16 if b.dtype == torch.bfloat16 else torch.int32))
+        for r in range(world):
+            assert eq(outs[r], out_single[r * L:(r + 1) * L]), ("output", r)
+            g = grads[r]
+            assert torch.isfinite(g["d_x"].float()).all()
+            assert eq(g["d_x"], want["d_x"][r * L:(r + 1) * L]), ("d_x", r)
+            assert eq(g["d_router_weights"], want["d_router_weights"][r * L:(r + 1) * L]), ("d_router_weights", r)
+            for name in ("d_w_routed_gate", "d_w_routed_up", "d_w_routed_down"):
+                assert eq(g[name], want[name][r * El:(r + 1) * El]), (name, r)
+    finally:
+        torch.cuda.synchronize()
+        group.close()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_ipc_group_forward_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
