@@ -254,12 +254,16 @@ int plb_ep_gather_rows(const void* const* src_peers, const int32_t* peer_rank, c
                        const int32_t* num_tokens, int64_t capacity, int cols, void* dst_bf16, void* stream);
 
 /* plb_moe_gemm_down with the combine push (combine_kernel, comm.cu:124-129,327): row p is
- * stored to combine_peers[peer_rank[p]][dest_row[p]] from the GEMM epilogue. */
+ * stored to combine_peers[peer_rank[p]][dest_row[p]] from the GEMM epilogue. Rows are ordered by
+ * (expert, source rank), so ranks that walked their tiles in the same order would all write to
+ * the same home rank at the same time; tile_rotation (>= 0, in 256-row tiles, CTA-pair variant)
+ * makes this rank start that many tiles in and wrap around. Pass rank * tiles per (expert,
+ * source rank) block, or 0. The result does not depend on it. */
 int plb_moe_gemm_down_push(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
                            const void* w2_sc, const int32_t* block_expert,
                            const int32_t* num_tokens, const int32_t* dest_row,
                            const int32_t* peer_rank, int64_t capacity, int experts, int inter,
-                           int hidden, void* const* combine_peers, plb_status* status,
+                           int hidden, int tile_rotation, void* const* combine_peers, plb_status* status,
                            void* stream);
 
 /* ops.fwd_epilogue (campaigns/mok/host/mok_port_host.py:204):

@@ -49,7 +49,7 @@ PROTOTYPES = {
                                   c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_void_p]),
     "plb_moe_gemm_down_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                       c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p,
+                                       c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                                        c_void_p, c_void_p]),
     "plb_ep_barrier": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "plb_ep_publish": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),

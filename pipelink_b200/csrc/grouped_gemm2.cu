@@ -94,6 +94,7 @@ struct Params2 {
   long long* prof;          // per-CTA cycle counters; only written by profiling builds
   const int* block_expert;  // per 128-row block
   const int* num_rows_dev;
+  int m_rotation;           // modes 0/1: the tile loop starts this many 256-row tiles in (wraps around)
   int max_m_tiles;          // capacity / 256
   int k_steps;
   int n_tiles;              // weight rows per expert / 256
@@ -130,7 +131,7 @@ struct Tile {
 };
 
 template <int MODE>
-__device__ __forceinline__ Tile decode_tile(const Params2& p, int tile, int cta_rank) {
+__device__ __forceinline__ Tile decode_tile(const Params2& p, int tile, int cta_rank, int m_tiles_live, int m_rot) {
   Tile t;
   if (MODE == 2) {
     const int per_expert = p.m_tiles * p.n_tiles;
@@ -144,8 +145,12 @@ __device__ __forceinline__ Tile decode_tile(const Params2& p, int tile, int cta_
     t.k_pitch = p.k_blocks_total;
     t.out_row0 = (static_cast<int64_t>(e) * p.m_tiles + m_tile) * 256;
   } else {
-    const int m_tile = tile / p.n_tiles;
+    int m_tile = tile / p.n_tiles;
     t.n_tile = tile - m_tile * p.n_tiles;
+    // A rank that pushes rows to their home ranks starts at a different source-rank segment
+    // than its peers, so the group writes all-to-all instead of all-to-one.
+    m_tile += m_rot;
+    if (m_tile >= m_tiles_live) m_tile -= m_tiles_live;
     const int expert = p.block_expert[m_tile * 2];
     t.a_blk = m_tile * 2 + cta_rank;
     t.b_blk0 = (expert * p.n_tiles + t.n_tile) * 2;
@@ -238,14 +243,15 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
-  int total_tiles;
+  int total_tiles, m_tiles_live = 0;
   if (MODE == 2) {
     total_tiles = p.experts * p.m_tiles * p.n_tiles;
   } else {
-    int m_tiles = *p.num_rows_dev >> 8;
-    if (m_tiles > p.max_m_tiles) m_tiles = p.max_m_tiles;
-    total_tiles = m_tiles * p.n_tiles;
+    m_tiles_live = *p.num_rows_dev >> 8;
+    if (m_tiles_live > p.max_m_tiles) m_tiles_live = p.max_m_tiles;
+    total_tiles = m_tiles_live * p.n_tiles;
   }
+  const int m_rot = m_tiles_live > 0 ? p.m_rotation % m_tiles_live : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -282,7 +288,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       PROF_DECL(t_empty);
       PROF_T0(t_begin);
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-        const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank));
+        const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank), m_tiles_live, m_rot);
         const int a_blk = t.a_blk, b_blk0 = t.b_blk0;
         const int b_blk = b_blk0 + static_cast<int>(cta_rank);
         for (int kb = 0; kb < t.k_steps; ++kb) {
@@ -329,7 +335,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       PROF_DECL(t_full);
       PROF_T0(t_begin);
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-        const Tile t = decode_tile<MODE>(p, tile, 0);
+        const Tile t = decode_tile<MODE>(p, tile, 0, m_tiles_live, m_rot);
         if (t.k_steps == 0) continue;  // empty expert: the epilogue writes zeros on its own
         PROF_T0(ta);
         if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY,
@@ -395,7 +401,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     PROF_DECL(t_drain);
     PROF_DECL(t_work);
     for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-      const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank));
+      const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank), m_tiles_live, m_rot);
       const int n_tile = t.n_tile;
       const int64_t row = t.out_row0 + cta_rank * 128 + quad * 32 + lane;
       if (MODE == 2 && t.k_steps == 0) {
@@ -610,6 +616,7 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
   p.prof = static_cast<long long*>(a.profile);
   p.block_expert = a.block_expert;
   p.num_rows_dev = a.num_rows_dev;
+  p.m_rotation = a.m_rotation < 0 ? 0 : a.m_rotation;
   p.max_m_tiles = static_cast<int>(a.rows_capacity / 256);
   p.k_steps = static_cast<int>(k_steps);
   p.n_tiles = a.n_rows / 256;

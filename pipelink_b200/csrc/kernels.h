@@ -76,6 +76,7 @@ struct GroupedGemmArgs {
   const int* dest_row;
   void* const* out_peers = nullptr;  // mode 1: per-source-rank output bases (device array), or null
   const int* peer_rank = nullptr;    // mode 1 with out_peers
+  int m_rotation = 0;                // pair variant: 256-row tiles are visited starting this many tiles in
   int num_sms;
   Status* status;
   void* profile = nullptr;  // cycle counters [grid, 16] i64, written only by profiling builds

@@ -167,6 +167,9 @@ class EpMoKHost(mok.MoKHost):
         self.buffers["combine_buffer"] = tensor_from_ptr(me + lay.combine, (L * k, H), torch.bfloat16, dev)
         self.routes_local = torch.empty((L, k), dtype=torch.int32, device=dev)
         self.barrier_state = torch.zeros(1, dtype=torch.int32, device=dev)
+        # Pushing GEMMs start `rank` source-rank blocks into their tile list: a block is the rows one
+        # rank sends to one expert, L * k / E on average, in 256-row tiles.
+        self.push_rotation = rank * max(1, (L * k // shape.experts) // 256) if W > 1 else 0
         if lay.train:
             self.x_peers, self.d_out_peers = table(lay.x_bf16), table(lay.d_out)
             self.router_w_peers, self.d_x_rows_peers = table(lay.router_w), table(lay.d_x_rows)
@@ -213,7 +216,7 @@ class EpMoKHost(mok.MoKHost):
                   w["w_routed_down_fp8"].data_ptr(), w["w_routed_down_sc"].data_ptr(),
                   s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(),
                   s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
-                  self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
+                  self.push_rotation, self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
 
     def device_step(self, train: bool = False):
         """Everything after the inputs sit in x_buffer / routes_local / router_weight_buffer."""
@@ -263,7 +266,8 @@ class EpMoKHost(mok.MoKHost):
         # d_x rows go straight from the GEMM epilogue into the home rank's [tokens * topk, H] buffer
         _lib.call("plb_moe_gemm_down_push", dgu_q.data_ptr(), dgu_sc.data_ptr(), w["w_cat_t_fp8"].data_ptr(),
                   w["w_cat_t_sc"].data_ptr(), s.block_expert.data_ptr(), nt, s.dest_row.data_ptr(), s.peer_rank.data_ptr(),
-                  P, self.num_local_experts, 2 * I, H, self.d_x_rows_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
+                  P, self.num_local_experts, 2 * I, H, self.push_rotation, self.d_x_rows_peers.data_ptr(),
+                  self.status.buf.data_ptr(), mok._stream())
         _lib.call("plb_ep_gather_rows", self.x_peers.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), nt, P, H,
                   b["x_routed_bf16"].data_ptr(), mok._stream())
         _, _, x_t, x_t_sc = mok.mxfp8_quantize(b["x_routed_bf16"], False, True)
