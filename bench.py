@@ -340,6 +340,10 @@ def attention_leg(dev, pk, seq=32768, steps=3):
     tf = 4.0 * 128 * Hq * seq * (seq + 1) / 2 / (ms * 1e-3) / 1e12
     return {"metric": "causal_prefill_attention_tflops", "value": tf, "unit": "TFLOP/s", "ms": ms, "seq": seq,
             "heads": [Hq, Hkv], "dtype": "bf16",
+            # the reference's published figure for causal prefill at 32K, 32/8 heads, d = 128 (other
+            # hardware): 614.5 useful TFLOP/s on one H200 (campaigns/attention/README.md:172)
+            **({"vs_baseline": tf / 614.5, "baseline": {"value": 614.5, "unit": "TFLOP/s", "hardware": "1x H200 @ 1305 MHz"}}
+               if seq == 32768 else {}),
             "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_sustained"], "unit": "TFLOP/s",
                          "frac": tf / pk["bf16_sustained"], "peak_source": f"bf16_tflops_sustained of {pk['source']} peaks"}}
 
@@ -416,6 +420,9 @@ def decode_leg(dev, pk, steps=128, prefill=4096):
     return {"metric": "llama1b_decode_ms_per_token", "value": ms, "unit": "ms/token", "steps": steps,
             "prefill": prefill, "higher_is_better": False, "dtype": "bf16", "launches_per_token": 1,
             "tokens": s.token_out[prefill + 1: prefill + 5].tolist(),
+            # the reference's published figure for this configuration (other hardware): 1.701 ms/token
+            # on one sm103 at 1102 MHz (campaigns/megakernel/evidence/CUTE-RESULT.md:14)
+            "vs_baseline": ms / 1.701, "baseline": {"value": 1.701, "unit": "ms/token", "hardware": "1x sm103 @ 1102 MHz"},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
                          "bytes_per_token": nbytes, "peak_source": f"hbm_gbs of {pk['source']} peaks"}}
 
