@@ -64,6 +64,15 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []
+        self.t_begin = self.t_end = None
+
+    def mark_begin(self):
+        """The timed region starts now (the sampler itself is started earlier: nvidia-smi needs a
+        few hundred milliseconds before its first sample)."""
+        self.t_begin = time.monotonic()
+
+    def mark_end(self):
+        self.t_end = time.monotonic()
 
     def start(self):
         try:
@@ -77,7 +86,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
     def stop(self):
         if self.proc is None:
@@ -89,7 +98,12 @@ class ClockSampler:
             self.proc.kill()
         mhz, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        lines = self.lines
+        if self.t_begin is not None and self.t_end is not None:
+            # samples taken while the timed steps ran; one sampling interval of slack on both sides
+            inside = [l for l in lines if self.t_begin - 0.03 <= l[0] <= self.t_end + 0.03]
+            lines = inside or lines[-3:]
+        for _, line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -185,24 +199,38 @@ def run_native(args):
 
     flop_per_rank = 6.0 * shape.tokens * shape.topk * shape.hidden * shape.intermediate
     launches_per_step = session.launches_per_step
-    for _ in range(max(args.warmup, 3)):
-        session.step()
-    session.check()
-
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        session.step()
+    session.check()
+    # keep every GPU under the same load until rank 0's sampler has produced its first lines
+    # (all ranks step together: an expert-parallel step contains group barriers)
+    t_wait = time.monotonic()
+    while True:
+        ready = rank != 0 or len(sampler.lines) >= 2 or sampler.proc is None or time.monotonic() - t_wait > 4.0
+        if world > 1:
+            flag = torch.tensor([1 if ready else 0], dtype=torch.int32, device=dev)
+            dist.broadcast(flag, 0)
+            ready = bool(flag.item())
+        if ready:
+            break
+        session.step()
+        torch.cuda.synchronize()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     session.kernel_events = []
+    sampler.mark_begin()
     ev[0].record()
     for _ in range(args.steps):
         session.step(record=True)
     ev[1].record()
     torch.cuda.synchronize()
+    sampler.mark_end()
     ms_local = ev[0].elapsed_time(ev[1])
     t = torch.tensor([ms_local], dtype=torch.float64, device=dev)
     if world > 1:
