@@ -84,6 +84,8 @@ int plb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t cols, void* d
   if (!aligned16(dst_fp8) || !aligned16(dst_sc) || !aligned16(dst_t_fp8) || !aligned16(dst_t_sc))
     return PLB_E_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dst_t_fp8 != nullptr)   // the transposed orientation, alone or with the other: one pass over the input
+    return from_cuda(plb::launch_quantize_tile(src_bf16, rows, cols, dst_fp8, dst_sc, dst_t_fp8, dst_t_sc, s));
   if (dst_fp8 != nullptr) {
     const int rc = from_cuda(plb::launch_quantize_plain(src_bf16, rows, cols, dst_fp8, dst_sc, s));
     if (rc != PLB_OK) return rc;

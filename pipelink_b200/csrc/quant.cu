@@ -131,6 +131,92 @@ quantize_transposed_kernel(const uint32_t* __restrict__ src, int64_t rows, int64
   }
 }
 
+// One pass over the input for both orientations: a CTA stages a 128 x 128 bf16 tile in shared
+// memory (coalesced 16-byte loads), then quantises it along the columns (row orientation: 32
+// consecutive columns per block, four threads of a warp finish 128 contiguous output bytes of a
+// row) and along the rows (transposed orientation: 32 consecutive rows per block, the four row
+// blocks of a column are written by the same CTA so L2 sees whole 128-byte lines). Either output
+// may be absent. Same arithmetic as the two kernels above, so the same bytes.
+constexpr int kTile = 128;
+constexpr int kTilePitch = kTile * 2 + 16;   // bytes per staged row; the pad keeps 16-byte alignment
+
+__device__ __forceinline__ float bf16_at(const uint8_t* row, int col) {
+  return __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(row + col * 2)) << 16);
+}
+
+__global__ void __launch_bounds__(kThreads)
+quantize_tile_kernel(const uint4* __restrict__ src, int64_t rows, int64_t cols, uint8_t* __restrict__ dst_fp8,
+                     uint8_t* __restrict__ dst_sc, uint8_t* __restrict__ dst_t_fp8, uint8_t* __restrict__ dst_t_sc) {
+  extern __shared__ __align__(16) uint8_t tile[];
+  const int64_t col_tiles = cols >> 7, row_tiles = rows >> 7;
+  for (int64_t tid = blockIdx.x; tid < row_tiles * col_tiles; tid += gridDim.x) {
+    const int64_t tr = tid / col_tiles, tc = tid - tr * col_tiles;
+    const int64_t r0 = tr * kTile, c0 = tc * kTile;
+    // stage: 16 threads per row, 16 rows per pass
+    for (int i = threadIdx.x; i < kTile * 16; i += kThreads) {
+      const int r = i >> 4, v = i & 15;
+      *reinterpret_cast<uint4*>(tile + r * kTilePitch + v * 16) = src[((r0 + r) * cols + c0) / 8 + v];
+    }
+    __syncthreads();
+    if (dst_fp8 != nullptr) {
+      for (int i = threadIdx.x; i < kTile * 4; i += kThreads) {
+        const int r = i >> 2, blk = i & 3;   // a warp covers 8 rows x 4 blocks
+        const uint8_t* row = tile + r * kTilePitch + blk * 64;
+        float x[32];
+        float amax = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 w = *reinterpret_cast<const uint4*>(row + q * 16);
+          const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            x[q * 8 + e * 2] = bf16_lo(ws[e]);
+            x[q * 8 + e * 2 + 1] = bf16_hi(ws[e]);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 32; ++e) amax = fmaxf(amax, fabsf(x[e]));
+        const uint32_t eb = e8m0_from_amax(amax);
+        const float inv = e8m0_inverse(eb);
+        uint4 o[2];
+        uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          ow[q] = cvt_e4m3x4(x[q * 4] * inv, x[q * 4 + 1] * inv, x[q * 4 + 2] * inv, x[q * 4 + 3] * inv);
+        uint4* out = reinterpret_cast<uint4*>(dst_fp8 + (r0 + r) * cols + c0 + blk * 32);
+        out[0] = o[0];
+        out[1] = o[1];
+        dst_sc[scale_offset(r0 + r, (c0 >> 5) + blk, col_tiles)] = static_cast<uint8_t>(eb);
+      }
+    }
+    if (dst_t_fp8 != nullptr) {
+      for (int i = threadIdx.x; i < kTile * 4; i += kThreads) {
+        const int col = i & 127, rb = i >> 7;   // a warp covers 32 consecutive columns of one row block
+        const uint8_t* base = tile + (rb * 32) * kTilePitch;
+        float x[32];
+        float amax = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          x[e] = bf16_at(base + e * kTilePitch, col);
+          amax = fmaxf(amax, fabsf(x[e]));
+        }
+        const uint32_t eb = e8m0_from_amax(amax);
+        const float inv = e8m0_inverse(eb);
+        uint4 o[2];
+        uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          ow[q] = cvt_e4m3x4(x[q * 4] * inv, x[q * 4 + 1] * inv, x[q * 4 + 2] * inv, x[q * 4 + 3] * inv);
+        uint4* out = reinterpret_cast<uint4*>(dst_t_fp8 + (c0 + col) * rows + r0 + rb * 32);
+        out[0] = o[0];
+        out[1] = o[1];
+        dst_t_sc[scale_offset(c0 + col, (r0 >> 5) + rb, row_tiles)] = static_cast<uint8_t>(eb);
+      }
+    }
+    __syncthreads();
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 dequantize_kernel(const uint8_t* __restrict__ src, const uint8_t* __restrict__ sc, int64_t rows,
                   int64_t cols, float* __restrict__ dst) {
@@ -273,6 +359,27 @@ cudaError_t launch_quantize_transposed(const void* src_bf16, int64_t rows, int64
   quantize_transposed_kernel<<<grid_for((rows >> 5) * (cols >> 1)), kThreads, 0, stream>>>(
       static_cast<const uint32_t*>(src_bf16), rows, cols, static_cast<uint8_t*>(dst_t_fp8),
       static_cast<uint8_t*>(dst_t_sc));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_tile(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8, void* dst_sc,
+                                 void* dst_t_fp8, void* dst_t_sc, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return cudaSuccess;
+  const int smem = kTile * kTilePitch;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(quantize_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return err;
+    configured = true;
+  }
+  const int64_t tiles = (rows >> 7) * (cols >> 7);
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t resident = static_cast<int64_t>(sms > 0 ? sms : 148) * 6;   // 34 KB of shared memory per CTA
+  quantize_tile_kernel<<<static_cast<unsigned>(tiles < resident ? tiles : resident), kThreads, smem, stream>>>(
+      static_cast<const uint4*>(src_bf16), rows, cols, static_cast<uint8_t*>(dst_fp8), static_cast<uint8_t*>(dst_sc),
+      static_cast<uint8_t*>(dst_t_fp8), static_cast<uint8_t*>(dst_t_sc));
   return cudaGetLastError();
 }
 
