@@ -378,6 +378,10 @@ class MoKHost:
             self.status.check("after MoE forward")
         return {"output": out, **self.context_tensors()}
 
+    def host_pipeline(self):
+        """A forward loop over HOST buffers (see HostPipeline)."""
+        return HostPipeline(self)
+
     def context_tensors(self):
         b = self.buffers
         return {"x_routed_data": b["x_routed_fp8"], "x_routed_scale": b["x_routed_sc"],
@@ -394,3 +398,65 @@ class MoKHost:
             experts.copy_(torch.arange(shape.topk, device=device).expand(shape.tokens, -1))
         x = torch.randn(shape.tokens, shape.hidden, generator=gen, device=device, dtype=torch.bfloat16)
         return Inputs(x, experts, torch.softmax(values.float(), dim=-1))
+
+
+class HostPipeline:
+    """Single-rank forward for callers whose tokens and results live in pinned HOST memory.
+
+    Three streams and two-deep staging: while step i computes, the inputs of step i+1 travel
+    host -> device and the result of step i-1 travels device -> host, so a loop runs at the pace
+    of the slowest of the three instead of their sum. Every step still moves its own inputs and
+    its own result; nothing is cached between steps.
+
+        pipe = host.host_pipeline()
+        for x, routes, router, out in batches:      # pinned host tensors
+            pipe.submit(x, routes, router, out)
+        pipe.drain()                                # every `out` is complete after this
+    """
+
+    def __init__(self, host: MoKHost):
+        if host.world != 1:
+            raise ValueError("HostPipeline drives a single-rank session")
+        self.host, dev = host, host.device
+        L, H, k = host.shape.tokens, host.shape.hidden, host.shape.topk
+        self.copy_in, self.copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self.x = [torch.empty((L, H), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.routes = [torch.empty((1, L, k), dtype=torch.int32, device=dev) for _ in range(2)]
+        self.router = [torch.empty((L, k), dtype=torch.float32, device=dev) for _ in range(2)]
+        self.out = [torch.empty((L, H), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.in_ready = [torch.cuda.Event() for _ in range(2)]      # inputs of a slot have landed
+        self.in_free = [torch.cuda.Event() for _ in range(2)]       # compute has consumed a slot's inputs
+        self.out_ready = [torch.cuda.Event() for _ in range(2)]     # compute has filled a slot's result
+        self.out_free = [torch.cuda.Event() for _ in range(2)]      # a slot's result has left the device
+        self.step = 0
+
+    def submit(self, h_x, h_routes, h_router, h_out):
+        host, i = self.host, self.step % 2
+        compute = torch.cuda.current_stream()
+        with torch.cuda.stream(self.copy_in):
+            if self.step >= 2:
+                self.copy_in.wait_event(self.in_free[i])
+            self.x[i].copy_(h_x, non_blocking=True)
+            self.routes[i].copy_(h_routes.reshape(self.routes[i].shape), non_blocking=True)
+            self.router[i].copy_(h_router, non_blocking=True)
+            self.in_ready[i].record(self.copy_in)
+        compute.wait_event(self.in_ready[i])
+        host.x_buffer.copy_(self.x[i])
+        host.router_weight_buffer.copy_(self.router[i])
+        host.schedule_into(self.routes[i])
+        self.in_free[i].record(compute)
+        host.megakernel()
+        result = host.fwd_epilogue()
+        if self.step >= 2:
+            compute.wait_event(self.out_free[i])
+        self.out[i].copy_(result)
+        self.out_ready[i].record(compute)
+        with torch.cuda.stream(self.copy_out):
+            self.copy_out.wait_event(self.out_ready[i])
+            h_out.copy_(self.out[i], non_blocking=True)
+            self.out_free[i].record(self.copy_out)
+        self.step += 1
+
+    def drain(self):
+        self.copy_out.synchronize()
+        torch.cuda.current_stream().synchronize()

@@ -336,3 +336,28 @@ def test_forward_is_deterministic(mok):
     b = host.forward(inputs)["output"].clone()
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
     assert torch.equal(h1, host.buffers["hidden_routed_fp8"])
+
+
+def test_host_pipeline_equals_the_plain_forward(native_lib):
+    """Three different batches in flight through the three-stream host pipeline give, bit for bit,
+    what one forward per batch gives."""
+    from pipelink_b200 import mok
+    mok.set_gemm_variant(2)
+    shape = mok.Shape("pipe", 8, 512, 256, 2, 640)
+    torch.manual_seed(2)
+    E, H, I = shape.experts, shape.hidden, shape.intermediate
+    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.05).to(torch.bfloat16)
+    host = mok.MoKHost(shape)
+    host.load_weights(mk(E, I, H), mk(E, I, H), mk(E, H, I))
+    batches = [mok.MoKHost.new_inputs(shape, g, "cuda") for g in (1, 2, 3, 4, 5)]
+    want = [host.forward(b)["output"].clone().cpu() for b in batches]
+    pin = lambda t: t.cpu().pin_memory()
+    h_in = [(pin(b.x), pin(b.experts.to(torch.int32)), pin(b.router)) for b in batches]
+    h_out = [torch.full((shape.tokens, H), float("nan"), dtype=torch.bfloat16).pin_memory() for _ in batches]
+    pipe = host.host_pipeline()
+    for (x, r, w), o in zip(h_in, h_out):
+        pipe.submit(x, r, w, o)
+    pipe.drain()
+    host.status.check("host pipeline")
+    for i, (o, w) in enumerate(zip(h_out, want)):
+        assert torch.equal(o.view(torch.int16), w.view(torch.int16)), i
