@@ -339,10 +339,15 @@ typedef struct plb_attn_work {
   int32_t reserved;
 } plb_attn_work;
 /* heads_per_work: 1 = one record per head; 2 = one record per pair of heads (head, head + 1) that
- * share a KV head (q_heads / kv_heads must be even, head even): K / V are fetched once for both. */
+ * share a KV head (q_heads / kv_heads must be even, head even): K / V are fetched once for both.
+ * window > 0: sliding-window mask on top of the causal one, key visible iff kv_pos > q_pos - window
+ * (campaigns/attention/src/sm90/stage_mask_window.cu:8-11); the work list should then start each
+ * tile at the first block that holds a visible key. softcap > 0: the scaled score becomes
+ * softcap * tanh(score * scale / softcap) (campaigns/attention/src/sm90/stage_score_softcap.cu:10-13,
+ * family_params.cuh:112-113). 0 switches either off. */
 int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
                       const plb_attn_work* work, int num_work, int heads_per_work, int q_heads, int kv_heads, int seq_q,
-                      uint64_t q_rows, uint64_t kv_rows, float scale, const uint32_t* ready,
+                      uint64_t q_rows, uint64_t kv_rows, float scale, int window, float softcap, const uint32_t* ready,
                       uint32_t ready_target, plb_status* status, void* stream);
 
 /* Context-parallel K/V exchange (kv_gather_role_gather, campaigns/attention/src/sm90/stage_kv_gather.cu:16-78):

@@ -51,9 +51,12 @@ def philox_bf16(count: int, numeric_case: int, role: int) -> np.ndarray:
     return bf16_round((-2.0 + 4.0 * u).astype(np.float32))
 
 
-def reference_rows(q, k, v, rows, scale, q_pos=None):
+def reference_rows(q, k, v, rows, scale, q_pos=None, window=0, softcap=0.0):
     """q [Sq, Hq, D], k/v [Sk, Hkv, D] fp32; rows = query rows to evaluate; q_pos[r] = global
-    position of query r (defaults to r). Returns (out [len(rows), Hq, D], lse [Hq, len(rows)])."""
+    position of query r (defaults to r). Returns (out [len(rows), Hq, D], lse [Hq, len(rows)]).
+    window > 0 keeps keys with kv_pos > q_pos - window (campaigns/attention/src/sm90/stage_mask_window.cu:8-11);
+    softcap > 0 replaces the scaled score by softcap * tanh(score / softcap)
+    (stage_score_softcap.cu:10-13 with family_params.cuh:112-113)."""
     Sq, Hq, D = q.shape
     Hkv = k.shape[1]
     g = Hq // Hkv
@@ -62,10 +65,13 @@ def reference_rows(q, k, v, rows, scale, q_pos=None):
     for i, r in enumerate(rows):
         pos = r if q_pos is None else int(q_pos[r])
         for h in range(Hq):
-            s = (k[: pos + 1, h // g].astype(np.float64) @ q[r, h].astype(np.float64)) * scale
+            first = max(0, pos - window + 1) if window > 0 else 0
+            s = (k[first: pos + 1, h // g].astype(np.float64) @ q[r, h].astype(np.float64)) * scale
+            if softcap > 0:
+                s = softcap * np.tanh(s / softcap)
             m = s.max()
             p = np.exp(s - m)
-            out[i, h] = (p @ v[: pos + 1, h // g].astype(np.float64)) / p.sum()
+            out[i, h] = (p @ v[first: pos + 1, h // g].astype(np.float64)) / p.sum()
             lse[h, i] = m + math.log(p.sum())
     return out, lse
 

@@ -14,6 +14,7 @@ kernels on one GPU wait on each other.
 from __future__ import annotations
 
 import ctypes
+import functools
 import math
 
 import numpy as np
@@ -31,14 +32,22 @@ def heads_per_work(q_heads: int, kv_heads: int) -> int:
     return 2 if (q_heads // kv_heads) % 2 == 0 else 1
 
 
-def causal_work(batch: int, seq: int, q_heads: int, step: int = 1) -> np.ndarray:
+@functools.lru_cache(maxsize=64)
+def _device_work(batch, seq, q_heads, step, window, device):
+    return torch.from_numpy(causal_work(batch, seq, q_heads, step, window)).to(device)
+
+
+def causal_work(batch: int, seq: int, q_heads: int, step: int = 1, window: int = 0) -> np.ndarray:
     """i32 [n, 8]: (q_row0, q_pos0, kv_row0, kv_pos0, kv_blocks, head, batch, 0), longest tiles first;
-    one record per `step` consecutive heads."""
+    one record per `step` consecutive heads. With a sliding window a tile starts at the block that
+    holds the oldest key its first query still sees."""
     rows = []
     for qb in range(seq // BLK - 1, -1, -1):
+        first = max(0, (qb * BLK - window + 1) // BLK) if window > 0 else 0
         for b in range(batch):
             for h in range(0, q_heads, step):
-                rows.append((b * seq + qb * BLK, qb * BLK, b * seq, 0, qb + 1, h, b, 0))
+                rows.append((b * seq + qb * BLK, qb * BLK, b * seq + first * BLK, first * BLK, qb + 1 - first, h, b, 0))
+    rows.sort(key=lambda r: -r[4])
     return np.asarray(rows, dtype=np.int32).reshape(-1, 8)
 
 
@@ -58,17 +67,21 @@ def zigzag_work(seq: int, world: int, rank: int, q_heads: int, step: int = 1) ->
     return np.asarray(rows, dtype=np.int32).reshape(-1, 8)
 
 
-def _launch(q, k, v, out, lse, work, step, seq_q, ready, ready_target, status):
+def _launch(q, k, v, out, lse, work, step, seq_q, ready, ready_target, status, window=0, softcap=0.0):
     q_rows, q_heads = q.shape[0], q.shape[1]
     kv_rows, kv_heads = k.shape[0], k.shape[1]
     _lib.call("plb_attention_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
               work.data_ptr(), work.shape[0], step, q_heads, kv_heads, seq_q, q_rows, kv_rows, 1.0 / math.sqrt(D),
-              0 if ready is None else ready.data_ptr(), ready_target, status.buf.data_ptr(), _stream())
+              int(window), float(softcap), 0 if ready is None else ready.data_ptr(), ready_target, status.buf.data_ptr(),
+              _stream())
 
 
-def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, check: bool = True, pair_heads: bool | None = None):
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, check: bool = True, pair_heads: bool | None = None,
+                  window: int = 0, softcap: float = 0.0):
     """q [B, S, Hq, 128], k / v [B, S, Hkv, 128] bf16 CUDA. Returns (O like q, LSE f32 [B*Hq, S]).
-    `pair_heads` None picks the two-heads-per-CTA kernel whenever Hq / Hkv is even."""
+    `pair_heads` None picks the two-heads-per-CTA kernel whenever Hq / Hkv is even. `window` > 0 adds
+    the sliding-window mask (a query sees its last `window` keys), `softcap` > 0 the tanh soft cap
+    on the scaled scores; both are the reference's mask / score stage variants."""
     B, S, Hq, d = q.shape
     if d != D or S % BLK or q.dtype != torch.bfloat16:
         raise ValueError("attention_fwd wants bf16, head_dim 128 and a sequence that is a multiple of 128")
@@ -76,10 +89,10 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, check: b
     out = torch.empty_like(q)
     lse = torch.empty((B * Hq, S), dtype=torch.float32, device=q.device)
     step = heads_per_work(Hq, Hkv) if pair_heads is None else (2 if pair_heads else 1)
-    work = torch.from_numpy(causal_work(B, S, Hq, step)).to(q.device)
+    work = _device_work(B, S, Hq, step, window, q.device)   # built once per shape and device
     status = DeviceStatus(q.device)
     _launch(q.reshape(B * S, Hq, D), k.reshape(B * S, Hkv, D), v.reshape(B * S, Hkv, D), out.reshape(B * S, Hq, D),
-            lse, work, step, S, None, 0, status)
+            lse, work, step, S, None, 0, status, window, softcap)
     if check:
         status.check("attention_fwd")
     return out, lse

@@ -63,7 +63,20 @@ __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
   return v;
 }
 
-template <bool kUseCounters>
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Raw score q.k -> score in the base-2 softmax domain. Plain: s * scale * log2(e). With a soft cap c
+// (score_softcap_score_mod, campaigns/attention/src/sm90/stage_score_softcap.cu:10-13): the scaled
+// score becomes c * tanh(s * scale / c); cap_in = scale / c, cap_out = c * log2(e).
+template <bool kSoftcap>
+__device__ __forceinline__ float score_log2(float s, const AttnParams& p) {
+  return kSoftcap ? p.cap_out * tanh_approx(s * p.cap_in) : s * p.scale_log2;
+}
+
+template <bool kUseCounters, bool kSoftcap>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -251,7 +264,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tc_fence_after();
         // pass 1 over the 128 scores of this row: block maximum (scaled, causal mask applied)
         const int key0 = wk.kv_pos0 + j * kBlk;
-        const bool diag = key0 + kBlk - 1 > q_pos;
+        // visible keys of the row inside this block: [lo, hi); the sliding window keeps
+        // kv_pos > q_pos - window (mask_window_mask_mod, campaigns/attention/src/sm90/stage_mask_window.cu:8-11)
+        const int hi = q_pos - key0 + 1;
+        const int lo = p.window > 0 ? q_pos - p.window + 1 - key0 : 0;
+        const bool diag = hi < kBlk || lo > 0;
         float bm = m;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -260,8 +277,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float sv = __uint_as_float(v[i]) * p.scale_log2;
-            if (!diag || key0 + c * 32 + i <= q_pos) bm = fmaxf(bm, sv);
+            const float sv = score_log2<kSoftcap>(__uint_as_float(v[i]), p);
+            if (!diag || (c * 32 + i < hi && c * 32 + i >= lo)) bm = fmaxf(bm, sv);
           }
         }
         const float alpha = m == -INFINITY ? 0.0f : exp2f(m - bm);
@@ -282,8 +299,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           for (int i = 0; i < 32; i += 2) {
             float p0 = 0.0f, p1 = 0.0f;
             if (bm != -INFINITY) {
-              if (!diag || key0 + c * 32 + i <= q_pos) p0 = exp2f(__uint_as_float(v[i]) * p.scale_log2 - bm);
-              if (!diag || key0 + c * 32 + i + 1 <= q_pos) p1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - bm);
+              if (!diag || (c * 32 + i < hi && c * 32 + i >= lo)) p0 = exp2f(score_log2<kSoftcap>(__uint_as_float(v[i]), p) - bm);
+              if (!diag || (c * 32 + i + 1 < hi && c * 32 + i + 1 >= lo)) p1 = exp2f(score_log2<kSoftcap>(__uint_as_float(v[i + 1]), p) - bm);
             }
             __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
             sum += __bfloat162float(t.x) + __bfloat162float(t.y);
@@ -394,7 +411,7 @@ struct PairBars {
 };
 static_assert(sizeof(PairBars) <= 256, "barrier block");
 
-template <bool kUseCounters>
+template <bool kUseCounters, bool kSoftcap>
 __global__ void __launch_bounds__(kPairThreads, 1)
 attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                           const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -587,8 +604,10 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         if (!ok) break;
         tc_fence_after();
         const int key0 = wk.kv_pos0 + j * kBlk;
-        const int valid = q_pos - key0 + 1;  // keys [0, valid) of this block are visible to the row
-        const bool diag = key0 + kBlk - 1 > wk.q_pos0;  // uniform per block: some row is masked
+        const int valid = q_pos - key0 + 1;  // keys [lo, valid) of this block are visible to the row
+        const int lo = p.window > 0 ? q_pos - p.window + 1 - key0 : 0;
+        // uniform per block: some row of the tile is masked (causal edge or the window's lower edge)
+        const bool diag = key0 + kBlk - 1 > wk.q_pos0 || (p.window > 0 && wk.q_pos0 + kBlk - 1 - p.window + 1 > key0);
         float bm = -INFINITY;
         {
           // pass 1: block maximum of the raw scores, two 32-column chunks in flight
@@ -602,8 +621,8 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             if (diag) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                if (h * 64 + i < valid) b0 = fmaxf(b0, __uint_as_float(a[i]));
-                if (h * 64 + 32 + i < valid) b1 = fmaxf(b1, __uint_as_float(b[i]));
+                if (h * 64 + i < valid && h * 64 + i >= lo) b0 = fmaxf(b0, __uint_as_float(a[i]));
+                if (h * 64 + 32 + i < valid && h * 64 + 32 + i >= lo) b1 = fmaxf(b1, __uint_as_float(b[i]));
               }
             } else {
 #pragma unroll
@@ -615,7 +634,7 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           }
           bm = fmaxf(b0, b1);
         }
-        bm *= scale;  // scale > 0
+        bm = bm == -INFINITY ? bm : score_log2<kSoftcap>(bm, p);  // monotonic: the maximum of the scores is the score of the maximum
         const float m_new = fmaxf(m_ref, bm);
         const bool need = m_new > m_ref && (m_ref == -INFINITY || m_new - m_ref > kRescaleThreshold);
         if (__any_sync(0xFFFFFFFFu, need)) {
@@ -648,15 +667,23 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float a0 = ex2_approx(fmaf(__uint_as_float(a[i]), scale, -m_use));
-            float a1 = ex2_approx(fmaf(__uint_as_float(a[i + 1]), scale, -m_use));
-            float c0 = ex2_approx(fmaf(__uint_as_float(b[i]), scale, -m_use));
-            float c1 = ex2_approx(fmaf(__uint_as_float(b[i + 1]), scale, -m_use));
+            float a0, a1, c0, c1;
+            if (kSoftcap) {
+              a0 = ex2_approx(score_log2<true>(__uint_as_float(a[i]), p) - m_use);
+              a1 = ex2_approx(score_log2<true>(__uint_as_float(a[i + 1]), p) - m_use);
+              c0 = ex2_approx(score_log2<true>(__uint_as_float(b[i]), p) - m_use);
+              c1 = ex2_approx(score_log2<true>(__uint_as_float(b[i + 1]), p) - m_use);
+            } else {
+              a0 = ex2_approx(fmaf(__uint_as_float(a[i]), scale, -m_use));
+              a1 = ex2_approx(fmaf(__uint_as_float(a[i + 1]), scale, -m_use));
+              c0 = ex2_approx(fmaf(__uint_as_float(b[i]), scale, -m_use));
+              c1 = ex2_approx(fmaf(__uint_as_float(b[i + 1]), scale, -m_use));
+            }
             if (decltype(masked)::value) {
-              if (h * 64 + i >= valid) a0 = 0.0f;
-              if (h * 64 + i + 1 >= valid) a1 = 0.0f;
-              if (h * 64 + 32 + i >= valid) c0 = 0.0f;
-              if (h * 64 + 32 + i + 1 >= valid) c1 = 0.0f;
+              if (h * 64 + i >= valid || h * 64 + i < lo) a0 = 0.0f;
+              if (h * 64 + i + 1 >= valid || h * 64 + i + 1 < lo) a1 = 0.0f;
+              if (h * 64 + 32 + i >= valid || h * 64 + 32 + i < lo) c0 = 0.0f;
+              if (h * 64 + 32 + i + 1 >= valid || h * 64 + 32 + i + 1 < lo) c1 = 0.0f;
             }
             sum0 += a0 + a1;
             sum1 += c0 + c1;
@@ -767,14 +794,20 @@ cudaError_t launch_attention_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.status = a.status;
   int grid = a.num_sms < a.num_work ? a.num_sms : a.num_work;
   cudaError_t err;
+  p.window = a.window;
+  p.cap_in = a.softcap > 0.0f ? a.scale / a.softcap : 0.0f;
+  p.cap_out = a.softcap * 1.4426950408889634f;
+  const bool counters = a.ready != nullptr, cap = a.softcap > 0.0f;
   if (a.heads_per_work == 2) {
     if (p.q_per_kv % 2 != 0) return cudaErrorInvalidValue;
-    auto kern = a.ready != nullptr ? attention_fwd_pair_kernel<true> : attention_fwd_pair_kernel<false>;
+    auto kern = counters ? (cap ? attention_fwd_pair_kernel<true, true> : attention_fwd_pair_kernel<true, false>)
+                         : (cap ? attention_fwd_pair_kernel<false, true> : attention_fwd_pair_kernel<false, false>);
     err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
     if (err != cudaSuccess) return err;
     kern<<<grid, kPairThreads, kPairSmem, stream>>>(mq, mk, mv, p);
   } else {
-    auto kern = a.ready != nullptr ? attention_fwd_kernel<true> : attention_fwd_kernel<false>;
+    auto kern = counters ? (cap ? attention_fwd_kernel<true, true> : attention_fwd_kernel<true, false>)
+                         : (cap ? attention_fwd_kernel<false, true> : attention_fwd_kernel<false, false>);
     err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
     if (err != cudaSuccess) return err;
     kern<<<grid, kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, p);

@@ -28,6 +28,8 @@ struct AttnParams {
   __nv_bfloat16* out;
   float* lse;
   float scale_log2;
+  float cap_in, cap_out;  // soft cap: score = cap_out * tanh(s * cap_in) in the base-2 domain (unused without a cap)
+  int window;             // sliding window: keys with kv_pos > q_pos - window are visible; 0 = none
   unsigned ready_target;
   const unsigned* ready;  // per 128-key block readiness counters (context parallel), or null
   Status* status;
@@ -46,6 +48,8 @@ struct AttnArgs {
   int seq_q;
   uint64_t q_rows, kv_rows;
   float scale;
+  float softcap;          // 0 = none
+  int window;             // 0 = none
   const unsigned* ready;
   unsigned ready_target;
   int num_sms;

@@ -509,7 +509,7 @@ int plb_ep_gather_rows(const void* const* src_peers, const int32_t* peer_rank, c
 
 int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
                       const plb_attn_work* work, int num_work, int heads_per_work, int q_heads, int kv_heads, int seq_q,
-                      uint64_t q_rows, uint64_t kv_rows, float scale, const uint32_t* ready,
+                      uint64_t q_rows, uint64_t kv_rows, float scale, int window, float softcap, const uint32_t* ready,
                       uint32_t ready_target, plb_status* status, void* stream) {
   static_assert(sizeof(plb_attn_work) == sizeof(plb::AttnWork), "work descriptor layouts differ");
   if (!q || !k || !v || !out || !lse || !work || !status || num_work < 0) return PLB_E_ARGUMENT;
@@ -525,7 +525,10 @@ int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, fl
   a.num_work = num_work;
   a.q_heads = q_heads; a.kv_heads = kv_heads; a.seq_q = seq_q;
   a.q_rows = q_rows; a.kv_rows = kv_rows;
+  if (window < 0 || softcap < 0.0f) return PLB_E_ARGUMENT;
   a.scale = scale;
+  a.window = window;
+  a.softcap = softcap;
   a.ready = ready; a.ready_target = ready_target;
   a.num_sms = sm_count();
   a.status = reinterpret_cast<plb::Status*>(status);

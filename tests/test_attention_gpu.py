@@ -59,6 +59,28 @@ def test_attention_growing_scores_both_kernels(native_lib, pair):
     assert oa.matches(got_lse, ref_lse) == 0, np.abs(got_lse - ref_lse).max()
 
 
+@pytest.mark.parametrize("Hq,Hkv,window,softcap", [(4, 2, 200, 0.0), (4, 2, 128, 0.0), (4, 4, 1000, 0.0), (4, 2, 0, 30.0),
+                                                    (2, 2, 0, 8.0), (8, 2, 300, 20.0)])
+def test_window_and_softcap_variants_vs_oracle(native_lib, Hq, Hkv, window, softcap):
+    """The reference's mask-window and score-softcap stage variants on both kernels (two heads per
+    CTA when Hq / Hkv is even, one otherwise): rows around every block and window edge."""
+    from pipelink_b200 import attention as att
+    S = 1536
+    (q, k, v), (dq, dk, dv) = _inputs(S, Hq, Hkv, case=window + int(softcap))
+    out, lse = att.attention_fwd(dq[None], dk[None], dv[None], window=window, softcap=softcap)
+    torch.cuda.synchronize()
+    extra = [S // 2 + 3, S - 130]
+    if window:
+        extra += [window - 1, window, window + 1, 2 * window + 5, 127 + window, 128 + window, S - 1]
+    sel = sorted({r for r in oa.boundary_rows(S, extra=tuple(e for e in extra if 0 <= e < S))})
+    ref_o, ref_lse = oa.reference_rows(q, k, v, sel, 1.0 / np.sqrt(128.0), window=window, softcap=softcap)
+    got_o = out[0].float().cpu().numpy()[sel]
+    got_lse = lse.cpu().numpy()[:, sel]
+    assert np.isfinite(got_o).all()
+    assert oa.matches(got_o, ref_o) == 0, np.abs(got_o - ref_o).max()
+    assert oa.matches(got_lse, ref_lse) == 0, np.abs(got_lse - ref_lse).max()
+
+
 def test_attention_deterministic(native_lib):
     from pipelink_b200 import attention as att
     _, (dq, dk, dv) = _inputs(1024, 8, 2, case=7)
