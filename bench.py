@@ -157,12 +157,14 @@ def run_reference(args):
         return
     from pipelink_b200 import mok
     shape = mok.CONFIG2
-    base, sec = cpu_sample(shape.hidden, shape.intermediate, steps=max(1, min(args.steps, 3)),
-                           warmup=min(args.warmup, 1))
+    # every pass is tens of seconds of host work, so at most three passes are timed (and one warm-up
+    # pass run) however large --steps is; `sample_passes` says how many
+    passes = max(1, min(args.steps, 3))
+    base, sec = cpu_sample(shape.hidden, shape.intermediate, steps=passes, warmup=min(args.warmup, 1))
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU port of the e4m3/ue8m0 path)",
-            "data": "synthetic", "config": {"workload": shape.name, "sample": base["sample"]},
+            "data": "synthetic", "config": {"workload": shape.name, "sample": base["sample"], "sample_passes": passes},
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
