@@ -78,3 +78,39 @@ def test_zigzag_work_tiles_the_causal_triangle(world, seq):
         # zigzag balances the causal work: every rank visits the same number of KV blocks
         assert per_rank == (seq // 128) * (seq // 128 + 1) // 2 // world
     assert (covered == 1).all() and total_blocks == (seq // 128) * (seq // 128 + 1) // 2
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_slab_layout_regions_do_not_overlap(world):
+    """Peer-visible regions of one rank's symmetric slab (forward and training) are 256-byte
+    aligned, disjoint and inside the allocation."""
+    from pipelink_b200 import ep, mok
+    shape = mok.Shape("slab", 64, 4096, 2048, 8, 1024)
+    for train in (False, True):
+        lay = ep.SlabLayout(shape, world, train)
+        L, H, k = shape.tokens, shape.hidden, shape.topk
+        regions = [("flags", lay.flags, 4 * 32), ("xq", lay.xq, L * H), ("xsc", lay.xsc, L // 128 * (H // 128) * 512),
+                   ("routes_all", lay.routes_all, world * L * k * 4), ("combine", lay.combine, L * k * H * 2)]
+        if train:
+            regions += [("x_bf16", lay.x_bf16, L * H * 2), ("d_out", lay.d_out, L * H * 2),
+                        ("router_w", lay.router_w, L * k * 4), ("d_x_rows", lay.d_x_rows, L * k * H * 2)]
+        regions.sort(key=lambda r: r[1])
+        for (name, off, size), nxt in zip(regions, regions[1:] + [("end", lay.nbytes, 0)]):
+            assert off % 256 == 0, name
+            assert off + size <= nxt[1], (name, nxt[0])
+
+
+def test_push_rotation_separates_the_ranks():
+    """Rows are ordered by (expert, source rank). With the rotation every rank starts its pushing
+    GEMM at a different source-rank block, so at equal progress no two ranks address the same home
+    rank (balanced routing: a block is L * k / E rows)."""
+    L, k, E, world = 8192, 8, 64, 8
+    block_tiles = max(1, (L * k // E) // 256)
+    tiles_per_expert = block_tiles * world
+    for step in range(0, tiles_per_expert * 2, block_tiles):
+        homes = set()
+        for rank in range(world):
+            rot = rank * block_tiles                     # ep.EpMoKHost.push_rotation
+            tile = (step + rot) % tiles_per_expert       # position inside an expert's segment
+            homes.add(tile // block_tiles)               # source (= home) rank of that block
+        assert len(homes) == world
