@@ -114,3 +114,38 @@ def test_push_rotation_separates_the_ranks():
             tile = (step + rot) % tiles_per_expert       # position inside an expert's segment
             homes.add(tile // block_tiles)               # source (= home) rank of that block
         assert len(homes) == world
+
+
+def _bootstrap_with_a_missing_rank(rank, world, port, tmp):
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    from pipelink_b200 import ep
+    outcome = "left"
+    if rank == 0:
+        # rank 1 leaves before the handle exchange: the bootstrap must end with an error on the host,
+        # well before any kernel could wait on a peer that is not there
+        try:
+            ep.exchange_handles(bytes([rank]) * 64, world)
+            outcome = "completed"
+        except Exception as e:   # gloo reports the lost peer or the timeout
+            outcome = "error:" + type(e).__name__
+    with open(os.path.join(tmp, f"outcome{rank}.txt"), "w") as f:
+        f.write(outcome)
+    if rank == 0:
+        os._exit(0)     # the group is broken; skip the collective teardown
+
+
+def test_bootstrap_fails_on_the_host_when_a_rank_never_joins(tmp_path):
+    """Failure made on the host: one rank exits before contributing its IPC handle."""
+    world, port = 2, _free_port()
+    ctx = mp.spawn(_bootstrap_with_a_missing_rank, args=(world, port, str(tmp_path)), nprocs=world, join=False)
+    ctx.join(timeout=60)
+    assert (tmp_path / "outcome1.txt").read_text() == "left"
+    assert (tmp_path / "outcome0.txt").read_text().startswith("error:")
+
+
+def test_exchange_rejects_a_malformed_handle():
+    from pipelink_b200 import ep
+    with pytest.raises(ValueError):
+        ep.exchange_handles(b"short", 2)
