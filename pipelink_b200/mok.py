@@ -313,11 +313,18 @@ class MoKHost:
                   self.schedule.expert_offsets.data_ptr(), self.capacity, self.num_local_experts, m_rows, n_rows,
                   out.data_ptr(), self.status.buf.data_ptr(), _stream())
 
-    def backward(self, d_out: torch.Tensor, *, check: bool = True):
+    def backward(self, d_out: torch.Tensor, *, check: bool = True, recompute: bool = False):
         """Backward of the last ``forward(train=True)`` (single rank). Returns the gradients the
         reference reports (GRAD_NAMES, mok_port_host.py:29-30, routed part): d_x, d_router_weights,
-        d_w_routed_gate / up / down."""
+        d_w_routed_gate / up / down. ``recompute=True`` is the reference's recompute pass
+        (campaigns/mok/port/framework/interp_rec.cu): the forward was a plain ``forward(inputs)`` that
+        kept only what inference keeps, and the gate / up / hidden activations are produced again
+        from the routed tokens before the gradients are taken."""
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        if recompute:
+            if "w_down_t_fp8" not in self.weights:
+                raise RuntimeError("load_weights(..., train=True) first")
+            self.gemm_gate_up_train()
         P, H, I, k = self.capacity, sh.hidden, sh.intermediate, sh.topk
         nt = s.num_tokens.data_ptr()
         # combine backward + router-weight gradient

@@ -56,3 +56,28 @@ def test_backward_vs_oracle(native_lib, shape_args, generation):
     empty = np.nonzero(ref_f["schedule"]["tokens_per_expert"] == 0)[0]
     for e in empty:
         assert not _f(grads["d_w_routed_down"][e]).any() and not _f(grads["d_w_routed_gate"][e]).any()
+
+
+def test_recompute_pass_gives_the_same_gradients(native_lib):
+    """A plain forward followed by backward(recompute=True) equals forward(train=True) + backward bit
+    for bit: the recompute pass regenerates exactly the saved activations."""
+    from pipelink_b200 import mok
+    mok.set_gemm_variant(2)
+    shape = mok.Shape("rec", 8, 512, 256, 2, 384)
+    torch.manual_seed(9)
+    E, H, I = shape.experts, shape.hidden, shape.intermediate
+    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.05).to(torch.bfloat16)
+    host = mok.MoKHost(shape)
+    host.load_weights(mk(E, I, H), mk(E, I, H), mk(E, H, I), train=True)
+    inputs = mok.MoKHost.new_inputs(shape, 2, "cuda")
+    d_out = torch.randn(shape.tokens, H, device="cuda").to(torch.bfloat16)
+    host.forward(inputs, train=True)
+    want = {k: v.clone() for k, v in host.backward(d_out).items()}
+    for name in ("gate_routed_fp8", "up_routed_fp8", "hidden_routed_bf16"):
+        host.buffers[name].zero_()                      # nothing may survive from the training forward
+    host.forward(inputs)
+    got = host.backward(d_out, recompute=True)
+    for name, w in want.items():
+        g = got[name]
+        view = torch.int16 if g.dtype == torch.bfloat16 else torch.int32
+        assert torch.equal(g.contiguous().view(view), w.contiguous().view(view)), name
