@@ -185,9 +185,6 @@ def run_native(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # NCCL prints its version banner on stdout at this level; stdout carries the one JSON line
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
 
     pk = peaks()
@@ -556,10 +553,17 @@ class SingleRank:
 
 def main():
     args = parse()
+    # stdout carries the one JSON line and nothing else: libraries that write to file descriptor 1
+    # (NCCL's version banner, for one) are sent to stderr while the benchmark runs
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
     if args.impl == "reference":
         run_reference(args)
     else:
         run_native(args)
+    sys.stdout.flush()
 
 
 if __name__ == "__main__":

@@ -415,18 +415,67 @@ class BenchSession:
         return None
 
     def e2e(self, steps):
-        h = self.host
+        """Pinned host buffers in and out every step through EpHostPipeline; device-timed from the
+        first submit to the last result leaving the device."""
+        pipe = EpHostPipeline(self.host)
+        outs = [self.h_out, torch.empty_like(self.h_out).pin_memory()]
+        for i in range(2):
+            pipe.submit(self.h_x, self.h_routes, self.h_router, outs[i % 2])
+        pipe.drain()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
         a.record()
-        for _ in range(steps):
-            h.x_buffer.copy_(self.h_x, non_blocking=True)
-            h.routes_local.copy_(self.h_routes, non_blocking=True)
-            h.router_weight_buffer.copy_(self.h_router, non_blocking=True)
-            out = h.device_step()
-            self.h_out.copy_(out, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-        b.record()
-        torch.cuda.synchronize()
+        for i in range(steps):
+            pipe.submit(self.h_x, self.h_routes, self.h_router, outs[i % 2])
+        b.record(pipe.copy_out)
+        pipe.drain()
+        self.host.status.check("bench (EP e2e)")
         h2d = self.h_x.numel() * 2 + self.h_routes.numel() * 4 + self.h_router.numel() * 4
         return a.elapsed_time(b) / steps, h2d, self.h_out.numel() * 2
+
+
+class EpHostPipeline:
+    """mok.HostPipeline for one rank of a distributed group: inputs of step i+1 travel host -> device
+    and the result of step i-1 device -> host on side streams while step i (with its group barriers)
+    runs on the current stream. Every rank must submit the same number of steps."""
+
+    def __init__(self, host: EpMoKHost):
+        self.host, dev = host, host.device
+        L, H, k = host.shape.tokens, host.shape.hidden, host.shape.topk
+        self.copy_in, self.copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self.x = [torch.empty((L, H), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.routes = [torch.empty((L, k), dtype=torch.int32, device=dev) for _ in range(2)]
+        self.router = [torch.empty((L, k), dtype=torch.float32, device=dev) for _ in range(2)]
+        self.out = [torch.empty((L, H), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        ev = lambda: [torch.cuda.Event() for _ in range(2)]
+        self.in_ready, self.in_free, self.out_ready, self.out_free = ev(), ev(), ev(), ev()
+        self.step = 0
+
+    def submit(self, h_x, h_routes, h_router, h_out):
+        host, i = self.host, self.step % 2
+        compute = torch.cuda.current_stream()
+        with torch.cuda.stream(self.copy_in):
+            if self.step >= 2:
+                self.copy_in.wait_event(self.in_free[i])
+            self.x[i].copy_(h_x, non_blocking=True)
+            self.routes[i].copy_(h_routes, non_blocking=True)
+            self.router[i].copy_(h_router, non_blocking=True)
+            self.in_ready[i].record(self.copy_in)
+        compute.wait_event(self.in_ready[i])
+        host.x_buffer.copy_(self.x[i])
+        host.routes_local.copy_(self.routes[i])
+        host.router_weight_buffer.copy_(self.router[i])
+        self.in_free[i].record(compute)
+        result = host.device_step()
+        if self.step >= 2:
+            compute.wait_event(self.out_free[i])
+        self.out[i].copy_(result)
+        self.out_ready[i].record(compute)
+        with torch.cuda.stream(self.copy_out):
+            self.copy_out.wait_event(self.out_ready[i])
+            h_out.copy_(self.out[i], non_blocking=True)
+            self.out_free[i].record(self.copy_out)
+        self.step += 1
+
+    def drain(self):
+        self.copy_out.synchronize()
+        torch.cuda.current_stream().synchronize()

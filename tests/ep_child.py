@@ -41,6 +41,18 @@ def main():
                                       padding=mok.expert_padding())
         s = omoe.error_stats(ref["outputs"][rank], out)
         assert np.isfinite(out).all() and s["relative"] <= 2e-2, (rank, generation, s)
+    # ---- host pipeline: three batches in flight give what one forward per batch gives
+    batches = [mok.MoKHost.new_inputs(shape, g, dev, rank=rank, world=world) for g in (1, 2, 3)]
+    want = [host.forward(b)["output"].clone().cpu() for b in batches]
+    pin = lambda t: t.cpu().pin_memory()
+    h_out = [torch.full((shape.tokens, H), float("nan"), dtype=torch.bfloat16).pin_memory() for _ in batches]
+    pipe = ep.EpHostPipeline(host)
+    for b, o in zip(batches, h_out):
+        pipe.submit(pin(b.x), pin(b.experts.to(torch.int32)), pin(b.router), o)
+    pipe.drain()
+    host.status.check("EP host pipeline")
+    for i, (o, w) in enumerate(zip(h_out, want)):
+        assert torch.equal(o.view(torch.int16), w.view(torch.int16)), (rank, "pipeline", i)
     torch.cuda.synchronize()
     dist.barrier()
     group.close()
