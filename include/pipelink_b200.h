@@ -63,6 +63,14 @@ int plb_last_cuda_error(void);
 int plb_moe_set_gemm_variant(int variant);
 int plb_moe_gemm_variant(void);
 int plb_moe_tile_rows(void);
+/* Clamped SwiGLU, process-wide like the tiling variant (the reference selects it per link through
+ * the variant handle pipelink_mok_clamp, campaigns/mok/port/act/act.cu:9,246-249, and carries the
+ * bound as the scalar mok.clamp, act.cu:294): limit > 0 makes the gate/up epilogue compute
+ * silu(min(gate, limit)) * clamp(up, -limit, limit) and plb_moe_swiglu_bwd pass no gradient
+ * through a bound that is reached (campaigns/mok/port/act_gptoss/swiglu.cuh:13-37); 0 (default)
+ * is the plain activation. Forward, recompute and backward calls must run under the same value. */
+int plb_moe_set_swiglu_limit(float limit);
+float plb_moe_swiglu_limit(void);
 /* Diagnostics: a device buffer of [grid, 16] int64 that profiling builds of the library
  * (-DPLB_GEMM_PROFILE) fill with per-role cycle counters; ignored by regular builds. */
 int plb_debug_set_profile_buffer(void* device_i64_grid_by_16);
@@ -265,6 +273,25 @@ int plb_moe_gemm_down_push(const void* hidden_fp8, const void* hidden_sc, const 
                            const int32_t* peer_rank, int64_t capacity, int experts, int inter,
                            int hidden, int tile_rotation, void* const* combine_peers, plb_status* status,
                            void* stream);
+
+/* bf16 routed precision (the reference's second value of the variant handle
+ * pipelink_mok_precision, campaigns/mok/port/act/act.cu:246-249; gemm stage precision variants,
+ * campaigns/mok/README.md:99-104): the gate/up and down grouped GEMMs on bf16 operands with fp32
+ * accumulation, no quantisation anywhere on the routed path. x_routed_bf16 [capacity, hidden] are
+ * the rows in schedule order (plb_moe_gather_rows / plb_ep_gather_rows); w13_bf16
+ * [experts, 2*inter, hidden] interleaves, per 256 rows, 128 gate rows then the 128 up rows of the
+ * same hidden columns; hidden_bf16 [capacity, inter] = bf16(act(bf16 gate, bf16 up)) under the
+ * current plb_moe_set_swiglu_limit. plb_moe_gemm_down_bf16 places rows like plb_moe_gemm_down
+ * (combine_bf16 set, combine_peers NULL) or pushes them like plb_moe_gemm_down_push (combine_peers
+ * and peer_rank set, combine_bf16 NULL). CTA-pair variant only (PLB_E_CONTRACT otherwise);
+ * capacity multiple of 256, inter of 128, hidden of 256. Forward pass only. */
+int plb_moe_gemm_gate_up_bf16(const void* x_routed_bf16, const void* w13_bf16, const int32_t* block_expert,
+                              const int32_t* num_tokens, int64_t capacity, int experts, int inter, int hidden,
+                              void* hidden_bf16, plb_status* status, void* stream);
+int plb_moe_gemm_down_bf16(const void* hidden_bf16, const void* w2_bf16, const int32_t* block_expert,
+                           const int32_t* num_tokens, const int32_t* dest_row, const int32_t* peer_rank,
+                           int64_t capacity, int experts, int inter, int hidden, int tile_rotation,
+                           void* combine_bf16, void* const* combine_peers, plb_status* status, void* stream);
 
 /* ops.fwd_epilogue (campaigns/mok/host/mok_port_host.py:204):
  * out[t] = y_shared[t] + sum_j router_weights[t, j] * combine[t * topk + j], j ascending,

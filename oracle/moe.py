@@ -29,8 +29,13 @@ def _mm(a: np.ndarray, b: np.ndarray) -> np.ndarray:
                         torch.from_numpy(np.ascontiguousarray(b)).T).numpy()
 
 
-def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+def silu_mul(gate: np.ndarray, up: np.ndarray, limit: float = 0.0) -> np.ndarray:
+    """silu(gate) * up; with limit > 0 the clamped variant: gate bounded from above, up from both
+    sides (campaigns/mok/port/act_gptoss/swiglu.cuh:143-147 applies the same bounds)."""
     g = gate.astype(np.float32)
+    if limit > 0:
+        g = np.minimum(g, np.float32(limit))
+        up = np.clip(up.astype(np.float32), np.float32(-limit), np.float32(limit))
     s = (g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))).astype(np.float32)
     return (s * up.astype(np.float32)).astype(np.float32)
 
@@ -69,7 +74,7 @@ def dispatch(x_by_rank, sched):
     return q, sc
 
 
-def expert_ffn(xq, xsc, weights, sched, round_gate_up=True, context=None):
+def expert_ffn(xq, xsc, weights, sched, round_gate_up=True, context=None, limit=0.0):
     """Rows [total, H] quantised -> (hidden_q, hidden_sc, y bf16-valued fp32 [total, H]).
     `context` (a dict) receives the bf16 gate / up / hidden the backward pass differentiates through."""
     total, H = xq.shape
@@ -93,7 +98,7 @@ def expert_ffn(xq, xsc, weights, sched, round_gate_up=True, context=None):
         if round_gate_up:
             g, u = mxfp8.bf16_round(g), mxfp8.bf16_round(u)
         gate_all[lo:hi], up_all[lo:hi] = g, u
-        hidden[lo:hi] = mxfp8.bf16_round(silu_mul(g, u))
+        hidden[lo:hi] = mxfp8.bf16_round(silu_mul(g, u, limit))
     if context is not None:
         context.update(gate=gate_all, up=up_all, hidden=hidden.copy())
     hq, hsc = mxfp8.quantize(hidden)
@@ -129,7 +134,7 @@ def fwd_epilogue(combine_buf, router_w, y_shared=None):
     return mxfp8.bf16_round(acc)
 
 
-def forward_single_rank(x, routes, router_w, weights, padding=128, capacity=None, context=None):
+def forward_single_rank(x, routes, router_w, weights, padding=128, capacity=None, context=None, limit=0.0):
     """Whole forward on one rank. x fp32 (bf16 values) [T, H]; routes i32 [T, k]."""
     from . import routing
     T, k = routes.shape
@@ -138,7 +143,7 @@ def forward_single_rank(x, routes, router_w, weights, padding=128, capacity=None
         capacity = ((T * k + E * (padding - 1)) + 127) // 128 * 128
     sched = routing.build_schedule(routes[None], 0, E, capacity, padding)
     xq, xsc = dispatch([x], sched)
-    hq, hsc, y = expert_ffn(xq, xsc, weights, sched, context=context)
+    hq, hsc, y = expert_ffn(xq, xsc, weights, sched, context=context, limit=limit)
     buf = combine(y, sched, 0, T, k)
     out = fwd_epilogue(buf, router_w)
     return dict(schedule=sched, x_routed=(xq, xsc), hidden=(hq, hsc), y=y, combine=buf, output=out)
@@ -193,7 +198,7 @@ def _deq_t(a):
     return mxfp8.dequantize(*mxfp8.quantize_transposed(a))
 
 
-def backward_single_rank(x, router_w, w_gate, w_up, w_down, fwd, ctx, d_out):
+def backward_single_rank(x, router_w, w_gate, w_up, w_down, fwd, ctx, d_out, limit=0.0):
     """Backward of forward_single_rank with the same quantisation points as the device path:
     d_y, d_hidden and [d_gate | d_up] are bf16 tensors quantised along the contraction dimension of
     each GEMM that consumes them (normal orientation for data gradients, transposed for weight
@@ -222,9 +227,15 @@ def backward_single_rank(x, router_w, w_gate, w_up, w_down, fwd, ctx, d_out):
             d_w_down[e] = mxfp8.bf16_round(_mm(dy_t[:, lo:hi], hid_t[:, lo:hi]))            # [H, rows] x [I, rows]^T
     g = mxfp8.dequantize(*mxfp8.quantize(ctx["gate"]))
     u = mxfp8.dequantize(*mxfp8.quantize(ctx["up"]))
+    g_open, u_open = np.ones_like(g, dtype=bool), np.ones_like(u, dtype=bool)
+    if limit > 0:
+        # no gradient through a bound that is active or met with equality (swiglu.cuh:13-21,29-37)
+        lim = np.float32(limit)
+        g_open, u_open = g < lim, (u > -lim) & (u < lim)
+        g, u = np.minimum(g, lim), np.clip(u, -lim, lim)
     sg = (np.float32(1.0) / (np.float32(1.0) + np.exp(-g))).astype(np.float32)
-    d_up = d_hidden * (g * sg)
-    d_gate = d_hidden * u * sg * (np.float32(1.0) + g * (np.float32(1.0) - sg))
+    d_up = np.where(u_open, d_hidden * (g * sg), np.float32(0.0))
+    d_gate = np.where(g_open, d_hidden * u * sg * (np.float32(1.0) + g * (np.float32(1.0) - sg)), np.float32(0.0))
     dgu = mxfp8.bf16_round(np.concatenate([d_gate, d_up], axis=1).astype(np.float32))
     dgud = mxfp8.dequantize(*mxfp8.quantize(dgu))
     rows = np.zeros((total, H), np.float32)

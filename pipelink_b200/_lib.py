@@ -25,6 +25,8 @@ PROTOTYPES = {
     "plb_last_cuda_error": (c_int, []),
     "plb_moe_set_gemm_variant": (c_int, [c_int]),
     "plb_moe_gemm_variant": (c_int, []),
+    "plb_moe_set_swiglu_limit": (c_int, [c_float]),
+    "plb_moe_swiglu_limit": (c_float, []),
     "plb_moe_tile_rows": (c_int, []),
     "plb_debug_set_profile_buffer": (c_int, [c_void_p]),
     "plb_mxfp8_quantize": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
@@ -51,6 +53,10 @@ PROTOTYPES = {
     "plb_moe_gemm_down_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                                        c_void_p, c_void_p]),
+    "plb_moe_gemm_gate_up_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
+                                          c_void_p, c_void_p, c_void_p]),
+    "plb_moe_gemm_down_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                       c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "plb_ep_barrier": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "plb_ep_publish": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
     "plb_ep_pull_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

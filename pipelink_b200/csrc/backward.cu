@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ gate_sc,
                   const uint8_t* __restrict__ up, const uint8_t* __restrict__ up_sc,
                   const uint4* __restrict__ d_hidden, const int* __restrict__ num_rows_dev, int64_t capacity,
-                  int inter, uint4* __restrict__ dgu) {
+                  int inter, float limit, uint4* __restrict__ dgu) {
   int64_t rows = *num_rows_dev;
   if (rows > capacity) rows = capacity;
   const int vecs = inter >> 3;
@@ -89,10 +89,14 @@ swiglu_bwd_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ 
     for (int i = 0; i < 8; ++i) {
       const uint32_t gb = ((i < 4 ? gq.x : gq.y) >> (8 * (i & 3))) & 0xFFu;
       const uint32_t ub = ((i < 4 ? uq.x : uq.y) >> (8 * (i & 3))) & 0xFFu;
-      const float g = e4m3_to_float(gb) * gs, u = e4m3_to_float(ub) * us;
+      const float g_raw = e4m3_to_float(gb) * gs, u_raw = e4m3_to_float(ub) * us;
+      // clamped variant: the bounds of the forward pass, and no gradient through a bound that is
+      // active or met with equality (swiglu.cuh:13-21); limit = +inf keeps every gradient
+      const bool g_open = g_raw < limit, u_open = u_raw > -limit && u_raw < limit;
+      const float g = fminf(g_raw, limit), u = fminf(fmaxf(u_raw, -limit), limit);
       const float sg = 1.0f / (1.0f + __expf(-g));
-      du[i] = dhf[i] * (g * sg);
-      dg[i] = dhf[i] * u * sg * (1.0f + g * (1.0f - sg));
+      du[i] = u_open ? dhf[i] * (g * sg) : 0.0f;
+      dg[i] = g_open ? dhf[i] * u * sg * (1.0f + g * (1.0f - sg)) : 0.0f;
     }
     uint4 og, ou;
     og.x = pack2(dg[0], dg[1]); og.y = pack2(dg[2], dg[3]); og.z = pack2(dg[4], dg[5]); og.w = pack2(dg[6], dg[7]);
@@ -239,12 +243,13 @@ cudaError_t launch_bwd_dy(const void* d_out, const void* y, const float* router_
 
 cudaError_t launch_swiglu_bwd(const void* gate, const void* gate_sc, const void* up, const void* up_sc,
                               const void* d_hidden, const int* num_rows_dev, int64_t capacity, int inter,
-                              void* dgu, cudaStream_t stream) {
+                              float limit, void* dgu, cudaStream_t stream) {
   if (capacity == 0) return cudaSuccess;
+  const float bound = limit > 0.0f ? limit : HUGE_VALF;
   swiglu_bwd_kernel<<<sm_grid(8), 256, 0, stream>>>(
       static_cast<const uint8_t*>(gate), static_cast<const uint8_t*>(gate_sc), static_cast<const uint8_t*>(up),
       static_cast<const uint8_t*>(up_sc), static_cast<const uint4*>(d_hidden), num_rows_dev, capacity, inter,
-      static_cast<uint4*>(dgu));
+      bound, static_cast<uint4*>(dgu));
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
   zero_tail_kernel<<<sm_grid(2), 256, 0, stream>>>(static_cast<uint4*>(dgu), num_rows_dev, capacity, (2 * inter) >> 3);

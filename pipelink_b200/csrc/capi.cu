@@ -14,11 +14,13 @@ thread_local int g_last_cuda_error = 0;
 
 // 1 = one CTA per 128x128 tile (grouped_gemm.cu), 2 = CTA pair per 256x256 tile (grouped_gemm2.cu)
 int g_gemm_variant = 2;
+float g_swiglu_limit = 0.0f;  // 0: plain SwiGLU
 
 void* g_profile_buffer = nullptr;
 
 cudaError_t run_gemm(plb::GroupedGemmArgs& a, cudaStream_t s) {
   a.profile = g_profile_buffer;
+  a.swiglu_limit = g_swiglu_limit;
   return g_gemm_variant == 2 ? plb::launch_grouped_gemm_pair(a, s) : plb::launch_grouped_gemm(a, s);
 }
 
@@ -66,6 +68,14 @@ int plb_moe_set_gemm_variant(int variant) {
   return PLB_OK;
 }
 int plb_moe_gemm_variant(void) { return g_gemm_variant; }
+
+int plb_moe_set_swiglu_limit(float limit) {
+  if (!(limit >= 0.0f) || limit > 3.0e38f) return PLB_E_ARGUMENT;
+  g_swiglu_limit = limit;
+  return PLB_OK;
+}
+
+float plb_moe_swiglu_limit(void) { return g_swiglu_limit; }
 int plb_debug_set_profile_buffer(void* device_i64_grid_by_16) {
   g_profile_buffer = device_i64_grid_by_16;
 #ifdef PLB_DECODE_PROFILE
@@ -373,6 +383,52 @@ int plb_ipc_import(const void* handle64, void** out) {
 
 int plb_ipc_close(void* p) { return p ? from_cuda(cudaIpcCloseMemHandle(p)) : PLB_OK; }
 
+// bf16 routed precision: the same two GEMMs on bf16 operands (pair variant only).
+int plb_moe_gemm_gate_up_bf16(const void* x_routed_bf16, const void* w13_bf16, const int32_t* block_expert,
+                              const int32_t* num_tokens, int64_t capacity, int experts, int inter, int hidden,
+                              void* hidden_bf16, plb_status* status, void* stream) {
+  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
+  if (capacity < 0 || capacity % 256 || experts < 1 || inter < 128 || inter % 128 || hidden < 128 || hidden % 128)
+    return PLB_E_ARGUMENT;
+  if (!x_routed_bf16 || !w13_bf16 || !block_expert || !num_tokens || !hidden_bf16 || !status) return PLB_E_ARGUMENT;
+  if (!aligned16(x_routed_bf16) || !aligned16(w13_bf16) || !aligned16(hidden_bf16)) return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.bf16 = true;
+  a.a_fp8 = x_routed_bf16; a.a_sc = nullptr; a.b_fp8 = w13_bf16; a.b_sc = nullptr;
+  a.rows_capacity = capacity; a.experts = experts; a.n_rows = 2 * inter; a.K = hidden;
+  a.block_expert = block_expert; a.num_rows_dev = num_tokens; a.mode = 0;
+  a.out = hidden_bf16; a.out_sc = nullptr; a.dest_row = nullptr;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_gemm_down_bf16(const void* hidden_bf16, const void* w2_bf16, const int32_t* block_expert,
+                           const int32_t* num_tokens, const int32_t* dest_row, const int32_t* peer_rank,
+                           int64_t capacity, int experts, int inter, int hidden, int tile_rotation,
+                           void* combine_bf16, void* const* combine_peers, plb_status* status, void* stream) {
+  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
+  if (tile_rotation < 0 || capacity < 0 || capacity % 256 || experts < 1 || inter < 128 || inter % 128 ||
+      hidden < 256 || hidden % 256)
+    return PLB_E_ARGUMENT;
+  if (!hidden_bf16 || !w2_bf16 || !block_expert || !num_tokens || !dest_row || !status) return PLB_E_ARGUMENT;
+  if ((combine_peers == nullptr) == (combine_bf16 == nullptr)) return PLB_E_ARGUMENT;  // exactly one destination form
+  if (combine_peers != nullptr && peer_rank == nullptr) return PLB_E_ARGUMENT;
+  if (!aligned16(hidden_bf16) || !aligned16(w2_bf16) || !aligned16(combine_bf16)) return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.bf16 = true;
+  a.a_fp8 = hidden_bf16; a.a_sc = nullptr; a.b_fp8 = w2_bf16; a.b_sc = nullptr;
+  a.rows_capacity = capacity; a.experts = experts; a.n_rows = hidden; a.K = inter;
+  a.block_expert = block_expert; a.num_rows_dev = num_tokens; a.mode = 1; a.m_rotation = tile_rotation;
+  a.out = combine_bf16; a.out_sc = nullptr; a.dest_row = dest_row;
+  a.out_peers = combine_peers; a.peer_rank = peer_rank;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
+}
+
 int plb_moe_fwd_epilogue(const void* y_shared_bf16, const void* combine_bf16,
                          const float* router_weights, int64_t tokens, int topk, int64_t hidden,
                          void* out_bf16, void* stream) {
@@ -470,7 +526,8 @@ int plb_moe_swiglu_bwd(const void* gate_fp8, const void* gate_sc, const void* up
       capacity < 0 || capacity % 128 || inter <= 0 || inter % 128)
     return PLB_E_ARGUMENT;
   return from_cuda(plb::launch_swiglu_bwd(gate_fp8, gate_sc, up_fp8, up_sc, d_hidden_bf16, num_tokens, capacity,
-                                          inter, d_gate_up_bf16, static_cast<cudaStream_t>(stream)));
+                                          inter, g_swiglu_limit, d_gate_up_bf16,
+                                          static_cast<cudaStream_t>(stream)));
 }
 
 int plb_moe_gather_rows(const void* src_bf16, const int32_t* peer_rank, const int32_t* peer_token_idx,

@@ -70,6 +70,7 @@ struct KernelParams {
   uint8_t* const* out_peers;  // mode 1, optional: output base per source rank (peer-mapped)
   const int* peer_rank;       // mode 1 with out_peers: which base row p goes to
   Status* status;
+  float limit;  // mode 0: SwiGLU clamp bound, +inf when off
 };
 
 __device__ __forceinline__ float bf16_round(float x) {
@@ -247,8 +248,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           for (int i = 0; i < 32; ++i) {
             const float gf = bf16_round(__uint_as_float(g[i]));
             const float uf = bf16_round(__uint_as_float(u[i]));
-            const float s = __fdividef(gf, 1.0f + __expf(-gf));
-            h[i] = bf16_round(s * uf);
+            const float gc = fminf(gf, p.limit);
+            const float uc = fminf(fmaxf(uf, -p.limit), p.limit);
+            const float s = __fdividef(gc, 1.0f + __expf(-gc));
+            h[i] = bf16_round(s * uc);
             amax = fmaxf(amax, fabsf(h[i]));
           }
           const uint32_t e = e8m0_from_amax(amax);
@@ -374,6 +377,7 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
   p.out_peers = reinterpret_cast<uint8_t* const*>(a.out_peers);
   p.peer_rank = a.peer_rank;
   p.status = a.status;
+  p.limit = a.swiglu_limit > 0.0f ? a.swiglu_limit : HUGE_VALF;
   static bool attr_set[2] = {false, false};
   cudaError_t err;
   if (a.mode == 0) {

@@ -28,6 +28,7 @@
 // store instruction writes two 256-byte row segments (NVLink-friendly for the push).
 #include "kernels.h"
 #include "mxfp8.cuh"
+#include <cstring>
 
 namespace plb {
 
@@ -65,6 +66,7 @@ constexpr int kTmemCols = 512;
 constexpr int kSfColBase = 256;
 constexpr int kSfColsPerStage = 16;  // 4 (A) + 8 (B) used
 constexpr uint32_t kIdescPair = idesc_mxf8(256, 256);
+constexpr uint32_t kIdescPairBf16 = idesc_bf16(256, 256, 0, 0);
 
 struct Barriers2 {
   uint64_t full[kStages];   // used in the leader CTA: 2 arrivals + both CTAs' bytes
@@ -95,6 +97,7 @@ struct Params2 {
   const int* block_expert;  // per 128-row block
   const int* num_rows_dev;
   int m_rotation;           // modes 0/1: the tile loop starts this many 256-row tiles in (wraps around)
+  float limit;              // mode 0: gate <= limit, |up| <= limit before the activation; +inf = unclamped
   int max_m_tiles;          // capacity / 256
   int k_steps;
   int n_tiles;              // weight rows per expert / 256
@@ -169,16 +172,23 @@ __device__ __forceinline__ uint32_t pack_bf16(uint32_t a_bits, uint32_t b_bits) 
 }
 
 // 32 gate + 32 up accumulator values -> 32 E4M3 bytes (two uint4) and the block's scale byte.
-__device__ __forceinline__ uint32_t swiglu_quant32(const uint32_t* g, const uint32_t* u, uint4& q0,
-                                                   uint4& q1) {
+// Clamped SwiGLU of one bf16-valued pair (campaigns/mok/port/act_gptoss/swiglu.cuh:143-147 applies
+// the same bounds: gate from above only, up from both sides); limit = +inf leaves both unchanged.
+__device__ __forceinline__ float swiglu_clamped(float gf, float uf, float limit) {
+  gf = fminf(gf, limit);
+  uf = fminf(fmaxf(uf, -limit), limit);
+  return __fdividef(gf, 1.0f + __expf(-gf)) * uf;
+}
+
+__device__ __forceinline__ uint32_t swiglu_quant32(const uint32_t* g, const uint32_t* u, float limit,
+                                                   uint4& q0, uint4& q1) {
   float h[32];
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     const float gf = bf16r(__uint_as_float(g[i]));
     const float uf = bf16r(__uint_as_float(u[i]));
-    const float s = __fdividef(gf, 1.0f + __expf(-gf));
-    h[i] = bf16r(s * uf);
+    h[i] = bf16r(swiglu_clamped(gf, uf, limit));
     amax = fmaxf(amax, fabsf(h[i]));
   }
   const uint32_t e = e8m0_from_amax(amax);
@@ -195,10 +205,10 @@ __device__ __forceinline__ uint32_t swiglu_quant32(const uint32_t* g, const uint
 }
 
 // hidden value of one element pair exactly as swiglu_quant32 computes it (bf16-valued float)
-__device__ __forceinline__ float swiglu_bf16(uint32_t g_bits, uint32_t u_bits) {
+__device__ __forceinline__ float swiglu_bf16(uint32_t g_bits, uint32_t u_bits, float limit) {
   const float gf = bf16r(__uint_as_float(g_bits));
   const float uf = bf16r(__uint_as_float(u_bits));
-  return bf16r(__fdividef(gf, 1.0f + __expf(-gf)) * uf);
+  return bf16r(swiglu_clamped(gf, uf, limit));
 }
 
 // 32 accumulator values -> bf16 round -> MXFP8 block (two uint4 of E4M3 + scale byte)
@@ -223,7 +233,10 @@ __device__ __forceinline__ uint32_t quant32_bf16(const uint32_t* a, uint4& q0, u
   return e;
 }
 
-template <int MODE>
+// BF16 = true is the reference's bf16 routed precision (pipelink_mok_precision,
+// campaigns/mok/port/act/act.cu:246-249): bf16 operands, 64-element K steps of kind::f16 MMAs, no
+// scale tensors, and in mode 0 the hidden rows leave as bf16 instead of MXFP8.
+template <int MODE, bool BF16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b,
@@ -264,8 +277,10 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     fence_mbar_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
-    prefetch_tensormap(&map_sfa);
-    prefetch_tensormap(&map_sfb);
+    if (!BF16) {
+      prefetch_tensormap(&map_sfa);
+      prefetch_tensormap(&map_sfb);
+    }
   }
   if (warp == 2) {
     tmem_alloc_pair(smem_u32(&bars->tmem_base), kTmemCols);
@@ -300,17 +315,19 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           PROF_ADD(t_empty, t0);
           const uint32_t full = mapa_shared(smem_u32(&bars->full[stage]), 0);
-          mbar_arrive_expect_tx_cluster(full, kStageTx);
+          mbar_arrive_expect_tx_cluster(full, BF16 ? 2u * kTileBytes : kStageTx);
           const uint32_t sf = smem_base + kOffSf + stage * kSfStageBytes;
           const int kk = t.k_blk0 + kb;
-          tma_load_2d_pair(smem_base + kOffA + stage * kTileBytes, &map_a, full, kk * 128,
-                           a_blk * 128);
-          tma_load_2d_pair(smem_base + kOffB + stage * kTileBytes, &map_b, full, kk * 128,
-                           b_blk * 128);
+          // the x coordinate counts elements: 128 E4M3 or 64 bf16 per 128-byte K step
+          const int kx = kk * (BF16 ? 64 : 128);
+          tma_load_2d_pair(smem_base + kOffA + stage * kTileBytes, &map_a, full, kx, a_blk * 128);
+          tma_load_2d_pair(smem_base + kOffB + stage * kTileBytes, &map_b, full, kx, b_blk * 128);
 #ifndef PLB_EXP_NOSF
-          tma_load_2d_pair(sf, &map_sfa, full, 0, a_blk * t.k_pitch + kk);
-          tma_load_2d_pair(sf + kSfBytes, &map_sfb, full, 0, b_blk0 * t.k_pitch + kk);
-          tma_load_2d_pair(sf + 2 * kSfBytes, &map_sfb, full, 0, (b_blk0 + 1) * t.k_pitch + kk);
+          if (!BF16) {
+            tma_load_2d_pair(sf, &map_sfa, full, 0, a_blk * t.k_pitch + kk);
+            tma_load_2d_pair(sf + kSfBytes, &map_sfb, full, 0, b_blk0 * t.k_pitch + kk);
+            tma_load_2d_pair(sf + 2 * kSfBytes, &map_sfb, full, 0, (b_blk0 + 1) * t.k_pitch + kk);
+          }
 #endif
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -356,15 +373,21 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t sf = smem_base + kOffSf + stage * kSfStageBytes;
           const uint32_t sfa_t = tmem_base + kSfColBase + stage * kSfColsPerStage;
           const uint32_t sfb_t = sfa_t + 4;
-          tc_cp_32x128b_warpx4_pair(sfa_t, smem_desc(sf, kDescScale));
-          tc_cp_32x128b_warpx4_pair(sfb_t, smem_desc(sf + kSfBytes, kDescScale));
-          tc_cp_32x128b_warpx4_pair(sfb_t + 4, smem_desc(sf + 2 * kSfBytes, kDescScale));
+          if (!BF16) {
+            tc_cp_32x128b_warpx4_pair(sfa_t, smem_desc(sf, kDescScale));
+            tc_cp_32x128b_warpx4_pair(sfb_t, smem_desc(sf + kSfBytes, kDescScale));
+            tc_cp_32x128b_warpx4_pair(sfb_t + 4, smem_desc(sf + 2 * kSfBytes, kDescScale));
+          }
           const uint64_t adesc = smem_desc(smem_base + kOffA + stage * kTileBytes, kDescSw128KMajor);
           const uint64_t bdesc = smem_desc(smem_base + kOffB + stage * kTileBytes, kDescSw128KMajor);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            tc_mma_mxf8_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(kIdescPair, k),
-                             sfa_t, sfb_t, (kb | k) != 0 ? 1u : 0u);
+            // 32 bytes further along K per MMA: 32 E4M3 or 16 bf16 elements
+            if (BF16)
+              tc_mma_f16_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, kIdescPairBf16, (kb | k) != 0 ? 1u : 0u);
+            else
+              tc_mma_mxf8_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(kIdescPair, k),
+                               sfa_t, sfb_t, (kb | k) != 0 ? 1u : 0u);
           }
           const uint32_t empty_own = smem_u32(&bars->empty[stage]);
           tc_commit_pair(empty_own);
@@ -431,6 +454,25 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         PROF_ADD(t_drain, td);
         PROF_T0(tm);
+        if (BF16) {
+          // bf16 routed precision: 64 hidden values of this row, 128 contiguous bytes
+          uint4* dst = reinterpret_cast<uint4*>(
+              p.out + (static_cast<size_t>(row) * p.out_cols + n_tile * 128 + ch * 64) * 2);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t w0[4], w1[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i = 8 * c + 2 * j;
+              w0[j] = pack_bf16(__float_as_uint(swiglu_bf16(g0[i], u0[i], p.limit)),
+                                __float_as_uint(swiglu_bf16(g0[i + 1], u0[i + 1], p.limit)));
+              w1[j] = pack_bf16(__float_as_uint(swiglu_bf16(g1[i], u1[i], p.limit)),
+                                __float_as_uint(swiglu_bf16(g1[i + 1], u1[i + 1], p.limit)));
+            }
+            dst[c] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+            dst[4 + c] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+          }
+        } else {
         const size_t elem0 = static_cast<size_t>(row) * p.out_cols + n_tile * 128 + ch * 64;
         const size_t sc_off = scale_offset(row, n_tile * 4 + ch * 2, p.out_cols >> 7);
         if (p.save_gate != nullptr) {
@@ -452,13 +494,13 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
           uint32_t* hd = reinterpret_cast<uint32_t*>(p.save_hidden + elem0);
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            hd[i >> 1] = pack_bf16(__float_as_uint(swiglu_bf16(g0[i], u0[i])), __float_as_uint(swiglu_bf16(g0[i + 1], u0[i + 1])));
-            hd[16 + (i >> 1)] = pack_bf16(__float_as_uint(swiglu_bf16(g1[i], u1[i])), __float_as_uint(swiglu_bf16(g1[i + 1], u1[i + 1])));
+            hd[i >> 1] = pack_bf16(__float_as_uint(swiglu_bf16(g0[i], u0[i], p.limit)), __float_as_uint(swiglu_bf16(g0[i + 1], u0[i + 1], p.limit)));
+            hd[16 + (i >> 1)] = pack_bf16(__float_as_uint(swiglu_bf16(g1[i], u1[i], p.limit)), __float_as_uint(swiglu_bf16(g1[i + 1], u1[i + 1], p.limit)));
           }
         }
         uint4 q0, q1, q2, q3;
-        const uint32_t e0 = swiglu_quant32(g0, u0, q0, q1);
-        const uint32_t e1 = swiglu_quant32(g1, u1, q2, q3);
+        const uint32_t e0 = swiglu_quant32(g0, u0, p.limit, q0, q1);
+        const uint32_t e1 = swiglu_quant32(g1, u1, p.limit, q2, q3);
         uint4* dst = reinterpret_cast<uint4*>(p.out + row * p.out_cols + n_tile * 128 + ch * 64);
         dst[0] = q0;
         dst[1] = q1;
@@ -466,6 +508,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         dst[3] = q3;
         const size_t off = scale_offset(row, n_tile * 4 + ch * 2, p.out_cols >> 7);
         *reinterpret_cast<uint16_t*>(p.out_sc + off) = static_cast<uint16_t>(e0 | (e1 << 8));
+        }
         PROF_ADD(t_work, tm);
       } else {
         uint32_t v0[32], v1[32], v2[32], v3[32];
@@ -564,14 +607,15 @@ EncodeTiledFn encode_fn2() {
   return fn;
 }
 
-bool encode_operand(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k) {
+// k counts elements; a box is 128 rows by 128 bytes of K either way.
+bool encode_operand(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, bool bf16 = false) {
   EncodeTiledFn fn = encode_fn2();
   if (fn == nullptr) return false;
   const cuuint64_t dims[2] = {k, rows};
-  const cuuint64_t strides[1] = {k};
-  const cuuint32_t box[2] = {128, 128};
+  const cuuint64_t strides[1] = {bf16 ? 2 * k : k};
+  const cuuint32_t box[2] = {bf16 ? 64u : 128u, 128};
   const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
             elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -602,21 +646,26 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
   } else if (a.K % 128 || a.K <= 0) {
     return cudaErrorInvalidValue;
   }
+  if (a.bf16 && (a.mode == 2 || a.save_gate != nullptr || a.save_hidden != nullptr)) return cudaErrorInvalidValue;
   if (a.rows_capacity == 0 || a.experts == 0) return cudaSuccess;
   CUtensorMap map_a, map_b, map_sfa, map_sfb;
+  memset(&map_sfa, 0, sizeof(map_sfa));
+  memset(&map_sfb, 0, sizeof(map_sfb));
   const uint64_t k_len = a.mode == 2 ? static_cast<uint64_t>(a.rows_capacity) : static_cast<uint64_t>(a.K);
-  const uint64_t k_steps = k_len / 128;
+  const uint64_t k_steps = k_len / (a.bf16 ? 64 : 128);
   const uint64_t a_rows = a.mode == 2 ? static_cast<uint64_t>(a.m_rows) : static_cast<uint64_t>(a.rows_capacity);
   const uint64_t b_rows = a.mode == 2 ? static_cast<uint64_t>(a.n_rows) : static_cast<uint64_t>(a.experts) * a.n_rows;
-  if (!encode_operand(&map_a, a.a_fp8, a_rows, k_len) || !encode_operand(&map_b, a.b_fp8, b_rows, k_len) ||
-      !encode_scales(&map_sfa, a.a_sc, (a_rows / 128) * k_steps) ||
-      !encode_scales(&map_sfb, a.b_sc, (b_rows / 128) * k_steps))
+  if (!encode_operand(&map_a, a.a_fp8, a_rows, k_len, a.bf16) || !encode_operand(&map_b, a.b_fp8, b_rows, k_len, a.bf16))
+    return cudaErrorInvalidValue;
+  if (!a.bf16 && (!encode_scales(&map_sfa, a.a_sc, (a_rows / 128) * k_steps) ||
+                  !encode_scales(&map_sfb, a.b_sc, (b_rows / 128) * k_steps)))
     return cudaErrorInvalidValue;
   Params2 p;
   p.prof = static_cast<long long*>(a.profile);
   p.block_expert = a.block_expert;
   p.num_rows_dev = a.num_rows_dev;
   p.m_rotation = a.m_rotation < 0 ? 0 : a.m_rotation;
+  p.limit = a.swiglu_limit > 0.0f ? a.swiglu_limit : HUGE_VALF;
   p.max_m_tiles = static_cast<int>(a.rows_capacity / 256);
   p.k_steps = static_cast<int>(k_steps);
   p.n_tiles = a.n_rows / 256;
@@ -639,17 +688,21 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
   const int grid = a.num_sms & ~1;
   if (grid < 2) return cudaErrorInvalidValue;
   cudaError_t err;
-#define PLB_LAUNCH_PAIR(M)                                                                              \
-  err = cudaFuncSetAttribute(grouped_gemm2_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+#define PLB_LAUNCH_PAIR(M, B)                                                                           \
+  err = cudaFuncSetAttribute(grouped_gemm2_kernel<M, B>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                              kSmemBytes2);                                                              \
   if (err != cudaSuccess) return err;                                                                   \
-  grouped_gemm2_kernel<M><<<grid, kThreads2, kSmemBytes2, stream>>>(map_a, map_b, map_sfa, map_sfb, p)
-  if (a.mode == 0) {
-    PLB_LAUNCH_PAIR(0);
+  grouped_gemm2_kernel<M, B><<<grid, kThreads2, kSmemBytes2, stream>>>(map_a, map_b, map_sfa, map_sfb, p)
+  if (a.mode == 0 && a.bf16) {
+    PLB_LAUNCH_PAIR(0, true);
+  } else if (a.mode == 1 && a.bf16) {
+    PLB_LAUNCH_PAIR(1, true);
+  } else if (a.mode == 0) {
+    PLB_LAUNCH_PAIR(0, false);
   } else if (a.mode == 1) {
-    PLB_LAUNCH_PAIR(1);
+    PLB_LAUNCH_PAIR(1, false);
   } else {
-    PLB_LAUNCH_PAIR(2);
+    PLB_LAUNCH_PAIR(2, false);
   }
 #undef PLB_LAUNCH_PAIR
   return cudaGetLastError();

@@ -152,8 +152,9 @@ class IpcGroup:
 class EpMoKHost(mok.MoKHost):
     """One rank of the group. ``shape.tokens`` is tokens per rank, ``shape.experts`` the global count."""
 
-    def __init__(self, shape: mok.Shape, rank: int, group, padding: int | None = None):
-        super().__init__(shape, device=group.device, rank=rank, world=group.world, padding=padding)
+    def __init__(self, shape: mok.Shape, rank: int, group, padding: int | None = None, swiglu_limit: float = 0.0):
+        super().__init__(shape, device=group.device, rank=rank, world=group.world, padding=padding,
+                         swiglu_limit=swiglu_limit)
         self.group, lay = group, group.layout
         ptrs = group.ptrs_for(rank)
         dev, L, H, k, W = self.device, shape.tokens, shape.hidden, shape.topk, group.world
@@ -259,6 +260,7 @@ class EpMoKHost(mok.MoKHost):
         self._gemm_rows(dy_q, dy_sc, w["w_down_t_fp8"], w["w_down_t_sc"], H, I, b["d_hidden_routed"], self._identity_rows)
         _, _, h_t, h_t_sc = mok.mxfp8_quantize(b["hidden_routed_bf16"], False, True)
         self._wgrad(dy_t, dy_t_sc, h_t, h_t_sc, H, I, b["d_w_routed_down"])
+        self.select_activation()
         _lib.call("plb_moe_swiglu_bwd", b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(),
                   b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(), b["d_hidden_routed"].data_ptr(), nt, P, I,
                   b["d_gate_up_routed"].data_ptr(), mok._stream())

@@ -138,7 +138,7 @@ class MoKHost:
     """One rank's persistent forward session."""
 
     def __init__(self, shape: Shape, *, device="cuda", rank: int = 0, world: int = 1,
-                 padding: int | None = None, capacity: int | None = None):
+                 padding: int | None = None, capacity: int | None = None, swiglu_limit: float = 0.0):
         if shape.experts % world:
             raise ValueError("shape/process group disagrees: experts % world != 0")
         _lib.load()
@@ -146,6 +146,9 @@ class MoKHost:
         if shape.hidden % expert_padding() or shape.intermediate % expert_padding():
             raise ValueError(f"hidden and intermediate must be multiples of {expert_padding()}")
         self.shape, self.rank, self.world, self.padding = shape, rank, world, padding
+        # clamped-SwiGLU variant of this session (the reference's c1 cells use 4.0,
+        # campaigns/mok/README.md:82-84); applied to the library before each activation launch
+        self.swiglu_limit = float(swiglu_limit)
         self.device = torch.device(device)
         E = shape.experts // world
         L, H, I, k = shape.tokens, shape.hidden, shape.intermediate, shape.topk
@@ -248,8 +251,12 @@ class MoKHost:
         self.quantize_tokens()
         self.pull()
 
+    def select_activation(self):
+        _lib.call("plb_moe_set_swiglu_limit", self.swiglu_limit)
+
     def gemm_gate_up(self):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        self.select_activation()
         _lib.call("plb_moe_gemm_gate_up", b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
                   w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(), s.block_expert.data_ptr(),
                   s.num_tokens.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate,
@@ -293,6 +300,7 @@ class MoKHost:
 
     def gemm_gate_up_train(self):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        self.select_activation()
         _lib.call("plb_moe_gemm_gate_up_train", b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
                   w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(), s.block_expert.data_ptr(), s.num_tokens.data_ptr(),
                   self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
@@ -337,6 +345,7 @@ class MoKHost:
         _, _, h_t, h_t_sc = mxfp8_quantize(b["hidden_routed_bf16"], False, True)
         self._wgrad(dy_t, dy_t_sc, h_t, h_t_sc, H, I, b["d_w_routed_down"])
         # SwiGLU
+        self.select_activation()
         _lib.call("plb_moe_swiglu_bwd", b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(),
                   b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(), b["d_hidden_routed"].data_ptr(), nt, P, I,
                   b["d_gate_up_routed"].data_ptr(), _stream())

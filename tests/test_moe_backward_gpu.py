@@ -16,6 +16,21 @@ def _f(t):
 @pytest.mark.parametrize("shape_args,generation", [(("bwd-small", 4, 256, 256, 2, 384), 1), (("bwd-empty", 8, 512, 256, 2, 300), 3),
                                                    (("bwd-mid", 8, 1024, 512, 4, 512), 2)])
 def test_backward_vs_oracle(native_lib, shape_args, generation):
+    _forward_backward_vs_oracle(shape_args, generation, 0.0)
+
+
+def test_clamped_activation_vs_oracle(native_lib):
+    """The clamped-SwiGLU variant (the reference's c1 cells, campaigns/mok/README.md:82-84), with a
+    bound low enough that a good share of gate and up values reach it."""
+    from pipelink_b200 import _lib
+    try:
+        _forward_backward_vs_oracle(("bwd-clamp", 8, 512, 256, 2, 384), 2, 0.5)
+    finally:
+        _lib.call("plb_moe_set_swiglu_limit", 0.0)
+    assert _lib.load().plb_moe_swiglu_limit() == 0.0
+
+
+def _forward_backward_vs_oracle(shape_args, generation, limit):
     from pipelink_b200 import mok
     mok.set_gemm_variant(2)
     shape = mok.Shape(*shape_args)
@@ -26,7 +41,7 @@ def test_backward_vs_oracle(native_lib, shape_args, generation):
     wd = (torch.randn(E, H, I, device="cuda") * 0.05).to(torch.bfloat16)
     inputs = mok.MoKHost.new_inputs(shape, generation, "cuda")
     d_out = torch.randn(shape.tokens, H, device="cuda").to(torch.bfloat16)
-    host = mok.MoKHost(shape)
+    host = mok.MoKHost(shape, swiglu_limit=limit)
     host.load_weights(wg, wu, wd, train=True)
     fwd_plain = host.forward(inputs)["output"].clone()
     fwd_train = host.forward(inputs, train=True)["output"].clone()
@@ -37,9 +52,18 @@ def test_backward_vs_oracle(native_lib, shape_args, generation):
     weights = omoe.quantize_weights(_f(wg), _f(wu), _f(wd))
     ctx = {}
     ref_f = omoe.forward_single_rank(_f(inputs.x), inputs.experts.cpu().numpy().astype(np.int32), inputs.router.cpu().numpy(),
-                                     weights, padding=host.padding, capacity=host.capacity, context=ctx)
-    ref = omoe.backward_single_rank(_f(inputs.x), inputs.router.cpu().numpy(), _f(wg), _f(wu), _f(wd), ref_f, ctx, _f(d_out))
+                                     weights, padding=host.padding, capacity=host.capacity, context=ctx, limit=limit)
+    ref = omoe.backward_single_rank(_f(inputs.x), inputs.router.cpu().numpy(), _f(wg), _f(wu), _f(wd), ref_f, ctx, _f(d_out),
+                                    limit=limit)
     total = int(ref_f["schedule"]["num_tokens"][0])
+    st = omoe.error_stats(ref_f["output"], _f(fwd_train))
+    assert st["relative"] <= 2e-2, ("output", st)
+    if limit > 0:
+        live = ref_f["schedule"]["peer_rank"][:total] >= 0
+        share = float((ctx["gate"][live] >= limit).mean()), float((np.abs(ctx["up"][live]) >= limit).mean())
+        assert min(share) > 0.05, share                 # the bound is exercised on both operands
+        closed = ctx["gate"][live] >= limit * 1.15      # beyond the bound by more than an E4M3 rounding step
+        assert not _f(host.buffers["d_gate_up_routed"][:total])[live][:, :I][closed].any()
     # stage by stage: the combine backward is exact arithmetic on identical inputs up to the forward's y
     s = omoe.error_stats(ref["d_y"], _f(host.buffers["d_y_routed"])[:total])
     assert s["abs_max"] == 0.0, s
