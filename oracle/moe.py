@@ -149,6 +149,34 @@ def forward_single_rank(x, routes, router_w, weights, padding=128, capacity=None
     return dict(schedule=sched, x_routed=(xq, xsc), hidden=(hq, hsc), y=y, combine=buf, output=out)
 
 
+def forward_single_rank_bf16(x, routes, router_w, w_gate, w_up, w_down, padding=128, capacity=None, limit=0.0):
+    """Forward with the bf16 routed precision (the reference's second precision value,
+    campaigns/mok/port/act/act.cu:246-249): no quantisation on the routed path; gate / up and the
+    hidden rows are rounded to bf16 where the reference's bf16 tensors hold them
+    (campaigns/mok/port/act_gptoss/swiglu.cuh:138-156), GEMMs accumulate in fp32.
+    x fp32 (bf16 values) [T, H]; weights bf16-valued fp32 [E, I, H], [E, I, H], [E, H, I]."""
+    from . import routing
+    T, k = routes.shape
+    E, I, H = w_gate.shape
+    if capacity is None:
+        capacity = ((T * k + E * (padding - 1)) + 127) // 128 * 128
+    sched = routing.build_schedule(routes[None], 0, E, capacity, padding)
+    total = int(sched["num_tokens"][0])
+    pr, pt, off = sched["peer_rank"][:total], sched["peer_token_idx"][:total], sched["expert_offsets"]
+    rows = np.zeros((total, H), np.float32)
+    rows[pr >= 0] = x[pt[pr >= 0]]
+    hidden = np.zeros((total, I), np.float32)
+    y = np.zeros((total, H), np.float32)
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            g, u = mxfp8.bf16_round(_mm(rows[lo:hi], w_gate[e])), mxfp8.bf16_round(_mm(rows[lo:hi], w_up[e]))
+            hidden[lo:hi] = mxfp8.bf16_round(silu_mul(g, u, limit))
+            y[lo:hi] = mxfp8.bf16_round(_mm(hidden[lo:hi], w_down[e]))
+    buf = combine(y, sched, 0, T, k)
+    return dict(schedule=sched, x_routed=rows, hidden=hidden, y=y, combine=buf, output=fwd_epilogue(buf, router_w))
+
+
 def error_stats(expected, actual):
     """abs-mean, abs-max, relative (= sum|err| / sum|ref|), and relative L2."""
     e = np.asarray(expected, dtype=np.float64).reshape(-1)

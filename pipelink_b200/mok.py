@@ -138,7 +138,10 @@ class MoKHost:
     """One rank's persistent forward session."""
 
     def __init__(self, shape: Shape, *, device="cuda", rank: int = 0, world: int = 1,
-                 padding: int | None = None, capacity: int | None = None, swiglu_limit: float = 0.0):
+                 padding: int | None = None, capacity: int | None = None, swiglu_limit: float = 0.0,
+                 precision: str = "mxfp8"):
+        if precision not in ("mxfp8", "bf16"):
+            raise ValueError("precision is 'mxfp8' or 'bf16'")
         if shape.experts % world:
             raise ValueError("shape/process group disagrees: experts % world != 0")
         _lib.load()
@@ -149,6 +152,9 @@ class MoKHost:
         # clamped-SwiGLU variant of this session (the reference's c1 cells use 4.0,
         # campaigns/mok/README.md:82-84); applied to the library before each activation launch
         self.swiglu_limit = float(swiglu_limit)
+        # routed precision of this session (pipelink_mok_precision of the reference's links,
+        # campaigns/mok/README.md:86-93): "bf16" runs both grouped GEMMs on bf16 operands, forward only
+        self.precision = precision
         self.device = torch.device(device)
         E = shape.experts // world
         L, H, I, k = shape.tokens, shape.hidden, shape.intermediate, shape.topk
@@ -177,6 +183,11 @@ class MoKHost:
             "combine_buffer": torch.empty((L * k, H), dtype=torch.bfloat16, device=self.device),
             "output": torch.empty((L, H), dtype=torch.bfloat16, device=self.device),
         }
+        if precision == "bf16":
+            if _lib.load().plb_moe_gemm_variant() != 2:
+                raise ValueError("the bf16 routed precision exists in the CTA-pair GEMM variant only")
+            bf = dict(dtype=torch.bfloat16, device=self.device)
+            self.buffers.update(x_routed_bf16=torch.empty((P, H), **bf), hidden_routed_bf16=torch.empty((P, I), **bf))
         self.weights = None
 
     # ------------------------------------------------------------------ weights
@@ -188,6 +199,14 @@ class MoKHost:
         E, I, H = self.num_local_experts, self.shape.intermediate, self.shape.hidden
         if tuple(w_gate.shape) != (E, I, H) or tuple(w_up.shape) != (E, I, H) or tuple(w_down.shape) != (E, H, I):
             raise ValueError("weight shapes disagree with the session shape")
+        if self.precision == "bf16":
+            if train:
+                raise ValueError("the bf16 routed precision is forward only")
+            # per 256 rows of the gate/up operand: 128 gate rows, then the 128 up rows of the same columns
+            w13 = torch.stack([w_gate.reshape(E, I // 128, 128, H), w_up.reshape(E, I // 128, 128, H)], dim=2)
+            self.weights = dict(w13_bf16=w13.reshape(E, 2 * I, H).to(torch.bfloat16).contiguous(),
+                                w_routed_down_bf16=w_down.to(torch.bfloat16).contiguous())
+            return
         gq, gsc, _, _ = mxfp8_quantize(w_gate.contiguous())
         uq, usc, _, _ = mxfp8_quantize(w_up.contiguous())
         dq, dsc, _, _ = mxfp8_quantize(w_down.contiguous())
@@ -235,6 +254,8 @@ class MoKHost:
 
     def quantize_tokens(self):
         """x_buffer (bf16) -> xq / xsc, the buffers dispatch pulls rows from."""
+        if self.precision == "bf16":
+            return                      # rows are gathered as bf16
         rows = self._x_storage.shape[0]
         _lib.call("plb_mxfp8_quantize", self._x_storage.data_ptr(), rows, self.shape.hidden,
                   self.xq.data_ptr(), self.xsc.data_ptr(), None, None, _stream())
@@ -242,10 +263,17 @@ class MoKHost:
     def pull(self):
         """Dispatch: gather every scheduled row's E4M3 bytes and scale words (comm.cu:105-123)."""
         s, b, sh = self.schedule, self.buffers, self.shape
+        if self.precision == "bf16":
+            return self.pull_bf16()
         _lib.call("plb_ep_pull_rows", self.xq_peers.data_ptr(), self.xsc_peers.data_ptr(),
                   s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),
                   self.capacity, sh.hidden, b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
                   _stream())
+
+    def pull_bf16(self):
+        s, b, sh = self.schedule, self.buffers, self.shape
+        _lib.call("plb_moe_gather_rows", self.x_buffer.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
+                  s.num_tokens.data_ptr(), self.capacity, sh.hidden, b["x_routed_bf16"].data_ptr(), _stream())
 
     def dispatch(self):
         self.quantize_tokens()
@@ -257,6 +285,11 @@ class MoKHost:
     def gemm_gate_up(self):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
         self.select_activation()
+        if self.precision == "bf16":
+            _lib.call("plb_moe_gemm_gate_up_bf16", b["x_routed_bf16"].data_ptr(), w["w13_bf16"].data_ptr(),
+                      s.block_expert.data_ptr(), s.num_tokens.data_ptr(), self.capacity, self.num_local_experts,
+                      sh.intermediate, sh.hidden, b["hidden_routed_bf16"].data_ptr(), self.status.buf.data_ptr(), _stream())
+            return
         _lib.call("plb_moe_gemm_gate_up", b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
                   w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(), s.block_expert.data_ptr(),
                   s.num_tokens.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate,
@@ -265,6 +298,12 @@ class MoKHost:
 
     def gemm_down(self):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        if self.precision == "bf16":
+            _lib.call("plb_moe_gemm_down_bf16", b["hidden_routed_bf16"].data_ptr(), w["w_routed_down_bf16"].data_ptr(),
+                      s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(), None, self.capacity,
+                      self.num_local_experts, sh.intermediate, sh.hidden, 0, b["combine_buffer"].data_ptr(), None,
+                      self.status.buf.data_ptr(), _stream())
+            return
         _lib.call("plb_moe_gemm_down", b["hidden_routed_fp8"].data_ptr(),
                   b["hidden_routed_sc"].data_ptr(), w["w_routed_down_fp8"].data_ptr(),
                   w["w_routed_down_sc"].data_ptr(), s.block_expert.data_ptr(),
@@ -381,6 +420,8 @@ class MoKHost:
         self.schedule_into(inputs.experts[None])
         self.x_buffer.copy_(inputs.x)
         self.router_weight_buffer.copy_(inputs.router)
+        if train and self.precision == "bf16":
+            raise ValueError("the bf16 routed precision is forward only")
         if train:
             if "w_down_t_fp8" not in self.weights:
                 raise RuntimeError("load_weights(..., train=True) first")
@@ -400,6 +441,9 @@ class MoKHost:
 
     def context_tensors(self):
         b = self.buffers
+        if self.precision == "bf16":
+            return {"x_routed": b["x_routed_bf16"], "hidden_routed": b["hidden_routed_bf16"],
+                    "combine_buffer": b["combine_buffer"]}
         return {"x_routed_data": b["x_routed_fp8"], "x_routed_scale": b["x_routed_sc"],
                 "hidden_routed_data": b["hidden_routed_fp8"], "hidden_routed_scale": b["hidden_routed_sc"],
                 "combine_buffer": b["combine_buffer"]}

@@ -361,3 +361,40 @@ def test_host_pipeline_equals_the_plain_forward(native_lib):
     host.status.check("host pipeline")
     for i, (o, w) in enumerate(zip(h_out, want)):
         assert torch.equal(o.view(torch.int16), w.view(torch.int16)), i
+
+
+@pytest.mark.parametrize("shape_args,generation,limit", [(("bf16-small", 4, 256, 256, 2, 384), 1, 0.0),
+                                                         (("bf16-empty", 8, 512, 256, 2, 300), 3, 0.0),
+                                                         (("bf16-mid", 8, 1024, 512, 4, 1024), 2, 0.75)])
+def test_bf16_routed_precision_vs_oracle(native_lib, shape_args, generation, limit):
+    """The reference's bf16 routed precision (campaigns/mok/README.md:86-93): both grouped GEMMs on
+    bf16 operands, nothing quantised. Tolerance: the device and the oracle differ only in fp32
+    summation order, which moves some bf16 roundings of gate / up / hidden by one ulp (2^-8)."""
+    from oracle import moe as omoe
+    from pipelink_b200 import _lib, mok
+    mok.set_gemm_variant(2)
+    shape = mok.Shape(*shape_args)
+    torch.manual_seed(21)
+    E, H, I = shape.experts, shape.hidden, shape.intermediate
+    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.05).to(torch.bfloat16)
+    wg, wu, wd = mk(E, I, H), mk(E, I, H), mk(E, H, I)
+    inputs = mok.MoKHost.new_inputs(shape, generation, "cuda")
+    f = lambda t: t.detach().float().cpu().numpy()
+    try:
+        host = mok.MoKHost(shape, precision="bf16", swiglu_limit=limit)
+        host.load_weights(wg, wu, wd)
+        got = host.forward(inputs)
+        torch.cuda.synchronize()
+    finally:
+        _lib.call("plb_moe_set_swiglu_limit", 0.0)
+    ref = omoe.forward_single_rank_bf16(f(inputs.x), inputs.experts.cpu().numpy().astype(np.int32), inputs.router.cpu().numpy(),
+                                        f(wg), f(wu), f(wd), padding=host.padding, capacity=host.capacity, limit=limit)
+    total = int(ref["schedule"]["num_tokens"][0])
+    assert np.array_equal(f(got["x_routed"])[:total], ref["x_routed"])            # a gather: exact
+    for name, want, have, tol in (("hidden", ref["hidden"], f(got["hidden_routed"])[:total], 4e-3),
+                                  ("combine", ref["combine"], f(got["combine_buffer"]), 6e-3),
+                                  ("output", ref["output"], f(got["output"]), 6e-3)):
+        st = omoe.error_stats(want, have)
+        assert np.isfinite(have).all() and st["relative"] <= tol, (name, st)
+    with pytest.raises(ValueError):
+        host.forward(inputs, train=True)

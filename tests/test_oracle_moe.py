@@ -92,3 +92,19 @@ def test_forward_backward_match_autograd_within_mxfp8_noise(limit):
         assert (ctx["gate"][live] >= limit).mean() > 0.05
         plain = omoe.forward_single_rank(x, routes, router_w, weights)["output"]
         assert _rel(plain, fwd["output"]) > 0.05          # the bound changes the result
+
+
+@pytest.mark.parametrize("limit", [0.0, 0.5])
+def test_bf16_precision_forward_matches_dense_model(limit):
+    """The bf16 routed precision has no quantisation noise: only bf16 roundings separate it from fp64."""
+    rng = np.random.default_rng(12)
+    E, H, I, k, T = 4, 256, 128, 2, 96
+    bf = lambda a: mxfp8.bf16_round(a.astype(np.float32))
+    wg, wu = bf(rng.standard_normal((E, I, H)) * 0.05), bf(rng.standard_normal((E, I, H)) * 0.05)
+    wd, x = bf(rng.standard_normal((E, H, I)) * 0.05), bf(rng.standard_normal((T, H)))
+    routes = np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+    router_w = rng.random((T, k)).astype(np.float32)
+    got = omoe.forward_single_rank_bf16(x, routes, router_w, wg, wu, wd, limit=limit)
+    t = lambda a: torch.tensor(a, dtype=torch.float64)
+    want = _dense_ffn(t(x), routes, t(router_w), t(wg), t(wu), t(wd), limit)
+    assert _rel(want.numpy(), got["output"]) < 6e-3
