@@ -387,6 +387,33 @@ int plb_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks, i
                    int rank, int world, void* const* k_gather_peers, void* const* v_gather_peers,
                    void* const* ready_peers, int ctas, void* stream);
 
+/* Tensor-parallel GEMM compositions (examples/comm-overlap: `ag` = C_r = gather(A_q) @ B_r^T,
+ * `rs` = rows [r*M/W, (r+1)*M/W) of sum_q A_q @ B_q^T; README "AllGather protocol" and
+ * "ReduceScatter protocol"), bf16 operands, fp32 accumulation, bf16 results.
+ *
+ * plb_tp_push_rows: the all-gather side. `src` is this rank's shard, `blocks` row blocks of
+ * block_bytes each (a block = 256 rows, the GEMM's tile height); every block is copied, in `parts`
+ * pieces, into gather_peers[c] at the shard's place for every c != rank, and each piece adds 1 to
+ * ready_peers[c][rank * blocks + block] with release semantics at system scope (the rank's own
+ * counters advance too; its shard must already sit in its gathered buffer). After step g (1-based)
+ * a complete block's counter reads g * parts.
+ *
+ * plb_tp_gemm_bf16: out[dest_row[i]] = A[i, :] @ B^T for the m rows of A ([m, k] bf16; B [n, k]),
+ * CTA pairs on 256 x 256 tiles starting `tile_rotation` row tiles in. `ready` (nullable): the
+ * loads of row tile t wait, bounded, for ready[t] >= ready_target (status code 5 if it never
+ * comes). Exactly one of out_bf16 (local placement) and out_peers (row i goes to
+ * out_peers[peer_rank[i]], the reduce-scatter push into the owner's receive slots; the owner then
+ * sums its slots in rank order with plb_moe_fwd_epilogue on unit weights) is given.
+ * block_group: m / 128 zeros; num_rows: device int32 holding m. The pushing kernel of a step must
+ * be launched before that step's GEMM on the same stream, and a group barrier (plb_ep_barrier)
+ * separates the steps: a GEMM never waits for a kernel that is queued behind it on its own GPU. */
+int plb_tp_push_rows(const void* src, int blocks, int64_t block_bytes, int parts, int rank, int world,
+                     void* const* gather_peers, void* const* ready_peers, int ctas, void* stream);
+int plb_tp_gemm_bf16(const void* a_bf16, const void* b_bf16, const int32_t* block_group, const int32_t* num_rows,
+                     const int32_t* dest_row, const int32_t* peer_rank, int64_t m, int n, int k, int tile_rotation,
+                     const uint32_t* ready, uint32_t ready_target, void* out_bf16, void* const* out_peers,
+                     plb_status* status, void* stream);
+
 /* ------------------------------------------------------------------ linked images
  * Load and launch a linked pipeline image (`pipeline.cubin` + `link.json` of the link driver):
  * the roles of CudaBackend in the reference (pipec/src/pipec2/host/cuda.py:123-286: module load,

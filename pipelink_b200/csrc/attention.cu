@@ -57,11 +57,6 @@ struct AttnBars {
 };
 static_assert(sizeof(AttnBars) <= 256, "barrier block");
 
-__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 __device__ __forceinline__ float tanh_approx(float x) {
   float y;

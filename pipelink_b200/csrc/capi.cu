@@ -606,6 +606,42 @@ int plb_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks, i
                                           static_cast<cudaStream_t>(stream)));
 }
 
+// ---- tensor-parallel compositions: all-gather -> GEMM and GEMM -> reduce-scatter push
+int plb_tp_push_rows(const void* src, int blocks, int64_t block_bytes, int parts, int rank, int world,
+                     void* const* gather_peers, void* const* ready_peers, int ctas, void* stream) {
+  if (!src || !gather_peers || !ready_peers) return PLB_E_ARGUMENT;
+  if (blocks < 0 || parts < 1 || block_bytes <= 0 || block_bytes % (16 * parts) || world < 1 || rank < 0 ||
+      rank >= world || ctas < 1)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_tp_push_rows(src, blocks, block_bytes, parts, rank, world, gather_peers,
+                                            reinterpret_cast<unsigned* const*>(ready_peers), ctas,
+                                            static_cast<cudaStream_t>(stream)));
+}
+
+int plb_tp_gemm_bf16(const void* a_bf16, const void* b_bf16, const int32_t* block_group, const int32_t* num_rows,
+                     const int32_t* dest_row, const int32_t* peer_rank, int64_t m, int n, int k, int tile_rotation,
+                     const uint32_t* ready, uint32_t ready_target, void* out_bf16, void* const* out_peers,
+                     plb_status* status, void* stream) {
+  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
+  if (m <= 0 || m % 256 || n < 256 || n % 256 || k < 128 || k % 128 || tile_rotation < 0) return PLB_E_ARGUMENT;
+  if (!a_bf16 || !b_bf16 || !block_group || !num_rows || !dest_row || !status) return PLB_E_ARGUMENT;
+  if ((out_peers == nullptr) == (out_bf16 == nullptr)) return PLB_E_ARGUMENT;
+  if (out_peers != nullptr && peer_rank == nullptr) return PLB_E_ARGUMENT;
+  if (!aligned16(a_bf16) || !aligned16(b_bf16) || !aligned16(out_bf16)) return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.bf16 = true;
+  a.a_fp8 = a_bf16; a.a_sc = nullptr; a.b_fp8 = b_bf16; a.b_sc = nullptr;
+  a.rows_capacity = m; a.experts = 1; a.n_rows = n; a.K = k;
+  a.block_expert = block_group; a.num_rows_dev = num_rows; a.mode = 1; a.m_rotation = tile_rotation;
+  a.ready = ready; a.ready_target = ready_target;
+  a.out = out_bf16; a.out_sc = nullptr; a.dest_row = dest_row;
+  a.out_peers = out_peers; a.peer_rank = peer_rank;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
+}
+
 // ---- linked-image launcher (cudaLibrary API) and tensor-map helper for stage providers
 int plb_image_load(const void* image, const char* symbol, int dyn_smem_bytes, void** library,
                    void** kernel) {

@@ -48,6 +48,11 @@ __device__ __forceinline__ int ld_volatile_i32(const int* p) {
   return v;
 }
 
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void report_failure(Status* st, int code, int what, unsigned observed,
                                                unsigned expected) {
   if (atomicCAS(&st->code, 0, code) == 0) {

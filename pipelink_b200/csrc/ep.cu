@@ -188,7 +188,60 @@ cp_push_kv_kernel(const uint4* __restrict__ k_local, const uint4* __restrict__ v
   }
 }
 
+// All-gather push (examples/comm-overlap README, "AllGather protocol": a chunk is copied to one
+// peer, every writing thread's stores are fenced at system scope, one release increment lands on
+// the peer's row-block counter). A task is one part of one 256-row block for one consumer; a
+// rank's blocks go first to the consumer whose GEMM reaches them first (it starts at its own
+// rows and walks upward through the ranks). The task for consumer == rank copies nothing: the
+// shard already sits in this rank's gathered buffer, only its counters advance.
+__global__ void __launch_bounds__(256)
+tp_push_rows_kernel(const uint4* __restrict__ src, int blocks, int vec_per_part, int parts, int rank, int world,
+                    uint4* const* __restrict__ gather_peers, unsigned* const* __restrict__ ready_peers) {
+  const int per_consumer = blocks * parts;
+  const int total = per_consumer * world;
+  for (int t = blockIdx.x; t < total; t += gridDim.x) {
+    const int ci = t / per_consumer, r = t - ci * per_consumer;
+    const int b = r / parts, part = r - b * parts;
+    const int consumer = (rank - 1 - ci + 2 * world) % world;      // ci = world - 1 is this rank itself
+    if (consumer != rank) {
+      const size_t off = (static_cast<size_t>(b) * parts + part) * vec_per_part;
+      const uint4* s = src + off;
+      uint4* d = gather_peers[consumer] + static_cast<size_t>(rank) * blocks * parts * vec_per_part + off;
+      for (int i0 = threadIdx.x; i0 < vec_per_part; i0 += blockDim.x * 4) {
+        uint4 a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * blockDim.x;
+          if (i < vec_per_part) a[u] = s[i];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * blockDim.x;
+          if (i < vec_per_part) d[i] = a[u];
+        }
+      }
+      __threadfence_system();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      fence_acq_rel_sys();
+      red_release_sys_add(ready_peers[consumer] + rank * blocks + b, 1u);
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_tp_push_rows(const void* src, int blocks, int64_t block_bytes, int parts, int rank, int world,
+                                void* const* gather_peers, unsigned* const* ready_peers, int ctas,
+                                cudaStream_t stream) {
+  if (blocks == 0) return cudaSuccess;
+  tp_push_rows_kernel<<<ctas, 256, 0, stream>>>(static_cast<const uint4*>(src), blocks,
+                                                static_cast<int>((block_bytes / parts) >> 4), parts, rank, world,
+                                                reinterpret_cast<uint4* const*>(gather_peers), ready_peers);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks,
                               int64_t block_bytes, int rank, int world, void* const* k_peers,

@@ -97,6 +97,8 @@ struct Params2 {
   const int* block_expert;  // per 128-row block
   const int* num_rows_dev;
   int m_rotation;           // modes 0/1: the tile loop starts this many 256-row tiles in (wraps around)
+  const unsigned* ready;    // mode 1: per 256-row tile of A, a counter that reaches ready_target once the
+  unsigned ready_target;    //         tile's rows have all arrived (all-gather -> GEMM); null = rows are local
   float limit;              // mode 0: gate <= limit, |up| <= limit before the activation; +inf = unclamped
   int max_m_tiles;          // capacity / 256
   int k_steps;
@@ -306,6 +308,22 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank), m_tiles_live, m_rot);
         const int a_blk = t.a_blk, b_blk0 = t.b_blk0;
         const int b_blk = b_blk0 + static_cast<int>(cta_rank);
+        if (MODE == 1 && p.ready != nullptr) {
+          // rows pushed by a peer are usable once its counter increment (a release at system scope,
+          // examples/comm-overlap README "AllGather protocol") is observed; then order the TMA reads after it
+          const unsigned* flag = p.ready + (a_blk >> 1);
+          const long long t0 = clock64();
+          while (static_cast<int>(ld_acquire_sys_u32(flag) - p.ready_target) < 0) {
+            // half the budget of the barrier waits downstream, so the record names the cause
+            if (clock64() - t0 > kWaitBudgetCycles / 2 || ld_volatile_i32(&p.status->code) != 0) {
+              report_failure(p.status, ST_TIMEOUT_COUNTER, 310, ld_acquire_sys_u32(flag), p.ready_target);
+              ok = false;
+              break;
+            }
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = 0; kb < t.k_steps; ++kb) {
           PROF_T0(t0);
           if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY,
@@ -665,6 +683,8 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
   p.block_expert = a.block_expert;
   p.num_rows_dev = a.num_rows_dev;
   p.m_rotation = a.m_rotation < 0 ? 0 : a.m_rotation;
+  p.ready = a.ready;
+  p.ready_target = a.ready_target;
   p.limit = a.swiglu_limit > 0.0f ? a.swiglu_limit : HUGE_VALF;
   p.max_m_tiles = static_cast<int>(a.rows_capacity / 256);
   p.k_steps = static_cast<int>(k_steps);

@@ -78,6 +78,8 @@ struct GroupedGemmArgs {
   const int* dest_row;
   void* const* out_peers = nullptr;  // mode 1: per-source-rank output bases (device array), or null
   const int* peer_rank = nullptr;    // mode 1 with out_peers
+  const unsigned* ready = nullptr;   // pair variant, mode 1: readiness counter per 256-row tile of A
+  unsigned ready_target = 0;
   bool bf16 = false;                 // pair variant, modes 0/1: a_fp8 / b_fp8 hold bf16, no scales, mode 0 writes bf16
   float swiglu_limit = 0.0f;         // mode 0: > 0 bounds gate from above and up from both sides
   int m_rotation = 0;                // pair variant: 256-row tiles are visited starting this many tiles in
@@ -107,6 +109,9 @@ cudaError_t launch_bwd_dy(const void* d_out, const void* y, const float* router_
 cudaError_t launch_swiglu_bwd(const void* gate, const void* gate_sc, const void* up, const void* up_sc,
                               const void* d_hidden, const int* num_rows_dev, int64_t capacity, int inter,
                               float limit, void* dgu, cudaStream_t stream);
+cudaError_t launch_tp_push_rows(const void* src, int blocks, int64_t block_bytes, int parts, int rank, int world,
+                                void* const* gather_peers, unsigned* const* ready_peers, int ctas,
+                                cudaStream_t stream);
 cudaError_t launch_ep_bwd_dy(const void* const* d_out_peers, const float* const* router_w_peers, const int* peer_rank,
                              const int* peer_token_idx, const int* dest_row, const int* num_rows_dev, int64_t capacity,
                              int hidden, void* dy, cudaStream_t stream);

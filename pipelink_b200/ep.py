@@ -152,9 +152,13 @@ class IpcGroup:
 class EpMoKHost(mok.MoKHost):
     """One rank of the group. ``shape.tokens`` is tokens per rank, ``shape.experts`` the global count."""
 
-    def __init__(self, shape: mok.Shape, rank: int, group, padding: int | None = None, swiglu_limit: float = 0.0):
+    def __init__(self, shape: mok.Shape, rank: int, group, padding: int | None = None, swiglu_limit: float = 0.0,
+                 precision: str = "mxfp8"):
+        if precision == "bf16" and not group.layout.train:
+            raise ValueError("the bf16 routed precision dispatches bf16 rows: open the group with train=True, "
+                             "which adds the peer-visible bf16 token region")
         super().__init__(shape, device=group.device, rank=rank, world=group.world, padding=padding,
-                         swiglu_limit=swiglu_limit)
+                         swiglu_limit=swiglu_limit, precision=precision)
         self.group, lay = group, group.layout
         ptrs = group.ptrs_for(rank)
         dev, L, H, k, W = self.device, shape.tokens, shape.hidden, shape.topk, group.world
@@ -211,8 +215,20 @@ class EpMoKHost(mok.MoKHost):
                   s.block_expert.data_ptr(), s.scratch.data_ptr(), s.scratch.numel() * 4,
                   self.status.buf.data_ptr(), mok._stream())
 
+    def pull_bf16(self):
+        """Dispatch of the bf16 routed precision: rows come from the home ranks' bf16 tokens."""
+        s, b, sh = self.schedule, self.buffers, self.shape
+        _lib.call("plb_ep_gather_rows", self.x_peers.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
+                  s.num_tokens.data_ptr(), self.capacity, sh.hidden, b["x_routed_bf16"].data_ptr(), mok._stream())
+
     def gemm_down_push(self):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        if self.precision == "bf16":
+            _lib.call("plb_moe_gemm_down_bf16", b["hidden_routed_bf16"].data_ptr(), w["w_routed_down_bf16"].data_ptr(),
+                      s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(), s.peer_rank.data_ptr(),
+                      self.capacity, self.num_local_experts, sh.intermediate, sh.hidden, self.push_rotation, None,
+                      self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
+            return
         _lib.call("plb_moe_gemm_down_push", b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(),
                   w["w_routed_down_fp8"].data_ptr(), w["w_routed_down_sc"].data_ptr(),
                   s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(),

@@ -116,6 +116,43 @@ def test_local_group_backward_equals_the_single_rank_backward(native_lib, world,
         group.close()
 
 
+@pytest.mark.parametrize("world,shape_args", [(2, ("ep2h", 8, 512, 256, 2, 256)), (4, ("ep4h", 8, 256, 256, 4, 128))])
+def test_local_group_bf16_precision_equals_the_single_rank_forward(native_lib, world, shape_args):
+    """bf16 routed precision over a group: rows are dispatched as bf16 from the home ranks' token
+    buffers and pushed back from the down GEMM; the result equals, bit for bit, one rank holding
+    every token and expert (itself held to the oracle in test_moe_gpu.py)."""
+    from pipelink_b200 import ep, mok
+    mok.set_gemm_variant(2)
+    shape = mok.Shape(*shape_args)
+    wg, wu, wd, inputs = make_group_case(mok, shape, world, seed=5)
+    whole = mok.Shape("whole", shape.experts, shape.hidden, shape.intermediate, shape.topk, shape.tokens * world)
+    single = mok.MoKHost(whole, precision="bf16")
+    single.load_weights(wg, wu, wd)
+    joined = mok.Inputs(torch.cat([i.x for i in inputs]), torch.cat([i.experts for i in inputs]), torch.cat([i.router for i in inputs]))
+    want = single.forward(joined)["output"].clone()
+    with pytest.raises(ValueError):
+        plain = ep.LocalGroup(shape, world, "cuda")
+        try:
+            ep.EpMoKHost(shape, 0, plain, precision="bf16")        # no peer-visible bf16 tokens in this slab
+        finally:
+            plain.close()
+    group = ep.LocalGroup(shape, world, "cuda", train=True)
+    try:
+        hosts = [ep.EpMoKHost(shape, r, group, precision="bf16") for r in range(world)]
+        El, L = shape.experts // world, shape.tokens
+        for r, h in enumerate(hosts):
+            h.load_weights(wg[r * El:(r + 1) * El], wu[r * El:(r + 1) * El], wd[r * El:(r + 1) * El])
+            h.buffers["combine_buffer"].fill_(float("nan"))
+        outs = ep.forward_local_group(hosts, inputs)
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.isfinite(outs[r].float()).all()
+            assert torch.equal(outs[r].view(torch.int16), want[r * L:(r + 1) * L].view(torch.int16)), r
+    finally:
+        torch.cuda.synchronize()
+        group.close()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_ipc_group_forward_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
