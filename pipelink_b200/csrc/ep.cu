@@ -188,6 +188,112 @@ cp_push_kv_kernel(const uint4* __restrict__ k_local, const uint4* __restrict__ v
   }
 }
 
+// Dispatch pull on the bulk-copy engine: a warp streams rows peer -> shared memory -> local
+// memory with untiled bulk copies (one 4 KB request per row and direction instead of 256 16-byte
+// ones), three rows in flight per warp. The scale words of a row (one 4-byte word per 128
+// columns, 512 bytes apart in the tensor-core layout) travel through registers, loaded when the
+// row's copy is issued and stored when it lands.
+constexpr int kPullWarps = 4;
+constexpr int kPullStages = 4;
+constexpr int kPullAhead = kPullStages - 1;
+
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(kPullWarps * 32)
+ep_pull_rows_bulk_kernel(const uint8_t* const* __restrict__ xq_peers, const uint8_t* const* __restrict__ xsc_peers,
+                         const int* __restrict__ peer_rank, const int* __restrict__ peer_token_idx,
+                         const int* __restrict__ num_rows_dev, int64_t capacity, int hidden,
+                         uint8_t* __restrict__ x_routed_fp8, uint8_t* __restrict__ x_routed_sc, Status* status) {
+  extern __shared__ __align__(128) uint8_t pull_smem[];
+  __shared__ uint64_t bars[kPullWarps][kPullStages];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    for (int s = 0; s < kPullStages; ++s) mbar_init(smem_u32(&bars[warp][s]), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  int64_t rows = *num_rows_dev;
+  if (rows > capacity) rows = capacity;
+  const int col_blocks = hidden >> 7;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * kPullWarps;
+  const int64_t w0 = static_cast<int64_t>(blockIdx.x) * kPullWarps + warp;
+  const int64_t n = w0 < rows ? (rows - w0 + warps - 1) / warps : 0;      // rows of this warp: w0 + i * warps
+  const uint32_t ring = smem_u32(pull_smem) + static_cast<uint32_t>(warp) * kPullStages * hidden;
+  uint32_t sc_word[kPullStages];
+  bool live[kPullStages];
+  uint32_t parity = 0;                                                      // bit s: phase of stage s
+  bool ok = true;
+
+  // issue row i into stage s: the bulk load, and this lane's scale word into a register
+  auto issue = [&](int64_t i, int s) {
+    const int64_t p = w0 + i * warps;
+    const int src_rank = peer_rank[p];
+    live[s] = src_rank >= 0;
+    sc_word[s] = 0u;
+    if (!live[s]) return;
+    const int64_t t = peer_token_idx[p];
+    if (lane == 0) {
+      const uint32_t bar = smem_u32(&bars[warp][s]);
+      mbar_arrive_expect_tx(bar, static_cast<uint32_t>(hidden));
+      bulk_load(ring + static_cast<uint32_t>(s) * hidden, xq_peers[src_rank] + t * hidden, static_cast<uint32_t>(hidden), bar);
+    }
+    if (lane < col_blocks) {
+      const uint8_t* src_sc = xsc_peers[src_rank] + static_cast<size_t>(t >> 7) * col_blocks * 512 + (t & 31) * 16 +
+                              ((t & 127) >> 5) * 4;
+      sc_word[s] = *reinterpret_cast<const uint32_t*>(src_sc + static_cast<size_t>(lane) * 512);
+    }
+  };
+  // retire row i from stage s: wait for the load, store the row and the scale word
+  auto retire = [&](int64_t i, int s) {
+    const int64_t p = w0 + i * warps;
+    uint8_t* dst = x_routed_fp8 + p * hidden;
+    if (live[s]) {
+      if (lane == 0) {
+        if (!mbar_wait(smem_u32(&bars[warp][s]), (parity >> s) & 1u, status, ST_TIMEOUT_FULL, 320 + s)) ok = false;
+        if (ok) {
+          fence_proxy_async_smem();
+          bulk_store(dst, ring + static_cast<uint32_t>(s) * hidden, static_cast<uint32_t>(hidden));
+        } else {
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      parity ^= 1u << s;
+      ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+    } else {
+      uint4* d = reinterpret_cast<uint4*>(dst);
+      for (int v = lane; v < (hidden >> 4); v += 32) d[v] = make_uint4(0u, 0u, 0u, 0u);
+      // every retired row commits one group, so "at most one group pending" always means
+      // "everything but the latest row's store has been read out of shared memory"
+      if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+    if (lane < col_blocks) {
+      const size_t off = static_cast<size_t>(p >> 7) * col_blocks * 512 + (p & 31) * 16 + ((p & 127) >> 5) * 4;
+      *reinterpret_cast<uint32_t*>(x_routed_sc + off + static_cast<size_t>(lane) * 512) = sc_word[s];
+    }
+  };
+
+  for (int64_t i0 = 0; i0 < n + kPullAhead && ok; i0 += kPullStages) {
+#pragma unroll
+    for (int u = 0; u < kPullStages; ++u) {
+      const int64_t i = i0 + u;                        // row issued now, into stage u
+      const int64_t r = i - kPullAhead;                // row retired now, from stage (u + 1) % stages
+      if (r >= 0 && r < n && ok) retire(r, (u + 1) % kPullStages);
+      if (i < n && ok) {
+        // stage u was last read by the store of row i - stages, committed at least one retire ago
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+        issue(i, u);
+      }
+    }
+  }
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  __syncwarp();
+}
+
 // All-gather push (examples/comm-overlap README, "AllGather protocol": a chunk is copied to one
 // peer, every writing thread's stores are fenced at system scope, one release increment lands on
 // the peer's row-block counter). A task is one part of one 256-row block for one consumer; a
@@ -284,6 +390,25 @@ cudaError_t launch_ep_pull_rows(const void* const* xq_peers, const void* const* 
       reinterpret_cast<const uint8_t* const*>(xq_peers),
       reinterpret_cast<const uint8_t* const*>(xsc_peers), peer_rank, peer_token_idx, num_rows_dev,
       capacity, hidden, static_cast<uint8_t*>(x_routed_fp8), static_cast<uint8_t*>(x_routed_sc));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_pull_rows_bulk(const void* const* xq_peers, const void* const* xsc_peers, const int* peer_rank,
+                                     const int* peer_token_idx, const int* num_rows_dev, int64_t capacity, int hidden,
+                                     void* x_routed_fp8, void* x_routed_sc, Status* status, cudaStream_t stream) {
+  if (capacity == 0) return cudaSuccess;
+  // one scale word per lane and 16-byte aligned bulk copies
+  if (hidden > 4096 || hidden % 128) return cudaErrorInvalidValue;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int smem = kPullWarps * kPullStages * hidden;
+  cudaError_t err = cudaFuncSetAttribute(ep_pull_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err != cudaSuccess) return err;
+  ep_pull_rows_bulk_kernel<<<sms * 3, kPullWarps * 32, smem, stream>>>(
+      reinterpret_cast<const uint8_t* const*>(xq_peers), reinterpret_cast<const uint8_t* const*>(xsc_peers), peer_rank,
+      peer_token_idx, num_rows_dev, capacity, hidden, static_cast<uint8_t*>(x_routed_fp8),
+      static_cast<uint8_t*>(x_routed_sc), status);
   return cudaGetLastError();
 }
 

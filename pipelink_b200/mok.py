@@ -155,6 +155,7 @@ class MoKHost:
         # routed precision of this session (pipelink_mok_precision of the reference's links,
         # campaigns/mok/README.md:86-93): "bf16" runs both grouped GEMMs on bf16 operands, forward only
         self.precision = precision
+        self.pull_variant = "loads"     # dispatch pull: "loads" (16-byte loads per lane) or "bulk" (bulk-copy engine)
         self.device = torch.device(device)
         E = shape.experts // world
         L, H, I, k = shape.tokens, shape.hidden, shape.intermediate, shape.topk
@@ -265,6 +266,12 @@ class MoKHost:
         s, b, sh = self.schedule, self.buffers, self.shape
         if self.precision == "bf16":
             return self.pull_bf16()
+        if self.pull_variant == "bulk" and sh.hidden <= 4096:
+            _lib.call("plb_ep_pull_rows_bulk", self.xq_peers.data_ptr(), self.xsc_peers.data_ptr(),
+                      s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),
+                      self.capacity, sh.hidden, b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
+                      self.status.buf.data_ptr(), _stream())
+            return
         _lib.call("plb_ep_pull_rows", self.xq_peers.data_ptr(), self.xsc_peers.data_ptr(),
                   s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),
                   self.capacity, sh.hidden, b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),

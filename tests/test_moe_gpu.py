@@ -165,8 +165,15 @@ def test_dispatch_paths_bit_exact(mok):
     ts = torch.tensor([xsc.data_ptr()], dtype=torch.int64, device="cuda")
     _lib.call("plb_ep_pull_rows", tq.data_ptr(), ts.data_ptr(), s.peer_rank.data_ptr(),
               s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(), cap, H, q2.data_ptr(), sc2.data_ptr(), None)
+    q3 = torch.full((cap, H), 255, **u8)
+    sc3 = torch.full((cap // 128, H // 128, 32, 16), 255, **u8)
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+    _lib.call("plb_ep_pull_rows_bulk", tq.data_ptr(), ts.data_ptr(), s.peer_rank.data_ptr(),
+              s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(), cap, H, q3.data_ptr(), sc3.data_ptr(),
+              status.data_ptr(), None)
     torch.cuda.synchronize()
-    for q, sc in ((q1, sc1), (q2, sc2)):
+    assert status[0].item() == 0
+    for q, sc in ((q1, sc1), (q2, sc2), (q3, sc3)):
         assert np.array_equal(_np(q)[:total], rq)
         assert np.array_equal(_np(sc)[: total // 128], rsc)
         assert (_np(q)[total:] == 255).all()      # rows beyond the live schedule are untouched
