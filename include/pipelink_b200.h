@@ -243,10 +243,14 @@ int plb_ep_pull_rows(const void* const* xq_peers, const void* const* xsc_peers,
                      void* x_routed_fp8, void* x_routed_sc, void* stream);
 /* The same dispatch on the bulk-copy engine (cp.async.bulk peer -> shared -> local, one request
  * per row and direction; scale words through registers). hidden <= 4096; every xq_peers[r] is
- * 16-byte aligned. A load that never completes is reported in `status` (code 1). */
+ * 16-byte aligned. scale_rows != 0: xsc_peers point at plb_ep_scale_rows' output instead of the
+ * tensor-core layout, so a row's scale words cross NVLink as one 128-byte request instead of one
+ * 32-byte sector per word. A load that never completes is reported in `status` (code 1).
+ * plb_ep_scale_rows: u32 [tokens, hidden / 128] from xsc (tokens a multiple of 128), at home. */
 int plb_ep_pull_rows_bulk(const void* const* xq_peers, const void* const* xsc_peers, const int32_t* peer_rank,
                           const int32_t* peer_token_idx, const int32_t* num_tokens, int64_t capacity, int64_t hidden,
-                          void* x_routed_fp8, void* x_routed_sc, plb_status* status, void* stream);
+                          void* x_routed_fp8, void* x_routed_sc, int scale_rows, plb_status* status, void* stream);
+int plb_ep_scale_rows(const void* xsc, int64_t tokens, int64_t hidden, void* scale_rows_u32, void* stream);
 
 /* Expert-parallel backward, the mirror of dispatch and combine (mok_comm_bwd,
  * campaigns/mok/port/comm/comm.cu:226-262): gradients of routed rows are pulled from the token's

@@ -58,7 +58,8 @@ PROTOTYPES = {
     "plb_moe_gemm_down_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                        c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "plb_ep_pull_rows_bulk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
-                                      c_void_p, c_void_p, c_void_p, c_void_p]),
+                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "plb_ep_scale_rows": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "plb_tp_push_rows": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "plb_tp_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                  c_int, c_void_p, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),

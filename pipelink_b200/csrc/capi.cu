@@ -354,16 +354,22 @@ int plb_ep_pull_rows(const void* const* xq_peers, const void* const* xsc_peers,
 
 int plb_ep_pull_rows_bulk(const void* const* xq_peers, const void* const* xsc_peers, const int32_t* peer_rank,
                           const int32_t* peer_token_idx, const int32_t* num_tokens, int64_t capacity, int64_t hidden,
-                          void* x_routed_fp8, void* x_routed_sc, plb_status* status, void* stream) {
+                          void* x_routed_fp8, void* x_routed_sc, int scale_rows, plb_status* status, void* stream) {
   if (capacity < 0 || capacity % 128 || hidden <= 0 || hidden % 128 || hidden > 4096) return PLB_E_ARGUMENT;
   if (!xq_peers || !xsc_peers || !peer_rank || !peer_token_idx || !num_tokens || !x_routed_fp8 || !x_routed_sc ||
       !status)
     return PLB_E_ARGUMENT;
   if (!aligned16(x_routed_fp8) || !aligned16(x_routed_sc)) return PLB_E_ARGUMENT;
   return from_cuda(plb::launch_ep_pull_rows_bulk(xq_peers, xsc_peers, peer_rank, peer_token_idx, num_tokens, capacity,
-                                                 static_cast<int>(hidden), x_routed_fp8, x_routed_sc,
+                                                 static_cast<int>(hidden), x_routed_fp8, x_routed_sc, scale_rows,
                                                  reinterpret_cast<plb::Status*>(status),
                                                  static_cast<cudaStream_t>(stream)));
+}
+
+int plb_ep_scale_rows(const void* xsc, int64_t tokens, int64_t hidden, void* scale_rows_u32, void* stream) {
+  if (!xsc || !scale_rows_u32 || tokens < 0 || tokens % 128 || hidden <= 0 || hidden % 128) return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_scale_rows(xsc, tokens, static_cast<int>(hidden), scale_rows_u32,
+                                          static_cast<cudaStream_t>(stream)));
 }
 
 int plb_sym_alloc(size_t bytes, void** out) {

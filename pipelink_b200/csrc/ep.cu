@@ -193,6 +193,21 @@ cp_push_kv_kernel(const uint4* __restrict__ k_local, const uint4* __restrict__ v
 // ones), three rows in flight per warp. The scale words of a row (one 4-byte word per 128
 // columns, 512 bytes apart in the tensor-core layout) travel through registers, loaded when the
 // row's copy is issued and stored when it lands.
+// Scale words of each token gathered into one contiguous run: [tokens, hidden / 128] u32 next to the
+// tensor-core layout (where a row's words sit 512 bytes apart), so that a peer fetches a row's
+// scales with one 128-byte request instead of one 32-byte sector per word.
+__global__ void __launch_bounds__(256)
+scale_rows_kernel(const uint8_t* __restrict__ xsc, int64_t tokens, int col_blocks, uint32_t* __restrict__ out) {
+  const int64_t total = tokens * col_blocks;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / col_blocks;
+    const int c = static_cast<int>(i - t * col_blocks);
+    out[i] = *reinterpret_cast<const uint32_t*>(xsc + static_cast<size_t>(t >> 7) * col_blocks * 512 +
+                                                static_cast<size_t>(c) * 512 + (t & 31) * 16 + ((t & 127) >> 5) * 4);
+  }
+}
+
 constexpr int kPullWarps = 4;
 constexpr int kPullStages = 4;
 constexpr int kPullAhead = kPullStages - 1;
@@ -207,7 +222,8 @@ __global__ void __launch_bounds__(kPullWarps * 32)
 ep_pull_rows_bulk_kernel(const uint8_t* const* __restrict__ xq_peers, const uint8_t* const* __restrict__ xsc_peers,
                          const int* __restrict__ peer_rank, const int* __restrict__ peer_token_idx,
                          const int* __restrict__ num_rows_dev, int64_t capacity, int hidden,
-                         uint8_t* __restrict__ x_routed_fp8, uint8_t* __restrict__ x_routed_sc, Status* status) {
+                         uint8_t* __restrict__ x_routed_fp8, uint8_t* __restrict__ x_routed_sc, int scale_rows,
+                         Status* status) {
   extern __shared__ __align__(128) uint8_t pull_smem[];
   __shared__ uint64_t bars[kPullWarps][kPullStages];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -242,9 +258,13 @@ ep_pull_rows_bulk_kernel(const uint8_t* const* __restrict__ xq_peers, const uint
       bulk_load(ring + static_cast<uint32_t>(s) * hidden, xq_peers[src_rank] + t * hidden, static_cast<uint32_t>(hidden), bar);
     }
     if (lane < col_blocks) {
-      const uint8_t* src_sc = xsc_peers[src_rank] + static_cast<size_t>(t >> 7) * col_blocks * 512 + (t & 31) * 16 +
-                              ((t & 127) >> 5) * 4;
-      sc_word[s] = *reinterpret_cast<const uint32_t*>(src_sc + static_cast<size_t>(lane) * 512);
+      if (scale_rows) {
+        sc_word[s] = reinterpret_cast<const uint32_t*>(xsc_peers[src_rank])[t * col_blocks + lane];
+      } else {
+        const uint8_t* src_sc = xsc_peers[src_rank] + static_cast<size_t>(t >> 7) * col_blocks * 512 + (t & 31) * 16 +
+                                ((t & 127) >> 5) * 4;
+        sc_word[s] = *reinterpret_cast<const uint32_t*>(src_sc + static_cast<size_t>(lane) * 512);
+      }
     }
   };
   // retire row i from stage s: wait for the load, store the row and the scale word
@@ -395,7 +415,8 @@ cudaError_t launch_ep_pull_rows(const void* const* xq_peers, const void* const* 
 
 cudaError_t launch_ep_pull_rows_bulk(const void* const* xq_peers, const void* const* xsc_peers, const int* peer_rank,
                                      const int* peer_token_idx, const int* num_rows_dev, int64_t capacity, int hidden,
-                                     void* x_routed_fp8, void* x_routed_sc, Status* status, cudaStream_t stream) {
+                                     void* x_routed_fp8, void* x_routed_sc, int scale_rows, Status* status,
+                                     cudaStream_t stream) {
   if (capacity == 0) return cudaSuccess;
   // one scale word per lane and 16-byte aligned bulk copies
   if (hidden > 4096 || hidden % 128) return cudaErrorInvalidValue;
@@ -408,7 +429,17 @@ cudaError_t launch_ep_pull_rows_bulk(const void* const* xq_peers, const void* co
   ep_pull_rows_bulk_kernel<<<sms * 3, kPullWarps * 32, smem, stream>>>(
       reinterpret_cast<const uint8_t* const*>(xq_peers), reinterpret_cast<const uint8_t* const*>(xsc_peers), peer_rank,
       peer_token_idx, num_rows_dev, capacity, hidden, static_cast<uint8_t*>(x_routed_fp8),
-      static_cast<uint8_t*>(x_routed_sc), status);
+      static_cast<uint8_t*>(x_routed_sc), scale_rows, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scale_rows(const void* xsc, int64_t tokens, int hidden, void* out, cudaStream_t stream) {
+  if (tokens == 0) return cudaSuccess;
+  const int64_t total = tokens * (hidden >> 7);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 1184) blocks = 1184;
+  scale_rows_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint8_t*>(xsc), tokens, hidden >> 7,
+                                                                  static_cast<uint32_t*>(out));
   return cudaGetLastError();
 }
 

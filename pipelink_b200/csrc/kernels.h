@@ -111,7 +111,9 @@ cudaError_t launch_swiglu_bwd(const void* gate, const void* gate_sc, const void*
                               float limit, void* dgu, cudaStream_t stream);
 cudaError_t launch_ep_pull_rows_bulk(const void* const* xq_peers, const void* const* xsc_peers, const int* peer_rank,
                                      const int* peer_token_idx, const int* num_rows_dev, int64_t capacity, int hidden,
-                                     void* x_routed_fp8, void* x_routed_sc, Status* status, cudaStream_t stream);
+                                     void* x_routed_fp8, void* x_routed_sc, int scale_rows, Status* status,
+                                     cudaStream_t stream);
+cudaError_t launch_scale_rows(const void* xsc, int64_t tokens, int hidden, void* out, cudaStream_t stream);
 cudaError_t launch_tp_push_rows(const void* src, int blocks, int64_t block_bytes, int parts, int rank, int world,
                                 void* const* gather_peers, unsigned* const* ready_peers, int ctas,
                                 cudaStream_t stream);

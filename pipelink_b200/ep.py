@@ -37,6 +37,7 @@ class SlabLayout:
         self.flags = off; off += _align(4 * 32)
         self.xq = off; off += _align(L * H)
         self.xsc = off; off += _align(L // 128 * (H // 128) * 512)
+        self.xsc_rows = off; off += _align(L * (H // 128) * 4)     # the same words, one contiguous run per token
         self.routes_all = off; off += _align(world * L * k * 4)
         self.combine = off; off += _align(L * k * H * 2)
         self.train = train
@@ -165,6 +166,9 @@ class EpMoKHost(mok.MoKHost):
         table = lambda off: torch.tensor([p + off for p in ptrs], dtype=torch.int64, device=dev)
         self.flags_peers, self.xq_peers, self.xsc_peers = table(lay.flags), table(lay.xq), table(lay.xsc)
         self.routes_peers, self.combine_peers = table(lay.routes_all), table(lay.combine)
+        self.xsc_rows_peers = table(lay.xsc_rows)
+        self.xsc_rows = tensor_from_ptr(ptrs[rank] + lay.xsc_rows, (L, H // 128), torch.int32, dev)
+        self.pull_variant = "bulk"
         me = ptrs[rank]
         self.xq = tensor_from_ptr(me + lay.xq, (L, H), torch.uint8, dev)
         self.xsc = tensor_from_ptr(me + lay.xsc, (L // 128, H // 128, 32, 16), torch.uint8, dev)
@@ -196,6 +200,12 @@ class EpMoKHost(mok.MoKHost):
         self.router_weight_buffer.copy_(inputs.router)
         self.routes_local.copy_(inputs.experts)
         self.quantize_tokens()
+
+    def quantize_tokens(self):
+        super().quantize_tokens()
+        if self.precision != "bf16" and self.pull_variant == "bulk":
+            _lib.call("plb_ep_scale_rows", self.xsc.data_ptr(), self.shape.tokens, self.shape.hidden,
+                      self.xsc_rows.data_ptr(), mok._stream())
 
     def publish_routes(self):
         _lib.call("plb_ep_publish", self.routes_local.data_ptr(), self.routes_local.numel() * 4,
@@ -361,10 +371,10 @@ def forward_local_group(hosts, inputs_per_rank, train: bool = False):
 class BenchSession:
     """bench.py's N > 1 arm: one rank of an IpcGroup at BASELINE config 4's per-rank shape."""
 
-    launches_per_step = 11  # quantise, publish, barrier x2, schedule x3, pull, 2 GEMMs, epilogue
+    launches_per_step = 12  # quantise, scale rows, publish, barrier x2, schedule x3, pull, 2 GEMMs, epilogue
     # backward adds: barrier x2, router grad, d_y pull, 5 quantise, 2 dgrad GEMMs, SwiGLU backward, x gather,
     # 2 wgrad GEMMs, slot sum, 2 tail-zeroing launches
-    launches_per_step_train = 11 + 18
+    launches_per_step_train = 12 + 18
 
     def __init__(self, shape: mok.Shape, dev, rank: int, world: int, train: bool = False):
         self.shape, self.dev, self.train = shape, dev, train

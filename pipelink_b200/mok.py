@@ -267,10 +267,11 @@ class MoKHost:
         if self.precision == "bf16":
             return self.pull_bf16()
         if self.pull_variant == "bulk" and sh.hidden <= 4096:
-            _lib.call("plb_ep_pull_rows_bulk", self.xq_peers.data_ptr(), self.xsc_peers.data_ptr(),
+            rows = getattr(self, "xsc_rows_peers", None)      # groups publish row-contiguous scale words
+            _lib.call("plb_ep_pull_rows_bulk", self.xq_peers.data_ptr(), (rows if rows is not None else self.xsc_peers).data_ptr(),
                       s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),
                       self.capacity, sh.hidden, b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
-                      self.status.buf.data_ptr(), _stream())
+                      1 if rows is not None else 0, self.status.buf.data_ptr(), _stream())
             return
         _lib.call("plb_ep_pull_rows", self.xq_peers.data_ptr(), self.xsc_peers.data_ptr(),
                   s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),

@@ -169,11 +169,20 @@ def test_dispatch_paths_bit_exact(mok):
     sc3 = torch.full((cap // 128, H // 128, 32, 16), 255, **u8)
     status = torch.zeros(8, dtype=torch.int32, device="cuda")
     _lib.call("plb_ep_pull_rows_bulk", tq.data_ptr(), ts.data_ptr(), s.peer_rank.data_ptr(),
-              s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(), cap, H, q3.data_ptr(), sc3.data_ptr(),
+              s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(), cap, H, q3.data_ptr(), sc3.data_ptr(), 0,
+              status.data_ptr(), None)
+    # the same with the scale words repacked into one run per token
+    q4 = torch.full((cap, H), 255, **u8)
+    sc4 = torch.full((cap // 128, H // 128, 32, 16), 255, **u8)
+    rows = torch.empty((pad, H // 128), dtype=torch.int32, device="cuda")
+    _lib.call("plb_ep_scale_rows", xsc.data_ptr(), pad, H, rows.data_ptr(), None)
+    tr = torch.tensor([rows.data_ptr()], dtype=torch.int64, device="cuda")
+    _lib.call("plb_ep_pull_rows_bulk", tq.data_ptr(), tr.data_ptr(), s.peer_rank.data_ptr(),
+              s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(), cap, H, q4.data_ptr(), sc4.data_ptr(), 1,
               status.data_ptr(), None)
     torch.cuda.synchronize()
     assert status[0].item() == 0
-    for q, sc in ((q1, sc1), (q2, sc2), (q3, sc3)):
+    for q, sc in ((q1, sc1), (q2, sc2), (q3, sc3), (q4, sc4)):
         assert np.array_equal(_np(q)[:total], rq)
         assert np.array_equal(_np(sc)[: total // 128], rsc)
         assert (_np(q)[total:] == 255).all()      # rows beyond the live schedule are untouched
