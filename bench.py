@@ -42,6 +42,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-1B decode ms/token leg")
     ap.add_argument("--no-train", action="store_true", help="skip the expert-parallel forward+backward leg (N > 1)")
+    ap.add_argument("--no-tp", action="store_true", help="skip the all-gather / reduce-scatter GEMM leg (N > 1)")
     ap.add_argument("--no-attention", action="store_true", help="skip the causal prefill attention leg")
     return ap.parse_args()
 
@@ -282,6 +283,10 @@ def run_native(args):
         session = None
         train = ep_train_leg(shape, dev, rank, world, pk)
 
+    tp_gemm = None
+    if world > 1 and not args.no_tp and args.tokens is None:
+        tp_gemm = tp_leg(dev, pk, rank, world)
+
     decode = None
     if rank == 0 and world == 1 and not args.no_decode and args.tokens is None:
         del session
@@ -304,6 +309,7 @@ def run_native(args):
                            "expert_padding": mok.expert_padding(), "gemm_variant": "cta-pair 256x256" if mok.expert_padding() == 256 else "single-cta 128x128"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
                 "roofline": roof, "cpu_baseline": cpu, "decode": decode, "attention": attention, "ep_fwd_bwd": train,
+                "tp_gemm": tp_gemm,
                 "frac_of_fp8_peak_whole_step": value / world / fp8_peak}
         print(json.dumps(line))
     if world > 1:
@@ -344,6 +350,57 @@ def ep_train_leg(shape, dev, rank, world, pk, steps=5):
            "nvlink_payload_bytes_per_rank": {"dispatch_e4m3": payload * (1 + 1 / 32), "combine_bf16": payload * 2,
                                              "d_out_bf16": payload * 2, "x_bf16": payload * 2, "d_x_bf16": payload * 2}}
     session.group.close()
+    return out
+
+
+def tp_leg(dev, pk, rank, world, steps=20):
+    """All-gather -> GEMM and GEMM -> reduce-scatter at the global problem the reference's
+    examples/comm-overlap reports (8192 x 8192 x 4096, bf16): step time is the max over ranks of the
+    device time of `steps` back-to-back steps, operands resident."""
+    import torch.distributed as dist
+    from pipelink_b200 import tp
+    m, n, k = 8192, 8192, 4096
+    if m % (256 * world) or k % (128 * world):
+        return None
+    ms, nl, kl = m // world, n // world, k // world
+    group = tp.IpcTpGroup(m, n, k, rank, world, dev)
+    me = group.rank
+    gen = torch.Generator(device=dev).manual_seed(99)
+    a = torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16)
+    b = (torch.randn(n, k, generator=gen, device=dev) * 0.05).to(torch.bfloat16)
+    b_ag = b[rank * nl:(rank + 1) * nl].contiguous()
+    a_rs, b_rs = a[:, rank * kl:(rank + 1) * kl].contiguous(), b[:, rank * kl:(rank + 1) * kl].contiguous()
+    for p in range(2):
+        me.gathered[p][rank * ms:(rank + 1) * ms].copy_(a[rank * ms:(rank + 1) * ms])
+
+    def timed(step):
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    t_ag = timed(lambda: me.ag(b_ag))
+    t_rs = timed(lambda: me.rs(a_rs, b_rs))
+    me.status.check("bench (tensor-parallel GEMMs)")
+    group.close()
+    flop = 2.0 * m * n * k
+    peak = pk["bf16_sustained"] * world
+    published = {2: (0.7927, 0.8242), 4: (0.4953, 0.9325)}.get(world)      # H200 at 1300 MHz, the reference's README
+    out = {"problem": [m, n, k], "dtype": "bf16", "world": world, "scaling": "strong", "steps": steps,
+           "ag": {"ms_per_step": t_ag, "tflops": flop / (t_ag * 1e-3) / 1e12, "frac_of_bf16_peak": flop / (t_ag * 1e-3) / 1e12 / peak},
+           "rs": {"ms_per_step": t_rs, "tflops": flop / (t_rs * 1e-3) / 1e12, "frac_of_bf16_peak": flop / (t_rs * 1e-3) / 1e12 / peak}}
+    if published:
+        out["reference_published_ms"] = {"ag": published[0], "rs": published[1], "hardware": "H200, 1300 MHz"}
     return out
 
 

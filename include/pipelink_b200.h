@@ -275,14 +275,17 @@ int plb_ep_gather_rows(const void* const* src_peers, const int32_t* peer_rank, c
  * stored to combine_peers[peer_rank[p]][dest_row[p]] from the GEMM epilogue. Rows are ordered by
  * (expert, source rank), so ranks that walked their tiles in the same order would all write to
  * the same home rank at the same time; tile_rotation (>= 0, in 256-row tiles, CTA-pair variant)
- * makes this rank start that many tiles in and wrap around. Pass rank * tiles per (expert,
- * source rank) block, or 0. The result does not depend on it. */
+ * makes this rank start that many tiles in and wrap around, and tile_stride (>= 1) makes
+ * consecutive steps of the tile loop that many row tiles apart (rounded up to the next value
+ * coprime to the live tile count), so that the tiles in flight at any moment go to different home
+ * ranks. Pass rank * tiles per (expert, source rank) block and those tiles + 1, or 0 and 1. The
+ * result does not depend on either. */
 int plb_moe_gemm_down_push(const void* hidden_fp8, const void* hidden_sc, const void* w2_fp8,
                            const void* w2_sc, const int32_t* block_expert,
                            const int32_t* num_tokens, const int32_t* dest_row,
                            const int32_t* peer_rank, int64_t capacity, int experts, int inter,
-                           int hidden, int tile_rotation, void* const* combine_peers, plb_status* status,
-                           void* stream);
+                           int hidden, int tile_rotation, int tile_stride, void* const* combine_peers,
+                           plb_status* status, void* stream);
 
 /* bf16 routed precision (the reference's second value of the variant handle
  * pipelink_mok_precision, campaigns/mok/port/act/act.cu:246-249; gemm stage precision variants,

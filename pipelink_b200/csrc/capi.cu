@@ -260,9 +260,9 @@ static int gemm_down_impl(const void* hidden_fp8, const void* hidden_sc, const v
                           const void* w2_sc, const int32_t* block_expert,
                           const int32_t* num_tokens, const int32_t* dest_row, int64_t capacity,
                           int experts, int inter, int hidden, void* combine_bf16,
-                          void* const* combine_peers, const int32_t* peer_rank, int tile_rotation,
+                          void* const* combine_peers, const int32_t* peer_rank, int tile_rotation, int tile_stride,
                           plb_status* status, void* stream) {
-  if (tile_rotation < 0) return PLB_E_ARGUMENT;
+  if (tile_rotation < 0 || tile_stride < 1) return PLB_E_ARGUMENT;
   if (capacity < 0 || capacity % 128 || experts < 1 || inter < 128 || inter % 128 ||
       hidden < 128 || hidden % 128)
     return PLB_E_ARGUMENT;
@@ -285,6 +285,7 @@ static int gemm_down_impl(const void* hidden_fp8, const void* hidden_sc, const v
   a.num_rows_dev = num_tokens;
   a.mode = 1;
   a.m_rotation = tile_rotation;
+  a.m_stride = tile_stride;
   a.out = combine_bf16;
   a.out_sc = nullptr;
   a.dest_row = dest_row;
@@ -301,7 +302,7 @@ int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void*
                       const int32_t* dest_row, int64_t capacity, int experts, int inter, int hidden,
                       void* combine_bf16, plb_status* status, void* stream) {
   return gemm_down_impl(hidden_fp8, hidden_sc, w2_fp8, w2_sc, block_expert, num_tokens, dest_row,
-                        capacity, experts, inter, hidden, combine_bf16, nullptr, nullptr, 0, status,
+                        capacity, experts, inter, hidden, combine_bf16, nullptr, nullptr, 0, 1, status,
                         stream);
 }
 
@@ -309,13 +310,13 @@ int plb_moe_gemm_down_push(const void* hidden_fp8, const void* hidden_sc, const 
                            const void* w2_sc, const int32_t* block_expert,
                            const int32_t* num_tokens, const int32_t* dest_row,
                            const int32_t* peer_rank, int64_t capacity, int experts, int inter,
-                           int hidden, int tile_rotation, void* const* combine_peers,
+                           int hidden, int tile_rotation, int tile_stride, void* const* combine_peers,
                            plb_status* status, void* stream) {
   if (!combine_peers || !peer_rank) return PLB_E_ARGUMENT;
   // the local base is only a non-null placeholder; every row is addressed through the table
   return gemm_down_impl(hidden_fp8, hidden_sc, w2_fp8, w2_sc, block_expert, num_tokens, dest_row,
                         capacity, experts, inter, hidden, const_cast<void**>(combine_peers),
-                        combine_peers, peer_rank, tile_rotation, status, stream);
+                        combine_peers, peer_rank, tile_rotation, tile_stride, status, stream);
 }
 
 int plb_ep_barrier(void* const* flags_peers, void* state, int rank, int world, plb_status* status,

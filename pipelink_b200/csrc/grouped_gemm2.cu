@@ -97,6 +97,7 @@ struct Params2 {
   const int* block_expert;  // per 128-row block
   const int* num_rows_dev;
   int m_rotation;           // modes 0/1: the tile loop starts this many 256-row tiles in (wraps around)
+  int m_stride;             // modes 0/1: consecutive steps of the loop are this many row tiles apart (>= 1)
   const unsigned* ready;    // mode 1: per 256-row tile of A, a counter that reaches ready_target once the
   unsigned ready_target;    //         tile's rows have all arrived (all-gather -> GEMM); null = rows are local
   float limit;              // mode 0: gate <= limit, |up| <= limit before the activation; +inf = unclamped
@@ -136,7 +137,8 @@ struct Tile {
 };
 
 template <int MODE>
-__device__ __forceinline__ Tile decode_tile(const Params2& p, int tile, int cta_rank, int m_tiles_live, int m_rot) {
+__device__ __forceinline__ Tile decode_tile(const Params2& p, int tile, int cta_rank, int m_tiles_live, int m_rot,
+                                            int m_stride = 1) {
   Tile t;
   if (MODE == 2) {
     const int per_expert = p.m_tiles * p.n_tiles;
@@ -154,8 +156,9 @@ __device__ __forceinline__ Tile decode_tile(const Params2& p, int tile, int cta_
     t.n_tile = tile - m_tile * p.n_tiles;
     // A rank that pushes rows to their home ranks starts at a different source-rank segment
     // than its peers, so the group writes all-to-all instead of all-to-one.
-    m_tile += m_rot;
-    if (m_tile >= m_tiles_live) m_tile -= m_tiles_live;
+    // ... and walks them with a stride coprime to their count, so the tiles in flight at any time
+    // belong to different source ranks: a permutation of the same tiles, results unchanged.
+    m_tile = static_cast<int>((static_cast<long long>(m_tile) * m_stride + m_rot) % m_tiles_live);
     const int expert = p.block_expert[m_tile * 2];
     t.a_blk = m_tile * 2 + cta_rank;
     t.b_blk0 = (expert * p.n_tiles + t.n_tile) * 2;
@@ -267,6 +270,15 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     total_tiles = m_tiles_live * p.n_tiles;
   }
   const int m_rot = m_tiles_live > 0 ? p.m_rotation % m_tiles_live : 0;
+  int m_stride = 1;
+  if (MODE != 2 && p.m_stride > 1 && m_tiles_live > 1) {
+    // smallest stride >= the requested one that is coprime to the live tile count
+    for (m_stride = p.m_stride % m_tiles_live == 0 ? 1 : p.m_stride % m_tiles_live;; ++m_stride) {
+      int a = m_stride, b = m_tiles_live;
+      while (b != 0) { const int t = a % b; a = b; b = t; }
+      if (a == 1) break;
+    }
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -305,7 +317,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       PROF_DECL(t_empty);
       PROF_T0(t_begin);
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-        const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank), m_tiles_live, m_rot);
+        const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank), m_tiles_live, m_rot, m_stride);
         const int a_blk = t.a_blk, b_blk0 = t.b_blk0;
         const int b_blk = b_blk0 + static_cast<int>(cta_rank);
         if (MODE == 1 && p.ready != nullptr) {
@@ -370,7 +382,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       PROF_DECL(t_full);
       PROF_T0(t_begin);
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-        const Tile t = decode_tile<MODE>(p, tile, 0, m_tiles_live, m_rot);
+        const Tile t = decode_tile<MODE>(p, tile, 0, m_tiles_live, m_rot, m_stride);
         if (t.k_steps == 0) continue;  // empty expert: the epilogue writes zeros on its own
         PROF_T0(ta);
         if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY,
@@ -442,7 +454,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     PROF_DECL(t_drain);
     PROF_DECL(t_work);
     for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-      const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank), m_tiles_live, m_rot);
+      const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank), m_tiles_live, m_rot, m_stride);
       const int n_tile = t.n_tile;
       const int64_t row = t.out_row0 + cta_rank * 128 + quad * 32 + lane;
       if (MODE == 2 && t.k_steps == 0) {
@@ -683,6 +695,7 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
   p.block_expert = a.block_expert;
   p.num_rows_dev = a.num_rows_dev;
   p.m_rotation = a.m_rotation < 0 ? 0 : a.m_rotation;
+  p.m_stride = a.m_stride < 1 ? 1 : a.m_stride;
   p.ready = a.ready;
   p.ready_target = a.ready_target;
   p.limit = a.swiglu_limit > 0.0f ? a.swiglu_limit : HUGE_VALF;

@@ -82,6 +82,7 @@ struct GroupedGemmArgs {
   unsigned ready_target = 0;
   bool bf16 = false;                 // pair variant, modes 0/1: a_fp8 / b_fp8 hold bf16, no scales, mode 0 writes bf16
   float swiglu_limit = 0.0f;         // mode 0: > 0 bounds gate from above and up from both sides
+  int m_stride = 1;                  // pair variant: row-tile distance between consecutive loop steps
   int m_rotation = 0;                // pair variant: 256-row tiles are visited starting this many tiles in
   int num_sms;
   Status* status;

@@ -179,6 +179,9 @@ class EpMoKHost(mok.MoKHost):
         # Pushing GEMMs start `rank` source-rank blocks into their tile list: a block is the rows one
         # rank sends to one expert, L * k / E on average, in 256-row tiles.
         self.push_rotation = rank * max(1, (L * k // shape.experts) // 256) if W > 1 else 0
+        # ... and step through the tiles a block and a bit at a time, so that the tiles in flight at
+        # any moment belong to different home ranks
+        self.push_stride = max(1, (L * k // shape.experts) // 256) + 1 if W > 1 else 1
         if lay.train:
             self.x_peers, self.d_out_peers = table(lay.x_bf16), table(lay.d_out)
             self.router_w_peers, self.d_x_rows_peers = table(lay.router_w), table(lay.d_x_rows)
@@ -243,7 +246,7 @@ class EpMoKHost(mok.MoKHost):
                   w["w_routed_down_fp8"].data_ptr(), w["w_routed_down_sc"].data_ptr(),
                   s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(),
                   s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
-                  self.push_rotation, self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
+                  self.push_rotation, self.push_stride, self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
 
     def device_step(self, train: bool = False):
         """Everything after the inputs sit in x_buffer / routes_local / router_weight_buffer."""
@@ -294,7 +297,7 @@ class EpMoKHost(mok.MoKHost):
         # d_x rows go straight from the GEMM epilogue into the home rank's [tokens * topk, H] buffer
         _lib.call("plb_moe_gemm_down_push", dgu_q.data_ptr(), dgu_sc.data_ptr(), w["w_cat_t_fp8"].data_ptr(),
                   w["w_cat_t_sc"].data_ptr(), s.block_expert.data_ptr(), nt, s.dest_row.data_ptr(), s.peer_rank.data_ptr(),
-                  P, self.num_local_experts, 2 * I, H, self.push_rotation, self.d_x_rows_peers.data_ptr(),
+                  P, self.num_local_experts, 2 * I, H, self.push_rotation, self.push_stride, self.d_x_rows_peers.data_ptr(),
                   self.status.buf.data_ptr(), mok._stream())
         _lib.call("plb_ep_gather_rows", self.x_peers.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), nt, P, H,
                   b["x_routed_bf16"].data_ptr(), mok._stream())
