@@ -357,6 +357,7 @@ def tp_leg(dev, pk, rank, world, steps=20):
     """All-gather -> GEMM and GEMM -> reduce-scatter at the global problem the reference's
     examples/comm-overlap reports (8192 x 8192 x 4096, bf16): step time is the max over ranks of the
     device time of `steps` back-to-back steps, operands resident."""
+    import torch
     import torch.distributed as dist
     from pipelink_b200 import tp
     m, n, k = 8192, 8192, 4096

@@ -287,6 +287,22 @@ int plb_moe_gemm_down_push(const void* hidden_fp8, const void* hidden_sc, const 
                            int hidden, int tile_rotation, int tile_stride, void* const* combine_peers,
                            plb_status* status, void* stream);
 
+/* plb_ep_pull_rows_bulk + plb_moe_gemm_gate_up in one kernel, the shape of the reference's
+ * megakernel, whose comm CTAs dispatch rows while its GEMM CTAs compute
+ * (campaigns/mok/port/comm/comm.cu:105-123, campaigns/mok/port/framework/interp_fwd.cu): one warp
+ * of every CTA takes row tickets, copies the row peer -> shared -> x_routed with bulk copies (scale
+ * words from plb_ep_scale_rows' layout through registers) and counts it into its 256-row tile; the
+ * TMA lane acquires a tile's count (256) before its first read of the tile. x_routed_fp8 /
+ * x_routed_sc are written exactly as plb_ep_pull_rows writes them. scratch_u32: capacity / 256 + 1
+ * words, zeroed on the stream by this call. CTA-pair variant, hidden <= 4096, capacity % 256 == 0.
+ * A row that never arrives is reported as status code 1 (its copy) or 5 (the tile's count). */
+int plb_moe_gemm_gate_up_dispatch(const void* const* xq_peers, const void* const* xsc_rows_peers,
+                                  const int32_t* peer_rank, const int32_t* peer_token_idx, void* x_routed_fp8,
+                                  void* x_routed_sc, const void* w13_fp8, const void* w13_sc,
+                                  const int32_t* block_expert, const int32_t* num_tokens, int64_t capacity,
+                                  int experts, int inter, int hidden, void* hidden_fp8, void* hidden_sc,
+                                  void* scratch_u32, plb_status* status, void* stream);
+
 /* bf16 routed precision (the reference's second value of the variant handle
  * pipelink_mok_precision, campaigns/mok/port/act/act.cu:246-249; gemm stage precision variants,
  * campaigns/mok/README.md:99-104): the gate/up and down grouped GEMMs on bf16 operands with fp32

@@ -53,6 +53,9 @@ PROTOTYPES = {
     "plb_moe_gemm_down_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                        c_void_p, c_void_p]),
+    "plb_moe_gemm_gate_up_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_void_p]),
     "plb_moe_gemm_gate_up_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                           c_void_p, c_void_p, c_void_p]),
     "plb_moe_gemm_down_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,

@@ -404,6 +404,37 @@ int plb_ipc_import(const void* handle64, void** out) {
 
 int plb_ipc_close(void* p) { return p ? from_cuda(cudaIpcCloseMemHandle(p)) : PLB_OK; }
 
+// Dispatch fused into the gate/up GEMM: rows are pulled into x_routed by a warp of every CTA
+// while the tensor pipe works on the tiles already complete.
+int plb_moe_gemm_gate_up_dispatch(const void* const* xq_peers, const void* const* xsc_rows_peers,
+                                  const int32_t* peer_rank, const int32_t* peer_token_idx, void* x_routed_fp8,
+                                  void* x_routed_sc, const void* w13_fp8, const void* w13_sc,
+                                  const int32_t* block_expert, const int32_t* num_tokens, int64_t capacity,
+                                  int experts, int inter, int hidden, void* hidden_fp8, void* hidden_sc,
+                                  void* scratch_u32, plb_status* status, void* stream) {
+  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
+  if (capacity < 0 || capacity % 256 || experts < 1 || inter < 128 || inter % 128 || hidden < 128 || hidden % 128 ||
+      hidden > 4096)
+    return PLB_E_ARGUMENT;
+  if (!xq_peers || !xsc_rows_peers || !peer_rank || !peer_token_idx || !x_routed_fp8 || !x_routed_sc || !w13_fp8 ||
+      !w13_sc || !block_expert || !num_tokens || !hidden_fp8 || !hidden_sc || !scratch_u32 || !status)
+    return PLB_E_ARGUMENT;
+  if (!aligned16(x_routed_fp8) || !aligned16(x_routed_sc) || !aligned16(w13_fp8) || !aligned16(w13_sc) ||
+      !aligned16(hidden_fp8) || !aligned16(hidden_sc))
+    return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.a_fp8 = x_routed_fp8; a.a_sc = x_routed_sc; a.b_fp8 = w13_fp8; a.b_sc = w13_sc;
+  a.rows_capacity = capacity; a.experts = experts; a.n_rows = 2 * inter; a.K = hidden;
+  a.block_expert = block_expert; a.num_rows_dev = num_tokens; a.mode = 0;
+  a.out = hidden_fp8; a.out_sc = hidden_sc; a.dest_row = nullptr;
+  a.pull_xq = xq_peers; a.pull_sc_rows = xsc_rows_peers; a.pull_peer_rank = peer_rank;
+  a.pull_token_idx = peer_token_idx; a.pull_scratch = scratch_u32;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
+}
+
 // bf16 routed precision: the same two GEMMs on bf16 operands (pair variant only).
 int plb_moe_gemm_gate_up_bf16(const void* x_routed_bf16, const void* w13_bf16, const int32_t* block_expert,
                               const int32_t* num_tokens, int64_t capacity, int experts, int inter, int hidden,

@@ -74,6 +74,7 @@ struct Barriers2 {
   uint64_t acc_full;        // per CTA: 1 arrival (leader's commit)
   uint64_t acc_empty;       // used in the leader CTA: one arrival per epilogue warp of the pair
   uint64_t drain;
+  uint64_t pull[8];         // mode 0 with the in-kernel dispatch: one per stage of the two dispatch warps' rings
   uint32_t tmem_base;
   uint32_t pad;
 };
@@ -100,6 +101,20 @@ struct Params2 {
   int m_stride;             // modes 0/1: consecutive steps of the loop are this many row tiles apart (>= 1)
   const unsigned* ready;    // mode 1: per 256-row tile of A, a counter that reaches ready_target once the
   unsigned ready_target;    //         tile's rows have all arrived (all-gather -> GEMM); null = rows are local
+  // mode 0, optional in-kernel dispatch (null pull_xq = A is already in place): warp 3 of every CTA
+  // takes row tickets, copies the row's E4M3 bytes peer -> shared -> A with bulk copies and its scale
+  // words through registers, and counts the row into its 256-row tile; the load lane acquires a
+  // tile's count before the tile's first TMA read (campaigns/mok/port/comm/comm.cu:105-123 gives the
+  // reference's megakernel the same dispatch role)
+  const uint8_t* const* pull_xq;        // per rank: u8 [tokens, K]
+  const uint32_t* const* pull_sc_rows;  // per rank: u32 [tokens, K / 128], one run of scale words per token
+  const int* pull_peer_rank;
+  const int* pull_token_idx;
+  uint8_t* pull_dst;                    // the A operand
+  uint8_t* pull_dst_sc;                 // its scale tensor
+  unsigned* pull_ready;                 // [max_m_tiles] zeroed by the launcher; 256 = tile complete
+  unsigned* pull_ticket;                // zeroed by the launcher
+  int pull_row_bytes;                   // K
   float limit;              // mode 0: gate <= limit, |up| <= limit before the activation; +inf = unclamped
   int max_m_tiles;          // capacity / 256
   int k_steps;
@@ -288,6 +303,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     mbar_init(smem_u32(&bars->acc_full), 1);
     mbar_init(smem_u32(&bars->acc_empty), 2 * kEpilogueWarps);
     mbar_init(smem_u32(&bars->drain), 1);
+    for (int s = 0; s < 8; ++s) mbar_init(smem_u32(&bars->pull[s]), 1);
     fence_mbar_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -320,6 +336,19 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank), m_tiles_live, m_rot, m_stride);
         const int a_blk = t.a_blk, b_blk0 = t.b_blk0;
         const int b_blk = b_blk0 + static_cast<int>(cta_rank);
+        if (MODE == 0 && p.pull_xq != nullptr) {
+          const unsigned* flag = p.pull_ready + (a_blk >> 1);
+          const long long t0 = clock64();
+          while (ld_acquire_gpu_u32(flag) < 256u) {
+            if (clock64() - t0 > kWaitBudgetCycles / 2 || ld_volatile_i32(&p.status->code) != 0) {
+              report_failure(p.status, ST_TIMEOUT_COUNTER, 311, ld_acquire_gpu_u32(flag), 256u);
+              ok = false;
+              break;
+            }
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         if (MODE == 1 && p.ready != nullptr) {
           // rows pushed by a peer are usable once its counter increment (a release at system scope,
           // examples/comm-overlap README "AllGather protocol") is observed; then order the TMA reads after it
@@ -439,6 +468,90 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
           if (clock64() - t0 > 20000000LL) break;
         }
       }
+    } else if (MODE == 0 && warp >= 2 && p.pull_xq != nullptr) {
+      // ---------------------------------------------------------- dispatch warps (two per CTA)
+      // A ticket is a chunk of 32 consecutive rows (an eighth of a row tile): lane l holds row l's
+      // source, the rows stream through a four-stage ring with three copies in flight, and the
+      // chunk is counted into its tile once all of its stores have completed.
+      constexpr int S = 4;
+      const int dw = warp - 2;
+      const uint32_t rb = static_cast<uint32_t>(p.pull_row_bytes);
+      const uint32_t ring = smem_base + kOffStaging + static_cast<uint32_t>(dw) * S * rb;   // staging is unused in mode 0
+      uint64_t* pbar = bars->pull + dw * S;
+      const int col_blocks = p.pull_row_bytes >> 7;
+      const int rows_live = m_tiles_live * 256;
+      uint32_t sc_word[S];
+      bool live[S];
+      uint32_t parity = 0;
+      bool ok = true;
+      while (ok) {
+        int base = 0;
+        if (lane == 0) base = static_cast<int>(atomicAdd(p.pull_ticket, 32u));
+        base = __shfl_sync(0xFFFFFFFFu, base, 0);
+        if (base >= rows_live) break;
+        const int my_src = p.pull_peer_rank[base + lane];
+        const int my_tok = my_src >= 0 ? p.pull_token_idx[base + lane] : 0;
+        auto issue = [&](int i, int s) {
+          const int src = __shfl_sync(0xFFFFFFFFu, my_src, i);
+          const int64_t t = __shfl_sync(0xFFFFFFFFu, my_tok, i);
+          live[s] = src >= 0;
+          sc_word[s] = 0u;
+          if (!live[s]) return;
+          if (lane == 0) {
+            // the store that last read this stage was committed at least one retire ago
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            const uint32_t bar = smem_u32(&pbar[s]);
+            mbar_arrive_expect_tx(bar, rb);
+            bulk_load(ring + static_cast<uint32_t>(s) * rb, p.pull_xq[src] + t * rb, rb, bar);
+          }
+          if (lane < col_blocks) sc_word[s] = p.pull_sc_rows[src][t * col_blocks + lane];
+        };
+        auto retire = [&](int i, int s) {
+          const int r = base + i;
+          uint8_t* dst = p.pull_dst + static_cast<size_t>(r) * rb;
+          if (live[s]) {
+            if (lane == 0) {
+              if (!mbar_wait(smem_u32(&pbar[s]), (parity >> s) & 1u, p.status, ST_TIMEOUT_FULL, 330 + s)) ok = false;
+              if (ok) {
+                fence_proxy_async_smem();
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                             "r"(ring + static_cast<uint32_t>(s) * rb), "r"(rb)
+                             : "memory");
+              }
+            }
+            parity ^= 1u << s;
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+          } else {
+            uint4* d = reinterpret_cast<uint4*>(dst);
+            for (int v = lane; v < static_cast<int>(rb >> 4); v += 32) d[v] = make_uint4(0u, 0u, 0u, 0u);
+          }
+          // one group per retired row, so "at most one pending" always excludes the row before
+          if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          if (lane < col_blocks) {
+            const size_t off = static_cast<size_t>(r >> 7) * col_blocks * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4;
+            *reinterpret_cast<uint32_t*>(p.pull_dst_sc + off + static_cast<size_t>(lane) * 512) = sc_word[s];
+          }
+        };
+#pragma unroll 1
+        for (int i0 = 0; i0 < 32 + S; i0 += S) {
+#pragma unroll
+          for (int u = 0; u < S; ++u) {
+            const int i = i0 + u;                            // row issued now, into stage u
+            const int r = i - (S - 1);                       // row retired now, from stage (u + 1) % S
+            if (r >= 0 && r < 32 && ok) retire(r, (u + 1) % S);
+            if (i < 32 && ok) issue(i, u);
+          }
+        }
+        // chunk complete: its stores are in memory, then every lane's scale words, then the count
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        __syncwarp();
+        if (lane == 0 && ok) {
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          __threadfence();
+          red_release_gpu_add(p.pull_ready + (base >> 8), 32u);
+        }
+      }
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
   } else {
     // -------------------------------------------------------------- epilogue (both CTAs)
@@ -698,6 +811,24 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
   p.m_stride = a.m_stride < 1 ? 1 : a.m_stride;
   p.ready = a.ready;
   p.ready_target = a.ready_target;
+  p.pull_xq = nullptr;
+  if (a.pull_xq != nullptr) {
+    if (a.mode != 0 || a.bf16 || a.K > 4096 || !a.pull_sc_rows || !a.pull_peer_rank || !a.pull_token_idx ||
+        !a.pull_scratch)
+      return cudaErrorInvalidValue;
+    const size_t tiles = static_cast<size_t>(a.rows_capacity / 256);
+    cudaError_t merr = cudaMemsetAsync(a.pull_scratch, 0, (tiles + 1) * sizeof(unsigned), stream);
+    if (merr != cudaSuccess) return merr;
+    p.pull_xq = reinterpret_cast<const uint8_t* const*>(a.pull_xq);
+    p.pull_sc_rows = reinterpret_cast<const uint32_t* const*>(a.pull_sc_rows);
+    p.pull_peer_rank = a.pull_peer_rank;
+    p.pull_token_idx = a.pull_token_idx;
+    p.pull_dst = static_cast<uint8_t*>(const_cast<void*>(a.a_fp8));
+    p.pull_dst_sc = static_cast<uint8_t*>(const_cast<void*>(a.a_sc));
+    p.pull_ready = static_cast<unsigned*>(a.pull_scratch);
+    p.pull_ticket = static_cast<unsigned*>(a.pull_scratch) + tiles;
+    p.pull_row_bytes = a.K;
+  }
   p.limit = a.swiglu_limit > 0.0f ? a.swiglu_limit : HUGE_VALF;
   p.max_m_tiles = static_cast<int>(a.rows_capacity / 256);
   p.k_steps = static_cast<int>(k_steps);

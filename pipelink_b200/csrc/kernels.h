@@ -82,6 +82,12 @@ struct GroupedGemmArgs {
   unsigned ready_target = 0;
   bool bf16 = false;                 // pair variant, modes 0/1: a_fp8 / b_fp8 hold bf16, no scales, mode 0 writes bf16
   float swiglu_limit = 0.0f;         // mode 0: > 0 bounds gate from above and up from both sides
+  // pair variant, mode 0: dispatch inside the GEMM kernel (all null = A is already in place)
+  const void* const* pull_xq = nullptr;        // per rank: u8 [tokens, K]
+  const void* const* pull_sc_rows = nullptr;   // per rank: u32 [tokens, K / 128]
+  const int* pull_peer_rank = nullptr;
+  const int* pull_token_idx = nullptr;
+  void* pull_scratch = nullptr;                // u32 [rows_capacity / 256 + 1], zeroed by the launcher
   int m_stride = 1;                  // pair variant: row-tile distance between consecutive loop steps
   int m_rotation = 0;                // pair variant: 256-row tiles are visited starting this many tiles in
   int num_sms;

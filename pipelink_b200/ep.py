@@ -204,12 +204,6 @@ class EpMoKHost(mok.MoKHost):
         self.routes_local.copy_(inputs.experts)
         self.quantize_tokens()
 
-    def quantize_tokens(self):
-        super().quantize_tokens()
-        if self.precision != "bf16" and self.pull_variant == "bulk":
-            _lib.call("plb_ep_scale_rows", self.xsc.data_ptr(), self.shape.tokens, self.shape.hidden,
-                      self.xsc_rows.data_ptr(), mok._stream())
-
     def publish_routes(self):
         _lib.call("plb_ep_publish", self.routes_local.data_ptr(), self.routes_local.numel() * 4,
                   self.routes_peers.data_ptr(), self.rank, self.world, mok._stream())

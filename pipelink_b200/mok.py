@@ -176,6 +176,12 @@ class MoKHost:
         self.xsc = torch.empty((L_pad // 128, H // 128, 32, 16), **u8)
         self.xq_peers = torch.tensor([self.xq.data_ptr()] * world, dtype=torch.int64, device=self.device)
         self.xsc_peers = torch.tensor([self.xsc.data_ptr()] * world, dtype=torch.int64, device=self.device)
+        # the same scale words with one contiguous run per token (what the bulk-copy dispatch fetches)
+        self.xsc_rows = torch.empty((L_pad, H // 128), dtype=torch.int32, device=self.device)
+        self.xsc_rows_peers = torch.tensor([self.xsc_rows.data_ptr()] * world, dtype=torch.int64, device=self.device)
+        self.dispatch_scratch = torch.zeros(P // 256 + 1, dtype=torch.int32, device=self.device)
+        # dispatch inside the gate/up GEMM kernel instead of a pull kernel in front of it
+        self.fused_dispatch = False
         self.buffers = {
             "x_routed_fp8": torch.empty((P, H), **u8),
             "x_routed_sc": torch.empty((P // 128, H // 128, 32, 16), **u8),
@@ -260,18 +266,24 @@ class MoKHost:
         rows = self._x_storage.shape[0]
         _lib.call("plb_mxfp8_quantize", self._x_storage.data_ptr(), rows, self.shape.hidden,
                   self.xq.data_ptr(), self.xsc.data_ptr(), None, None, _stream())
+        if self.pull_variant == "bulk" or self.fused_dispatch:
+            _lib.call("plb_ep_scale_rows", self.xsc.data_ptr(), rows, self.shape.hidden, self.xsc_rows.data_ptr(), _stream())
 
     def pull(self):
         """Dispatch: gather every scheduled row's E4M3 bytes and scale words (comm.cu:105-123)."""
-        s, b, sh = self.schedule, self.buffers, self.shape
         if self.precision == "bf16":
             return self.pull_bf16()
+        if self.fused_dispatch:
+            return                      # the gate/up GEMM kernel pulls its own rows
+        self.pull_now()
+
+    def pull_now(self):
+        s, b, sh = self.schedule, self.buffers, self.shape
         if self.pull_variant == "bulk" and sh.hidden <= 4096:
-            rows = getattr(self, "xsc_rows_peers", None)      # groups publish row-contiguous scale words
-            _lib.call("plb_ep_pull_rows_bulk", self.xq_peers.data_ptr(), (rows if rows is not None else self.xsc_peers).data_ptr(),
+            _lib.call("plb_ep_pull_rows_bulk", self.xq_peers.data_ptr(), self.xsc_rows_peers.data_ptr(),
                       s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),
                       self.capacity, sh.hidden, b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
-                      1 if rows is not None else 0, self.status.buf.data_ptr(), _stream())
+                      1, self.status.buf.data_ptr(), _stream())
             return
         _lib.call("plb_ep_pull_rows", self.xq_peers.data_ptr(), self.xsc_peers.data_ptr(),
                   s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.num_tokens.data_ptr(),
@@ -297,6 +309,14 @@ class MoKHost:
             _lib.call("plb_moe_gemm_gate_up_bf16", b["x_routed_bf16"].data_ptr(), w["w13_bf16"].data_ptr(),
                       s.block_expert.data_ptr(), s.num_tokens.data_ptr(), self.capacity, self.num_local_experts,
                       sh.intermediate, sh.hidden, b["hidden_routed_bf16"].data_ptr(), self.status.buf.data_ptr(), _stream())
+            return
+        if self.fused_dispatch:
+            _lib.call("plb_moe_gemm_gate_up_dispatch", self.xq_peers.data_ptr(), self.xsc_rows_peers.data_ptr(),
+                      s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), b["x_routed_fp8"].data_ptr(),
+                      b["x_routed_sc"].data_ptr(), w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(),
+                      s.block_expert.data_ptr(), s.num_tokens.data_ptr(), self.capacity, self.num_local_experts,
+                      sh.intermediate, sh.hidden, b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(),
+                      self.dispatch_scratch.data_ptr(), self.status.buf.data_ptr(), _stream())
             return
         _lib.call("plb_moe_gemm_gate_up", b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
                   w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(), s.block_expert.data_ptr(),
@@ -348,6 +368,8 @@ class MoKHost:
     def gemm_gate_up_train(self):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
         self.select_activation()
+        if self.fused_dispatch:
+            self.pull_now()             # the saving epilogue has no fused dispatch: pull in front of it
         _lib.call("plb_moe_gemm_gate_up_train", b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
                   w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(), s.block_expert.data_ptr(), s.num_tokens.data_ptr(),
                   self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,

@@ -414,3 +414,33 @@ def test_bf16_routed_precision_vs_oracle(native_lib, shape_args, generation, lim
         assert np.isfinite(have).all() and st["relative"] <= tol, (name, st)
     with pytest.raises(ValueError):
         host.forward(inputs, train=True)
+
+
+@pytest.mark.parametrize("shape_args,generation", [(("fd-small", 4, 256, 256, 2, 384), 1), (("fd-empty", 8, 512, 256, 2, 300), 3),
+                                                   (("fd-wide", 8, 4096, 256, 4, 1024), 2)])
+def test_fused_dispatch_equals_pull_then_gemm(native_lib, shape_args, generation):
+    """The gate/up GEMM that pulls its own rows (a dispatch warp per CTA, tiles gated on row counts)
+    leaves the same routed rows, hidden activations and output, bit for bit, as the pull kernel
+    followed by the plain GEMM; repeated steps reuse the zeroed counters correctly."""
+    from pipelink_b200 import mok
+    mok.set_gemm_variant(2)
+    shape = mok.Shape(*shape_args)
+    torch.manual_seed(31)
+    E, H, I = shape.experts, shape.hidden, shape.intermediate
+    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.05).to(torch.bfloat16)
+    wg, wu, wd = mk(E, I, H), mk(E, I, H), mk(E, H, I)
+    plain, fused = mok.MoKHost(shape), mok.MoKHost(shape)
+    fused.fused_dispatch = True
+    for h in (plain, fused):
+        h.load_weights(wg, wu, wd)
+    for step in range(3):
+        inputs = mok.MoKHost.new_inputs(shape, generation + step, "cuda")
+        fused.buffers["x_routed_fp8"].fill_(77)
+        want, got = plain.forward(inputs), fused.forward(inputs)
+        torch.cuda.synchronize()
+        total = int(plain.schedule.num_tokens.item())
+        for name in ("x_routed_data", "hidden_routed_data"):
+            assert torch.equal(got[name][:total], want[name][:total]), (step, name)
+        for name in ("x_routed_scale", "hidden_routed_scale"):
+            assert torch.equal(got[name][: total // 128], want[name][: total // 128]), (step, name)
+        assert torch.equal(got["output"].view(torch.int16), want["output"].view(torch.int16)), step
