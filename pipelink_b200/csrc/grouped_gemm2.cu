@@ -61,6 +61,12 @@ constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes2 = kOffBars + kBarrierBytes + 1024;
 static_assert(kOffSf % 1024 == 0 && kOffStaging % 16 == 0, "shared memory layout");
 constexpr int kThreads2 = 384;
+// Register hand-over between the roles. ptxas gives every thread 168 registers (launch bounds of 384
+// threads, one CTA per SM), the CTA's pool is what it was launched with, and setmaxnreg.inc blocks
+// until the pool can serve it: warps 0-3 must therefore drop to 56 before the eight epilogue warps
+// can rise to 224. Any larger value for warps 0-3 makes the kernel wait forever.
+constexpr int kRegsAtLaunch = 168, kRegsHelpers = 56, kRegsEpilogue = 224;
+static_assert(kThreads2 * kRegsAtLaunch - 128 * kRegsHelpers >= 256 * kRegsEpilogue, "register pool of the CTA");
 constexpr int kEpilogueWarps = 8;
 constexpr int kTmemCols = 512;
 constexpr int kSfColBase = 256;
@@ -74,7 +80,6 @@ struct Barriers2 {
   uint64_t acc_full;        // per CTA: 1 arrival (leader's commit)
   uint64_t acc_empty;       // used in the leader CTA: one arrival per epilogue warp of the pair
   uint64_t drain;
-  uint64_t pull[8];         // mode 0 with the in-kernel dispatch: one per stage of the two dispatch warps' rings
   uint32_t tmem_base;
   uint32_t pad;
 };
@@ -101,10 +106,10 @@ struct Params2 {
   int m_stride;             // modes 0/1: consecutive steps of the loop are this many row tiles apart (>= 1)
   const unsigned* ready;    // mode 1: per 256-row tile of A, a counter that reaches ready_target once the
   unsigned ready_target;    //         tile's rows have all arrived (all-gather -> GEMM); null = rows are local
-  // mode 0, optional in-kernel dispatch (null pull_xq = A is already in place): warp 3 of every CTA
-  // takes row tickets, copies the row's E4M3 bytes peer -> shared -> A with bulk copies and its scale
-  // words through registers, and counts the row into its 256-row tile; the load lane acquires a
-  // tile's count before the tile's first TMA read (campaigns/mok/port/comm/comm.cu:105-123 gives the
+  // mode 0, optional in-kernel dispatch (null pull_xq = A is already in place): warps 2 and 3 of every
+  // CTA take tickets of 32 rows, copy each row's E4M3 bytes and scale words peer -> A through
+  // registers, and count the chunk into its 256-row tile; the load lane acquires a tile's count
+  // before the tile's first TMA read (campaigns/mok/port/comm/comm.cu:105-123 gives the
   // reference's megakernel the same dispatch role)
   const uint8_t* const* pull_xq;        // per rank: u8 [tokens, K]
   const uint32_t* const* pull_sc_rows;  // per rank: u32 [tokens, K / 128], one run of scale words per token
@@ -303,7 +308,6 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     mbar_init(smem_u32(&bars->acc_full), 1);
     mbar_init(smem_u32(&bars->acc_empty), 2 * kEpilogueWarps);
     mbar_init(smem_u32(&bars->drain), 1);
-    for (int s = 0; s < 8; ++s) mbar_init(smem_u32(&bars->pull[s]), 1);
     fence_mbar_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -324,7 +328,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
   if (warp < 4) {
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<kRegsHelpers>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------- TMA producer (both CTAs)
       int stage = 0;
@@ -471,91 +475,57 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     } else if (MODE == 0 && warp >= 2 && p.pull_xq != nullptr) {
       // ---------------------------------------------------------- dispatch warps (two per CTA)
       // A ticket is a chunk of 32 consecutive rows (an eighth of a row tile): lane l holds row l's
-      // source, the rows stream through a four-stage ring with three copies in flight, and the
-      // chunk is counted into its tile once all of its stores have completed.
-      constexpr int S = 4;
-      const int dw = warp - 2;
-      const uint32_t rb = static_cast<uint32_t>(p.pull_row_bytes);
-      const uint32_t ring = smem_base + kOffStaging + static_cast<uint32_t>(dw) * S * rb;   // staging is unused in mode 0
-      uint64_t* pbar = bars->pull + dw * S;
+      // source; each row crosses as 16-byte loads into registers and 16-byte stores (the load/store
+      // path is idle while the TMA unit and shared memory feed the tensor pipe: bulk copies here
+      // cost the mainloop as much as the separate pull kernel they replaced); the chunk is counted
+      // into its tile after a fence.
+      const int vecs = p.pull_row_bytes >> 4;                  // <= 256
       const int col_blocks = p.pull_row_bytes >> 7;
       const int rows_live = m_tiles_live * 256;
-      uint32_t sc_word[S];
-      bool live[S];
-      uint32_t parity = 0;
-      bool ok = true;
-      while (ok) {
+      for (;;) {
         int base = 0;
         if (lane == 0) base = static_cast<int>(atomicAdd(p.pull_ticket, 32u));
         base = __shfl_sync(0xFFFFFFFFu, base, 0);
         if (base >= rows_live) break;
         const int my_src = p.pull_peer_rank[base + lane];
         const int my_tok = my_src >= 0 ? p.pull_token_idx[base + lane] : 0;
-        auto issue = [&](int i, int s) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
           const int src = __shfl_sync(0xFFFFFFFFu, my_src, i);
           const int64_t t = __shfl_sync(0xFFFFFFFFu, my_tok, i);
-          live[s] = src >= 0;
-          sc_word[s] = 0u;
-          if (!live[s]) return;
-          if (lane == 0) {
-            // the store that last read this stage was committed at least one retire ago
-            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            const uint32_t bar = smem_u32(&pbar[s]);
-            mbar_arrive_expect_tx(bar, rb);
-            bulk_load(ring + static_cast<uint32_t>(s) * rb, p.pull_xq[src] + t * rb, rb, bar);
-          }
-          if (lane < col_blocks) sc_word[s] = p.pull_sc_rows[src][t * col_blocks + lane];
-        };
-        auto retire = [&](int i, int s) {
           const int r = base + i;
-          uint8_t* dst = p.pull_dst + static_cast<size_t>(r) * rb;
-          if (live[s]) {
-            if (lane == 0) {
-              if (!mbar_wait(smem_u32(&pbar[s]), (parity >> s) & 1u, p.status, ST_TIMEOUT_FULL, 330 + s)) ok = false;
-              if (ok) {
-                fence_proxy_async_smem();
-                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
-                             "r"(ring + static_cast<uint32_t>(s) * rb), "r"(rb)
-                             : "memory");
-              }
+          uint4* dst = reinterpret_cast<uint4*>(p.pull_dst + static_cast<size_t>(r) * p.pull_row_bytes);
+          uint32_t word = 0u;
+          const uint4* from = src >= 0 ? reinterpret_cast<const uint4*>(p.pull_xq[src] + t * p.pull_row_bytes) : nullptr;
+          if (src >= 0 && lane < col_blocks) word = p.pull_sc_rows[src][t * col_blocks + lane];
+#pragma unroll 1
+          for (int v0 = 0; v0 < vecs; v0 += 128) {           // 2 KB of the row per pass
+            uint4 tmp[4];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int idx = v0 + v * 32 + lane;
+              tmp[v] = (from != nullptr && idx < vecs) ? from[idx] : make_uint4(0u, 0u, 0u, 0u);
             }
-            parity ^= 1u << s;
-            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-          } else {
-            uint4* d = reinterpret_cast<uint4*>(dst);
-            for (int v = lane; v < static_cast<int>(rb >> 4); v += 32) d[v] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int idx = v0 + v * 32 + lane;
+              if (idx < vecs) dst[idx] = tmp[v];
+            }
           }
-          // one group per retired row, so "at most one pending" always excludes the row before
-          if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           if (lane < col_blocks) {
             const size_t off = static_cast<size_t>(r >> 7) * col_blocks * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4;
-            *reinterpret_cast<uint32_t*>(p.pull_dst_sc + off + static_cast<size_t>(lane) * 512) = sc_word[s];
-          }
-        };
-#pragma unroll 1
-        for (int i0 = 0; i0 < 32 + S; i0 += S) {
-#pragma unroll
-          for (int u = 0; u < S; ++u) {
-            const int i = i0 + u;                            // row issued now, into stage u
-            const int r = i - (S - 1);                       // row retired now, from stage (u + 1) % S
-            if (r >= 0 && r < 32 && ok) retire(r, (u + 1) % S);
-            if (i < 32 && ok) issue(i, u);
+            *reinterpret_cast<uint32_t*>(p.pull_dst_sc + off + static_cast<size_t>(lane) * 512) = word;
           }
         }
-        // chunk complete: its stores are in memory, then every lane's scale words, then the count
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        // every lane's stores, then one release increment for the chunk
+        __threadfence();
         __syncwarp();
-        if (lane == 0 && ok) {
-          asm volatile("fence.proxy.async.global;" ::: "memory");
-          __threadfence();
-          red_release_gpu_add(p.pull_ready + (base >> 8), 32u);
-        }
+        if (lane == 0) red_release_gpu_add(p.pull_ready + (base >> 8), 32u);
       }
-      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
   } else {
     // -------------------------------------------------------------- epilogue (both CTAs)
-    setmaxnreg_inc<224>();
+    setmaxnreg_inc<kRegsEpilogue>();
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
     const int ch = (warp - 4) >> 2;       // which half of the accumulator columns
     const uint32_t acc_empty_leader = mapa_shared(smem_u32(&bars->acc_empty), 0);
