@@ -149,3 +149,34 @@ def test_exchange_rejects_a_malformed_handle():
     from pipelink_b200 import ep
     with pytest.raises(ValueError):
         ep.exchange_handles(b"short", 2)
+
+
+def test_tp_layout_regions_are_disjoint_and_aligned():
+    """Slab layout of the tensor-parallel compositions: two parities of counters, gathered buffers
+    and receive slots, none overlapping; shapes that do not tile are refused."""
+    from pipelink_b200.tp import TILE, TpLayout
+    lay = TpLayout(2048, 1024, 1024, 4)
+    regions = [(lay.flags, 16)]
+    for p in range(2):
+        regions += [(lay.ready[p], 4 * (2048 // TILE)), (lay.gather[p], 2048 * 1024 * 2), (lay.slots[p], 2048 * 1024 * 2)]
+    regions.sort()
+    for (a, n), (b, _) in zip(regions, regions[1:]):
+        assert a % 1024 == 0 and a + n <= b
+    assert regions[-1][0] + regions[-1][1] <= lay.nbytes
+    for bad in ((2048 + 256, 1024, 1024, 4), (2048, 1024 + 256, 1024, 4), (2048, 1024, 1024 + 128, 4)):
+        with pytest.raises(ValueError):
+            TpLayout(*bad)
+
+
+def test_tp_reduce_scatter_row_maps():
+    """Row i of a rank's partial product goes to owner i // (M / W), slot row (i % (M / W)) * W + rank:
+    together the W ranks fill every [row, source] slot of every owner exactly once."""
+    m, w = 1024, 4
+    ms = m // w
+    seen = set()
+    for rank in range(w):
+        for i in range(m):
+            owner, dest = i // ms, (i % ms) * w + rank
+            assert 0 <= dest < ms * w
+            seen.add((owner, dest))
+    assert len(seen) == w * ms * w
