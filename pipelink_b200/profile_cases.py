@@ -4,6 +4,10 @@
 ``python -m pipelink_b200.profile_cases attention``  causal prefill, S=8192, 32 query / 8 KV heads, d=128
 ``python -m pipelink_b200.profile_cases moe``        MoE forward, 4096 tokens of the headline shape
 
+``torchrun --nproc-per-node N -m pipelink_b200.profile_cases ep-phases``
+                                                     device time of every phase of the expert-parallel forward
+                                                     (CUDA events; a timing tool, not a profiler case)
+
 Each case holds a few GB on the device at most, touches more than the L2 holds, and launches the
 kernel of interest a handful of times.
 """
@@ -58,7 +62,60 @@ def moe_case(dev, tokens=4096):
     print("moe ok", float(out.float().abs().mean()))
 
 
+def ep_phases_case(tokens=8192, steps=10):
+    """One rank per GPU under torchrun. Prints, for each phase of the expert-parallel forward step at
+    the headline expert shape, the mean / min / max over ranks of its device time."""
+    import os
+
+    import torch.distributed as dist
+
+    from . import ep, mok
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    base = mok.CONFIG2
+    shape = mok.Shape("ep-phases", base.experts, base.hidden, base.intermediate, base.topk, tokens)
+    session = ep.BenchSession(shape, dev, rank, world)
+    h = session.host
+    phases = [("quantise", h.quantize_tokens), ("publish routes", h.publish_routes), ("barrier", h.barrier),
+              ("schedule", h.build_schedule), ("pull", h.pull), ("gate/up GEMM", h.gemm_gate_up),
+              ("down GEMM + push", h.gemm_down_push), ("barrier ", h.barrier), ("epilogue", h.fwd_epilogue)]
+    for _ in range(5):
+        session.step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    acc = [0.0] * len(phases)
+    for _ in range(steps):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(phases) + 1)]
+        evs[0].record()
+        for i, (_, fn) in enumerate(phases):
+            fn()
+            evs[i + 1].record()
+        torch.cuda.synchronize()
+        for i in range(len(phases)):
+            acc[i] += evs[i].elapsed_time(evs[i + 1]) / steps
+    mine = torch.tensor(acc, device=dev)
+    every = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    h.status.check("ep-phases")
+    if rank == 0:
+        m = torch.stack(every).cpu()
+        print(f"world {world}, tokens per rank {tokens}, rows on rank 0: {int(h.schedule.num_tokens.item())}")
+        for i, (name, _) in enumerate(phases):
+            print(f"{name:18s} mean {m[:, i].mean():.3f}  min {m[:, i].min():.3f}  max {m[:, i].max():.3f} ms")
+        print(f"{'sum of means':18s} {float(m.mean(0).sum()):.3f} ms")
+    dist.barrier()
+    session.group.close()
+    dist.destroy_process_group()
+
+
 def main(argv):
+    if len(argv) >= 2 and argv[1] == "ep-phases":
+        if not torch.cuda.is_available():
+            raise SystemExit("profile_cases needs a CUDA device")
+        return ep_phases_case()
     if len(argv) < 2 or argv[1] not in ("decode", "attention", "moe"):
         raise SystemExit(__doc__)
     if not torch.cuda.is_available():
