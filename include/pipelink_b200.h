@@ -416,6 +416,25 @@ int plb_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks, i
                    int rank, int world, void* const* k_gather_peers, void* const* v_gather_peers,
                    void* const* ready_peers, int ctas, void* stream);
 
+/* Receive streams for the combine push. plb_moe_gemm_down_push writes row p to
+ * `token * topk + slot` of its home rank: 8 KB rows scattered over every peer's combine buffer,
+ * which on eight GPUs costs almost twice the time of the same bytes written in order. With
+ * streams, row p goes to position rank * stream_cap + (earlier rows of this rank with the same
+ * home) of the home rank's receive buffer [world * stream_cap, hidden], and the home rank reads
+ * its (token, slot) rows through an index.
+ * plb_ep_stream_rows (after the schedule): stream_row[p] = that position (-1 for padding rows), to
+ * be passed to plb_moe_gemm_down_push as dest_row with the receive buffers as combine_peers; and
+ * index_peers[peer_rank[p]][dest_row[p]] = stream_row[p], a 4-byte write to the home rank.
+ * stream_cap >= rows any one rank can send to any one home (tokens * topk is always enough).
+ * plb_moe_fwd_epilogue_indexed (after the group barrier): plb_moe_fwd_epilogue with slot
+ * t * topk + j read from rows_bf16[row_index[t * topk + j]]. Same arithmetic, same result. */
+int plb_ep_stream_rows(const int32_t* peer_rank, const int32_t* dest_row, const int32_t* num_tokens, int64_t capacity,
+                       int rank, int world, int64_t stream_cap, int32_t* stream_row, void* const* index_peers,
+                       void* stream);
+int plb_moe_fwd_epilogue_indexed(const void* y_shared_bf16, const void* rows_bf16, const int32_t* row_index,
+                                 const float* router_weights, int64_t tokens, int topk, int64_t hidden,
+                                 void* out_bf16, void* stream);
+
 /* Tensor-parallel GEMM compositions (examples/comm-overlap: `ag` = C_r = gather(A_q) @ B_r^T,
  * `rs` = rows [r*M/W, (r+1)*M/W) of sum_q A_q @ B_q^T; README "AllGather protocol" and
  * "ReduceScatter protocol"), bf16 operands, fp32 accumulation, bf16 results.

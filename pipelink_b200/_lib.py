@@ -63,6 +63,10 @@ PROTOTYPES = {
     "plb_ep_pull_rows_bulk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                       c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "plb_ep_scale_rows": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "plb_ep_stream_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p, c_void_p,
+                                   c_void_p]),
+    "plb_moe_fwd_epilogue_indexed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_void_p,
+                                             c_void_p]),
     "plb_tp_push_rows": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "plb_tp_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                  c_int, c_void_p, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),

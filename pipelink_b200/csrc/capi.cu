@@ -373,6 +373,27 @@ int plb_ep_scale_rows(const void* xsc, int64_t tokens, int64_t hidden, void* sca
                                           static_cast<cudaStream_t>(stream)));
 }
 
+int plb_ep_stream_rows(const int32_t* peer_rank, const int32_t* dest_row, const int32_t* num_tokens, int64_t capacity,
+                       int rank, int world, int64_t stream_cap, int32_t* stream_row, void* const* index_peers,
+                       void* stream) {
+  if (!peer_rank || !dest_row || !num_tokens || !stream_row || !index_peers || capacity < 0 || world < 1 ||
+      world > 32 || rank < 0 || rank >= world || stream_cap < 1 || stream_cap * world > 2147483647LL)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_ep_stream_rows(peer_rank, dest_row, num_tokens, capacity, rank, world, stream_cap,
+                                              stream_row, reinterpret_cast<int* const*>(index_peers),
+                                              static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_fwd_epilogue_indexed(const void* y_shared_bf16, const void* rows_bf16, const int32_t* row_index,
+                                 const float* router_weights, int64_t tokens, int topk, int64_t hidden,
+                                 void* out_bf16, void* stream) {
+  if (tokens < 0 || topk < 1 || hidden <= 0 || hidden % 8) return PLB_E_ARGUMENT;
+  if (!rows_bf16 || !row_index || !router_weights || !out_bf16) return PLB_E_ARGUMENT;
+  if (!aligned16(rows_bf16) || !aligned16(out_bf16) || !aligned16(y_shared_bf16)) return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_weighted_combine(rows_bf16, router_weights, y_shared_bf16, tokens, topk, hidden,
+                                                out_bf16, static_cast<cudaStream_t>(stream), row_index));
+}
+
 int plb_sym_alloc(size_t bytes, void** out) {
   if (!out || bytes == 0) return PLB_E_ARGUMENT;
   void* p = nullptr;

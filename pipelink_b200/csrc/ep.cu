@@ -314,6 +314,54 @@ ep_pull_rows_bulk_kernel(const uint8_t* const* __restrict__ xq_peers, const uint
   __syncwarp();
 }
 
+// Receive streams for the combine push. Writing row p to `token * topk + slot` of its home rank
+// scatters 8 KB rows over the whole combine buffer of every peer; measured on eight GPUs that costs
+// 1.31 ms where the same bytes written in order cost 0.75 ms. Here every (source, home) pair gets a
+// stream in the home rank's receive buffer: row p of this rank goes to position
+// rank * stream_cap + (number of earlier rows with the same home), and the home rank learns where
+// each (token, slot) landed through a 4-byte index written beside it.
+// One CTA: the ranks are a running count per home over the schedule's row order.
+__global__ void __launch_bounds__(1024)
+ep_stream_rows_kernel(const int* __restrict__ peer_rank, const int* __restrict__ dest_row,
+                      const int* __restrict__ num_rows_dev, int64_t capacity, int rank, int world,
+                      int64_t stream_cap, int* __restrict__ stream_row, int* const* __restrict__ index_peers) {
+  __shared__ int warp_count[32][32];   // [warp][home]
+  __shared__ int base[32];             // rows already counted per home
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int64_t rows = *num_rows_dev;
+  if (rows > capacity) rows = capacity;
+  if (threadIdx.x < 32) base[threadIdx.x] = 0;
+  __syncthreads();
+  for (int64_t p0 = 0; p0 < rows; p0 += 1024) {
+    const int64_t p = p0 + threadIdx.x;
+    const int h = p < rows ? peer_rank[p] : -1;
+    const unsigned same = __match_any_sync(0xFFFFFFFFu, h);
+    const int before = __popc(same & ((1u << lane) - 1u));
+    if (lane < world) warp_count[warp][lane] = 0;
+    __syncwarp();
+    if (h >= 0 && before == 0) warp_count[warp][h] = __popc(same);
+    __syncthreads();
+    int pos = -1;
+    if (h >= 0) {
+      int earlier = base[h];
+      for (int w = 0; w < warp; ++w) earlier += warp_count[w][h];
+      pos = earlier + before;
+    }
+    __syncthreads();
+    if (threadIdx.x < world) {
+      int add = 0;
+      for (int w = 0; w < 32; ++w) add += warp_count[w][threadIdx.x];
+      base[threadIdx.x] += add;
+    }
+    if (p < rows) {
+      const int row = h >= 0 ? static_cast<int>(static_cast<int64_t>(rank) * stream_cap + pos) : -1;
+      stream_row[p] = row;
+      if (h >= 0) index_peers[h][dest_row[p]] = row;
+    }
+    __syncthreads();
+  }
+}
+
 // All-gather push (examples/comm-overlap README, "AllGather protocol": a chunk is copied to one
 // peer, every writing thread's stores are fenced at system scope, one release increment lands on
 // the peer's row-block counter). A task is one part of one 256-row block for one consumer; a
@@ -440,6 +488,16 @@ cudaError_t launch_scale_rows(const void* xsc, int64_t tokens, int hidden, void*
   if (blocks > 1184) blocks = 1184;
   scale_rows_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint8_t*>(xsc), tokens, hidden >> 7,
                                                                   static_cast<uint32_t*>(out));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_stream_rows(const int* peer_rank, const int* dest_row, const int* num_rows_dev, int64_t capacity,
+                                  int rank, int world, int64_t stream_cap, int* stream_row, int* const* index_peers,
+                                  cudaStream_t stream) {
+  if (capacity == 0) return cudaSuccess;
+  if (world < 1 || world > 32) return cudaErrorInvalidValue;
+  ep_stream_rows_kernel<<<1, 1024, 0, stream>>>(peer_rank, dest_row, num_rows_dev, capacity, rank, world, stream_cap,
+                                                stream_row, index_peers);
   return cudaGetLastError();
 }
 

@@ -27,7 +27,7 @@ cudaError_t launch_pack_gate_up(const void* gate_fp8, const void* gate_sc, const
                                 void* w13_fp8, void* w13_sc, cudaStream_t stream);
 cudaError_t launch_weighted_combine(const void* combine_bf16, const float* router_weights,
                                     const void* y_shared_bf16, int64_t tokens, int topk,
-                                    int64_t hidden, void* out_bf16, cudaStream_t stream);
+                                    int64_t hidden, void* out_bf16, cudaStream_t stream, const int* index = nullptr);
 
 // ---- routing schedule (schedule.cu)
 struct ScheduleArgs {
@@ -121,6 +121,9 @@ cudaError_t launch_ep_pull_rows_bulk(const void* const* xq_peers, const void* co
                                      void* x_routed_fp8, void* x_routed_sc, int scale_rows, Status* status,
                                      cudaStream_t stream);
 cudaError_t launch_scale_rows(const void* xsc, int64_t tokens, int hidden, void* out, cudaStream_t stream);
+cudaError_t launch_ep_stream_rows(const int* peer_rank, const int* dest_row, const int* num_rows_dev, int64_t capacity,
+                                  int rank, int world, int64_t stream_cap, int* stream_row, int* const* index_peers,
+                                  cudaStream_t stream);
 cudaError_t launch_tp_push_rows(const void* src, int blocks, int64_t block_bytes, int parts, int rank, int world,
                                 void* const* gather_peers, unsigned* const* ready_peers, int ctas,
                                 cudaStream_t stream);

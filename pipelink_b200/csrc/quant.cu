@@ -267,13 +267,14 @@ pack_gate_up_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict_
 }
 
 // out[t, c] = bf16( (y_shared ? y_shared[t,c] : 0) + sum_{j<k} w[t,j] * combine[t*k+j, c] )
+// (`index` non-null: the row of slot t*k+j is combine[index[t*k+j]], rows received in arrival order)
 // with every multiply and add rounded separately in fp32 and j ascending, so the
 // result is a pure function of its inputs (deterministic combine order).
 template <int TOPK>  // 0 = runtime top-k; otherwise the loads of all slots are issued together
 __global__ void __launch_bounds__(kThreads)
 weighted_combine_kernel(const uint4* __restrict__ combine, const float* __restrict__ w,
                         const uint4* __restrict__ y_shared, int64_t tokens, int topk_rt,
-                        int64_t hidden, uint4* __restrict__ out) {
+                        int64_t hidden, uint4* __restrict__ out, const int* __restrict__ index) {
   const int topk = TOPK > 0 ? TOPK : topk_rt;
   const int64_t vec_per_row = hidden >> 3;
   const int64_t total = tokens * vec_per_row;
@@ -293,7 +294,7 @@ weighted_combine_kernel(const uint4* __restrict__ combine, const float* __restri
 #pragma unroll
       for (int s = 0; s < TOPK; ++s) {
         ws[s] = w[t * TOPK + s];
-        c[s] = combine[(t * TOPK + s) * vec_per_row + j];
+        c[s] = combine[static_cast<int64_t>(index != nullptr ? index[t * TOPK + s] : t * TOPK + s) * vec_per_row + j];
       }
 #pragma unroll
       for (int s = 0; s < TOPK; ++s) {
@@ -305,7 +306,7 @@ weighted_combine_kernel(const uint4* __restrict__ combine, const float* __restri
     } else
     for (int s = 0; s < topk; ++s) {
       const float ws = w[t * topk + s];
-      const uint4 c = combine[(t * topk + s) * vec_per_row + j];
+      const uint4 c = combine[static_cast<int64_t>(index != nullptr ? index[t * topk + s] : t * topk + s) * vec_per_row + j];
       const float f[8] = {bf16_lo(c.x), bf16_hi(c.x), bf16_lo(c.y), bf16_hi(c.y),
                           bf16_lo(c.z), bf16_hi(c.z), bf16_lo(c.w), bf16_hi(c.w)};
 #pragma unroll
@@ -404,14 +405,14 @@ cudaError_t launch_pack_gate_up(const void* gate_fp8, const void* gate_sc, const
 
 cudaError_t launch_weighted_combine(const void* combine_bf16, const float* router_weights,
                                     const void* y_shared_bf16, int64_t tokens, int topk,
-                                    int64_t hidden, void* out_bf16, cudaStream_t stream) {
+                                    int64_t hidden, void* out_bf16, cudaStream_t stream, const int* index) {
   if (tokens == 0) return cudaSuccess;
   const int grid = grid_for(tokens * (hidden >> 3));
   const uint4* c = static_cast<const uint4*>(combine_bf16);
   const uint4* y = static_cast<const uint4*>(y_shared_bf16);
   uint4* o = static_cast<uint4*>(out_bf16);
 #define PLB_COMBINE(K) \
-  weighted_combine_kernel<K><<<grid, kThreads, 0, stream>>>(c, router_weights, y, tokens, topk, hidden, o)
+  weighted_combine_kernel<K><<<grid, kThreads, 0, stream>>>(c, router_weights, y, tokens, topk, hidden, o, index)
   switch (topk) {
     case 1: PLB_COMBINE(1); break;
     case 2: PLB_COMBINE(2); break;

@@ -29,7 +29,7 @@ def _align(n, a=256):
 class SlabLayout:
     """Offsets of the peer-visible buffers inside one rank's symmetric slab."""
 
-    def __init__(self, shape: mok.Shape, world: int, train: bool = False):
+    def __init__(self, shape: mok.Shape, world: int, train: bool = False, stream: bool = False):
         L, H, k = shape.tokens, shape.hidden, shape.topk
         if L % 128:
             raise ValueError("tokens per rank must be a multiple of 128")
@@ -40,6 +40,10 @@ class SlabLayout:
         self.xsc_rows = off; off += _align(L * (H // 128) * 4)     # the same words, one contiguous run per token
         self.routes_all = off; off += _align(world * L * k * 4)
         self.combine = off; off += _align(L * k * H * 2)
+        self.stream = stream
+        if stream:  # receive streams of the combine push: one per source rank, rows in arrival order
+            self.recv = off; off += _align(world * L * k * H * 2)
+            self.recv_index = off; off += _align(L * k * 4)
         self.train = train
         if train:   # what the backward pass reads from / writes to a token's home rank
             self.x_bf16 = off; off += _align(L * H * 2)        # tokens, for the gate/up weight gradient
@@ -74,9 +78,9 @@ def sym_alloc(nbytes: int) -> int:
 class LocalGroup:
     """`world` ranks emulated in one process: every slab is an allocation on the current device."""
 
-    def __init__(self, shape: mok.Shape, world: int, device, train: bool = False):
+    def __init__(self, shape: mok.Shape, world: int, device, train: bool = False, stream: bool = False):
         self.world, self.device, self.distributed = world, torch.device(device), False
-        self.layout = SlabLayout(shape, world, train)
+        self.layout = SlabLayout(shape, world, train, stream)
         self.slabs = [sym_alloc(self.layout.nbytes) for _ in range(world)]
 
     def ptrs_for(self, rank: int):
@@ -135,9 +139,10 @@ class IpcSlab:
 class IpcGroup:
     """One process per GPU; handles travel through ``torch.distributed`` (bootstrap only)."""
 
-    def __init__(self, shape: mok.Shape, rank: int, world: int, device, group=None, train: bool = False):
+    def __init__(self, shape: mok.Shape, rank: int, world: int, device, group=None, train: bool = False,
+                 stream: bool = False):
         self.world, self.rank, self.device, self.distributed = world, rank, torch.device(device), True
-        self.layout = SlabLayout(shape, world, train)
+        self.layout = SlabLayout(shape, world, train, stream)
         self.slab = IpcSlab(self.layout.nbytes, rank, world, group)
         self.peer_ptrs = self.slab.ptrs
 
@@ -164,11 +169,21 @@ class EpMoKHost(mok.MoKHost):
         ptrs = group.ptrs_for(rank)
         dev, L, H, k, W = self.device, shape.tokens, shape.hidden, shape.topk, group.world
         table = lambda off: torch.tensor([p + off for p in ptrs], dtype=torch.int64, device=dev)
+        me_ptr = ptrs[rank]
         self.flags_peers, self.xq_peers, self.xsc_peers = table(lay.flags), table(lay.xq), table(lay.xsc)
         self.routes_peers, self.combine_peers = table(lay.routes_all), table(lay.combine)
         self.xsc_rows_peers = table(lay.xsc_rows)
         self.xsc_rows = tensor_from_ptr(ptrs[rank] + lay.xsc_rows, (L, H // 128), torch.int32, dev)
         self.pull_variant = "bulk"
+        # combine push into receive streams (sequential writes at the home rank) instead of into
+        # [token * topk + slot]; forward passes without a saved context only
+        self.stream_push = bool(lay.stream)
+        if self.stream_push:
+            self.recv_peers, self.recv_index_peers = table(lay.recv), table(lay.recv_index)
+            self.recv = tensor_from_ptr(me_ptr + lay.recv, (W * L * k, H), torch.bfloat16, dev)
+            self.recv_index = tensor_from_ptr(me_ptr + lay.recv_index, (L * k,), torch.int32, dev)
+            self.stream_row = torch.empty(self.capacity, dtype=torch.int32, device=dev)
+        self._streamed = False
         me = ptrs[rank]
         self.xq = tensor_from_ptr(me + lay.xq, (L, H), torch.uint8, dev)
         self.xsc = tensor_from_ptr(me + lay.xsc, (L // 128, H // 128, 32, 16), torch.uint8, dev)
@@ -228,8 +243,26 @@ class EpMoKHost(mok.MoKHost):
         _lib.call("plb_ep_gather_rows", self.x_peers.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
                   s.num_tokens.data_ptr(), self.capacity, sh.hidden, b["x_routed_bf16"].data_ptr(), mok._stream())
 
-    def gemm_down_push(self):
+    def stream_rows(self):
+        """Positions of this rank's rows in the home ranks' receive streams, and the index the home
+        ranks read their (token, slot) rows through."""
+        s, sh = self.schedule, self.shape
+        _lib.call("plb_ep_stream_rows", s.peer_rank.data_ptr(), s.dest_row.data_ptr(), s.num_tokens.data_ptr(),
+                  self.capacity, self.rank, self.world, sh.tokens * sh.topk, self.stream_row.data_ptr(),
+                  self.recv_index_peers.data_ptr(), mok._stream())
+
+    def gemm_down_push(self, train: bool = False):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        self._streamed = self.stream_push and not train and self.precision != "bf16"
+        if self._streamed:
+            self.stream_rows()
+            _lib.call("plb_moe_gemm_down_push", b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(),
+                      w["w_routed_down_fp8"].data_ptr(), w["w_routed_down_sc"].data_ptr(),
+                      s.block_expert.data_ptr(), s.num_tokens.data_ptr(), self.stream_row.data_ptr(),
+                      s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
+                      self.push_rotation, self.push_stride, self.recv_peers.data_ptr(), self.status.buf.data_ptr(),
+                      mok._stream())
+            return
         if self.precision == "bf16":
             _lib.call("plb_moe_gemm_down_bf16", b["hidden_routed_bf16"].data_ptr(), w["w_routed_down_bf16"].data_ptr(),
                       s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(), s.peer_rank.data_ptr(),
@@ -242,6 +275,15 @@ class EpMoKHost(mok.MoKHost):
                   s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
                   self.push_rotation, self.push_stride, self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
 
+    def fwd_epilogue(self, y_shared=None):
+        if not self._streamed:
+            return super().fwd_epilogue(y_shared)
+        b, sh = self.buffers, self.shape
+        _lib.call("plb_moe_fwd_epilogue_indexed", mok._ptr(y_shared), self.recv.data_ptr(), self.recv_index.data_ptr(),
+                  self.router_weight_buffer.data_ptr(), sh.tokens, sh.topk, sh.hidden, b["output"].data_ptr(),
+                  mok._stream())
+        return b["output"]
+
     def device_step(self, train: bool = False):
         """Everything after the inputs sit in x_buffer / routes_local / router_weight_buffer."""
         self.quantize_tokens()
@@ -253,7 +295,7 @@ class EpMoKHost(mok.MoKHost):
             self.gemm_gate_up_train()
         else:
             self.gemm_gate_up()
-        self.gemm_down_push()
+        self.gemm_down_push(train)
         self.barrier()          # every rank's rows have landed in my combine buffer
         return self.fwd_epilogue()
 
@@ -358,25 +400,32 @@ def forward_local_group(hosts, inputs_per_rank, train: bool = False):
         else:
             h.gemm_gate_up()
     for h in hosts:
-        h.gemm_down_push()
+        h.gemm_down_push(train)
     outs = [h.fwd_epilogue() for h in hosts]
     for h in hosts:
         h.status.check("after local-group forward")
     return outs
 
 
+STREAM_PUSH_MIN_WORLD = 4
+
+
 class BenchSession:
     """bench.py's N > 1 arm: one rank of an IpcGroup at BASELINE config 4's per-rank shape."""
 
-    launches_per_step = 12  # quantise, scale rows, publish, barrier x2, schedule x3, pull, 2 GEMMs, epilogue
+    launches_per_step = 12  # quantise, scale rows, publish, barrier x2, schedule x3, pull, 2 GEMMs, epilogue (+1 with receive streams)
     # backward adds: barrier x2, router grad, d_y pull, 5 quantise, 2 dgrad GEMMs, SwiGLU backward, x gather,
     # 2 wgrad GEMMs, slot sum, 2 tail-zeroing launches
-    launches_per_step_train = 12 + 18
+    launches_per_step_train = 12 + 18    # no stream rows: the backward pass reads the [token, slot] layout
 
     def __init__(self, shape: mok.Shape, dev, rank: int, world: int, train: bool = False):
         self.shape, self.dev, self.train = shape, dev, train
-        self.group = IpcGroup(shape, rank, world, dev, train=train)
+        # receive streams pay for their row-position pass (about 0.1 ms) once the combine rows scatter
+        # over several peers: measured slower at two ranks, 0.55 ms faster per push at eight
+        self.group = IpcGroup(shape, rank, world, dev, train=train, stream=(not train) and world >= STREAM_PUSH_MIN_WORLD)
         self.host = EpMoKHost(shape, rank, self.group)
+        if self.host.stream_push:
+            self.launches_per_step = self.launches_per_step + 1
         torch.manual_seed(1234 + rank)
         E, H, I = self.host.num_local_experts, shape.hidden, shape.intermediate
         if train:
@@ -427,7 +476,7 @@ class BenchSession:
             self.kernel_events.append((a, b))
         else:
             gate_up()
-        h.gemm_down_push()
+        h.gemm_down_push(self.train)
         h.barrier()
         h.fwd_epilogue()
         if self.train:

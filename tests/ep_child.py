@@ -57,6 +57,26 @@ def main():
     dist.barrier()
     group.close()
 
+    # ---- receive streams: the same forward with the combine push written in arrival order
+    group = ep.IpcGroup(shape, rank, world, dev, stream=True)
+    host = ep.EpMoKHost(shape, rank, group)
+    host.load_weights(wg[rank * El:(rank + 1) * El], wu[rank * El:(rank + 1) * El], wd[rank * El:(rank + 1) * El])
+    assert host.stream_push
+    for b, w in zip(batches, want):
+        got = host.forward(b)["output"].cpu()
+        assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "receive streams")
+    h_out = [torch.full((shape.tokens, H), float("nan"), dtype=torch.bfloat16).pin_memory() for _ in batches]
+    pipe = ep.EpHostPipeline(host)
+    for b, o in zip(batches, h_out):
+        pipe.submit(pin(b.x), pin(b.experts.to(torch.int32)), pin(b.router), o)
+    pipe.drain()
+    host.status.check("EP host pipeline, receive streams")
+    for i, (o, w) in enumerate(zip(h_out, want)):
+        assert torch.equal(o.view(torch.int16), w.view(torch.int16)), (rank, "pipeline, receive streams", i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    group.close()
+
     # ---- training: forward + backward across the group == the single-rank pass on the whole problem
     mok.set_gemm_variant(2)
     group = ep.IpcGroup(shape, rank, world, dev, train=True)

@@ -153,6 +153,44 @@ def test_local_group_bf16_precision_equals_the_single_rank_forward(native_lib, w
         group.close()
 
 
+@pytest.mark.parametrize("world,shape_args", [(2, ("ep2s", 8, 512, 256, 2, 256)), (4, ("ep4s", 16, 256, 256, 4, 384))])
+def test_local_group_receive_streams_equal_the_slot_layout(native_lib, world, shape_args):
+    """The combine push into per-source receive streams plus the indexed epilogue gives the same
+    output, bit for bit, as the push into [token * topk + slot]; every stream position is used once."""
+    from pipelink_b200 import ep, mok
+    mok.set_gemm_variant(2)
+    shape = mok.Shape(*shape_args)
+    wg, wu, wd, inputs = make_group_case(mok, shape, world, seed=7)
+    El = shape.experts // world
+    outs = {}
+    for stream in (False, True):
+        group = ep.LocalGroup(shape, world, "cuda", stream=stream)
+        try:
+            hosts = [ep.EpMoKHost(shape, r, group) for r in range(world)]
+            for r, h in enumerate(hosts):
+                h.load_weights(wg[r * El:(r + 1) * El], wu[r * El:(r + 1) * El], wd[r * El:(r + 1) * El])
+                assert h.stream_push == stream
+                if stream:
+                    h.recv_index.fill_(-7)
+            for step in range(2):           # second step: different routing, positions recomputed
+                res = ep.forward_local_group(hosts, [mok.MoKHost.new_inputs(shape, 1 + step + (r == 1) * 2, "cuda", rank=r, world=world)
+                                                     for r in range(world)])
+                outs[(stream, step)] = [o.clone() for o in res]
+            torch.cuda.synchronize()
+            if stream:
+                Lk = shape.tokens * shape.topk
+                for h in hosts:
+                    idx = h.recv_index.cpu().numpy()
+                    assert (idx >= 0).all() and (idx < world * Lk).all()       # every (token, slot) was indexed
+                    assert len(np.unique(idx)) == Lk
+        finally:
+            torch.cuda.synchronize()
+            group.close()
+    for step in range(2):
+        for r in range(world):
+            assert torch.equal(outs[(True, step)][r].view(torch.int16), outs[(False, step)][r].view(torch.int16)), (step, r)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_ipc_group_forward_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
