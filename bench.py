@@ -306,7 +306,7 @@ def run_native(args):
                 "config": {"workload": shape.name, "tokens_per_rank": shape.tokens, "hidden": shape.hidden,
                            "experts": shape.experts, "topk": shape.topk, "intermediate": shape.intermediate,
                            "l2": "inputs larger than L2 (weights 1.5 GB, activations > 1 GB per step)",
-                           "expert_padding": mok.expert_padding(), "gemm_variant": "cta-pair 256x256" if mok.expert_padding() == 256 else "single-cta 128x128"},
+                           "expert_padding": mok.expert_padding(), "gemm_tile": "cta-pair 256x256"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
                 "roofline": roof, "cpu_baseline": cpu, "decode": decode, "attention": attention, "ep_fwd_bwd": train,
                 "tp_gemm": tp_gemm,

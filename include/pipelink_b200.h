@@ -54,16 +54,14 @@ int plb_abi_version(void);
 const char* plb_error_string(int code);
 int plb_last_cuda_error(void);
 
-/* Grouped-GEMM tiling variant, process-wide: 2 (default) = CTA pairs on 256x256 tiles
- * (cta_group::2, the reference's geometry, campaigns/mok/port/gemm/gemm.cu:26-36);
- * 1 = one CTA per 128x128 tile. plb_moe_tile_rows() is the row granularity the current
- * variant needs: `padding` of the schedule, `capacity`, `inter` and `hidden` must be
- * multiples of it, and plb_moe_pack_gate_up interleaves in blocks of half of it. Choose the
- * variant before packing weights. */
-int plb_moe_set_gemm_variant(int variant);
-int plb_moe_gemm_variant(void);
+/* Row granularity of the grouped GEMMs: CTA pairs on 256x256 tiles (cta_group::2, the reference's
+ * geometry, campaigns/mok/port/gemm/gemm.cu:26-36). `padding` of the schedule, `capacity`, `inter`
+ * and `hidden` must be multiples of it, and plb_moe_pack_gate_up interleaves in blocks of half of
+ * it. A GEMM entry point refuses a capacity that is not a multiple (PLB_E_ARGUMENT), and a row tile
+ * whose two 128-row blocks belong to different experts, or a row count that is not a multiple, is
+ * reported on the device (status code 6) instead of being multiplied by the wrong weights. */
 int plb_moe_tile_rows(void);
-/* Clamped SwiGLU, process-wide like the tiling variant (the reference selects it per link through
+/* Clamped SwiGLU, process-wide (the reference selects it per link through
  * the variant handle pipelink_mok_clamp, campaigns/mok/port/act/act.cu:9,246-249, and carries the
  * bound as the scalar mok.clamp, act.cu:294): limit > 0 makes the gate/up epilogue compute
  * silu(min(gate, limit)) * clamp(up, -limit, limit) and plb_moe_swiglu_bwd pass no gradient
@@ -274,7 +272,7 @@ int plb_ep_gather_rows(const void* const* src_peers, const int32_t* peer_rank, c
 /* plb_moe_gemm_down with the combine push (combine_kernel, comm.cu:124-129,327): row p is
  * stored to combine_peers[peer_rank[p]][dest_row[p]] from the GEMM epilogue. Rows are ordered by
  * (expert, source rank), so ranks that walked their tiles in the same order would all write to
- * the same home rank at the same time; tile_rotation (>= 0, in 256-row tiles, CTA-pair variant)
+ * the same home rank at the same time; tile_rotation (>= 0, in 256-row tiles)
  * makes this rank start that many tiles in and wrap around, and tile_stride (>= 1) makes
  * consecutive steps of the tile loop that many row tiles apart (rounded up to the next value
  * coprime to the live tile count), so that the tiles in flight at any moment go to different home
@@ -294,7 +292,7 @@ int plb_moe_gemm_down_push(const void* hidden_fp8, const void* hidden_sc, const 
  * words from plb_ep_scale_rows' layout through registers) and counts it into its 256-row tile; the
  * TMA lane acquires a tile's count (256) before its first read of the tile. x_routed_fp8 /
  * x_routed_sc are written exactly as plb_ep_pull_rows writes them. scratch_u32: capacity / 256 + 1
- * words, zeroed on the stream by this call. CTA-pair variant, hidden <= 4096, capacity % 256 == 0.
+ * words, zeroed on the stream by this call. hidden <= 4096, capacity % 256 == 0.
  * A row that never arrives is reported as status code 1 (its copy) or 5 (the tile's count). */
 int plb_moe_gemm_gate_up_dispatch(const void* const* xq_peers, const void* const* xsc_rows_peers,
                                   const int32_t* peer_rank, const int32_t* peer_token_idx, void* x_routed_fp8,
@@ -312,7 +310,7 @@ int plb_moe_gemm_gate_up_dispatch(const void* const* xq_peers, const void* const
  * same hidden columns; hidden_bf16 [capacity, inter] = bf16(act(bf16 gate, bf16 up)) under the
  * current plb_moe_set_swiglu_limit. plb_moe_gemm_down_bf16 places rows like plb_moe_gemm_down
  * (combine_bf16 set, combine_peers NULL) or pushes them like plb_moe_gemm_down_push (combine_peers
- * and peer_rank set, combine_bf16 NULL). CTA-pair variant only (PLB_E_CONTRACT otherwise);
+ * and peer_rank set, combine_bf16 NULL);
  * capacity multiple of 256, inter of 128, hidden of 256. Forward pass only. */
 int plb_moe_gemm_gate_up_bf16(const void* x_routed_bf16, const void* w13_bf16, const int32_t* block_expert,
                               const int32_t* num_tokens, int64_t capacity, int experts, int inter, int hidden,

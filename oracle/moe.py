@@ -177,6 +177,38 @@ def forward_single_rank_bf16(x, routes, router_w, w_gate, w_up, w_down, padding=
     return dict(schedule=sched, x_routed=rows, hidden=hidden, y=y, combine=buf, output=fwd_epilogue(buf, router_w))
 
 
+def _pad_rows(a: np.ndarray, multiple: int = 128) -> np.ndarray:
+    pad = (-a.shape[0]) % multiple
+    return a if pad == 0 else np.concatenate([a, np.zeros((pad, a.shape[1]), dtype=a.dtype)])
+
+
+def forward_token_rows(x_rows, routes, router_w, expert_weights, limit=0.0):
+    """Spot rows of the forward pass: the outputs of a few tokens of a problem too large to run
+    whole on the host (the method of the reference's own large cases, which check boundary rows
+    only: campaigns/attention/src/slot/family.cuh:156-229). Every step of the path is local to a
+    row (quantisation blocks run along a row, a GEMM row needs its own operand row and the
+    expert's weights, the epilogue sums one token's slots), so the rows need no schedule.
+
+    x_rows fp32 (bf16 values) [n, H]; routes i32 [n, k] global expert ids; router_w fp32 [n, k];
+    expert_weights(e) -> ((gate_q, gate_sc), (up_q, up_sc), (down_q, down_sc)) of expert e, each
+    quantised as quantize() writes a [rows, cols] matrix. Returns bf16-valued fp32 [n, H]."""
+    n, H = x_rows.shape
+    k = routes.shape[1]
+    xq, xsc = mxfp8.quantize(_pad_rows(np.asarray(x_rows, dtype=np.float32)))
+    xd = mxfp8.dequantize(xq, xsc)[:n]
+    y = np.zeros((n * k, H), dtype=np.float32)
+    for e in np.unique(routes):
+        tok, slot = np.nonzero(routes == e)
+        (gq, gsc), (uq, usc), (dq, dsc) = expert_weights(int(e))
+        wg, wu, wd = mxfp8.dequantize(gq, gsc), mxfp8.dequantize(uq, usc), mxfp8.dequantize(dq, dsc)
+        g = mxfp8.bf16_round(_mm(xd[tok], wg))
+        u = mxfp8.bf16_round(_mm(xd[tok], wu))
+        hidden = _pad_rows(mxfp8.bf16_round(silu_mul(g, u, limit)))
+        hd = mxfp8.dequantize(*mxfp8.quantize(hidden))[:len(tok)]
+        y[tok * k + slot] = mxfp8.bf16_round(_mm(hd, wd))
+    return fwd_epilogue(y, np.asarray(router_w, dtype=np.float32))
+
+
 def error_stats(expected, actual):
     """abs-mean, abs-max, relative (= sum|err| / sum|ref|), and relative L2."""
     e = np.asarray(expected, dtype=np.float64).reshape(-1)

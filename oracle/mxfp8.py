@@ -132,7 +132,15 @@ def quantize_transposed(x: np.ndarray):
     return quantize(np.ascontiguousarray(np.asarray(x, dtype=np.float32).T))
 
 
+_E4M3_TABLE = None
+
+
 def dequantize(q: np.ndarray, sc: np.ndarray) -> np.ndarray:
+    """Element value (e4m3_to_float, through a 256-entry table of it) times the block's 2^(byte - 127)."""
+    global _E4M3_TABLE
+    if _E4M3_TABLE is None:
+        _E4M3_TABLE = e4m3_to_float(np.arange(256, dtype=np.uint8))
     rows, cols = q.shape
     s = e8m0_value(unpack_scales(sc, rows, cols))
-    return (e4m3_to_float(q).reshape(rows, cols // 32, 32) * s[:, :, None]).reshape(rows, cols).astype(np.float32)
+    vals = _E4M3_TABLE[np.asarray(q, dtype=np.uint8)]
+    return (vals.reshape(rows, cols // 32, 32) * s[:, :, None]).reshape(rows, cols).astype(np.float32)

@@ -23,8 +23,6 @@ PROTOTYPES = {
     "plb_abi_version": (c_int, []),
     "plb_error_string": (c_char_p, [c_int]),
     "plb_last_cuda_error": (c_int, []),
-    "plb_moe_set_gemm_variant": (c_int, [c_int]),
-    "plb_moe_gemm_variant": (c_int, []),
     "plb_moe_set_swiglu_limit": (c_int, [c_float]),
     "plb_moe_swiglu_limit": (c_float, []),
     "plb_moe_tile_rows": (c_int, []),

@@ -104,7 +104,7 @@ class CpRank:
     (``ep.IpcGroup``-style) or, for single-GPU tests, allocated side by side in one process."""
 
     def __init__(self, seq: int, q_heads: int, kv_heads: int, rank: int, world: int, slab_ptrs, layout, device):
-        from .ep import tensor_from_ptr
+        from .ep import barrier_state_for, tensor_from_ptr
         self.seq, self.rank, self.world, self.device = seq, rank, world, torch.device(device)
         self.C = seq // (2 * world)
         if self.C % BLK:
@@ -120,9 +120,11 @@ class CpRank:
         self.ready_peers, self.flags_peers = table(layout["ready"]), table(layout["flags"])
         self.step_heads = heads_per_work(q_heads, kv_heads)
         self.work = torch.from_numpy(zigzag_work(seq, world, rank, q_heads, self.step_heads)).to(dev)
-        self.barrier_state = torch.zeros(1, dtype=torch.int32, device=dev)
+        # a session opened on a slab that has been used before continues from the generation its
+        # flags and readiness counters already hold (one session at a time per slab and rank)
+        self.barrier_state = barrier_state_for(me + layout["flags"], rank, dev)
         self.status = DeviceStatus(dev)
-        self.generation = 0
+        self.generation = int(self.ready.max().item())
         self.out = torch.empty((2 * self.C, q_heads, D), dtype=torch.bfloat16, device=dev)
         self.lse = torch.empty((q_heads, 2 * self.C), dtype=torch.float32, device=dev)
 

@@ -12,8 +12,6 @@ namespace {
 
 thread_local int g_last_cuda_error = 0;
 
-// 1 = one CTA per 128x128 tile (grouped_gemm.cu), 2 = CTA pair per 256x256 tile (grouped_gemm2.cu)
-int g_gemm_variant = 2;
 float g_swiglu_limit = 0.0f;  // 0: plain SwiGLU
 
 void* g_profile_buffer = nullptr;
@@ -21,7 +19,7 @@ void* g_profile_buffer = nullptr;
 cudaError_t run_gemm(plb::GroupedGemmArgs& a, cudaStream_t s) {
   a.profile = g_profile_buffer;
   a.swiglu_limit = g_swiglu_limit;
-  return g_gemm_variant == 2 ? plb::launch_grouped_gemm_pair(a, s) : plb::launch_grouped_gemm(a, s);
+  return plb::launch_grouped_gemm_pair(a, s);
 }
 
 int from_cuda(cudaError_t err) {
@@ -62,13 +60,6 @@ const char* plb_error_string(int code) {
 
 int plb_last_cuda_error(void) { return g_last_cuda_error; }
 
-int plb_moe_set_gemm_variant(int variant) {
-  if (variant != 1 && variant != 2) return PLB_E_ARGUMENT;
-  g_gemm_variant = variant;
-  return PLB_OK;
-}
-int plb_moe_gemm_variant(void) { return g_gemm_variant; }
-
 int plb_moe_set_swiglu_limit(float limit) {
   if (!(limit >= 0.0f) || limit > 3.0e38f) return PLB_E_ARGUMENT;
   g_swiglu_limit = limit;
@@ -83,7 +74,7 @@ int plb_debug_set_profile_buffer(void* device_i64_grid_by_16) {
 #endif
   return PLB_OK;
 }
-int plb_moe_tile_rows(void) { return g_gemm_variant == 2 ? 256 : 128; }
+int plb_moe_tile_rows(void) { return 256; }
 
 int plb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,
                        void* dst_sc, void* dst_t_fp8, void* dst_t_sc, void* stream) {
@@ -226,7 +217,7 @@ int plb_moe_gemm_gate_up(const void* x_routed_fp8, const void* x_routed_sc, cons
                          const int32_t* num_tokens, int64_t capacity, int experts, int inter,
                          int hidden, void* hidden_fp8, void* hidden_sc, plb_status* status,
                          void* stream) {
-  if (capacity < 0 || capacity % 128 || experts < 1 || inter < 128 || inter % 128 ||
+  if (capacity < 0 || capacity % plb_moe_tile_rows() || experts < 1 || inter < 128 || inter % 128 ||
       hidden < 128 || hidden % 128)
     return PLB_E_ARGUMENT;
   if (!x_routed_fp8 || !x_routed_sc || !w13_fp8 || !w13_sc || !block_expert || !num_tokens ||
@@ -263,7 +254,7 @@ static int gemm_down_impl(const void* hidden_fp8, const void* hidden_sc, const v
                           void* const* combine_peers, const int32_t* peer_rank, int tile_rotation, int tile_stride,
                           plb_status* status, void* stream) {
   if (tile_rotation < 0 || tile_stride < 1) return PLB_E_ARGUMENT;
-  if (capacity < 0 || capacity % 128 || experts < 1 || inter < 128 || inter % 128 ||
+  if (capacity < 0 || capacity % plb_moe_tile_rows() || experts < 1 || inter < 128 || inter % 128 ||
       hidden < 128 || hidden % 128)
     return PLB_E_ARGUMENT;
   if (!hidden_fp8 || !hidden_sc || !w2_fp8 || !w2_sc || !block_expert || !num_tokens ||
@@ -433,7 +424,6 @@ int plb_moe_gemm_gate_up_dispatch(const void* const* xq_peers, const void* const
                                   const int32_t* block_expert, const int32_t* num_tokens, int64_t capacity,
                                   int experts, int inter, int hidden, void* hidden_fp8, void* hidden_sc,
                                   void* scratch_u32, plb_status* status, void* stream) {
-  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
   if (capacity < 0 || capacity % 256 || experts < 1 || inter < 128 || inter % 128 || hidden < 128 || hidden % 128 ||
       hidden > 4096)
     return PLB_E_ARGUMENT;
@@ -456,11 +446,10 @@ int plb_moe_gemm_gate_up_dispatch(const void* const* xq_peers, const void* const
   return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
 }
 
-// bf16 routed precision: the same two GEMMs on bf16 operands (pair variant only).
+// bf16 routed precision: the same two GEMMs on bf16 operands.
 int plb_moe_gemm_gate_up_bf16(const void* x_routed_bf16, const void* w13_bf16, const int32_t* block_expert,
                               const int32_t* num_tokens, int64_t capacity, int experts, int inter, int hidden,
                               void* hidden_bf16, plb_status* status, void* stream) {
-  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
   if (capacity < 0 || capacity % 256 || experts < 1 || inter < 128 || inter % 128 || hidden < 128 || hidden % 128)
     return PLB_E_ARGUMENT;
   if (!x_routed_bf16 || !w13_bf16 || !block_expert || !num_tokens || !hidden_bf16 || !status) return PLB_E_ARGUMENT;
@@ -481,7 +470,6 @@ int plb_moe_gemm_down_bf16(const void* hidden_bf16, const void* w2_bf16, const i
                            const int32_t* num_tokens, const int32_t* dest_row, const int32_t* peer_rank,
                            int64_t capacity, int experts, int inter, int hidden, int tile_rotation,
                            void* combine_bf16, void* const* combine_peers, plb_status* status, void* stream) {
-  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
   if (tile_rotation < 0 || capacity < 0 || capacity % 256 || experts < 1 || inter < 128 || inter % 128 ||
       hidden < 256 || hidden % 256)
     return PLB_E_ARGUMENT;
@@ -542,7 +530,6 @@ int plb_moe_gemm_gate_up_train(const void* x_routed_fp8, const void* x_routed_sc
                                int64_t capacity, int experts, int inter, int hidden, void* hidden_fp8,
                                void* hidden_sc, void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc,
                                void* hidden_bf16, plb_status* status, void* stream) {
-  if (g_gemm_variant != 2) return PLB_E_CONTRACT;  // the saving epilogue exists in the CTA-pair kernel
   if (capacity < 0 || capacity % 256 || experts < 1 || inter < 256 || inter % 256 || hidden < 256 || hidden % 256)
     return PLB_E_ARGUMENT;
   if (!x_routed_fp8 || !x_routed_sc || !w13_fp8 || !w13_sc || !block_expert || !num_tokens || !hidden_fp8 ||
@@ -564,7 +551,6 @@ int plb_moe_gemm_gate_up_train(const void* x_routed_fp8, const void* x_routed_sc
 int plb_moe_gemm_wgrad(const void* a_t_fp8, const void* a_t_sc, const void* b_t_fp8, const void* b_t_sc,
                        const int32_t* expert_offsets, int64_t capacity, int experts, int m_rows, int n_rows,
                        void* d_w_bf16, plb_status* status, void* stream) {
-  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
   if (capacity < 0 || capacity % 256 || experts < 1 || m_rows < 256 || m_rows % 256 || n_rows < 256 || n_rows % 256)
     return PLB_E_ARGUMENT;
   if (!a_t_fp8 || !a_t_sc || !b_t_fp8 || !b_t_sc || !expert_offsets || !d_w_bf16 || !status) return PLB_E_ARGUMENT;
@@ -695,7 +681,6 @@ int plb_tp_gemm_bf16(const void* a_bf16, const void* b_bf16, const int32_t* bloc
                      const int32_t* dest_row, const int32_t* peer_rank, int64_t m, int n, int k, int tile_rotation,
                      const uint32_t* ready, uint32_t ready_target, void* out_bf16, void* const* out_peers,
                      plb_status* status, void* stream) {
-  if (g_gemm_variant != 2) return PLB_E_CONTRACT;
   if (m <= 0 || m % 256 || n < 256 || n % 256 || k < 128 || k % 128 || tile_rotation < 0) return PLB_E_ARGUMENT;
   if (!a_bf16 || !b_bf16 || !block_group || !num_rows || !dest_row || !status) return PLB_E_ARGUMENT;
   if ((out_peers == nullptr) == (out_bf16 == nullptr)) return PLB_E_ARGUMENT;

@@ -116,7 +116,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Status*
   }
 }
 
-// ---------------------------------------------------------------- TMA (local memory only)
+// ---------------------------------------------------------------- TMA
+// Tiled loads read this GPU's own memory only; the untiled bulk_load below is also used on
+// peer-mapped rows by the dispatch pull. None of them uses cluster multicast.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int x, int y) {
   asm volatile(

@@ -8,8 +8,10 @@
 // Here every rank quantises its own tokens once, peers pull E4M3 rows plus their scale
 // words (half the NVLink bytes of pulling bf16, and bit-identical because MXFP8 blocks
 // run along the hidden dimension of a single row), and the combine push happens inside
-// the down GEMM's epilogue. No TMA touches peer memory: all peer traffic is plain
-// 16-byte loads and stores.
+// the down GEMM's epilogue. Peer traffic is plain 16-byte loads and stores, except the
+// default dispatch pull (ep_pull_rows_bulk_kernel), which reads rows from peers with untiled,
+// non-multicast bulk copies (cp.async.bulk global -> shared). No copy with cluster multicast
+// exists anywhere in this library.
 //
 // Counter protocol (examples/comm-overlap/comm/push_gather.cuh:16-150): flags are never
 // reset; a launch generation kept in device memory gives each barrier its target value;

@@ -34,28 +34,16 @@ namespace plb {
 
 namespace {
 
-#ifdef PLB_EXP_STAGES
-constexpr int kStages = PLB_EXP_STAGES;
-#else
 constexpr int kStages = 5;
-#endif
 constexpr int kTileBytes = 128 * 128;                  // one CTA's A or B tile per K step
 constexpr int kSfBytes = 512;
 constexpr int kSfStageBytes = 3 * kSfBytes;            // A scales, B scales rows 0-127, 128-255
-#ifdef PLB_EXP_NOSF
-constexpr uint32_t kStageTx = 2 * kTileBytes;
-#else
 constexpr uint32_t kStageTx = 2 * kTileBytes + kSfStageBytes;  // per CTA per stage
-#endif
 constexpr int kOffA = 0;
 constexpr int kOffB = kStages * kTileBytes;
 constexpr int kOffSf = 2 * kStages * kTileBytes;
 constexpr int kOffStaging = kOffSf + kStages * kSfStageBytes;  // 8 warps x 4 KB
-#ifdef PLB_EXP_NOSTAGING
-constexpr int kStagingBytes = 0;
-#else
 constexpr int kStagingBytes = 8 * 4096;
-#endif
 constexpr int kOffBars = kOffStaging + kStagingBytes;
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes2 = kOffBars + kBarrierBytes + 1024;
@@ -282,12 +270,20 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
   const int num_pairs = gridDim.x >> 1;
 
   int total_tiles, m_tiles_live = 0;
+  int rows_in_use = 0, bad_schedule = 0;
   if (MODE == 2) {
     total_tiles = p.experts * p.m_tiles * p.n_tiles;
   } else {
-    m_tiles_live = *p.num_rows_dev >> 8;
+    rows_in_use = *p.num_rows_dev;
+    m_tiles_live = rows_in_use >> 8;
     if (m_tiles_live > p.max_m_tiles) m_tiles_live = p.max_m_tiles;
     total_tiles = m_tiles_live * p.n_tiles;
+    // A 256-row tile is multiplied by ONE expert's weights: a schedule padded to less than the tile
+    // (a trailing 128-row block, or a tile whose two blocks belong to different experts) is refused
+    // below rather than computed with the wrong weights.
+    bad_schedule = (rows_in_use & 255) != 0;
+    for (int m = threadIdx.x; m < m_tiles_live; m += kThreads2)
+      bad_schedule |= p.block_expert[2 * m] != p.block_expert[2 * m + 1];
   }
   const int m_rot = m_tiles_live > 0 ? p.m_rotation % m_tiles_live : 0;
   int m_stride = 1;
@@ -321,11 +317,16 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     tmem_relinquish_pair();
   }
   tc_fence_before();
-  __syncthreads();
+  bad_schedule = __syncthreads_or(bad_schedule);
   cluster_arrive();
   cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  if (bad_schedule) {   // both CTAs of every pair see the same schedule and agree
+    if (threadIdx.x == 0) report_failure(p.status, ST_BAD_ARGUMENT, 320, static_cast<unsigned>(rows_in_use), 256u);
+    total_tiles = 0;
+    m_tiles_live = 0;
+  }
 
   if (warp < 4) {
     setmaxnreg_dec<kRegsHelpers>();
@@ -385,13 +386,11 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
           const int kx = kk * (BF16 ? 64 : 128);
           tma_load_2d_pair(smem_base + kOffA + stage * kTileBytes, &map_a, full, kx, a_blk * 128);
           tma_load_2d_pair(smem_base + kOffB + stage * kTileBytes, &map_b, full, kx, b_blk * 128);
-#ifndef PLB_EXP_NOSF
           if (!BF16) {
             tma_load_2d_pair(sf, &map_sfa, full, 0, a_blk * t.k_pitch + kk);
             tma_load_2d_pair(sf + kSfBytes, &map_sfb, full, 0, b_blk0 * t.k_pitch + kk);
             tma_load_2d_pair(sf + 2 * kSfBytes, &map_sfb, full, 0, (b_blk0 + 1) * t.k_pitch + kk);
           }
-#endif
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }

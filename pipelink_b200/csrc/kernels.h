@@ -58,19 +58,19 @@ cudaError_t launch_schedule(const ScheduleArgs& a, cudaStream_t stream);
 cudaError_t launch_schedule_static(const ScheduleArgs& a, cudaStream_t stream);
 int64_t schedule_static_scratch_ints();
 
-// ---- grouped MXFP8 GEMM (grouped_gemm.cu)
+// ---- grouped MXFP8 GEMM (grouped_gemm2.cu)
 struct GroupedGemmArgs {
   const void* a_fp8;      // [rows_capacity, K]
   const void* a_sc;       // [rows_capacity/128, K/128, 32, 16]
   const void* b_fp8;      // [experts * n_rows, K]
   const void* b_sc;       // [experts * n_rows/128, K/128, 32, 16]
-  int64_t rows_capacity;  // multiple of 128
+  int64_t rows_capacity;  // multiple of 256
   int experts;
-  int n_rows;             // weight rows per expert (multiple of 128)
+  int n_rows;             // weight rows per expert (multiple of 256)
   int K;                  // multiple of 128
   const int* block_expert;
   const int* num_rows_dev;
-  // mode 0: tile columns [0,64) are gate, [64,128) are up -> hidden (fp8 + scales), [rows, n_rows/2]
+  // mode 0: tile columns [0,128) are gate, [128,256) are up -> hidden (fp8 + scales), [rows, n_rows/2]
   // mode 1: tile columns are output columns -> bf16 rows scattered through dest_row, [*, n_rows]
   int mode;
   void* out;
@@ -78,35 +78,34 @@ struct GroupedGemmArgs {
   const int* dest_row;
   void* const* out_peers = nullptr;  // mode 1: per-source-rank output bases (device array), or null
   const int* peer_rank = nullptr;    // mode 1 with out_peers
-  const unsigned* ready = nullptr;   // pair variant, mode 1: readiness counter per 256-row tile of A
+  const unsigned* ready = nullptr;   // mode 1: readiness counter per 256-row tile of A
   unsigned ready_target = 0;
-  bool bf16 = false;                 // pair variant, modes 0/1: a_fp8 / b_fp8 hold bf16, no scales, mode 0 writes bf16
+  bool bf16 = false;                 // modes 0/1: a_fp8 / b_fp8 hold bf16, no scales, mode 0 writes bf16
   float swiglu_limit = 0.0f;         // mode 0: > 0 bounds gate from above and up from both sides
-  // pair variant, mode 0: dispatch inside the GEMM kernel (all null = A is already in place)
+  // mode 0: dispatch inside the GEMM kernel (all null = A is already in place)
   const void* const* pull_xq = nullptr;        // per rank: u8 [tokens, K]
   const void* const* pull_sc_rows = nullptr;   // per rank: u32 [tokens, K / 128]
   const int* pull_peer_rank = nullptr;
   const int* pull_token_idx = nullptr;
   void* pull_scratch = nullptr;                // u32 [rows_capacity / 256 + 1], zeroed by the launcher
-  int m_stride = 1;                  // pair variant: row-tile distance between consecutive loop steps
-  int m_rotation = 0;                // pair variant: 256-row tiles are visited starting this many tiles in
+  int m_stride = 1;                  // row-tile distance between consecutive loop steps
+  int m_rotation = 0;                // 256-row tiles are visited starting this many tiles in
   int num_sms;
   Status* status;
   void* profile = nullptr;  // cycle counters [grid, 16] i64, written only by profiling builds
-  // mode 0, training (pair variant): MXFP8 gate / up and bf16 hidden kept for the backward pass
+  // mode 0, training: MXFP8 gate / up and bf16 hidden kept for the backward pass
   void* save_gate = nullptr;
   void* save_gate_sc = nullptr;
   void* save_up = nullptr;
   void* save_up_sc = nullptr;
   void* save_hidden = nullptr;
-  // mode 2 (pair variant): weight gradients, contraction over each expert's schedule rows
+  // mode 2: weight gradients, contraction over each expert's schedule rows
   const int* expert_offsets = nullptr;
   int m_rows = 0;
 };
-cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);
-// CTA-pair variant (grouped_gemm2.cu): 256-row tiles, mode 0 weights interleaved per 128 rows.
+// CTA pairs on 256x256 tiles: rows_capacity, every expert segment and n_rows are multiples of 256;
+// mode 0 weights are interleaved per 128 rows.
 cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stream);
-int grouped_gemm_smem_bytes();
 
 // ---- backward-pass stages (backward.cu)
 cudaError_t launch_bwd_dy(const void* d_out, const void* y, const float* router_w, const int* peer_rank,

@@ -69,6 +69,15 @@ def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor
     return torch.as_tensor(_RawTensor(ptr, shape, typestr), device=device)
 
 
+def barrier_state_for(flags_ptr: int, rank: int, device) -> torch.Tensor:
+    """Generation counter of `plb_ep_barrier` for a session opened on a slab whose flag words start at
+    ``flags_ptr``. A barrier adds one to word ``rank`` of every rank's flags, this rank's own included,
+    so that word counts the barriers this rank has completed on the slab: a session that starts from
+    it lines up with flags an earlier session left behind. One session at a time per slab and rank."""
+    torch.cuda.synchronize(device)
+    return tensor_from_ptr(flags_ptr + 4 * rank, (1,), torch.int32, device).clone()
+
+
 def sym_alloc(nbytes: int) -> int:
     out = ctypes.c_void_p()
     _lib.call("plb_sym_alloc", nbytes, ctypes.byref(out))
@@ -190,7 +199,7 @@ class EpMoKHost(mok.MoKHost):
         self.routes_all = tensor_from_ptr(me + lay.routes_all, (W, L, k), torch.int32, dev)
         self.buffers["combine_buffer"] = tensor_from_ptr(me + lay.combine, (L * k, H), torch.bfloat16, dev)
         self.routes_local = torch.empty((L, k), dtype=torch.int32, device=dev)
-        self.barrier_state = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.barrier_state = barrier_state_for(me + lay.flags, rank, dev)
         # Pushing GEMMs start `rank` source-rank blocks into their tile list: a block is the rows one
         # rank sends to one expert, L * k / E on average, in 256-row tiles.
         self.push_rotation = rank * max(1, (L * k // shape.experts) // 256) if W > 1 else 0

@@ -15,15 +15,9 @@ import torch
 from . import _lib
 
 def expert_padding() -> int:
-    """Rows every expert segment is padded to: one grouped-GEMM tile (256 for the CTA-pair
-    variant, as in the reference, campaigns/mok/port/framework/interp_fwd.cu:324; 128 for the
-    single-CTA variant)."""
+    """Rows every expert segment is padded to: one grouped-GEMM tile (256, as in the reference,
+    campaigns/mok/port/framework/interp_fwd.cu:324)."""
     return _lib.load().plb_moe_tile_rows()
-
-
-def set_gemm_variant(variant: int) -> None:
-    """1 = one CTA per 128x128 tile, 2 = CTA pair per 256x256 tile. Choose before loading weights."""
-    _lib.call("plb_moe_set_gemm_variant", variant)
 
 
 @dataclass(frozen=True)
@@ -191,8 +185,6 @@ class MoKHost:
             "output": torch.empty((L, H), dtype=torch.bfloat16, device=self.device),
         }
         if precision == "bf16":
-            if _lib.load().plb_moe_gemm_variant() != 2:
-                raise ValueError("the bf16 routed precision exists in the CTA-pair GEMM variant only")
             bf = dict(dtype=torch.bfloat16, device=self.device)
             self.buffers.update(x_routed_bf16=torch.empty((P, H), **bf), hidden_routed_bf16=torch.empty((P, I), **bf))
         self.weights = None

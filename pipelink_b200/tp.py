@@ -28,7 +28,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .ep import tensor_from_ptr
+from .ep import barrier_state_for, tensor_from_ptr
 from .mok import DeviceStatus, _stream
 
 PARTS = 8            # pieces a 256-row block is pushed in (more CTAs per block, same counter)
@@ -65,8 +65,6 @@ class TpRank:
 
     def __init__(self, layout: TpLayout, rank: int, ptrs, device, distributed: bool):
         _lib.load()
-        if _lib.load().plb_moe_gemm_variant() != 2:
-            raise ValueError("the compositions use the CTA-pair GEMM variant")
         lay, W = layout, layout.world
         self.layout, self.rank, self.world, self.distributed = lay, rank, W, distributed
         self.device = dev = torch.device(device)
@@ -82,9 +80,12 @@ class TpRank:
         self.ready = [tensor_from_ptr(me + lay.ready[p], (lay.m // TILE,), torch.int32, dev) for p in range(2)]
         self.gathered = [tensor_from_ptr(me + lay.gather[p], (lay.m, lay.k), torch.bfloat16, dev) for p in range(2)]
         self.slots = [tensor_from_ptr(me + lay.slots[p], (self.ms * W, lay.n), torch.bfloat16, dev) for p in range(2)]
-        self.barrier_state = torch.zeros(1, **i32)
+        self.barrier_state = barrier_state_for(me + lay.flags, rank, dev)
         self.status = DeviceStatus(dev)
-        self.generation = 0
+        # ag and rs advance separately: the gathered buffers and their counters follow the number of
+        # ag steps, the receive slots the number of rs steps, whatever order the two are called in
+        self.ag_generation = 0
+        self.rs_generation = 0
         # helper arrays of the grouped-GEMM entry point: one group, every row live
         self.block_group = torch.zeros(lay.m // 128, **i32)
         self.num_rows = torch.tensor([lay.m], **i32)
@@ -101,20 +102,21 @@ class TpRank:
     # ------------------------------------------------------------------ all-gather -> GEMM
     def shard_view(self, generation: int | None = None) -> torch.Tensor:
         """Where the caller writes this rank's A shard for the next ``ag`` step ([M/W, K] bf16)."""
-        g = self.generation if generation is None else generation
+        g = self.ag_generation if generation is None else generation
         return self.gathered[g & 1][self.rank * self.ms:(self.rank + 1) * self.ms]
 
     def ag_push(self):
-        p = self.generation & 1
+        p = self.ag_generation & 1
         _lib.call("plb_tp_push_rows", self.shard_view().data_ptr(), self.ms // TILE, TILE * self.layout.k * 2, PARTS,
                   self.rank, self.world, self.gather_peers[p].data_ptr(), self.ready_peers[p].data_ptr(),
                   min(self.sms, (self.ms // TILE) * PARTS * self.world), _stream())
 
     def ag_gemm(self, b_local: torch.Tensor) -> torch.Tensor:
-        lay, p = self.layout, self.generation & 1
+        lay, p = self.layout, self.ag_generation & 1
         if tuple(b_local.shape) != (self.nl, lay.k) or b_local.dtype != torch.bfloat16 or not b_local.is_contiguous():
             raise ValueError("B_r is a contiguous bf16 [N / W, K]")
-        target = ((self.generation >> 1) + 1) * PARTS
+        # every ag step with this parity has added PARTS to each block's counter
+        target = ((self.ag_generation >> 1) + 1) * PARTS
         _lib.call("plb_tp_gemm_bf16", self.gathered[p].data_ptr(), b_local.data_ptr(), self.block_group.data_ptr(),
                   self.num_rows.data_ptr(), self.identity.data_ptr(), None, lay.m, self.nl, lay.k, self.rotation,
                   self.ready[p].data_ptr(), target, self.ag_out.data_ptr(), None, self.status.buf.data_ptr(), _stream())
@@ -125,7 +127,7 @@ class TpRank:
         one stream: the GEMM waits for the peers' pushes, never for a kernel queued behind it here."""
         self.ag_push()
         out = self.ag_gemm(b_local)
-        self.generation += 1
+        self.ag_generation += 1
         return out
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter
@@ -135,7 +137,7 @@ class TpRank:
                       self.status.buf.data_ptr(), _stream())
 
     def rs_gemm_push(self, a_local: torch.Tensor, b_local: torch.Tensor):
-        lay, p = self.layout, self.generation & 1
+        lay, p = self.layout, self.rs_generation & 1
         for t, shape in ((a_local, (lay.m, self.kl)), (b_local, (lay.n, self.kl))):
             if tuple(t.shape) != shape or t.dtype != torch.bfloat16 or not t.is_contiguous():
                 raise ValueError("A_q is a contiguous bf16 [M, K / W] and B_q [N, K / W]")
@@ -144,7 +146,7 @@ class TpRank:
                   self.rotation, None, 0, None, self.slots_peers[p].data_ptr(), self.status.buf.data_ptr(), _stream())
 
     def rs_reduce(self) -> torch.Tensor:
-        p = self.generation & 1
+        p = self.rs_generation & 1
         _lib.call("plb_moe_fwd_epilogue", None, self.slots[p].data_ptr(), self.ones.data_ptr(), self.ms, self.world,
                   self.layout.n, self.rs_out.data_ptr(), _stream())
         return self.rs_out
@@ -153,7 +155,7 @@ class TpRank:
         self.rs_gemm_push(a_local, b_local)
         self.barrier()                      # every rank's partial rows have landed in my slots
         out = self.rs_reduce()
-        self.generation += 1
+        self.rs_generation += 1
         return out
 
 
@@ -174,7 +176,7 @@ class LocalTpGroup:
             r.ag_push()
         outs = [r.ag_gemm(b) for r, b in zip(self.ranks, b_locals)]
         for r in self.ranks:
-            r.generation += 1
+            r.ag_generation += 1
             r.status.check("all-gather GEMM")
         return outs
 
@@ -183,7 +185,7 @@ class LocalTpGroup:
             r.rs_gemm_push(a, b)
         outs = [r.rs_reduce() for r in self.ranks]
         for r in self.ranks:
-            r.generation += 1
+            r.rs_generation += 1
             r.status.check("reduce-scatter GEMM")
         return outs
 

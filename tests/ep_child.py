@@ -78,7 +78,6 @@ def main():
     group.close()
 
     # ---- training: forward + backward across the group == the single-rank pass on the whole problem
-    mok.set_gemm_variant(2)
     group = ep.IpcGroup(shape, rank, world, dev, train=True)
     host = ep.EpMoKHost(shape, rank, group)
     host.load_weights(wg[rank * El:(rank + 1) * El] * 2.5, wu[rank * El:(rank + 1) * El] * 2.5, wd[rank * El:(rank + 1) * El] * 2.5, train=True)

@@ -134,3 +134,27 @@ def test_context_parallel_two_gpus():
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "CP CHILD OK" in out.stdout
+
+
+def test_attention_seq32768_boundary_rows(native_lib):
+    """The benchmarked prefill size (S = 32768, 32 query / 8 KV heads, d = 128, N(0,1) inputs as the
+    configuration names them): boundary and interior spot rows against the fp64 oracle over all
+    visible keys (campaigns/attention/src/slot/family.cuh:156-229), the reference's predicate."""
+    from pipelink_b200 import attention as att
+    S, Hq, Hkv = 32768, 32, 8
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = torch.randn(1, S, Hq, 128, generator=g, device="cuda").to(torch.bfloat16)
+    k = torch.randn(1, S, Hkv, 128, generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn(1, S, Hkv, 128, generator=g, device="cuda").to(torch.bfloat16)
+    out, lse = att.attention_fwd(q, k, v)
+    torch.cuda.synchronize()
+    sel = [0, 1, 127, 128, 129, 4095, 4096, 16383, 16384, 16385, 20001, S - 130, S - 129, S - 128, S - 2, S - 1]
+    idx = torch.tensor(sel, device="cuda")
+    q_rows = q[0, idx].float().cpu().numpy()                   # only the sampled query rows travel to the host
+    kf, vf = k[0].float().cpu().numpy(), v[0].float().cpu().numpy()
+    ref_o, ref_lse = oa.reference_rows(q_rows, kf, vf, list(range(len(sel))), 1.0 / np.sqrt(128.0), q_pos=sel)
+    got_o = out[0, idx].float().cpu().numpy()
+    got_lse = lse[:, idx].cpu().numpy()
+    assert np.isfinite(got_o).all()
+    assert oa.matches(got_o, ref_o) == 0, np.abs(got_o - ref_o).max()
+    assert oa.matches(got_lse, ref_lse) == 0, np.abs(got_lse - ref_lse).max()

@@ -78,7 +78,6 @@ def test_local_group_backward_equals_the_single_rank_backward(native_lib, world,
     every quantisation block, GEMM and reduction sees the same operands. (The single-rank backward
     is itself held to the CPU oracle in test_moe_backward_gpu.py.)"""
     from pipelink_b200 import ep, mok
-    mok.set_gemm_variant(2)
     shape = mok.Shape(*shape_args)
     wg, wu, wd, inputs = make_group_case(mok, shape, world, seed=3)
     wg, wu, wd = wg * 2.5, wu * 2.5, wd * 2.5
@@ -122,7 +121,6 @@ def test_local_group_bf16_precision_equals_the_single_rank_forward(native_lib, w
     buffers and pushed back from the down GEMM; the result equals, bit for bit, one rank holding
     every token and expert (itself held to the oracle in test_moe_gpu.py)."""
     from pipelink_b200 import ep, mok
-    mok.set_gemm_variant(2)
     shape = mok.Shape(*shape_args)
     wg, wu, wd, inputs = make_group_case(mok, shape, world, seed=5)
     whole = mok.Shape("whole", shape.experts, shape.hidden, shape.intermediate, shape.topk, shape.tokens * world)
@@ -158,7 +156,6 @@ def test_local_group_receive_streams_equal_the_slot_layout(native_lib, world, sh
     """The combine push into per-source receive streams plus the indexed epilogue gives the same
     output, bit for bit, as the push into [token * topk + slot]; every stream position is used once."""
     from pipelink_b200 import ep, mok
-    mok.set_gemm_variant(2)
     shape = mok.Shape(*shape_args)
     wg, wu, wd, inputs = make_group_case(mok, shape, world, seed=7)
     El = shape.experts // world

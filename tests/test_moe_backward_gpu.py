@@ -32,7 +32,6 @@ def test_clamped_activation_vs_oracle(native_lib):
 
 def _forward_backward_vs_oracle(shape_args, generation, limit):
     from pipelink_b200 import mok
-    mok.set_gemm_variant(2)
     shape = mok.Shape(*shape_args)
     torch.manual_seed(5)
     E, H, I = shape.experts, shape.hidden, shape.intermediate
@@ -86,7 +85,6 @@ def test_recompute_pass_gives_the_same_gradients(native_lib):
     """A plain forward followed by backward(recompute=True) equals forward(train=True) + backward bit
     for bit: the recompute pass regenerates exactly the saved activations."""
     from pipelink_b200 import mok
-    mok.set_gemm_variant(2)
     shape = mok.Shape("rec", 8, 512, 256, 2, 384)
     torch.manual_seed(9)
     E, H, I = shape.experts, shape.hidden, shape.intermediate

@@ -26,13 +26,10 @@ def _bf16_np(t):
     return t.detach().float().cpu().numpy()
 
 
-@pytest.fixture(scope="module", params=[2, 1], ids=["cta-pair", "single-cta"])
-def mok(native_lib, request):
-    """The host module with the grouped-GEMM variant under test selected (restored afterwards)."""
+@pytest.fixture(scope="module")
+def mok(native_lib):
     from pipelink_b200 import mok
-    mok.set_gemm_variant(request.param)
-    yield mok
-    mok.set_gemm_variant(2)
+    return mok
 
 
 def _tile(mok):
@@ -280,6 +277,35 @@ def test_gemm_down_scatter_and_padding(mok):
     assert stats["relative"] <= REL_TOL, stats
 
 
+def test_gemm_refuses_a_schedule_padded_to_less_than_a_tile(mok):
+    """A schedule padded to 128 rows puts two experts into one 256-row tile (or leaves a trailing
+    128-row block). The GEMM multiplies a tile by one expert's weights, so it must report the
+    schedule (status 6) and write nothing, and a capacity off the tile grid is refused on the host."""
+    from pipelink_b200 import _lib
+    K, N = 256, 256
+    a_q = torch.full((512, K), 0x38, dtype=torch.uint8, device="cuda")
+    b_q = torch.full((2 * N, K), 0x38, dtype=torch.uint8, device="cuda")
+    a_sc = torch.full((4, K // 128, 32, 16), 127, dtype=torch.uint8, device="cuda")
+    b_sc = torch.full((2 * N // 128, K // 128, 32, 16), 127, dtype=torch.uint8, device="cuda")
+    for rows_in_use, owners in ((512, [0, 1, 1, 1]), (384, [0, 0, 1, 1])):
+        sched = _identity_schedule(mok, 512, owners)
+        sched["num_tokens"].fill_(rows_in_use)
+        out = torch.full((512, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        st = _status(mok)
+        _lib.call("plb_moe_gemm_down", a_q.data_ptr(), a_sc.data_ptr(), b_q.data_ptr(), b_sc.data_ptr(),
+                  sched["block_expert"].data_ptr(), sched["num_tokens"].data_ptr(), sched["dest_row"].data_ptr(),
+                  512, 2, K, N, out.data_ptr(), st.buf.data_ptr(), None)
+        with pytest.raises(RuntimeError, match="status 6"):
+            st.check("gemm on a 128-padded schedule")
+        assert torch.isnan(out.float()).all()
+    sched = _identity_schedule(mok, 384, [0, 0, 1])
+    with pytest.raises(_lib.PlbError) as e:
+        _lib.call("plb_moe_gemm_down", a_q.data_ptr(), a_sc.data_ptr(), b_q.data_ptr(), b_sc.data_ptr(),
+                  sched["block_expert"].data_ptr(), sched["num_tokens"].data_ptr(), sched["dest_row"].data_ptr(),
+                  384, 2, K, N, a_q.data_ptr(), _status(mok).buf.data_ptr(), None)
+    assert e.value.code == 3
+
+
 # ------------------------------------------------------------------ whole forward
 def _make_case(mok, shape, generation, seed=0):
     torch.manual_seed(seed)
@@ -358,7 +384,6 @@ def test_host_pipeline_equals_the_plain_forward(native_lib):
     """Three different batches in flight through the three-stream host pipeline give, bit for bit,
     what one forward per batch gives."""
     from pipelink_b200 import mok
-    mok.set_gemm_variant(2)
     shape = mok.Shape("pipe", 8, 512, 256, 2, 640)
     torch.manual_seed(2)
     E, H, I = shape.experts, shape.hidden, shape.intermediate
@@ -388,7 +413,6 @@ def test_bf16_routed_precision_vs_oracle(native_lib, shape_args, generation, lim
     summation order, which moves some bf16 roundings of gate / up / hidden by one ulp (2^-8)."""
     from oracle import moe as omoe
     from pipelink_b200 import _lib, mok
-    mok.set_gemm_variant(2)
     shape = mok.Shape(*shape_args)
     torch.manual_seed(21)
     E, H, I = shape.experts, shape.hidden, shape.intermediate
@@ -423,7 +447,6 @@ def test_fused_dispatch_equals_pull_then_gemm(native_lib, shape_args, generation
     leaves the same routed rows, hidden activations and output, bit for bit, as the pull kernel
     followed by the plain GEMM; repeated steps reuse the zeroed counters correctly."""
     from pipelink_b200 import mok
-    mok.set_gemm_variant(2)
     shape = mok.Shape(*shape_args)
     torch.manual_seed(31)
     E, H, I = shape.experts, shape.hidden, shape.intermediate
@@ -444,3 +467,64 @@ def test_fused_dispatch_equals_pull_then_gemm(native_lib, shape_args, generation
         for name in ("x_routed_scale", "hidden_routed_scale"):
             assert torch.equal(got[name][: total // 128], want[name][: total // 128]), (step, name)
         assert torch.equal(got["output"].view(torch.int16), want["output"].view(torch.int16)), step
+
+
+# ------------------------------------------------------------------ the benchmarked size itself
+def test_forward_full_size_spot_rows(mok):
+    """T = 16384 tokens, 64 experts, H = 4096, I = 2048, top-8: the size the throughput is quoted on.
+    The whole problem is hours of host work, so the oracle evaluates spot rows (the reference's own
+    method for its large cases, campaigns/attention/src/slot/family.cuh:156-229): the full routing
+    schedule bit for bit, the dispatched bytes of the sampled tokens bit for bit, and the outputs
+    of 32 sampled tokens (each through its eight experts) within the two-GEMM tolerance."""
+    shape = mok.CONFIG2
+    E, H, I, k, T = shape.experts, shape.hidden, shape.intermediate, shape.topk, shape.tokens
+    torch.manual_seed(0)
+    q = {}
+    for name, rows, cols in (("gate", I, H), ("up", I, H), ("down", H, I)):
+        fp8 = torch.empty((E, rows, cols), dtype=torch.uint8, device="cuda")
+        sc = torch.empty((E * rows // 128, cols // 128, 32, 16), dtype=torch.uint8, device="cuda")
+        for e in range(E):
+            w = (torch.randn(rows, cols, device="cuda") * 0.02).to(torch.bfloat16)
+            a, b, _, _ = mok.mxfp8_quantize(w)
+            fp8[e].copy_(a)
+            sc[e * rows // 128:(e + 1) * rows // 128].copy_(b)
+        q[name] = (fp8, sc)
+    host = mok.MoKHost(shape)
+    host.load_quantized_weights(*q["gate"], *q["up"], *q["down"], keep_unpacked=False)
+    inputs = mok.MoKHost.new_inputs(shape, 1, "cuda")
+    res = host.forward(inputs)
+    torch.cuda.synchronize()
+    out = _bf16_np(res["output"])
+    assert np.isfinite(out).all()
+
+    # routing / indexing: the whole schedule, bit-exact
+    routes = _np(inputs.experts).astype(np.int32)
+    ref = oroute.build_schedule(routes[None], 0, E, host.capacity, host.padding)
+    total = int(ref["num_tokens"][0])
+    s = host.schedule
+    assert int(s.num_tokens.item()) == total
+    for f in ("tokens_per_expert", "expert_offsets"):
+        assert np.array_equal(_np(getattr(s, f)), ref[f]), f
+    for f in ("peer_rank", "peer_token_idx", "dest_row"):
+        assert np.array_equal(_np(getattr(s, f))[:total], ref[f][:total]), f
+    assert np.array_equal(_np(s.block_expert)[: total // 128], ref["block_expert"][: total // 128])
+
+    rng = np.random.default_rng(7)
+    sel = np.unique(np.concatenate([[0, T - 1], rng.choice(T, 30, replace=False)]))
+    x = _bf16_np(inputs.x[torch.from_numpy(sel).cuda()])
+    # dispatch: the quantised bytes of every routed copy of a sampled token
+    xq_ref, _ = omx.quantize(omoe._pad_rows(x))
+    rows_of = {int(t): np.nonzero((ref["peer_token_idx"][:total] == t) & (ref["peer_rank"][:total] == 0))[0] for t in sel}
+    picked = torch.from_numpy(np.concatenate([rows_of[int(t)] for t in sel])).cuda()
+    got_rows = _np(res["x_routed_data"][picked]).reshape(len(sel), k, H)
+    assert all(len(rows_of[int(t)]) == k for t in sel)
+    assert np.array_equal(got_rows, np.repeat(xq_ref[:len(sel), None], k, axis=1))
+
+    def expert_weights(e):
+        return [(_np(q[n][0][e]), _np(q[n][1][e * r // 128:(e + 1) * r // 128])) for n, r in (("gate", I), ("up", I), ("down", H))]
+
+    want = omoe.forward_token_rows(x, routes[sel], _np(inputs.router)[sel], expert_weights)
+    stats = omoe.error_stats(want, out[sel])
+    # bf16 tolerance of the two-GEMM chain, stated: relative (sum|err| / sum|ref|) and relative L2 <= 2e-2
+    assert stats["relative"] <= 2e-2 and stats["rel_l2"] <= 2e-2, stats
+    print("full-size spot rows:", len(sel), "tokens,", stats)

@@ -108,3 +108,28 @@ def test_bf16_precision_forward_matches_dense_model(limit):
     t = lambda a: torch.tensor(a, dtype=torch.float64)
     want = _dense_ffn(t(x), routes, t(router_w), t(wg), t(wu), t(wd), limit)
     assert _rel(want.numpy(), got["output"]) < 6e-3
+
+
+def test_spot_rows_equal_rows_of_the_full_forward():
+    """forward_token_rows (what the full-size GPU test is held to) against forward_single_rank on a
+    problem small enough to run whole: the sampled tokens' outputs are the same bits."""
+    from oracle import routing as oroute
+    rng = np.random.default_rng(1)
+    E, H, I, T, k = 8, 256, 256, 300, 2
+    w = [mxfp8.bf16_round(rng.standard_normal(s, dtype=np.float32) * np.float32(0.05))
+         for s in ((E, I, H), (E, I, H), (E, H, I))]
+    weights = omoe.quantize_weights(*w)
+    x = mxfp8.bf16_round(rng.standard_normal((T, H), dtype=np.float32))
+    ids, rw = oroute.route_topk(rng.standard_normal((T, E), dtype=np.float32), k)
+    full = omoe.forward_single_rank(x, ids, rw, weights)["output"]
+
+    def expert_weights(e):
+        out = []
+        for name, (R, C) in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+            q, sc = weights[name]
+            out.append((q[e], mxfp8.pack_scales(mxfp8.unpack_scales(sc, E * R, C)[e * R:(e + 1) * R])))
+        return out
+
+    sel = np.array([0, 5, 17, 123, 299])
+    got = omoe.forward_token_rows(x[sel], ids[sel], rw[sel], expert_weights)
+    assert np.array_equal(got, full[sel])

@@ -55,7 +55,7 @@ def test_gemm_reduce_scatter_emulated_ranks(native_lib, world, m, n, k):
         for step in range(3):
             a, b, ref = _case(m, n, k, world, 20 + step)
             for r in group.ranks:
-                r.slots[r.generation & 1].fill_(float("nan"))       # every slot row must be pushed by its source
+                r.slots[r.rs_generation & 1].fill_(float("nan"))       # every slot row must be pushed by its source
             a_l = [a[:, r * kl:(r + 1) * kl].contiguous() for r in range(world)]
             b_l = [b[:, r * kl:(r + 1) * kl].contiguous() for r in range(world)]
             outs = [o.clone() for o in group.rs(a_l, b_l)]
@@ -73,6 +73,34 @@ def test_gemm_reduce_scatter_emulated_ranks(native_lib, world, m, n, k):
             again = [o.clone() for o in group.rs(a_l, b_l)]                 # other parity, same operands
             for r in range(world):
                 assert torch.equal(again[r].view(torch.int16), outs[r].view(torch.int16))    # bitwise repeatable
+    finally:
+        group.close()
+
+
+@pytest.mark.parametrize("order", ["ag,ag,rs,ag,ag", "rs,ag,ag", "ag,rs,rs,ag,rs,ag,ag,ag"])
+def test_interleaved_ag_and_rs_keep_their_own_generations(native_lib, order):
+    """The gathered buffers follow the number of ag steps and the receive slots the number of rs steps:
+    any interleaving gives correct results and a clean status (a shared step counter made the
+    all-gather GEMM wait for a counter value that its parity never reaches)."""
+    from pipelink_b200 import tp
+    world, m, n, k = 2, 1024, 1024, 512
+    group = tp.LocalTpGroup(m, n, k, world)
+    try:
+        ms, nl, kl = m // world, n // world, k // world
+        for step, op in enumerate(order.split(",")):
+            a, b, ref = _case(m, n, k, world, 40 + step)
+            if op == "ag":
+                outs = group.ag([a[r * ms:(r + 1) * ms] for r in range(world)],
+                                [b[r * nl:(r + 1) * nl].contiguous() for r in range(world)])
+                torch.cuda.synchronize()
+                assert _rel(ref, torch.cat(outs, dim=1)) < 3e-3, (step, op)
+            else:
+                for r in group.ranks:
+                    r.slots[r.rs_generation & 1].fill_(float("nan"))
+                outs = group.rs([a[:, r * kl:(r + 1) * kl].contiguous() for r in range(world)],
+                                [b[:, r * kl:(r + 1) * kl].contiguous() for r in range(world)])
+                torch.cuda.synchronize()
+                assert _rel(ref, torch.cat(outs, dim=0)) < 1e-2, (step, op)
     finally:
         group.close()
 
