@@ -1,9 +1,14 @@
 #!/usr/bin/env python
-"""Headline benchmark: MXFP8 MoE FFN forward (BASELINE.json configs[1]) on N GPUs of one node.
+"""Headline benchmark: MXFP8 MoE FFN forward on N GPUs of one node. One GPU runs the single-GPU
+workload (16384 tokens, 64 experts, hidden 4096, intermediate 2048, top-8); N > 1 runs the
+expert-parallel workload (8192 tokens per rank, the same experts sharded over the ranks).
 
     python bench.py --gpus 1 --steps 20 --warmup 3
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference        # the CPU port of the reference path, host cores
+    python bench.py --case moe|attention|decode     # one small, self-terminating case of a hot kernel,
+                                                    # sized for a profiler capture (a few GB on the device)
+    torchrun ... bench.py --case ep-phases          # device time of every phase of the expert-parallel step
 
 A step is one forward pass over one synthetic batch: routing schedule -> dispatch (gather +
 MXFP8 quantise) -> gate/up grouped GEMM with fused SwiGLU + requantise -> down grouped GEMM with
@@ -44,6 +49,9 @@ def parse():
     ap.add_argument("--no-train", action="store_true", help="skip the expert-parallel forward+backward leg (N > 1)")
     ap.add_argument("--no-tp", action="store_true", help="skip the all-gather / reduce-scatter GEMM leg (N > 1)")
     ap.add_argument("--no-attention", action="store_true", help="skip the causal prefill attention leg")
+    ap.add_argument("--no-parity", action="store_true", help="skip the value checks of the N > 1 legs")
+    ap.add_argument("--case", default=None, choices=["moe", "attention", "decode", "ep-phases"],
+                    help="run one small case of a hot kernel (for profiler captures) instead of the benchmark")
     return ap.parse_args()
 
 
@@ -124,9 +132,11 @@ class ClockSampler:
 # CPU arm: the oracle port of the reference path on the host cores, on a bounded sample
 # ---------------------------------------------------------------------------------------------
 def cpu_sample(hidden, inter, steps=1, warmup=0):
-    """Forward of a bounded sample (8 experts, 2048 tokens x top-8 => 16384 rows) on the host."""
+    """Forward of a bounded sample (8 experts, 2048 tokens x top-8 => 16384 rows) on the host,
+    with every host thread torch can use (a launcher that pins OMP_NUM_THREADS=1 is overridden)."""
     import numpy as np
     import torch
+    torch.set_num_threads(os.cpu_count() or 1)
 
     from oracle import moe as omoe
     from oracle import mxfp8 as omx
@@ -153,22 +163,270 @@ def cpu_sample(hidden, inter, steps=1, warmup=0):
 
 
 def run_reference(args):
+    """The reference arm: the oracle port of the path on this machine's host cores. A pass of the
+    sample is tens of seconds, so at most three passes are timed whatever --steps asks for; the
+    line's `steps` and `warmup` are the passes actually run and `config` names the sample."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from pipelink_b200 import mok
     shape = mok.CONFIG2
-    # every pass is tens of seconds of host work, so at most three passes are timed (and one warm-up
-    # pass run) however large --steps is; `sample_passes` says how many
     passes = max(1, min(args.steps, 3))
-    base, sec = cpu_sample(shape.hidden, shape.intermediate, steps=passes, warmup=min(args.warmup, 1))
+    warm = min(args.warmup, 1)
+    base, sec = cpu_sample(shape.hidden, shape.intermediate, steps=passes, warmup=warm)
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "steps": passes, "warmup": warm, "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU port of the e4m3/ue8m0 path)",
-            "data": "synthetic", "config": {"workload": shape.name, "sample": base["sample"], "sample_passes": passes},
+            "data": "synthetic",
+            "config": {"workload": shape.name + " (bounded sample)", "same_config": False, "sample": base["sample"],
+                       "sample_passes": passes, "hidden": shape.hidden, "intermediate": shape.intermediate,
+                       "topk": shape.topk},
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# small cases: one hot kernel each, a few GB on the device, a handful of launches
+# ---------------------------------------------------------------------------------------------
+def run_case(args):
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("--case needs a CUDA device")
+    if args.case == "ep-phases":
+        return ep_phases_case(args.tokens or 8192)
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    if args.case == "moe":
+        # MoE forward at the headline expert shape on a quarter of the tokens
+        from pipelink_b200 import mok
+        shape = mok.Shape("case", 64, 4096, 2048, 8, args.tokens or 4096)
+        E, H, I = shape.experts, shape.hidden, shape.intermediate
+        mk = lambda *d: (torch.randn(*d, device=dev) * 0.02).to(torch.bfloat16)
+        host = mok.MoKHost(shape)
+        host.load_weights(mk(E, I, H), mk(E, I, H), mk(E, H, I))
+        inputs = mok.MoKHost.new_inputs(shape, 1, dev)
+        for _ in range(3):
+            out = host.forward(inputs)["output"]
+        torch.cuda.synchronize()
+        print("moe ok", float(out.float().abs().mean()))
+    elif args.case == "attention":
+        from pipelink_b200 import attention as att
+        seq = args.tokens or 8192
+        q = torch.randn(1, seq, 32, 128, device=dev).to(torch.bfloat16)
+        k = torch.randn(1, seq, 8, 128, device=dev).to(torch.bfloat16)
+        v = torch.randn(1, seq, 8, 128, device=dev).to(torch.bfloat16)
+        for _ in range(3):
+            out, _ = att.attention_fwd(q, k, v)
+        torch.cuda.synchronize()
+        print("attention ok", float(out.float().abs().mean()))
+    else:
+        # 16 layers, vocabulary 128256, four tokens at position 4096
+        from pipelink_b200 import decode as hd
+        L, V = 16, 128256
+        mk = lambda *d: (torch.randn(*d, device=dev) * 0.02).to(torch.bfloat16)
+        ones = lambda *d: torch.ones(*d, device=dev)
+        w = dict(qkv_w=mk(L, hd.QKV_ROWS, hd.HIDDEN), o_w=mk(L, hd.HIDDEN, hd.HIDDEN), up_w=mk(L, hd.FFN, hd.HIDDEN),
+                 gate_w=mk(L, hd.FFN, hd.HIDDEN), down_w=mk(L, hd.HIDDEN, hd.FFN), attn_norm=ones(L, hd.HIDDEN),
+                 mlp_norm=ones(L, hd.HIDDEN), lm_norm=ones(hd.HIDDEN), lm_head=mk(V, hd.HIDDEN))
+        s = hd.DecodeSession(w, max_seq_len=4096 + 16, device=dev)
+        s.k_cache[:, :4096].normal_()
+        s.v_cache[:, :4096].normal_()
+        s.start(1, 4096)
+        s.decode(4)
+        print("tokens", s.token_out[4097:4101].tolist())
+
+
+def ep_phases_case(tokens, steps=10):
+    """One rank per GPU under torchrun. Prints, for each phase of the expert-parallel forward and
+    backward step at the headline expert shape, the mean / min / max over ranks of its device time
+    (CUDA events around each call; phases run back to back on one stream)."""
+    import torch
+    import torch.distributed as dist
+
+    from pipelink_b200 import ep, mok
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    base = mok.CONFIG2
+    shape = mok.Shape("ep-phases", base.experts, base.hidden, base.intermediate, base.topk, tokens)
+
+    def table(title, session, phases):
+        h = session.host
+        for _ in range(3):
+            session.step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        acc = [0.0] * len(phases)
+        for _ in range(steps):
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(phases) + 1)]
+            evs[0].record()
+            for i, (_, fn) in enumerate(phases):
+                fn()
+                evs[i + 1].record()
+            torch.cuda.synchronize()
+            for i in range(len(phases)):
+                acc[i] += evs[i].elapsed_time(evs[i + 1]) / steps
+        mine = torch.tensor(acc, device=dev)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        h.status.check("ep-phases")
+        if rank == 0:
+            m = torch.stack(every).cpu()
+            print(f"{title}: world {world}, tokens per rank {tokens}, rows on rank 0: {int(h.schedule.num_tokens.item())}")
+            for i, (name, _) in enumerate(phases):
+                print(f"  {name:24s} mean {m[:, i].mean():.3f}  min {m[:, i].min():.3f}  max {m[:, i].max():.3f} ms")
+            print(f"  {'sum of means':24s} {float(m.mean(0).sum()):.3f} ms", flush=True)
+        dist.barrier()
+
+    session = ep.BenchSession(shape, dev, rank, world)
+    h = session.host
+    table("forward", session, h.forward_phases())
+    session.group.close()
+    del session, h
+    torch.cuda.empty_cache()
+    session = ep.BenchSession(shape, dev, rank, world, train=True)
+    h = session.host
+    h.d_out_buffer.copy_(session.d_out)
+    table("forward (training) + backward", session, h.forward_phases(train=True) + h.backward_phases())
+    session.group.close()
+    dist.destroy_process_group()
+
+
+def measure_fp8_peak(dev, seconds=2.0, n=8192):
+    """Dense FP8 throughput of this GPU, measured in this run: cuBLASLt E4M3 x E4M3 -> bf16, n^3,
+    through torch._scaled_mm with unit per-tensor scales. `burst` is the best of 10 single calls,
+    `sustained` the mean over at least `seconds` of back-to-back calls (the figure a kernel timed
+    inside a long step is held to). Returns None with the reason if the call is not available."""
+    import torch
+    try:
+        a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()        # column-major operand
+        one = torch.ones((), device=dev)
+        run = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        flop = 2.0 * n ** 3
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        total_ms, calls = 0.0, 0
+        while total_ms < seconds * 1e3:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(200):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            total_ms += e0.elapsed_time(e1)
+            calls += 200
+        return {"burst": flop / (best * 1e-3) / 1e12, "sustained": flop * calls / (total_ms * 1e-3) / 1e12,
+                "unit": UNIT, "how": f"torch._scaled_mm e4m3 {n}^3 -> bf16 (cuBLASLt): best of 10 calls; "
+                                     f"{calls} calls back to back over {total_ms / 1e3:.1f} s"}
+    except Exception as exc:  # noqa: BLE001 - any failure means "no measured figure", never a failed bench
+        return {"burst": None, "sustained": None, "unit": UNIT, "how": f"unavailable: {type(exc).__name__}: {exc}"[:200]}
+
+
+def host_copy_ceiling(dev, world, nbytes_in, nbytes_out, iters=10):
+    """What the machine gives N ranks that do nothing but this benchmark's host copies at the same
+    time: pinned host -> device of one step's inputs and device -> host of one step's result, on two
+    streams, all ranks together. Returns GB/s per rank (min and mean over ranks) and the step time
+    those rates alone would allow."""
+    import torch
+    import torch.distributed as dist
+    h_in = torch.empty(nbytes_in, dtype=torch.uint8).pin_memory()
+    h_out = torch.empty(nbytes_out, dtype=torch.uint8).pin_memory()
+    d_in = torch.empty(nbytes_in, dtype=torch.uint8, device=dev)
+    d_out = torch.empty(nbytes_out, dtype=torch.uint8, device=dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def run(n):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        with torch.cuda.stream(s_in):
+            ev[0].record()
+            for _ in range(n):
+                d_in.copy_(h_in, non_blocking=True)
+            ev[1].record()
+        with torch.cuda.stream(s_out):
+            ev[2].record()
+            for _ in range(n):
+                h_out.copy_(d_out, non_blocking=True)
+            ev[3].record()
+        torch.cuda.synchronize()
+        return ev[0].elapsed_time(ev[1]) / n, ev[2].elapsed_time(ev[3]) / n
+
+    run(2)
+    if world > 1:
+        dist.barrier()
+    ms_in, ms_out = run(iters)
+    t = torch.tensor([ms_in, ms_out], dtype=torch.float64, device=dev)
+    every = [torch.zeros_like(t) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(every, t)
+    else:
+        every = [t]
+    m = torch.stack(every).cpu()
+    gbs_in, gbs_out = nbytes_in / (m[:, 0] * 1e-3) / 1e9, nbytes_out / (m[:, 1] * 1e-3) / 1e9
+    return {"h2d_gbs_per_rank": {"min": float(gbs_in.min()), "mean": float(gbs_in.mean())},
+            "d2h_gbs_per_rank": {"min": float(gbs_out.min()), "mean": float(gbs_out.mean())},
+            "ms_per_step_from_copies_alone": float(torch.maximum(m[:, 0], m[:, 1]).max()),
+            "ranks_copying_together": world, "iters": iters}
+
+
+def ep_forward_parity(session, dev, rank, world, sample=256):
+    """Value check of the expert-parallel forward inside the run that is timed: `sample` tokens of
+    every rank (inputs all-gathered with torch.distributed, as are the ranks' quantised expert
+    weights) go through a single-rank pass of this library on this GPU, and this rank's rows of the
+    expert-parallel output must equal that pass bit for bit (every step of the path is local to a
+    row, and the combine order is fixed, so the two passes do the same arithmetic per row)."""
+    import torch
+    import torch.distributed as dist
+    from pipelink_b200 import mok
+    h, sh = session.host, session.shape
+    session.step()
+    h.status.check("parity step")
+    torch.cuda.synchronize()
+    gen = torch.Generator().manual_seed(4242)
+    idx = torch.randperm(sh.tokens, generator=gen)[:sample].sort().values.to(dev)
+
+    def gather(t):
+        t = t.contiguous()
+        out = torch.empty((world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+        dist.all_gather_into_tensor(out, t)
+        return out
+
+    x = gather(session.inputs.x[idx])
+    routes = gather(session.inputs.experts[idx].to(torch.int32))
+    router = gather(session.inputs.router[idx])
+    w = h.weights
+    single = mok.MoKHost(mok.Shape("parity", sh.experts, sh.hidden, sh.intermediate, sh.topk, world * sample), device=dev)
+    single.weights = {name: gather(w[name]) for name in ("w13_fp8", "w13_sc", "w_routed_down_fp8", "w_routed_down_sc")}
+    want = single.forward(mok.Inputs(x, routes.long(), router))["output"][rank * sample:(rank + 1) * sample]
+    got = h.buffers["output"][idx]
+    torch.cuda.synchronize()
+    equal = bool(torch.equal(want.view(torch.int16), got.view(torch.int16)))
+    finite = bool(torch.isfinite(got.float()).all()) and float(got.float().abs().mean()) > 0
+    diff = float((want.float() - got.float()).abs().max())
+    flags = torch.tensor([int(equal and finite)], dtype=torch.int32, device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    worst = torch.tensor([diff], dtype=torch.float64, device=dev)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    del single
+    torch.cuda.empty_cache()
+    return {"ok": bool(flags.item()), "bitwise_equal_on_every_rank": bool(flags.item()), "rows_per_rank": sample,
+            "max_abs_diff": float(worst.item()), "receive_streams": bool(h.stream_push),
+            "dispatch": "in-kernel" if h.fused_dispatch else "pull kernel",
+            "against": "single-rank pass of this library over the all-gathered sample (same GPU)"}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -201,6 +459,11 @@ def run_native(args):
         session = ep.BenchSession(shape, dev, rank, world)
 
     flop_per_rank = 6.0 * shape.tokens * shape.topk * shape.hidden * shape.intermediate
+    parity = None
+    if world > 1 and not args.no_parity:
+        parity = {"ep_forward": ep_forward_parity(session, dev, rank, world)}
+        if not parity["ep_forward"]["ok"]:
+            raise RuntimeError(f"expert-parallel forward differs from the single-rank pass: {parity}")
     launches_per_step = session.launches_per_step
     sampler = ClockSampler(local)
     if rank == 0:
@@ -246,17 +509,33 @@ def run_native(args):
     ms_step = ms_total / args.steps
     value = flop_per_rank * world / (ms_step * 1e-3) / 1e12
 
-    # dominant kernel: the fused gate/up GEMM (2/3 of the FLOPs)
+    # dominant kernel: the fused gate/up GEMM (2/3 of the FLOPs), timed with CUDA events inside the
+    # timed steps; held to the dense FP8 rate cuBLASLt sustains on this GPU in this run
     k_ms = statistics.mean(a.elapsed_time(b) for a, b in session.kernel_events) if session.kernel_events else None
-    fp8_peak = 2.0 * pk["bf16_sustained"]
+    fp8 = measure_fp8_peak(dev) if rank == 0 else None
+    if world > 1:
+        box = [fp8]
+        dist.broadcast_object_list(box, src=0)
+        fp8 = box[0]
+    assumed = 2.0 * pk["bf16_sustained"]
+    if fp8 and fp8["sustained"]:
+        fp8_peak = fp8["sustained"]
+        peak_source = "dense FP8 GEMM measured in this run (fp8_tflops_measured.sustained)"
+    else:
+        fp8_peak = assumed
+        peak_source = f"assumed: 2 x bf16_tflops_sustained of {pk['source']} peaks (no FP8 figure could be measured)"
     roof = None
     if k_ms:
         achieved = (4.0 * shape.tokens * shape.topk * shape.hidden * shape.intermediate) / (k_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": "grouped gate/up GEMM + SwiGLU + requantise",
                 "achieved": achieved, "peak": fp8_peak, "unit": UNIT, "frac": achieved / fp8_peak,
+                "peak_source": peak_source,
+                "frac_of_fp8_burst_measured": achieved / fp8["burst"] if fp8 and fp8["burst"] else None,
+                "frac_of_2x_bf16_sustained": achieved / assumed,
+                "frac_of_nominal_4500": achieved / 4500.0,
                 "traffic": session.traffic_per_launch(),
-                "peak_source": f"2 x bf16_tflops_sustained of {pk['source']} peaks (dense FP8 = 2 x bf16 rate; "
-                               "the peaks file holds no FP8 figure)",
+                "traffic_source": "estimated: algorithmic bytes of this launch x the ratio dram bytes / algorithmic "
+                                  "bytes of a profiler capture of the 4096-token case (not a counter of this launch)",
                 "ms_per_launch": k_ms}
 
     e2e = None
@@ -267,13 +546,17 @@ def run_native(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e = {"value": flop_per_rank * world / (float(t.item()) * 1e-3) / 1e12, "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": float(t.item())}
+        if world > 1:
+            e2e["host_copy_ceiling"] = host_copy_ceiling(dev, world, h2d, d2h)
 
     attention = None
     if not args.no_attention and args.tokens is None:
         if world == 1:
             attention = attention_leg(dev, pk)
         else:
-            attention = cp_attention_leg(dev, pk, rank, world)
+            attention = cp_attention_leg(dev, pk, rank, world, check=not args.no_parity)
+            if parity is not None and attention.get("parity") is not None:
+                parity["cp_attention"] = attention["parity"]
 
     train = None
     if world > 1 and not args.no_train and args.tokens is None:
@@ -309,8 +592,9 @@ def run_native(args):
                            "expert_padding": mok.expert_padding(), "gemm_tile": "cta-pair 256x256"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
                 "roofline": roof, "cpu_baseline": cpu, "decode": decode, "attention": attention, "ep_fwd_bwd": train,
-                "tp_gemm": tp_gemm,
-                "frac_of_fp8_peak_whole_step": value / world / fp8_peak}
+                "tp_gemm": tp_gemm, "parity": parity, "fp8_tflops_measured": fp8,
+                "frac_of_fp8_peak_whole_step": value / world / fp8_peak,
+                "frac_of_nominal_4500_whole_step": value / world / 4500.0}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -346,7 +630,8 @@ def ep_train_leg(shape, dev, rank, world, pk, steps=5):
     out = {"metric": "mxfp8_moe_ffn_fwd_bwd_tflops", "value": flop * world / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms,
            "steps": steps, "tokens_per_rank": shape.tokens, "world": world, "scaling": "weak",
            "gpu_launches": session.launches_per_step * steps,
-           "frac_of_fp8_peak": flop / (ms * 1e-3) / 1e12 / (2.0 * pk["bf16_sustained"]),
+           "frac_of_2x_bf16_sustained": flop / (ms * 1e-3) / 1e12 / (2.0 * pk["bf16_sustained"]),
+           "frac_of_nominal_4500": flop / (ms * 1e-3) / 1e12 / 4500.0,
            "nvlink_payload_bytes_per_rank": {"dispatch_e4m3": payload * (1 + 1 / 32), "combine_bf16": payload * 2,
                                              "d_out_bf16": payload * 2, "x_bf16": payload * 2, "d_x_bf16": payload * 2}}
     session.group.close()
@@ -436,9 +721,11 @@ def attention_leg(dev, pk, seq=32768, steps=3):
                          "frac": tf / pk["bf16_sustained"], "peak_source": f"bf16_tflops_sustained of {pk['source']} peaks"}}
 
 
-def cp_attention_leg(dev, pk, rank, world, seq=131072, steps=2):
-    """BASELINE.json configs[4]: context-parallel causal prefill, S = 131072 split zigzag over the
-    ranks, K/V pushed over NVLink with per-block counters. Time = max over ranks."""
+def cp_attention_leg(dev, pk, rank, world, seq=131072, steps=2, check=True):
+    """Context-parallel causal prefill: S = 131072 split zigzag over the ranks, K/V pushed over
+    NVLink with per-block counters. Time = max over ranks. With `check`, every rank also runs the
+    whole sequence through the single-GPU kernel (Q, K, V all-gathered) and compares its own rows
+    of O and LSE with that result bit for bit."""
     import torch
     import torch.distributed as dist
 
@@ -454,6 +741,30 @@ def cp_attention_leg(dev, pk, rank, world, seq=131072, steps=2):
     r = att.CpRank(seq, Hq, Hkv, rank, world, slab.ptrs, layout, dev)
     r.step(q, k, v)
     torch.cuda.synchronize()
+    parity = None
+    if check:
+        def whole(t):
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t)
+            full = torch.empty((seq,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+            C = seq // (2 * world)
+            for w_, part in enumerate(parts):      # rank w_ owns chunks w_ and 2W - 1 - w_
+                full[w_ * C:(w_ + 1) * C] = part[:C]
+                full[(2 * world - 1 - w_) * C:(2 * world - w_) * C] = part[C:]
+            return full
+        o_full, lse_full = att.attention_fwd(whole(q)[None], whole(k)[None], whole(v)[None])
+        mine = att.shard_zigzag(o_full[0], world, rank)
+        lse_mine = att.shard_zigzag(lse_full.T.contiguous(), world, rank).T
+        ok = torch.equal(mine.view(torch.int16), r.out.view(torch.int16)) and torch.equal(lse_mine, r.lse) \
+            and bool(torch.isfinite(r.lse).all())
+        flag = torch.tensor([int(ok)], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity = {"ok": bool(flag.item()), "bitwise_equal_on_every_rank": bool(flag.item()), "rows_per_rank": C2,
+                  "against": "single-GPU kernel over the all-gathered sequence (same GPU)"}
+        del o_full, lse_full, mine, lse_mine
+        torch.cuda.empty_cache()
+        if not parity["ok"]:
+            raise RuntimeError("context-parallel attention differs from the single-GPU result")
     dist.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
@@ -471,14 +782,14 @@ def cp_attention_leg(dev, pk, rank, world, seq=131072, steps=2):
     chunk = seq // (2 * world)
     payload = 1.5 * world * (world - 1) * chunk * Hkv * 128 * 2 * 2   # K+V bytes that must cross NVLink, all ranks
     return {"metric": "cp_causal_prefill_attention_tflops", "value": tf, "unit": "TFLOP/s", "ms": ms, "seq": seq,
-            "world": world, "nvlink_payload_bytes": payload, "scaling": "strong",
+            "world": world, "nvlink_payload_bytes": payload, "scaling": "strong", "parity": parity,
             "roofline": {"bound": "tensor", "achieved": tf / world, "peak": pk["bf16_sustained"], "unit": "TFLOP/s per GPU",
                          "frac": tf / world / pk["bf16_sustained"]}}
 
 
 def decode_leg(dev, pk, steps=128, prefill=4096):
-    """BASELINE.json configs[2]: Llama-1B-shaped batch-1 greedy decode, KV pre-filled to 4096,
-    128 steps, one cooperative launch per token. Replicas only: the path does not shard."""
+    """Llama-1B-shaped batch-1 greedy decode, KV pre-filled to 4096, 128 steps, one cooperative
+    launch per token. Replicas only: the path does not shard."""
     import torch
 
     from pipelink_b200 import decode as hd
@@ -516,7 +827,7 @@ def decode_leg(dev, pk, steps=128, prefill=4096):
 
 
 class SingleRank:
-    """configs[1]: every token and every expert on one GPU."""
+    """The single-GPU workload: every token and every expert on one GPU."""
 
     launches_per_step = 7  # schedule x3, dispatch, gate/up GEMM, down GEMM, epilogue
 
@@ -575,9 +886,9 @@ class SingleRank:
         self.host.status.check("bench")
 
     def traffic_per_launch(self):
-        """dram bytes of one gate/up GEMM launch: the ncu capture of the 4096-token case
-        (profiles/grouped_gemm_pair_moe_ffn_fwd.md) read 1.062 x that case's algorithmic bytes;
-        scaled here by this workload's algorithmic bytes (A, output and their scales grow with rows)."""
+        """An estimate of the dram bytes of one gate/up GEMM launch: a profiler capture of the
+        4096-token case read 1.062 x that case's algorithmic bytes; scaled here by this workload's
+        algorithmic bytes (A, output and their scales grow with rows, B does not)."""
         sh, P = self.shape, self.host.capacity
         H, I, E = sh.hidden, sh.intermediate, sh.experts
         rows = min(P, sh.tokens * sh.topk + E * self.host.padding // 2)
@@ -617,7 +928,10 @@ def main():
     real_stdout = os.dup(1)
     os.dup2(2, 1)
     sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
-    if args.impl == "reference":
+    if args.case is not None:
+        sys.stdout = sys.stderr         # a case prints no benchmark line
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_native(args)

@@ -429,6 +429,22 @@ int plb_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks, i
 int plb_ep_stream_rows(const int32_t* peer_rank, const int32_t* dest_row, const int32_t* num_tokens, int64_t capacity,
                        int rank, int world, int64_t stream_cap, int32_t* stream_row, void* const* index_peers,
                        void* stream);
+/* plb_moe_schedule with the receive-stream positions written by the same launches (no separate
+ * plb_ep_stream_rows pass): stream_row and the home ranks' index come out exactly as that pass
+ * writes them, because inside an expert segment the rows of one source rank form one run and the
+ * counts the schedule already keeps give every run's place in its stream. Needs
+ * tokens * topk % 1024 == 0 (PLB_E_ARGUMENT otherwise; use the two-call form then) and scratch of
+ * plb_moe_schedule_streams_scratch_bytes(). The reference builds its schedule on the host before
+ * the kernel (campaigns/mok/host/mok_port_host.py:59-69); the stream positions have no counterpart
+ * there (its combine writes token * topk + slot, campaigns/mok/port/comm/comm.cu:124-129). */
+size_t plb_moe_schedule_streams_scratch_bytes(int world, int tokens, int topk, int num_local_experts);
+int plb_moe_schedule_streams(const int32_t* routes, int world, int tokens, int topk, int expert_base,
+                             int num_local_experts, int capacity, int padding, int32_t* peer_rank,
+                             int32_t* peer_token_idx, int32_t* dest_row, int32_t* num_tokens,
+                             int32_t* tokens_per_expert, int32_t* expert_offsets, int32_t* block_expert,
+                             void* scratch, size_t scratch_bytes, int rank, int64_t stream_cap,
+                             int32_t* stream_row, void* const* index_peers, plb_status* status,
+                             void* stream);
 int plb_moe_fwd_epilogue_indexed(const void* y_shared_bf16, const void* rows_bf16, const int32_t* row_index,
                                  const float* router_weights, int64_t tokens, int topk, int64_t hidden,
                                  void* out_bf16, void* stream);

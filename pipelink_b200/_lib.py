@@ -34,6 +34,10 @@ PROTOTYPES = {
     "plb_moe_schedule": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "plb_moe_schedule_streams_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "plb_moe_schedule_streams": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_size_t, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "plb_moe_schedule_noalloc_max_scratch_bytes": (c_size_t, []),
     "plb_moe_schedule_noalloc": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -146,6 +146,56 @@ int plb_moe_schedule(const int32_t* routes, int world, int tokens, int topk, int
   return from_cuda(plb::launch_schedule(a, static_cast<cudaStream_t>(stream)));
 }
 
+size_t plb_moe_schedule_streams_scratch_bytes(int world, int tokens, int topk, int num_local_experts) {
+  return plb_moe_schedule_scratch_bytes(world, tokens, topk, num_local_experts) +
+         2u * static_cast<size_t>(world) * num_local_experts * sizeof(int);
+}
+
+int plb_moe_schedule_streams(const int32_t* routes, int world, int tokens, int topk, int expert_base,
+                             int num_local_experts, int capacity, int padding, int32_t* peer_rank,
+                             int32_t* peer_token_idx, int32_t* dest_row, int32_t* num_tokens,
+                             int32_t* tokens_per_expert, int32_t* expert_offsets, int32_t* block_expert,
+                             void* scratch, size_t scratch_bytes, int rank, int64_t stream_cap,
+                             int32_t* stream_row, void* const* index_peers, plb_status* status,
+                             void* stream) {
+  if (world < 1 || world > 32 || tokens < 0 || topk < 1 || num_local_experts < 1 || num_local_experts > 1024)
+    return PLB_E_ARGUMENT;
+  if (capacity < 0 || capacity % 128 || padding < 128 || padding % 128) return PLB_E_ARGUMENT;
+  if (!routes || !peer_rank || !peer_token_idx || !dest_row || !num_tokens || !tokens_per_expert ||
+      !expert_offsets || !block_expert || !status || !stream_row || !index_peers)
+    return PLB_E_ARGUMENT;
+  if (rank < 0 || rank >= world || stream_cap < 1 || stream_cap * world > 2147483647LL) return PLB_E_ARGUMENT;
+  // a counting chunk must not span two source ranks
+  if ((static_cast<int64_t>(tokens) * topk) % plb::kScheduleChunk != 0) return PLB_E_ARGUMENT;
+  const size_t need = plb_moe_schedule_streams_scratch_bytes(world, tokens, topk, num_local_experts);
+  if (scratch == nullptr || scratch_bytes < need) return PLB_E_CAPACITY;
+  plb::ScheduleArgs a;
+  a.routes = routes;
+  a.world = world;
+  a.tokens = tokens;
+  a.topk = topk;
+  a.expert_base = expert_base;
+  a.num_local_experts = num_local_experts;
+  a.capacity = capacity;
+  a.padding = padding;
+  a.peer_rank = peer_rank;
+  a.peer_token_idx = peer_token_idx;
+  a.dest_row = dest_row;
+  a.num_tokens = num_tokens;
+  a.tokens_per_expert = tokens_per_expert;
+  a.expert_offsets = expert_offsets;
+  a.block_expert = block_expert;
+  a.scratch = static_cast<int*>(scratch);
+  a.status = reinterpret_cast<plb::Status*>(status);
+  a.stream_row = stream_row;
+  a.stream_index_peers = reinterpret_cast<int* const*>(index_peers);
+  a.stream_tables = static_cast<int*>(scratch) +
+                    plb_moe_schedule_scratch_bytes(world, tokens, topk, num_local_experts) / sizeof(int);
+  a.rank = rank;
+  a.stream_cap = stream_cap;
+  return from_cuda(plb::launch_schedule(a, static_cast<cudaStream_t>(stream)));
+}
+
 size_t plb_moe_schedule_noalloc_max_scratch_bytes(void) {
   return static_cast<size_t>(plb::schedule_static_scratch_ints()) * sizeof(int);
 }

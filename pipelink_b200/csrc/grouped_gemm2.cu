@@ -48,6 +48,7 @@ constexpr int kOffBars = kOffStaging + kStagingBytes;
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes2 = kOffBars + kBarrierBytes + 1024;
 static_assert(kOffSf % 1024 == 0 && kOffStaging % 16 == 0, "shared memory layout");
+static_assert(kStagingBytes / 2 >= 4 * 4096, "dispatch ring: four rows of up to 4096 bytes per dispatch warp");
 constexpr int kThreads2 = 384;
 // Register hand-over between the roles. ptxas gives every thread 168 registers (launch bounds of 384
 // threads, one CTA per SM), the CTA's pool is what it was launched with, and setmaxnreg.inc blocks
@@ -95,8 +96,8 @@ struct Params2 {
   const unsigned* ready;    // mode 1: per 256-row tile of A, a counter that reaches ready_target once the
   unsigned ready_target;    //         tile's rows have all arrived (all-gather -> GEMM); null = rows are local
   // mode 0, optional in-kernel dispatch (null pull_xq = A is already in place): warps 2 and 3 of every
-  // CTA take tickets of 32 rows, copy each row's E4M3 bytes and scale words peer -> A through
-  // registers, and count the chunk into its 256-row tile; the load lane acquires a tile's count
+  // CTA take tickets of four rows, copy each row's E4M3 bytes (peer -> shared -> A) and scale words
+  // (through registers), and count the ticket into its 256-row tile; the load lane acquires a tile's count
   // before the tile's first TMA read (campaigns/mok/port/comm/comm.cu:105-123 gives the
   // reference's megakernel the same dispatch role)
   const uint8_t* const* pull_xq;        // per rank: u8 [tokens, K]
@@ -473,53 +474,69 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     } else if (MODE == 0 && warp >= 2 && p.pull_xq != nullptr) {
       // ---------------------------------------------------------- dispatch warps (two per CTA)
-      // A ticket is a chunk of 32 consecutive rows (an eighth of a row tile): lane l holds row l's
-      // source; each row crosses as 16-byte loads into registers and 16-byte stores (the load/store
-      // path is idle while the TMA unit and shared memory feed the tensor pipe: bulk copies here
-      // cost the mainloop as much as the separate pull kernel they replaced); the chunk is counted
-      // into its tile after a fence.
+      // A ticket is four consecutive rows. Their bytes cross as 16-byte asynchronous copies
+      // peer -> shared memory (no registers held while the loads are in flight, so all four rows,
+      // up to 16 KB per warp, travel at once; the ring is the staging area of the row-store
+      // epilogue, which this mode does not use), then shared -> A with plain stores, and the ticket
+      // is counted into its row tile after a fence. Any resident CTA can serve any ticket, and the
+      // dispatch warps wait for nothing, so the tiles the load lanes wait for always complete.
+      // (Bulk copies here cost the mainloop as much as the separate pull kernel they replaced: the
+      // TMA unit is what feeds the tensor pipe. The load/store path is idle in this kernel.)
+      constexpr int kTicketRows = 4;
+      const uint32_t ring = smem_base + kOffStaging + static_cast<uint32_t>(warp - 2) * (kStagingBytes / 2);
       const int vecs = p.pull_row_bytes >> 4;                  // <= 256
       const int col_blocks = p.pull_row_bytes >> 7;
       const int rows_live = m_tiles_live * 256;
       for (;;) {
         int base = 0;
-        if (lane == 0) base = static_cast<int>(atomicAdd(p.pull_ticket, 32u));
+        if (lane == 0) base = static_cast<int>(atomicAdd(p.pull_ticket, static_cast<unsigned>(kTicketRows)));
         base = __shfl_sync(0xFFFFFFFFu, base, 0);
         if (base >= rows_live) break;
-        const int my_src = p.pull_peer_rank[base + lane];
-        const int my_tok = my_src >= 0 ? p.pull_token_idx[base + lane] : 0;
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i) {
+        int my_src = -1, my_tok = 0;
+        if (lane < kTicketRows) {
+          my_src = p.pull_peer_rank[base + lane];
+          my_tok = my_src >= 0 ? p.pull_token_idx[base + lane] : 0;
+        }
+        uint32_t word[kTicketRows];
+#pragma unroll
+        for (int i = 0; i < kTicketRows; ++i) {
           const int src = __shfl_sync(0xFFFFFFFFu, my_src, i);
           const int64_t t = __shfl_sync(0xFFFFFFFFu, my_tok, i);
+          word[i] = 0u;
+          if (src >= 0) {
+            const uint8_t* from = p.pull_xq[src] + t * p.pull_row_bytes;
+            for (int v = lane; v < vecs; v += 32)
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring + i * 4096 + v * 16), "l"(from + v * 16)
+                           : "memory");
+            if (lane < col_blocks) word[i] = p.pull_sc_rows[src][t * col_blocks + lane];
+          }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < kTicketRows; ++i) {
+          const int src = __shfl_sync(0xFFFFFFFFu, my_src, i);
           const int r = base + i;
           uint4* dst = reinterpret_cast<uint4*>(p.pull_dst + static_cast<size_t>(r) * p.pull_row_bytes);
-          uint32_t word = 0u;
-          const uint4* from = src >= 0 ? reinterpret_cast<const uint4*>(p.pull_xq[src] + t * p.pull_row_bytes) : nullptr;
-          if (src >= 0 && lane < col_blocks) word = p.pull_sc_rows[src][t * col_blocks + lane];
-#pragma unroll 1
-          for (int v0 = 0; v0 < vecs; v0 += 128) {           // 2 KB of the row per pass
-            uint4 tmp[4];
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const int idx = v0 + v * 32 + lane;
-              tmp[v] = (from != nullptr && idx < vecs) ? from[idx] : make_uint4(0u, 0u, 0u, 0u);
-            }
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const int idx = v0 + v * 32 + lane;
-              if (idx < vecs) dst[idx] = tmp[v];
-            }
+          // every lane reads back exactly the 16-byte pieces it copied in
+          for (int v = lane; v < vecs; v += 32) {
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (src >= 0)
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                           : "r"(ring + i * 4096 + v * 16)
+                           : "memory");
+            dst[v] = val;
           }
           if (lane < col_blocks) {
             const size_t off = static_cast<size_t>(r >> 7) * col_blocks * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4;
-            *reinterpret_cast<uint32_t*>(p.pull_dst_sc + off + static_cast<size_t>(lane) * 512) = word;
+            *reinterpret_cast<uint32_t*>(p.pull_dst_sc + off + static_cast<size_t>(lane) * 512) = word[i];
           }
         }
-        // every lane's stores, then one release increment for the chunk
+        // every lane's stores, then one release increment for the ticket
         __threadfence();
         __syncwarp();
-        if (lane == 0) red_release_gpu_add(p.pull_ready + (base >> 8), 32u);
+        if (lane == 0) red_release_gpu_add(p.pull_ready + (base >> 8), static_cast<unsigned>(kTicketRows));
       }
     }
   } else {

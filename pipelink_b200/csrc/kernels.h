@@ -46,6 +46,16 @@ struct ScheduleArgs {
   int* block_expert;      // [capacity / 128] local expert of each 128-row block, -1 if unused
   int* scratch;           // [schedule_scratch_ints(...)]
   Status* status;
+  // Receive-stream positions of the combine push, written by the same three launches when
+  // stream_row is set (needs tokens * topk % kScheduleChunk == 0, so that no chunk spans two ranks):
+  // stream_row[p] = rank * stream_cap + (earlier rows of this schedule with the same home rank), and
+  // that position is also stored at stream_index_peers[home][dest_row[p]], where the home rank's
+  // epilogue looks its (token, slot) rows up.
+  int* stream_row = nullptr;                // [capacity], -1 on padding rows
+  int* const* stream_index_peers = nullptr; // per home rank: i32 [tokens * topk]
+  int* stream_tables = nullptr;             // scratch, [2 * world * num_local_experts]
+  int rank = 0;
+  int64_t stream_cap = 0;
 };
 constexpr int kScheduleChunk = 1024;
 inline int64_t schedule_scratch_ints(int64_t entries, int num_local_experts) {

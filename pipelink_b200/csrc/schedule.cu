@@ -64,6 +64,29 @@ __global__ void schedule_scan_kernel(ScheduleArgs a, int chunks) {
     }
   }
   __syncthreads();
+  if (a.stream_row != nullptr && chunks > 0) {
+    // Inside an expert segment the rows of source rank r form one run. Its first row (relative to
+    // the segment) is the exclusive count at r's first chunk; the rows rank r has in the segments
+    // of earlier experts are what precedes that run in r's receive stream.
+    const int per_rank_chunks = chunks / a.world;
+    int* base = a.stream_tables;
+    int* start = a.stream_tables + a.world * E;
+    for (int i = threadIdx.x; i < a.world * E; i += blockDim.x) {
+      const int r = i / E, e = i - r * E;
+      start[i] = a.scratch[static_cast<int64_t>(r) * per_rank_chunks * E + e];
+    }
+    __syncthreads();
+    if (threadIdx.x < a.world) {
+      const int r = threadIdx.x;
+      int running = 0;
+      for (int e = 0; e < E; ++e) {
+        const int end = r + 1 < a.world ? start[(r + 1) * E + e] : a.tokens_per_expert[e];
+        base[r * E + e] = running;
+        running += end - start[r * E + e];
+      }
+    }
+    __syncthreads();
+  }
   if (threadIdx.x == 0) {
     int64_t off = 0;
     for (int e = 0; e < E; ++e) {
@@ -137,6 +160,12 @@ schedule_fill_kernel(ScheduleArgs a, int64_t entries) {
       a.peer_rank[pos] = src;
       a.peer_token_idx[pos] = rem / a.topk;
       a.dest_row[pos] = rem;
+      if (a.stream_row != nullptr) {
+        const int in_run = pos - a.expert_offsets[e] - a.stream_tables[(a.world + src) * E + e];
+        const int at = static_cast<int>(static_cast<int64_t>(a.rank) * a.stream_cap) + a.stream_tables[src * E + e] + in_run;
+        a.stream_row[pos] = at;
+        a.stream_index_peers[src][rem] = at;
+      }
     }
     __syncthreads();
     for (int x = threadIdx.x; x < E; x += blockDim.x) {
@@ -155,6 +184,7 @@ schedule_fill_kernel(ScheduleArgs a, int64_t entries) {
         a.peer_rank[p] = -1;
         a.peer_token_idx[p] = 0;
         a.dest_row[p] = -1;
+        if (a.stream_row != nullptr) a.stream_row[p] = -1;
       }
     }
   }
@@ -198,6 +228,10 @@ cudaError_t launch_schedule_static(const ScheduleArgs& args, cudaStream_t stream
 
 cudaError_t launch_schedule(const ScheduleArgs& a, cudaStream_t stream) {
   const int64_t entries = static_cast<int64_t>(a.world) * a.tokens * a.topk;
+  if (a.stream_row != nullptr &&
+      (a.stream_index_peers == nullptr || a.stream_tables == nullptr || a.world > 1024 ||
+       (static_cast<int64_t>(a.tokens) * a.topk) % kScheduleChunk != 0))
+    return cudaErrorInvalidValue;
   const int chunks = static_cast<int>((entries + kScheduleChunk - 1) / kScheduleChunk);
   const int E = a.num_local_experts;
   if (chunks > 0) {

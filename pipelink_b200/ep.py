@@ -192,6 +192,12 @@ class EpMoKHost(mok.MoKHost):
             self.recv = tensor_from_ptr(me_ptr + lay.recv, (W * L * k, H), torch.bfloat16, dev)
             self.recv_index = tensor_from_ptr(me_ptr + lay.recv_index, (L * k,), torch.int32, dev)
             self.stream_row = torch.empty(self.capacity, dtype=torch.int32, device=dev)
+            # the schedule launches write the stream positions themselves when no counting chunk spans
+            # two source ranks; otherwise a separate pass (plb_ep_stream_rows) follows the schedule
+            self.schedule_writes_streams = (L * k) % 1024 == 0
+            if self.schedule_writes_streams:
+                nbytes = _lib.load().plb_moe_schedule_streams_scratch_bytes(W, L, k, self.num_local_experts)
+                self.stream_scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.int32, device=dev)
         self._streamed = False
         me = ptrs[rank]
         self.xq = tensor_from_ptr(me + lay.xq, (L, H), torch.uint8, dev)
@@ -239,6 +245,15 @@ class EpMoKHost(mok.MoKHost):
 
     def build_schedule(self):
         s, sh = self.schedule, self.shape
+        if self.stream_push and self.schedule_writes_streams:
+            _lib.call("plb_moe_schedule_streams", self.routes_all.data_ptr(), self.world, sh.tokens, sh.topk,
+                      self.rank * self.num_local_experts, self.num_local_experts, self.capacity, self.padding,
+                      s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.dest_row.data_ptr(),
+                      s.num_tokens.data_ptr(), s.tokens_per_expert.data_ptr(), s.expert_offsets.data_ptr(),
+                      s.block_expert.data_ptr(), self.stream_scratch.data_ptr(), self.stream_scratch.numel() * 4,
+                      self.rank, sh.tokens * sh.topk, self.stream_row.data_ptr(), self.recv_index_peers.data_ptr(),
+                      self.status.buf.data_ptr(), mok._stream())
+            return
         _lib.call("plb_moe_schedule", self.routes_all.data_ptr(), self.world, sh.tokens, sh.topk,
                   self.rank * self.num_local_experts, self.num_local_experts, self.capacity, self.padding,
                   s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.dest_row.data_ptr(),
@@ -264,7 +279,8 @@ class EpMoKHost(mok.MoKHost):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
         self._streamed = self.stream_push and not train and self.precision != "bf16"
         if self._streamed:
-            self.stream_rows()
+            if not self.schedule_writes_streams:
+                self.stream_rows()
             _lib.call("plb_moe_gemm_down_push", b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(),
                       w["w_routed_down_fp8"].data_ptr(), w["w_routed_down_sc"].data_ptr(),
                       s.block_expert.data_ptr(), s.num_tokens.data_ptr(), self.stream_row.data_ptr(),
@@ -308,6 +324,22 @@ class EpMoKHost(mok.MoKHost):
         self.barrier()          # every rank's rows have landed in my combine buffer
         return self.fwd_epilogue()
 
+    def forward_phases(self, train: bool = False):
+        """device_step() as (name, call) pairs, for per-phase timing."""
+        gate_up = self.gemm_gate_up_train if train else self.gemm_gate_up
+        return [("quantise tokens", self.quantize_tokens), ("publish routes", self.publish_routes),
+                ("barrier", self.barrier), ("schedule", self.build_schedule), ("dispatch pull", self.pull),
+                ("gate/up GEMM", gate_up), ("down GEMM + push", lambda: self.gemm_down_push(train)),
+                ("barrier ", self.barrier), ("epilogue", self.fwd_epilogue)]
+
+    def backward_phases(self):
+        """backward() as (name, call) pairs (d_out already staged in d_out_buffer)."""
+        return [("bwd barrier", self.barrier), ("router gradient", self.bwd_home_side_early),
+                ("d_y pull", self.bwd_pull_dy), ("down dgrad + wgrad", self.bwd_down),
+                ("SwiGLU backward", self.bwd_activation), ("gate/up dgrad + d_x push", self.bwd_push_dx),
+                ("x pull + gate/up wgrad", self.bwd_gate_up_wgrad), ("bwd barrier ", self.barrier),
+                ("slot sum", self.bwd_home_side_late)]
+
     def forward(self, inputs: mok.Inputs, *, check: bool = True, train: bool = False):
         if not self.group.distributed:
             raise ValueError("ranks of a LocalGroup are stepped together: use forward_local_group()")
@@ -321,33 +353,60 @@ class EpMoKHost(mok.MoKHost):
         return {"output": out, **self.context_tensors()}
 
     # ---- backward, in the order backward() issues the steps (mirror of dispatch / combine)
-    def bwd_expert_side(self):
-        """Everything this rank does for the rows of ITS experts: pull w * d_out from the tokens'
-        home ranks, both data gradients, SwiGLU backward, the three weight gradients, and the push
-        of the input-gradient rows back to the home ranks."""
-        s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
-        P, H, I = self.capacity, sh.hidden, sh.intermediate
-        nt = s.num_tokens.data_ptr()
+    def bwd_pull_dy(self):
+        """d_y rows of this rank's experts: w * d_out pulled from the tokens' home ranks."""
+        s, b, sh = self.schedule, self.buffers, self.shape
         _lib.call("plb_ep_bwd_dy", self.d_out_peers.data_ptr(), self.router_w_peers.data_ptr(), s.peer_rank.data_ptr(),
-                  s.peer_token_idx.data_ptr(), s.dest_row.data_ptr(), nt, P, H, b["d_y_routed"].data_ptr(), mok._stream())
+                  s.peer_token_idx.data_ptr(), s.dest_row.data_ptr(), s.num_tokens.data_ptr(), self.capacity, sh.hidden,
+                  b["d_y_routed"].data_ptr(), mok._stream())
+
+    def bwd_down(self):
+        """Down projection: data gradient d_hidden, then the weight gradient over each expert's rows."""
+        b, w, sh = self.buffers, self.weights, self.shape
+        H, I = sh.hidden, sh.intermediate
         dy_q, dy_sc, dy_t, dy_t_sc = mok.mxfp8_quantize(b["d_y_routed"], True, True)
         self._gemm_rows(dy_q, dy_sc, w["w_down_t_fp8"], w["w_down_t_sc"], H, I, b["d_hidden_routed"], self._identity_rows)
         _, _, h_t, h_t_sc = mok.mxfp8_quantize(b["hidden_routed_bf16"], False, True)
         self._wgrad(dy_t, dy_t_sc, h_t, h_t_sc, H, I, b["d_w_routed_down"])
+
+    def bwd_activation(self):
+        s, b, sh = self.schedule, self.buffers, self.shape
         self.select_activation()
         _lib.call("plb_moe_swiglu_bwd", b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(),
-                  b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(), b["d_hidden_routed"].data_ptr(), nt, P, I,
-                  b["d_gate_up_routed"].data_ptr(), mok._stream())
-        dgu_q, dgu_sc, dgu_t, dgu_t_sc = mok.mxfp8_quantize(b["d_gate_up_routed"], True, True)
-        # d_x rows go straight from the GEMM epilogue into the home rank's [tokens * topk, H] buffer
+                  b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(), b["d_hidden_routed"].data_ptr(),
+                  s.num_tokens.data_ptr(), self.capacity, sh.intermediate, b["d_gate_up_routed"].data_ptr(), mok._stream())
+        self._dgu = mok.mxfp8_quantize(b["d_gate_up_routed"], True, True)
+
+    def bwd_push_dx(self):
+        """Gate/up data gradient: d_x rows leave the GEMM epilogue straight into the home rank's
+        [tokens * topk, H] buffer."""
+        s, w, sh = self.schedule, self.weights, self.shape
+        dgu_q, dgu_sc, _, _ = self._dgu
         _lib.call("plb_moe_gemm_down_push", dgu_q.data_ptr(), dgu_sc.data_ptr(), w["w_cat_t_fp8"].data_ptr(),
-                  w["w_cat_t_sc"].data_ptr(), s.block_expert.data_ptr(), nt, s.dest_row.data_ptr(), s.peer_rank.data_ptr(),
-                  P, self.num_local_experts, 2 * I, H, self.push_rotation, self.push_stride, self.d_x_rows_peers.data_ptr(),
-                  self.status.buf.data_ptr(), mok._stream())
-        _lib.call("plb_ep_gather_rows", self.x_peers.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), nt, P, H,
-                  b["x_routed_bf16"].data_ptr(), mok._stream())
+                  w["w_cat_t_sc"].data_ptr(), s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(),
+                  s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, 2 * sh.intermediate, sh.hidden,
+                  self.push_rotation, self.push_stride, self.d_x_rows_peers.data_ptr(), self.status.buf.data_ptr(),
+                  mok._stream())
+
+    def bwd_gate_up_wgrad(self):
+        """Gate/up weight gradient: the bf16 token rows pulled from their home ranks, quantised along the rows."""
+        s, b, sh = self.schedule, self.buffers, self.shape
+        _, _, dgu_t, dgu_t_sc = self._dgu
+        _lib.call("plb_ep_gather_rows", self.x_peers.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
+                  s.num_tokens.data_ptr(), self.capacity, sh.hidden, b["x_routed_bf16"].data_ptr(), mok._stream())
         _, _, x_t, x_t_sc = mok.mxfp8_quantize(b["x_routed_bf16"], False, True)
-        self._wgrad(dgu_t, dgu_t_sc, x_t, x_t_sc, 2 * I, H, b["d_w_routed_gate_up"])
+        self._wgrad(dgu_t, dgu_t_sc, x_t, x_t_sc, 2 * sh.intermediate, sh.hidden, b["d_w_routed_gate_up"])
+        self._dgu = None
+
+    def bwd_expert_side(self):
+        """Everything this rank does for the rows of ITS experts: pull w * d_out from the tokens'
+        home ranks, both data gradients, SwiGLU backward, the three weight gradients, and the push
+        of the input-gradient rows back to the home ranks."""
+        self.bwd_pull_dy()
+        self.bwd_down()
+        self.bwd_activation()
+        self.bwd_push_dx()
+        self.bwd_gate_up_wgrad()
 
     def bwd_home_side_early(self):
         """Needs only this rank's own tokens: the router-weight gradient."""
@@ -420,9 +479,10 @@ STREAM_PUSH_MIN_WORLD = 4
 
 
 class BenchSession:
-    """bench.py's N > 1 arm: one rank of an IpcGroup at BASELINE config 4's per-rank shape."""
+    """One rank of an IpcGroup with synthetic weights and inputs, stepped by the benchmark: the
+    expert-parallel workload at 8192 tokens per rank, forward or forward + backward."""
 
-    launches_per_step = 12  # quantise, scale rows, publish, barrier x2, schedule x3, pull, 2 GEMMs, epilogue (+1 with receive streams)
+    launches_per_step = 12  # quantise, scale rows, publish, barrier x2, schedule x3, pull, 2 GEMMs, epilogue
     # backward adds: barrier x2, router grad, d_y pull, 5 quantise, 2 dgrad GEMMs, SwiGLU backward, x gather,
     # 2 wgrad GEMMs, slot sum, 2 tail-zeroing launches
     launches_per_step_train = 12 + 18    # no stream rows: the backward pass reads the [token, slot] layout
@@ -433,8 +493,8 @@ class BenchSession:
         # over several peers: measured slower at two ranks, 0.55 ms faster per push at eight
         self.group = IpcGroup(shape, rank, world, dev, train=train, stream=(not train) and world >= STREAM_PUSH_MIN_WORLD)
         self.host = EpMoKHost(shape, rank, self.group)
-        if self.host.stream_push:
-            self.launches_per_step = self.launches_per_step + 1
+        if self.host.stream_push and not self.host.schedule_writes_streams:
+            self.launches_per_step = self.launches_per_step + 1     # the separate stream-position pass
         torch.manual_seed(1234 + rank)
         E, H, I = self.host.num_local_experts, shape.hidden, shape.intermediate
         if train:

@@ -151,10 +151,13 @@ def test_local_group_bf16_precision_equals_the_single_rank_forward(native_lib, w
         group.close()
 
 
-@pytest.mark.parametrize("world,shape_args", [(2, ("ep2s", 8, 512, 256, 2, 256)), (4, ("ep4s", 16, 256, 256, 4, 384))])
+@pytest.mark.parametrize("world,shape_args", [(2, ("ep2s", 8, 512, 256, 2, 256)), (4, ("ep4s", 16, 256, 256, 4, 384)),
+                                              (2, ("ep2f", 8, 512, 256, 2, 512)), (4, ("ep4f", 16, 256, 256, 4, 512))])
 def test_local_group_receive_streams_equal_the_slot_layout(native_lib, world, shape_args):
     """The combine push into per-source receive streams plus the indexed epilogue gives the same
-    output, bit for bit, as the push into [token * topk + slot]; every stream position is used once."""
+    output, bit for bit, as the push into [token * topk + slot]; every stream position is used once.
+    Where tokens * topk is a multiple of 1024 the schedule launches write the stream positions
+    themselves (the last two cases): they must be the positions the separate pass computes."""
     from pipelink_b200 import ep, mok
     shape = mok.Shape(*shape_args)
     wg, wu, wd, inputs = make_group_case(mok, shape, world, seed=7)
@@ -180,6 +183,19 @@ def test_local_group_receive_streams_equal_the_slot_layout(native_lib, world, sh
                     idx = h.recv_index.cpu().numpy()
                     assert (idx >= 0).all() and (idx < world * Lk).all()       # every (token, slot) was indexed
                     assert len(np.unique(idx)) == Lk
+                assert hosts[0].schedule_writes_streams == (Lk % 1024 == 0)
+                if hosts[0].schedule_writes_streams:
+                    folded = [(h.stream_row.clone(), h.recv_index.clone()) for h in hosts]
+                    for h in hosts:
+                        h.stream_row.fill_(-9)
+                        h.recv_index.fill_(-9)
+                    for h in hosts:
+                        h.stream_rows()                 # the separate pass, on the same schedule
+                    torch.cuda.synchronize()
+                    for h, (rows, index) in zip(hosts, folded):
+                        total = int(h.schedule.num_tokens.item())
+                        assert torch.equal(rows[:total], h.stream_row[:total])
+                        assert torch.equal(index, h.recv_index)
         finally:
             torch.cuda.synchronize()
             group.close()
