@@ -459,12 +459,16 @@ def run_native(args):
         session = ep.BenchSession(shape, dev, rank, world)
 
     flop_per_rank = 6.0 * shape.tokens * shape.topk * shape.hidden * shape.intermediate
+    dispatch_choice = session.choose_dispatch() if world > 1 else None
     parity = None
     if world > 1 and not args.no_parity:
         parity = {"ep_forward": ep_forward_parity(session, dev, rank, world)}
         if not parity["ep_forward"]["ok"]:
             raise RuntimeError(f"expert-parallel forward differs from the single-rank pass: {parity}")
     launches_per_step = session.launches_per_step
+    session_streams = world > 1 and session.host.stream_push
+    if world > 1 and session.host.fused_dispatch:
+        launches_per_step -= 1           # no pull kernel: the gate/up GEMM fetches its own rows
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -589,7 +593,8 @@ def run_native(args):
                 "config": {"workload": shape.name, "tokens_per_rank": shape.tokens, "hidden": shape.hidden,
                            "experts": shape.experts, "topk": shape.topk, "intermediate": shape.intermediate,
                            "l2": "inputs larger than L2 (weights 1.5 GB, activations > 1 GB per step)",
-                           "expert_padding": mok.expert_padding(), "gemm_tile": "cta-pair 256x256"},
+                           "expert_padding": mok.expert_padding(), "gemm_tile": "cta-pair 256x256",
+                           **({"dispatch": dispatch_choice, "receive_streams": bool(session_streams)} if world > 1 else {})},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
                 "roofline": roof, "cpu_baseline": cpu, "decode": decode, "attention": attention, "ep_fwd_bwd": train,
                 "tp_gemm": tp_gemm, "parity": parity, "fp8_tflops_measured": fp8,

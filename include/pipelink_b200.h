@@ -266,6 +266,11 @@ int plb_ep_bwd_dy(const void* const* d_out_peers, const float* const* router_w_p
                   int hidden, void* d_y_bf16, void* stream);
 int plb_moe_router_grad(const void* d_out_bf16, const void* combine_bf16, int64_t tokens, int topk, int hidden,
                         float* d_router_weights, void* stream);
+/* plb_moe_router_grad for a forward pass whose combine rows were pushed into receive streams:
+ * slot t * topk + j is read from rows_bf16[row_index[t * topk + j]] (the receive buffer and the
+ * index plb_moe_schedule_streams / plb_ep_stream_rows wrote). Same arithmetic, same result. */
+int plb_moe_router_grad_indexed(const void* d_out_bf16, const void* rows_bf16, const int32_t* row_index, int64_t tokens,
+                                int topk, int hidden, float* d_router_weights, void* stream);
 int plb_ep_gather_rows(const void* const* src_peers, const int32_t* peer_rank, const int32_t* peer_token_idx,
                        const int32_t* num_tokens, int64_t capacity, int cols, void* dst_bf16, void* stream);
 

@@ -91,6 +91,7 @@ PROTOTYPES = {
     "plb_moe_gemm_wgrad": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "plb_ep_bwd_dy": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "plb_moe_router_grad": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "plb_moe_router_grad_indexed": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "plb_ep_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "plb_attention_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                   c_int, ctypes.c_uint64, ctypes.c_uint64, c_float, c_int, c_float, c_void_p, ctypes.c_uint32,

@@ -166,14 +166,15 @@ ep_bwd_dy_kernel(const uint4* const* __restrict__ d_out_peers, const float* cons
 // d_router_w[t * topk + j] = <d_out[t], combine[t * topk + j]>: one warp per (token, slot), the
 // same lane partition, fma order and shuffle tree as bwd_dy_kernel, so both give the same bits.
 __global__ void __launch_bounds__(256)
-router_grad_kernel(const uint4* __restrict__ d_out, const uint4* __restrict__ y, int64_t tokens, int topk, int hidden,
-                   float* __restrict__ d_router_w) {
+router_grad_kernel(const uint4* __restrict__ d_out, const uint4* __restrict__ y, const int* __restrict__ row_index,
+                   int64_t tokens, int topk, int hidden, float* __restrict__ d_router_w) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int vecs = hidden >> 3;
   for (int64_t d = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; d < tokens * topk; d += warps) {
     const uint4* src = d_out + (d / topk) * vecs;
-    const uint4* yr = y + d * vecs;
+    // row_index: where the (token, slot) row sits when the combine rows were pushed into receive streams
+    const uint4* yr = y + (row_index != nullptr ? static_cast<int64_t>(row_index[d]) : d) * vecs;
     float dot = 0.0f;
     for (int v = lane; v < vecs; v += 32) {
       const uint4 g = src[v], yy = yr[v];
@@ -276,10 +277,10 @@ cudaError_t launch_ep_bwd_dy(const void* const* d_out_peers, const float* const*
 }
 
 cudaError_t launch_router_grad(const void* d_out, const void* combine, int64_t tokens, int topk, int hidden,
-                               float* d_router_w, cudaStream_t stream) {
+                               float* d_router_w, cudaStream_t stream, const int* row_index) {
   if (tokens == 0) return cudaSuccess;
   router_grad_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const uint4*>(d_out), static_cast<const uint4*>(combine),
-                                                     tokens, topk, hidden, d_router_w);
+                                                     row_index, tokens, topk, hidden, d_router_w);
   return cudaGetLastError();
 }
 

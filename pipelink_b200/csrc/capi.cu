@@ -665,6 +665,15 @@ int plb_moe_router_grad(const void* d_out_bf16, const void* combine_bf16, int64_
                                            static_cast<cudaStream_t>(stream)));
 }
 
+int plb_moe_router_grad_indexed(const void* d_out_bf16, const void* rows_bf16, const int32_t* row_index, int64_t tokens,
+                                int topk, int hidden, float* d_router_weights, void* stream) {
+  if (!d_out_bf16 || !rows_bf16 || !row_index || !d_router_weights || tokens < 0 || topk < 1 || hidden <= 0 ||
+      hidden % 8)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_router_grad(d_out_bf16, rows_bf16, tokens, topk, hidden, d_router_weights,
+                                           static_cast<cudaStream_t>(stream), row_index));
+}
+
 int plb_ep_gather_rows(const void* const* src_peers, const int32_t* peer_rank, const int32_t* peer_token_idx,
                        const int32_t* num_tokens, int64_t capacity, int cols, void* dst_bf16, void* stream) {
   if (!src_peers || !peer_rank || !peer_token_idx || !num_tokens || !dst_bf16 || capacity < 0 || cols <= 0 || cols % 8)

@@ -24,8 +24,8 @@
 //
 // Mode 0: weight rows per 256-row tile are [128 gate | 128 up] of the same hidden
 // indices; out = MXFP8(bf16(silu(bf16 gate) * bf16 up)).
-// Mode 1: bf16 rows to out_base[dest_row], staged through shared memory so every
-// store instruction writes two 256-byte row segments (NVLink-friendly for the push).
+// Mode 1: bf16 rows to out_base[dest_row], staged through shared memory (eight rows at a time) so
+// every store instruction writes two 256-byte row segments (NVLink-friendly for the push).
 #include "kernels.h"
 #include "mxfp8.cuh"
 #include <cstring>
@@ -42,13 +42,14 @@ constexpr uint32_t kStageTx = 2 * kTileBytes + kSfStageBytes;  // per CTA per st
 constexpr int kOffA = 0;
 constexpr int kOffB = kStages * kTileBytes;
 constexpr int kOffSf = 2 * kStages * kTileBytes;
-constexpr int kOffStaging = kOffSf + kStages * kSfStageBytes;  // 8 warps x 4 KB
-constexpr int kStagingBytes = 8 * 4096;
+constexpr int kOffStaging = kOffSf + kStages * kSfStageBytes;  // 8 warps x 2 KB
+constexpr int kStagingBytes = 8 * 2048;
 constexpr int kOffBars = kOffStaging + kStagingBytes;
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes2 = kOffBars + kBarrierBytes + 1024;
 static_assert(kOffSf % 1024 == 0 && kOffStaging % 16 == 0, "shared memory layout");
-static_assert(kStagingBytes / 2 >= 4 * 4096, "dispatch ring: four rows of up to 4096 bytes per dispatch warp");
+static_assert(kStagingBytes / 2 >= 2 * 4096, "dispatch ring: two rows of up to 4096 bytes per dispatch warp");
+static_assert(kSmemBytes2 <= 232448, "shared memory of one CTA");
 constexpr int kThreads2 = 384;
 // Register hand-over between the roles. ptxas gives every thread 168 registers (launch bounds of 384
 // threads, one CTA per SM), the CTA's pool is what it was launched with, and setmaxnreg.inc blocks
@@ -96,7 +97,7 @@ struct Params2 {
   const unsigned* ready;    // mode 1: per 256-row tile of A, a counter that reaches ready_target once the
   unsigned ready_target;    //         tile's rows have all arrived (all-gather -> GEMM); null = rows are local
   // mode 0, optional in-kernel dispatch (null pull_xq = A is already in place): warps 2 and 3 of every
-  // CTA take tickets of four rows, copy each row's E4M3 bytes (peer -> shared -> A) and scale words
+  // CTA take tickets of two rows, copy each row's E4M3 bytes (peer -> shared -> A) and scale words
   // (through registers), and count the ticket into its 256-row tile; the load lane acquires a tile's count
   // before the tile's first TMA read (campaigns/mok/port/comm/comm.cu:105-123 gives the
   // reference's megakernel the same dispatch role)
@@ -474,15 +475,15 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     } else if (MODE == 0 && warp >= 2 && p.pull_xq != nullptr) {
       // ---------------------------------------------------------- dispatch warps (two per CTA)
-      // A ticket is four consecutive rows. Their bytes cross as 16-byte asynchronous copies
-      // peer -> shared memory (no registers held while the loads are in flight, so all four rows,
-      // up to 16 KB per warp, travel at once; the ring is the staging area of the row-store
+      // A ticket is two consecutive rows. Their bytes cross as 16-byte asynchronous copies
+      // peer -> shared memory (no registers held while the loads are in flight, so both rows,
+      // up to 8 KB per warp, travel at once; the ring is the staging area of the row-store
       // epilogue, which this mode does not use), then shared -> A with plain stores, and the ticket
       // is counted into its row tile after a fence. Any resident CTA can serve any ticket, and the
       // dispatch warps wait for nothing, so the tiles the load lanes wait for always complete.
       // (Bulk copies here cost the mainloop as much as the separate pull kernel they replaced: the
       // TMA unit is what feeds the tensor pipe. The load/store path is idle in this kernel.)
-      constexpr int kTicketRows = 4;
+      constexpr int kTicketRows = 2;
       const uint32_t ring = smem_base + kOffStaging + static_cast<uint32_t>(warp - 2) * (kStagingBytes / 2);
       const int vecs = p.pull_row_bytes >> 4;                  // <= 256
       const int col_blocks = p.pull_row_bytes >> 7;
@@ -546,7 +547,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
     const int ch = (warp - 4) >> 2;       // which half of the accumulator columns
     const uint32_t acc_empty_leader = mapa_shared(smem_u32(&bars->acc_empty), 0);
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-    const uint32_t stage_base = smem_base + kOffStaging + (warp - 4) * 4096;
+    const uint32_t stage_base = smem_base + kOffStaging + (warp - 4) * 2048;
     uint32_t acc_phase = 0;
     bool ok = true;
     PROF_DECL(t_wait);
@@ -663,13 +664,16 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         const int dest = MODE == 2 ? static_cast<int>(row) : p.dest_row[row];
         const int pr = (p.out_peers != nullptr && dest >= 0) ? p.peer_rank[row] : 0;
         const size_t col_byte = (static_cast<size_t>(n_tile) * 256 + ch * 128) * 2;
+        // four passes of eight rows through 2 KB of staging per warp: eight lanes park their rows
+        // (chunks rotated by the row number, so neither side has bank conflicts), then every store
+        // instruction of the warp writes two 256-byte row segments
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if ((lane >> 4) == h) {
-            const uint32_t r16 = lane & 15;
+        for (int h = 0; h < 4; ++h) {
+          if ((lane >> 3) == h) {
+            const uint32_t r8 = lane & 7;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const uint32_t addr = stage_base + r16 * 256 + ((static_cast<uint32_t>(j) ^ r16) << 4);
+              const uint32_t addr = stage_base + r8 * 256 + ((static_cast<uint32_t>(j) ^ r8) << 4);
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]),
                            "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
                            : "memory");
@@ -677,10 +681,10 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 4; ++i) {
             const uint32_t rr = i * 2 + (lane >> 4);
             const uint32_t c = lane & 15;
-            const int src_lane = h * 16 + static_cast<int>(rr);
+            const int src_lane = h * 8 + static_cast<int>(rr);
             const int d = __shfl_sync(0xFFFFFFFFu, dest, src_lane);
             const int prr = __shfl_sync(0xFFFFFFFFu, pr, src_lane);
             uint4 val;

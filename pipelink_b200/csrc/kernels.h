@@ -140,7 +140,7 @@ cudaError_t launch_ep_bwd_dy(const void* const* d_out_peers, const float* const*
                              const int* peer_token_idx, const int* dest_row, const int* num_rows_dev, int64_t capacity,
                              int hidden, void* dy, cudaStream_t stream);
 cudaError_t launch_router_grad(const void* d_out, const void* combine, int64_t tokens, int topk, int hidden,
-                               float* d_router_w, cudaStream_t stream);
+                               float* d_router_w, cudaStream_t stream, const int* row_index = nullptr);
 cudaError_t launch_ep_gather_rows(const void* const* src_peers, const int* peer_rank, const int* peer_token_idx,
                                   const int* num_rows_dev, int64_t capacity, int cols, void* dst, cudaStream_t stream);
 cudaError_t launch_gather_rows(const void* src, const int* peer_rank, const int* peer_token_idx,

@@ -50,6 +50,9 @@ class SlabLayout:
             self.d_out = off; off += _align(L * H * 2)         # upstream gradient
             self.router_w = off; off += _align(L * k * 4)      # router weights (d_y = w * d_out)
             self.d_x_rows = off; off += _align(L * k * H * 2)  # input-gradient rows, one per (token, slot)
+            if stream:  # receive streams of the input-gradient push (the forward's hold the combine rows
+                        # until the router gradient has read them, so the two cannot share a buffer)
+                self.d_x_recv = off; off += _align(world * L * k * H * 2)
         self.nbytes = off
 
 
@@ -184,8 +187,8 @@ class EpMoKHost(mok.MoKHost):
         self.xsc_rows_peers = table(lay.xsc_rows)
         self.xsc_rows = tensor_from_ptr(ptrs[rank] + lay.xsc_rows, (L, H // 128), torch.int32, dev)
         self.pull_variant = "bulk"
-        # combine push into receive streams (sequential writes at the home rank) instead of into
-        # [token * topk + slot]; forward passes without a saved context only
+        # combine push (and, in training, the input-gradient push) into receive streams: sequential
+        # writes at the home rank instead of rows scattered to [token * topk + slot]
         self.stream_push = bool(lay.stream)
         if self.stream_push:
             self.recv_peers, self.recv_index_peers = table(lay.recv), table(lay.recv_index)
@@ -221,6 +224,9 @@ class EpMoKHost(mok.MoKHost):
             self.router_weight_buffer = tensor_from_ptr(me + lay.router_w, (L, k), torch.float32, dev)
             self.d_out_buffer = tensor_from_ptr(me + lay.d_out, (L, H), torch.bfloat16, dev)
             self._d_x_rows = tensor_from_ptr(me + lay.d_x_rows, (L * k, H), torch.bfloat16, dev)
+            if lay.stream:
+                self.d_x_recv_peers = table(lay.d_x_recv)
+                self.d_x_recv = tensor_from_ptr(me + lay.d_x_recv, (W * L * k, H), torch.bfloat16, dev)
 
     def _alloc_train_buffers(self):
         super()._alloc_train_buffers()
@@ -277,7 +283,7 @@ class EpMoKHost(mok.MoKHost):
 
     def gemm_down_push(self, train: bool = False):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
-        self._streamed = self.stream_push and not train and self.precision != "bf16"
+        self._streamed = self.stream_push and self.precision != "bf16"
         if self._streamed:
             if not self.schedule_writes_streams:
                 self.stream_rows()
@@ -382,11 +388,12 @@ class EpMoKHost(mok.MoKHost):
         [tokens * topk, H] buffer."""
         s, w, sh = self.schedule, self.weights, self.shape
         dgu_q, dgu_sc, _, _ = self._dgu
+        # with receive streams the rows take the positions the forward's combine rows took (same schedule)
+        dest, peers = (self.stream_row, self.d_x_recv_peers) if self._streamed else (s.dest_row, self.d_x_rows_peers)
         _lib.call("plb_moe_gemm_down_push", dgu_q.data_ptr(), dgu_sc.data_ptr(), w["w_cat_t_fp8"].data_ptr(),
-                  w["w_cat_t_sc"].data_ptr(), s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(),
+                  w["w_cat_t_sc"].data_ptr(), s.block_expert.data_ptr(), s.num_tokens.data_ptr(), dest.data_ptr(),
                   s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, 2 * sh.intermediate, sh.hidden,
-                  self.push_rotation, self.push_stride, self.d_x_rows_peers.data_ptr(), self.status.buf.data_ptr(),
-                  mok._stream())
+                  self.push_rotation, self.push_stride, peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
 
     def bwd_gate_up_wgrad(self):
         """Gate/up weight gradient: the bf16 token rows pulled from their home ranks, quantised along the rows."""
@@ -411,12 +418,21 @@ class EpMoKHost(mok.MoKHost):
     def bwd_home_side_early(self):
         """Needs only this rank's own tokens: the router-weight gradient."""
         b, sh = self.buffers, self.shape
+        if self._streamed:
+            _lib.call("plb_moe_router_grad_indexed", self.d_out_buffer.data_ptr(), self.recv.data_ptr(),
+                      self.recv_index.data_ptr(), sh.tokens, sh.topk, sh.hidden, b["d_router_weights"].data_ptr(),
+                      mok._stream())
+            return
         _lib.call("plb_moe_router_grad", self.d_out_buffer.data_ptr(), b["combine_buffer"].data_ptr(), sh.tokens, sh.topk,
                   sh.hidden, b["d_router_weights"].data_ptr(), mok._stream())
 
     def bwd_home_side_late(self):
         """After every rank's input-gradient rows have landed: sum the slots of each token."""
         b, sh = self.buffers, self.shape
+        if self._streamed:
+            _lib.call("plb_moe_fwd_epilogue_indexed", None, self.d_x_recv.data_ptr(), self.recv_index.data_ptr(),
+                      self._ones.data_ptr(), sh.tokens, sh.topk, sh.hidden, b["d_x"].data_ptr(), mok._stream())
+            return
         _lib.call("plb_moe_fwd_epilogue", None, b["d_x_routed_buffer"].data_ptr(), self._ones.data_ptr(), sh.tokens,
                   sh.topk, sh.hidden, b["d_x"].data_ptr(), mok._stream())
 
@@ -485,13 +501,13 @@ class BenchSession:
     launches_per_step = 12  # quantise, scale rows, publish, barrier x2, schedule x3, pull, 2 GEMMs, epilogue
     # backward adds: barrier x2, router grad, d_y pull, 5 quantise, 2 dgrad GEMMs, SwiGLU backward, x gather,
     # 2 wgrad GEMMs, slot sum, 2 tail-zeroing launches
-    launches_per_step_train = 12 + 18    # no stream rows: the backward pass reads the [token, slot] layout
+    launches_per_step_train = 12 + 18
 
     def __init__(self, shape: mok.Shape, dev, rank: int, world: int, train: bool = False):
         self.shape, self.dev, self.train = shape, dev, train
-        # receive streams pay for their row-position pass (about 0.1 ms) once the combine rows scatter
-        # over several peers: measured slower at two ranks, 0.55 ms faster per push at eight
-        self.group = IpcGroup(shape, rank, world, dev, train=train, stream=(not train) and world >= STREAM_PUSH_MIN_WORLD)
+        # receive streams pay once the combine rows scatter over several peers: no gain at two ranks,
+        # 0.55 ms faster per push at eight
+        self.group = IpcGroup(shape, rank, world, dev, train=train, stream=world >= STREAM_PUSH_MIN_WORLD)
         self.host = EpMoKHost(shape, rank, self.group)
         if self.host.stream_push and not self.host.schedule_writes_streams:
             self.launches_per_step = self.launches_per_step + 1     # the separate stream-position pass
@@ -553,6 +569,37 @@ class BenchSession:
 
     def check(self):
         self.host.status.check("bench (EP)")
+
+    def choose_dispatch(self, steps: int = 6):
+        """Decide where the dispatch runs by timing it: `steps` steps with the pull kernel in front of
+        the gate/up GEMM and `steps` with the dispatch warps inside it, device time, slowest rank;
+        the faster stays on. Whether rows arriving under the mainloop beat rows fetched before it
+        depends on how many of them are remote, so it is measured on the group at hand. Returns both
+        times in ms per step. Forward sessions of the MXFP8 precision only."""
+        import torch.distributed as dist
+        h = self.host
+        if self.train or h.precision != "mxfp8" or h.shape.hidden > 4096:
+            return None
+        times = {}
+        for name, fused in (("pull kernel", False), ("in-kernel", True)):
+            h.fused_dispatch = fused
+            for _ in range(2):
+                self.step()
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                self.step()
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device=self.dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times[name] = float(t.item())
+        h.status.check("bench (EP, dispatch choice)")
+        h.fused_dispatch = times["in-kernel"] < times["pull kernel"]
+        return {"ms_per_step": times, "chosen": "in-kernel" if h.fused_dispatch else "pull kernel"}
 
     def traffic_per_launch(self):
         return None

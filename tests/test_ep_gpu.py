@@ -71,8 +71,10 @@ def test_local_group_forward_vs_oracle(native_lib, world, shape_args):
         group.close()
 
 
-@pytest.mark.parametrize("world,shape_args", [(2, ("ep2b", 8, 512, 256, 2, 256)), (4, ("ep4b", 8, 256, 256, 4, 128))])
-def test_local_group_backward_equals_the_single_rank_backward(native_lib, world, shape_args):
+@pytest.mark.parametrize("stream", [False, True], ids=["slots", "streams"])
+@pytest.mark.parametrize("world,shape_args", [(2, ("ep2b", 8, 512, 256, 2, 256)), (4, ("ep4b", 8, 256, 256, 4, 128)),
+                                              (4, ("ep4c", 8, 256, 256, 4, 256))])
+def test_local_group_backward_equals_the_single_rank_backward(native_lib, world, shape_args, stream):
     """Forward + backward over a group must give, bit for bit, what one rank holding every token and
     every expert computes: an expert's rows arrive in the same order on the rank that owns it, so
     every quantisation block, GEMM and reduction sees the same operands. (The single-rank backward
@@ -90,13 +92,16 @@ def test_local_group_backward_equals_the_single_rank_backward(native_lib, world,
     joined = mok.Inputs(torch.cat([i.x for i in inputs]), torch.cat([i.experts for i in inputs]), torch.cat([i.router for i in inputs]))
     out_single = single.forward(joined, train=True)["output"].clone()
     want = {k: v.clone() for k, v in single.backward(torch.cat(d_outs)).items()}
-    group = ep.LocalGroup(shape, world, "cuda", train=True)
+    group = ep.LocalGroup(shape, world, "cuda", train=True, stream=stream)
     try:
         hosts = [ep.EpMoKHost(shape, r, group) for r in range(world)]
         El, L = shape.experts // world, shape.tokens
         for r, h in enumerate(hosts):
             h.load_weights(wg[r * El:(r + 1) * El], wu[r * El:(r + 1) * El], wd[r * El:(r + 1) * El], train=True)
             h.buffers["d_x_routed_buffer"].fill_(float("nan"))      # every (token, slot) row must be pushed by some rank
+            if stream:      # rows travel through the receive streams instead: the index must reach every one
+                h.d_x_recv.fill_(float("nan"))
+                h.recv.fill_(float("nan"))
         outs = ep.forward_local_group(hosts, inputs, train=True)
         grads = ep.backward_local_group(hosts, d_outs)
         torch.cuda.synchronize()
