@@ -568,7 +568,7 @@ def run_native(args):
         del session
         torch.cuda.empty_cache()
         session = None
-        train = ep_train_leg(shape, dev, rank, world, pk)
+        train = ep_train_leg(shape, dev, rank, world, pk, fused_dispatch=bool(dispatch_choice and dispatch_choice["chosen"] == "in-kernel"))
 
     tp_gemm = None
     if world > 1 and not args.no_tp and args.tokens is None:
@@ -605,14 +605,14 @@ def run_native(args):
         dist.destroy_process_group()
 
 
-def ep_train_leg(shape, dev, rank, world, pk, steps=5):
+def ep_train_leg(shape, dev, rank, world, pk, steps=5, fused_dispatch=False):
     """Expert-parallel forward + backward at the same per-rank shape (the fwd+bwd case of the
     expert-parallel configuration): 18 T k H I FLOP per rank and step (forward 6, both data
     gradients 6, both weight gradients 6), device time, max over ranks."""
     import torch
     import torch.distributed as dist
     from pipelink_b200 import ep
-    session = ep.BenchSession(shape, dev, rank, world, train=True)
+    session = ep.BenchSession(shape, dev, rank, world, train=True, fused_dispatch=fused_dispatch)
     for _ in range(3):
         session.step()
     session.check()
@@ -634,7 +634,8 @@ def ep_train_leg(shape, dev, rank, world, pk, steps=5):
     payload = shape.tokens * shape.topk * shape.hidden * (world - 1) / world
     out = {"metric": "mxfp8_moe_ffn_fwd_bwd_tflops", "value": flop * world / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms,
            "steps": steps, "tokens_per_rank": shape.tokens, "world": world, "scaling": "weak",
-           "gpu_launches": session.launches_per_step * steps,
+           "gpu_launches": (session.launches_per_step - int(fused_dispatch)) * steps,
+           "dispatch": "in-kernel" if fused_dispatch else "pull kernel", "receive_streams": bool(session.host.stream_push),
            "frac_of_2x_bf16_sustained": flop / (ms * 1e-3) / 1e12 / (2.0 * pk["bf16_sustained"]),
            "frac_of_nominal_4500": flop / (ms * 1e-3) / 1e12 / 4500.0,
            "nvlink_payload_bytes_per_rank": {"dispatch_e4m3": payload * (1 + 1 / 32), "combine_bf16": payload * 2,

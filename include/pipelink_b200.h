@@ -187,6 +187,16 @@ int plb_moe_gemm_gate_up_train(const void* x_routed_fp8, const void* x_routed_sc
                                int64_t capacity, int experts, int inter, int hidden, void* hidden_fp8,
                                void* hidden_sc, void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc,
                                void* hidden_bf16, plb_status* status, void* stream);
+/* plb_moe_gemm_gate_up_train with the dispatch inside the kernel, as plb_moe_gemm_gate_up_dispatch
+ * does it for the inference forward: x_routed_* are filled by the kernel's dispatch warps while the
+ * tensor pipe works on the row tiles already complete. scratch_u32: capacity / 256 + 1 words. */
+int plb_moe_gemm_gate_up_train_dispatch(const void* const* xq_peers, const void* const* xsc_rows_peers,
+                                        const int32_t* peer_rank, const int32_t* peer_token_idx, void* x_routed_fp8,
+                                        void* x_routed_sc, const void* w13_fp8, const void* w13_sc,
+                                        const int32_t* block_expert, const int32_t* num_tokens, int64_t capacity,
+                                        int experts, int inter, int hidden, void* hidden_fp8, void* hidden_sc,
+                                        void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc, void* hidden_bf16,
+                                        void* scratch_u32, plb_status* status, void* stream);
 int plb_moe_bwd_dy(const void* d_out_bf16, const void* combine_bf16, const float* router_weights,
                    const int32_t* peer_rank, const int32_t* peer_token_idx, const int32_t* dest_row,
                    const int32_t* num_tokens, int64_t capacity, int hidden, int topk, void* d_y_bf16,

@@ -85,6 +85,7 @@ PROTOTYPES = {
     "plb_decode_attention_partial": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                              c_float, c_void_p]),
     "plb_moe_gemm_gate_up_train": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_int] + [c_void_p] * 9),
+    "plb_moe_gemm_gate_up_train_dispatch": (c_int, [c_void_p] * 10 + [c_int64, c_int, c_int, c_int] + [c_void_p] * 10),
     "plb_moe_bwd_dy": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "plb_moe_swiglu_bwd": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_void_p, c_void_p]),
     "plb_moe_gather_rows": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_void_p, c_void_p]),

@@ -575,11 +575,12 @@ int plb_decode_attention_partial(const void* q, const void* k, const void* v, fl
                                                  static_cast<cudaStream_t>(stream)));
 }
 
-int plb_moe_gemm_gate_up_train(const void* x_routed_fp8, const void* x_routed_sc, const void* w13_fp8,
-                               const void* w13_sc, const int32_t* block_expert, const int32_t* num_tokens,
-                               int64_t capacity, int experts, int inter, int hidden, void* hidden_fp8,
-                               void* hidden_sc, void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc,
-                               void* hidden_bf16, plb_status* status, void* stream) {
+static int gate_up_train_impl(const void* const* xq_peers, const void* const* xsc_rows_peers, const int32_t* peer_rank,
+                              const int32_t* peer_token_idx, void* scratch_u32, const void* x_routed_fp8,
+                              const void* x_routed_sc, const void* w13_fp8, const void* w13_sc,
+                              const int32_t* block_expert, const int32_t* num_tokens, int64_t capacity, int experts,
+                              int inter, int hidden, void* hidden_fp8, void* hidden_sc, void* gate_fp8, void* gate_sc,
+                              void* up_fp8, void* up_sc, void* hidden_bf16, plb_status* status, void* stream) {
   if (capacity < 0 || capacity % 256 || experts < 1 || inter < 256 || inter % 256 || hidden < 256 || hidden % 256)
     return PLB_E_ARGUMENT;
   if (!x_routed_fp8 || !x_routed_sc || !w13_fp8 || !w13_sc || !block_expert || !num_tokens || !hidden_fp8 ||
@@ -592,10 +593,38 @@ int plb_moe_gemm_gate_up_train(const void* x_routed_fp8, const void* x_routed_sc
   a.out = hidden_fp8; a.out_sc = hidden_sc; a.dest_row = nullptr;
   a.save_gate = gate_fp8; a.save_gate_sc = gate_sc; a.save_up = up_fp8; a.save_up_sc = up_sc;
   a.save_hidden = hidden_bf16;
+  if (xq_peers != nullptr) {
+    if (!xsc_rows_peers || !peer_rank || !peer_token_idx || !scratch_u32 || hidden > 4096) return PLB_E_ARGUMENT;
+    a.pull_xq = xq_peers; a.pull_sc_rows = xsc_rows_peers; a.pull_peer_rank = peer_rank;
+    a.pull_token_idx = peer_token_idx; a.pull_scratch = scratch_u32;
+  }
   a.num_sms = sm_count();
   a.status = reinterpret_cast<plb::Status*>(status);
   if (a.num_sms <= 0) return PLB_E_CUDA;
   return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_gemm_gate_up_train(const void* x_routed_fp8, const void* x_routed_sc, const void* w13_fp8,
+                               const void* w13_sc, const int32_t* block_expert, const int32_t* num_tokens,
+                               int64_t capacity, int experts, int inter, int hidden, void* hidden_fp8,
+                               void* hidden_sc, void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc,
+                               void* hidden_bf16, plb_status* status, void* stream) {
+  return gate_up_train_impl(nullptr, nullptr, nullptr, nullptr, nullptr, x_routed_fp8, x_routed_sc, w13_fp8, w13_sc,
+                            block_expert, num_tokens, capacity, experts, inter, hidden, hidden_fp8, hidden_sc, gate_fp8,
+                            gate_sc, up_fp8, up_sc, hidden_bf16, status, stream);
+}
+
+int plb_moe_gemm_gate_up_train_dispatch(const void* const* xq_peers, const void* const* xsc_rows_peers,
+                                        const int32_t* peer_rank, const int32_t* peer_token_idx, void* x_routed_fp8,
+                                        void* x_routed_sc, const void* w13_fp8, const void* w13_sc,
+                                        const int32_t* block_expert, const int32_t* num_tokens, int64_t capacity,
+                                        int experts, int inter, int hidden, void* hidden_fp8, void* hidden_sc,
+                                        void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc, void* hidden_bf16,
+                                        void* scratch_u32, plb_status* status, void* stream) {
+  if (!xq_peers) return PLB_E_ARGUMENT;
+  return gate_up_train_impl(xq_peers, xsc_rows_peers, peer_rank, peer_token_idx, scratch_u32, x_routed_fp8, x_routed_sc,
+                            w13_fp8, w13_sc, block_expert, num_tokens, capacity, experts, inter, hidden, hidden_fp8,
+                            hidden_sc, gate_fp8, gate_sc, up_fp8, up_sc, hidden_bf16, status, stream);
 }
 
 int plb_moe_gemm_wgrad(const void* a_t_fp8, const void* a_t_sc, const void* b_t_fp8, const void* b_t_sc,

@@ -503,12 +503,13 @@ class BenchSession:
     # 2 wgrad GEMMs, slot sum, 2 tail-zeroing launches
     launches_per_step_train = 12 + 18
 
-    def __init__(self, shape: mok.Shape, dev, rank: int, world: int, train: bool = False):
+    def __init__(self, shape: mok.Shape, dev, rank: int, world: int, train: bool = False, fused_dispatch: bool = False):
         self.shape, self.dev, self.train = shape, dev, train
         # receive streams pay once the combine rows scatter over several peers: no gain at two ranks,
         # 0.55 ms faster per push at eight
         self.group = IpcGroup(shape, rank, world, dev, train=train, stream=world >= STREAM_PUSH_MIN_WORLD)
         self.host = EpMoKHost(shape, rank, self.group)
+        self.host.fused_dispatch = fused_dispatch
         if self.host.stream_push and not self.host.schedule_writes_streams:
             self.launches_per_step = self.launches_per_step + 1     # the separate stream-position pass
         torch.manual_seed(1234 + rank)

@@ -361,7 +361,15 @@ class MoKHost:
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
         self.select_activation()
         if self.fused_dispatch:
-            self.pull_now()             # the saving epilogue has no fused dispatch: pull in front of it
+            _lib.call("plb_moe_gemm_gate_up_train_dispatch", self.xq_peers.data_ptr(), self.xsc_rows_peers.data_ptr(),
+                      s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), b["x_routed_fp8"].data_ptr(),
+                      b["x_routed_sc"].data_ptr(), w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(),
+                      s.block_expert.data_ptr(), s.num_tokens.data_ptr(), self.capacity, self.num_local_experts,
+                      sh.intermediate, sh.hidden, b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(),
+                      b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(), b["up_routed_fp8"].data_ptr(),
+                      b["up_routed_sc"].data_ptr(), b["hidden_routed_bf16"].data_ptr(), self.dispatch_scratch.data_ptr(),
+                      self.status.buf.data_ptr(), _stream())
+            return
         _lib.call("plb_moe_gemm_gate_up_train", b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
                   w["w13_fp8"].data_ptr(), w["w13_sc"].data_ptr(), s.block_expert.data_ptr(), s.num_tokens.data_ptr(),
                   self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,

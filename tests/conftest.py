@@ -33,3 +33,4 @@ def native_lib():
     if not _lib.LIB_PATH.exists():
         build.build_all()
     return _lib.load()
+

@@ -121,19 +121,13 @@ def test_context_parallel_matches_single_gpu(native_lib, world, S):
             _lib.call("plb_sym_free", p)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_context_parallel_two_gpus():
-    import os
-    import subprocess
-    import sys
-    from pathlib import Path
-    root = Path(__file__).resolve().parent.parent
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", "29547", str(root / "tests" / "cp_child.py")]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    assert "CP CHILD OK" in out.stdout
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_context_parallel_real_gpus(world):
+    from tests.ranks import gpu_count, run_ranks
+    if gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    run_ranks("cp_child.py", world, 29561 + world, "CP CHILD OK")
+
 
 
 def test_attention_seq32768_boundary_rows(native_lib):

@@ -467,6 +467,19 @@ def test_fused_dispatch_equals_pull_then_gemm(native_lib, shape_args, generation
         for name in ("x_routed_scale", "hidden_routed_scale"):
             assert torch.equal(got[name][: total // 128], want[name][: total // 128]), (step, name)
         assert torch.equal(got["output"].view(torch.int16), want["output"].view(torch.int16)), step
+    # the training forward (gate, up and hidden kept for the backward pass) with the same dispatch
+    for h in (plain, fused):
+        h.load_weights(wg, wu, wd, train=True)
+    inputs = mok.MoKHost.new_inputs(shape, generation, "cuda")
+    fused.buffers["x_routed_fp8"].fill_(77)
+    want, got = plain.forward(inputs, train=True), fused.forward(inputs, train=True)
+    torch.cuda.synchronize()
+    total = int(plain.schedule.num_tokens.item())
+    assert torch.equal(got["output"].view(torch.int16), want["output"].view(torch.int16))
+    for name in ("x_routed_fp8", "gate_routed_fp8", "up_routed_fp8", "hidden_routed_fp8"):
+        assert torch.equal(fused.buffers[name][:total], plain.buffers[name][:total]), name
+    assert torch.equal(fused.buffers["hidden_routed_bf16"][:total].view(torch.int16),
+                       plain.buffers["hidden_routed_bf16"][:total].view(torch.int16))
 
 
 # ------------------------------------------------------------------ the benchmarked size itself

@@ -124,11 +124,9 @@ def test_allgather_gemm_reports_rows_that_never_arrive(native_lib):
         group.close()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_ipc_tp_group_two_gpus():
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-           "--master-addr", "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "tp_child.py")]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    assert "TP CHILD OK" in out.stdout
+@pytest.mark.parametrize("world", [2, 4])
+def test_ipc_tp_group_real_gpus(world):
+    from tests.ranks import gpu_count, run_ranks
+    if gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    run_ranks("tp_child.py", world, 29551 + world, "TP CHILD OK")
