@@ -574,6 +574,10 @@ def run_native(args):
     if world > 1 and not args.no_tp and args.tokens is None:
         tp_gemm = tp_leg(dev, pk, rank, world)
 
+    linked = None
+    if world == 1 and args.tokens is None:
+        linked = linked_leg(session)
+
     decode = None
     if rank == 0 and world == 1 and not args.no_decode and args.tokens is None:
         del session
@@ -597,7 +601,7 @@ def run_native(args):
                            **({"dispatch": dispatch_choice, "receive_streams": bool(session_streams)} if world > 1 else {})},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
                 "roofline": roof, "cpu_baseline": cpu, "decode": decode, "attention": attention, "ep_fwd_bwd": train,
-                "tp_gemm": tp_gemm, "parity": parity, "fp8_tflops_measured": fp8,
+                "tp_gemm": tp_gemm, "linked_moe": linked, "parity": parity, "fp8_tflops_measured": fp8,
                 "frac_of_fp8_peak_whole_step": value / world / fp8_peak,
                 "frac_of_nominal_4500_whole_step": value / world / 4500.0}
         print(json.dumps(line))
@@ -694,6 +698,44 @@ def tp_leg(dev, pk, rank, world, steps=20):
     if published:
         out["reference_published_ms"] = {"ag": published[0], "rs": published[1], "hardware": "H200, 1300 MHz"}
     return out
+
+
+def linked_leg(session, steps=10):
+    """The same two grouped GEMMs launched as LINKED images (the packages of stages/moe joined by the
+    link driver) and as the library's kernels, alternating, on the benchmark's own buffers: device
+    time per launch and the ratio linked / library (the reference's gate for a linked build is 1 % of
+    the single-unit build)."""
+    import torch
+    from pipelink_b200 import moe_linked
+    h = session.host
+    try:
+        linked = moe_linked.LinkedMoE(h)
+    except Exception as exc:  # noqa: BLE001 - images absent: report, do not fail the benchmark
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    session.step()
+    out = {}
+    for name, lib_fn, lnk_fn in (("gate_up", h.gemm_gate_up, linked.gemm_gate_up), ("down", h.gemm_down, linked.gemm_down)):
+        t = {"library": 0.0, "linked": 0.0}
+        for i in range(steps + 2):
+            for which, fn in (("library", lib_fn), ("linked", lnk_fn)):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                h.dispatch()                    # other traffic between the launches, as in a step
+                a.record()
+                fn()
+                b.record()
+                torch.cuda.synchronize()
+                if i >= 2:
+                    t[which] += a.elapsed_time(b) / steps
+        out[name] = {"library_ms": t["library"], "linked_ms": t["linked"], "ratio": t["linked"] / t["library"]}
+    h.status.check("bench (linked images)")
+    linked.close()
+    out["ring_depth"] = {"library": 5, "linked": linked_depth()}
+    return out
+
+
+def linked_depth():
+    from pipelink_b200 import moe_linked
+    return json.loads((moe_linked.OUT_DIR / "gate_up" / "link.json").read_text())["bindings"]["pipelink_moe_depth"][0]
 
 
 def attention_leg(dev, pk, seq=32768, steps=3):

@@ -508,6 +508,10 @@ int plb_image_unload(void* library);
  * box_rows x box_bytes, optional 128-byte swizzle; out128 receives the 128-byte CUtensorMap. */
 int plb_tensor_map_2d_u8(void* out128, const void* base, uint64_t rows, uint64_t row_bytes,
                          uint32_t box_rows, uint32_t box_bytes, int swizzle128);
+/* The same for a row-major [rows, cols] tensor of 32-bit words without swizzle (the scale tensors
+ * seen as one 128-word row per 512-byte scale block). */
+int plb_tensor_map_2d_u32(void* out128, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                          uint32_t box_cols);
 
 #ifdef __cplusplus
 }

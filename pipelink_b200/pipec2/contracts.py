@@ -33,14 +33,114 @@ def canonical_layout(layout: dict | None):
             "swizzle": layout.get("swizzle")}
 
 
-def pair_channels(manifests: list[dict]):
-    """-> {channel: (producer (stage_id, endpoint), consumer (stage_id, endpoint))}"""
+def _by_name(manifests):
     by_name = {}
     for m in manifests:
         for ep in m.get("endpoints", []):
             by_name.setdefault(ep["name"], []).append((m["stage"]["id"], ep))
+    return by_name
+
+
+def _is_counter(eps) -> bool:
+    return any((e[1].get("protocol") or {}).get("kind") == "counter" for e in eps)
+
+
+def counter_channels(manifests: list[dict]):
+    """Counter channels: one or more producers and any number of consumers, across stages
+    (docs/reference/annotations.md:217-237). -> {channel: (producers, consumers)}; a consumer
+    without a producer is an L-PAIR failure."""
+    failures, out = [], {}
+    for name, eps in sorted(_by_name(manifests).items()):
+        if not _is_counter(eps):
+            continue
+        prod = [e for e in eps if e[1]["direction"] == "produce"]
+        cons = [e for e in eps if e[1]["direction"] == "consume"]
+        if not prod:
+            failures.append(ClauseFailure("L-PAIR", f"channels.{name}", "a counter channel needs at least one producer"))
+            continue
+        out[name] = (prod, cons)
+    if failures:
+        raise PipeLinkError(failures)
+    return out
+
+
+def expand_counters(counters, handles) -> list[dict]:
+    """One record per counter channel: `counter` = [slot handle, release operation, sorted acquire
+    patterns] (pipec/src/pipec2/protocol.py:821-853). Every endpoint agrees on scope, slot and
+    release; each consumer chooses its own acquire pattern."""
+    releases = {"grid": "red.release.gpu", "system": "red.release.sys"}
+    acquires = {"grid": ("ld.acquire.gpu", "ld.relaxed.gpu+fence.acquire.gpu"),
+                "system": ("ld.acquire.sys", "ld.relaxed.sys+fence.acquire.sys")}
+    failures, out = [], []
+    for name, (prod, cons) in sorted(counters.items()):
+        path = f"channels.{name}.protocol"
+        eps = [e for _, e in prod + cons]
+        decls = [(e.get("protocol") or {}).get("counter") for e in eps]
+        if any(e.get("protocol", {}).get("kind") != "counter" or d is None for e, d in zip(eps, decls)):
+            failures.append(ClauseFailure("L-PROTO", path, "counter channel needs a counter declaration on every endpoint"))
+            continue
+        first = decls[0]
+        h = handles.get(first["slot"])
+        if h is None or h.get("class") != "base" or h.get("domain") != "gmem_counter":
+            failures.append(ClauseFailure("L-PROTO", path, "counter slot handle is not declared in the gmem_counter domain"))
+            continue
+        if any(e.get("space") != "gmem" for e in eps):
+            failures.append(ClauseFailure("L-PROTO", path, "counter channels must use gmem space"))
+            continue
+        scope = eps[0].get("scope")
+        if scope not in releases:
+            failures.append(ClauseFailure("L-PROTO", f"{path}.scope", "a counter is grid- or system-scoped"))
+            continue
+        agreed = (scope, first["slot"], first.get("release", releases[scope]))
+        if any((e.get("scope"), d["slot"], d.get("release", releases[scope])) != agreed for e, d in zip(eps, decls)):
+            failures.append(ClauseFailure("L-PROTO", path, "counter scope, slot or release operation disagree"))
+            continue
+        if agreed[2] != releases[scope]:
+            failures.append(ClauseFailure("L-PROTO", f"{path}.release", f"a {scope}-scoped counter is released with {releases[scope]}"))
+            continue
+        acq = sorted({d.get("acquire", acquires[scope][0]) for (_, e), d in zip(prod + cons, decls) if e["direction"] == "consume"})
+        if any(a not in acquires[scope] for a in acq):
+            failures.append(ClauseFailure("L-PROTO", f"{path}.acquire", "acquire pattern outside the scope's vocabulary"))
+            continue
+        out.append({"channel": name, "kind": "counter", "producers": sorted(s for s, _ in prod),
+                    "consumers": sorted(s for s, _ in cons), "counter": [first["slot"], agreed[2], acq]})
+    if failures:
+        raise PipeLinkError(failures)
+    return out
+
+
+def check_topology(manifests, profile):
+    """All stages of one image agree on the CTA group and on the compiled cluster shape
+    (clause L-TOPO; the reference intersects the same declarations, pipec/src/pipec2/link.py:1040-1100)."""
+    failures = []
+    groups = {m["stage"]["id"]: (m.get("topology", {}).get("cta_group") or {}).get("fixed", 1) for m in manifests}
+    clusters = {m["stage"]["id"]: tuple((m.get("topology", {}).get("cluster") or {}).get("compiled", [1, 1, 1])) for m in manifests}
+    if len(set(groups.values())) > 1:
+        failures.append(ClauseFailure("L-TOPO", "topology.cta_group", "stages were compiled for different CTA groups", {"stages": groups}))
+    if len(set(clusters.values())) > 1:
+        failures.append(ClauseFailure("L-TOPO", "topology.cluster.compiled", "stages were compiled for different cluster shapes",
+                                      {"stages": {k: list(v) for k, v in clusters.items()}}))
+    if failures:
+        raise PipeLinkError(failures)
+    group, cluster = next(iter(groups.values())), next(iter(clusters.values()))
+    caps = profile.get("caps", {})
+    if group not in caps.get("cta_group_legal", (1,)):
+        raise PipeLinkError(ClauseFailure("L-TOPO", "topology.cta_group", f"CTA group {group} is not legal on this target"))
+    if any(c < 1 or c > mx for c, mx in zip(cluster, caps.get("max_cluster", (1, 1, 1)))):
+        raise PipeLinkError(ClauseFailure("L-TOPO", "topology.cluster.compiled", f"cluster {list(cluster)} exceeds the target's limit"))
+    size = cluster[0] * cluster[1] * cluster[2]
+    if group == 2 and size % 2:
+        raise PipeLinkError(ClauseFailure("L-TOPO", "topology.cluster.compiled", "a CTA pair needs an even cluster"))
+    return group, cluster
+
+
+def pair_channels(manifests: list[dict]):
+    """-> {channel: (producer (stage_id, endpoint), consumer (stage_id, endpoint))} for every channel
+    that pairs exactly one producer with one consumer (all protocols but counters)."""
     failures, channels = [], {}
-    for name, eps in sorted(by_name.items()):
+    for name, eps in sorted(_by_name(manifests).items()):
+        if _is_counter(eps):
+            continue
         prod = [e for e in eps if e[1]["direction"] == "produce"]
         cons = [e for e in eps if e[1]["direction"] == "consume"]
         if len(prod) != 1 or len(cons) != 1:
@@ -96,8 +196,11 @@ def _role_sizes(manifests):
     return sizes
 
 
-def expand_protocols(channels, manifests) -> list[dict]:
-    """One expansion record per channel: barrier slot handles, arrival counts, tx bytes, depth."""
+def expand_protocols(channels, manifests, cluster_size: int = 1) -> list[dict]:
+    """One expansion record per channel: barrier slot handles, arrival counts, tx bytes, depth.
+    A cluster-scoped channel may collect its arrivals from the role's warps in every CTA of the
+    cluster (the reference's example: pl::side{..., {"producer", 2}, 0} under .scope("cluster"),
+    docs/reference/annotations.md:205-209)."""
     warps = _role_sizes(manifests)
     failures, out = [], []
     for name, ((ps, pe), (cs, ce)) in sorted(channels.items()):
@@ -117,15 +220,22 @@ def expand_protocols(channels, manifests) -> list[dict]:
                     failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.{side}.arrive.by", f"unknown role {by!r}"))
                     continue
                 legal = {1, warps[by], 32 * warps[by]}
+                if pe.get("scope") == "cluster":
+                    legal |= {cluster_size * n for n in (1, warps[by], 32 * warps[by])}
                 if count not in legal:
                     failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.{side}.arrive.count",
                                                   f"{count} arrivals cannot come from role {by!r} ({warps[by]} warps)",
                                                   {"legal": sorted(legal)}))
                 rec[side] = {"slots": s["slots"], "count": count, "by": by, "tx_bytes": s.get("tx_bytes", 0)}
             full = proto.get("full") or {}
-            if full.get("tx_bytes", 0) not in (0, ring.get("stage_stride_bytes", 0)) and pe["proxy"] == "async" and pe["space"] == "smem":
+            tx, stride = full.get("tx_bytes", 0), ring.get("stage_stride_bytes", 0)
+            # a slot may carry padding behind its payload (alignment of the next slot), never less than it
+            payload = ring.get("payload_bytes", stride)
+            if tx not in (0, payload, cluster_size * payload) and pe["proxy"] == "async" and pe["space"] == "smem":
                 failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.full.tx_bytes",
-                                              "expected transaction bytes differ from the ring's stage stride"))
+                                              "expected transaction bytes differ from the ring slot's payload"))
+            if payload > stride:
+                failures.append(ClauseFailure("L-PROTO", f"channels.{name}.ring.payload_bytes", "a slot's payload exceeds its stride"))
             init = proto.get("init", {})
             if init.get("materializer") != "dispatch":
                 failures.append(ClauseFailure("L-OWNER", f"channels.{name}.protocol.init", "barrier init needs a single materializer (dispatch)"))

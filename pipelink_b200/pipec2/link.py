@@ -24,6 +24,8 @@ def _unify_claims(manifests, handles):
     claims, failures = {}, []
     for m in manifests:
         for cl in m.get("claims", []):
+            if cl.get("domain") == "regs":
+                continue                    # register claims are grouped by _reg_claims
             rec = {k: v for k, v in cl.items() if k != "roles"}
             h = cl["handle"]
             if h in claims:
@@ -44,6 +46,50 @@ def _unify_claims(manifests, handles):
     if failures:
         raise PipeLinkError(failures)
     return claims
+
+
+def _reg_claims(manifests, handles):
+    """Register claims of all stages; owners that state the same group must state it identically."""
+    out, failures = {}, []
+    for m in manifests:
+        for cl in m.get("claims", []):
+            if cl.get("domain") != "regs":
+                continue
+            h = cl["handle"]
+            if h not in handles:
+                failures.append(ClauseFailure("L-HANDLE", f"claims.{h}", "claim handle is not declared by the pipeline"))
+                continue
+            rec = {"handle": h, "values": list(cl["values"]), "reg_group": cl.get("reg_group")}
+            if h in out:
+                if {k: out[h][k] for k in rec} != rec:
+                    failures.append(ClauseFailure("L-OWNER", f"claims.{h}", "owners disagree about the register group"))
+                out[h]["roles"] = sorted(set(out[h]["roles"]) | set(cl["roles"]))
+            else:
+                out[h] = dict(rec, roles=sorted(cl["roles"]))
+    if failures:
+        raise PipeLinkError(failures)
+    return list(out.values())
+
+
+def _register_audit(info: str, launch_regs):
+    """What the device link reports for the linked kernel: (registers, stack bytes, spill bytes).
+    The register groups were solved for a launch allocation of `launch_regs` per thread; an image
+    that needs more, or that spills, does not run as solved (the reference audits the same figures
+    after its link and re-solves or fails, pipec/src/pipec2/link.py:1706,1810-1825)."""
+    import re
+    regs = re.search(r"Used (\d+) registers", info)
+    frame = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", info)
+    if regs is None:
+        return (-1, -1, -1)
+    observed = (int(regs.group(1)), int(frame.group(1)) if frame else -1,
+                int(frame.group(2)) + int(frame.group(3)) if frame else -1)
+    if launch_regs is not None:
+        if observed[0] > launch_regs:
+            raise PipeLinkError(ClauseFailure("L-REGS", "link.register_audit",
+                                              f"the linked kernel needs {observed[0]} registers per thread, the register groups were solved for {launch_regs}"))
+        if observed[2] > 0:
+            raise PipeLinkError(ClauseFailure("L-REGS", "link.register_audit", f"the linked kernel spills {observed[2]} bytes"))
+    return observed
 
 
 def _params_layout(manifests, profile):
@@ -84,9 +130,12 @@ def link(pipeline_path, out_dir, *, device_link=True):
     profile = PROFILES[profiles.pop()]
     handles = dict(pipe.get("handles", {}))
 
+    cta_group, cluster = contracts.check_topology(manifests, profile)
+    cluster_size = cluster[0] * cluster[1] * cluster[2]
     channels = contracts.pair_channels(manifests)
     contracts.check_compatibility(channels)
-    expansions = contracts.expand_protocols(channels, manifests)
+    expansions = contracts.expand_protocols(channels, manifests, cluster_size)
+    expansions += contracts.expand_counters(contracts.counter_channels(manifests), handles)
     for e in expansions:
         d = e.get("depth")
         if isinstance(d, dict) and "handle" in d and handles.get(d["handle"], {}).get("class") != "depth":
@@ -99,9 +148,18 @@ def link(pipeline_path, out_dir, *, device_link=True):
         claims[TMEM_SLOT_HANDLE] = {"rec": {"handle": TMEM_SLOT_HANDLE, "domain": "smem", "extent": {"const": 16, "per": {}}, "align": 16},
                                     "stage": "pipec2.dispatch", "roles": []}
     params = _params_layout(manifests, profile)
+    role_warps = {}
+    for m in manifests:
+        for rname, r in m["stage"]["roles"].items():
+            mine = [h for h, c in claims.items() if c["rec"]["domain"] == "warp" and (m["stage"]["id"], rname) in c["roles"]]
+            if len(mine) == 1:
+                role_warps[rname] = (mine[0], r["warps"])
     bindings, intervals, solver = solve({h: c["rec"] for h, c in claims.items()}, handles, profile,
                                         depth_priority=pipe.get("depth_priority", []),
-                                        forced=pipe.get("forced_bindings", {}))
+                                        forced=pipe.get("forced_bindings", {}),
+                                        regs_priority=pipe.get("regs_priority", []),
+                                        reg_claims=_reg_claims(manifests, handles), role_warps=role_warps,
+                                        pipeline_domains=pipe.get("domains", {}))
 
     # roles: warp interval from the role's warp claim, params offset from the layout
     offsets = {e[0]: e[1] for e in params["entries"]}
@@ -130,7 +188,11 @@ def link(pipeline_path, out_dir, *, device_link=True):
         "binding_stub.cu": codegen.binding_stub(bindings),
         "dispatch.cu": codegen.dispatch(threads=threads, params_total=params["total_bytes"], roles=roles,
                                         expansions=expansions, bindings=bindings, tmem_columns=tmem_cols,
-                                        tmem_slot=bindings.get(TMEM_SLOT_HANDLE, [0])[0], tmem_warp=roles[0]["warp_lo"]),
+                                        tmem_slot=bindings.get(TMEM_SLOT_HANDLE, [0])[0], tmem_warp=roles[0]["warp_lo"],
+                                        cta_group=cta_group, cluster=cluster, reg_groups=solver.get("reg_groups", []),
+                                        launch_regs=solver.get("launch_regs"),
+                                        extra_barriers={h: c["rec"]["init_count"] for h, c in claims.items()
+                                                        if c["rec"]["domain"] == "mbarrier" and "init_count" in c["rec"]}),
     }
     out_dir.mkdir(parents=True, exist_ok=True)
     gen_dir = out_dir / "generated"
@@ -145,12 +207,14 @@ def link(pipeline_path, out_dir, *, device_link=True):
                 obj = Path(tmp) / (name + ".o")
                 jitlink.compile_lto(str(gen_dir / name), str(obj), profile)
                 objects.append((name, obj.read_bytes()))
-        cubin, info = jitlink.link(objects, profile["sm"])
+        cubin, info = jitlink.link(objects, profile["sm"], extra=["-Xptxas=-v"])
         (out_dir / "pipeline.cubin").write_bytes(cubin)
         (out_dir / "nvjitlink.log").write_text(info)
+        observed = _register_audit(info, solver.get("launch_regs"))
     result = LinkResult(
-        kernel_symbol="pipelink_kernel", threads=threads, regs_cap=min(255, 65536 // max(threads, 1) // 8 * 8),
-        dyn_smem_bytes=smem_hw, cluster=(1, 1, 1), params=params, bindings=bindings, variants={},
+        kernel_symbol="pipelink_kernel", threads=threads,
+        regs_cap=solver.get("launch_regs") or min(255, 65536 // max(threads, 1) // 8 * 8),
+        dyn_smem_bytes=smem_hw, cluster=tuple(cluster), params=params, bindings=bindings, variants={},
         intervals=intervals, protocol_expansions=expansions, observed=observed, input_hashes=input_hashes,
         generated_hashes={k: hashlib.sha256(v.encode()).hexdigest() for k, v in generated.items()},
         solver=solver, roles=roles, tmem_columns=tmem_cols)

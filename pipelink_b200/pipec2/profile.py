@@ -6,7 +6,7 @@ from dataclasses import dataclass
 @dataclass(frozen=True)
 class Domain:
     unit: str
-    capacity: int
+    capacity: object   # int, or "pipeline": the pipeline description states the capacity
     lowest: int
     granularity: int
     physical: str      # domains sharing a physical resource must not overlap each other
@@ -22,6 +22,12 @@ SM_100A = {
         "tmem": Domain("columns", 512, 0, 32, "tmem", 1),
         "named_barrier": Domain("IDs", 16, 1, 1, "named_barrier", 1),
         "warp": Domain("launch warps", 32, 0, 1, "warp", 1),
+        "regs": Domain("per-thread registers", 256, 24, 8, "regs", 1),
+        "gmem_counter": Domain("4-byte slots", "pipeline", 0, 1, "gmem_counter", 1),
     },
+    # register file of one SM, setmaxnreg granularity, warps per warpgroup, legal CTA groups and
+    # the largest cluster (pipec/src/pipec2/profile.py:141-149 gives sm_103a the same caps)
+    "caps": {"regs_per_sm": 65536, "reg_alloc_granularity": 8, "regs_min": 24, "regs_max": 255,
+             "warpgroup_warps": 4, "cta_group_legal": (1, 2), "max_cluster": (8, 8, 8)},
 }
 PROFILES = {"sm_100a": SM_100A}

@@ -80,7 +80,11 @@ def validate_manifest(m: dict, where: str = "manifest") -> None:
         if cl.get("domain") not in PROFILES.get(target.get("profile"), {"domains": {}})["domains"]:
             c.add("L-BUDGET", f"{p}.domain", f"unknown domain {cl.get('domain')!r}")
         ext = cl.get("extent", {})
-        if not isinstance(ext.get("const", 0), int) or ext.get("const", 0) < 0:
+        if cl.get("domain") == "regs":
+            # a register claim names the roles of one reg group and the per-thread counts it accepts
+            if not cl.get("roles") or not cl.get("values") or any(not isinstance(v, int) for v in cl["values"]):
+                c.add("L-REGS", f"{p}", "a regs claim needs roles and candidate values")
+        elif not isinstance(ext.get("const", 0), int) or ext.get("const", 0) < 0:
             c.add("L-BUDGET", f"{p}.extent.const", "extent must be a non-negative integer")
         for r in cl.get("roles", []):
             if r not in roles:
@@ -104,8 +108,8 @@ def validate_pipeline(p: dict) -> None:
             c.add("L-HANDLE", f"pipeline.handles.{name}.class", f"unknown class {cls!r}")
         elif not str(h.get("owner", "")).startswith(HANDLE_CLASSES[cls]):
             c.add("L-HANDLE", f"pipeline.handles.{name}.owner", f"owner of a {cls} handle must start with {HANDLE_CLASSES[cls]!r}")
-        if cls == "depth" and not h.get("values"):
-            c.add("L-HANDLE", f"pipeline.handles.{name}.values", "a depth handle needs candidate values")
+        if cls in ("depth", "regs") and not h.get("values"):
+            c.add("L-HANDLE", f"pipeline.handles.{name}.values", f"a {cls} handle needs candidate values")
         if h.get("binding") not in ("bind", "fixed", "launch"):
             c.add("L-HANDLE", f"pipeline.handles.{name}.binding", "binding must be bind, fixed or launch")
     for name in pipe.get("forced_bindings", {}):
@@ -114,4 +118,10 @@ def validate_pipeline(p: dict) -> None:
     for name in pipe.get("depth_priority", []):
         if pipe.get("handles", {}).get(name, {}).get("class") != "depth":
             c.add("L-HANDLE", f"pipeline.depth_priority.{name}", "not a depth handle")
+    for name in pipe.get("regs_priority", []):
+        if pipe.get("handles", {}).get(name, {}).get("class") != "regs":
+            c.add("L-HANDLE", f"pipeline.regs_priority.{name}", "not a regs handle")
+    for dom, d in pipe.get("domains", {}).items():
+        if not isinstance(d.get("capacity"), int) or d["capacity"] < 0:
+            c.add("L-BUDGET", f"pipeline.domains.{dom}.capacity", "a pipeline domain needs a non-negative capacity")
     c.raise_if_any()

@@ -16,7 +16,7 @@ import z3
 
 from .model import ClauseFailure, PipeLinkError
 
-PRECEDENCE = ("L-BUDGET", "L-OVERLAP", "L-HANDLE", "L-TOPO", "L-ALIGN")
+PRECEDENCE = ("L-BUDGET", "L-OVERLAP", "L-HANDLE", "L-TOPO", "L-ALIGN", "L-REGS")
 
 
 def _extent_expr(extent, depth_vars):
@@ -26,9 +26,13 @@ def _extent_expr(extent, depth_vars):
     return e
 
 
-def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forced=None, total_warps=None):
-    """claims: handle -> unified claim record. Returns (bindings, intervals, tiers)."""
+def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forced=None, total_warps=None,
+          regs_priority=(), reg_claims=(), role_warps=None, pipeline_domains=None):
+    """claims: handle -> unified claim record (every domain but `regs`). reg_claims: the register
+    claims ({handle, roles, values, reg_group?}); role_warps: role -> (warp claim handle, warps).
+    Returns (bindings, intervals, tiers)."""
     forced = forced or {}
+    pipeline_domains = pipeline_domains or {}
     opt = z3.Optimize()
     opt.set(priority="lex")
     tracked = []  # (bool, clause, path) for diagnostics through a parallel Solver
@@ -50,7 +54,11 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         add(z3.Or([v == x for x in values]), "L-HANDLE", f"handles.{name}.values")
 
     base_vars, ext_exprs = {}, {}
-    domains = profile["domains"]
+    domains = dict(profile["domains"])
+    for dname, dom in list(domains.items()):
+        if dom.capacity == "pipeline":      # the pipeline description sizes this domain (0 when it does not)
+            cap = int((pipeline_domains.get(dname) or {}).get("capacity", 0))
+            domains[dname] = type(dom)(dom.unit, cap, dom.lowest, dom.granularity, dom.physical, dom.scale)
     for name, cl in claims.items():
         dom = domains[cl["domain"]]
         b = z3.Int(name)
@@ -91,6 +99,53 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         if total > domains["warp"].capacity:
             raise PipeLinkError(ClauseFailure("L-TOPO", "topology.warps", f"{total} warps exceed the launch limit"))
 
+    # register groups (pipec/src/pipec2/solve.py:737-812): every group is a run of whole warpgroups
+    # that contains exactly its member roles; the chosen per-thread counts must fit the register
+    # file the launch is given (launch threads x the launch's per-thread allocation)
+    regs_vars, reg_groups = {}, []
+    caps = profile.get("caps", {})
+    if reg_claims:
+        path = "solve.register_groups"
+        role_warps = role_warps or {}
+        wg = caps.get("warpgroup_warps", 4)
+        assigned, pool = set(), 0
+        launch_threads = 32 * sum(w for _, w in role_warps.values())
+        for cl in sorted(reg_claims, key=lambda c: c["handle"]):
+            name = cl.get("reg_group") or (cl["roles"][0] if len(cl["roles"]) == 1 else None)
+            h = handles.get(cl["handle"])
+            members = sorted(set(cl["roles"]))
+            bad = (name is None or h is None or h.get("class") != "regs" or h.get("domain") != "regs" or
+                   h.get("owner") != f"reg_group:{name}" or not members or
+                   any(r in assigned or r not in role_warps for r in members))
+            if bad:
+                add(z3.BoolVal(False), "L-REGS", path)
+                continue
+            assigned.update(members)
+            v = z3.Int(cl["handle"])
+            regs_vars[cl["handle"]] = v
+            values = [forced[cl["handle"]]] if cl["handle"] in forced else sorted(set(h["values"]) & set(cl["values"]))
+            add(z3.Or([v == x for x in values]) if values else z3.BoolVal(False), "L-REGS", path)
+            width = sum(role_warps[r][1] for r in members)
+            lo = z3.Int(f"reg_group:{name}:lo")
+            add(z3.And(lo >= 0, lo % wg == 0, (lo + width) % wg == 0), "L-REGS", path)
+            for r in members:
+                rb = base_vars[role_warps[r][0]]
+                add(z3.And(rb >= lo, rb + role_warps[r][1] <= lo + width), "L-REGS", path)
+            pool = pool + v * width * 32
+            reg_groups.append({"name": name, "handle": cl["handle"], "roles": members, "lo": lo, "width": width})
+        if assigned != set(role_warps):
+            add(z3.BoolVal(False), "L-REGS", path)
+        expected = {n for n, h in handles.items() if h.get("class") == "regs"}
+        if expected != set(regs_vars):
+            add(z3.BoolVal(False), "L-REGS", path)
+        gran = caps.get("reg_alloc_granularity", 8)
+        launch_regs = z3.Int("__launch_regs")
+        add(z3.And(launch_regs % gran == 0, launch_regs >= caps.get("regs_min", 24), launch_regs <= caps.get("regs_max", 255),
+                   launch_regs * launch_threads <= caps.get("regs_per_sm", 65536), pool <= launch_regs * launch_threads),
+            "L-REGS", path)
+    elif any(h.get("class") == "regs" for h in handles.values()):
+        add(z3.BoolVal(False), "L-REGS", "solve.register_groups")
+
     for expr, _, _ in cons:
         opt.add(expr)
 
@@ -103,6 +158,13 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         if name not in depth_priority:
             opt.maximize(depth_vars[name])
             tiers.append({"name": f"max {name}"})
+    for name in list(regs_priority) + sorted(n for n in regs_vars if n not in regs_priority):
+        if name in regs_vars:
+            opt.maximize(regs_vars[name])
+            tiers.append({"name": f"max {name}"})
+    if reg_claims:
+        opt.minimize(z3.Int("__launch_regs"))       # the smallest launch allocation that covers the pool
+        tiers.append({"name": "min launch registers"})
     highwater = {}
     for phys in sorted({d.physical for d in domains.values()}):
         members = [n for n in names if domains[claims[n]["domain"]].physical == phys]
@@ -133,7 +195,14 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
     for tier in tiers:
         tier["status"] = "optimal"
     hw_vals = {phys: val(hw) for phys, hw in highwater.items()}
-    return bindings, intervals, {"tiers": tiers, "high_water": hw_vals, "engine": f"z3 {z3.get_version_string()} Optimize(lex)"}
+    info = {"tiers": tiers, "high_water": hw_vals, "engine": f"z3 {z3.get_version_string()} Optimize(lex)"}
+    if reg_claims:
+        for n, v in regs_vars.items():
+            bindings[n] = [val(v), "forced" if n in forced else "solved"]
+        info["launch_regs"] = val(z3.Int("__launch_regs"))
+        info["reg_groups"] = [{"name": g["name"], "handle": g["handle"], "roles": g["roles"], "warp_lo": val(g["lo"]),
+                               "warp_hi": val(g["lo"]) + g["width"], "regs": val(regs_vars[g["handle"]])} for g in reg_groups]
+    return bindings, intervals, info
 
 
 def _diagnose(cons):

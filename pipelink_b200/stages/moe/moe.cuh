@@ -1,0 +1,161 @@
+// Shared vocabulary of the MoE grouped-GEMM stages: tile geometry, per-stage parameter blocks
+// and the link-time handles the stages read.
+//
+// The linked image is the CTA-pair grouped MXFP8 GEMM of csrc/grouped_gemm2.cu cut along its
+// warp roles into separately packed owners, the way the reference cuts its MoE megakernel into
+// comm / gemm / act packages joined by channel contracts (campaigns/mok/port/pipelines/fwd.json,
+// campaigns/mok/port/gemm/gemm.cu:447-468 for the GEMM owner's channel list):
+//   moe.load       1 warp   TMA producer of the operands ring (both CTAs of a pair)
+//   moe.mma        1 warp   tcgen05 cta_group::2 MMA issuer (leader CTA), scale blocks -> TMEM
+//   moe.comm.*     2 warps  dispatch: pulls routed rows from the home ranks under the mainloop
+//                           (moe.comm.dispatch), or does nothing (moe.comm.none)
+//   moe.epilogue.* 8 warps  accumulator -> SwiGLU + MXFP8 requantise (gate/up projection), or
+//                           accumulator -> bf16 rows placed / pushed to the home rank (down projection)
+// joined by an `operands` ring in shared memory whose depth is bound at link time, an
+// `accumulator` channel in tensor memory and a `rows_ready` counter channel in global memory
+// (comm -> load). Every pipelink_* function is resolved by the generated binding stub; after the
+// LTO link each call folds to a constant.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+#include "../../csrc/common.cuh"
+#include "../../csrc/mxfp8.cuh"
+
+namespace moe {
+constexpr int TileBytes = 128 * 128;                       // one CTA's A or B tile of a K step
+constexpr int SfBytes = 512;                               // one 128-row x 4-group scale block
+constexpr int SlotBytes = 2 * TileBytes + 3 * SfBytes + 512;   // A | B | SFA SFB0 SFB1 | pad to 1 KiB
+constexpr int SlotTx = 2 * TileBytes + 3 * SfBytes;        // bytes one CTA's loads credit per K step
+constexpr int OffA = 0, OffB = TileBytes, OffSf = 2 * TileBytes;
+constexpr int SfColsPerSlot = 16;                          // TMEM columns: 4 (A) + 8 (B) used
+constexpr int AccCols = 256;
+constexpr int EpilogueWarps = 8;
+constexpr int MaxRowTiles = 4096;                          // counter slots claimed for rows_ready (1 M schedule rows)
+static_assert(SlotBytes % 1024 == 0, "operand tiles need 1 KiB alignment for the 128-byte swizzle");
+}  // namespace moe
+
+// What every role needs to walk the same tile list.
+struct MoeGeometry {
+  const int* block_expert;   // expert of each 128-row block of the schedule
+  const int* num_rows_dev;   // padded rows in use (device scalar)
+  plb::Status* status;
+  int max_m_tiles;           // capacity / 256
+  int k_steps;               // K / 128
+  int n_tiles;               // weight rows per expert / 256
+  int m_rotation;            // the tile loop starts this many row tiles in
+  int m_stride;              // and steps this many row tiles at a time (made coprime to the live count)
+  int pad;
+};
+
+struct alignas(64) MoeLoadParams {
+  CUtensorMap a, b, sfa, sfb;
+  MoeGeometry g;
+  const unsigned* counters;     // the image's counter workspace (null: A is already in place);
+                                // slot pipelink_moe_rows_ready() + m_tile reaches 256 when the tile is complete
+};
+struct alignas(16) MoeMmaParams {
+  MoeGeometry g;
+};
+struct alignas(16) MoeCommParams {
+  MoeGeometry g;
+  const uint8_t* const* xq_peers;        // per rank: u8 [tokens, K]
+  const uint32_t* const* sc_rows_peers;  // per rank: u32 [tokens, K / 128]
+  const int* peer_rank;
+  const int* peer_token_idx;
+  uint8_t* dst;                          // the A operand
+  uint8_t* dst_sc;
+  unsigned* counters;                    // the image's counter workspace, zeroed before the launch:
+                                         // pipelink_moe_rows_ready() + m_tile and pipelink_moe_ticket()
+  int row_bytes;                         // K
+  int pad;
+};
+struct alignas(16) MoeSwigluParams {
+  MoeGeometry g;
+  uint8_t* out;        // E4M3 [rows, out_cols]
+  uint8_t* out_sc;
+  int out_cols;        // I
+  float limit;         // +inf: plain SwiGLU
+};
+struct alignas(16) MoeRowsParams {
+  MoeGeometry g;
+  uint8_t* out;                  // bf16 rows, local placement
+  uint8_t* const* out_peers;     // or per-rank bases (push), null for local
+  const int* dest_row;
+  const int* peer_rank;
+  int out_cols;                  // H
+  int pad;
+};
+
+extern "C" __device__ int pipelink_moe_depth();
+extern "C" __device__ int pipelink_moe_operands();     // smem byte offset of the ring
+extern "C" __device__ int pipelink_moe_full();         // first mbarrier slot (16 bytes each)
+extern "C" __device__ int pipelink_moe_empty();
+extern "C" __device__ int pipelink_moe_acc_full();
+extern "C" __device__ int pipelink_moe_acc_empty();
+extern "C" __device__ int pipelink_moe_drain();        // mbarrier slot the MMA owner drains through on failure
+extern "C" __device__ int pipelink_moe_acc();          // first TMEM column of the accumulator
+extern "C" __device__ int pipelink_moe_sfcols();       // first TMEM column of the scale slots
+extern "C" __device__ int pipelink_moe_staging();      // smem byte offset: 2 KiB per epilogue warp / dispatch ring
+extern "C" __device__ int pipelink_moe_warp_epilogue();// first warp of the epilogue role
+extern "C" __device__ int pipelink_moe_warp_comm();    // first warp of the comm role
+extern "C" __device__ int pipelink_moe_rows_ready();   // first counter slot of the per-row-tile counts (gmem_counter domain)
+extern "C" __device__ int pipelink_moe_ticket();       // counter slot of the dispatch ticket
+extern "C" __device__ int pipelink_tmem_slot();        // smem byte offset where dispatch put the TMEM base
+
+namespace moe {
+__device__ __forceinline__ uint32_t bar(uint32_t smem_base, int base, int slot = 0) {
+  return smem_base + 16u * static_cast<uint32_t>(base + slot);
+}
+
+struct Walk {          // the tile list of this launch, identical for every role
+  int total_tiles, m_tiles_live, m_rot, m_stride;
+};
+struct Tile {
+  int a_blk, b_blk0, n_tile;
+  int64_t out_row0;
+};
+
+// A 256-row tile is multiplied by one expert's weights: a schedule padded to less than the tile is
+// refused (every warp of every role evaluates this on its own and reaches the same answer).
+__device__ __forceinline__ Walk make_walk(const MoeGeometry& g, int lane, bool report) {
+  Walk w;
+  const int rows = *g.num_rows_dev;
+  w.m_tiles_live = rows >> 8;
+  if (w.m_tiles_live > g.max_m_tiles) w.m_tiles_live = g.max_m_tiles;
+  int bad = (rows & 255) != 0;
+  for (int m = lane; m < w.m_tiles_live; m += 32) bad |= g.block_expert[2 * m] != g.block_expert[2 * m + 1];
+  bad = __any_sync(0xFFFFFFFFu, bad);
+  if (bad) {
+    if (report && lane == 0) plb::report_failure(g.status, plb::ST_BAD_ARGUMENT, 320, static_cast<unsigned>(rows), 256u);
+    w.m_tiles_live = 0;
+  }
+  w.total_tiles = w.m_tiles_live * g.n_tiles;
+  w.m_rot = w.m_tiles_live > 0 ? g.m_rotation % w.m_tiles_live : 0;
+  w.m_stride = 1;
+  if (g.m_stride > 1 && w.m_tiles_live > 1) {
+    for (w.m_stride = g.m_stride % w.m_tiles_live == 0 ? 1 : g.m_stride % w.m_tiles_live;; ++w.m_stride) {
+      int a = w.m_stride, b = w.m_tiles_live;
+      while (b != 0) { const int t = a % b; a = b; b = t; }
+      if (a == 1) break;
+    }
+  }
+  return w;
+}
+
+__device__ __forceinline__ Tile decode(const MoeGeometry& g, const Walk& w, int tile, int cta_rank) {
+  Tile t;
+  int m_tile = tile / g.n_tiles;
+  t.n_tile = tile - m_tile * g.n_tiles;
+  m_tile = static_cast<int>((static_cast<long long>(m_tile) * w.m_stride + w.m_rot) % w.m_tiles_live);
+  const int expert = g.block_expert[m_tile * 2];
+  t.a_blk = m_tile * 2 + cta_rank;
+  t.b_blk0 = (expert * g.n_tiles + t.n_tile) * 2;
+  t.out_row0 = static_cast<int64_t>(m_tile) * 256;
+  return t;
+}
+}  // namespace moe
+
+static_assert(sizeof(MoeGeometry) == 48 && sizeof(MoeLoadParams) == 576 && sizeof(MoeMmaParams) == 48 &&
+              sizeof(MoeCommParams) == 112 && sizeof(MoeSwigluParams) == 80 && sizeof(MoeRowsParams) == 96,
+              "parameter blocks: the manifests and the host image state these sizes");
