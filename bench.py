@@ -700,24 +700,25 @@ def tp_leg(dev, pk, rank, world, steps=20):
     return out
 
 
-def linked_leg(session, steps=10):
-    """The same two grouped GEMMs launched as LINKED images (the packages of stages/moe joined by the
-    link driver) and as the library's kernels, alternating, on the benchmark's own buffers: device
-    time per launch and the ratio linked / library (the reference's gate for a linked build is 1 % of
-    the single-unit build)."""
+def linked_leg(session, steps=24):
+    """The same two grouped GEMMs launched three ways, alternating, on the benchmark's own buffers:
+    the library's kernels, the LINKED images (the packages of stages/moe joined by the link driver)
+    and the one-translation-unit build of those same stage sources. Device time per launch; `ratio`
+    is linked / one-unit, the reference's gate for a linked build (within 1 %)."""
     import torch
     from pipelink_b200 import moe_linked
     h = session.host
     try:
-        linked = moe_linked.LinkedMoE(h)
+        linked, one_tu = moe_linked.LinkedMoE(h), moe_linked.LinkedMoE(h, image="one_tu.cubin")
     except Exception as exc:  # noqa: BLE001 - images absent: report, do not fail the benchmark
         return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
     session.step()
     out = {}
-    for name, lib_fn, lnk_fn in (("gate_up", h.gemm_gate_up, linked.gemm_gate_up), ("down", h.gemm_down, linked.gemm_down)):
-        t = {"library": 0.0, "linked": 0.0}
+    for name, fns in (("gate_up", (("library", h.gemm_gate_up), ("linked", linked.gemm_gate_up), ("one_unit", one_tu.gemm_gate_up))),
+                      ("down", (("library", h.gemm_down), ("linked", linked.gemm_down), ("one_unit", one_tu.gemm_down)))):
+        t = {k: [] for k, _ in fns}
         for i in range(steps + 2):
-            for which, fn in (("library", lib_fn), ("linked", lnk_fn)):
+            for which, fn in fns[i % 3:] + fns[:i % 3]:      # rotate the order: no arm always runs on the hottest GPU
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 h.dispatch()                    # other traffic between the launches, as in a step
                 a.record()
@@ -725,10 +726,14 @@ def linked_leg(session, steps=10):
                 b.record()
                 torch.cuda.synchronize()
                 if i >= 2:
-                    t[which] += a.elapsed_time(b) / steps
-        out[name] = {"library_ms": t["library"], "linked_ms": t["linked"], "ratio": t["linked"] / t["library"]}
+                    t[which].append(a.elapsed_time(b))
+        med = {k: statistics.median(v) for k, v in t.items()}
+        out[name] = {"library_ms": med["library"], "linked_ms": med["linked"], "one_unit_ms": med["one_unit"],
+                     "ratio": med["linked"] / med["one_unit"], "linked_over_library": med["linked"] / med["library"],
+                     "spread_ms": {k: [min(v), max(v)] for k, v in t.items()}, "launches_per_arm": steps}
     h.status.check("bench (linked images)")
     linked.close()
+    one_tu.close()
     out["ring_depth"] = {"library": 5, "linked": linked_depth()}
     return out
 
@@ -813,17 +818,36 @@ def cp_attention_leg(dev, pk, rank, world, seq=131072, steps=2, check=True):
         torch.cuda.empty_cache()
         if not parity["ok"]:
             raise RuntimeError("context-parallel attention differs from the single-GPU result")
+    def timed(rank_session):
+        rank_session.step(q, k, v)          # warm-up of this form of the exchange
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            rank_session.step(q, k, v)
+        b.record()
+        torch.cuda.synchronize()
+        rank_session.status.check("cp attention leg")
+        t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # the K/V exchange as a launch in front of the attention kernel, and inside it (gather warps of
+    # every attention CTA): both are timed, the faster one is the leg's figure
+    times = {"launch in front": timed(r)}
     dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
-        r.step(q, k, v)
-    b.record()
-    torch.cuda.synchronize()
-    r.status.check("cp attention leg")
-    t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    fused = att.CpRank(seq, Hq, Hkv, rank, world, slab.ptrs, layout, dev, fused_push=True)
+    times["inside the attention launch"] = timed(fused)
+    if check:
+        ok = torch.equal(fused.out.view(torch.int16), r.out.view(torch.int16)) and torch.equal(fused.lse, r.lse)
+        flag = torch.tensor([int(ok)], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity["exchange_inside_the_launch_equal"] = bool(flag.item())
+        if not flag.item():
+            raise RuntimeError("attention with the in-kernel K/V exchange differs from the separate push")
+    ms = min(times.values())
+    exchange = {"ms": times, "chosen": min(times, key=times.get)}
     dist.barrier()
     slab.close()
     tf = 4.0 * 128 * Hq * seq * (seq + 1) / 2 / (ms * 1e-3) / 1e12
@@ -831,6 +855,7 @@ def cp_attention_leg(dev, pk, rank, world, seq=131072, steps=2, check=True):
     payload = 1.5 * world * (world - 1) * chunk * Hkv * 128 * 2 * 2   # K+V bytes that must cross NVLink, all ranks
     return {"metric": "cp_causal_prefill_attention_tflops", "value": tf, "unit": "TFLOP/s", "ms": ms, "seq": seq,
             "world": world, "nvlink_payload_bytes": payload, "scaling": "strong", "parity": parity,
+            "kv_exchange": exchange,
             "roofline": {"bound": "tensor", "achieved": tf / world, "peak": pk["bf16_sustained"], "unit": "TFLOP/s per GPU",
                          "frac": tf / world / pk["bf16_sustained"]}}
 

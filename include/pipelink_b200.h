@@ -429,6 +429,23 @@ int plb_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks, i
                    int rank, int world, void* const* k_gather_peers, void* const* v_gather_peers,
                    void* const* ready_peers, int ctas, void* stream);
 
+/* Context-parallel attention with the K/V exchange INSIDE the attention launch
+ * (kv_gather_role_gather in the attention CTA, campaigns/attention/src/sm90/stage_kv_gather.cu:16-78;
+ * ticket queue and publish of examples/comm-overlap/comm/push_gather.cuh:80-150): two warps of every
+ * CTA copy this rank's 128-token K/V blocks, in `parts` pieces each, into the gathered buffers of
+ * the ranks that need them and add 1 per piece to that rank's ready[block]; the load lanes wait
+ * for ready_target = (launches so far) * parts. k_local / v_local as for plb_cp_push_kv; the
+ * gathered buffers, counters and peers tables are the same slab regions; ticket_u32 is one word
+ * of scratch, zeroed on the stream by this call. Head pairs only (q_heads / kv_heads even), no
+ * window or soft cap. Every CTA of the launch must be resident at once (the grid is one CTA per
+ * SM at most), so do not share the GPU with other work while it runs. */
+int plb_attention_fwd_cp(const void* q, const void* k_gather, const void* v_gather, void* out, float* lse,
+                         const plb_attn_work* work, int num_work, int q_heads, int kv_heads, int seq_q, uint64_t q_rows,
+                         uint64_t kv_rows, float scale, const uint32_t* ready, uint32_t ready_target, const void* k_local,
+                         const void* v_local, int chunk_blocks, int64_t block_bytes, int parts, int rank, int world,
+                         void* const* k_gather_peers, void* const* v_gather_peers, void* const* ready_peers,
+                         void* ticket_u32, plb_status* status, void* stream);
+
 /* Receive streams for the combine push. plb_moe_gemm_down_push writes row p to
  * `token * topk + slot` of its home rank: 8 KB rows scattered over every peer's combine buffer,
  * which on eight GPUs costs almost twice the time of the same bytes written in order. With

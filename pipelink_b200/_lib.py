@@ -99,6 +99,9 @@ PROTOTYPES = {
                                   c_void_p, c_void_p]),
     "plb_cp_push_kv": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                c_int, c_void_p]),
+    "plb_attention_fwd_cp": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_int, ctypes.c_uint64, ctypes.c_uint64, c_float,
+                                     c_void_p, ctypes.c_uint32, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "plb_image_load": (c_int, [c_void_p, c_char_p, c_int, POINTER(c_void_p), POINTER(c_void_p)]),
     "plb_image_launch": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "plb_image_unload": (c_int, [c_void_p]),

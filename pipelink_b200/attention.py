@@ -103,7 +103,14 @@ class CpRank:
     `v_gather`, `ready`, barrier `flags`) live in a slab that is shared through CUDA IPC
     (``ep.IpcGroup``-style) or, for single-GPU tests, allocated side by side in one process."""
 
-    def __init__(self, seq: int, q_heads: int, kv_heads: int, rank: int, world: int, slab_ptrs, layout, device):
+    PARTS = 8        # pieces a K/V block is pushed in by the gather warps of the attention launch
+
+    def __init__(self, seq: int, q_heads: int, kv_heads: int, rank: int, world: int, slab_ptrs, layout, device,
+                 fused_push: bool = False):
+        """fused_push: the K/V exchange runs inside the attention launch (two gather warps per CTA)
+        instead of as a launch in front of it. It needs head pairs, and ranks that are real GPUs:
+        ranks emulated one after another on one GPU would wait for blocks that only a later launch
+        pushes."""
         from .ep import barrier_state_for, tensor_from_ptr
         self.seq, self.rank, self.world, self.device = seq, rank, world, torch.device(device)
         self.C = seq // (2 * world)
@@ -124,7 +131,11 @@ class CpRank:
         # flags and readiness counters already hold (one session at a time per slab and rank)
         self.barrier_state = barrier_state_for(me + layout["flags"], rank, dev)
         self.status = DeviceStatus(dev)
-        self.generation = int(self.ready.max().item())
+        self.generation = int(self.ready.max().item())      # the value every needed counter holds after the last step
+        self.fused_push = bool(fused_push)
+        if self.fused_push and self.step_heads != 2:
+            raise ValueError("the gather warps live in the two-heads-per-CTA kernel: q_heads / kv_heads must be even")
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
         self.out = torch.empty((2 * self.C, q_heads, D), dtype=torch.bfloat16, device=dev)
         self.lse = torch.empty((q_heads, 2 * self.C), dtype=torch.float32, device=dev)
 
@@ -142,7 +153,7 @@ class CpRank:
 
     def push(self, k_local: torch.Tensor, v_local: torch.Tensor, ctas: int = 32):
         """k_local / v_local bf16 [2C, kv_heads, 128]: this rank's early chunk then its late chunk."""
-        self.generation += 1
+        self.generation += 1        # a separate push adds one per block
         _lib.call("plb_cp_push_kv", k_local.data_ptr(), v_local.data_ptr(), self.C // BLK, BLK * self.kv_heads * D * 2,
                   self.rank, self.world, self.k_peers.data_ptr(), self.v_peers.data_ptr(), self.ready_peers.data_ptr(),
                   ctas, _stream())
@@ -152,9 +163,22 @@ class CpRank:
                 self.generation, self.status)
         return self.out, self.lse
 
+    def attend_and_push(self, q_local, k_local, v_local):
+        """One launch: the gather warps push this rank's K/V while the other warps attend."""
+        self.generation += self.PARTS   # PARTS pieces per block
+        _lib.call("plb_attention_fwd_cp", q_local.data_ptr(), self.k_gather.data_ptr(), self.v_gather.data_ptr(),
+                  self.out.data_ptr(), self.lse.data_ptr(), self.work.data_ptr(), self.work.shape[0], self.q_heads,
+                  self.kv_heads, 2 * self.C, q_local.shape[0], self.seq, 1.0 / math.sqrt(D), self.ready.data_ptr(),
+                  self.generation, k_local.data_ptr(), v_local.data_ptr(), self.C // BLK, BLK * self.kv_heads * D * 2,
+                  self.PARTS, self.rank, self.world, self.k_peers.data_ptr(), self.v_peers.data_ptr(),
+                  self.ready_peers.data_ptr(), self.ticket.data_ptr(), self.status.buf.data_ptr(), _stream())
+        return self.out, self.lse
+
     def step(self, q_local, k_local, v_local, distributed: bool = True):
         if distributed:
             self.barrier()       # every rank has finished reading the previous step's gathered K/V
+        if self.fused_push:
+            return self.attend_and_push(q_local, k_local, v_local)
         self.push(k_local, v_local)
         return self.attend(q_local)
 

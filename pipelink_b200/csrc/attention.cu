@@ -576,6 +576,63 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         }
       }
     }
+  } else if (kUseCounters && p.push_k != nullptr) {
+    // ------------------------------------------------------------------ K/V gather warps (2 and 3)
+    // The context-parallel exchange inside the attention launch (the reference puts its gather warps
+    // into the attention CTA the same way, campaigns/attention/src/sm90/stage_kv_gather.cu:16-78, with
+    // the ticket / publish primitives of examples/comm-overlap/comm/push_gather.cuh:80-150). Tickets
+    // come from one global counter, so any resident CTA serves any piece and progress never depends
+    // on which CTA got which attention tile; the warps wait for nothing. Order: ascending global
+    // position, the order in which every consumer's tiles read their key blocks. Zigzag ownership
+    // (campaigns/attention/README.md:222-228): rank r holds chunks r and 2W-1-r of 2W; the early chunk is
+    // needed by every rank, the late chunk only by ranks <= r.
+    const int cb = p.push_chunk_blocks, parts = p.push_parts, W = p.push_world, r = p.push_rank;
+    const int early_tasks = cb * W, late_tasks = cb * (r + 1);
+    const unsigned total = static_cast<unsigned>(early_tasks + late_tasks) * static_cast<unsigned>(parts);
+    for (;;) {
+      unsigned tk = 0;
+      if (lane == 0) tk = atomicAdd(p.push_ticket, 1u);
+      tk = __shfl_sync(0xFFFFFFFFu, tk, 0);
+      if (tk >= total) break;
+      const int task = static_cast<int>(tk / parts), part = static_cast<int>(tk - static_cast<unsigned>(task) * parts);
+      int local_block, consumer, global_block;
+      if (task < early_tasks) {
+        const int b = task / W;
+        consumer = task - b * W;
+        local_block = b;
+        global_block = r * cb + b;
+      } else {
+        const int u = task - early_tasks;
+        const int b = u / (r + 1);
+        consumer = u - b * (r + 1);
+        local_block = cb + b;
+        global_block = (2 * W - 1 - r) * cb + b;
+      }
+      const size_t src_off = (static_cast<size_t>(local_block) * parts + part) * p.push_vec_per_part;
+      const size_t dst_off = (static_cast<size_t>(global_block) * parts + part) * p.push_vec_per_part;
+      const uint4* ks = p.push_k + src_off;
+      const uint4* vs = p.push_v + src_off;
+      uint4* kd = p.push_k_peers[consumer] + dst_off;
+      uint4* vd = p.push_v_peers[consumer] + dst_off;
+      for (int i0 = lane; i0 < p.push_vec_per_part; i0 += 128) {   // loads batched before the stores
+        uint4 a[4], b4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 32;
+          if (i < p.push_vec_per_part) { a[u] = ks[i]; b4[u] = vs[i]; }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 32;
+          if (i < p.push_vec_per_part) { kd[i] = a[u]; vd[i] = b4[u]; }
+        }
+      }
+      __threadfence_system();       // every lane's stores, then one release increment for the piece
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_ready_peers[consumer] + global_block), "r"(1u)
+                     : "memory");
+    }
   }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
@@ -787,6 +844,28 @@ cudaError_t launch_attention_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.ready = a.ready;
   p.ready_target = a.ready_target;
   p.status = a.status;
+  p.push_k = nullptr;
+  if (a.push_k != nullptr) {
+    // the gather warps live in the two-heads-per-CTA kernel; a piece is a whole number of 16-byte words
+    if (a.heads_per_work != 2 || a.ready == nullptr || !a.push_v || !a.push_k_peers || !a.push_v_peers ||
+        !a.push_ready_peers || !a.push_ticket || a.push_parts < 1 || a.push_world < 1 || a.push_rank < 0 ||
+        a.push_rank >= a.push_world || a.push_chunk_blocks < 0 || a.push_block_bytes <= 0 ||
+        a.push_block_bytes % (16 * a.push_parts))
+      return cudaErrorInvalidValue;
+    cudaError_t merr = cudaMemsetAsync(a.push_ticket, 0, sizeof(unsigned), stream);
+    if (merr != cudaSuccess) return merr;
+    p.push_k = static_cast<const uint4*>(a.push_k);
+    p.push_v = static_cast<const uint4*>(a.push_v);
+    p.push_k_peers = reinterpret_cast<uint4* const*>(a.push_k_peers);
+    p.push_v_peers = reinterpret_cast<uint4* const*>(a.push_v_peers);
+    p.push_ready_peers = a.push_ready_peers;
+    p.push_ticket = a.push_ticket;
+    p.push_chunk_blocks = a.push_chunk_blocks;
+    p.push_parts = a.push_parts;
+    p.push_vec_per_part = static_cast<int>((a.push_block_bytes / a.push_parts) >> 4);
+    p.push_rank = a.push_rank;
+    p.push_world = a.push_world;
+  }
   int grid = a.num_sms < a.num_work ? a.num_sms : a.num_work;
   cudaError_t err;
   p.window = a.window;

@@ -33,6 +33,17 @@ struct AttnParams {
   unsigned ready_target;
   const unsigned* ready;  // per 128-key block readiness counters (context parallel), or null
   Status* status;
+  // context parallel, K/V exchange inside this launch (null push_k: the blocks are pushed by a launch
+  // in front of this one, or are local). Warps 2 and 3 of every CTA take tickets; a ticket is one of
+  // push_parts pieces of one 128-token K/V block for one consumer rank, copied with 16-byte stores
+  // and counted into that rank's ready[block] with a system-scope release.
+  const uint4* push_k;
+  const uint4* push_v;
+  uint4* const* push_k_peers;
+  uint4* const* push_v_peers;
+  unsigned* const* push_ready_peers;
+  unsigned* push_ticket;      // zeroed before the launch
+  int push_chunk_blocks, push_vec_per_part, push_parts, push_rank, push_world;
 };
 
 struct AttnArgs {
@@ -54,6 +65,15 @@ struct AttnArgs {
   unsigned ready_target;
   int num_sms;
   Status* status;
+  // in-kernel K/V push (all null / 0 = off); see AttnParams
+  const void* push_k = nullptr;
+  const void* push_v = nullptr;
+  void* const* push_k_peers = nullptr;
+  void* const* push_v_peers = nullptr;
+  unsigned* const* push_ready_peers = nullptr;
+  unsigned* push_ticket = nullptr;
+  int push_chunk_blocks = 0, push_parts = 0, push_rank = 0, push_world = 0;
+  int64_t push_block_bytes = 0;
 };
 
 cudaError_t launch_attention_fwd(const AttnArgs& a, cudaStream_t stream);

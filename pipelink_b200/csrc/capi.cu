@@ -711,10 +711,10 @@ int plb_ep_gather_rows(const void* const* src_peers, const int32_t* peer_rank, c
                                               static_cast<cudaStream_t>(stream)));
 }
 
-int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
-                      const plb_attn_work* work, int num_work, int heads_per_work, int q_heads, int kv_heads, int seq_q,
-                      uint64_t q_rows, uint64_t kv_rows, float scale, int window, float softcap, const uint32_t* ready,
-                      uint32_t ready_target, plb_status* status, void* stream) {
+static int attention_impl(const void* q, const void* k, const void* v, void* out, float* lse,
+                          const plb_attn_work* work, int num_work, int heads_per_work, int q_heads, int kv_heads, int seq_q,
+                          uint64_t q_rows, uint64_t kv_rows, float scale, int window, float softcap, const uint32_t* ready,
+                          uint32_t ready_target, plb::AttnArgs& a, plb_status* status, void* stream) {
   static_assert(sizeof(plb_attn_work) == sizeof(plb::AttnWork), "work descriptor layouts differ");
   if (!q || !k || !v || !out || !lse || !work || !status || num_work < 0) return PLB_E_ARGUMENT;
   if (q_heads < 1 || kv_heads < 1 || q_heads % kv_heads || seq_q < 128 || seq_q % 128 ||
@@ -722,7 +722,6 @@ int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, fl
     return PLB_E_ARGUMENT;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return PLB_E_ARGUMENT;
   if (heads_per_work != 1 && !(heads_per_work == 2 && (q_heads / kv_heads) % 2 == 0)) return PLB_E_ARGUMENT;
-  plb::AttnArgs a;
   a.heads_per_work = heads_per_work;
   a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
   a.work = reinterpret_cast<const plb::AttnWork*>(work);
@@ -738,6 +737,37 @@ int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, fl
   a.status = reinterpret_cast<plb::Status*>(status);
   if (a.num_sms <= 0) return PLB_E_CUDA;
   return from_cuda(plb::launch_attention_fwd(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
+                      const plb_attn_work* work, int num_work, int heads_per_work, int q_heads, int kv_heads, int seq_q,
+                      uint64_t q_rows, uint64_t kv_rows, float scale, int window, float softcap, const uint32_t* ready,
+                      uint32_t ready_target, plb_status* status, void* stream) {
+  plb::AttnArgs a;
+  return attention_impl(q, k, v, out, lse, work, num_work, heads_per_work, q_heads, kv_heads, seq_q, q_rows, kv_rows, scale,
+                        window, softcap, ready, ready_target, a, status, stream);
+}
+
+int plb_attention_fwd_cp(const void* q, const void* k_gather, const void* v_gather, void* out, float* lse,
+                         const plb_attn_work* work, int num_work, int q_heads, int kv_heads, int seq_q, uint64_t q_rows,
+                         uint64_t kv_rows, float scale, const uint32_t* ready, uint32_t ready_target, const void* k_local,
+                         const void* v_local, int chunk_blocks, int64_t block_bytes, int parts, int rank, int world,
+                         void* const* k_gather_peers, void* const* v_gather_peers, void* const* ready_peers,
+                         void* ticket_u32, plb_status* status, void* stream) {
+  if (!ready || !k_local || !v_local || !k_gather_peers || !v_gather_peers || !ready_peers || !ticket_u32)
+    return PLB_E_ARGUMENT;
+  if (chunk_blocks < 0 || block_bytes <= 0 || parts < 1 || block_bytes % (16 * parts) || world < 1 || world > 32 ||
+      rank < 0 || rank >= world || (q_heads / (kv_heads > 0 ? kv_heads : 1)) % 2)
+    return PLB_E_ARGUMENT;
+  plb::AttnArgs a;
+  a.push_k = k_local; a.push_v = v_local;
+  a.push_k_peers = k_gather_peers; a.push_v_peers = v_gather_peers;
+  a.push_ready_peers = reinterpret_cast<unsigned* const*>(ready_peers);
+  a.push_ticket = static_cast<unsigned*>(ticket_u32);
+  a.push_chunk_blocks = chunk_blocks; a.push_parts = parts; a.push_rank = rank; a.push_world = world;
+  a.push_block_bytes = block_bytes;
+  return attention_impl(q, k_gather, v_gather, out, lse, work, num_work, 2, q_heads, kv_heads, seq_q, q_rows, kv_rows, scale, 0,
+                        0.0f, ready, ready_target, a, status, stream);
 }
 
 int plb_cp_push_kv(const void* k_local, const void* v_local, int chunk_blocks, int64_t block_bytes,

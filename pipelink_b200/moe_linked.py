@@ -29,7 +29,7 @@ COMPOSITIONS = ("gate_up", "gate_up_dispatch", "down")
 
 
 def ensure_built() -> Path:
-    if not all((OUT_DIR / c / "pipeline.cubin").exists() for c in COMPOSITIONS):
+    if not all((OUT_DIR / c / f).exists() for c in COMPOSITIONS for f in ("pipeline.cubin", "one_tu.cubin")):
         from .stages.moe import build
         build.build(OUT_DIR)
     return OUT_DIR
@@ -52,12 +52,14 @@ def _scale_map(t: torch.Tensor) -> bytes:
 
 
 class LinkedMoE:
-    def __init__(self, host: mok.MoKHost, out_dir=None):
+    def __init__(self, host: mok.MoKHost, out_dir=None, image: str = "pipeline.cubin"):
+        """image: "pipeline.cubin" (the linked image) or "one_tu.cubin" (the same sources compiled as
+        one translation unit: the control a linked image is timed against)."""
         if host.precision != "mxfp8":
             raise ValueError("the linked images are the MXFP8 GEMMs")
         self.host = host
         out = Path(out_dir or ensure_built())
-        self.sessions = {c: Session(out / c) for c in COMPOSITIONS}
+        self.sessions = {c: Session(out / c, image) for c in COMPOSITIONS}
         slots = self.sessions["gate_up_dispatch"].link["bindings"]
         self.rows_ready_slot, self.ticket_slot = slots["pipelink_moe_rows_ready"][0], slots["pipelink_moe_ticket"][0]
         # the images' counter workspace (gmem_counter domain): zeroed on the stream before a launch that uses it

@@ -22,7 +22,9 @@ import json
 import re
 from pathlib import Path
 
-from ...pipec2 import link as linker, pack as packer
+import subprocess
+
+from ...pipec2 import jitlink, link as linker, pack as packer
 
 HERE = Path(__file__).resolve().parent
 TILE, SF = 128 * 128, 512
@@ -204,8 +206,11 @@ def write_manifests():
         (HERE / f"{name}.manifest.json").write_text(json.dumps(m, indent=1, sort_keys=True) + "\n")
 
 
-def build(out: Path, depth=None, device_link=True):
-    """-> {composition: LinkResult}; images at out/<composition>/pipeline.cubin."""
+def build(out: Path, depth=None, device_link=True, one_tu=True):
+    """-> {composition: LinkResult}; images at out/<composition>/pipeline.cubin. With one_tu, also
+    out/<composition>/one_tu.cubin: the same stage sources, generated stub and dispatch compiled as
+    ONE translation unit by nvcc, the control a linked image is timed against (the reference's gate:
+    a linked build within 1 % of the single-unit build of the same sources)."""
     out.mkdir(parents=True, exist_ok=True)
     write_manifests()
     for name in MANIFESTS:
@@ -216,6 +221,15 @@ def build(out: Path, depth=None, device_link=True):
         spec = out / f"{comp}.pipeline.json"
         spec.write_text(json.dumps(pipeline_spec(comp, members, stages, depth), indent=1))
         results[comp] = linker.link(spec, out / comp, device_link=device_link)
+        if one_tu and device_link:
+            tu = out / comp / "generated" / "one_tu.cu"
+            tu.write_text("".join(f'#include "{HERE / (m + ".cu")}"\n' for m in members) +
+                          '#include "binding_stub.cu"\n#include "dispatch.cu"\n')
+            cmd = [jitlink.nvcc(), "-cubin", "-O3", "-std=c++17", "--expt-relaxed-constexpr", "-gencode",
+                   "arch=compute_100a,code=sm_100a", "-I", str(tu.parent), "-o", str(out / comp / "one_tu.cubin"), str(tu)]
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            if proc.returncode != 0:
+                raise RuntimeError("one-TU control failed:\n" + proc.stderr[-3000:])
     return results
 
 

@@ -10,7 +10,7 @@
 
 extern "C" __device__ void moe_comm_dispatch_role(const void* raw_params, unsigned) {
   using namespace moe;
-  const MoeCommParams& p = *static_cast<const MoeCommParams*>(raw_params);
+  const MoeCommParams p = *static_cast<const MoeCommParams*>(raw_params);   // a copy in registers
   extern __shared__ __align__(1024) unsigned char pl_smem[];
   const int lane = threadIdx.x & 31;
   const int warp = static_cast<int>(threadIdx.x >> 5) - pipelink_moe_warp_comm();

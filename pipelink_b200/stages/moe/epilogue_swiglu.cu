@@ -10,7 +10,7 @@
 
 extern "C" __device__ void moe_epilogue_swiglu_mxfp8_role(const void* raw_params, unsigned) {
   using namespace moe;
-  const MoeSwigluParams& p = *static_cast<const MoeSwigluParams*>(raw_params);
+  const MoeSwigluParams p = *static_cast<const MoeSwigluParams*>(raw_params);   // a copy in registers
   extern __shared__ __align__(1024) unsigned char pl_smem[];
   const uint32_t smem = plb::smem_u32(pl_smem);
   const int lane = threadIdx.x & 31;

@@ -8,9 +8,13 @@
 extern "C" __device__ void moe_load_role(const void* raw_params, unsigned) {
   using namespace moe;
   const MoeLoadParams& p = *static_cast<const MoeLoadParams*>(raw_params);
+  // the scalars are read once into registers: through the pointer the compiler would have to fetch
+  // them from the parameter block again after every barrier operation of the K loop
+  const MoeGeometry g = p.g;
+  const unsigned* const counters = p.counters;
   extern __shared__ __align__(1024) unsigned char pl_smem[];
   const int lane = threadIdx.x & 31;
-  const Walk w = make_walk(p.g, lane, blockIdx.x == 0);
+  const Walk w = make_walk(g, lane, blockIdx.x == 0);
   if (lane != 0) return;
   const uint32_t smem = plb::smem_u32(pl_smem);
   const uint32_t cta_rank = plb::cluster_ctarank();
@@ -24,16 +28,16 @@ extern "C" __device__ void moe_load_role(const void* raw_params, unsigned) {
   uint32_t phase = 0;
   bool ok = true;
   for (int tile = pair_id; tile < w.total_tiles && ok; tile += num_pairs) {
-    const Tile t = decode(p.g, w, tile, static_cast<int>(cta_rank));
+    const Tile t = decode(g, w, tile, static_cast<int>(cta_rank));
     const int b_blk = t.b_blk0 + static_cast<int>(cta_rank);
-    if (p.counters != nullptr) {
+    if (counters != nullptr) {
       // rows pulled by the comm owner are usable once their tile's count is complete; then order
       // the TMA reads after the count was observed
-      const unsigned* flag = p.counters + pipelink_moe_rows_ready() + (t.a_blk >> 1);
+      const unsigned* flag = counters + pipelink_moe_rows_ready() + (t.a_blk >> 1);
       const long long t0 = clock64();
       while (plb::ld_acquire_gpu_u32(flag) < 256u) {
-        if (clock64() - t0 > plb::kWaitBudgetCycles / 2 || plb::ld_volatile_i32(&p.g.status->code) != 0) {
-          plb::report_failure(p.g.status, plb::ST_TIMEOUT_COUNTER, 311, plb::ld_acquire_gpu_u32(flag), 256u);
+        if (clock64() - t0 > plb::kWaitBudgetCycles / 2 || plb::ld_volatile_i32(&g.status->code) != 0) {
+          plb::report_failure(g.status, plb::ST_TIMEOUT_COUNTER, 311, plb::ld_acquire_gpu_u32(flag), 256u);
           ok = false;
           break;
         }
@@ -41,8 +45,8 @@ extern "C" __device__ void moe_load_role(const void* raw_params, unsigned) {
       if (!ok) break;
       asm volatile("fence.proxy.async.global;" ::: "memory");
     }
-    for (int kb = 0; kb < p.g.k_steps; ++kb) {
-      if (!plb::mbar_wait(bar(smem, pipelink_moe_empty(), stage), phase ^ 1u, p.g.status, plb::ST_TIMEOUT_EMPTY, stage)) {
+    for (int kb = 0; kb < g.k_steps; ++kb) {
+      if (!plb::mbar_wait(bar(smem, pipelink_moe_empty(), stage), phase ^ 1u, g.status, plb::ST_TIMEOUT_EMPTY, stage)) {
         ok = false;
         break;
       }
@@ -51,9 +55,9 @@ extern "C" __device__ void moe_load_role(const void* raw_params, unsigned) {
       const uint32_t slot = smem + pipelink_moe_operands() + stage * SlotBytes;
       plb::tma_load_2d_pair(slot + OffA, &p.a, full, kb * 128, t.a_blk * 128);
       plb::tma_load_2d_pair(slot + OffB, &p.b, full, kb * 128, b_blk * 128);
-      plb::tma_load_2d_pair(slot + OffSf, &p.sfa, full, 0, t.a_blk * p.g.k_steps + kb);
-      plb::tma_load_2d_pair(slot + OffSf + SfBytes, &p.sfb, full, 0, t.b_blk0 * p.g.k_steps + kb);
-      plb::tma_load_2d_pair(slot + OffSf + 2 * SfBytes, &p.sfb, full, 0, (t.b_blk0 + 1) * p.g.k_steps + kb);
+      plb::tma_load_2d_pair(slot + OffSf, &p.sfa, full, 0, t.a_blk * g.k_steps + kb);
+      plb::tma_load_2d_pair(slot + OffSf + SfBytes, &p.sfb, full, 0, t.b_blk0 * g.k_steps + kb);
+      plb::tma_load_2d_pair(slot + OffSf + 2 * SfBytes, &p.sfb, full, 0, (t.b_blk0 + 1) * g.k_steps + kb);
       if (++stage == depth) { stage = 0; phase ^= 1u; }
     }
   }

@@ -7,10 +7,11 @@
 
 extern "C" __device__ void moe_mma_role(const void* raw_params, unsigned) {
   using namespace moe;
-  const MoeMmaParams& p = *static_cast<const MoeMmaParams*>(raw_params);
+  // read once into registers (see moe.load): the issue loop must not go back to the parameter block
+  const MoeGeometry g = static_cast<const MoeMmaParams*>(raw_params)->g;
   extern __shared__ __align__(1024) unsigned char pl_smem[];
   const int lane = threadIdx.x & 31;
-  const Walk w = make_walk(p.g, lane, false);
+  const Walk w = make_walk(g, lane, false);
   if (lane != 0 || plb::cluster_ctarank() != 0) return;
   const uint32_t smem = plb::smem_u32(pl_smem);
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(pl_smem + pipelink_tmem_slot());
@@ -24,13 +25,13 @@ extern "C" __device__ void moe_mma_role(const void* raw_params, unsigned) {
   uint32_t phase = 0, acc_phase = 0;
   bool ok = true;
   for (int tile = pair_id; tile < w.total_tiles && ok; tile += num_pairs) {
-    if (!plb::mbar_wait(bar(smem, pipelink_moe_acc_empty()), acc_phase ^ 1u, p.g.status, plb::ST_TIMEOUT_TMEM_EMPTY, 0)) {
+    if (!plb::mbar_wait(bar(smem, pipelink_moe_acc_empty()), acc_phase ^ 1u, g.status, plb::ST_TIMEOUT_TMEM_EMPTY, 0)) {
       ok = false;
       break;
     }
     plb::tc_fence_after();
-    for (int kb = 0; kb < p.g.k_steps; ++kb) {
-      if (!plb::mbar_wait(bar(smem, pipelink_moe_full(), stage), phase, p.g.status, plb::ST_TIMEOUT_FULL, stage)) {
+    for (int kb = 0; kb < g.k_steps; ++kb) {
+      if (!plb::mbar_wait(bar(smem, pipelink_moe_full(), stage), phase, g.status, plb::ST_TIMEOUT_FULL, stage)) {
         ok = false;
         break;
       }

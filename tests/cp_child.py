@@ -23,15 +23,18 @@ def main():
     full_o, full_lse = att.attention_fwd(q[None], k[None], v[None])
     layout = att.CpRank.slab_layout(S, Hkv)
     slab = ep.IpcSlab(layout["nbytes"], rank, world)
-    r = att.CpRank(S, Hq, Hkv, rank, world, slab.ptrs, layout, dev)
     pos = torch.from_numpy(oa.zigzag_rows(S, world, rank)).to(dev)
-    for step in range(3):
-        o, lse = r.step(att.shard_zigzag(q, world, rank), att.shard_zigzag(k, world, rank), att.shard_zigzag(v, world, rank))
+    # the K/V exchange as a launch in front of the attention kernel, then inside it (gather warps)
+    for fused in (False, True):
+        r = att.CpRank(S, Hq, Hkv, rank, world, slab.ptrs, layout, dev, fused_push=fused)
+        for step in range(3):
+            o, lse = r.step(att.shard_zigzag(q, world, rank), att.shard_zigzag(k, world, rank), att.shard_zigzag(v, world, rank))
+            torch.cuda.synchronize()
+            r.status.check(f"cp step {step} (fused push: {fused})")
+            assert torch.equal(o.view(torch.int16), full_o[0][pos].view(torch.int16)), (rank, step, fused)
+            assert torch.equal(lse, full_lse[:, pos]), (rank, step, fused)
         torch.cuda.synchronize()
-        r.status.check(f"cp step {step}")
-        assert torch.equal(o.view(torch.int16), full_o[0][pos].view(torch.int16)), (rank, step)
-        assert torch.equal(lse, full_lse[:, pos]), (rank, step)
-    dist.barrier()
+        dist.barrier()
     slab.close()
     dist.destroy_process_group()
     if rank == 0:

@@ -121,6 +121,35 @@ def test_context_parallel_matches_single_gpu(native_lib, world, S):
             _lib.call("plb_sym_free", p)
 
 
+@pytest.mark.parametrize("S,Hq,Hkv", [(2048, 8, 2), (8192, 8, 4)])
+def test_kv_exchange_inside_the_attention_launch_single_rank(native_lib, S, Hq, Hkv):
+    """The gather warps of the attention kernel on a group of one: every K/V block this rank owns goes
+    from its local tensors into its own gathered buffers in pieces, counted per block, while the same
+    launch's load lanes wait for those counts. All CTAs of the launch are resident at once and the
+    gather warps wait for nothing, so one GPU can run it (ranks emulated as separate launches could
+    not: an earlier launch would wait for a later one). Result: the plain kernel's, bit for bit."""
+    from pipelink_b200 import _lib, attention as att, ep
+    (q, k, v), (dq, dk, dv) = _inputs(S, Hq, Hkv, case=3)
+    full_o, full_lse = att.attention_fwd(dq[None], dk[None], dv[None])
+    torch.cuda.synchronize()
+    layout = att.CpRank.slab_layout(S, Hkv)
+    slab = ep.sym_alloc(layout["nbytes"])
+    try:
+        rnk = att.CpRank(S, Hq, Hkv, 0, 1, [slab], layout, "cuda", fused_push=True)
+        rnk.k_gather.fill_(float("nan"))
+        rnk.v_gather.fill_(float("nan"))
+        for step in range(3):
+            o, lse = rnk.step(dq, dk, dv, distributed=False)
+            torch.cuda.synchronize()
+            rnk.status.check(f"fused push, step {step}")
+            assert torch.equal(o.view(torch.int16), full_o[0].view(torch.int16)), step
+            assert torch.equal(lse, full_lse), step
+            assert (rnk.ready.cpu().numpy() == (step + 1) * att.CpRank.PARTS).all()
+    finally:
+        torch.cuda.synchronize()
+        _lib.call("plb_sym_free", slab)
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_context_parallel_real_gpus(world):
     from tests.ranks import gpu_count, run_ranks
