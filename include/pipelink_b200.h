@@ -335,6 +335,27 @@ int plb_moe_gemm_down_bf16(const void* hidden_bf16, const void* w2_bf16, const i
                            int64_t capacity, int experts, int inter, int hidden, int tile_rotation,
                            void* combine_bf16, void* const* combine_peers, plb_status* status, void* stream);
 
+/* The backward and recompute cells of the bf16 routed precision (campaigns/mok/README.md:86-104: the
+ * bf16 value of pipelink_mok_precision under the bwd and rec passes; same pass structure as the
+ * MXFP8 cells, campaigns/mok/port/gemm/gemm.cu:166-243, with no quantisation anywhere).
+ * plb_moe_gemm_gate_up_bf16_train: plb_moe_gemm_gate_up_bf16 that also keeps the bf16 gate and up
+ *   rows [capacity, inter] the activation backward differentiates through.
+ * plb_moe_gemm_wgrad_bf16: plb_moe_gemm_wgrad on bf16 operands: a_t [m_rows, capacity] and b_t
+ *   [n_rows, capacity] are the TRANSPOSES of the row-major activations (plb_bf16_transpose), the
+ *   contraction runs over each expert's rows of the schedule, out is bf16 [experts, m_rows, n_rows].
+ * plb_moe_swiglu_bwd_bf16: plb_moe_swiglu_bwd with bf16 gate / up inputs.
+ * The data gradients are plb_moe_gemm_down_bf16 calls on the transposed weights (a reshape on the
+ * host at weight load). */
+int plb_moe_gemm_gate_up_bf16_train(const void* x_routed_bf16, const void* w13_bf16, const int32_t* block_expert,
+                                    const int32_t* num_tokens, int64_t capacity, int experts, int inter, int hidden,
+                                    void* hidden_bf16, void* gate_bf16, void* up_bf16, plb_status* status, void* stream);
+int plb_moe_gemm_wgrad_bf16(const void* a_t_bf16, const void* b_t_bf16, const int32_t* expert_offsets, int64_t capacity,
+                            int experts, int m_rows, int n_rows, void* d_w_bf16, plb_status* status, void* stream);
+int plb_moe_swiglu_bwd_bf16(const void* gate_bf16, const void* up_bf16, const void* d_hidden_bf16,
+                            const int32_t* num_tokens, int64_t capacity, int inter, void* d_gate_up_bf16, void* stream);
+/* dst [cols, rows] = src [rows, cols]^T, bf16, rows and cols multiples of 64. */
+int plb_bf16_transpose(const void* src_bf16, int64_t rows, int64_t cols, void* dst_bf16, void* stream);
+
 /* ops.fwd_epilogue (campaigns/mok/host/mok_port_host.py:204):
  * out[t] = y_shared[t] + sum_j router_weights[t, j] * combine[t * topk + j], j ascending,
  * fp32, every operation rounded separately. y_shared may be NULL. */

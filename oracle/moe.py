@@ -149,7 +149,8 @@ def forward_single_rank(x, routes, router_w, weights, padding=128, capacity=None
     return dict(schedule=sched, x_routed=(xq, xsc), hidden=(hq, hsc), y=y, combine=buf, output=out)
 
 
-def forward_single_rank_bf16(x, routes, router_w, w_gate, w_up, w_down, padding=128, capacity=None, limit=0.0):
+def forward_single_rank_bf16(x, routes, router_w, w_gate, w_up, w_down, padding=128, capacity=None, limit=0.0,
+                             context=None):
     """Forward with the bf16 routed precision (the reference's second precision value,
     campaigns/mok/port/act/act.cu:246-249): no quantisation on the routed path; gate / up and the
     hidden rows are rounded to bf16 where the reference's bf16 tensors hold them
@@ -166,13 +167,17 @@ def forward_single_rank_bf16(x, routes, router_w, w_gate, w_up, w_down, padding=
     rows = np.zeros((total, H), np.float32)
     rows[pr >= 0] = x[pt[pr >= 0]]
     hidden = np.zeros((total, I), np.float32)
+    gate_all, up_all = np.zeros((total, I), np.float32), np.zeros((total, I), np.float32)
     y = np.zeros((total, H), np.float32)
     for e in range(E):
         lo, hi = int(off[e]), int(off[e + 1])
         if hi > lo:
             g, u = mxfp8.bf16_round(_mm(rows[lo:hi], w_gate[e])), mxfp8.bf16_round(_mm(rows[lo:hi], w_up[e]))
+            gate_all[lo:hi], up_all[lo:hi] = g, u
             hidden[lo:hi] = mxfp8.bf16_round(silu_mul(g, u, limit))
             y[lo:hi] = mxfp8.bf16_round(_mm(hidden[lo:hi], w_down[e]))
+    if context is not None:
+        context.update(gate=gate_all, up=up_all, hidden=hidden.copy())
     buf = combine(y, sched, 0, T, k)
     return dict(schedule=sched, x_routed=rows, hidden=hidden, y=y, combine=buf, output=fwd_epilogue(buf, router_w))
 
@@ -310,6 +315,56 @@ def backward_single_rank(x, router_w, w_gate, w_up, w_down, fwd, ctx, d_out, lim
             sel = pr[lo:hi] >= 0
             d_x_buf[dr[lo:hi][sel]] = dxr[sel]
             d_w_cat[e] = mxfp8.bf16_round(_mm(dgu_t[:, lo:hi], x_t[:, lo:hi]))                       # [2I, rows] x [H, rows]^T
+    d_x = fwd_epilogue(d_x_buf, np.ones((T, k), np.float32))
+    return dict(d_x=d_x, d_router_weights=d_router.reshape(T, k), d_w_routed_gate=d_w_cat[:, :I], d_w_routed_up=d_w_cat[:, I:],
+                d_w_routed_down=d_w_down, d_hidden=d_hidden, d_gate_up=dgu, d_y=dy)
+
+
+def backward_single_rank_bf16(x, router_w, w_gate, w_up, w_down, fwd, ctx, d_out, limit=0.0):
+    """Backward of forward_single_rank_bf16 (the bwd / rec cells of the bf16 routed precision,
+    campaigns/mok/README.md:86-104): the pass structure of backward_single_rank
+    (campaigns/mok/port/gemm/gemm.cu:166-243) with no quantisation: every GEMM takes the bf16 tensors
+    themselves, accumulates in fp32 and its result is rounded to bf16 where a bf16 tensor holds it."""
+    sched = fwd["schedule"]
+    total = int(sched["num_tokens"][0])
+    off, pr, pt, dr = sched["expert_offsets"], sched["peer_rank"][:total], sched["peer_token_idx"][:total], sched["dest_row"][:total]
+    T, k = router_w.shape
+    E, I, H = w_gate.shape
+    live = pr >= 0
+    wflat = router_w.reshape(-1).astype(np.float32)
+    dy = np.zeros((total, H), np.float32)
+    dy[live] = mxfp8.bf16_round((wflat[dr[live]][:, None] * d_out[pt[live]]).astype(np.float32))
+    d_router = np.zeros(T * k, np.float32)
+    d_router[dr[live]] = (d_out[pt[live]].astype(np.float64) * fwd["combine"][dr[live]].astype(np.float64)).sum(axis=1)
+    hidden = ctx["hidden"]
+    d_hidden = np.zeros((total, I), np.float32)
+    d_w_down = np.zeros((E, H, I), np.float32)
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            d_hidden[lo:hi] = mxfp8.bf16_round(_mm(dy[lo:hi], w_down[e].T))                 # [rows, H] x [I, H]^T
+            d_w_down[e] = mxfp8.bf16_round(_mm(dy[lo:hi].T, hidden[lo:hi].T))               # [H, rows] x [I, rows]^T
+    g, u = ctx["gate"], ctx["up"]
+    g_open, u_open = np.ones_like(g, dtype=bool), np.ones_like(u, dtype=bool)
+    if limit > 0:
+        lim = np.float32(limit)
+        g_open, u_open = g < lim, (u > -lim) & (u < lim)
+        g, u = np.minimum(g, lim), np.clip(u, -lim, lim)
+    sg = (np.float32(1.0) / (np.float32(1.0) + np.exp(-g))).astype(np.float32)
+    d_up = np.where(u_open, d_hidden * (g * sg), np.float32(0.0))
+    d_gate = np.where(g_open, d_hidden * u * sg * (np.float32(1.0) + g * (np.float32(1.0) - sg)), np.float32(0.0))
+    dgu = mxfp8.bf16_round(np.concatenate([d_gate, d_up], axis=1).astype(np.float32))
+    rows = np.zeros((total, H), np.float32)
+    rows[live] = x[pt[live]]
+    d_x_buf = np.zeros((T * k, H), np.float32)
+    d_w_cat = np.zeros((E, 2 * I, H), np.float32)
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            dxr = mxfp8.bf16_round(_mm(dgu[lo:hi], np.concatenate([w_gate[e], w_up[e]]).T))   # [rows, 2I] x [H, 2I]^T
+            sel = pr[lo:hi] >= 0
+            d_x_buf[dr[lo:hi][sel]] = dxr[sel]
+            d_w_cat[e] = mxfp8.bf16_round(_mm(dgu[lo:hi].T, rows[lo:hi].T))                   # [2I, rows] x [H, rows]^T
     d_x = fwd_epilogue(d_x_buf, np.ones((T, k), np.float32))
     return dict(d_x=d_x, d_router_weights=d_router.reshape(T, k), d_w_routed_gate=d_w_cat[:, :I], d_w_routed_up=d_w_cat[:, I:],
                 d_w_routed_down=d_w_down, d_hidden=d_hidden, d_gate_up=dgu, d_y=dy)

@@ -163,6 +163,66 @@ ep_bwd_dy_kernel(const uint4* const* __restrict__ d_out_peers, const float* cons
   }
 }
 
+// bf16 routed precision: the saved gate / up are bf16 rows, everything else as above.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_bf16_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, const uint4* __restrict__ d_hidden,
+                       const int* __restrict__ num_rows_dev, int64_t capacity, int inter, float limit,
+                       uint4* __restrict__ dgu) {
+  int64_t rows = *num_rows_dev;
+  if (rows > capacity) rows = capacity;
+  const int vecs = inter >> 3;
+  const int64_t total = rows * vecs;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total; v += stride) {
+    const int64_t r = v / vecs, j = v - r * vecs;
+    const uint4 gq = gate[v], uq = up[v], dh = d_hidden[v];
+    const float gf[8] = {lo16(gq.x), hi16(gq.x), lo16(gq.y), hi16(gq.y), lo16(gq.z), hi16(gq.z), lo16(gq.w), hi16(gq.w)};
+    const float uf[8] = {lo16(uq.x), hi16(uq.x), lo16(uq.y), hi16(uq.y), lo16(uq.z), hi16(uq.z), lo16(uq.w), hi16(uq.w)};
+    const float dhf[8] = {lo16(dh.x), hi16(dh.x), lo16(dh.y), hi16(dh.y), lo16(dh.z), hi16(dh.z), lo16(dh.w), hi16(dh.w)};
+    float dg[8], du[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool g_open = gf[i] < limit, u_open = uf[i] > -limit && uf[i] < limit;
+      const float g = fminf(gf[i], limit), u = fminf(fmaxf(uf[i], -limit), limit);
+      const float sg = 1.0f / (1.0f + __expf(-g));
+      du[i] = u_open ? dhf[i] * (g * sg) : 0.0f;
+      dg[i] = g_open ? dhf[i] * u * sg * (1.0f + g * (1.0f - sg)) : 0.0f;
+    }
+    uint4 og, ou;
+    og.x = pack2(dg[0], dg[1]); og.y = pack2(dg[2], dg[3]); og.z = pack2(dg[4], dg[5]); og.w = pack2(dg[6], dg[7]);
+    ou.x = pack2(du[0], du[1]); ou.y = pack2(du[2], du[3]); ou.z = pack2(du[4], du[5]); ou.w = pack2(du[6], du[7]);
+    dgu[r * (2 * vecs) + j] = og;
+    dgu[r * (2 * vecs) + vecs + j] = ou;
+  }
+}
+
+// out[c, r] = in[r, c] for a bf16 [rows, cols] tensor (both multiples of 64): 64 x 64 tiles through
+// shared memory, 128-byte segments on both sides. The bf16 weight-gradient GEMMs contract over the
+// schedule rows, so their operands are the transposes of the row-major activations.
+__global__ void __launch_bounds__(256)
+transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, int64_t rows, int64_t cols, __nv_bfloat16* __restrict__ out) {
+  __shared__ __nv_bfloat16 tile[64][66];
+  const int64_t tiles_c = cols >> 6, total = (rows >> 6) * tiles_c;
+  for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const int64_t r0 = (t / tiles_c) << 6, c0 = (t % tiles_c) << 6;
+    for (int i = threadIdx.x; i < 64 * 32; i += 256) {       // 32 pairs per row
+      const int r = i >> 5, c2 = (i & 31) << 1;
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(in + (r0 + r) * cols + c0 + c2);
+      tile[r][c2] = v.x;
+      tile[r][c2 + 1] = v.y;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 32; i += 256) {
+      const int c = i >> 5, r2 = (i & 31) << 1;
+      __nv_bfloat162 v;
+      v.x = tile[r2][c];
+      v.y = tile[r2 + 1][c];
+      *reinterpret_cast<__nv_bfloat162*>(out + (c0 + c) * rows + r0 + r2) = v;
+    }
+    __syncthreads();
+  }
+}
+
 // d_router_w[t * topk + j] = <d_out[t], combine[t * topk + j]>: one warp per (token, slot), the
 // same lane partition, fma order and shuffle tree as bwd_dy_kernel, so both give the same bits.
 __global__ void __launch_bounds__(256)
@@ -273,6 +333,22 @@ cudaError_t launch_ep_bwd_dy(const void* const* d_out_peers, const float* const*
   ep_bwd_dy_kernel<<<sm_grid(8), 256, 0, stream>>>(reinterpret_cast<const uint4* const*>(d_out_peers), router_w_peers,
                                                    peer_rank, peer_token_idx, dest_row, num_rows_dev, capacity, hidden,
                                                    static_cast<uint4*>(dy));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_bwd_bf16(const void* gate, const void* up, const void* d_hidden, const int* num_rows_dev,
+                                   int64_t capacity, int inter, float limit, void* dgu, cudaStream_t stream) {
+  if (capacity == 0) return cudaSuccess;
+  swiglu_bwd_bf16_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const uint4*>(gate), static_cast<const uint4*>(up),
+                                                         static_cast<const uint4*>(d_hidden), num_rows_dev, capacity, inter,
+                                                         limit > 0.0f ? limit : HUGE_VALF, static_cast<uint4*>(dgu));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_transpose_bf16(const void* in, int64_t rows, int64_t cols, void* out, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return cudaSuccess;
+  transpose_bf16_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), rows, cols,
+                                                        static_cast<__nv_bfloat16*>(out));
   return cudaGetLastError();
 }
 

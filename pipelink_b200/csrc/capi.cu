@@ -516,6 +516,61 @@ int plb_moe_gemm_gate_up_bf16(const void* x_routed_bf16, const void* w13_bf16, c
   return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
 }
 
+int plb_moe_gemm_gate_up_bf16_train(const void* x_routed_bf16, const void* w13_bf16, const int32_t* block_expert,
+                                    const int32_t* num_tokens, int64_t capacity, int experts, int inter, int hidden,
+                                    void* hidden_bf16, void* gate_bf16, void* up_bf16, plb_status* status, void* stream) {
+  if (capacity < 0 || capacity % 256 || experts < 1 || inter < 128 || inter % 128 || hidden < 128 || hidden % 128)
+    return PLB_E_ARGUMENT;
+  if (!x_routed_bf16 || !w13_bf16 || !block_expert || !num_tokens || !hidden_bf16 || !gate_bf16 || !up_bf16 || !status)
+    return PLB_E_ARGUMENT;
+  if (!aligned16(x_routed_bf16) || !aligned16(w13_bf16) || !aligned16(hidden_bf16) || !aligned16(gate_bf16) ||
+      !aligned16(up_bf16))
+    return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.bf16 = true;
+  a.a_fp8 = x_routed_bf16; a.a_sc = nullptr; a.b_fp8 = w13_bf16; a.b_sc = nullptr;
+  a.rows_capacity = capacity; a.experts = experts; a.n_rows = 2 * inter; a.K = hidden;
+  a.block_expert = block_expert; a.num_rows_dev = num_tokens; a.mode = 0;
+  a.out = hidden_bf16; a.out_sc = nullptr; a.dest_row = nullptr;
+  a.save_gate = gate_bf16; a.save_up = up_bf16;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(run_gemm(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_gemm_wgrad_bf16(const void* a_t_bf16, const void* b_t_bf16, const int32_t* expert_offsets, int64_t capacity,
+                            int experts, int m_rows, int n_rows, void* d_w_bf16, plb_status* status, void* stream) {
+  if (capacity < 0 || capacity % 256 || experts < 1 || m_rows < 256 || m_rows % 256 || n_rows < 256 || n_rows % 256)
+    return PLB_E_ARGUMENT;
+  if (!a_t_bf16 || !b_t_bf16 || !expert_offsets || !d_w_bf16 || !status) return PLB_E_ARGUMENT;
+  if (!aligned16(a_t_bf16) || !aligned16(b_t_bf16) || !aligned16(d_w_bf16)) return PLB_E_ARGUMENT;
+  plb::GroupedGemmArgs a;
+  a.bf16 = true;
+  a.a_fp8 = a_t_bf16; a.a_sc = nullptr; a.b_fp8 = b_t_bf16; a.b_sc = nullptr;
+  a.rows_capacity = capacity; a.experts = experts; a.n_rows = n_rows; a.m_rows = m_rows; a.K = 0;
+  a.block_expert = nullptr; a.num_rows_dev = nullptr; a.mode = 2;
+  a.out = d_w_bf16; a.out_sc = nullptr; a.dest_row = nullptr;
+  a.expert_offsets = expert_offsets;
+  a.num_sms = sm_count();
+  a.status = reinterpret_cast<plb::Status*>(status);
+  if (a.num_sms <= 0) return PLB_E_CUDA;
+  return from_cuda(plb::launch_grouped_gemm_pair(a, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_moe_swiglu_bwd_bf16(const void* gate_bf16, const void* up_bf16, const void* d_hidden_bf16,
+                            const int32_t* num_tokens, int64_t capacity, int inter, void* d_gate_up_bf16, void* stream) {
+  if (!gate_bf16 || !up_bf16 || !d_hidden_bf16 || !num_tokens || !d_gate_up_bf16 || capacity < 0 || inter <= 0 || inter % 8)
+    return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_swiglu_bwd_bf16(gate_bf16, up_bf16, d_hidden_bf16, num_tokens, capacity, inter,
+                                               g_swiglu_limit, d_gate_up_bf16, static_cast<cudaStream_t>(stream)));
+}
+
+int plb_bf16_transpose(const void* src_bf16, int64_t rows, int64_t cols, void* dst_bf16, void* stream) {
+  if (!src_bf16 || !dst_bf16 || rows < 0 || cols < 0 || rows % 64 || cols % 64) return PLB_E_ARGUMENT;
+  return from_cuda(plb::launch_transpose_bf16(src_bf16, rows, cols, dst_bf16, static_cast<cudaStream_t>(stream)));
+}
+
 int plb_moe_gemm_down_bf16(const void* hidden_bf16, const void* w2_bf16, const int32_t* block_expert,
                            const int32_t* num_tokens, const int32_t* dest_row, const int32_t* peer_rank,
                            int64_t capacity, int experts, int inter, int hidden, int tile_rotation,

@@ -133,7 +133,8 @@ struct Params2 {
   const int* expert_offsets;  // [experts + 1]
   int experts;
   int m_tiles;                // A rows / 256
-  int k_blocks_total;         // contraction length of the whole tensors / 128
+  int k_blocks_total;         // contraction length of the whole tensors in K steps
+  int k_shift;                // log2 of the schedule rows one K step contracts: 7 (128 E4M3) or 6 (64 bf16)
 };
 
 // What one tile means for the loads and the epilogue, identical for every role.
@@ -158,8 +159,8 @@ __device__ __forceinline__ Tile decode_tile(const Params2& p, int tile, int cta_
     t.n_tile = r - m_tile * p.n_tiles;
     t.a_blk = m_tile * 2 + cta_rank;
     t.b_blk0 = t.n_tile * 2;
-    t.k_blk0 = p.expert_offsets[e] >> 7;
-    t.k_steps = (p.expert_offsets[e + 1] - p.expert_offsets[e]) >> 7;
+    t.k_blk0 = p.expert_offsets[e] >> p.k_shift;
+    t.k_steps = (p.expert_offsets[e + 1] - p.expert_offsets[e]) >> p.k_shift;
     t.k_pitch = p.k_blocks_total;
     t.out_row0 = (static_cast<int64_t>(e) * p.m_tiles + m_tile) * 256;
   } else {
@@ -547,6 +548,19 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         PROF_ADD(t_drain, td);
         PROF_T0(tm);
         if (BF16) {
+          if (p.save_gate != nullptr) {
+            // training: the bf16 gate and up values the backward pass differentiates through
+            uint4* gd = reinterpret_cast<uint4*>(p.save_gate + (static_cast<size_t>(row) * p.out_cols + n_tile * 128 + ch * 64) * 2);
+            uint4* ud = reinterpret_cast<uint4*>(p.save_up + (static_cast<size_t>(row) * p.out_cols + n_tile * 128 + ch * 64) * 2);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int i = 8 * c;
+              gd[c] = make_uint4(pack_bf16(g0[i], g0[i + 1]), pack_bf16(g0[i + 2], g0[i + 3]), pack_bf16(g0[i + 4], g0[i + 5]), pack_bf16(g0[i + 6], g0[i + 7]));
+              gd[4 + c] = make_uint4(pack_bf16(g1[i], g1[i + 1]), pack_bf16(g1[i + 2], g1[i + 3]), pack_bf16(g1[i + 4], g1[i + 5]), pack_bf16(g1[i + 6], g1[i + 7]));
+              ud[c] = make_uint4(pack_bf16(u0[i], u0[i + 1]), pack_bf16(u0[i + 2], u0[i + 3]), pack_bf16(u0[i + 4], u0[i + 5]), pack_bf16(u0[i + 6], u0[i + 7]));
+              ud[4 + c] = make_uint4(pack_bf16(u1[i], u1[i + 1]), pack_bf16(u1[i + 2], u1[i + 3]), pack_bf16(u1[i + 4], u1[i + 5]), pack_bf16(u1[i + 6], u1[i + 7]));
+            }
+          }
           // bf16 routed precision: 64 hidden values of this row, 128 contiguous bytes
           uint4* dst = reinterpret_cast<uint4*>(
               p.out + (static_cast<size_t>(row) * p.out_cols + n_tile * 128 + ch * 64) * 2);
@@ -741,7 +755,8 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
   } else if (a.K % 128 || a.K <= 0) {
     return cudaErrorInvalidValue;
   }
-  if (a.bf16 && (a.mode == 2 || a.save_gate != nullptr || a.save_hidden != nullptr)) return cudaErrorInvalidValue;
+  // bf16 training keeps gate and up as bf16 rows (save_gate / save_up); its hidden output is the bf16 value itself
+  if (a.bf16 && (a.save_hidden != nullptr || a.save_gate_sc != nullptr || a.save_up_sc != nullptr)) return cudaErrorInvalidValue;
   if (a.rows_capacity == 0 || a.experts == 0) return cudaSuccess;
   CUtensorMap map_a, map_b, map_sfa, map_sfb;
   memset(&map_sfa, 0, sizeof(map_sfa));
@@ -801,6 +816,7 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
   p.experts = a.experts;
   p.m_tiles = a.mode == 2 ? a.m_rows / 256 : 0;
   p.k_blocks_total = static_cast<int>(k_steps);
+  p.k_shift = a.bf16 ? 6 : 7;
   const int grid = a.num_sms & ~1;
   if (grid < 2) return cudaErrorInvalidValue;
   cudaError_t err;
@@ -817,6 +833,8 @@ cudaError_t launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stre
     PLB_LAUNCH_PAIR(0, false);
   } else if (a.mode == 1) {
     PLB_LAUNCH_PAIR(1, false);
+  } else if (a.bf16) {
+    PLB_LAUNCH_PAIR(2, true);
   } else {
     PLB_LAUNCH_PAIR(2, false);
   }

@@ -444,6 +444,8 @@ class EpMoKHost(mok.MoKHost):
 
     def backward(self, d_out: torch.Tensor, *, check: bool = True):
         """Backward of the last ``forward(train=True)`` of a distributed group."""
+        if self.precision == "bf16":
+            raise ValueError("the backward cells of the bf16 routed precision are single-rank (mok.MoKHost)")
         if not self.group.distributed:
             raise ValueError("ranks of a LocalGroup are stepped together: use backward_local_group()")
         self.d_out_buffer.copy_(d_out)

@@ -147,7 +147,7 @@ class MoKHost:
         # campaigns/mok/README.md:82-84); applied to the library before each activation launch
         self.swiglu_limit = float(swiglu_limit)
         # routed precision of this session (pipelink_mok_precision of the reference's links,
-        # campaigns/mok/README.md:86-93): "bf16" runs both grouped GEMMs on bf16 operands, forward only
+        # campaigns/mok/README.md:86-93): "bf16" runs every grouped GEMM on bf16 operands
         self.precision = precision
         self.pull_variant = "loads"     # dispatch pull: "loads" (16-byte loads per lane) or "bulk" (bulk-copy engine)
         self.device = torch.device(device)
@@ -199,12 +199,16 @@ class MoKHost:
         if tuple(w_gate.shape) != (E, I, H) or tuple(w_up.shape) != (E, I, H) or tuple(w_down.shape) != (E, H, I):
             raise ValueError("weight shapes disagree with the session shape")
         if self.precision == "bf16":
-            if train:
-                raise ValueError("the bf16 routed precision is forward only")
             # per 256 rows of the gate/up operand: 128 gate rows, then the 128 up rows of the same columns
             w13 = torch.stack([w_gate.reshape(E, I // 128, 128, H), w_up.reshape(E, I // 128, 128, H)], dim=2)
             self.weights = dict(w13_bf16=w13.reshape(E, 2 * I, H).to(torch.bfloat16).contiguous(),
                                 w_routed_down_bf16=w_down.to(torch.bfloat16).contiguous())
+            if train:
+                # the data gradients contract with the transposed weights: W_down^T [E, I, H], [W_gate; W_up]^T [E, H, 2I]
+                self.weights.update(
+                    w_down_t_bf16=w_down.to(torch.bfloat16).transpose(1, 2).contiguous(),
+                    w_cat_t_bf16=torch.cat([w_gate, w_up], dim=1).to(torch.bfloat16).transpose(1, 2).contiguous())
+                self._alloc_train_buffers()
             return
         gq, gsc, _, _ = mxfp8_quantize(w_gate.contiguous())
         uq, usc, _, _ = mxfp8_quantize(w_up.contiguous())
@@ -346,6 +350,21 @@ class MoKHost:
         bf = dict(dtype=torch.bfloat16, device=dev)
         sc = lambda r, c: torch.empty((r // 128, c // 128, 32, 16), **u8)
         b = self.buffers
+        if self.precision == "bf16":
+            b.update(gate_routed_bf16=torch.zeros((P, I), **bf), up_routed_bf16=torch.zeros((P, I), **bf),
+                     d_y_routed=torch.zeros((P, H), **bf), d_hidden_routed=torch.zeros((P, I), **bf),
+                     d_gate_up_routed=torch.zeros((P, 2 * I), **bf),
+                     d_x_routed_buffer=torch.zeros((L * k, H), **bf), d_x=torch.empty((L, H), **bf),
+                     d_router_weights=torch.zeros((L, k), dtype=torch.float32, device=dev),
+                     d_w_routed_down=torch.empty((E, H, I), **bf), d_w_routed_gate_up=torch.empty((E, 2 * I, H), **bf),
+                     # transposes of the row-major activations: the operands of the weight-gradient GEMMs
+                     t_rows_h=torch.zeros((H, P), **bf), t_rows_i=torch.zeros((I, P), **bf),
+                     t_rows_2i=torch.zeros((2 * I, P), **bf), t_rows_h2=torch.zeros((H, P), **bf))
+            b["x_routed_bf16"].zero_()
+            b["hidden_routed_bf16"].zero_()
+            self._ones = torch.ones((L, k), dtype=torch.float32, device=dev)
+            self._identity_rows = torch.arange(P, dtype=torch.int32, device=dev)
+            return
         b.update(gate_routed_fp8=torch.empty((P, I), **u8), gate_routed_sc=sc(P, I),
                  up_routed_fp8=torch.empty((P, I), **u8), up_routed_sc=sc(P, I),
                  hidden_routed_bf16=torch.zeros((P, I), **bf),
@@ -360,6 +379,12 @@ class MoKHost:
     def gemm_gate_up_train(self):
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
         self.select_activation()
+        if self.precision == "bf16":
+            _lib.call("plb_moe_gemm_gate_up_bf16_train", b["x_routed_bf16"].data_ptr(), w["w13_bf16"].data_ptr(),
+                      s.block_expert.data_ptr(), s.num_tokens.data_ptr(), self.capacity, self.num_local_experts,
+                      sh.intermediate, sh.hidden, b["hidden_routed_bf16"].data_ptr(), b["gate_routed_bf16"].data_ptr(),
+                      b["up_routed_bf16"].data_ptr(), self.status.buf.data_ptr(), _stream())
+            return
         if self.fused_dispatch:
             _lib.call("plb_moe_gemm_gate_up_train_dispatch", self.xq_peers.data_ptr(), self.xsc_rows_peers.data_ptr(),
                       s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), b["x_routed_fp8"].data_ptr(),
@@ -399,9 +424,11 @@ class MoKHost:
         from the routed tokens before the gradients are taken."""
         s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
         if recompute:
-            if "w_down_t_fp8" not in self.weights:
+            if "w_down_t_fp8" not in self.weights and "w_down_t_bf16" not in self.weights:
                 raise RuntimeError("load_weights(..., train=True) first")
             self.gemm_gate_up_train()
+        if self.precision == "bf16":
+            return self._backward_bf16(d_out, check)
         P, H, I, k = self.capacity, sh.hidden, sh.intermediate, sh.topk
         nt = s.num_tokens.data_ptr()
         # combine backward + router-weight gradient
@@ -433,6 +460,46 @@ class MoKHost:
         return {"d_x": b["d_x"], "d_router_weights": b["d_router_weights"], "d_w_routed_gate": g[:, :I],
                 "d_w_routed_up": g[:, I:], "d_w_routed_down": b["d_w_routed_down"]}
 
+    def _rows_gemm_bf16(self, a_rows, b_t, K, N, out, dest_rows):
+        """bf16 out[dest_rows[p]] = A[p] . B_t[expert(p)]^T with A [P, K] and B_t [E, N, K]."""
+        s = self.schedule
+        _lib.call("plb_moe_gemm_down_bf16", a_rows.data_ptr(), b_t.data_ptr(), s.block_expert.data_ptr(), s.num_tokens.data_ptr(),
+                  dest_rows.data_ptr(), None, self.capacity, self.num_local_experts, K, N, 0, out.data_ptr(), None,
+                  self.status.buf.data_ptr(), _stream())
+
+    def _wgrad_bf16(self, a_rows, a_t, b_rows, b_t, out):
+        """out[e] = A_e^T . B_e over each expert's rows of the schedule: A [P, M], B [P, N] row-major."""
+        P, M, N = self.capacity, a_rows.shape[1], b_rows.shape[1]
+        _lib.call("plb_bf16_transpose", a_rows.data_ptr(), P, M, a_t.data_ptr(), _stream())
+        _lib.call("plb_bf16_transpose", b_rows.data_ptr(), P, N, b_t.data_ptr(), _stream())
+        _lib.call("plb_moe_gemm_wgrad_bf16", a_t.data_ptr(), b_t.data_ptr(), self.schedule.expert_offsets.data_ptr(), P,
+                  self.num_local_experts, M, N, out.data_ptr(), self.status.buf.data_ptr(), _stream())
+
+    def _backward_bf16(self, d_out, check):
+        """The backward pass of the bf16 routed precision: the MXFP8 pass without its quantisations
+        (data gradients on the transposed weights, weight gradients on transposed activations)."""
+        s, b, w, sh = self.schedule, self.buffers, self.weights, self.shape
+        P, H, I, k = self.capacity, sh.hidden, sh.intermediate, sh.topk
+        nt = s.num_tokens.data_ptr()
+        _lib.call("plb_moe_bwd_dy", d_out.data_ptr(), b["combine_buffer"].data_ptr(), self.router_weight_buffer.data_ptr(),
+                  s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.dest_row.data_ptr(), nt, P, H, k,
+                  b["d_y_routed"].data_ptr(), b["d_router_weights"].data_ptr(), _stream())
+        self._rows_gemm_bf16(b["d_y_routed"], w["w_down_t_bf16"], H, I, b["d_hidden_routed"], self._identity_rows)
+        self._wgrad_bf16(b["d_y_routed"], b["t_rows_h"], b["hidden_routed_bf16"], b["t_rows_i"], b["d_w_routed_down"])
+        self.select_activation()
+        _lib.call("plb_moe_swiglu_bwd_bf16", b["gate_routed_bf16"].data_ptr(), b["up_routed_bf16"].data_ptr(),
+                  b["d_hidden_routed"].data_ptr(), nt, P, I, b["d_gate_up_routed"].data_ptr(), _stream())
+        self._rows_gemm_bf16(b["d_gate_up_routed"], w["w_cat_t_bf16"], 2 * I, H, b["d_x_routed_buffer"], s.dest_row)
+        _lib.call("plb_moe_fwd_epilogue", None, b["d_x_routed_buffer"].data_ptr(), self._ones.data_ptr(), sh.tokens, k, H,
+                  b["d_x"].data_ptr(), _stream())
+        # the dispatched bf16 token rows of the forward are still in place
+        self._wgrad_bf16(b["d_gate_up_routed"], b["t_rows_2i"], b["x_routed_bf16"], b["t_rows_h2"], b["d_w_routed_gate_up"])
+        if check:
+            self.status.check("after MoE backward (bf16)")
+        g = b["d_w_routed_gate_up"]
+        return {"d_x": b["d_x"], "d_router_weights": b["d_router_weights"], "d_w_routed_gate": g[:, :I],
+                "d_w_routed_up": g[:, I:], "d_w_routed_down": b["d_w_routed_down"]}
+
     def megakernel(self):
         """The device part between the barriers of the reference's forward (mok_port_host.py:203)."""
         self.dispatch()
@@ -450,10 +517,8 @@ class MoKHost:
         self.schedule_into(inputs.experts[None])
         self.x_buffer.copy_(inputs.x)
         self.router_weight_buffer.copy_(inputs.router)
-        if train and self.precision == "bf16":
-            raise ValueError("the bf16 routed precision is forward only")
         if train:
-            if "w_down_t_fp8" not in self.weights:
+            if "w_down_t_fp8" not in self.weights and "w_down_t_bf16" not in self.weights:
                 raise RuntimeError("load_weights(..., train=True) first")
             self.dispatch()
             self.gemm_gate_up_train()

@@ -3,7 +3,7 @@ protocol expansion -> Z3 solve) answers for this repo's three-stage GEMM package
 
 Run in the build container, where the reference tree is mounted (it does not travel):
 
-    python tests/golden/make_linker_golden.py [/root/reference]
+    python tests/golden/make_linker_golden.py <path to a checkout of the reference>
 
 writes tests/golden/gemm3_reference_linker.json. Two facts of this image differ from the
 reference's sm_100a profile and are patched in memory before loading, nothing else is touched:
@@ -20,7 +20,9 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
-REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: " + Path(__file__).name + " <path to a checkout of the reference>")
+REFERENCE = Path(sys.argv[1])
 sys.path.insert(0, str(REFERENCE / "pipec" / "src"))
 
 from pipec2 import link as rlink, profile as rprofile, schema as rschema  # noqa: E402  (the reference)

@@ -3,7 +3,7 @@ family (namespace F2; roles 1 = Q, 2 = K, 3 = V), as its own Python restatement 
 
 Run in the build container, where the reference tree is mounted (it does not travel):
 
-    python tests/golden/make_stream_golden.py [/root/reference]
+    python tests/golden/make_stream_golden.py <path to a checkout of the reference>
 
 writes tests/golden/philox_f2_streams.json. The bf16 element is the reference's single rounding
 of the binary64 value -2 + 4u (evaluator/harness/parity/streams.py `_bfloat16_bits_rne`, the same
@@ -13,7 +13,9 @@ import json
 import sys
 from pathlib import Path
 
-REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: " + Path(__file__).name + " <path to a checkout of the reference>")
+REFERENCE = Path(sys.argv[1])
 sys.path.insert(0, str(REFERENCE))
 
 from evaluator.harness.parity import streams  # noqa: E402  (the reference)

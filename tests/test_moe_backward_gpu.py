@@ -103,3 +103,57 @@ def test_recompute_pass_gives_the_same_gradients(native_lib):
         g = got[name]
         view = torch.int16 if g.dtype == torch.bfloat16 else torch.int32
         assert torch.equal(g.contiguous().view(view), w.contiguous().view(view)), name
+
+
+@pytest.mark.parametrize("shape_args,generation,limit", [(("bf-small", 4, 256, 256, 2, 384), 1, 0.0), (("bf-empty", 8, 512, 256, 2, 300), 3, 0.0),
+                                                         (("bf-mid", 8, 1024, 512, 4, 512), 2, 0.0), (("bf-clamp", 8, 512, 256, 2, 384), 2, 0.5)])
+def test_bf16_precision_backward_vs_oracle(native_lib, shape_args, generation, limit):
+    """The backward cells of the bf16 routed precision (campaigns/mok/README.md:86-104): no quantisation
+    anywhere, so the device and the oracle differ only in fp32 summation order and one bf16 rounding
+    per stored tensor: relative (sum|err| / sum|ref|) <= 1e-2 on every gradient, d_y exact."""
+    from pipelink_b200 import _lib, mok
+    shape = mok.Shape(*shape_args)
+    torch.manual_seed(6)
+    E, H, I = shape.experts, shape.hidden, shape.intermediate
+    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.05).to(torch.bfloat16)
+    wg, wu, wd = mk(E, I, H), mk(E, I, H), mk(E, H, I)
+    inputs = mok.MoKHost.new_inputs(shape, generation, "cuda")
+    d_out = torch.randn(shape.tokens, H, device="cuda").to(torch.bfloat16)
+    try:
+        host = mok.MoKHost(shape, precision="bf16", swiglu_limit=limit)
+        host.load_weights(wg, wu, wd, train=True)
+        fwd_plain = host.forward(inputs)["output"].clone()
+        fwd_train = host.forward(inputs, train=True)["output"].clone()
+        assert torch.equal(fwd_plain.view(torch.int16), fwd_train.view(torch.int16))
+        grads = {k: v.clone() for k, v in host.backward(d_out).items()}
+        torch.cuda.synchronize()
+        ctx = {}
+        ref_f = omoe.forward_single_rank_bf16(_f(inputs.x), inputs.experts.cpu().numpy().astype(np.int32), inputs.router.cpu().numpy(),
+                                              _f(wg), _f(wu), _f(wd), padding=host.padding, capacity=host.capacity, limit=limit,
+                                              context=ctx)
+        ref = omoe.backward_single_rank_bf16(_f(inputs.x), inputs.router.cpu().numpy(), _f(wg), _f(wu), _f(wd), ref_f, ctx, _f(d_out),
+                                             limit=limit)
+        total = int(ref_f["schedule"]["num_tokens"][0])
+        assert omoe.error_stats(ref_f["output"], _f(fwd_train))["relative"] <= 1e-2
+        assert omoe.error_stats(ref["d_y"], _f(host.buffers["d_y_routed"])[:total])["abs_max"] == 0.0
+        for name, got in (("d_hidden", host.buffers["d_hidden_routed"][:total]), ("d_gate_up", host.buffers["d_gate_up_routed"][:total]),
+                          ("d_router_weights", grads["d_router_weights"]), ("d_x", grads["d_x"]),
+                          ("d_w_routed_down", grads["d_w_routed_down"]), ("d_w_routed_gate", grads["d_w_routed_gate"]),
+                          ("d_w_routed_up", grads["d_w_routed_up"])):
+            g = _f(got)
+            assert np.isfinite(g).all(), name
+            st = omoe.error_stats(ref[name], g)
+            assert st["relative"] <= 1e-2, (name, st)
+        for e in np.nonzero(ref_f["schedule"]["tokens_per_expert"] == 0)[0]:
+            assert not _f(grads["d_w_routed_down"][e]).any() and not _f(grads["d_w_routed_gate"][e]).any()
+        # the recompute cell: a plain forward, then the activations regenerated inside the backward pass
+        for name in ("gate_routed_bf16", "up_routed_bf16"):
+            host.buffers[name].zero_()
+        host.forward(inputs)
+        again = host.backward(d_out, recompute=True)
+        for name, w in grads.items():
+            g = again[name]
+            view = torch.int16 if g.dtype == torch.bfloat16 else torch.int32
+            assert torch.equal(g.contiguous().view(view), w.contiguous().view(view)), ("recompute", name)
+    finally:
+        _lib.call("plb_moe_set_swiglu_limit", 0.0)

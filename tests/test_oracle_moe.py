@@ -133,3 +133,31 @@ def test_spot_rows_equal_rows_of_the_full_forward():
     sel = np.array([0, 5, 17, 123, 299])
     got = omoe.forward_token_rows(x[sel], ids[sel], rw[sel], expert_weights)
     assert np.array_equal(got, full[sel])
+
+
+@pytest.mark.parametrize("limit", [0.0, 0.75])
+def test_bf16_backward_oracle_matches_autograd(limit):
+    """backward_single_rank_bf16 against fp64 autograd of the unquantised FFN: with no quantisation on
+    the path only bf16 roundings separate them (the MXFP8 oracle needs a few per cent)."""
+    from oracle import routing as oroute
+    rng = np.random.default_rng(4)
+    E, H, I, T, k = 4, 128, 128, 96, 2
+    bf = mxfp8.bf16_round
+    wg, wu, wd = (bf(rng.standard_normal(s, dtype=np.float32) * np.float32(0.2)) for s in ((E, I, H), (E, I, H), (E, H, I)))
+    x = bf(rng.standard_normal((T, H), dtype=np.float32))
+    d_out = bf(rng.standard_normal((T, H), dtype=np.float32))
+    ids, rw = oroute.route_topk(rng.standard_normal((T, E), dtype=np.float32), k)
+    ctx = {}
+    fwd = omoe.forward_single_rank_bf16(x, ids, rw, wg, wu, wd, limit=limit, context=ctx)
+    got = omoe.backward_single_rank_bf16(x, rw, wg, wu, wd, fwd, ctx, d_out, limit=limit)
+    t = lambda a: torch.tensor(a, dtype=torch.float64, requires_grad=True)
+    xt, rwt, wgt, wut, wdt = t(x), t(rw), t(wg), t(wu), t(wd)
+    out = _dense_ffn(xt, ids, rwt, wgt, wut, wdt, limit)
+    out.backward(torch.tensor(d_out, dtype=torch.float64))
+    assert _rel(out.detach().numpy(), fwd["output"]) < 1e-2
+    # with a bound, the decision is taken on bf16-rounded gate / up: an element within half a bf16 step
+    # of the bound flips, and each flip is a whole gradient term (the MXFP8 test above carries the same note)
+    tol = 1e-2 if limit == 0 else 8e-2
+    for name, ref in (("d_x", xt.grad), ("d_router_weights", rwt.grad), ("d_w_routed_gate", wgt.grad),
+                      ("d_w_routed_up", wut.grad), ("d_w_routed_down", wdt.grad)):
+        assert _rel(ref.numpy(), got[name]) < tol, name
