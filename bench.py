@@ -50,6 +50,8 @@ def parse():
     ap.add_argument("--no-tp", action="store_true", help="skip the all-gather / reduce-scatter GEMM leg (N > 1)")
     ap.add_argument("--no-attention", action="store_true", help="skip the causal prefill attention leg")
     ap.add_argument("--no-parity", action="store_true", help="skip the value checks of the N > 1 legs")
+    ap.add_argument("--no-fp8-peak", action="store_true", help="skip the cuBLASLt FP8 peak measurement (thousands of launches)")
+    ap.add_argument("--no-linked", action="store_true", help="skip the linked-images leg")
     ap.add_argument("--case", default=None, choices=["moe", "attention", "decode", "ep-phases"],
                     help="run one small case of a hot kernel (for profiler captures) instead of the benchmark")
     return ap.parse_args()
@@ -516,7 +518,7 @@ def run_native(args):
     # dominant kernel: the fused gate/up GEMM (2/3 of the FLOPs), timed with CUDA events inside the
     # timed steps; held to the dense FP8 rate cuBLASLt sustains on this GPU in this run
     k_ms = statistics.mean(a.elapsed_time(b) for a, b in session.kernel_events) if session.kernel_events else None
-    fp8 = measure_fp8_peak(dev) if rank == 0 else None
+    fp8 = measure_fp8_peak(dev) if rank == 0 and not args.no_fp8_peak else None
     if world > 1:
         box = [fp8]
         dist.broadcast_object_list(box, src=0)
@@ -553,12 +555,21 @@ def run_native(args):
         if world > 1:
             e2e["host_copy_ceiling"] = host_copy_ceiling(dev, world, h2d, d2h)
 
+    def leg(name, fn):
+        """A secondary leg must not take the headline line down with it: its failure is reported in
+        its place (every rank runs the same code on the same shapes, so a failure is one of all ranks)."""
+        try:
+            return fn()
+        except Exception as exc:  # noqa: BLE001
+            print(f"[bench] leg {name} failed: {type(exc).__name__}: {exc}", file=sys.stderr)
+            return {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
     attention = None
     if not args.no_attention and args.tokens is None:
         if world == 1:
-            attention = attention_leg(dev, pk)
+            attention = leg("attention", lambda: attention_leg(dev, pk))
         else:
-            attention = cp_attention_leg(dev, pk, rank, world, check=not args.no_parity)
+            attention = leg("cp_attention", lambda: cp_attention_leg(dev, pk, rank, world, check=not args.no_parity))
             if parity is not None and attention.get("parity") is not None:
                 parity["cp_attention"] = attention["parity"]
 
@@ -568,21 +579,22 @@ def run_native(args):
         del session
         torch.cuda.empty_cache()
         session = None
-        train = ep_train_leg(shape, dev, rank, world, pk, fused_dispatch=bool(dispatch_choice and dispatch_choice["chosen"] == "in-kernel"))
+        fused = bool(dispatch_choice and dispatch_choice["chosen"] == "in-kernel")
+        train = leg("ep_fwd_bwd", lambda: ep_train_leg(shape, dev, rank, world, pk, fused_dispatch=fused))
 
     tp_gemm = None
     if world > 1 and not args.no_tp and args.tokens is None:
-        tp_gemm = tp_leg(dev, pk, rank, world)
+        tp_gemm = leg("tp_gemm", lambda: tp_leg(dev, pk, rank, world))
 
     linked = None
-    if world == 1 and args.tokens is None:
-        linked = linked_leg(session)
+    if world == 1 and args.tokens is None and not args.no_linked:
+        linked = leg("linked_moe", lambda: linked_leg(session))
 
     decode = None
     if rank == 0 and world == 1 and not args.no_decode and args.tokens is None:
         del session
         torch.cuda.empty_cache()
-        decode = decode_leg(dev, pk)
+        decode = leg("decode", lambda: decode_leg(dev, pk))
         session = None
 
     cpu = None

@@ -227,6 +227,16 @@ class EpMoKHost(mok.MoKHost):
             if lay.stream:
                 self.d_x_recv_peers = table(lay.d_x_recv)
                 self.d_x_recv = tensor_from_ptr(me + lay.d_x_recv, (W * L * k, H), torch.bfloat16, dev)
+            # The gate/up weight gradient needs the bf16 token rows of this rank's experts. They are the
+            # same tokens the forward dispatched, so every peer's token buffer is copied whole during
+            # the forward, by the copy engines on a side stream (W * L rows: no more bytes than T * k
+            # row pulls once top-k >= W, far fewer below), and the backward gathers its rows locally.
+            self.x_all = torch.empty((W, L, H), dtype=torch.bfloat16, device=dev)
+            self.x_all_table = torch.tensor([self.x_all[q].data_ptr() for q in range(W)], dtype=torch.int64, device=dev)
+            self._peer_x = [tensor_from_ptr(ptrs[q] + lay.x_bf16, (L, H), torch.bfloat16, dev) for q in range(W)]
+            self.copy_stream = torch.cuda.Stream(dev)
+            self._x_readable, self._x_gathered = torch.cuda.Event(), torch.cuda.Event()
+            self._x_gather_pending = False
 
     def _alloc_train_buffers(self):
         super()._alloc_train_buffers()
@@ -315,11 +325,32 @@ class EpMoKHost(mok.MoKHost):
                   mok._stream())
         return b["output"]
 
+    def start_token_gather(self):
+        """Training forward, after the first barrier (every rank's tokens are in place): copy all of
+        them here on the side stream while the GEMMs run."""
+        main = torch.cuda.current_stream()
+        self._x_readable.record(main)
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self._x_readable)
+            for q in range(self.world):
+                self.x_all[q].copy_(self._peer_x[q], non_blocking=True)
+            self._x_gathered.record(self.copy_stream)
+        self._x_gather_pending = True
+
+    def join_token_gather(self):
+        """The copies have landed before anything queued after this call runs. Called before the
+        forward's second barrier, so no rank can be overwriting its tokens for the next step while a
+        peer still reads them, and again (a no-op then) where the backward uses the copies."""
+        if self._x_gather_pending:
+            torch.cuda.current_stream().wait_event(self._x_gathered)
+
     def device_step(self, train: bool = False):
         """Everything after the inputs sit in x_buffer / routes_local / router_weight_buffer."""
         self.quantize_tokens()
         self.publish_routes()
         self.barrier()          # routes gathered, every rank's quantised tokens readable
+        if train and self.group.layout.train and self.precision == "mxfp8":
+            self.start_token_gather()
         self.build_schedule()
         self.pull()
         if train:
@@ -333,9 +364,11 @@ class EpMoKHost(mok.MoKHost):
     def forward_phases(self, train: bool = False):
         """device_step() as (name, call) pairs, for per-phase timing."""
         gate_up = self.gemm_gate_up_train if train else self.gemm_gate_up
+        gather = [("token copies (side stream)", self.start_token_gather)] if train else []
+        join = [("join token copies", self.join_token_gather)] if train else []
         return [("quantise tokens", self.quantize_tokens), ("publish routes", self.publish_routes),
-                ("barrier", self.barrier), ("schedule", self.build_schedule), ("dispatch pull", self.pull),
-                ("gate/up GEMM", gate_up), ("down GEMM + push", lambda: self.gemm_down_push(train)),
+                ("barrier", self.barrier), *gather, ("schedule", self.build_schedule), ("dispatch pull", self.pull),
+                ("gate/up GEMM", gate_up), ("down GEMM + push", lambda: self.gemm_down_push(train)), *join,
                 ("barrier ", self.barrier), ("epilogue", self.fwd_epilogue)]
 
     def backward_phases(self):
@@ -399,7 +432,13 @@ class EpMoKHost(mok.MoKHost):
         """Gate/up weight gradient: the bf16 token rows pulled from their home ranks, quantised along the rows."""
         s, b, sh = self.schedule, self.buffers, self.shape
         _, _, dgu_t, dgu_t_sc = self._dgu
-        _lib.call("plb_ep_gather_rows", self.x_peers.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
+        # rows come from the copies the forward made of every rank's tokens (local reads); without a
+        # training forward in front (a LocalGroup stepping phases by hand) they are pulled from the peers
+        src = self.x_peers
+        if self._x_gather_pending:
+            self.join_token_gather()
+            src = self.x_all_table
+        _lib.call("plb_ep_gather_rows", src.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
                   s.num_tokens.data_ptr(), self.capacity, sh.hidden, b["x_routed_bf16"].data_ptr(), mok._stream())
         _, _, x_t, x_t_sc = mok.mxfp8_quantize(b["x_routed_bf16"], False, True)
         self._wgrad(dgu_t, dgu_t_sc, x_t, x_t_sc, 2 * sh.intermediate, sh.hidden, b["d_w_routed_gate_up"])
@@ -553,6 +592,8 @@ class BenchSession:
         h.quantize_tokens()
         h.publish_routes()
         h.barrier()
+        if self.train:
+            h.start_token_gather()
         h.build_schedule()
         h.pull()
         gate_up = h.gemm_gate_up_train if self.train else h.gemm_gate_up
@@ -565,6 +606,8 @@ class BenchSession:
         else:
             gate_up()
         h.gemm_down_push(self.train)
+        if self.train:
+            h.join_token_gather()
         h.barrier()
         h.fwd_epilogue()
         if self.train:
