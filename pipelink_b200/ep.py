@@ -626,7 +626,7 @@ class BenchSession:
         h = self.host
         if self.train or h.precision != "mxfp8" or h.shape.hidden > 4096:
             return None
-        times = {}
+        times, failed = {}, None
         for name, fused in (("pull kernel", False), ("in-kernel", True)):
             h.fused_dispatch = fused
             for _ in range(2):
@@ -640,11 +640,23 @@ class BenchSession:
                 self.step()
             b.record()
             torch.cuda.synchronize()
+            # a form that reports a device status on any rank is out, whatever its time
+            bad = torch.tensor([int(h.status.buf[0].item() != 0)], dtype=torch.int32, device=self.dev)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+            if bad.item():
+                failed = name
+                h.status.reset()
+                torch.cuda.synchronize()
+                dist.barrier()
+                continue
             t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device=self.dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             times[name] = float(t.item())
-        h.status.check("bench (EP, dispatch choice)")
-        h.fused_dispatch = times["in-kernel"] < times["pull kernel"]
+        if "pull kernel" not in times:
+            raise RuntimeError("the expert-parallel step reports a device status with the pull kernel")
+        h.fused_dispatch = "in-kernel" in times and times["in-kernel"] < times["pull kernel"]
+        if failed:
+            return {"ms_per_step": times, "chosen": "pull kernel", "rejected": f"{failed}: device status during its timing"}
         return {"ms_per_step": times, "chosen": "in-kernel" if h.fused_dispatch else "pull kernel"}
 
     def traffic_per_launch(self):
