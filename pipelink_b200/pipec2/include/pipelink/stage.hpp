@@ -1,0 +1,511 @@
+// <pipelink/stage.hpp>: the PL_* annotations a stage translation unit declares its contract with.
+//
+// `pipec2 pack stage.cu` compiles the unit twice. Once as the device payload, where every
+// annotation below expands to nothing; and once with -DPIPELINK_EMIT as a host program, where each
+// annotation is a static object that records one piece of the manifest and the `main` this header
+// supplies prints the schema-3.0 manifest as JSON. Parameter sizes, alignments and member offsets
+// come from the compiler that also builds the payload, so a manifest cannot drift from the
+// struct it describes. The vocabulary follows the reference's device annotation set
+// (docs/reference/annotations.md "Overview": PL_STAGE, PL_PARAMS / PL_NO_PARAMS /
+// PL_PARAMS_OPAQUE, PL_ROLE, PL_EXPORT, PL_ENDPOINT, PL_CLAIM / PL_CLAIM_EX / PL_CLAIM_REGS,
+// PL_TOPOLOGY, PL_VARIANT, PL_HINT); each annotation ends in `;`.
+//
+//   PL_STAGE("moe.load", "1.0.0");
+//   PL_PARAMS(MoeLoadParams, a, b, sfa, sfb, g, counters);
+//   PL_ROLE(load, moe_load_role, 1);
+//   PL_ENDPOINT(operands, pl::endpoint(pl::produce, "load").space("smem")...);
+//   PL_CLAIM(smem, pipelink_moe_operands, pl::per("pipelink_moe_depth", 35840), 1024);
+//   PL_TOPOLOGY(pl::topology().cta_group(2).cluster(2, 1, 1).persistent());
+#pragma once
+
+#ifndef PIPELINK_EMIT
+
+#define PL_STAGE(id, version) static_assert(true, "")
+#define PL_PARAMS(T, ...) static_assert(true, "")
+#define PL_PARAMS_OPAQUE(T) static_assert(true, "")
+#define PL_NO_PARAMS() static_assert(true, "")
+#define PL_ROLE(name, fn, warps) static_assert(true, "")
+#define PL_EXPORT(name, fn) static_assert(true, "")
+#define PL_ENDPOINT(name, ...) static_assert(true, "")
+#define PL_CLAIM(domain, handle, extent, align) static_assert(true, "")
+#define PL_CLAIM_EX(domain, handle, extent, align, key, value) static_assert(true, "")
+#define PL_CLAIM_WARPS(handle, role, warps, align) static_assert(true, "")
+#define PL_CLAIM_REGS(handle, role, group, regs) static_assert(true, "")
+#define PL_TOPOLOGY(...) static_assert(true, "")
+#define PL_VARIANT(index, key) static_assert(true, "")
+#define PL_HINT(key, value) static_assert(true, "")
+
+#else  // PIPELINK_EMIT: the host projection
+
+// the manifest pass is plain C++: declarations of device functions parse, their bodies are left out
+// by the unit (#ifndef PIPELINK_EMIT around the device code)
+#ifndef __CUDACC__
+#define __device__
+#define __host__
+#define __global__
+#define __forceinline__ inline
+#endif
+
+#include <cstddef>
+#include <cstdio>
+#include <initializer_list>
+#include <map>
+#include <memory>
+#include <string>
+#include <type_traits>
+#include <utility>
+#include <vector>
+
+namespace pl {
+
+// A JSON value: enough of one to print a manifest (objects print with sorted keys).
+class json {
+ public:
+  enum Kind { Null, Bool, Int, Str, Arr, Obj };
+  json() : kind_(Null) {}
+  json(bool b) : kind_(Bool), i_(b) {}
+  json(int v) : kind_(Int), i_(v) {}
+  json(long v) : kind_(Int), i_(v) {}
+  json(long long v) : kind_(Int), i_(v) {}
+  json(unsigned long v) : kind_(Int), i_(static_cast<long long>(v)) {}
+  json(const char* s) : kind_(Str), s_(s) {}
+  json(const std::string& s) : kind_(Str), s_(s) {}
+  static json array() { json j; j.kind_ = Arr; return j; }
+  static json object() { json j; j.kind_ = Obj; return j; }
+  template <class T>
+  static json list(std::initializer_list<T> items) {
+    json j = array();
+    for (const T& item : items) j.push(json(item));
+    return j;
+  }
+  json& push(json v) { kind_ = Arr; a_.push_back(std::move(v)); return *this; }
+  json& operator[](const std::string& key) { kind_ = Obj; return o_[key]; }
+  json& set(const std::string& key, json v) { (*this)[key] = std::move(v); return *this; }
+  bool is_null() const { return kind_ == Null; }
+  std::string dump() const {
+    switch (kind_) {
+      case Null: return "null";
+      case Bool: return i_ ? "true" : "false";
+      case Int: return std::to_string(i_);
+      case Str: return quote(s_);
+      case Arr: {
+        std::string out = "[";
+        for (size_t i = 0; i < a_.size(); ++i) out += (i ? "," : "") + a_[i].dump();
+        return out + "]";
+      }
+      default: {
+        std::string out = "{";
+        bool first = true;
+        for (const auto& kv : o_) {
+          out += (first ? "" : ",") + quote(kv.first) + ":" + kv.second.dump();
+          first = false;
+        }
+        return out + "}";
+      }
+    }
+  }
+
+ private:
+  static std::string quote(const std::string& s) {
+    std::string out = "\"";
+    for (char c : s) {
+      if (c == '"' || c == '\\') { out += '\\'; out += c; }
+      else if (c == '\n') out += "\\n";
+      else out += c;
+    }
+    return out + "\"";
+  }
+  Kind kind_;
+  long long i_ = 0;
+  std::string s_;
+  std::vector<json> a_;
+  std::map<std::string, json> o_;
+};
+
+constexpr const char* produce = "produce";
+constexpr const char* consume = "consume";
+
+// extent of a claim: a constant, or a multiple of a link-time handle (a ring depth), or both
+struct extent {
+  long long constant = 0;
+  std::map<std::string, long long> per_handle;
+  extent operator+(const extent& o) const {
+    extent e = *this;
+    e.constant += o.constant;
+    for (const auto& kv : o.per_handle) e.per_handle[kv.first] += kv.second;
+    return e;
+  }
+  json to_json() const {
+    json per = json::object();
+    for (const auto& kv : per_handle) per[kv.first] = json(kv.second);
+    json j = json::object();
+    j["const"] = json(constant);
+    j["per"] = per;
+    return j;
+  }
+};
+inline extent units(long long n) { extent e; e.constant = n; return e; }
+inline extent per(const char* handle, long long n) { extent e; e.per_handle[handle] = n; return e; }
+
+// depth of a ring: bound at link time through a handle, or fixed by the stage
+struct depth {
+  json j = json::object();
+  static depth handle(const char* h) { depth d; d.j["handle"] = json(h); return d; }
+  static depth fixed(int n) { depth d; d.j["fixed"] = json(n); return d; }
+};
+
+// one side of a barrier pair: who arrives, how many arrivals complete a phase, bytes credited
+struct arrivals {
+  json j = json::object();
+  arrivals(const char* slots_handle, int count, const char* by_role, long long tx_bytes = 0) {
+    j["slots"] = json(slots_handle);
+    json a = json::object();
+    a["count"] = json(count);
+    a["by"] = json(by_role);
+    j["arrive"] = a;
+    j["tx_bytes"] = json(tx_bytes);
+  }
+};
+
+// PL_ENDPOINT's builder: one end of a channel (mbarrier ring or grid-scoped counter)
+class endpoint {
+ public:
+  endpoint(const char* direction, const char* owner_role) {
+    j_["direction"] = json(direction);
+    j_["owner_role"] = owner_role ? json(owner_role) : json();
+  }
+  endpoint& space(const char* s) { j_["space"] = json(s); return *this; }
+  endpoint& scope(const char* s) { j_["scope"] = json(s); return *this; }
+  endpoint& proxy(const char* s) { j_["proxy"] = json(s); return *this; }
+  endpoint& tile(const char* dtype, std::initializer_list<int> shape) {
+    json t = json::object();
+    t["dtype"] = json(dtype);
+    t["shape"] = json::list(shape);
+    j_["tile"] = t;
+    return *this;
+  }
+  // shared-memory tile layout: per-mode shapes and strides in elements, optional swizzle <B, M, S>
+  endpoint& layout_smem(int elem_bits, std::initializer_list<int> shape, std::initializer_list<int> stride,
+                        int swizzle_b = 0, int swizzle_m = 0, int swizzle_s = 0) {
+    json l = json::object();
+    l["encoding"] = json("pl-layout-v2");
+    l["elem_bits"] = json(elem_bits);
+    json sh = json::array(), st = json::array();
+    for (int v : shape) sh.push(json::list({v}));
+    for (int v : stride) st.push(json::list({v}));
+    l["shape"] = sh;
+    l["stride"] = st;
+    if (swizzle_b != 0) {
+      json sw = json::object();
+      sw["B"] = json(swizzle_b);
+      sw["M"] = json(swizzle_m);
+      sw["S"] = json(swizzle_s);
+      l["swizzle"] = sw;
+    }
+    j_["layout"] = l;
+    return *this;
+  }
+  // tensor-memory tile layout: a lane interval and a column count
+  endpoint& layout_tmem(int elem_bits, int lane_begin, int lane_end, int cols) {
+    json l = json::object();
+    l["encoding"] = json("pl-layout-v2");
+    l["elem_bits"] = json(elem_bits);
+    l["lanes"] = json::list({lane_begin, lane_end});
+    l["cols"] = json(cols);
+    j_["layout"] = l;
+    return *this;
+  }
+  endpoint& ring(const depth& d, long long stage_stride_bytes, long long payload_bytes = -1) {
+    json r = json::object();
+    r["depth"] = d.j;
+    r["stage_stride_bytes"] = json(stage_stride_bytes);
+    if (payload_bytes >= 0) r["payload_bytes"] = json(payload_bytes);
+    j_["ring"] = r;
+    return *this;
+  }
+  endpoint& mbarrier(const arrivals& full, const arrivals& empty, const char* init_owner) {
+    json p = json::object();
+    p["kind"] = json("mbarrier");
+    p["full"] = full.j;
+    p["empty"] = empty.j;
+    json init = json::object();
+    init["owner"] = json(init_owner);
+    init["phase"] = json(0);
+    init["materializer"] = json("dispatch");
+    p["init"] = init;
+    p["release"] = json("once-per-acquire");
+    j_["protocol"] = p;
+    return *this;
+  }
+  endpoint& counter(const char* slot_handle, const char* release, const char* acquire) {
+    json c = json::object();
+    c["slot"] = json(slot_handle);
+    c["release"] = json(release);
+    c["acquire"] = json(acquire);
+    json p = json::object();
+    p["kind"] = json("counter");
+    p["counter"] = c;
+    j_["protocol"] = p;
+    return *this;
+  }
+  endpoint& bind(const char* what, const char* handle) {
+    if (j_["binds"].is_null()) j_["binds"] = json::object();
+    j_["binds"][what] = json(handle);
+    return *this;
+  }
+  json to_json(const char* name) const {
+    json j = j_;
+    j["name"] = json(name);
+    return j;
+  }
+
+ private:
+  json j_ = json::object();
+};
+
+class topology {
+ public:
+  topology() {
+    j_["multicast"] = json::array();
+    j_["persistent"] = json(false);
+    j_["scheduler"] = json("static");
+  }
+  topology& cta_group(int n) {
+    json g = json::object();
+    g["fixed"] = json(n);
+    j_["cta_group"] = g;
+    return *this;
+  }
+  topology& cluster(int x, int y, int z) {
+    json launch = json::object();
+    launch["x_multiple_of"] = json(x);
+    launch["max"] = json::list({x, y, z});
+    json c = json::object();
+    c["compiled"] = json::list({x, y, z});
+    c["launch"] = launch;
+    j_["cluster"] = c;
+    return *this;
+  }
+  topology& persistent(bool on = true) { j_["persistent"] = json(on); return *this; }
+  topology& scheduler(const char* s) { j_["scheduler"] = json(s); return *this; }
+  const json& to_json() const { return j_; }
+
+ private:
+  json j_ = json::object();
+};
+
+// What the annotations of one translation unit add up to.
+struct registry {
+  json stage = json::object(), roles = json::object(), exports = json::object();
+  json endpoints = json::array(), claims = json::array(), variants = json::array();
+  json topology, params, hints = json::object();
+  json strong = json::array();
+  int errors = 0;
+  static registry& get() { static registry r; return r; }
+  void fail(const std::string& what) { std::fprintf(stderr, "stage.hpp: %s\n", what.c_str()); ++errors; }
+};
+
+struct reg_stage {
+  reg_stage(const char* id, const char* version) {
+    registry& r = registry::get();
+    if (!r.stage.is_null() && r.stage.dump() != "{}") r.fail("more than one PL_STAGE");
+    std::string prefix;
+    for (const char* c = id; *c; ++c) prefix += (*c == '.' || *c == '-') ? '_' : *c;
+    r.stage["id"] = json(id);
+    r.stage["version"] = json(version);
+    r.stage["symbol_prefix"] = json(prefix + "_");
+  }
+};
+
+struct member { const char* name; size_t offset, size; };
+struct reg_params {
+  reg_params(const char* type, size_t bytes, size_t align, bool opaque, std::initializer_list<member> members) {
+    registry& r = registry::get();
+    if (!r.params.is_null()) r.fail("more than one PL_PARAMS / PL_NO_PARAMS / PL_PARAMS_OPAQUE");
+    json p = json::object();
+    p["type"] = json(type);
+    p["bytes"] = json(static_cast<long long>(bytes));
+    p["align"] = json(static_cast<long long>(align));
+    p["opaque"] = json(opaque);
+    json ms = json::array();
+    for (const member& m : members) {
+      json e = json::object();
+      e["name"] = json(m.name);
+      e["offset"] = json(static_cast<long long>(m.offset));
+      e["bytes"] = json(static_cast<long long>(m.size));
+      ms.push(e);
+    }
+    p["members"] = ms;
+    r.params = p;
+  }
+};
+
+struct reg_role {
+  reg_role(const char* name, const char* entry, int warps) {
+    registry& r = registry::get();
+    json role = json::object();
+    role["entry"] = json(entry);
+    role["warps"] = json(warps);
+    r.roles[name] = role;
+    r.strong.push(json(entry));
+  }
+};
+
+struct reg_export {
+  reg_export(const char* name, const char* fn) {
+    registry& r = registry::get();
+    json e = json::object();
+    e["symbol"] = json(fn);
+    r.exports[name] = e;
+    r.strong.push(json(fn));
+  }
+};
+
+struct reg_endpoint {
+  reg_endpoint(const char* name, const endpoint& e) { registry::get().endpoints.push(e.to_json(name)); }
+};
+
+struct reg_claim {
+  reg_claim(const char* domain, const char* handle, const extent& e, int align, const char* key = nullptr, json value = json()) {
+    json c = json::object();
+    c["domain"] = json(domain);
+    c["handle"] = json(handle);
+    c["extent"] = e.to_json();
+    c["align"] = json(align);
+    c["lifetime"] = json("kernel");
+    if (key != nullptr) c[key] = value;
+    registry::get().claims.push(c);
+  }
+};
+
+struct reg_warps {
+  reg_warps(const char* handle, const char* role, int warps, int align) {
+    json c = json::object();
+    c["domain"] = json("warp");
+    c["handle"] = json(handle);
+    c["extent"] = units(warps).to_json();
+    c["align"] = json(align);
+    c["lifetime"] = json("kernel");
+    c["roles"] = json::list({role});
+    registry::get().claims.push(c);
+  }
+};
+
+struct reg_regs {
+  reg_regs(const char* handle, const char* role, const char* group, int regs) {
+    json c = json::object();
+    c["domain"] = json("regs");
+    c["handle"] = json(handle);
+    c["roles"] = json::list({role});
+    c["values"] = json::list({regs});
+    c["reg_group"] = json(group);
+    registry::get().claims.push(c);
+  }
+};
+
+struct reg_topology {
+  explicit reg_topology(const topology& t) {
+    registry& r = registry::get();
+    if (!r.topology.is_null()) r.fail("more than one PL_TOPOLOGY");
+    r.topology = t.to_json();
+  }
+};
+
+struct reg_variant {
+  reg_variant(int index, json key) {
+    json v = json::object();
+    v["index"] = json(index);
+    v["key"] = key.is_null() ? json::object() : key;
+    registry::get().variants.push(v);
+  }
+};
+
+struct reg_hint {
+  reg_hint(const char* key, json value) { registry::get().hints[key] = std::move(value); }
+};
+
+inline int emit_main() {
+  registry& r = registry::get();
+  if (r.stage.dump() == "{}") r.fail("no PL_STAGE");
+  if (r.params.is_null()) r.fail("no PL_PARAMS / PL_NO_PARAMS / PL_PARAMS_OPAQUE");
+  if (r.topology.is_null()) r.topology = topology().to_json();
+  if (r.errors != 0) return 1;
+  if (r.variants.dump() == "[]") reg_variant(0, json::object());
+  json stage = r.stage;
+  stage["entry_abi"] = json("v2");
+  stage["entry_signature"] = json("void(const void* params, unsigned variant)");
+  stage["roles"] = r.roles;
+  stage["exports"] = r.exports;
+  stage["variants"] = r.variants;
+  json symbols = json::object();
+  symbols["defined_strong"] = r.strong;
+  json out = json::object();
+  out["stage"] = stage;
+  out["endpoints"] = r.endpoints;
+  out["claims"] = r.claims;
+  out["topology"] = r.topology;
+  out["params"] = r.params;
+  out["hints"] = r.hints;
+  out["symbols"] = symbols;
+  std::puts(out.dump().c_str());
+  return 0;
+}
+
+// the entry signature every role has (docs/reference/annotations.md "Parameters and types")
+template <class F>
+constexpr bool is_role_entry = std::is_same<F, void(const void*, unsigned)>::value;
+
+}  // namespace pl
+
+#define PL_CAT2(a, b) a##b
+#define PL_CAT(a, b) PL_CAT2(a, b)
+#define PL_REG(type) static ::pl::type PL_CAT(pl_reg_, __COUNTER__)
+
+#define PL_MEMBER(T, m) ::pl::member{#m, offsetof(T, m), sizeof(((T*)nullptr)->m)}
+#define PL_FE_1(T, a) PL_MEMBER(T, a)
+#define PL_FE_2(T, a, ...) PL_MEMBER(T, a), PL_FE_1(T, __VA_ARGS__)
+#define PL_FE_3(T, a, ...) PL_MEMBER(T, a), PL_FE_2(T, __VA_ARGS__)
+#define PL_FE_4(T, a, ...) PL_MEMBER(T, a), PL_FE_3(T, __VA_ARGS__)
+#define PL_FE_5(T, a, ...) PL_MEMBER(T, a), PL_FE_4(T, __VA_ARGS__)
+#define PL_FE_6(T, a, ...) PL_MEMBER(T, a), PL_FE_5(T, __VA_ARGS__)
+#define PL_FE_7(T, a, ...) PL_MEMBER(T, a), PL_FE_6(T, __VA_ARGS__)
+#define PL_FE_8(T, a, ...) PL_MEMBER(T, a), PL_FE_7(T, __VA_ARGS__)
+#define PL_FE_9(T, a, ...) PL_MEMBER(T, a), PL_FE_8(T, __VA_ARGS__)
+#define PL_FE_10(T, a, ...) PL_MEMBER(T, a), PL_FE_9(T, __VA_ARGS__)
+#define PL_FE_11(T, a, ...) PL_MEMBER(T, a), PL_FE_10(T, __VA_ARGS__)
+#define PL_FE_12(T, a, ...) PL_MEMBER(T, a), PL_FE_11(T, __VA_ARGS__)
+#define PL_FE_13(T, a, ...) PL_MEMBER(T, a), PL_FE_12(T, __VA_ARGS__)
+#define PL_FE_14(T, a, ...) PL_MEMBER(T, a), PL_FE_13(T, __VA_ARGS__)
+#define PL_FE_15(T, a, ...) PL_MEMBER(T, a), PL_FE_14(T, __VA_ARGS__)
+#define PL_FE_16(T, a, ...) PL_MEMBER(T, a), PL_FE_15(T, __VA_ARGS__)
+#define PL_FE_PICK(_1, _2, _3, _4, _5, _6, _7, _8, _9, _10, _11, _12, _13, _14, _15, _16, name, ...) name
+#define PL_FOR_EACH_MEMBER(T, ...)                                                                                   \
+  PL_FE_PICK(__VA_ARGS__, PL_FE_16, PL_FE_15, PL_FE_14, PL_FE_13, PL_FE_12, PL_FE_11, PL_FE_10, PL_FE_9, PL_FE_8, \
+             PL_FE_7, PL_FE_6, PL_FE_5, PL_FE_4, PL_FE_3, PL_FE_2, PL_FE_1)(T, __VA_ARGS__)
+
+#define PL_STAGE(id, version) PL_REG(reg_stage)(id, version)
+#define PL_PARAMS(T, ...)                                                                                      \
+  static_assert(std::is_standard_layout<T>::value && std::is_trivially_copyable<T>::value,                    \
+                "PL_PARAMS: a standard-layout, trivially copyable type");                                     \
+  PL_REG(reg_params)(#T, sizeof(T), alignof(T), false, {PL_FOR_EACH_MEMBER(T, __VA_ARGS__)})
+#define PL_PARAMS_OPAQUE(T) PL_REG(reg_params)(#T, sizeof(T), alignof(T), true, {})
+#define PL_NO_PARAMS() PL_REG(reg_params)("void", 0, 1, false, {})
+#define PL_ROLE(name, fn, warps)                                                                  \
+  static_assert(::pl::is_role_entry<decltype(fn)>, "PL_ROLE: void(const void* params, unsigned variant)"); \
+  PL_REG(reg_role)(#name, #fn, warps)
+#define PL_EXPORT(name, fn) PL_REG(reg_export)(#name, #fn)
+#define PL_ENDPOINT(name, ...) PL_REG(reg_endpoint){#name, __VA_ARGS__}
+#define PL_CLAIM(domain, handle, extent, align) PL_REG(reg_claim)(#domain, #handle, extent, align)
+#define PL_CLAIM_EX(domain, handle, extent, align, key, value) \
+  PL_REG(reg_claim)(#domain, #handle, extent, align, key, ::pl::json(value))
+#define PL_CLAIM_WARPS(handle, role, warps, align) PL_REG(reg_warps)(#handle, #role, warps, align)
+#define PL_CLAIM_REGS(handle, role, group, regs) PL_REG(reg_regs)(#handle, #role, #group, regs)
+#define PL_TOPOLOGY(...) PL_REG(reg_topology){__VA_ARGS__}   // braces: no vexing parse of pl::topology()
+#define PL_VARIANT(index, key) PL_REG(reg_variant)(index, key)
+#define PL_HINT(key, value) PL_REG(reg_hint)(key, ::pl::json(value))
+
+#ifndef PIPELINK_EMIT_NO_MAIN
+int main() { return ::pl::emit_main(); }
+#endif
+
+#endif  // PIPELINK_EMIT

@@ -92,6 +92,29 @@ def _register_audit(info: str, launch_regs):
     return observed
 
 
+def _check_symbols(manifests, bindings):
+    """L-SYM: no two stages define the same strong symbol, and every function a stage calls without
+    defining it is either a handle the binding stub defines or another stage's strong definition
+    (the reference resolves the same sets from its packages' symbol tables,
+    pipec/src/pipec2/link.py:1203-1290)."""
+    owners, failures = {}, []
+    for m in manifests:
+        for sym in m.get("symbols", {}).get("defined_strong", []):
+            if sym in owners:
+                failures.append(ClauseFailure("L-SYM", f"symbols.{sym}", "defined by two stages",
+                                              {"first": owners[sym], "second": m["stage"]["id"]}))
+            owners[sym] = m["stage"]["id"]
+    for m in manifests:
+        for sym in m.get("symbols", {}).get("undefined", {}):
+            if sym in owners and owners[sym] != m["stage"]["id"]:
+                continue
+            if sym not in bindings:
+                failures.append(ClauseFailure("L-SYM", f"{m['stage']['id']}.symbols.{sym}",
+                                              "called by the stage, bound by no handle and defined by no stage"))
+    if failures:
+        raise PipeLinkError(failures)
+
+
 def _params_layout(manifests, profile):
     entries, off = [], 0
     for m in manifests:
@@ -160,6 +183,8 @@ def link(pipeline_path, out_dir, *, device_link=True):
                                         regs_priority=pipe.get("regs_priority", []),
                                         reg_claims=_reg_claims(manifests, handles), role_warps=role_warps,
                                         pipeline_domains=pipe.get("domains", {}))
+
+    _check_symbols(manifests, bindings)
 
     # roles: warp interval from the role's warp claim, params offset from the layout
     offsets = {e[0]: e[1] for e in params["entries"]}

@@ -1,38 +1,102 @@
-"""``pipec2 pack``: stage source + manifest -> ``.plink``.
+"""``pipec2 pack``: stage source -> ``.plink``.
 
-The reference emits the manifest by running the translation unit's host projection of its
-``PL_*`` annotations (docs/reference/pack-and-link.md:23-43). This build keeps the manifest as a
-JSON document beside the source (``<stage>.manifest.json``, same schema 3.0 records the
-annotations would register) and does the two remaining pack steps: compile the LTO payload
-(``nvcc -dc -gencode arch=compute_100a,code=lto_100a``) and assemble the canonical container.
+The manifest comes from the translation unit itself, the way the reference emits it by running the
+host projection of the unit's ``PL_*`` annotations (docs/reference/pack-and-link.md:23-43,
+docs/reference/annotations.md): the unit is compiled once with ``-DPIPELINK_EMIT`` as a host
+program whose ``main`` (from ``<pipelink/stage.hpp>``) prints the schema-3.0 records, sizes and
+member offsets of the parameter block included, and once as the LTO payload
+(``nvcc -dc -gencode arch=compute_100a,code=lto_100a``). The undefined ``pipelink_*`` symbols the
+link must bind are read from the unit's own PTX (``.extern .func`` declarations survive only for
+functions the code calls). A unit without annotations can still be packed with a manifest kept as
+JSON beside it (``manifest_path``).
 """
 from __future__ import annotations
 
 import hashlib
 import json
+import os
+import re
+import subprocess
 import tempfile
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 from . import container, jitlink, schema
+from .model import fail
 from .profile import PROFILES
+
+INCLUDE = Path(__file__).resolve().parent / "include"
+CUDA_INCLUDE = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+ABI = {"schema": "3.0", "target": {"toolkit": "cuda-12.9", "math": {"ftz": False, "prec_div": True, "prec_sqrt": True,
+                                                                   "fmad": True}}}
+
+
+def emit_manifest(source, includes=(), defines=()) -> dict:
+    """Run the unit's host projection: g++ -DPIPELINK_EMIT, execute, parse what it prints."""
+    source = Path(source)
+    with tempfile.TemporaryDirectory() as tmp:
+        exe = Path(tmp) / "emit"
+        cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-x", "c++", "-DPIPELINK_EMIT", "-I", str(INCLUDE),
+               "-I", str(CUDA_INCLUDE), *[f"-I{i}" for i in includes], *[f"-D{d}" for d in defines], str(source), "-o", str(exe)]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            fail("P-COMPILE", f"{source}:emit", proc.stderr[-2000:])
+        run = subprocess.run([str(exe)], capture_output=True, text=True)
+        if run.returncode != 0:
+            fail("P-ANNOTATION", str(source), run.stderr.strip() or "the manifest pass failed")
+    m = json.loads(run.stdout)
+    params = m["params"]
+    # the layout probe: what the compiler says about the block, member by member
+    probe = json.dumps([params["type"], params["bytes"], params["align"],
+                        [[x["name"], x["offset"], x["bytes"]] for x in params["members"]]])
+    params["sha256_of_layout_probe"] = hashlib.sha256(probe.encode()).hexdigest()
+    return m
+
+
+def undefined_symbols(source, profile: dict, includes=(), defines=()) -> dict:
+    """External functions the unit calls and does not define, from its PTX."""
+    with tempfile.TemporaryDirectory() as tmp:
+        ptx = Path(tmp) / "stage.ptx"
+        cmd = [jitlink.nvcc(), "-ptx", "-rdc=true", "-O3", "-std=c++17", "--expt-relaxed-constexpr", "-gencode",
+               f"arch={profile['gencode'][0]},code={profile['gencode'][0]}", "-I", str(INCLUDE),
+               *[f"-I{i}" for i in includes], *[f"-D{d}" for d in defines], "-o", str(ptx), str(source)]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            fail("P-COMPILE", f"{source}:ptx", proc.stderr[-2000:])
+        text = ptx.read_text()
+    return {name: "function" for name in sorted(set(re.findall(r"^\.extern \.func[^;]*?\b(\w+)\s*(?:\(|;)", text, re.M)))}
 
 
 def pack_cu(source, manifest_path=None, out=None, profile="sm_100a", includes=(), defines=()):
     source = Path(source)
-    manifest_path = Path(manifest_path) if manifest_path else source.with_suffix(".manifest.json")
-    manifest = json.loads(manifest_path.read_text())
-    manifest["pipelink_abi"]["target"]["profile"] = profile
-    manifest["pipelink_abi"]["target"]["lto_arch"] = PROFILES[profile]["lto_arch"]
-    schema.validate_manifest(manifest, where=manifest["stage"].get("id", str(source)))
-    with tempfile.TemporaryDirectory() as tmp:
+    prof = PROFILES[profile]
+    includes = [str(INCLUDE), *includes]
+    with tempfile.TemporaryDirectory() as tmp, ThreadPoolExecutor(3) as pool:
         obj = Path(tmp) / "stage.o"
-        jitlink.compile_lto(str(source), str(obj), PROFILES[profile], includes, defines)
+        payload_job = pool.submit(jitlink.compile_lto, str(source), str(obj), prof, includes, defines)
+        if manifest_path is None:
+            undefined_job = pool.submit(undefined_symbols, source, prof, includes[1:], defines)
+            manifest = emit_manifest(source, includes[1:], defines)
+            manifest["symbols"].update(mechanism="ptx-extern", defined_weak=[], undefined=undefined_job.result())
+            manifest["payload"] = {"file": "stage.o"}
+            inputs = {"tu": hashlib.sha256(source.read_bytes()).hexdigest(),
+                      "annotations": hashlib.sha256((INCLUDE / "pipelink" / "stage.hpp").read_bytes()).hexdigest()}
+            mechanism = "annotations"
+        else:
+            manifest_path = Path(manifest_path)
+            manifest = json.loads(manifest_path.read_text())
+            inputs = {"tu": hashlib.sha256(source.read_bytes()).hexdigest(),
+                      "manifest": hashlib.sha256(manifest_path.read_bytes()).hexdigest()}
+            mechanism = "declared-json"
+        abi = manifest.setdefault("pipelink_abi", json.loads(json.dumps(ABI)))
+        abi["target"]["profile"] = profile
+        abi["target"]["lto_arch"] = prof["lto_arch"]
+        schema.validate_manifest(manifest, where=manifest["stage"].get("id", str(source)))
+        payload_job.result()
         payload = obj.read_bytes()
     # provenance as the reference records it (pipec/src/pipec2/schema.py:1015-1030): how the
     # manifest came to be and the digests of what it was made from
-    manifest["provenance"] = {"mechanism": "declared-json",
-                              "inputs": {"tu": hashlib.sha256(source.read_bytes()).hexdigest(),
-                                         "manifest": hashlib.sha256(manifest_path.read_bytes()).hexdigest()}}
+    manifest["provenance"] = {"mechanism": mechanism, "inputs": inputs}
     data = container.pack(manifest, payload)
     out = Path(out) if out else source.with_suffix(".plink")
     out.write_bytes(data)

@@ -1,6 +1,7 @@
 """Pack the MoE grouped-GEMM owners and link their compositions.
 
-The packages: ``moe.load``, ``moe.mma``, two comm owners (``moe.comm.none``, ``moe.comm.dispatch``)
+Every package's manifest comes from the ``PL_*`` annotations in its source (``pipec2 pack`` runs
+the unit's host projection). The packages: ``moe.load``, ``moe.mma``, two comm owners (``moe.comm.none``, ``moe.comm.dispatch``)
 and two epilogue owners (``moe.epilogue.swiglu-mxfp8``, ``moe.epilogue.rows-bf16``). One artifact
 set, three images (the reference links its MoE cells the same way from one set of packages,
 campaigns/mok/README.md:80-118):
@@ -17,12 +18,11 @@ tensor-memory / counter base, the warp tiling and the two register groups. Runs 
 from __future__ import annotations
 
 import argparse
-import hashlib
 import json
-import re
 from pathlib import Path
 
 import subprocess
+from concurrent.futures import ThreadPoolExecutor
 
 from ...pipec2 import jitlink, link as linker, pack as packer
 
@@ -33,145 +33,31 @@ SLOT = SLOT_TX + 512                      # moe::SlotBytes
 MAX_ROW_TILES = 4096                      # moe::MaxRowTiles
 ABI = {"schema": "3.0", "target": {"profile": "sm_100a", "lto_arch": "lto_100a", "toolkit": "cuda-12.9",
                                    "math": {"ftz": False, "prec_div": True, "prec_sqrt": True, "fmad": True}}}
-SIG = "void(const void* params, unsigned variant)"
-TOPOLOGY = {"cta_group": {"fixed": 2}, "cluster": {"compiled": [2, 1, 1], "launch": {"x_multiple_of": 2, "max": [2, 1, 1]}},
-            "multicast": [], "persistent": True, "scheduler": "static"}
-
-
-def _operands(direction, role):
-    """The ring both CTAs of a pair fill: A tile | B tile | three scale blocks per slot. The leader
-    CTA's full barrier collects one arrival and one slot payload from each CTA of the pair."""
-    return {"name": "operands", "direction": direction, "owner_role": role, "space": "smem", "scope": "cluster", "proxy": "async",
-            "tile": {"dtype": "e4m3+ue8m0", "shape": [2, 128, 128]},
-            "layout": {"encoding": "pl-layout-v2", "elem_bits": 8, "shape": [[2], [128], [128]],
-                       "stride": [[TILE], [128], [1]], "swizzle": {"B": 3, "M": 4, "S": 3}},
-            "ring": {"depth": {"handle": "pipelink_moe_depth"}, "stage_stride_bytes": SLOT, "payload_bytes": SLOT_TX},
-            "protocol": {"kind": "mbarrier",
-                         "full": {"slots": "pipelink_moe_full", "arrive": {"count": 2, "by": "load"}, "tx_bytes": 2 * SLOT_TX},
-                         "empty": {"slots": "pipelink_moe_empty", "arrive": {"count": 1, "by": "mma"}, "tx_bytes": 0},
-                         "init": {"owner": "load", "phase": 0, "materializer": "dispatch"}, "release": "once-per-acquire"},
-            "binds": {"base": "pipelink_moe_operands", "full": "pipelink_moe_full", "empty": "pipelink_moe_empty"}}
-
-
-def _accumulator(direction, role):
-    """128 lanes x 256 fp32 columns per CTA; the leader's commit completes both CTAs' full barriers,
-    and every epilogue warp of the pair arrives on the leader's empty barrier."""
-    return {"name": "accumulator", "direction": direction, "owner_role": role, "space": "tmem", "scope": "cluster", "proxy": "async",
-            "tile": {"dtype": "f32", "shape": [128, 256]},
-            "layout": {"encoding": "pl-layout-v2", "elem_bits": 32, "lanes": [0, 128], "cols": 256},
-            "ring": {"depth": {"fixed": 1}, "stage_stride_bytes": 131072},
-            "protocol": {"kind": "mbarrier",
-                         "full": {"slots": "pipelink_moe_acc_full", "arrive": {"count": 1, "by": "mma"}, "tx_bytes": 0},
-                         "empty": {"slots": "pipelink_moe_acc_empty", "arrive": {"count": 16, "by": "epilogue"}, "tx_bytes": 0},
-                         "init": {"owner": "mma", "phase": 0, "materializer": "dispatch"}, "release": "once-per-acquire"},
-            "binds": {"base": "pipelink_moe_acc", "full": "pipelink_moe_acc_full", "empty": "pipelink_moe_acc_empty"}}
-
-
-def _rows_ready(direction, role):
-    """Per row tile, how many of its 256 rows the comm owner has put in place: a grid-scoped
-    counter released with red.release.gpu and acquired by the load owner before its first TMA
-    read of the tile (docs/reference/annotations.md, "Counters")."""
-    return {"name": "rows_ready", "direction": direction, "owner_role": role, "space": "gmem", "scope": "grid", "proxy": "generic",
-            "tile": {"dtype": "e4m3+ue8m0", "shape": [256]},
-            "protocol": {"kind": "counter", "counter": {"slot": "pipelink_moe_rows_ready", "release": "red.release.gpu",
-                                                        "acquire": "ld.acquire.gpu"}},
-            "binds": {"slot": "pipelink_moe_rows_ready"}}
-
-
-def _claim(domain, handle, const=0, per=None, align=1, **extra):
-    return dict({"domain": domain, "handle": handle, "extent": {"const": const, "per": per or {}}, "align": align,
-                 "lifetime": "kernel"}, **extra)
-
-
-OPERAND_CLAIMS = [
-    _claim("smem", "pipelink_moe_operands", per={"pipelink_moe_depth": SLOT}, align=1024),
-    _claim("mbarrier", "pipelink_moe_full", per={"pipelink_moe_depth": 1}),
-    _claim("mbarrier", "pipelink_moe_empty", per={"pipelink_moe_depth": 1}),
-]
-ACC_CLAIMS = [
-    _claim("tmem", "pipelink_moe_acc", const=256, align=32),
-    _claim("mbarrier", "pipelink_moe_acc_full", const=1),
-    _claim("mbarrier", "pipelink_moe_acc_empty", const=1),
-]
-SF_CLAIM = _claim("tmem", "pipelink_moe_sfcols", per={"pipelink_moe_depth": 16}, align=32)
-DRAIN_CLAIM = _claim("mbarrier", "pipelink_moe_drain", const=1, init_count=1)
-STAGING_CLAIM = _claim("smem", "pipelink_moe_staging", const=8 * 2048, align=16)
-COUNTER_CLAIMS = [
-    _claim("gmem_counter", "pipelink_moe_rows_ready", const=MAX_ROW_TILES),
-    _claim("gmem_counter", "pipelink_moe_ticket", const=1),
-]
-
-
-def _warp(handle, n, role, align=1):
-    return dict(_claim("warp", handle, const=n, align=align), roles=[role])
-
-
-def _regs(handle, group, role, value):
-    return {"domain": "regs", "handle": handle, "roles": [role], "values": [value], "reg_group": group}
-
-
 HELPERS = ("pipelink_moe_regs_helpers", "helpers", 56)     # load + mma + comm: one warpgroup
 EPILOGUE = ("pipelink_moe_regs_epilogue", "epilogue", 224)  # two warpgroups
+STAGES = ("load", "mma", "comm_none", "comm_dispatch", "epilogue_swiglu", "epilogue_rows")
+_manifests = None
 
 
-def _layout_probe(type_name: str) -> str:
-    """sha256 over the parameter struct's definition in moe.cuh (whitespace-normalised)."""
-    text = (HERE / "moe.cuh").read_text()
-    m = re.search(r"struct\s+(alignas\(\d+\)\s+)?" + type_name + r"\s*\{.*?\};", text, re.S)
-    if m is None:
-        raise ValueError(f"{type_name} is not defined in moe.cuh")
-    return hashlib.sha256(" ".join(m.group(0).split()).encode()).hexdigest()
+def manifests() -> dict:
+    """{stage file stem: manifest}: what each unit's PL_* annotations state, read by running the
+    unit's host projection (g++, no GPU and no nvcc; the undefined-symbol list is added at pack time)."""
+    global _manifests
+    if _manifests is None:
+        with ThreadPoolExecutor(len(STAGES)) as pool:
+            emitted = list(pool.map(lambda n: packer.emit_manifest(HERE / f"{n}.cu"), STAGES))
+        for m in emitted:
+            m["pipelink_abi"] = json.loads(json.dumps(ABI))
+        _manifests = dict(zip(STAGES, emitted))
+    return _manifests
 
 
-def _manifest(stage_id, role, entry, warps, endpoints, claims, params, undefined):
-    prefix = re.sub(r"[.-]", "_", stage_id) + "_"
-    params = dict(params, sha256_of_layout_probe=_layout_probe(params["type"]))
-    return {"pipelink_abi": json.loads(json.dumps(ABI)),
-            "stage": {"id": stage_id, "version": "1.0.0", "symbol_prefix": prefix, "entry_abi": "v2",
-                      "roles": {role: {"entry": entry, "warps": warps}}, "exports": {}, "entry_signature": SIG,
-                      "variants": [{"key": {}, "index": 0}]},
-            "endpoints": endpoints, "claims": claims, "topology": json.loads(json.dumps(TOPOLOGY)),
-            "params": params, "hints": {},
-            "symbols": {"mechanism": "declared", "defined_strong": [entry], "defined_weak": [],
-                        "undefined": {u: "function" for u in undefined}},
-            "provenance": {}, "payload": {"file": "stage.o"}}
+def __getattr__(name):
+    if name == "MANIFESTS":
+        return manifests()
+    raise AttributeError(name)
 
 
-RING = ["pipelink_moe_depth", "pipelink_moe_operands", "pipelink_moe_full", "pipelink_moe_empty"]
-ACC = ["pipelink_moe_acc", "pipelink_moe_acc_full", "pipelink_moe_acc_empty", "pipelink_tmem_slot"]
-MANIFESTS = {
-    "load": _manifest("moe.load", "load", "moe_load_role", 1,
-                      [_operands("produce", "load"), _rows_ready("consume", "load")],
-                      [_warp("pipelink_moe_warp_load", 1, "load"), _regs(*HELPERS[:2], "load", HELPERS[2]), *OPERAND_CLAIMS,
-                       COUNTER_CLAIMS[0]],
-                      {"bytes": 576, "align": 64, "type": "MoeLoadParams"}, RING + ["pipelink_moe_rows_ready"]),
-    "mma": _manifest("moe.mma", "mma", "moe_mma_role", 1,
-                     [_operands("consume", "mma"), _accumulator("produce", "mma")],
-                     [_warp("pipelink_moe_warp_mma", 1, "mma"), _regs(*HELPERS[:2], "mma", HELPERS[2]), *OPERAND_CLAIMS,
-                      *ACC_CLAIMS, SF_CLAIM, DRAIN_CLAIM],
-                     {"bytes": 48, "align": 16, "type": "MoeMmaParams"},
-                     RING + ACC + ["pipelink_moe_sfcols", "pipelink_moe_drain"]),
-    "comm_none": _manifest("moe.comm.none", "comm", "moe_comm_none_role", 2, [_rows_ready("produce", "comm")],
-                           [_warp("pipelink_moe_warp_comm", 2, "comm"), _regs(*HELPERS[:2], "comm", HELPERS[2]),
-                            COUNTER_CLAIMS[0]],
-                           {"bytes": 0, "align": 16, "type": "MoeMmaParams"}, []),
-    "comm_dispatch": _manifest("moe.comm.dispatch", "comm", "moe_comm_dispatch_role", 2, [_rows_ready("produce", "comm")],
-                               [_warp("pipelink_moe_warp_comm", 2, "comm"), _regs(*HELPERS[:2], "comm", HELPERS[2]),
-                                STAGING_CLAIM, *COUNTER_CLAIMS],
-                               {"bytes": 112, "align": 16, "type": "MoeCommParams"},
-                               ["pipelink_moe_warp_comm", "pipelink_moe_staging", "pipelink_moe_rows_ready", "pipelink_moe_ticket"]),
-    "epilogue_swiglu": _manifest("moe.epilogue.swiglu-mxfp8", "epilogue", "moe_epilogue_swiglu_mxfp8_role", 8,
-                                 [_accumulator("consume", "epilogue")],
-                                 [_warp("pipelink_moe_warp_epilogue", 8, "epilogue", align=4),
-                                  _regs(*EPILOGUE[:2], "epilogue", EPILOGUE[2]), *ACC_CLAIMS],
-                                 {"bytes": 80, "align": 16, "type": "MoeSwigluParams"}, ACC + ["pipelink_moe_warp_epilogue"]),
-    "epilogue_rows": _manifest("moe.epilogue.rows-bf16", "epilogue", "moe_epilogue_rows_bf16_role", 8,
-                               [_accumulator("consume", "epilogue")],
-                               [_warp("pipelink_moe_warp_epilogue", 8, "epilogue", align=4),
-                                _regs(*EPILOGUE[:2], "epilogue", EPILOGUE[2]), *ACC_CLAIMS, STAGING_CLAIM],
-                               {"bytes": 96, "align": 16, "type": "MoeRowsParams"},
-                               ACC + ["pipelink_moe_warp_epilogue", "pipelink_moe_staging"]),
-}
 COMPOSITIONS = {
     "gate_up": ["load", "mma", "comm_none", "epilogue_swiglu"],
     "gate_up_dispatch": ["load", "mma", "comm_dispatch", "epilogue_swiglu"],
@@ -186,7 +72,7 @@ BASE_DOMAINS = {"pipelink_moe_operands": "smem", "pipelink_moe_staging": "smem",
 
 
 def pipeline_spec(name, members, stages, depth=None, values=(6, 5, 4, 3, 2)):
-    claimed = {cl["handle"] for m in members for cl in MANIFESTS[m]["claims"]}
+    claimed = {cl["handle"] for m in members for cl in manifests()[m]["claims"]}
     handles = {"pipelink_moe_depth": {"class": "depth", "binding": "bind", "values": list(values), "owner": "channel:operands"}}
     for h, dom in BASE_DOMAINS.items():
         if h in claimed:
@@ -201,23 +87,17 @@ def pipeline_spec(name, members, stages, depth=None, values=(6, 5, 4, 3, 2)):
                          "topology": {"persistent": True, "scheduler": "static"}}}
 
 
-def write_manifests():
-    for name, m in MANIFESTS.items():
-        (HERE / f"{name}.manifest.json").write_text(json.dumps(m, indent=1, sort_keys=True) + "\n")
-
-
 def build(out: Path, depth=None, device_link=True, one_tu=True):
     """-> {composition: LinkResult}; images at out/<composition>/pipeline.cubin. With one_tu, also
     out/<composition>/one_tu.cubin: the same stage sources, generated stub and dispatch compiled as
     ONE translation unit by nvcc, the control a linked image is timed against (the reference's gate:
     a linked build within 1 % of the single-unit build of the same sources)."""
     out.mkdir(parents=True, exist_ok=True)
-    write_manifests()
-    for name in MANIFESTS:
-        packer.pack_cu(HERE / f"{name}.cu", HERE / f"{name}.manifest.json", out / f"{name}.plink")
+    with ThreadPoolExecutor(len(STAGES)) as pool:
+        list(pool.map(lambda n: packer.pack_cu(HERE / f"{n}.cu", None, out / f"{n}.plink"), STAGES))
     results = {}
     for comp, members in COMPOSITIONS.items():
-        stages = [{"stage_id": MANIFESTS[m]["stage"]["id"], "artifact_path": f"{m}.plink"} for m in members]
+        stages = [{"stage_id": manifests()[m]["stage"]["id"], "artifact_path": f"{m}.plink"} for m in members]
         spec = out / f"{comp}.pipeline.json"
         spec.write_text(json.dumps(pipeline_spec(comp, members, stages, depth), indent=1))
         results[comp] = linker.link(spec, out / comp, device_link=device_link)
@@ -226,7 +106,7 @@ def build(out: Path, depth=None, device_link=True, one_tu=True):
             tu.write_text("".join(f'#include "{HERE / (m + ".cu")}"\n' for m in members) +
                           '#include "binding_stub.cu"\n#include "dispatch.cu"\n')
             cmd = [jitlink.nvcc(), "-cubin", "-O3", "-std=c++17", "--expt-relaxed-constexpr", "-gencode",
-                   "arch=compute_100a,code=sm_100a", "-I", str(tu.parent), "-o", str(out / comp / "one_tu.cubin"), str(tu)]
+                   "arch=compute_100a,code=sm_100a", "-I", str(tu.parent), "-I", str(packer.INCLUDE), "-o", str(out / comp / "one_tu.cubin"), str(tu)]
             proc = subprocess.run(cmd, capture_output=True, text=True)
             if proc.returncode != 0:
                 raise RuntimeError("one-TU control failed:\n" + proc.stderr[-3000:])

@@ -8,6 +8,19 @@
 // wait for nothing, so the tiles the load owners wait for always complete.
 #include "moe.cuh"
 
+extern "C" __device__ void moe_comm_dispatch_role(const void* params, unsigned variant);
+PL_STAGE("moe.comm.dispatch", "1.0.0");
+PL_PARAMS(MoeCommParams, g, xq_peers, sc_rows_peers, peer_rank, peer_token_idx, dst, dst_sc, counters, row_bytes);
+PL_ROLE(comm, moe_comm_dispatch_role, 2);
+MOE_TOPOLOGY();
+PL_ENDPOINT(rows_ready, moe::rows_ready(pl::produce, "comm"));
+PL_CLAIM_WARPS(pipelink_moe_warp_comm, comm, 2, 1);
+MOE_REGS_HELPER(comm);
+MOE_CLAIM_STAGING();
+MOE_CLAIM_ROWS_READY();
+PL_CLAIM(gmem_counter, pipelink_moe_ticket, pl::units(1), 1);
+
+#ifndef PIPELINK_EMIT
 extern "C" __device__ void moe_comm_dispatch_role(const void* raw_params, unsigned) {
   using namespace moe;
   const MoeCommParams p = *static_cast<const MoeCommParams*>(raw_params);   // a copy in registers
@@ -71,3 +84,4 @@ extern "C" __device__ void moe_comm_dispatch_role(const void* raw_params, unsign
     if (lane == 0) plb::red_release_gpu_add(p.counters + pipelink_moe_rows_ready() + (base >> 8), static_cast<unsigned>(kTicketRows));
   }
 }
+#endif  // !PIPELINK_EMIT

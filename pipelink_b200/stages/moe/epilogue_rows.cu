@@ -5,9 +5,21 @@
 // fed by its GEMM owner's FWD_ROUTED_DOWN case, campaigns/mok/port/gemm/gemm.cu:158-162). Rows pass
 // through 2 KiB of shared memory per warp, eight at a time, so that every store instruction of a
 // warp writes two 256-byte row segments.
-#include "../../csrc/swiglu.cuh"
 #include "moe.cuh"
 
+extern "C" __device__ void moe_epilogue_rows_bf16_role(const void* params, unsigned variant);
+PL_STAGE("moe.epilogue.rows-bf16", "1.0.0");
+PL_PARAMS(MoeRowsParams, g, out, out_peers, dest_row, peer_rank, out_cols);
+PL_ROLE(epilogue, moe_epilogue_rows_bf16_role, 8);
+MOE_TOPOLOGY();
+PL_ENDPOINT(accumulator, moe::accumulator(pl::consume, "epilogue"));
+PL_CLAIM_WARPS(pipelink_moe_warp_epilogue, epilogue, 8, 4);
+MOE_REGS_EPILOGUE(epilogue);
+MOE_CLAIM_ACCUMULATOR();
+MOE_CLAIM_STAGING();
+
+#ifndef PIPELINK_EMIT
+#include "../../csrc/swiglu.cuh"
 extern "C" __device__ void moe_epilogue_rows_bf16_role(const void* raw_params, unsigned) {
   using namespace moe;
   const MoeRowsParams p = *static_cast<const MoeRowsParams*>(raw_params);   // a copy in registers
@@ -90,3 +102,4 @@ extern "C" __device__ void moe_epilogue_rows_bf16_role(const void* raw_params, u
     acc_phase ^= 1u;
   }
 }
+#endif  // !PIPELINK_EMIT

@@ -5,9 +5,20 @@
 // E4M3 bytes and two scale bytes per row. The reference runs this arithmetic as its act owner
 // (campaigns/mok/port/act/act.cu:100-178) on bf16 gate / up written by the GEMM owner; here the
 // accumulator channel hands it the tile in tensor memory.
-#include "../../csrc/swiglu.cuh"
 #include "moe.cuh"
 
+extern "C" __device__ void moe_epilogue_swiglu_mxfp8_role(const void* params, unsigned variant);
+PL_STAGE("moe.epilogue.swiglu-mxfp8", "1.0.0");
+PL_PARAMS(MoeSwigluParams, g, out, out_sc, out_cols, limit);
+PL_ROLE(epilogue, moe_epilogue_swiglu_mxfp8_role, 8);
+MOE_TOPOLOGY();
+PL_ENDPOINT(accumulator, moe::accumulator(pl::consume, "epilogue"));
+PL_CLAIM_WARPS(pipelink_moe_warp_epilogue, epilogue, 8, 4);
+MOE_REGS_EPILOGUE(epilogue);
+MOE_CLAIM_ACCUMULATOR();
+
+#ifndef PIPELINK_EMIT
+#include "../../csrc/swiglu.cuh"
 extern "C" __device__ void moe_epilogue_swiglu_mxfp8_role(const void* raw_params, unsigned) {
   using namespace moe;
   const MoeSwigluParams p = *static_cast<const MoeSwigluParams*>(raw_params);   // a copy in registers
@@ -55,3 +66,4 @@ extern "C" __device__ void moe_epilogue_swiglu_mxfp8_role(const void* raw_params
     acc_phase ^= 1u;
   }
 }
+#endif  // !PIPELINK_EMIT

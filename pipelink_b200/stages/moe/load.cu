@@ -5,6 +5,19 @@
 // role inside its package, campaigns/mok/port/gemm/gemm.cu:292-325; here it is an owner of its own).
 #include "moe.cuh"
 
+extern "C" __device__ void moe_load_role(const void* params, unsigned variant);
+PL_STAGE("moe.load", "1.0.0");
+PL_PARAMS(MoeLoadParams, a, b, sfa, sfb, g, counters);
+PL_ROLE(load, moe_load_role, 1);
+MOE_TOPOLOGY();
+PL_ENDPOINT(operands, moe::operands(pl::produce, "load"));
+PL_ENDPOINT(rows_ready, moe::rows_ready(pl::consume, "load"));
+PL_CLAIM_WARPS(pipelink_moe_warp_load, load, 1, 1);
+MOE_REGS_HELPER(load);
+MOE_CLAIM_OPERANDS();
+MOE_CLAIM_ROWS_READY();
+
+#ifndef PIPELINK_EMIT
 extern "C" __device__ void moe_load_role(const void* raw_params, unsigned) {
   using namespace moe;
   const MoeLoadParams& p = *static_cast<const MoeLoadParams*>(raw_params);
@@ -68,3 +81,4 @@ extern "C" __device__ void moe_load_role(const void* raw_params, unsigned) {
     }
   }
 }
+#endif  // !PIPELINK_EMIT

@@ -5,6 +5,21 @@
 // (the reference: campaigns/mok/port/gemm/gemm.cu:150-162, the K loop of its GEMM owner).
 #include "moe.cuh"
 
+extern "C" __device__ void moe_mma_role(const void* params, unsigned variant);
+PL_STAGE("moe.mma", "1.0.0");
+PL_PARAMS(MoeMmaParams, g);
+PL_ROLE(mma, moe_mma_role, 1);
+MOE_TOPOLOGY();
+PL_ENDPOINT(operands, moe::operands(pl::consume, "mma"));
+PL_ENDPOINT(accumulator, moe::accumulator(pl::produce, "mma"));
+PL_CLAIM_WARPS(pipelink_moe_warp_mma, mma, 1, 1);
+MOE_REGS_HELPER(mma);
+MOE_CLAIM_OPERANDS();
+MOE_CLAIM_ACCUMULATOR();
+PL_CLAIM(tmem, pipelink_moe_sfcols, pl::per("pipelink_moe_depth", moe::SfColsPerSlot), 32);
+PL_CLAIM_EX(mbarrier, pipelink_moe_drain, pl::units(1), 1, "init_count", 1);
+
+#ifndef PIPELINK_EMIT
 extern "C" __device__ void moe_mma_role(const void* raw_params, unsigned) {
   using namespace moe;
   // read once into registers (see moe.load): the issue loop must not go back to the parameter block
@@ -67,3 +82,4 @@ extern "C" __device__ void moe_mma_role(const void* raw_params, unsigned) {
     }
   }
 }
+#endif  // !PIPELINK_EMIT

@@ -19,8 +19,14 @@
 #include <cuda.h>
 #include <stdint.h>
 
+#include <pipelink/stage.hpp>
+
+#ifndef PIPELINK_EMIT
 #include "../../csrc/common.cuh"
 #include "../../csrc/mxfp8.cuh"
+#else
+namespace plb { struct Status; }   // the manifest pass needs the parameter layouts only
+#endif
 
 namespace moe {
 constexpr int TileBytes = 128 * 128;                       // one CTA's A or B tile of a K step
@@ -103,6 +109,7 @@ extern "C" __device__ int pipelink_moe_rows_ready();   // first counter slot of 
 extern "C" __device__ int pipelink_moe_ticket();       // counter slot of the dispatch ticket
 extern "C" __device__ int pipelink_tmem_slot();        // smem byte offset where dispatch put the TMEM base
 
+#ifndef PIPELINK_EMIT
 namespace moe {
 __device__ __forceinline__ uint32_t bar(uint32_t smem_base, int base, int slot = 0) {
   return smem_base + 16u * static_cast<uint32_t>(base + slot);
@@ -155,6 +162,58 @@ __device__ __forceinline__ Tile decode(const MoeGeometry& g, const Walk& w, int 
   return t;
 }
 }  // namespace moe
+#endif  // !PIPELINK_EMIT
+
+// ---- the contracts the owners share, stated once (annotations: <pipelink/stage.hpp>) ----
+#ifdef PIPELINK_EMIT
+namespace moe {
+// The ring both CTAs of a pair fill: A tile | B tile | three scale blocks per slot. The leader
+// CTA's full barrier collects one arrival and one slot payload from each CTA of the pair.
+inline pl::endpoint operands(const char* direction, const char* role) {
+  return pl::endpoint(direction, role).space("smem").scope("cluster").proxy("async")
+      .tile("e4m3+ue8m0", {2, 128, 128})
+      .layout_smem(8, {2, 128, 128}, {TileBytes, 128, 1}, 3, 4, 3)
+      .ring(pl::depth::handle("pipelink_moe_depth"), SlotBytes, SlotTx)
+      .mbarrier(pl::arrivals("pipelink_moe_full", 2, "load", 2 * SlotTx), pl::arrivals("pipelink_moe_empty", 1, "mma"), "load")
+      .bind("base", "pipelink_moe_operands").bind("full", "pipelink_moe_full").bind("empty", "pipelink_moe_empty");
+}
+// 128 lanes x 256 fp32 columns per CTA; the leader's commit completes both CTAs' full barriers,
+// and every epilogue warp of the pair arrives on the leader's empty barrier.
+inline pl::endpoint accumulator(const char* direction, const char* role) {
+  return pl::endpoint(direction, role).space("tmem").scope("cluster").proxy("async")
+      .tile("f32", {128, AccCols})
+      .layout_tmem(32, 0, 128, AccCols)
+      .ring(pl::depth::fixed(1), 128 * AccCols * 4)
+      .mbarrier(pl::arrivals("pipelink_moe_acc_full", 1, "mma"),
+                pl::arrivals("pipelink_moe_acc_empty", 2 * EpilogueWarps, "epilogue"), "mma")
+      .bind("base", "pipelink_moe_acc").bind("full", "pipelink_moe_acc_full").bind("empty", "pipelink_moe_acc_empty");
+}
+// Per row tile, how many of its 256 rows the comm owner has put in place: a grid-scoped counter
+// released with red.release.gpu and acquired by the load owner before its first TMA read of the tile
+// (the reference's counter endpoints: docs/reference/annotations.md, "Counters").
+inline pl::endpoint rows_ready(const char* direction, const char* role) {
+  return pl::endpoint(direction, role).space("gmem").scope("grid").proxy("generic")
+      .tile("e4m3+ue8m0", {256})
+      .counter("pipelink_moe_rows_ready", "red.release.gpu", "ld.acquire.gpu")
+      .bind("slot", "pipelink_moe_rows_ready");
+}
+}  // namespace moe
+#endif
+
+#define MOE_TOPOLOGY() PL_TOPOLOGY(pl::topology().cta_group(2).cluster(2, 1, 1).persistent().scheduler("static"))
+#define MOE_CLAIM_OPERANDS()                                                                   \
+  PL_CLAIM(smem, pipelink_moe_operands, pl::per("pipelink_moe_depth", moe::SlotBytes), 1024);  \
+  PL_CLAIM(mbarrier, pipelink_moe_full, pl::per("pipelink_moe_depth", 1), 1);                  \
+  PL_CLAIM(mbarrier, pipelink_moe_empty, pl::per("pipelink_moe_depth", 1), 1)
+#define MOE_CLAIM_ACCUMULATOR()                                        \
+  PL_CLAIM(tmem, pipelink_moe_acc, pl::units(moe::AccCols), 32);       \
+  PL_CLAIM(mbarrier, pipelink_moe_acc_full, pl::units(1), 1);          \
+  PL_CLAIM(mbarrier, pipelink_moe_acc_empty, pl::units(1), 1)
+#define MOE_CLAIM_STAGING() PL_CLAIM(smem, pipelink_moe_staging, pl::units(moe::EpilogueWarps * 2048), 16)
+#define MOE_CLAIM_ROWS_READY() PL_CLAIM(gmem_counter, pipelink_moe_rows_ready, pl::units(moe::MaxRowTiles), 1)
+// the two register groups of an image: load + MMA + comm warps give registers up, the epilogue takes them
+#define MOE_REGS_HELPER(role) PL_CLAIM_REGS(pipelink_moe_regs_helpers, role, helpers, 56)
+#define MOE_REGS_EPILOGUE(role) PL_CLAIM_REGS(pipelink_moe_regs_epilogue, role, epilogue, 224)
 
 static_assert(sizeof(MoeGeometry) == 48 && sizeof(MoeLoadParams) == 576 && sizeof(MoeMmaParams) == 48 &&
               sizeof(MoeCommParams) == 112 && sizeof(MoeSwigluParams) == 80 && sizeof(MoeRowsParams) == 96,
