@@ -471,6 +471,8 @@ def run_native(args):
     session_streams = world > 1 and session.host.stream_push
     if world > 1 and session.host.fused_dispatch:
         launches_per_step -= 1           # no pull kernel: the gate/up GEMM fetches its own rows
+    if world > 1 and session.host.one_launch:
+        launches_per_step -= 1           # both projections in one launch of the linked forward image
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -579,7 +581,7 @@ def run_native(args):
         del session
         torch.cuda.empty_cache()
         session = None
-        fused = bool(dispatch_choice and dispatch_choice["chosen"] == "in-kernel")
+        fused = bool(dispatch_choice and dispatch_choice["chosen"] != "pull kernel")
         train = leg("ep_fwd_bwd", lambda: ep_train_leg(shape, dev, rank, world, pk, fused_dispatch=fused))
 
     tp_gemm = None
@@ -726,11 +728,19 @@ def linked_leg(session, steps=24):
         return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
     session.step()
     out = {}
+    def two(x):
+        return lambda: (x.gemm_gate_up(), x.gemm_down())
+
+    # `ffn`: both projections, as the library's two launches, the linked images' two launches, and ONE launch
+    # of the linked forward image (pass-2 tiles wait on per-row-tile counters of pass 1; its counter memset is timed)
     for name, fns in (("gate_up", (("library", h.gemm_gate_up), ("linked", linked.gemm_gate_up), ("one_unit", one_tu.gemm_gate_up))),
-                      ("down", (("library", h.gemm_down), ("linked", linked.gemm_down), ("one_unit", one_tu.gemm_down)))):
+                      ("down", (("library", h.gemm_down), ("linked", linked.gemm_down), ("one_unit", one_tu.gemm_down))),
+                      ("ffn", (("library", two(h)), ("linked", linked.forward_ffn), ("one_unit", one_tu.forward_ffn),
+                               ("linked_two_launches", two(linked))))):
         t = {k: [] for k, _ in fns}
+        n = len(fns)
         for i in range(steps + 2):
-            for which, fn in fns[i % 3:] + fns[:i % 3]:      # rotate the order: no arm always runs on the hottest GPU
+            for which, fn in fns[i % n:] + fns[:i % n]:      # rotate the order: no arm always runs on the hottest GPU
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 h.dispatch()                    # other traffic between the launches, as in a step
                 a.record()
@@ -743,6 +753,8 @@ def linked_leg(session, steps=24):
         out[name] = {"library_ms": med["library"], "linked_ms": med["linked"], "one_unit_ms": med["one_unit"],
                      "ratio": med["linked"] / med["one_unit"], "linked_over_library": med["linked"] / med["library"],
                      "spread_ms": {k: [min(v), max(v)] for k, v in t.items()}, "launches_per_arm": steps}
+        if "linked_two_launches" in med:
+            out[name].update(linked_two_launches_ms=med["linked_two_launches"], form="linked / one_unit: one launch; library: two")
     h.status.check("bench (linked images)")
     linked.close()
     one_tu.close()

@@ -202,6 +202,7 @@ class EpMoKHost(mok.MoKHost):
                 nbytes = _lib.load().plb_moe_schedule_streams_scratch_bytes(W, L, k, self.num_local_experts)
                 self.stream_scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.int32, device=dev)
         self._streamed = False
+        self.linked, self.one_launch = None, False      # attach_linked(): the FFN as one launch of the linked forward image
         me = ptrs[rank]
         self.xq = tensor_from_ptr(me + lay.xq, (L, H), torch.uint8, dev)
         self.xsc = tensor_from_ptr(me + lay.xsc, (L // 128, H // 128, 32, 16), torch.uint8, dev)
@@ -316,6 +317,24 @@ class EpMoKHost(mok.MoKHost):
                   s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
                   self.push_rotation, self.push_stride, self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
 
+    def attach_linked(self, linked):
+        """Run the inference forward's expert FFN through the linked forward image (moe_linked.LinkedMoE on
+        this host): dispatch warps, both projections and the combine push in ONE launch."""
+        self.linked, self.one_launch = linked, linked is not None
+
+    def ffn_one_launch(self):
+        """pull() + gemm_gate_up() + gemm_down_push() as one launch of the linked forward image."""
+        s = self.schedule
+        self._streamed = self.stream_push
+        if self._streamed and not self.schedule_writes_streams:
+            self.stream_rows()
+        if not self.fused_dispatch:
+            self.pull()
+        self.linked.forward_ffn(dispatch=self.fused_dispatch,
+                                dest_rows=self.stream_row if self._streamed else s.dest_row,
+                                out_peers=self.recv_peers if self._streamed else self.combine_peers,
+                                rotation=self.push_rotation, stride=self.push_stride)
+
     def fwd_epilogue(self, y_shared=None):
         if not self._streamed:
             return super().fwd_epilogue(y_shared)
@@ -352,12 +371,15 @@ class EpMoKHost(mok.MoKHost):
         if train and self.group.layout.train and self.precision == "mxfp8":
             self.start_token_gather()
         self.build_schedule()
-        self.pull()
-        if train:
-            self.gemm_gate_up_train()
+        if self.one_launch and not train:
+            self.ffn_one_launch()
         else:
-            self.gemm_gate_up()
-        self.gemm_down_push(train)
+            self.pull()
+            if train:
+                self.gemm_gate_up_train()
+            else:
+                self.gemm_gate_up()
+            self.gemm_down_push(train)
         self.barrier()          # every rank's rows have landed in my combine buffer
         return self.fwd_epilogue()
 
@@ -595,6 +617,11 @@ class BenchSession:
         if self.train:
             h.start_token_gather()
         h.build_schedule()
+        if h.one_launch and not self.train:
+            h.ffn_one_launch()
+            h.barrier()
+            h.fwd_epilogue()
+            return
         h.pull()
         gate_up = h.gemm_gate_up_train if self.train else h.gemm_gate_up
         if record:
@@ -617,18 +644,29 @@ class BenchSession:
         self.host.status.check("bench (EP)")
 
     def choose_dispatch(self, steps: int = 6):
-        """Decide where the dispatch runs by timing it: `steps` steps with the pull kernel in front of
-        the gate/up GEMM and `steps` with the dispatch warps inside it, device time, slowest rank;
-        the faster stays on. Whether rows arriving under the mainloop beat rows fetched before it
-        depends on how many of them are remote, so it is measured on the group at hand. Returns both
-        times in ms per step. Forward sessions of the MXFP8 precision only."""
+        """Decide the form of the expert FFN by timing it: `steps` steps with the pull kernel in front of
+        the gate/up GEMM, `steps` with the dispatch warps inside it and, when the linked images are
+        there, `steps` with the whole FFN (dispatch warps, both projections, combine push) as ONE
+        launch of the linked forward image; device time, slowest rank; the fastest stays on. Whether
+        rows arriving under the mainloop beat rows fetched before it depends on how many of them are
+        remote, so it is measured on the group at hand. Returns the times in ms per step. Forward
+        sessions of the MXFP8 precision only."""
         import torch.distributed as dist
         h = self.host
         if self.train or h.precision != "mxfp8" or h.shape.hidden > 4096:
             return None
         times, failed = {}, None
-        for name, fused in (("pull kernel", False), ("in-kernel", True)):
+        forms = [("pull kernel", False, False), ("in-kernel", True, False)]
+        linked = None
+        try:
+            from . import moe_linked
+            linked = moe_linked.LinkedMoE(h)
+            forms.append(("one launch (linked image)", True, True))
+        except Exception:  # noqa: BLE001 - images absent: the library's launches are timed alone
+            linked = None
+        for name, fused, one in forms:
             h.fused_dispatch = fused
+            h.attach_linked(linked if one else None)
             for _ in range(2):
                 self.step()
             torch.cuda.synchronize()
@@ -644,7 +682,7 @@ class BenchSession:
             bad = torch.tensor([int(h.status.buf[0].item() != 0)], dtype=torch.int32, device=self.dev)
             dist.all_reduce(bad, op=dist.ReduceOp.MAX)
             if bad.item():
-                failed = name
+                failed = name if failed is None else f"{failed}, {name}"
                 h.status.reset()
                 torch.cuda.synchronize()
                 dist.barrier()
@@ -654,10 +692,16 @@ class BenchSession:
             times[name] = float(t.item())
         if "pull kernel" not in times:
             raise RuntimeError("the expert-parallel step reports a device status with the pull kernel")
-        h.fused_dispatch = "in-kernel" in times and times["in-kernel"] < times["pull kernel"]
+        chosen = min(times, key=times.get)
+        _, fused, one = next(f for f in forms if f[0] == chosen)
+        h.fused_dispatch = fused
+        h.attach_linked(linked if one else None)
+        if linked is not None and not one:
+            linked.close()
+        out = {"ms_per_step": times, "chosen": chosen}
         if failed:
-            return {"ms_per_step": times, "chosen": "pull kernel", "rejected": f"{failed}: device status during its timing"}
-        return {"ms_per_step": times, "chosen": "in-kernel" if h.fused_dispatch else "pull kernel"}
+            out["rejected"] = f"{failed}: device status during its timing"
+        return out
 
     def traffic_per_launch(self):
         return None

@@ -6,6 +6,8 @@ launched here on the buffers of a ``MoKHost`` session in place of the library's 
     linked = LinkedMoE(host)            # loads the three images, builds their parameter blocks
     host.schedule_into(...); host.dispatch()
     linked.gemm_gate_up(); linked.gemm_down(); host.fwd_epilogue()
+    # or both projections in ONE launch (pass-2 tiles wait on per-row-tile counters of pass 1):
+    linked.forward_ffn(); host.fwd_epilogue()
 
 The stage sources are the library kernel's warp roles with every constant the link decides
 (ring depth, shared-memory / barrier / tensor-memory bases, warp numbers, counter slots) read
@@ -25,7 +27,7 @@ from . import _lib, mok
 from .pipec2.launcher import Session
 
 OUT_DIR = Path(__file__).resolve().parent / "stages" / "moe" / "out"
-COMPOSITIONS = ("gate_up", "gate_up_dispatch", "down")
+COMPOSITIONS = ("gate_up", "gate_up_dispatch", "down", "fwd", "fwd_dispatch")
 
 
 def ensure_built() -> Path:
@@ -63,7 +65,7 @@ class LinkedMoE:
         slots = self.sessions["gate_up_dispatch"].link["bindings"]
         self.rows_ready_slot, self.ticket_slot = slots["pipelink_moe_rows_ready"][0], slots["pipelink_moe_ticket"][0]
         # the images' counter workspace (gmem_counter domain): zeroed on the stream before a launch that uses it
-        self.counters = torch.zeros(4096 + 64, dtype=torch.int32, device=host.device)
+        self.counters = torch.zeros(2 * 4096 + 64, dtype=torch.int32, device=host.device)
         self.sms = torch.cuda.get_device_properties(host.device).multi_processor_count & ~1
         self.inf = float("inf")
 
@@ -115,6 +117,40 @@ class LinkedMoE:
         s.set_params("moe.epilogue.rows-bf16", g + struct.pack("<QQQQii", out.data_ptr(), 0 if out_peers is None else out_peers.data_ptr(),
                                                                 dest.data_ptr(), sched.peer_rank.data_ptr(), sh.hidden, 0))
         self._launch("down")
+
+    def forward_ffn(self, dispatch: bool = False, dest_rows=None, out=None, out_peers=None, rotation: int = 0, stride: int = 1):
+        """Gate/up projection + SwiGLU + requantise, then the down projection with its row placement (or
+        combine push), in ONE launch of a linked image: the work of gemm_gate_up() followed by gemm_down().
+        With dispatch, the comm owner also pulls the routed rows from the home ranks under the mainloop."""
+        h, b, w, sh = self.host, self.host.buffers, self.host.weights, self.host.shape
+        name = "fwd_dispatch" if dispatch else "fwd"
+        s = self.sessions[name]
+        if h.capacity // 256 > 4096 or sh.hidden > 4096:
+            raise ValueError("the forward image counts at most 4096 row tiles of rows up to 4096 bytes")
+        g1 = self._geometry(sh.hidden, 2 * sh.intermediate, rotation, stride)
+        g2 = self._geometry(sh.intermediate, sh.hidden, rotation, stride)
+        self.counters.zero_()
+        counters = self.counters.data_ptr()
+        sched = h.schedule
+        if dispatch:
+            s.set_params("moe.comm.dispatch", g1 + struct.pack("<QQQQQQQii", h.xq_peers.data_ptr(), h.xsc_rows_peers.data_ptr(),
+                                                               sched.peer_rank.data_ptr(), sched.peer_token_idx.data_ptr(),
+                                                               b["x_routed_fp8"].data_ptr(), b["x_routed_sc"].data_ptr(),
+                                                               counters, sh.hidden, 0))
+        s.set_params("moe.fwd.load",
+                     _operand_map(b["x_routed_fp8"]) + _operand_map(w["w13_fp8"]) + _scale_map(b["x_routed_sc"]) +
+                     _scale_map(w["w13_sc"]) + _operand_map(b["hidden_routed_fp8"]) + _operand_map(w["w_routed_down_fp8"]) +
+                     _scale_map(b["hidden_routed_sc"]) + _scale_map(w["w_routed_down_sc"]) + g1 + g2 +
+                     struct.pack("<Qii", counters, 1 if dispatch else 0, 0))
+        s.set_params("moe.fwd.mma", g1 + g2)
+        dest = sched.dest_row if dest_rows is None else dest_rows
+        out = b["combine_buffer"] if out is None else out
+        limit = h.swiglu_limit if h.swiglu_limit > 0 else self.inf
+        s.set_params("moe.fwd.epilogue", g1 + g2 + struct.pack(
+            "<QQQQQQQiifi", b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(), out.data_ptr(),
+            0 if out_peers is None else out_peers.data_ptr(), dest.data_ptr(), sched.peer_rank.data_ptr(), counters,
+            sh.intermediate, sh.hidden, limit, 0))
+        self._launch(name)
 
     def close(self):
         for s in self.sessions.values():

@@ -1,6 +1,7 @@
 """Pack, link and (optionally) build the one-TU control of the three-stage MXFP8 GEMM.
 
-Counterpart of the reference's examples/hopper-gemm-split/build.py: each owner is packed once,
+Counterpart of the reference's examples/hopper-gemm-split/build.py: each owner is packed once
+(its manifest emitted from the PL_* annotations in its source),
 the pipeline description declares the handles (ring depth with candidate values, resource bases),
 and ``link`` solves them. Everything here runs without a GPU.
 
@@ -20,93 +21,30 @@ HERE = Path(__file__).resolve().parent
 SLOT = 2 * 128 * 128 + 2 * 512          # gemm3::SlotBytes
 ABI = {"schema": "3.0", "target": {"profile": "sm_100a", "lto_arch": "lto_100a", "toolkit": "cuda-12.9",
                                    "math": {"ftz": False, "prec_div": True, "prec_sqrt": True, "fmad": True}}}
-SIG = "void(const void* params, unsigned variant)"
+STAGES = ("load", "mma", "epilogue_bias_silu")
+_manifests = None
 
 
-def _operands(direction, role):
-    return {"name": "operands", "direction": direction, "owner_role": role, "space": "smem", "scope": "cta", "proxy": "async",
-            "tile": {"dtype": "e4m3+ue8m0", "shape": [2, 128, 128]},
-            "layout": {"encoding": "pl-layout-v2", "elem_bits": 8, "shape": [[2], [128], [128]],
-                       "stride": [[16384], [128], [1]], "swizzle": {"B": 3, "M": 4, "S": 3}},
-            "ring": {"depth": {"handle": "pipelink_gemm_depth"}, "stage_stride_bytes": SLOT},
-            "protocol": {"kind": "mbarrier",
-                         "full": {"slots": "pipelink_gemm_full", "arrive": {"count": 1, "by": "load"}, "tx_bytes": SLOT},
-                         "empty": {"slots": "pipelink_gemm_empty", "arrive": {"count": 1, "by": "mma"}, "tx_bytes": 0},
-                         "init": {"owner": "load", "phase": 0, "materializer": "dispatch"}, "release": "once-per-acquire"},
-            "binds": {"base": "pipelink_gemm_operands", "full": "pipelink_gemm_full", "empty": "pipelink_gemm_empty"}}
+def manifests() -> dict:
+    """{stage file stem: manifest}: what each unit's PL_* annotations state (the unit's host projection,
+    run with g++; the undefined-symbol list is added at pack time)."""
+    global _manifests
+    if _manifests is None:
+        emitted = [packer.emit_manifest(HERE / f"{n}.cu") for n in STAGES]
+        for m in emitted:
+            m["pipelink_abi"] = json.loads(json.dumps(ABI))
+            m["symbols"].update(mechanism="ptx-extern", defined_weak=[], undefined={})
+            m["provenance"], m["payload"] = {}, {"file": "stage.o"}
+        _manifests = dict(zip(STAGES, emitted))
+    return _manifests
 
 
-def _accumulator(direction, role):
-    return {"name": "accumulator", "direction": direction, "owner_role": role, "space": "tmem", "scope": "cta", "proxy": "async",
-            "tile": {"dtype": "f32", "shape": [128, 128]},
-            "layout": {"encoding": "pl-layout-v2", "elem_bits": 32, "lanes": [0, 128], "cols": 128},
-            "ring": {"depth": {"fixed": 1}, "stage_stride_bytes": 65536},
-            "protocol": {"kind": "mbarrier",
-                         "full": {"slots": "pipelink_gemm_acc_ready", "arrive": {"count": 1, "by": "mma"}, "tx_bytes": 0},
-                         "empty": {"slots": "pipelink_gemm_acc_empty", "arrive": {"count": 4, "by": "epilogue"}, "tx_bytes": 0},
-                         "init": {"owner": "mma", "phase": 0, "materializer": "dispatch"}, "release": "once-per-acquire"},
-            "binds": {"base": "pipelink_gemm_acc", "full": "pipelink_gemm_acc_ready", "empty": "pipelink_gemm_acc_empty"}}
+def __getattr__(name):
+    if name == "MANIFESTS":
+        return manifests()
+    raise AttributeError(name)
 
 
-OPERAND_CLAIMS = [
-    {"domain": "smem", "handle": "pipelink_gemm_operands", "extent": {"const": 0, "per": {"pipelink_gemm_depth": SLOT}}, "align": 1024, "lifetime": "kernel"},
-    {"domain": "mbarrier", "handle": "pipelink_gemm_full", "extent": {"const": 0, "per": {"pipelink_gemm_depth": 1}}, "align": 1, "lifetime": "kernel"},
-    {"domain": "mbarrier", "handle": "pipelink_gemm_empty", "extent": {"const": 0, "per": {"pipelink_gemm_depth": 1}}, "align": 1, "lifetime": "kernel"},
-]
-ACC_CLAIMS = [
-    {"domain": "tmem", "handle": "pipelink_gemm_acc", "extent": {"const": 128, "per": {}}, "align": 32, "lifetime": "kernel"},
-    {"domain": "mbarrier", "handle": "pipelink_gemm_acc_ready", "extent": {"const": 1, "per": {}}, "align": 1, "lifetime": "kernel"},
-    {"domain": "mbarrier", "handle": "pipelink_gemm_acc_empty", "extent": {"const": 1, "per": {}}, "align": 1, "lifetime": "kernel"},
-]
-SF_CLAIM = {"domain": "tmem", "handle": "pipelink_gemm_sf", "extent": {"const": 0, "per": {"pipelink_gemm_depth": 8}}, "align": 32, "lifetime": "kernel"}
-
-
-def _warp(handle, n, role, align=1):
-    return {"domain": "warp", "handle": handle, "extent": {"const": n, "per": {}}, "align": align, "lifetime": "kernel", "roles": [role]}
-
-
-def _layout_probe(type_name: str) -> str:
-    """sha256 over the parameter struct's definition in gemm3.cuh (whitespace-normalised): the
-    manifest's `sha256_of_layout_probe`, which changes whenever a field, its type or order does."""
-    import hashlib
-    import re
-    text = (HERE / "gemm3.cuh").read_text()
-    m = re.search(r"struct\s+(alignas\(\d+\)\s+)?" + type_name + r"\s*\{.*?\};", text, re.S)
-    if m is None:
-        raise ValueError(f"{type_name} is not defined in gemm3.cuh")
-    return hashlib.sha256(" ".join(m.group(0).split()).encode()).hexdigest()
-
-
-def _manifest(stage_id, prefix, role, entry, warps, endpoints, claims, params, undefined):
-    params = dict(params, sha256_of_layout_probe=_layout_probe(params["type"]))
-    return {"pipelink_abi": json.loads(json.dumps(ABI)),
-            "stage": {"id": stage_id, "version": "1.0.0", "symbol_prefix": prefix, "entry_abi": "v2",
-                      "roles": {role: {"entry": entry, "warps": warps}}, "exports": {}, "entry_signature": SIG,
-                      "variants": [{"key": {}, "index": 0}]},
-            "endpoints": endpoints, "claims": claims,
-            "topology": {"cta_group": {"fixed": 1}, "cluster": {"compiled": [1, 1, 1], "launch": {"x_multiple_of": 1, "max": [1, 1, 1]}}, "multicast": [], "persistent": False, "scheduler": "static"},
-            "params": params, "hints": {},
-            "symbols": {"mechanism": "declared", "defined_strong": [entry], "defined_weak": [], "undefined": {u: "function" for u in undefined}},
-            "provenance": {}, "payload": {"file": "stage.o"}}
-
-
-MANIFESTS = {
-    "load": _manifest("gemm.load", "gemm_load_", "load", "gemm_load_role", 1, [_operands("produce", "load")],
-                      [_warp("pipelink_gemm_warp_load", 1, "load"), *OPERAND_CLAIMS],
-                      {"bytes": 320, "align": 64, "type": "Gemm3LoadParams"},
-                      ["pipelink_gemm_depth", "pipelink_gemm_operands", "pipelink_gemm_full", "pipelink_gemm_empty"]),
-    "mma": _manifest("gemm.mma", "gemm_mma_", "mma", "gemm_mma_role", 1,
-                     [_operands("consume", "mma"), _accumulator("produce", "mma")],
-                     [_warp("pipelink_gemm_warp_mma", 1, "mma"), *OPERAND_CLAIMS, *ACC_CLAIMS, SF_CLAIM],
-                     {"bytes": 16, "align": 16, "type": "Gemm3MmaParams"},
-                     ["pipelink_gemm_depth", "pipelink_gemm_operands", "pipelink_gemm_full", "pipelink_gemm_empty",
-                      "pipelink_gemm_acc", "pipelink_gemm_sf", "pipelink_gemm_acc_ready", "pipelink_gemm_acc_empty", "pipelink_tmem_slot"]),
-    "epilogue_bias_silu": _manifest("gemm.epilogue.bias-silu", "gemm_epilogue_bias_silu_", "epilogue",
-                                    "gemm_epilogue_bias_silu_role", 4, [_accumulator("consume", "epilogue")],
-                                    [_warp("pipelink_gemm_warp_epilogue", 4, "epilogue", align=4), *ACC_CLAIMS],
-                                    {"bytes": 32, "align": 16, "type": "Gemm3EpilogueParams"},
-                                    ["pipelink_gemm_acc", "pipelink_gemm_acc_ready", "pipelink_gemm_acc_empty", "pipelink_tmem_slot"]),
-}
 BASE_HANDLES = {"pipelink_gemm_operands": "smem", "pipelink_gemm_full": "mbarrier", "pipelink_gemm_empty": "mbarrier",
                 "pipelink_gemm_acc_ready": "mbarrier", "pipelink_gemm_acc_empty": "mbarrier", "pipelink_gemm_acc": "tmem", "pipelink_gemm_sf": "tmem",
                 "pipelink_gemm_warp_load": "warp", "pipelink_gemm_warp_mma": "warp", "pipelink_gemm_warp_epilogue": "warp"}
@@ -132,25 +70,18 @@ def build_provider(out: Path) -> Path:
     if lib.exists() and all(d.stat().st_mtime <= lib.stat().st_mtime for d in deps):
         return lib
     cmd = [jitlink.nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr",
-           "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(lib), str(src)]
+           "-gencode", "arch=compute_100a,code=sm_100a", "-I", str(packer.INCLUDE), "-o", str(lib), str(src)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("provider build failed:\n" + proc.stderr[-3000:])
     return lib
 
 
-def write_manifests():
-    for name, m in MANIFESTS.items():
-        (HERE / f"{name}.manifest.json").write_text(json.dumps(m, indent=1, sort_keys=True) + "\n")
-
-
 def build(out: Path, depth=None, one_tu=True):
     out.mkdir(parents=True, exist_ok=True)
-    write_manifests()
     stages = []
-    for name, m in MANIFESTS.items():
-        pkg = out / f"{name}.plink"
-        packer.pack_cu(HERE / f"{name}.cu", HERE / f"{name}.manifest.json", pkg)
+    for name, m in manifests().items():
+        packer.pack_cu(HERE / f"{name}.cu", None, out / f"{name}.plink")
         stages.append({"stage_id": m["stage"]["id"], "artifact_path": f"{name}.plink"})
     spec = out / "pipeline.json"
     spec.write_text(json.dumps(pipeline_spec(stages, depth), indent=1))
@@ -159,10 +90,11 @@ def build(out: Path, depth=None, one_tu=True):
     if one_tu:
         # same-source single translation unit: the parity denominator for the linked image
         tu = out / "link" / "generated" / "one_tu.cu"
-        tu.write_text("".join(f'#include "{HERE / (n + ".cu")}"\n' for n in MANIFESTS) +
+        tu.write_text("".join(f'#include "{HERE / (n + ".cu")}"\n' for n in STAGES) +
                       '#include "binding_stub.cu"\n#include "dispatch.cu"\n')
         cmd = [jitlink.nvcc(), "-cubin", "-O3", "-std=c++17", "--expt-relaxed-constexpr", "-gencode",
-               "arch=compute_100a,code=sm_100a", "-I", str(tu.parent), "-o", str(out / "link" / "one_tu.cubin"), str(tu)]
+               "arch=compute_100a,code=sm_100a", "-I", str(tu.parent), "-I", str(packer.INCLUDE), "-o",
+               str(out / "link" / "one_tu.cubin"), str(tu)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError("one-TU control failed:\n" + proc.stderr[-3000:])

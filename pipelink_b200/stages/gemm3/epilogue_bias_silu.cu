@@ -1,8 +1,17 @@
 // Stage gemm.epilogue.bias-silu: four warps drain the accumulator, add bias, apply SiLU, store bf16.
-#include <cuda_bf16.h>
-
 #include "gemm3.cuh"
 
+extern "C" __device__ void gemm_epilogue_bias_silu_role(const void* params, unsigned variant);
+PL_STAGE("gemm.epilogue.bias-silu", "1.0.0");
+PL_PARAMS(Gemm3EpilogueParams, bias, out, N);
+PL_ROLE(epilogue, gemm_epilogue_bias_silu_role, 4);
+GEMM3_TOPOLOGY();
+PL_ENDPOINT(accumulator, gemm3::accumulator(pl::consume, "epilogue"));
+PL_CLAIM_WARPS(pipelink_gemm_warp_epilogue, epilogue, 4, 4);
+GEMM3_CLAIM_ACCUMULATOR();
+
+#ifndef PIPELINK_EMIT
+#include <cuda_bf16.h>
 extern "C" __device__ void gemm_epilogue_bias_silu_role(const void* raw_params, unsigned) {
   using namespace gemm3;
   const Gemm3EpilogueParams& p = *static_cast<const Gemm3EpilogueParams*>(raw_params);
@@ -45,3 +54,4 @@ extern "C" __device__ void gemm_epilogue_bias_silu_role(const void* raw_params, 
   __syncwarp();
   if (lane == 0) plb::mbar_arrive(barrier_addr(smem, pipelink_gemm_acc_empty()));
 }
+#endif  // !PIPELINK_EMIT

@@ -13,7 +13,11 @@
 #include <cuda.h>
 #include <stdint.h>
 
+#include <pipelink/stage.hpp>
+
+#ifndef PIPELINK_EMIT
 #include "../../csrc/common.cuh"
+#endif
 
 namespace gemm3 {
 constexpr int TileM = 128, TileN = 128, TileK = 128;          // TileK in bytes = E4M3 elements
@@ -54,6 +58,7 @@ extern "C" __device__ int pipelink_gemm_sf();          // first TMEM column of t
 extern "C" __device__ int pipelink_tmem_slot();        // smem byte offset where dispatch put the TMEM base
 extern "C" __device__ int pipelink_gemm_warp_epilogue();
 
+#ifndef PIPELINK_EMIT
 namespace gemm3 {
 __device__ __forceinline__ uint32_t barrier_addr(uint32_t smem_base, int base, int slot = 0) {
   return smem_base + 16u * static_cast<uint32_t>(base + slot);
@@ -67,3 +72,36 @@ __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
   return true;
 }
 }  // namespace gemm3
+#endif  // !PIPELINK_EMIT
+
+// ---- the contracts the three owners share (annotations: <pipelink/stage.hpp>) ----
+#ifdef PIPELINK_EMIT
+namespace gemm3 {
+inline pl::endpoint operands(const char* direction, const char* role) {
+  return pl::endpoint(direction, role).space("smem").scope("cta").proxy("async")
+      .tile("e4m3+ue8m0", {2, 128, 128})
+      .layout_smem(8, {2, 128, 128}, {OperandBytes, 128, 1}, 3, 4, 3)
+      .ring(pl::depth::handle("pipelink_gemm_depth"), SlotBytes)
+      .mbarrier(pl::arrivals("pipelink_gemm_full", 1, "load", SlotBytes), pl::arrivals("pipelink_gemm_empty", 1, "mma"), "load")
+      .bind("base", "pipelink_gemm_operands").bind("full", "pipelink_gemm_full").bind("empty", "pipelink_gemm_empty");
+}
+inline pl::endpoint accumulator(const char* direction, const char* role) {
+  return pl::endpoint(direction, role).space("tmem").scope("cta").proxy("async")
+      .tile("f32", {128, AccCols})
+      .layout_tmem(32, 0, 128, AccCols)
+      .ring(pl::depth::fixed(1), 128 * AccCols * 4)
+      .mbarrier(pl::arrivals("pipelink_gemm_acc_ready", 1, "mma"), pl::arrivals("pipelink_gemm_acc_empty", 4, "epilogue"), "mma")
+      .bind("base", "pipelink_gemm_acc").bind("full", "pipelink_gemm_acc_ready").bind("empty", "pipelink_gemm_acc_empty");
+}
+}  // namespace gemm3
+#endif
+
+#define GEMM3_TOPOLOGY() PL_TOPOLOGY(pl::topology().cta_group(1).cluster(1, 1, 1))
+#define GEMM3_CLAIM_OPERANDS()                                                                     \
+  PL_CLAIM(smem, pipelink_gemm_operands, pl::per("pipelink_gemm_depth", gemm3::SlotBytes), 1024);  \
+  PL_CLAIM(mbarrier, pipelink_gemm_full, pl::per("pipelink_gemm_depth", 1), 1);                    \
+  PL_CLAIM(mbarrier, pipelink_gemm_empty, pl::per("pipelink_gemm_depth", 1), 1)
+#define GEMM3_CLAIM_ACCUMULATOR()                                      \
+  PL_CLAIM(tmem, pipelink_gemm_acc, pl::units(gemm3::AccCols), 32);    \
+  PL_CLAIM(mbarrier, pipelink_gemm_acc_ready, pl::units(1), 1);        \
+  PL_CLAIM(mbarrier, pipelink_gemm_acc_empty, pl::units(1), 1)

@@ -1,6 +1,16 @@
 // Stage gemm.load: one elected lane feeds the operands ring with TMA.
 #include "gemm3.cuh"
 
+extern "C" __device__ void gemm_load_role(const void* params, unsigned variant);
+PL_STAGE("gemm.load", "1.0.0");
+PL_PARAMS(Gemm3LoadParams, a, b, a_sc, b_sc, K);
+PL_ROLE(load, gemm_load_role, 1);
+GEMM3_TOPOLOGY();
+PL_ENDPOINT(operands, gemm3::operands(pl::produce, "load"));
+PL_CLAIM_WARPS(pipelink_gemm_warp_load, load, 1, 1);
+GEMM3_CLAIM_OPERANDS();
+
+#ifndef PIPELINK_EMIT
 extern "C" __device__ void gemm_load_role(const void* raw_params, unsigned) {
   using namespace gemm3;
   const Gemm3LoadParams& p = *static_cast<const Gemm3LoadParams*>(raw_params);
@@ -23,3 +33,4 @@ extern "C" __device__ void gemm_load_role(const void* raw_params, unsigned) {
     plb::bulk_load(dst + 2 * OperandBytes + ScaleBytes, p.b_sc + (static_cast<size_t>(n_blk) * k_steps + k) * ScaleBytes, ScaleBytes, full);
   }
 }
+#endif  // !PIPELINK_EMIT

@@ -1,6 +1,19 @@
 // Stage gemm.mma: one elected lane issues block-scaled tcgen05 MMAs into tensor memory.
 #include "gemm3.cuh"
 
+extern "C" __device__ void gemm_mma_role(const void* params, unsigned variant);
+PL_STAGE("gemm.mma", "1.0.0");
+PL_PARAMS(Gemm3MmaParams, K);
+PL_ROLE(mma, gemm_mma_role, 1);
+GEMM3_TOPOLOGY();
+PL_ENDPOINT(operands, gemm3::operands(pl::consume, "mma"));
+PL_ENDPOINT(accumulator, gemm3::accumulator(pl::produce, "mma"));
+PL_CLAIM_WARPS(pipelink_gemm_warp_mma, mma, 1, 1);
+GEMM3_CLAIM_OPERANDS();
+GEMM3_CLAIM_ACCUMULATOR();
+PL_CLAIM(tmem, pipelink_gemm_sf, pl::per("pipelink_gemm_depth", gemm3::ScaleColsPerSlot), 32);
+
+#ifndef PIPELINK_EMIT
 extern "C" __device__ void gemm_mma_role(const void* raw_params, unsigned) {
   using namespace gemm3;
   const Gemm3MmaParams& p = *static_cast<const Gemm3MmaParams*>(raw_params);
@@ -29,3 +42,4 @@ extern "C" __device__ void gemm_mma_role(const void* raw_params, unsigned) {
   }
   plb::tc_commit(barrier_addr(smem, pipelink_gemm_acc_ready()));
 }
+#endif  // !PIPELINK_EMIT

@@ -9,6 +9,8 @@ campaigns/mok/README.md:80-118):
     gate_up            load + mma + comm.none     + epilogue.swiglu-mxfp8   (rows already in place)
     gate_up_dispatch   load + mma + comm.dispatch + epilogue.swiglu-mxfp8   (rows pulled in the kernel)
     down               load + mma + comm.none     + epilogue.rows-bf16      (placement or combine push)
+    fwd                fwd.load + fwd.mma + comm.none     + fwd.epilogue    (both projections, one launch)
+    fwd_dispatch       fwd.load + fwd.mma + comm.dispatch + fwd.epilogue    (dispatch, both projections, combine push)
 
 The link solves the ring depth of the ``operands`` channel, every shared-memory / barrier /
 tensor-memory / counter base, the warp tiling and the two register groups. Runs without a GPU.
@@ -31,11 +33,12 @@ TILE, SF = 128 * 128, 512
 SLOT_TX = 2 * TILE + 3 * SF               # moe::SlotTx
 SLOT = SLOT_TX + 512                      # moe::SlotBytes
 MAX_ROW_TILES = 4096                      # moe::MaxRowTiles
+COUNTER_SLOTS = 2 * MAX_ROW_TILES + 64    # rows_ready + hidden_ready + the dispatch ticket: the images' counter workspace
 ABI = {"schema": "3.0", "target": {"profile": "sm_100a", "lto_arch": "lto_100a", "toolkit": "cuda-12.9",
                                    "math": {"ftz": False, "prec_div": True, "prec_sqrt": True, "fmad": True}}}
 HELPERS = ("pipelink_moe_regs_helpers", "helpers", 56)     # load + mma + comm: one warpgroup
 EPILOGUE = ("pipelink_moe_regs_epilogue", "epilogue", 224)  # two warpgroups
-STAGES = ("load", "mma", "comm_none", "comm_dispatch", "epilogue_swiglu", "epilogue_rows")
+STAGES = ("load", "mma", "comm_none", "comm_dispatch", "epilogue_swiglu", "epilogue_rows", "fwd_load", "fwd_mma", "fwd_epilogue")
 _manifests = None
 
 
@@ -62,8 +65,11 @@ COMPOSITIONS = {
     "gate_up": ["load", "mma", "comm_none", "epilogue_swiglu"],
     "gate_up_dispatch": ["load", "mma", "comm_dispatch", "epilogue_swiglu"],
     "down": ["load", "mma", "comm_none", "epilogue_rows"],
+    "fwd": ["fwd_load", "fwd_mma", "comm_none", "fwd_epilogue"],
+    "fwd_dispatch": ["fwd_load", "fwd_mma", "comm_dispatch", "fwd_epilogue"],
 }
-BASE_DOMAINS = {"pipelink_moe_operands": "smem", "pipelink_moe_staging": "smem", "pipelink_moe_full": "mbarrier",
+BASE_DOMAINS = {"pipelink_moe_operands": "smem", "pipelink_moe_staging": "smem", "pipelink_moe_dispatch_ring": "smem",
+                "pipelink_moe_hidden_ready": "gmem_counter", "pipelink_moe_full": "mbarrier",
                 "pipelink_moe_empty": "mbarrier", "pipelink_moe_acc_full": "mbarrier", "pipelink_moe_acc_empty": "mbarrier",
                 "pipelink_moe_drain": "mbarrier", "pipelink_moe_acc": "tmem", "pipelink_moe_sfcols": "tmem",
                 "pipelink_moe_warp_load": "warp", "pipelink_moe_warp_mma": "warp", "pipelink_moe_warp_comm": "warp",
@@ -81,7 +87,7 @@ def pipeline_spec(name, members, stages, depth=None, values=(6, 5, 4, 3, 2)):
         handles[handle] = {"class": "regs", "binding": "bind", "domain": "regs", "values": [value], "owner": f"reg_group:{group}"}
     return {"pipelink_abi": ABI,
             "pipeline": {"name": f"moe-{name.replace('_', '-')}", "stages": stages, "handles": handles, "phases": ["steady"],
-                         "exclusive": [], "domains": {"gmem_counter": {"capacity": MAX_ROW_TILES + 64}},
+                         "exclusive": [], "domains": {"gmem_counter": {"capacity": COUNTER_SLOTS}},
                          "depth_priority": ["pipelink_moe_depth"], "regs_priority": [EPILOGUE[0], HELPERS[0]],
                          "forced_bindings": {} if depth is None else {"pipelink_moe_depth": depth},
                          "topology": {"persistent": True, "scheduler": "static"}}}

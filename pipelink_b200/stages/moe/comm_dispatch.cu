@@ -16,7 +16,7 @@ MOE_TOPOLOGY();
 PL_ENDPOINT(rows_ready, moe::rows_ready(pl::produce, "comm"));
 PL_CLAIM_WARPS(pipelink_moe_warp_comm, comm, 2, 1);
 MOE_REGS_HELPER(comm);
-MOE_CLAIM_STAGING();
+PL_CLAIM(smem, pipelink_moe_dispatch_ring, pl::units(2 * 8192), 16);
 MOE_CLAIM_ROWS_READY();
 PL_CLAIM(gmem_counter, pipelink_moe_ticket, pl::units(1), 1);
 
@@ -29,8 +29,7 @@ extern "C" __device__ void moe_comm_dispatch_role(const void* raw_params, unsign
   const int warp = static_cast<int>(threadIdx.x >> 5) - pipelink_moe_warp_comm();
   const Walk w = make_walk(p.g, lane, false);
   constexpr int kTicketRows = 2;
-  // the ring is the staging area of the row-store epilogue, which the gate/up composition does not use
-  const uint32_t ring = plb::smem_u32(pl_smem) + pipelink_moe_staging() + static_cast<uint32_t>(warp) * (kTicketRows * 4096);
+  const uint32_t ring = plb::smem_u32(pl_smem) + pipelink_moe_dispatch_ring() + static_cast<uint32_t>(warp) * (kTicketRows * 4096);
   const int vecs = p.row_bytes >> 4;          // <= 256
   const int col_blocks = p.row_bytes >> 7;
   const int rows_live = w.m_tiles_live * 256;

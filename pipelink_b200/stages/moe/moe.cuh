@@ -93,6 +93,34 @@ struct alignas(16) MoeRowsParams {
   int pad;
 };
 
+// ---- the one-launch forward: gate/up projection tiles, then down projection tiles, one tile list ----
+struct alignas(64) MoeFwdLoadParams {
+  CUtensorMap a1, b1, sfa1, sfb1;   // pass 1: routed rows x interleaved gate/up weights
+  CUtensorMap a2, b2, sfa2, sfb2;   // pass 2: hidden rows (written by this launch) x down weights
+  MoeGeometry g1, g2;               // same schedule, K steps and column tiles of each pass
+  const unsigned* counters;         // slot pipelink_moe_hidden_ready() + m_tile counts epilogue warps done with the
+                                    // row tile's pass-1 tiles; pipelink_moe_rows_ready() + m_tile as in MoeLoadParams
+  int wait_rows_ready;              // 1 when a comm owner pulls the rows under the mainloop
+  int pad;
+};
+struct alignas(16) MoeFwdMmaParams {
+  MoeGeometry g1, g2;
+};
+struct alignas(16) MoeFwdEpilogueParams {
+  MoeGeometry g1, g2;
+  uint8_t* hidden;               // pass 1 out: E4M3 [rows, hidden_cols]
+  uint8_t* hidden_sc;
+  uint8_t* out;                  // pass 2 out: bf16 rows, local placement
+  uint8_t* const* out_peers;     // or per-rank bases (push), null for local
+  const int* dest_row;
+  const int* peer_rank;
+  unsigned* counters;
+  int hidden_cols;               // I
+  int out_cols;                  // H
+  float limit;                   // +inf: plain SwiGLU
+  int pad;
+};
+
 extern "C" __device__ int pipelink_moe_depth();
 extern "C" __device__ int pipelink_moe_operands();     // smem byte offset of the ring
 extern "C" __device__ int pipelink_moe_full();         // first mbarrier slot (16 bytes each)
@@ -102,11 +130,13 @@ extern "C" __device__ int pipelink_moe_acc_empty();
 extern "C" __device__ int pipelink_moe_drain();        // mbarrier slot the MMA owner drains through on failure
 extern "C" __device__ int pipelink_moe_acc();          // first TMEM column of the accumulator
 extern "C" __device__ int pipelink_moe_sfcols();       // first TMEM column of the scale slots
-extern "C" __device__ int pipelink_moe_staging();      // smem byte offset: 2 KiB per epilogue warp / dispatch ring
+extern "C" __device__ int pipelink_moe_staging();      // smem byte offset: 2 KiB per epilogue warp (row stores)
 extern "C" __device__ int pipelink_moe_warp_epilogue();// first warp of the epilogue role
 extern "C" __device__ int pipelink_moe_warp_comm();    // first warp of the comm role
 extern "C" __device__ int pipelink_moe_rows_ready();   // first counter slot of the per-row-tile counts (gmem_counter domain)
 extern "C" __device__ int pipelink_moe_ticket();       // counter slot of the dispatch ticket
+extern "C" __device__ int pipelink_moe_hidden_ready(); // first counter slot of the per-row-tile pass-1 completion counts
+extern "C" __device__ int pipelink_moe_dispatch_ring();// smem byte offset: 8 KiB per dispatch warp
 extern "C" __device__ int pipelink_tmem_slot();        // smem byte offset where dispatch put the TMEM base
 
 #ifndef PIPELINK_EMIT
@@ -148,6 +178,20 @@ __device__ __forceinline__ Walk make_walk(const MoeGeometry& g, int lane, bool r
     }
   }
   return w;
+}
+
+// the tile list of the one-launch forward: every pass-1 tile, then every pass-2 tile, row tiles in
+// the same order in both (a pass-2 tile's hidden rows were finished long before it is reached)
+struct FwdWalk {
+  Walk w;
+  int tiles1, total;
+};
+__device__ __forceinline__ FwdWalk make_fwd_walk(const MoeGeometry& g1, const MoeGeometry& g2, int lane, bool report) {
+  FwdWalk f;
+  f.w = make_walk(g1, lane, report);
+  f.tiles1 = f.w.total_tiles;
+  f.total = f.tiles1 + f.w.m_tiles_live * g2.n_tiles;
+  return f;
 }
 
 __device__ __forceinline__ Tile decode(const MoeGeometry& g, const Walk& w, int tile, int cta_rank) {
@@ -197,6 +241,14 @@ inline pl::endpoint rows_ready(const char* direction, const char* role) {
       .counter("pipelink_moe_rows_ready", "red.release.gpu", "ld.acquire.gpu")
       .bind("slot", "pipelink_moe_rows_ready");
 }
+// Per row tile, how many epilogue warps have stored their part of a pass-1 tile of it: the load owner
+// of the one-launch forward reads the hidden rows of a row tile once all column tiles are counted.
+inline pl::endpoint hidden_ready(const char* direction, const char* role) {
+  return pl::endpoint(direction, role).space("gmem").scope("grid").proxy("generic")
+      .tile("e4m3+ue8m0", {256})
+      .counter("pipelink_moe_hidden_ready", "red.release.gpu", "ld.acquire.gpu")
+      .bind("slot", "pipelink_moe_hidden_ready");
+}
 }  // namespace moe
 #endif
 
@@ -210,11 +262,13 @@ inline pl::endpoint rows_ready(const char* direction, const char* role) {
   PL_CLAIM(mbarrier, pipelink_moe_acc_full, pl::units(1), 1);          \
   PL_CLAIM(mbarrier, pipelink_moe_acc_empty, pl::units(1), 1)
 #define MOE_CLAIM_STAGING() PL_CLAIM(smem, pipelink_moe_staging, pl::units(moe::EpilogueWarps * 2048), 16)
+#define MOE_CLAIM_HIDDEN_READY() PL_CLAIM(gmem_counter, pipelink_moe_hidden_ready, pl::units(moe::MaxRowTiles), 1)
 #define MOE_CLAIM_ROWS_READY() PL_CLAIM(gmem_counter, pipelink_moe_rows_ready, pl::units(moe::MaxRowTiles), 1)
 // the two register groups of an image: load + MMA + comm warps give registers up, the epilogue takes them
 #define MOE_REGS_HELPER(role) PL_CLAIM_REGS(pipelink_moe_regs_helpers, role, helpers, 56)
 #define MOE_REGS_EPILOGUE(role) PL_CLAIM_REGS(pipelink_moe_regs_epilogue, role, epilogue, 224)
 
 static_assert(sizeof(MoeGeometry) == 48 && sizeof(MoeLoadParams) == 576 && sizeof(MoeMmaParams) == 48 &&
-              sizeof(MoeCommParams) == 112 && sizeof(MoeSwigluParams) == 80 && sizeof(MoeRowsParams) == 96,
+              sizeof(MoeCommParams) == 112 && sizeof(MoeSwigluParams) == 80 && sizeof(MoeRowsParams) == 96 &&
+              sizeof(MoeFwdLoadParams) == 1152 && sizeof(MoeFwdMmaParams) == 96 && sizeof(MoeFwdEpilogueParams) == 176,
               "parameter blocks: the manifests and the host image state these sizes");

@@ -49,7 +49,20 @@ def main():
     for b, w in zip(batches, want):
         got = host.forward(b)["output"].cpu()
         assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "in-kernel dispatch")
+    # ---- the FFN as ONE launch of the linked forward image (dispatch warps, both projections, combine push)
+    from pipelink_b200 import moe_linked
+    linked = moe_linked.LinkedMoE(host)
+    host.attach_linked(linked)
+    for fused in (True, False):
+        host.fused_dispatch = fused
+        for b, w in zip(batches, want):
+            got = host.forward(b)["output"].cpu()
+            assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "one-launch forward", fused)
+    host.attach_linked(None)
     host.fused_dispatch = False
+    torch.cuda.synchronize()
+    dist.barrier()
+    linked.close()
     pin = lambda t: t.cpu().pin_memory()
     h_out = [torch.full((shape.tokens, H), float("nan"), dtype=torch.bfloat16).pin_memory() for _ in batches]
     pipe = ep.EpHostPipeline(host)
@@ -71,6 +84,17 @@ def main():
     for b, w in zip(batches, want):
         got = host.forward(b)["output"].cpu()
         assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "receive streams")
+    linked = moe_linked.LinkedMoE(host)
+    host.attach_linked(linked)
+    host.fused_dispatch = True
+    for b, w in zip(batches, want):
+        got = host.forward(b)["output"].cpu()
+        assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "one-launch forward, receive streams")
+    host.attach_linked(None)
+    host.fused_dispatch = False
+    torch.cuda.synchronize()
+    dist.barrier()
+    linked.close()
     h_out = [torch.full((shape.tokens, H), float("nan"), dtype=torch.bfloat16).pin_memory() for _ in batches]
     pipe = ep.EpHostPipeline(host)
     for b, o in zip(batches, h_out):

@@ -1,6 +1,7 @@
 """The MoE grouped GEMMs as linked images (stages/moe packed separately, joined by the link
 driver) against the library's own kernels: same inputs, same bits, for the gate/up projection
-(rows in place, and rows pulled by the comm owner inside the image) and the down projection."""
+(rows in place, and rows pulled by the comm owner inside the image) and the down projection, as two
+launches and as the one-launch forward image."""
 import numpy as np
 import pytest
 import torch
@@ -31,7 +32,7 @@ def test_linked_images_equal_the_library_kernels(linked_dir, shape_args, generat
         for step in range(2):
             inputs = mok.MoKHost.new_inputs(shape, generation + step, "cuda")
             want = lib.forward(inputs)
-            for dispatch in (False, True):
+            for dispatch, one_launch in ((False, False), (True, False), (False, True), (True, True)):
                 lnk.status.reset()
                 lnk.fused_dispatch = dispatch               # quantise_tokens then also writes the scale rows
                 for name in ("x_routed_fp8", "hidden_routed_fp8"):
@@ -41,13 +42,16 @@ def test_linked_images_equal_the_library_kernels(linked_dir, shape_args, generat
                 lnk.x_buffer.copy_(inputs.x)
                 lnk.router_weight_buffer.copy_(inputs.router)
                 lnk.dispatch()                              # with dispatch: quantise only, the image pulls
-                linked.gemm_gate_up(dispatch=dispatch)
-                linked.gemm_down()
+                if one_launch:                              # both projections in one launch of the fwd image
+                    linked.forward_ffn(dispatch=dispatch)
+                else:
+                    linked.gemm_gate_up(dispatch=dispatch)
+                    linked.gemm_down()
                 out = lnk.fwd_epilogue()
                 torch.cuda.synchronize()
                 lnk.status.check("linked forward")
                 total = int(lib.schedule.num_tokens.item())
-                tag = (step, "dispatch" if dispatch else "in place")
+                tag = (step, "dispatch" if dispatch else "in place", "one launch" if one_launch else "two launches")
                 assert torch.equal(lnk.buffers["x_routed_fp8"][:total], want["x_routed_data"][:total]), tag
                 assert torch.equal(lnk.buffers["hidden_routed_fp8"][:total], want["hidden_routed_data"][:total]), tag
                 assert torch.equal(lnk.buffers["hidden_routed_sc"][: total // 128], want["hidden_routed_scale"][: total // 128]), tag

@@ -170,15 +170,17 @@ def linked(tmp_path_factory):
     return out, mb.build(out)
 
 
-def test_three_compositions_link_from_one_set_of_packages(linked):
+def test_five_compositions_link_from_one_set_of_packages(linked):
     out, results = linked
-    assert set(results) == {"gate_up", "gate_up_dispatch", "down"}
+    assert set(results) == {"gate_up", "gate_up_dispatch", "down", "fwd", "fwd_dispatch"}
     for comp, r in results.items():
         assert (r.threads, tuple(r.cluster), r.tmem_columns, r.regs_cap) == (384, (2, 1, 1), 512, 168)
         assert r.observed[0] <= 168 and r.observed[2] == 0          # register audit: fits the solved launch allocation, no spills
         assert (out / comp / "pipeline.cubin").stat().st_size > 10000
         receipt = json.loads((out / comp / "link.json").read_text())
-        assert receipt["bindings"]["pipelink_moe_depth"] == [6, "solved"]
+        # the one-launch forward with dispatch holds the operands ring, the row-store staging and the dispatch
+        # ring at once: the solve gives the ring one stage less
+        assert receipt["bindings"]["pipelink_moe_depth"] == [5 if comp == "fwd_dispatch" else 6, "solved"]
         text = (out / comp / "generated" / "dispatch.cu").read_text()
         assert "__cluster_dims__(2, 1, 1)" in text and "tcgen05.alloc.cta_group::2" in text
         assert "setmaxnreg.dec.sync.aligned.u32 56" in text and "setmaxnreg.inc.sync.aligned.u32 224" in text
@@ -187,3 +189,9 @@ def test_three_compositions_link_from_one_set_of_packages(linked):
     exp = [e for e in results["gate_up_dispatch"].protocol_expansions if e["kind"] == "counter"]
     assert exp and exp[0]["producers"] == ["moe.comm.dispatch"]
     assert results["gate_up"].dyn_smem_bytes < results["down"].dyn_smem_bytes
+    # the one-launch forward: a second counter channel, from the epilogue owner back to the load owner
+    exp = {e["channel"]: e for e in results["fwd_dispatch"].protocol_expansions if e["kind"] == "counter"}
+    assert exp["hidden_ready"]["producers"] == ["moe.fwd.epilogue"] and exp["rows_ready"]["producers"] == ["moe.comm.dispatch"]
+    b = results["fwd_dispatch"].bindings
+    slots = sorted((b[h][0], h) for h in ("pipelink_moe_hidden_ready", "pipelink_moe_rows_ready", "pipelink_moe_ticket"))
+    assert [s for s, _ in slots] == [0, 4096, 8192]                 # disjoint intervals of the counter workspace
