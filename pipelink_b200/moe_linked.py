@@ -127,7 +127,7 @@ class LinkedMoE:
         s = self.sessions[name]
         if h.capacity // 256 > 4096 or sh.hidden > 4096:
             raise ValueError("the forward image counts at most 4096 row tiles of rows up to 4096 bytes")
-        g1 = self._geometry(sh.hidden, 2 * sh.intermediate, rotation, stride)
+        g1 = self._geometry(sh.hidden, 2 * sh.intermediate)      # rows in schedule order, as the dispatch warps deliver them
         g2 = self._geometry(sh.intermediate, sh.hidden, rotation, stride)
         self.counters.zero_()
         counters = self.counters.data_ptr()

@@ -34,7 +34,7 @@ extern "C" __device__ void moe_fwd_epilogue_role(const void* raw_params, unsigne
   bool ok = true;
   for (int tile = pair_id; tile < f.total && ok; tile += num_pairs) {
     const bool second = tile >= f.tiles1;
-    const Tile t = decode(second ? p.g2 : p.g1, f.w, second ? tile - f.tiles1 : tile, static_cast<int>(e.cta_rank));
+    const Tile t = decode(second ? p.g2 : p.g1, second ? f.w2 : f.w1, second ? tile - f.tiles1 : tile, static_cast<int>(e.cta_rank));
     if (!plb::mbar_wait(bar(smem, pipelink_moe_acc_full()), acc_phase, p.g1.status, plb::ST_TIMEOUT_TMEM_FULL, 0)) ok = false;
     ok = __all_sync(0xFFFFFFFFu, ok);
     if (!ok) break;

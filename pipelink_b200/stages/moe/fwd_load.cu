@@ -65,7 +65,7 @@ extern "C" __device__ void moe_fwd_load_role(const void* raw_params, unsigned) {
   for (int tile = pair_id; tile < f.total && ok; tile += num_pairs) {
     const bool second = tile >= f.tiles1;
     const MoeGeometry& g = second ? g2 : g1;
-    const Tile t = decode(g, f.w, second ? tile - f.tiles1 : tile, static_cast<int>(cta_rank));
+    const Tile t = decode(g, second ? f.w2 : f.w1, second ? tile - f.tiles1 : tile, static_cast<int>(cta_rank));
     const int b_blk = t.b_blk0 + static_cast<int>(cta_rank);
     const CUtensorMap* const ma = second ? &p.a2 : &p.a1;
     const CUtensorMap* const mb = second ? &p.b2 : &p.b1;

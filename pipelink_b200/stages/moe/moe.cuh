@@ -153,6 +153,20 @@ struct Tile {
   int64_t out_row0;
 };
 
+// Row-tile order of a pass: start `m_rotation` tiles in, step with a stride made coprime to the live count.
+__device__ __forceinline__ void order_rows(Walk& w, const MoeGeometry& g) {
+  w.total_tiles = w.m_tiles_live * g.n_tiles;
+  w.m_rot = w.m_tiles_live > 0 ? g.m_rotation % w.m_tiles_live : 0;
+  w.m_stride = 1;
+  if (g.m_stride > 1 && w.m_tiles_live > 1) {
+    for (w.m_stride = g.m_stride % w.m_tiles_live == 0 ? 1 : g.m_stride % w.m_tiles_live;; ++w.m_stride) {
+      int a = w.m_stride, b = w.m_tiles_live;
+      while (b != 0) { const int t = a % b; a = b; b = t; }
+      if (a == 1) break;
+    }
+  }
+}
+
 // A 256-row tile is multiplied by one expert's weights: a schedule padded to less than the tile is
 // refused (every warp of every role evaluates this on its own and reaches the same answer).
 __device__ __forceinline__ Walk make_walk(const MoeGeometry& g, int lane, bool report) {
@@ -167,30 +181,24 @@ __device__ __forceinline__ Walk make_walk(const MoeGeometry& g, int lane, bool r
     if (report && lane == 0) plb::report_failure(g.status, plb::ST_BAD_ARGUMENT, 320, static_cast<unsigned>(rows), 256u);
     w.m_tiles_live = 0;
   }
-  w.total_tiles = w.m_tiles_live * g.n_tiles;
-  w.m_rot = w.m_tiles_live > 0 ? g.m_rotation % w.m_tiles_live : 0;
-  w.m_stride = 1;
-  if (g.m_stride > 1 && w.m_tiles_live > 1) {
-    for (w.m_stride = g.m_stride % w.m_tiles_live == 0 ? 1 : g.m_stride % w.m_tiles_live;; ++w.m_stride) {
-      int a = w.m_stride, b = w.m_tiles_live;
-      while (b != 0) { const int t = a % b; a = b; b = t; }
-      if (a == 1) break;
-    }
-  }
+  order_rows(w, g);
   return w;
 }
 
-// the tile list of the one-launch forward: every pass-1 tile, then every pass-2 tile, row tiles in
-// the same order in both (a pass-2 tile's hidden rows were finished long before it is reached)
+// the tile list of the one-launch forward: every pass-1 tile, then every pass-2 tile; each pass walks
+// the row tiles in its own order (pass 1 in the order the dispatch warps deliver rows, pass 2 in the
+// order that spreads the combine push over the home ranks)
 struct FwdWalk {
-  Walk w;
+  Walk w1, w2;
   int tiles1, total;
 };
 __device__ __forceinline__ FwdWalk make_fwd_walk(const MoeGeometry& g1, const MoeGeometry& g2, int lane, bool report) {
   FwdWalk f;
-  f.w = make_walk(g1, lane, report);
-  f.tiles1 = f.w.total_tiles;
-  f.total = f.tiles1 + f.w.m_tiles_live * g2.n_tiles;
+  f.w1 = make_walk(g1, lane, report);
+  f.w2 = f.w1;
+  order_rows(f.w2, g2);
+  f.tiles1 = f.w1.total_tiles;
+  f.total = f.tiles1 + f.w2.total_tiles;
   return f;
 }
 
