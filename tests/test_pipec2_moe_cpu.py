@@ -167,7 +167,7 @@ def test_counter_domain_capacity_comes_from_the_pipeline():
 @pytest.fixture(scope="module")
 def linked(tmp_path_factory):
     out = tmp_path_factory.mktemp("moe")
-    return out, mb.build(out)
+    return out, mb.build(out, one_tu=False)      # the one-unit control builds are for timing on a GPU
 
 
 def test_five_compositions_link_from_one_set_of_packages(linked):
