@@ -82,6 +82,12 @@ int plb_debug_set_profile_buffer(void* device_i64_grid_by_16);
  * Either pair of outputs may be NULL. */
 int plb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,
                        void* dst_sc, void* dst_t_fp8, void* dst_t_sc, void* stream);
+/* The same for a routed buffer sized for the worst case: only the 128-row tiles below
+ * *live_rows_dev (a device scalar, e.g. the schedule's num_tokens) are read and written; the
+ * tensors keep `rows` as their leading dimension, the rest of them is left as it was. With
+ * live_rows_dev NULL this is plb_mxfp8_quantize. */
+int plb_mxfp8_quantize_live(const void* src_bf16, int64_t rows, int64_t cols, const int32_t* live_rows_dev,
+                            void* dst_fp8, void* dst_sc, void* dst_t_fp8, void* dst_t_sc, void* stream);
 
 /* Inverse of the above for checking: fp32 [rows, cols]. (No reference counterpart on
  * the host; mirrors mxfp8::dequantize_single_block,
@@ -171,7 +177,8 @@ int plb_moe_gemm_down(const void* hidden_fp8, const void* hidden_sc, const void*
  * bf16 hidden that was quantised (its transposed quantisation is a plb_mxfp8_quantize call).
  * plb_moe_bwd_dy: backward of the weighted combine for every scheduled row p = (t, slot):
  *   d_y[p] = bf16(w[t, slot] * d_out[t]), d_w[t, slot] = <d_out[t], combine[t*k+slot]>; padding rows
- *   and rows beyond *num_tokens become zeros (the whole capacity is defined afterwards).
+ *   become zeros. Rows at and beyond *num_tokens are not written: nothing downstream reads them
+ *   (plb_mxfp8_quantize_live, the grouped GEMMs and the weight gradients stop at the rows in use).
  * plb_moe_swiglu_bwd: swiglu_bwd_kernel (campaigns/mok/port/act_gptoss/swiglu.cuh:219-558, default
  *   silu(g)*u math): d_gate_up bf16 [capacity, 2*inter] = [d_gate | d_up] from the saved MXFP8
  *   gate / up and bf16 d_hidden.

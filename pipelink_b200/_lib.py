@@ -29,6 +29,7 @@ PROTOTYPES = {
     "plb_debug_set_profile_buffer": (c_int, [c_void_p]),
     "plb_mxfp8_quantize": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p]),
+    "plb_mxfp8_quantize_live": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "plb_mxfp8_dequantize": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "plb_moe_schedule_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "plb_moe_schedule": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -106,17 +106,18 @@ swiglu_bwd_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ 
   }
 }
 
-// Rows beyond the live schedule are zero-filled so the transposed quantisation that follows
-// sees defined values over the whole capacity.
+// Padding rows inside the schedule become zeros; rows beyond it are left alone (the transposed
+// quantisation that follows stops at the rows in use).
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ peer_rank,
                    const int* __restrict__ peer_token_idx, const int* __restrict__ num_rows_dev,
                    int64_t capacity, int vecs, uint4* __restrict__ dst) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int64_t rows = *num_rows_dev;
-  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < capacity; p += warps) {
-    const bool live = p < rows && peer_rank[p] >= 0;
+  int64_t rows = *num_rows_dev;
+  if (rows > capacity) rows = capacity;
+  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < rows; p += warps) {
+    const bool live = peer_rank[p] >= 0;
     const uint4* s = live ? src + static_cast<int64_t>(peer_token_idx[p]) * vecs : nullptr;
     for (int v = lane; v < vecs; v += 32) dst[p * vecs + v] = live ? s[v] : make_uint4(0u, 0u, 0u, 0u);
   }
@@ -135,9 +136,9 @@ ep_bwd_dy_kernel(const uint4* const* __restrict__ d_out_peers, const float* cons
   int64_t rows = *num_rows_dev;
   if (rows > capacity) rows = capacity;
   const int vecs = hidden >> 3;
-  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < capacity; p += warps) {
+  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < rows; p += warps) {
     uint4* dst = dy + p * vecs;
-    const int r = p < rows ? peer_rank[p] : -1;
+    const int r = peer_rank[p];
     if (r < 0) {
       for (int v = lane; v < vecs; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
       continue;
@@ -255,9 +256,10 @@ ep_gather_rows_kernel(const uint4* const* __restrict__ src_peers, const int* __r
                       int64_t capacity, int vecs, uint4* __restrict__ dst) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int64_t rows = *num_rows_dev;
-  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < capacity; p += warps) {
-    const int r = p < rows ? peer_rank[p] : -1;
+  int64_t rows = *num_rows_dev;
+  if (rows > capacity) rows = capacity;
+  for (int64_t p = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < rows; p += warps) {
+    const int r = peer_rank[p];
     const uint4* s = r >= 0 ? src_peers[r] + static_cast<int64_t>(peer_token_idx[p]) * vecs : nullptr;
     for (int v0 = lane; v0 < vecs; v0 += 128) {
       uint4 g[4];
@@ -268,15 +270,6 @@ ep_gather_rows_kernel(const uint4* const* __restrict__ src_peers, const int* __r
         if (v0 + u * 32 < vecs) dst[p * vecs + v0 + u * 32] = g[u];
     }
   }
-}
-
-// Zero rows [*num_rows, capacity) of a bf16 [capacity, cols] tensor.
-__global__ void __launch_bounds__(256)
-zero_tail_kernel(uint4* __restrict__ t, const int* __restrict__ num_rows_dev, int64_t capacity, int vecs) {
-  const int64_t begin = static_cast<int64_t>(*num_rows_dev) * vecs, end = capacity * vecs;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < end; i += stride)
-    t[i] = make_uint4(0u, 0u, 0u, 0u);
 }
 
 int sm_grid(int mult) {
@@ -296,9 +289,6 @@ cudaError_t launch_bwd_dy(const void* d_out, const void* y, const float* router_
   bwd_dy_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const uint4*>(d_out), static_cast<const uint4*>(y),
                                                 router_w, peer_rank, peer_token_idx, dest_row, num_rows_dev,
                                                 capacity, hidden, topk, static_cast<uint4*>(dy), d_router_w);
-  cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess) return err;
-  zero_tail_kernel<<<sm_grid(2), 256, 0, stream>>>(static_cast<uint4*>(dy), num_rows_dev, capacity, hidden >> 3);
   return cudaGetLastError();
 }
 
@@ -311,9 +301,6 @@ cudaError_t launch_swiglu_bwd(const void* gate, const void* gate_sc, const void*
       static_cast<const uint8_t*>(gate), static_cast<const uint8_t*>(gate_sc), static_cast<const uint8_t*>(up),
       static_cast<const uint8_t*>(up_sc), static_cast<const uint4*>(d_hidden), num_rows_dev, capacity, inter,
       bound, static_cast<uint4*>(dgu));
-  cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess) return err;
-  zero_tail_kernel<<<sm_grid(2), 256, 0, stream>>>(static_cast<uint4*>(dgu), num_rows_dev, capacity, (2 * inter) >> 3);
   return cudaGetLastError();
 }
 

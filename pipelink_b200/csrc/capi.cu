@@ -78,6 +78,11 @@ int plb_moe_tile_rows(void) { return 256; }
 
 int plb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,
                        void* dst_sc, void* dst_t_fp8, void* dst_t_sc, void* stream) {
+  return plb_mxfp8_quantize_live(src_bf16, rows, cols, nullptr, dst_fp8, dst_sc, dst_t_fp8, dst_t_sc, stream);
+}
+
+int plb_mxfp8_quantize_live(const void* src_bf16, int64_t rows, int64_t cols, const int* live_rows_dev, void* dst_fp8,
+                            void* dst_sc, void* dst_t_fp8, void* dst_t_sc, void* stream) {
   if (rows < 0 || cols < 0 || rows % 128 || cols % 128) return PLB_E_ARGUMENT;
   if (src_bf16 == nullptr || !aligned16(src_bf16)) return PLB_E_ARGUMENT;
   if ((dst_fp8 == nullptr) != (dst_sc == nullptr)) return PLB_E_ARGUMENT;
@@ -85,8 +90,8 @@ int plb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t cols, void* d
   if (!aligned16(dst_fp8) || !aligned16(dst_sc) || !aligned16(dst_t_fp8) || !aligned16(dst_t_sc))
     return PLB_E_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dst_t_fp8 != nullptr)   // the transposed orientation, alone or with the other: one pass over the input
-    return from_cuda(plb::launch_quantize_tile(src_bf16, rows, cols, dst_fp8, dst_sc, dst_t_fp8, dst_t_sc, s));
+  if (dst_t_fp8 != nullptr || live_rows_dev != nullptr)   // the transposed orientation, alone or with the other: one pass
+    return from_cuda(plb::launch_quantize_tile(src_bf16, rows, cols, live_rows_dev, dst_fp8, dst_sc, dst_t_fp8, dst_t_sc, s));
   if (dst_fp8 != nullptr) {
     const int rc = from_cuda(plb::launch_quantize_plain(src_bf16, rows, cols, dst_fp8, dst_sc, s));
     if (rc != PLB_OK) return rc;

@@ -16,8 +16,8 @@ cudaError_t launch_quantize_rows(const void* const* src_peers, const int* peer_r
                                  cudaStream_t stream);
 cudaError_t launch_quantize_plain(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8,
                                   void* dst_sc, cudaStream_t stream);
-cudaError_t launch_quantize_tile(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8, void* dst_sc,
-                                 void* dst_t_fp8, void* dst_t_sc, cudaStream_t stream);
+cudaError_t launch_quantize_tile(const void* src_bf16, int64_t rows, int64_t cols, const int* live_rows_dev, void* dst_fp8,
+                                 void* dst_sc, void* dst_t_fp8, void* dst_t_sc, cudaStream_t stream);
 cudaError_t launch_quantize_transposed(const void* src_bf16, int64_t rows, int64_t cols,
                                        void* dst_t_fp8, void* dst_t_sc, cudaStream_t stream);
 cudaError_t launch_dequantize(const void* src_fp8, const void* src_sc, int64_t rows, int64_t cols,

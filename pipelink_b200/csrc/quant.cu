@@ -145,11 +145,19 @@ __device__ __forceinline__ float bf16_at(const uint8_t* row, int col) {
 }
 
 __global__ void __launch_bounds__(kThreads)
-quantize_tile_kernel(const uint4* __restrict__ src, int64_t rows, int64_t cols, uint8_t* __restrict__ dst_fp8,
-                     uint8_t* __restrict__ dst_sc, uint8_t* __restrict__ dst_t_fp8, uint8_t* __restrict__ dst_t_sc) {
+quantize_tile_kernel(const uint4* __restrict__ src, int64_t rows, int64_t cols, const int* __restrict__ live_rows_dev,
+                     uint8_t* __restrict__ dst_fp8, uint8_t* __restrict__ dst_sc, uint8_t* __restrict__ dst_t_fp8,
+                     uint8_t* __restrict__ dst_t_sc) {
   extern __shared__ __align__(16) uint8_t tile[];
   const int64_t col_tiles = cols >> 7, row_tiles = rows >> 7;
-  for (int64_t tid = blockIdx.x; tid < row_tiles * col_tiles; tid += gridDim.x) {
+  // a routed buffer is sized for the worst case; only the row tiles in use are read and written
+  // (the tensors keep the full `rows` as their leading dimension)
+  int64_t row_tiles_live = row_tiles;
+  if (live_rows_dev != nullptr) {
+    const int64_t live = (static_cast<int64_t>(*live_rows_dev) + kTile - 1) >> 7;
+    if (live < row_tiles_live) row_tiles_live = live < 0 ? 0 : live;
+  }
+  for (int64_t tid = blockIdx.x; tid < row_tiles_live * col_tiles; tid += gridDim.x) {
     const int64_t tr = tid / col_tiles, tc = tid - tr * col_tiles;
     const int64_t r0 = tr * kTile, c0 = tc * kTile;
     // stage: 16 threads per row, 16 rows per pass
@@ -363,8 +371,8 @@ cudaError_t launch_quantize_transposed(const void* src_bf16, int64_t rows, int64
   return cudaGetLastError();
 }
 
-cudaError_t launch_quantize_tile(const void* src_bf16, int64_t rows, int64_t cols, void* dst_fp8, void* dst_sc,
-                                 void* dst_t_fp8, void* dst_t_sc, cudaStream_t stream) {
+cudaError_t launch_quantize_tile(const void* src_bf16, int64_t rows, int64_t cols, const int* live_rows_dev, void* dst_fp8,
+                                 void* dst_sc, void* dst_t_fp8, void* dst_t_sc, cudaStream_t stream) {
   if (rows == 0 || cols == 0) return cudaSuccess;
   const int smem = kTile * kTilePitch;
   static bool configured = false;
@@ -379,8 +387,8 @@ cudaError_t launch_quantize_tile(const void* src_bf16, int64_t rows, int64_t col
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t resident = static_cast<int64_t>(sms > 0 ? sms : 148) * 6;   // 34 KB of shared memory per CTA
   quantize_tile_kernel<<<static_cast<unsigned>(tiles < resident ? tiles : resident), kThreads, smem, stream>>>(
-      static_cast<const uint4*>(src_bf16), rows, cols, static_cast<uint8_t*>(dst_fp8), static_cast<uint8_t*>(dst_sc),
-      static_cast<uint8_t*>(dst_t_fp8), static_cast<uint8_t*>(dst_t_sc));
+      static_cast<const uint4*>(src_bf16), rows, cols, live_rows_dev, static_cast<uint8_t*>(dst_fp8),
+      static_cast<uint8_t*>(dst_sc), static_cast<uint8_t*>(dst_t_fp8), static_cast<uint8_t*>(dst_t_sc));
   return cudaGetLastError();
 }
 

@@ -425,9 +425,9 @@ class EpMoKHost(mok.MoKHost):
         """Down projection: data gradient d_hidden, then the weight gradient over each expert's rows."""
         b, w, sh = self.buffers, self.weights, self.shape
         H, I = sh.hidden, sh.intermediate
-        dy_q, dy_sc, dy_t, dy_t_sc = mok.mxfp8_quantize(b["d_y_routed"], True, True)
+        dy_q, dy_sc, dy_t, dy_t_sc = mok.mxfp8_quantize(b["d_y_routed"], True, True, self.schedule.num_tokens)
         self._gemm_rows(dy_q, dy_sc, w["w_down_t_fp8"], w["w_down_t_sc"], H, I, b["d_hidden_routed"], self._identity_rows)
-        _, _, h_t, h_t_sc = mok.mxfp8_quantize(b["hidden_routed_bf16"], False, True)
+        _, _, h_t, h_t_sc = mok.mxfp8_quantize(b["hidden_routed_bf16"], False, True, self.schedule.num_tokens)
         self._wgrad(dy_t, dy_t_sc, h_t, h_t_sc, H, I, b["d_w_routed_down"])
 
     def bwd_activation(self):
@@ -436,7 +436,7 @@ class EpMoKHost(mok.MoKHost):
         _lib.call("plb_moe_swiglu_bwd", b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(),
                   b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(), b["d_hidden_routed"].data_ptr(),
                   s.num_tokens.data_ptr(), self.capacity, sh.intermediate, b["d_gate_up_routed"].data_ptr(), mok._stream())
-        self._dgu = mok.mxfp8_quantize(b["d_gate_up_routed"], True, True)
+        self._dgu = mok.mxfp8_quantize(b["d_gate_up_routed"], True, True, self.schedule.num_tokens)
 
     def bwd_push_dx(self):
         """Gate/up data gradient: d_x rows leave the GEMM epilogue straight into the home rank's
@@ -462,7 +462,7 @@ class EpMoKHost(mok.MoKHost):
             src = self.x_all_table
         _lib.call("plb_ep_gather_rows", src.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
                   s.num_tokens.data_ptr(), self.capacity, sh.hidden, b["x_routed_bf16"].data_ptr(), mok._stream())
-        _, _, x_t, x_t_sc = mok.mxfp8_quantize(b["x_routed_bf16"], False, True)
+        _, _, x_t, x_t_sc = mok.mxfp8_quantize(b["x_routed_bf16"], False, True, self.schedule.num_tokens)
         self._wgrad(dgu_t, dgu_t_sc, x_t, x_t_sc, 2 * sh.intermediate, sh.hidden, b["d_w_routed_gate_up"])
         self._dgu = None
 

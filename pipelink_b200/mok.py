@@ -56,12 +56,14 @@ def schedule_capacity(tokens_total: int, num_local_experts: int, padding: int | 
     return (need + padding - 1) // padding * padding
 
 
-def mxfp8_quantize(t: torch.Tensor, normal: bool = True, transposed: bool = False):
+def mxfp8_quantize(t: torch.Tensor, normal: bool = True, transposed: bool = False, live_rows: torch.Tensor | None = None):
     """``ops.mxfp8_quantize(tensor, normal, transposed)`` (mok_port_host.py:122).
 
     ``t`` is bf16 ``[..., rows, cols]`` on the device; leading dims are folded into rows.
     Returns ``(fp8, sc, fp8_t, sc_t)`` with ``None`` for the orientation not requested; fp8
-    tensors are uint8, scales are uint8 ``[rows/128, cols/128, 32, 16]``.
+    tensors are uint8, scales are uint8 ``[rows/128, cols/128, 32, 16]``. ``live_rows`` (a device
+    int32 scalar, the schedule's row count): only the 128-row tiles below it are read and written,
+    for routed buffers that are sized for the worst case.
     """
     if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous():
         raise ValueError("mxfp8_quantize wants a contiguous CUDA bf16 tensor")
@@ -79,7 +81,7 @@ def mxfp8_quantize(t: torch.Tensor, normal: bool = True, transposed: bool = Fals
             raise ValueError("the transposed orientation is defined for 2-D tensors")
         qt = torch.empty((cols, rows), dtype=torch.uint8, device=dev)
         sct = torch.empty((cols // 128, rows // 128, 32, 16), dtype=torch.uint8, device=dev)
-    _lib.call("plb_mxfp8_quantize", t.data_ptr(), rows, cols, _ptr(q), _ptr(sc), _ptr(qt),
+    _lib.call("plb_mxfp8_quantize_live", t.data_ptr(), rows, cols, _ptr(live_rows), _ptr(q), _ptr(sc), _ptr(qt),
               _ptr(sct), _stream())
     return q, sc, qt, sct
 
@@ -435,24 +437,24 @@ class MoKHost:
         _lib.call("plb_moe_bwd_dy", d_out.data_ptr(), b["combine_buffer"].data_ptr(), self.router_weight_buffer.data_ptr(),
                   s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(), s.dest_row.data_ptr(), nt, P, H, k,
                   b["d_y_routed"].data_ptr(), b["d_router_weights"].data_ptr(), _stream())
-        dy_q, dy_sc, dy_t, dy_t_sc = mxfp8_quantize(b["d_y_routed"], True, True)
+        dy_q, dy_sc, dy_t, dy_t_sc = mxfp8_quantize(b["d_y_routed"], True, True, s.num_tokens)
         # down projection: data gradient, then weight gradient (contraction over each expert's rows)
         self._gemm_rows(dy_q, dy_sc, w["w_down_t_fp8"], w["w_down_t_sc"], H, I, b["d_hidden_routed"], self._identity_rows)
-        _, _, h_t, h_t_sc = mxfp8_quantize(b["hidden_routed_bf16"], False, True)
+        _, _, h_t, h_t_sc = mxfp8_quantize(b["hidden_routed_bf16"], False, True, s.num_tokens)
         self._wgrad(dy_t, dy_t_sc, h_t, h_t_sc, H, I, b["d_w_routed_down"])
         # SwiGLU
         self.select_activation()
         _lib.call("plb_moe_swiglu_bwd", b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(),
                   b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(), b["d_hidden_routed"].data_ptr(), nt, P, I,
                   b["d_gate_up_routed"].data_ptr(), _stream())
-        dgu_q, dgu_sc, dgu_t, dgu_t_sc = mxfp8_quantize(b["d_gate_up_routed"], True, True)
+        dgu_q, dgu_sc, dgu_t, dgu_t_sc = mxfp8_quantize(b["d_gate_up_routed"], True, True, s.num_tokens)
         # gate/up projections: data gradient scattered to (token, slot) rows, then summed per token
         self._gemm_rows(dgu_q, dgu_sc, w["w_cat_t_fp8"], w["w_cat_t_sc"], 2 * I, H, b["d_x_routed_buffer"], s.dest_row)
         _lib.call("plb_moe_fwd_epilogue", None, b["d_x_routed_buffer"].data_ptr(), self._ones.data_ptr(), sh.tokens, k, H,
                   b["d_x"].data_ptr(), _stream())
         _lib.call("plb_moe_gather_rows", self.x_buffer.data_ptr(), s.peer_rank.data_ptr(), s.peer_token_idx.data_ptr(),
                   nt, P, H, b["x_routed_bf16"].data_ptr(), _stream())
-        _, _, x_t, x_t_sc = mxfp8_quantize(b["x_routed_bf16"], False, True)
+        _, _, x_t, x_t_sc = mxfp8_quantize(b["x_routed_bf16"], False, True, s.num_tokens)
         self._wgrad(dgu_t, dgu_t_sc, x_t, x_t_sc, 2 * I, H, b["d_w_routed_gate_up"])
         if check:
             self.status.check("after MoE backward")

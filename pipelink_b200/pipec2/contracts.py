@@ -116,9 +116,9 @@ def check_topology(manifests, profile):
     groups = {m["stage"]["id"]: (m.get("topology", {}).get("cta_group") or {}).get("fixed", 1) for m in manifests}
     clusters = {m["stage"]["id"]: tuple((m.get("topology", {}).get("cluster") or {}).get("compiled", [1, 1, 1])) for m in manifests}
     if len(set(groups.values())) > 1:
-        failures.append(ClauseFailure("L-TOPO", "topology.cta_group", "stages were compiled for different CTA groups", {"stages": groups}))
+        failures.append(ClauseFailure("L-TOPO", "stages.topology.cta_group", "stages were compiled for different CTA groups", {"stages": groups}))
     if len(set(clusters.values())) > 1:
-        failures.append(ClauseFailure("L-TOPO", "topology.cluster.compiled", "stages were compiled for different cluster shapes",
+        failures.append(ClauseFailure("L-TOPO", "stages.topology.cluster.compiled", "stages were compiled for different cluster shapes",
                                       {"stages": {k: list(v) for k, v in clusters.items()}}))
     if failures:
         raise PipeLinkError(failures)

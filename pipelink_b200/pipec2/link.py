@@ -101,7 +101,7 @@ def _check_symbols(manifests, bindings):
     for m in manifests:
         for sym in m.get("symbols", {}).get("defined_strong", []):
             if sym in owners:
-                failures.append(ClauseFailure("L-SYM", f"symbols.{sym}", "defined by two stages",
+                failures.append(ClauseFailure("L-SYM", f'$.symbols.defined_strong["{sym}"]', "defined by two stages",
                                               {"first": owners[sym], "second": m["stage"]["id"]}))
             owners[sym] = m["stage"]["id"]
     for m in manifests:
@@ -129,21 +129,10 @@ def _params_layout(manifests, profile):
     return {"total_bytes": total, "align": profile["param_align"], "entries": entries}
 
 
-def link(pipeline_path, out_dir, *, device_link=True):
-    pipeline_path, out_dir = Path(pipeline_path), Path(out_dir)
-    spec = json.loads(pipeline_path.read_text())
-    schema.validate_pipeline(spec)
-    pipe = spec["pipeline"]
-    manifests, payloads, input_hashes = [], [], {}
-    for st in pipe["stages"]:
-        path = (pipeline_path.parent / st["artifact_path"]).resolve()
-        m, payload = container.read(path)
-        schema.validate_manifest(m, where=m["stage"].get("id", str(path)))
-        if m["stage"]["id"] != st["stage_id"]:
-            raise PipeLinkError(ClauseFailure("L-LINK", f"pipeline.stages.{st['stage_id']}", f"package holds stage {m['stage']['id']!r}"))
-        manifests.append(m)
-        payloads.append(payload)
-        input_hashes[st["stage_id"]] = hashlib.sha256(path.read_bytes()).hexdigest()
+def front_end(manifests, pipe):
+    """The link phases before code generation, on documents in memory: one target profile, topology
+    agreement, channel pairing, layout identity, protocol expansion, symbol resolution, claim
+    unification, parameter layout and the solve. Returns what the later phases need."""
     profiles = {m["pipelink_abi"]["target"]["profile"] for m in manifests}
     if len(profiles) != 1:
         raise PipeLinkError(ClauseFailure("L-LINK", "pipelink_abi.target.profile", f"stages target different profiles: {sorted(profiles)}"))
@@ -171,32 +160,66 @@ def link(pipeline_path, out_dir, *, device_link=True):
         claims[TMEM_SLOT_HANDLE] = {"rec": {"handle": TMEM_SLOT_HANDLE, "domain": "smem", "extent": {"const": 16, "per": {}}, "align": 16},
                                     "stage": "pipec2.dispatch", "roles": []}
     params = _params_layout(manifests, profile)
-    role_warps = {}
-    for m in manifests:
-        for rname, r in m["stage"]["roles"].items():
-            mine = [h for h, c in claims.items() if c["rec"]["domain"] == "warp" and (m["stage"]["id"], rname) in c["roles"]]
-            if len(mine) == 1:
-                role_warps[rname] = (mine[0], r["warps"])
+    role_warps = _role_warps(manifests, claims)
     bindings, intervals, solver = solve({h: c["rec"] for h, c in claims.items()}, handles, profile,
                                         depth_priority=pipe.get("depth_priority", []),
                                         forced=pipe.get("forced_bindings", {}),
                                         regs_priority=pipe.get("regs_priority", []),
                                         reg_claims=_reg_claims(manifests, handles), role_warps=role_warps,
                                         pipeline_domains=pipe.get("domains", {}))
-
     _check_symbols(manifests, bindings)
+    return {"profile": profile, "handles": handles, "cta_group": cta_group, "cluster": cluster, "expansions": expansions,
+            "claims": claims, "uses_tmem": uses_tmem, "params": params, "role_warps": role_warps, "bindings": bindings,
+            "intervals": intervals, "solver": solver}
+
+
+def _role_warps(manifests, claims):
+    """role -> (warp claim handle, warps, offset inside the claim). A warp claim may cover several
+    roles of its stage; they occupy it in the order the claim lists them."""
+    out = {}
+    for h, c in claims.items():
+        if c["rec"]["domain"] != "warp":
+            continue
+        offset = 0
+        for stage_id, rname in c["roles"]:
+            m = next(m for m in manifests if m["stage"]["id"] == stage_id)
+            warps = m["stage"]["roles"][rname]["warps"]
+            out[rname] = (h, warps, offset)
+            offset += warps
+        if c["roles"] and offset != c["rec"]["extent"]["const"]:
+            raise PipeLinkError(ClauseFailure("L-TOPO", f"claims.{h}", "warp claim extent differs from its roles' warp counts"))
+    return out
+
+
+def link(pipeline_path, out_dir, *, device_link=True):
+    pipeline_path, out_dir = Path(pipeline_path), Path(out_dir)
+    spec = json.loads(pipeline_path.read_text())
+    schema.validate_pipeline(spec)
+    pipe = spec["pipeline"]
+    manifests, payloads, input_hashes = [], [], {}
+    for st in pipe["stages"]:
+        path = (pipeline_path.parent / st["artifact_path"]).resolve()
+        m, payload = container.read(path)
+        schema.validate_manifest(m, where=m["stage"].get("id", str(path)))
+        if m["stage"]["id"] != st["stage_id"]:
+            raise PipeLinkError(ClauseFailure("L-LINK", f"pipeline.stages.{st['stage_id']}", f"package holds stage {m['stage']['id']!r}"))
+        manifests.append(m)
+        payloads.append(payload)
+        input_hashes[st["stage_id"]] = hashlib.sha256(path.read_bytes()).hexdigest()
+    fe = front_end(manifests, pipe)
+    profile, handles, cta_group, cluster, expansions = fe["profile"], fe["handles"], fe["cta_group"], fe["cluster"], fe["expansions"]
+    claims, uses_tmem, params, bindings, intervals, solver = (fe["claims"], fe["uses_tmem"], fe["params"], fe["bindings"],
+                                                              fe["intervals"], fe["solver"])
 
     # roles: warp interval from the role's warp claim, params offset from the layout
     offsets = {e[0]: e[1] for e in params["entries"]}
     roles, covered = [], 0
     for m in manifests:
         for rname, r in m["stage"]["roles"].items():
-            claim = [h for h, c in claims.items() if c["rec"]["domain"] == "warp" and (m["stage"]["id"], rname) in c["roles"]]
-            if len(claim) != 1:
+            if rname not in fe["role_warps"]:
                 raise PipeLinkError(ClauseFailure("L-TOPO", f"{m['stage']['id']}.roles.{rname}", "a role needs exactly one warp claim"))
-            lo = bindings[claim[0]][0]
-            if claims[claim[0]]["rec"]["extent"]["const"] != r["warps"]:
-                raise PipeLinkError(ClauseFailure("L-TOPO", f"{m['stage']['id']}.roles.{rname}", "warp claim extent differs from the role's warp count"))
+            handle, warps, inside = fe["role_warps"][rname]
+            lo = bindings[handle][0] + inside
             roles.append({"stage": m["stage"]["id"], "role": rname, "entry": r["entry"], "warp_lo": lo,
                           "warp_hi": lo + r["warps"], "params_offset": offsets[m["stage"]["id"]], "variant": 0})
             covered += r["warps"]

@@ -21,6 +21,7 @@ CLAUSES = {
     "L-SYM": "symbols are unique and every undefined symbol is resolved",
     "L-TOPO": "stage topology constraints have a legal intersection",
     "L8": "paired endpoints describe the identical physical layout",
+    "T-CONTRACT": "a stage's tensor import / export section is well formed",
     "P-ANNOTATION": "a unit's annotations state exactly one stage, one parameter block and at most one topology",
     "P-COMPILE": "the stage payload compiles for the target profile",
     "P-CONTAINER": "the package container is well formed",

@@ -30,4 +30,7 @@ SM_100A = {
     "caps": {"regs_per_sm": 65536, "reg_alloc_granularity": 8, "regs_min": 24, "regs_max": 255,
              "warpgroup_warps": 4, "cta_group_legal": (1, 2), "max_cluster": (8, 8, 8)},
 }
-PROFILES = {"sm_100a": SM_100A}
+# B300's profile: the same capacities (pipec/src/pipec2/profile.py:141-149). Packages stamped for it are
+# checked and solved here like any other; their device link needs a toolkit that knows the architecture.
+SM_103A = dict(SM_100A, name="sm_103a", lto_arch="lto_103", gencode=("compute_103a", "lto_103a"), sm="sm_103a")
+PROFILES = {"sm_100a": SM_100A, "sm_103a": SM_103A}

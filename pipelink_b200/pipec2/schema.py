@@ -21,6 +21,7 @@ PROXIES = {"async", "generic"}
 DIRECTIONS = {"produce", "consume"}
 HANDLE_CLASSES = {"depth": "channel:", "regs": "reg_group:", "base": "claim:", "variant": "stage:"}
 ENTRY_SIGNATURE = "void(const void* params, unsigned variant)"
+SCHEMAS = ("3.0", "2.2", "2.0-draft")
 
 
 def symbol_prefix(stage_id: str) -> str:
@@ -42,7 +43,7 @@ class _Collector:
 def validate_manifest(m: dict, where: str = "manifest") -> None:
     c = _Collector()
     abi = m.get("pipelink_abi", {})
-    if abi.get("schema") not in ("3.0", "2.0-draft"):
+    if abi.get("schema") not in SCHEMAS:
         c.add("L-ENTRYABI", f"{where}.pipelink_abi.schema", "unsupported manifest schema")
     target = abi.get("target", {})
     if target.get("profile") not in PROFILES:
@@ -66,8 +67,14 @@ def validate_manifest(m: dict, where: str = "manifest") -> None:
         p = f"{where}.endpoints[{i}]"
         if ep.get("direction") not in DIRECTIONS:
             c.add("L-PAIR", f"{p}.direction", "direction must be produce or consume")
-        if ep.get("owner_role") not in roles:
+        provided_call = (ep.get("protocol") or {}).get("kind") == "call" and ep.get("direction") == "consume"
+        if ep.get("owner_role") not in roles and not (provided_call and ep.get("owner_role") is None):
             c.add("L-OWNER", f"{p}.owner_role", f"unknown role {ep.get('owner_role')!r}")
+        # a shared-completion root lists each member of its transaction sum once
+        for side in ("full", "empty"):
+            tx = ((ep.get("protocol") or {}).get(side) or {}).get("tx_bytes")
+            if isinstance(tx, dict) and len(set(tx.get("sum", []))) != len(tx.get("sum", [])):
+                c.add("L-PROTO", f"$.endpoints[{i}].protocol.{side}.tx_bytes.sum", "array entries must be unique")
         if ep.get("space") not in SPACES or ep.get("scope") not in SCOPES or ep.get("proxy") not in PROXIES:
             c.add("L-PAIR", f"{p}", "space/scope/proxy outside the vocabulary")
         for h in ep.get("binds", {}).values():
@@ -92,6 +99,18 @@ def validate_manifest(m: dict, where: str = "manifest") -> None:
     params = m.get("params", {})
     if params.get("bytes", 0) < 0 or params.get("align", 1) not in (1, 2, 4, 8, 16, 32, 64, 128):
         c.add("L-PARAMS", f"{where}.params", "bad parameter block size or alignment")
+    limit = PROFILES.get(target.get("profile"), {}).get("param_limit_bytes")
+    if limit is not None and params.get("bytes", 0) > limit:
+        c.add("L-PARAMS", "$.params.bytes", "parameter blob exceeds the target parameter limit", limit=limit)
+    # every variant row states a value for the same set of handles (the first row establishes it)
+    variants = st.get("variants", [])
+    for i, row in enumerate(variants[1:], start=1):
+        if set(row.get("key", {})) != set(variants[0].get("key", {})):
+            c.add("L-HANDLE", f"$.stage.variants[{i}].key", "variant key is incomplete")
+    if "tensor" in m:
+        from . import tensor
+        for clause, path, message in tensor.validate_section(m["tensor"], abi.get("schema")):
+            c.add(clause, path, message)
     c.raise_if_any()
 
 
@@ -121,6 +140,11 @@ def validate_pipeline(p: dict) -> None:
     for name in pipe.get("regs_priority", []):
         if pipe.get("handles", {}).get(name, {}).get("class") != "regs":
             c.add("L-HANDLE", f"pipeline.regs_priority.{name}", "not a regs handle")
+    phases = pipe.get("phases", ["steady"])
+    for i, pair in enumerate(pipe.get("exclusive", [])):
+        for j, name in enumerate(pair):
+            if name not in phases:
+                c.add("L-PHASE", f"$.pipeline.exclusive[{i}][{j}]", f"unknown phase {name!r}")
     for dom, d in pipe.get("domains", {}).items():
         if not isinstance(d.get("capacity"), int) or d["capacity"] < 0:
             c.add("L-BUDGET", f"pipeline.domains.{dom}.capacity", "a pipeline domain needs a non-negative capacity")

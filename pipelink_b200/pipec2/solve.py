@@ -29,7 +29,7 @@ def _extent_expr(extent, depth_vars):
 def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forced=None, total_warps=None,
           regs_priority=(), reg_claims=(), role_warps=None, pipeline_domains=None):
     """claims: handle -> unified claim record (every domain but `regs`). reg_claims: the register
-    claims ({handle, roles, values, reg_group?}); role_warps: role -> (warp claim handle, warps).
+    claims ({handle, roles, values, reg_group?}); role_warps: role -> (warp claim handle, warps[, offset inside the claim]).
     Returns (bindings, intervals, tiers)."""
     forced = forced or {}
     pipeline_domains = pipeline_domains or {}
@@ -109,7 +109,7 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         role_warps = role_warps or {}
         wg = caps.get("warpgroup_warps", 4)
         assigned, pool = set(), 0
-        launch_threads = 32 * sum(w for _, w in role_warps.values())
+        launch_threads = 32 * sum(rw[1] for rw in role_warps.values())
         for cl in sorted(reg_claims, key=lambda c: c["handle"]):
             name = cl.get("reg_group") or (cl["roles"][0] if len(cl["roles"]) == 1 else None)
             h = handles.get(cl["handle"])
@@ -129,7 +129,7 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
             lo = z3.Int(f"reg_group:{name}:lo")
             add(z3.And(lo >= 0, lo % wg == 0, (lo + width) % wg == 0), "L-REGS", path)
             for r in members:
-                rb = base_vars[role_warps[r][0]]
+                rb = base_vars[role_warps[r][0]] + (role_warps[r][2] if len(role_warps[r]) > 2 else 0)
                 add(z3.And(rb >= lo, rb + role_warps[r][1] <= lo + width), "L-REGS", path)
             pool = pool + v * width * 32
             reg_groups.append({"name": name, "handle": cl["handle"], "roles": members, "lo": lo, "width": width})
