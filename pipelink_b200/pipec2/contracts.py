@@ -20,8 +20,8 @@ def canonical_layout(layout: dict | None):
         return None
     if "lanes" in layout or "cols" in layout:   # tensor memory: a lane range and a column count
         return {"elem_bits": layout.get("elem_bits"), "lanes": list(layout.get("lanes", ())), "cols": layout.get("cols")}
-    shape = [s for mode in layout["shape"] for s in mode]
-    stride = [s for mode in layout["stride"] for s in mode]
+    flat = lambda modes: [s for mode in modes for s in (mode if isinstance(mode, (list, tuple)) else [mode])]
+    shape, stride = flat(layout["shape"]), flat(layout["stride"])
     modes = [(sh, st) for sh, st in zip(shape, stride) if sh != 1]
     merged = []
     for sh, st in reversed(modes):           # innermost first
@@ -182,10 +182,60 @@ def check_compatibility(channels) -> None:
         if physical_identity(pe) != physical_identity(ce):
             failures.append(ClauseFailure("L8", f"channels.{name}.layout", "paired endpoints describe different physical layouts",
                                           {"producer": physical_identity(pe), "consumer": physical_identity(ce)}))
-        if pe.get("protocol") != ce.get("protocol"):
-            failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol", "endpoint protocols differ"))
+        failures += _protocol_differences(name, pe.get("protocol") or {}, ce.get("protocol") or {})
     if failures:
         raise PipeLinkError(failures)
+
+
+def _protocol_differences(name, pp, cp):
+    """Where the two ends of a channel state their protocol differently, most specific path first
+    (the reference reports e.g. `channels.<name>.protocol.full.arrive`, pipec/src/pipec2/protocol.py:560-640)."""
+    path = f"channels.{name}.protocol"
+    if pp.get("kind") != cp.get("kind"):
+        return [ClauseFailure("L-PROTO", f"{path}.kind", "endpoint protocol kinds differ")]
+    if pp.get("kind") == "call":
+        # the two ends declare different functions by design (trampoline / implementation); they agree on
+        # the export they mean and on its signature
+        if (pp.get("export"), pp.get("signature")) != (cp.get("export"), cp.get("signature")):
+            return [ClauseFailure("L-PROTO", path, "caller and provider disagree on the export or its signature")]
+        return []
+    out = []
+    for side in ("full", "empty"):
+        ps, cs = pp.get(side) or {}, cp.get(side) or {}
+        if ps.get("arrive") != cs.get("arrive"):
+            out.append(ClauseFailure("L-PROTO", f"{path}.{side}.arrive", "producer and consumer arrival declarations disagree"))
+        for key in ("slots", "tx_bytes", "member_of"):
+            if ps.get(key) != cs.get(key):
+                out.append(ClauseFailure("L-PROTO", f"{path}.{side}.{key}", f"producer and consumer disagree on {key}"))
+    if pp.get("init") != cp.get("init"):
+        out.append(ClauseFailure("L-PROTO", f"{path}.init", "barrier ring has more than one init owner or materializer"))
+    rest = lambda d: {k: v for k, v in d.items() if k not in ("full", "empty", "init")}
+    if not out and rest(pp) != rest(cp):
+        out.append(ClauseFailure("L-PROTO", path, "endpoint protocols differ"))
+    return out
+
+
+DTYPE_BITS = {"bf16": 16, "f16": 16, "fp16": 16, "f32": 32, "fp32": 32, "s32": 32, "u32": 32, "s8": 8, "u8": 8, "e4m3": 8,
+              "e5m2": 8, "e4m3+ue8m0": 8}
+
+
+def _tile_bytes(ep):
+    tile = ep.get("tile") or {}
+    n = 1
+    for d in tile.get("shape", []):
+        n *= d
+    return n * DTYPE_BITS.get(tile.get("dtype"), 8) // 8
+
+
+def _arrival_count(count, warps):
+    """An arrival count is a number, or `threads(role)` / `warps(role)` of a role of the image."""
+    if isinstance(count, int):
+        return count
+    if isinstance(count, str) and count.endswith(")") and "(" in count:
+        fn, role = count[:-1].split("(", 1)
+        if role in warps and fn in ("threads", "warps"):
+            return warps[role] * (32 if fn == "threads" else 1)
+    return None
 
 
 def _role_sizes(manifests):
@@ -202,7 +252,12 @@ def expand_protocols(channels, manifests, cluster_size: int = 1) -> list[dict]:
     cluster (the reference's example: pl::side{..., {"producer", 2}, 0} under .scope("cluster"),
     docs/reference/annotations.md:205-209)."""
     warps = _role_sizes(manifests)
-    failures, out = [], []
+    failures, out, inits = [], [], {}
+    exports = {m["stage"]["id"]: m["stage"].get("exports", {}) for m in manifests}
+
+    def _tx(tx, ep):
+        return _tile_bytes(ep) if tx == "tile" else tx
+
     for name, ((ps, pe), (cs, ce)) in sorted(channels.items()):
         proto = pe["protocol"]
         ring = pe.get("ring", {})
@@ -215,7 +270,17 @@ def expand_protocols(channels, manifests, cluster_size: int = 1) -> list[dict]:
                 if s is None:
                     rec[side] = None
                     continue
-                by, count = s["arrive"]["by"], s["arrive"]["count"]
+                if "member_of" in s:
+                    # this side completes on another channel's barrier (shared completion): the target
+                    # must be a root, i.e. a side with arrivals of its own
+                    target = channels.get(s["member_of"])
+                    tside = (target[0][1]["protocol"].get(side) or {}) if target else {}
+                    if target is None or "member_of" in tside or "arrive" not in tside:
+                        failures.append(ClauseFailure("L-PROTO", f"channels.{s['member_of']}.protocol.{side}",
+                                                      "member_of may only target a root barrier side"))
+                    rec[side] = {"member_of": s["member_of"], "tx_bytes": _tx(s.get("tx_bytes", 0), pe)}
+                    continue
+                by, count = s["arrive"]["by"], _arrival_count(s["arrive"]["count"], warps)
                 if by not in warps:
                     failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.{side}.arrive.by", f"unknown role {by!r}"))
                     continue
@@ -224,27 +289,62 @@ def expand_protocols(channels, manifests, cluster_size: int = 1) -> list[dict]:
                     legal |= {cluster_size * n for n in (1, warps[by], 32 * warps[by])}
                 if count not in legal:
                     failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.{side}.arrive.count",
-                                                  f"{count} arrivals cannot come from role {by!r} ({warps[by]} warps)",
+                                                  f"{s['arrive']['count']} arrivals cannot come from role {by!r} ({warps[by]} warps)",
                                                   {"legal": sorted(legal)}))
-                rec[side] = {"slots": s["slots"], "count": count, "by": by, "tx_bytes": s.get("tx_bytes", 0)}
+                tx = s.get("tx_bytes", 0)
+                if isinstance(tx, dict):
+                    # the root of a shared completion: its transaction count is the sum over itself and
+                    # every channel whose same side names it as root
+                    members = {name} | {n for n, ((_, e), _c) in channels.items()
+                                        if ((e.get("protocol") or {}).get(side) or {}).get("member_of") == name}
+                    if set(tx.get("sum", [])) != members or len(tx.get("sum", [])) != len(members):
+                        failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.{side}.tx_bytes.sum",
+                                                      "root sum must name exactly the root and all direct members",
+                                                      {"members": sorted(members)}))
+                    total = sum(_tile_bytes(channels[n][0][1]) for n in members if n in channels)
+                    rec[side] = {"slots": s["slots"], "count": count, "by": by, "tx_bytes": total, "sum": sorted(members)}
+                else:
+                    rec[side] = {"slots": s["slots"], "count": count, "by": by, "tx_bytes": _tx(tx, pe)}
             full = proto.get("full") or {}
-            tx, stride = full.get("tx_bytes", 0), ring.get("stage_stride_bytes", 0)
+            tx, stride = (rec.get("full") or {}).get("tx_bytes", 0), ring.get("stage_stride_bytes", 0)
             # a slot may carry padding behind its payload (alignment of the next slot), never less than it
             payload = ring.get("payload_bytes", stride)
-            if tx not in (0, payload, cluster_size * payload) and pe["proxy"] == "async" and pe["space"] == "smem":
+            if (isinstance(full.get("tx_bytes", 0), int) and tx not in (0, payload, cluster_size * payload)
+                    and pe["proxy"] == "async" and pe["space"] == "smem"):
                 failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.full.tx_bytes",
                                               "expected transaction bytes differ from the ring slot's payload"))
             if payload > stride:
                 failures.append(ClauseFailure("L-PROTO", f"channels.{name}.ring.payload_bytes", "a slot's payload exceeds its stride"))
             init = proto.get("init", {})
-            if init.get("materializer") != "dispatch":
-                failures.append(ClauseFailure("L-OWNER", f"channels.{name}.protocol.init", "barrier init needs a single materializer (dispatch)"))
             rec["init"] = init
         elif proto["kind"] == "call":
             rec["callable"] = [proto["export"], proto.get("decl", "")]
+            # the provided side restates its stage's export record: declaration text and its digest
+            cproto = ce.get("protocol") or {}
+            record = exports.get(cs, {}).get(cproto.get("export"))
+            if record is not None and "decl" in record and (
+                    (cproto.get("decl"), cproto.get("decl_sha256")) != (record.get("decl"), record.get("decl_sha256"))):
+                failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol",
+                                              "consumer export declaration or hash disagrees with the channel"))
         else:
             failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.kind", f"unsupported protocol kind {proto['kind']!r}"))
         out.append(rec)
+    # channels over the same physical barrier ring (the same slot handles) are initialised once: the
+    # first declared states owner and materializer, a later one that differs is the failure
+    declared = []
+    for m in manifests:
+        for ep in m.get("endpoints", []):
+            if ep["name"] in channels and ep["name"] not in declared:
+                declared.append(ep["name"])
+    for name in declared:
+        proto = channels[name][0][1].get("protocol") or {}
+        ring_key = tuple((proto.get(side) or {}).get("slots") for side in ("full", "empty"))
+        if proto.get("kind") != "mbarrier" or None in ring_key:
+            continue
+        first = inits.setdefault(ring_key, (name, proto.get("init", {})))
+        if first[1] != proto.get("init", {}):
+            failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.init",
+                                          "barrier ring has more than one init owner or materializer", {"first": first[0]}))
     if failures:
         raise PipeLinkError(failures)
     return out

@@ -149,6 +149,9 @@ def front_end(manifests, pipe):
     expansions = contracts.expand_protocols(channels, manifests, cluster_size)
     expansions += contracts.expand_counters(contracts.counter_channels(manifests), handles)
     for e in expansions:
+        if e.get("kind") == "mbarrier" and (e.get("init") or {}).get("materializer", "dispatch") != "dispatch":
+            raise PipeLinkError(ClauseFailure("L-OWNER", f"channels.{e['channel']}.protocol.init",
+                                              "the generated dispatch kernel is the only barrier materializer of this build"))
         d = e.get("depth")
         if isinstance(d, dict) and "handle" in d and handles.get(d["handle"], {}).get("class") != "depth":
             raise PipeLinkError(ClauseFailure("L-HANDLE", f"channels.{e['channel']}.ring.depth", "ring depth handle is not declared"))

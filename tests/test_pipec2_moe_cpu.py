@@ -85,8 +85,8 @@ def test_solver_places_ring_counters_and_register_groups():
 
 
 NEGATIVE = [
-    ("mixed cta_group", lambda ms: ms[1]["topology"]["cta_group"].__setitem__("fixed", 1), "L-TOPO", "topology.cta_group"),
-    ("cluster shapes differ", lambda ms: ms[3]["topology"]["cluster"].__setitem__("compiled", [4, 1, 1]), "L-TOPO", "topology.cluster"),
+    ("mixed cta_group", lambda ms: ms[1]["topology"]["cta_group"].__setitem__("fixed", 1), "L-TOPO", "stages.topology.cta_group"),
+    ("cluster shapes differ", lambda ms: ms[3]["topology"]["cluster"].__setitem__("compiled", [4, 1, 1]), "L-TOPO", "stages.topology.cluster"),
     ("counter consumer without producer", lambda ms: ms[2]["endpoints"].pop(0), "L-PAIR", "channels.rows_ready"),
     ("counter release disagrees", lambda ms: ms[2]["endpoints"][0]["protocol"]["counter"].__setitem__("release", "red.release.sys"),
      "L-PROTO", "channels.rows_ready.protocol"),

@@ -74,3 +74,16 @@ def test_reference_negative_fixture(name):
     got = [(f.clause_id, f.path) for f in err.value.failures]
     assert {c for c, _ in got} == {case["expected_clause"]}, got
     assert any(case["expected_path"] in p for _, p in got), got
+
+
+def test_a_materializer_this_build_cannot_generate_is_refused_at_link():
+    """Both ends agree on a stage-side barrier initialiser: a valid contract (the reference accepts it)
+    that this build's code generator does not implement; the link says so instead of generating
+    a dispatch kernel that skips the initialisation."""
+    raw = copy.deepcopy(GOLDEN["bases"]["barrier"])
+    for st in raw["stages"]:
+        st["endpoints"][0]["protocol"]["init"]["materializer"] = "stage"
+    run_phase("protocol.expand", raw, {})
+    with pytest.raises(PipeLinkError) as err:
+        linker.front_end(raw["stages"], raw["pipeline"]["pipeline"])
+    assert [(f.clause_id, f.path) for f in err.value.failures] == [("L-OWNER", "channels.ring.protocol.init")]
