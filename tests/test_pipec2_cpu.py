@@ -30,7 +30,7 @@ def test_manifests_validate_and_symbol_prefix_rule():
         schema.validate_manifest(copy.deepcopy(m))
     assert schema.symbol_prefix("gemm.epilogue.bias-silu") == "gemm_epilogue_bias_silu_"
     bad = copy.deepcopy(g3.MANIFESTS["mma"])
-    bad["stage"]["roles"]["mma"]["entry"] = "other_role"
+    bad["stage"]["symbol_prefix"] = "other_"           # the prefix is derived from the stage id
     with pytest.raises(PipeLinkError, match="P-SYM"):
         schema.validate_manifest(bad)
     bad = copy.deepcopy(g3.MANIFESTS["mma"])
