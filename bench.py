@@ -913,7 +913,16 @@ def decode_leg(dev, pk, steps=128, prefill=4096):
     ms = a.elapsed_time(b) / steps
     nbytes = sum(s.bytes_per_token(prefill + i) for i in range(steps)) / steps
     gbs = nbytes / (ms * 1e-3) / 1e9
-    return {"metric": "llama1b_decode_ms_per_token", "value": ms, "unit": "ms/token", "steps": steps,
+    try:
+        linked = decode_linked_arms(s, prefill, steps, ms)
+    except Exception as exc:  # noqa: BLE001 - the image is absent or fails: report it, keep the library's figure
+        linked = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    path = "library kernel (plb_decode_step)"
+    if isinstance(linked, dict) and linked.get("same_tokens") and linked.get("linked_ms", ms) < ms:
+        # the linked image of the same device code is the product too (decode_linked.LinkedDecode): report the faster
+        ms, path = linked["linked_ms"], "linked image (stages/decode through the link driver)"
+        gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"metric": "llama1b_decode_ms_per_token", "value": ms, "unit": "ms/token", "steps": steps, "path": path, "linked": linked,
             "prefill": prefill, "higher_is_better": False, "dtype": "bf16", "launches_per_token": 1,
             "tokens": s.token_out[prefill + 1: prefill + 5].tolist(),
             # the reference's published figure for this configuration (other hardware): 1.701 ms/token
@@ -921,6 +930,41 @@ def decode_leg(dev, pk, steps=128, prefill=4096):
             "vs_baseline": ms / 1.701, "baseline": {"value": 1.701, "unit": "ms/token", "hardware": "1x sm103 @ 1102 MHz"},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
                          "bytes_per_token": nbytes, "peak_source": f"hbm_gbs of {pk['source']} peaks"}}
+
+
+def decode_linked_arms(s, prefill, steps, library_ms, rounds=3):
+    """The same decode through the LINKED image (stages/decode: stream and interpreter owners packed
+    separately, joined by the link driver) and through the single-unit build of the same stage
+    sources, alternating with the library kernel, `rounds` runs of `steps` tokens each from the same
+    start; the best run of each arm. `ratio` is linked / single unit: the reference's decode gate
+    (within 1 %). The three arms must produce the same tokens."""
+    import torch
+
+    from pipelink_b200 import decode_linked
+    arms = {"library": s, "linked": decode_linked.LinkedDecode(s), "one_unit": decode_linked.LinkedDecode(s, image="one_tu.cubin")}
+    times = {k: [] for k in arms}
+    tokens = {}
+    for _ in range(rounds):
+        for name, arm in arms.items():
+            s.start(1, prefill)
+            arm.decode(4, check=False)
+            s.start(1, prefill)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            arm.decode(steps, check=False)
+            b.record()
+            torch.cuda.synchronize()
+            s.status.check(f"decode leg ({name})")
+            times[name].append(a.elapsed_time(b) / steps)
+            tokens[name] = s.token_out[prefill + 1: prefill + 1 + steps].tolist()
+    for arm in (arms["linked"], arms["one_unit"]):
+        arm.close()
+    best = {k: min(v) for k, v in times.items()}
+    return {"library_ms": best["library"], "linked_ms": best["linked"], "one_unit_ms": best["one_unit"],
+            "ratio": best["linked"] / best["one_unit"], "linked_over_library": best["linked"] / best["library"],
+            "same_tokens": tokens["linked"] == tokens["library"] == tokens["one_unit"], "rounds": rounds,
+            "all_ms": times}
 
 
 class SingleRank:

@@ -546,6 +546,14 @@ int plb_image_load(const void* image, const char* symbol, int dyn_smem_bytes, vo
                    void** kernel);
 int plb_image_launch(void* kernel, int grid_x, int grid_y, int grid_z, int threads,
                      int dyn_smem_bytes, const void* params_image, void* stream);
+/* plb_image_launch for an image whose CTAs wait on one another (dependency counters between SMs, as the
+ * decode interpreter's): a cooperative launch, so that every CTA of the grid is resident. */
+int plb_image_launch_cooperative(void* kernel, int grid_x, int threads, int dyn_smem_bytes, const void* params_image,
+                                 void* stream);
+/* The 128-byte tensor map the decode interpreter reads a KV cache through (bf16 [layers, max_seq_len, 8, 64];
+ * box = 128 tokens of one KV head, 128-byte swizzle): plb_decode_step builds it internally, a host that launches
+ * the linked decode image (stages/decode) places two of them in the stream owner's parameter block. */
+int plb_decode_kv_map(void* out128, const void* cache_bf16, int layers, int max_seq_len);
 int plb_image_unload(void* library);
 
 /* Encode a 2-D byte tensor map (what an owner's provider writes into its residue,

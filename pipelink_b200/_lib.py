@@ -109,6 +109,8 @@ PROTOTYPES = {
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "plb_image_load": (c_int, [c_void_p, c_char_p, c_int, POINTER(c_void_p), POINTER(c_void_p)]),
     "plb_image_launch": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "plb_image_launch_cooperative": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "plb_decode_kv_map": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "plb_image_unload": (c_int, [c_void_p]),
     "plb_tensor_map_2d_u8": (c_int, [c_void_p, c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32,
                                      ctypes.c_uint32, c_int]),

@@ -908,6 +908,19 @@ int plb_image_launch(void* kernel, int grid_x, int grid_y, int grid_z, int threa
                                     dyn_smem_bytes, static_cast<cudaStream_t>(stream)));
 }
 
+int plb_image_launch_cooperative(void* kernel, int grid_x, int threads, int dyn_smem_bytes, const void* params_image,
+                                 void* stream) {
+  if (!kernel || !params_image || grid_x < 1 || threads < 32) return PLB_E_ARGUMENT;
+  void* args[] = {const_cast<void*>(params_image)};
+  // every CTA of the grid is resident at once: images whose CTAs wait on one another's counters need it
+  return from_cuda(cudaLaunchCooperativeKernel(kernel, dim3(grid_x), dim3(threads), args, dyn_smem_bytes,
+                                               static_cast<cudaStream_t>(stream)));
+}
+
+int plb_decode_kv_map(void* out128, const void* cache_bf16, int layers, int max_seq_len) {
+  return from_cuda(plb::encode_decode_kv_map(out128, cache_bf16, layers, max_seq_len));
+}
+
 int plb_image_unload(void* library) {
   return library ? from_cuda(cudaLibraryUnload(static_cast<cudaLibrary_t>(library))) : PLB_OK;
 }

@@ -50,6 +50,9 @@ struct DecodeGlobals {
 cudaError_t set_decode_profile(void* buffer);  // profiling builds only: [grid][9][8] i64 cycle sums
 #endif
 cudaError_t launch_decode_step(const DecodeGlobals& g, int num_sms, cudaStream_t stream);
+// The tensor map the decode kernel reads a KV cache through ([layers, max_seq_len, 8, 64] bf16, box = 128
+// tokens of one head, 128-byte swizzle), for hosts that launch the linked decode image themselves.
+cudaError_t encode_decode_kv_map(void* out128, const void* base, int layers, int max_seq_len);
 cudaError_t launch_attention_partial(const void* q, const void* k, const void* v, float* out,
                                      float* lse, int length, int partitions, float scale,
                                      cudaStream_t stream);

@@ -237,6 +237,20 @@ class endpoint {
     j_["protocol"] = p;
     return *this;
   }
+  // a one-way signal: arrivals on a full barrier and nothing flowing back
+  endpoint& mbarrier_full_only(const arrivals& full, const char* init_owner) {
+    json p = json::object();
+    p["kind"] = json("mbarrier");
+    p["full"] = full.j;
+    json init = json::object();
+    init["owner"] = json(init_owner);
+    init["phase"] = json(0);
+    init["materializer"] = json("dispatch");
+    p["init"] = init;
+    p["release"] = json("once-per-acquire");
+    j_["protocol"] = p;
+    return *this;
+  }
   endpoint& counter(const char* slot_handle, const char* release, const char* acquire) {
     json c = json::object();
     c["slot"] = json(slot_handle);
