@@ -787,15 +787,52 @@ def attention_leg(dev, pk, seq=32768, steps=3):
     b.record()
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / steps
+    try:
+        linked = attention_linked_arms(q, k, v, steps)
+    except Exception as exc:  # noqa: BLE001 - the images are absent or fail: report it, keep the library's figure
+        linked = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     tf = 4.0 * 128 * Hq * seq * (seq + 1) / 2 / (ms * 1e-3) / 1e12
     return {"metric": "causal_prefill_attention_tflops", "value": tf, "unit": "TFLOP/s", "ms": ms, "seq": seq,
-            "heads": [Hq, Hkv], "dtype": "bf16",
+            "heads": [Hq, Hkv], "dtype": "bf16", "linked": linked,
             # the reference's published figure for causal prefill at 32K, 32/8 heads, d = 128 (other
             # hardware): 614.5 useful TFLOP/s on one H200 (campaigns/attention/README.md:172)
             **({"vs_baseline": tf / 614.5, "baseline": {"value": 614.5, "unit": "TFLOP/s", "hardware": "1x H200 @ 1305 MHz"}}
                if seq == 32768 else {}),
             "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_sustained"], "unit": "TFLOP/s",
                          "frac": tf / pk["bf16_sustained"], "peak_source": f"bf16_tflops_sustained of {pk['source']} peaks"}}
+
+
+def attention_linked_arms(q, k, v, steps, rounds=3):
+    """The same prefill through the library kernel, the LINKED image (stages/attention) and the
+    single-unit build of the same stage sources, alternating; best of `rounds` per arm; the three
+    must give the same bits. `ratio` = linked / single unit."""
+    import torch
+
+    from pipelink_b200 import attention as att, attention_linked
+    linked, control = attention_linked.LinkedAttention(), attention_linked.LinkedAttention(image="one_tu.cubin")
+    arms = {"library": lambda: att.attention_fwd(q, k, v, check=False), "linked": lambda: linked.forward(q, k, v, check=False),
+            "one_unit": lambda: control.forward(q, k, v, check=False)}
+    times, outs = {n: [] for n in arms}, {}
+    for _ in range(rounds):
+        for name, fn in arms.items():
+            fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(steps):
+                o, lse = fn()
+            b.record()
+            torch.cuda.synchronize()
+            times[name].append(a.elapsed_time(b) / steps)
+            outs[name] = (o, lse)
+    same = all(torch.equal(outs[n][0].view(torch.int16), outs["library"][0].view(torch.int16)) and
+               torch.equal(outs[n][1].view(torch.int32), outs["library"][1].view(torch.int32)) for n in ("linked", "one_unit"))
+    linked.close()
+    control.close()
+    best = {n: min(v) for n, v in times.items()}
+    return {"library_ms": best["library"], "linked_ms": best["linked"], "one_unit_ms": best["one_unit"],
+            "ratio": best["linked"] / best["one_unit"], "linked_over_library": best["linked"] / best["library"],
+            "same_bits": bool(same), "rounds": rounds}
 
 
 def cp_attention_leg(dev, pk, rank, world, seq=131072, steps=2, check=True):

@@ -563,6 +563,10 @@ int plb_tensor_map_2d_u8(void* out128, const void* base, uint64_t rows, uint64_t
                          uint32_t box_rows, uint32_t box_bytes, int swizzle128);
 /* The same for a row-major [rows, cols] tensor of 32-bit words without swizzle (the scale tensors
  * seen as one 128-word row per 512-byte scale block). */
+/* The same for a bf16 [rows, cols] tensor: coordinates and box in elements (with the 128-byte swizzle a box row is
+ * 64 elements). The prefill attention image's Q / K / V maps: box 128 rows x 64 columns. */
+int plb_tensor_map_2d_bf16(void* out128, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                           uint32_t box_cols, int swizzle128);
 int plb_tensor_map_2d_u32(void* out128, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
                           uint32_t box_cols);
 

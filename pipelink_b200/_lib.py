@@ -114,6 +114,7 @@ PROTOTYPES = {
     "plb_image_unload": (c_int, [c_void_p]),
     "plb_tensor_map_2d_u8": (c_int, [c_void_p, c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32,
                                      ctypes.c_uint32, c_int]),
+    "plb_tensor_map_2d_bf16": (c_int, [c_void_p, c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, c_int]),
     "plb_tensor_map_2d_u32": (c_int, [c_void_p, c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32]),
     "plb_moe_fwd_epilogue": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64,
                                      c_void_p, c_void_p]),

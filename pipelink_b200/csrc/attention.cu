@@ -21,28 +21,15 @@
 //              bf16 into the 128-byte-swizzled A-operand layout, O kept in registers and
 //              rescaled per block (O = O * alpha + O_blk), final O / l and LSE
 // All peer/global traffic is TMA loads of LOCAL memory and plain stores; nothing is multicast.
-#include "kernels.h"
-#include "attention.h"
+#include <cstddef>
+
+#include "attention_roles.cuh"
 
 namespace plb {
 
-namespace {
+using namespace attn;
 
-constexpr int kD = 128;                 // head dim
-constexpr int kBlk = 128;               // queries per tile, keys per block
-constexpr int kAtomBytes = kBlk * 128;  // 128 rows x 128 bytes (64 bf16): one swizzle atom column
-constexpr int kTileBytes = 2 * kAtomBytes;  // 128 x 128 bf16
-constexpr int kKvStages = 2;
-constexpr int kOffQ = 0;
-constexpr int kOffK = kTileBytes;
-constexpr int kOffV = kOffK + kKvStages * kTileBytes;
-constexpr int kOffP = kOffV + kKvStages * kTileBytes;
-constexpr int kOffBar = kOffP + kTileBytes;
-constexpr int kAttnSmem = kOffBar + 256 + 1024;
-constexpr int kAttnThreads = 192;
-constexpr uint32_t kIdescQK = idesc_bf16(kBlk, kBlk, 0, 0);
-constexpr uint32_t kIdescPV = idesc_bf16(kBlk, kD, 0, 1);       // B (= V) is MN-major
-constexpr uint64_t kDescVMn = smem_desc_hi(1024, kAtomBytes, 2);  // 8-key groups 1 KB apart, d-halves 16 KB apart
+namespace {
 
 struct AttnBars {
   uint64_t q_full, q_empty;
@@ -57,19 +44,6 @@ struct AttnBars {
 };
 static_assert(sizeof(AttnBars) <= 256, "barrier block");
 
-
-__device__ __forceinline__ float tanh_approx(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// Raw score q.k -> score in the base-2 softmax domain. Plain: s * scale * log2(e). With a soft cap c
-// (score_softcap_score_mod, campaigns/attention/src/sm90/stage_score_softcap.cu:10-13): the scaled
-// score becomes c * tanh(s * scale / c); cap_in = scale / c, cap_out = c * log2(e).
-template <bool kSoftcap>
-__device__ __forceinline__ float score_log2(float s, const AttnParams& p) {
-  return kSoftcap ? p.cap_out * tanh_approx(s * p.cap_in) : s * p.scale_log2;
-}
 
 template <bool kUseCounters, bool kSoftcap>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -378,22 +352,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 //              maximum is only advanced (and O_t, l rescaled in TMEM) when a block raises it by
 //              more than 2^8; otherwise exponentials stay relative to the older maximum, which
 //              fp32 sums and bf16 P tolerate. Final O_t / l and LSE.
-constexpr int kPairThreads = 384;  // warpgroup 0: TMA, MMA, two idle warps; warpgroups 1 and 2: softmax
-constexpr int kPOffQ = 0;                              // two Q tiles
-constexpr int kPOffK = 2 * kTileBytes;
-constexpr int kPOffV = kPOffK + kKvStages * kTileBytes;
-constexpr int kPOffBar = kPOffV + kKvStages * kTileBytes;
-constexpr int kPairSmem = kPOffBar + 256 + 1024;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
-struct TrueTag { static constexpr bool value = true; };
-struct FalseTag { static constexpr bool value = false; };
-
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 struct PairBars {
   uint64_t q_full, q_empty;
   uint64_t k_full[kKvStages], k_empty[kKvStages];
@@ -406,6 +364,22 @@ struct PairBars {
 };
 static_assert(sizeof(PairBars) <= 256, "barrier block");
 
+// The library kernel's shared-memory and tensor-memory map, as constants.
+#define PLB_PAIR_BAR(name) \
+  __device__ static uint32_t name(uint32_t sb, int i = 0) { return sb + kPOffBar + offsetof(PairBars, name) + 8 * i; }
+struct LibPairLayout {
+  __device__ static constexpr int kv_depth() { return kKvStages; }
+  __device__ static constexpr int q() { return kPOffQ; }
+  __device__ static constexpr int k() { return kPOffK; }
+  __device__ static constexpr int v() { return kPOffV; }
+  __device__ static constexpr int s_col() { return 0; }
+  __device__ static constexpr int o_col() { return 256; }
+  __device__ static constexpr int warp_softmax() { return 4; }
+  PLB_PAIR_BAR(q_full) PLB_PAIR_BAR(q_empty) PLB_PAIR_BAR(k_full) PLB_PAIR_BAR(k_empty) PLB_PAIR_BAR(v_full)
+  PLB_PAIR_BAR(v_empty) PLB_PAIR_BAR(s_full) PLB_PAIR_BAR(p_full) PLB_PAIR_BAR(o_full) PLB_PAIR_BAR(o_free) PLB_PAIR_BAR(drain)
+};
+#undef PLB_PAIR_BAR
+
 template <bool kUseCounters, bool kSoftcap>
 __global__ void __launch_bounds__(kPairThreads, 1)
 attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -416,24 +390,25 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   uint8_t* smem = smem_raw + pad;
   const uint32_t sb = raw_addr + pad;
   PairBars* bars = reinterpret_cast<PairBars*>(smem + kPOffBar);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  using L = LibPairLayout;
 
   if (threadIdx.x == 0) {
-    mbar_init(smem_u32(&bars->q_full), 1);
-    mbar_init(smem_u32(&bars->q_empty), 1);
+    mbar_init(L::q_full(sb), 1);
+    mbar_init(L::q_empty(sb), 1);
     for (int s = 0; s < kKvStages; ++s) {
-      mbar_init(smem_u32(&bars->k_full[s]), 1);
-      mbar_init(smem_u32(&bars->k_empty[s]), 1);
-      mbar_init(smem_u32(&bars->v_full[s]), 1);
-      mbar_init(smem_u32(&bars->v_empty[s]), 1);
+      mbar_init(L::k_full(sb, s), 1);
+      mbar_init(L::k_empty(sb, s), 1);
+      mbar_init(L::v_full(sb, s), 1);
+      mbar_init(L::v_empty(sb, s), 1);
     }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(smem_u32(&bars->s_full[t]), 1);
-      mbar_init(smem_u32(&bars->p_full[t]), 128);
-      mbar_init(smem_u32(&bars->o_full[t]), 1);
-      mbar_init(smem_u32(&bars->o_free[t]), 128);
+      mbar_init(L::s_full(sb, t), 1);
+      mbar_init(L::p_full(sb, t), 128);
+      mbar_init(L::o_full(sb, t), 1);
+      mbar_init(L::o_free(sb, t), 128);
     }
-    mbar_init(smem_u32(&bars->drain), 1);
+    mbar_init(L::drain(sb), 1);
     fence_mbar_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
@@ -448,348 +423,14 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
-  if (warp < 4) {
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t q_phase = 0, k_it = 0, v_it = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
-        const AttnWork wk = p.work[w];
-        const int col = wk.head * kD;
-        const int kv_col = (wk.head / p.q_per_kv) * kD;
-        if (!mbar_wait(smem_u32(&bars->q_empty), q_phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, 10)) { ok = false; break; }
-        mbar_arrive_expect_tx(smem_u32(&bars->q_full), 2 * kTileBytes);
-#pragma unroll
-        for (int a = 0; a < 4; ++a)  // tile t = a / 2 (head + t), 64-column half a % 2
-          tma_load_2d(sb + kPOffQ + a * kAtomBytes, &map_q, smem_u32(&bars->q_full), col + a * 64, wk.q_row0);
-        q_phase ^= 1u;
-        for (int j = 0; j < wk.kv_blocks && ok; ++j) {
-          const int kv_row = wk.kv_row0 + j * kBlk;
-          if (kUseCounters && p.ready != nullptr) {
-            const unsigned* flag = p.ready + (wk.kv_row0 / kBlk + j);
-            const long long t0 = clock64();
-            while (static_cast<int>(ld_acquire_sys_u32(flag) - p.ready_target) < 0) {
-              if (clock64() - t0 > kWaitBudgetCycles || ld_volatile_i32(&p.status->code) != 0) {
-                report_failure(p.status, ST_TIMEOUT_COUNTER, 300, ld_acquire_sys_u32(flag), p.ready_target);
-                ok = false;
-                break;
-              }
-            }
-            if (!ok) break;
-            asm volatile("fence.proxy.async.global;" ::: "memory");
-          }
-          {
-            const int s = k_it % kKvStages;
-            if (!mbar_wait(smem_u32(&bars->k_empty[s]), ((k_it / kKvStages) & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, 11)) { ok = false; break; }
-            const uint32_t full = smem_u32(&bars->k_full[s]);
-            mbar_arrive_expect_tx(full, kTileBytes);
-            tma_load_2d(sb + kPOffK + s * kTileBytes, &map_k, full, kv_col, kv_row);
-            tma_load_2d(sb + kPOffK + s * kTileBytes + kAtomBytes, &map_k, full, kv_col + 64, kv_row);
-            ++k_it;
-          }
-          {
-            const int s = v_it % kKvStages;
-            if (!mbar_wait(smem_u32(&bars->v_empty[s]), ((v_it / kKvStages) & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, 12)) { ok = false; break; }
-            const uint32_t full = smem_u32(&bars->v_full[s]);
-            mbar_arrive_expect_tx(full, kTileBytes);
-            tma_load_2d(sb + kPOffV + s * kTileBytes, &map_v, full, kv_col, kv_row);
-            tma_load_2d(sb + kPOffV + s * kTileBytes + kAtomBytes, &map_v, full, kv_col + 64, kv_row);
-            ++v_it;
-          }
-        }
-      }
-      if (!ok) {
-        const long long t0 = clock64();
-        while (clock64() - t0 < 200000LL) {
-        }
-      }
-    }
+    load_role<L, kUseCounters>(&map_q, &map_k, &map_v, p, sb);
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      uint32_t q_phase = 0, k_it = 0, v_it = 0, blk_it = 0, item_it = 0;
-      bool ok = true;
-      auto issue_qk = [&](int t, int ks) {
-        const uint32_t qa = sb + kPOffQ + t * kTileBytes, ka = sb + kPOffK + ks * kTileBytes;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
-          tc_mma_f16(tmem + t * 128, smem_desc(qa + off, kDescSw128KMajor), smem_desc(ka + off, kDescSw128KMajor),
-                     kIdescQK, k != 0 ? 1u : 0u);
-        }
-        tc_commit(smem_u32(&bars->s_full[t]));
-      };
-      for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
-        const AttnWork wk = p.work[w];
-        const int n = wk.kv_blocks;
-        if (!mbar_wait(smem_u32(&bars->q_full), q_phase, p.status, ST_TIMEOUT_FULL, 22)) { ok = false; break; }
-        {
-          const int ks = k_it % kKvStages;
-          if (!mbar_wait(smem_u32(&bars->k_full[ks]), (k_it / kKvStages) & 1u, p.status, ST_TIMEOUT_FULL, 20)) { ok = false; break; }
-          tc_fence_after();
-          issue_qk(0, ks);
-          issue_qk(1, ks);
-          tc_commit(smem_u32(&bars->k_empty[ks]));
-          ++k_it;
-        }
-        for (int j = 0; j < n && ok; ++j) {
-          const bool have_next = j + 1 < n;
-          const int vs = v_it % kKvStages, ks = k_it % kKvStages;
-          if (!mbar_wait(smem_u32(&bars->v_full[vs]), (v_it / kKvStages) & 1u, p.status, ST_TIMEOUT_FULL, 23)) { ok = false; break; }
-          if (have_next &&
-              !mbar_wait(smem_u32(&bars->k_full[ks]), (k_it / kKvStages) & 1u, p.status, ST_TIMEOUT_FULL, 26)) { ok = false; break; }
-          const uint32_t va = sb + kPOffV + vs * kTileBytes;
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (!mbar_wait(smem_u32(&bars->p_full[t]), blk_it & 1u, p.status, ST_TIMEOUT_FULL, 24)) { ok = false; break; }
-            // the first P V of a record overwrites O_t: the previous record's epilogue must have read it
-            if (j == 0 &&
-                !mbar_wait(smem_u32(&bars->o_free[t]), (item_it & 1u) ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, 25)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < 8; ++k)  // 16 keys per step: 8 packed columns of P, 16 rows x 128 B of V
-              tc_mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + k * 8, smem_desc(va + k * 2048, kDescVMn), kIdescPV,
-                            (j != 0 || k != 0) ? 1u : 0u);
-            if (!have_next) tc_commit(smem_u32(&bars->o_full[t]));
-            if (have_next) issue_qk(t, ks);
-          }
-          if (!ok) break;
-          tc_commit(smem_u32(&bars->v_empty[vs]));
-          ++v_it;
-          if (have_next) {
-            tc_commit(smem_u32(&bars->k_empty[ks]));
-            ++k_it;
-          }
-          ++blk_it;
-        }
-        if (!ok) break;
-        tc_commit(smem_u32(&bars->q_empty));
-        q_phase ^= 1u;
-        ++item_it;
-      }
-      if (!ok) {
-        tc_commit(smem_u32(&bars->drain));
-        const long long t0 = clock64();
-        while (!mbar_try_wait(smem_u32(&bars->drain), 0)) {
-          if (clock64() - t0 > 20000000LL) break;
-        }
-      }
-    }
-  } else if (kUseCounters && p.push_k != nullptr) {
-    // ------------------------------------------------------------------ K/V gather warps (2 and 3)
-    // The context-parallel exchange inside the attention launch (the reference puts its gather warps
-    // into the attention CTA the same way, campaigns/attention/src/sm90/stage_kv_gather.cu:16-78, with
-    // the ticket / publish primitives of examples/comm-overlap/comm/push_gather.cuh:80-150). Tickets
-    // come from one global counter, so any resident CTA serves any piece and progress never depends
-    // on which CTA got which attention tile; the warps wait for nothing. Order: ascending global
-    // position, the order in which every consumer's tiles read their key blocks. Zigzag ownership
-    // (campaigns/attention/README.md:222-228): rank r holds chunks r and 2W-1-r of 2W; the early chunk is
-    // needed by every rank, the late chunk only by ranks <= r.
-    const int cb = p.push_chunk_blocks, parts = p.push_parts, W = p.push_world, r = p.push_rank;
-    const int early_tasks = cb * W, late_tasks = cb * (r + 1);
-    const unsigned total = static_cast<unsigned>(early_tasks + late_tasks) * static_cast<unsigned>(parts);
-    for (;;) {
-      unsigned tk = 0;
-      if (lane == 0) tk = atomicAdd(p.push_ticket, 1u);
-      tk = __shfl_sync(0xFFFFFFFFu, tk, 0);
-      if (tk >= total) break;
-      const int task = static_cast<int>(tk / parts), part = static_cast<int>(tk - static_cast<unsigned>(task) * parts);
-      int local_block, consumer, global_block;
-      if (task < early_tasks) {
-        const int b = task / W;
-        consumer = task - b * W;
-        local_block = b;
-        global_block = r * cb + b;
-      } else {
-        const int u = task - early_tasks;
-        const int b = u / (r + 1);
-        consumer = u - b * (r + 1);
-        local_block = cb + b;
-        global_block = (2 * W - 1 - r) * cb + b;
-      }
-      const size_t src_off = (static_cast<size_t>(local_block) * parts + part) * p.push_vec_per_part;
-      const size_t dst_off = (static_cast<size_t>(global_block) * parts + part) * p.push_vec_per_part;
-      const uint4* ks = p.push_k + src_off;
-      const uint4* vs = p.push_v + src_off;
-      uint4* kd = p.push_k_peers[consumer] + dst_off;
-      uint4* vd = p.push_v_peers[consumer] + dst_off;
-      for (int i0 = lane; i0 < p.push_vec_per_part; i0 += 128) {   // loads batched before the stores
-        uint4 a[4], b4[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * 32;
-          if (i < p.push_vec_per_part) { a[u] = ks[i]; b4[u] = vs[i]; }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * 32;
-          if (i < p.push_vec_per_part) { kd[i] = a[u]; vd[i] = b4[u]; }
-        }
-      }
-      __threadfence_system();       // every lane's stores, then one release increment for the piece
-      __syncwarp();
-      if (lane == 0)
-        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_ready_peers[consumer] + global_block), "r"(1u)
-                     : "memory");
-    }
-  }
+    mma_role<L>(p, sb, tmem);
+  } else if (warp < 4) {
+    if (kUseCounters && p.push_k != nullptr) gather_role(p);
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue
-    const int t = (warp - 4) >> 2;     // tile (head offset) of this warp
-    const int quad = warp & 3;         // TMEM lane quadrant this warp may touch
-    const int row = quad * 32 + lane;  // query row inside the tile == TMEM lane
-    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t tmem_s = tmem + t * 128 + lane_addr;
-    const uint32_t tmem_o = tmem + 256 + t * 128 + lane_addr;
-    const float scale = p.scale_log2;
-    uint32_t blk_it = 0, item_it = 0;
-    bool ok = true;
-    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
-      const AttnWork wk = p.work[w];
-      const int head = wk.head + t;
-      const int q_pos = wk.q_pos0 + row;
-      float m_ref = -INFINITY, l = 0.0f;
-      for (int j = 0; j < wk.kv_blocks; ++j) {
-        if (!mbar_wait(smem_u32(&bars->s_full[t]), blk_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, 30)) ok = false;
-        ok = __all_sync(0xFFFFFFFFu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        const int key0 = wk.kv_pos0 + j * kBlk;
-        const int valid = q_pos - key0 + 1;  // keys [lo, valid) of this block are visible to the row
-        const int lo = p.window > 0 ? q_pos - p.window + 1 - key0 : 0;
-        // uniform per block: some row of the tile is masked (causal edge or the window's lower edge)
-        const bool diag = key0 + kBlk - 1 > wk.q_pos0 || (p.window > 0 && wk.q_pos0 + kBlk - 1 - p.window + 1 > key0);
-        float bm = -INFINITY;
-        {
-          // pass 1: block maximum of the raw scores, two 32-column chunks in flight
-          float b0 = -INFINITY, b1 = -INFINITY;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t a[32], b[32];
-            tc_ld_32x32b_x32(tmem_s + h * 64, a);
-            tc_ld_32x32b_x32(tmem_s + h * 64 + 32, b);
-            tc_wait_ld();
-            if (diag) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                if (h * 64 + i < valid && h * 64 + i >= lo) b0 = fmaxf(b0, __uint_as_float(a[i]));
-                if (h * 64 + 32 + i < valid && h * 64 + 32 + i >= lo) b1 = fmaxf(b1, __uint_as_float(b[i]));
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                b0 = fmaxf(b0, __uint_as_float(a[i]));
-                b1 = fmaxf(b1, __uint_as_float(b[i]));
-              }
-            }
-          }
-          bm = fmaxf(b0, b1);
-        }
-        bm = bm == -INFINITY ? bm : score_log2<kSoftcap>(bm, p);  // monotonic: the maximum of the scores is the score of the maximum
-        const float m_new = fmaxf(m_ref, bm);
-        const bool need = m_new > m_ref && (m_ref == -INFINITY || m_new - m_ref > kRescaleThreshold);
-        if (__any_sync(0xFFFFFFFFu, need)) {
-          if (j > 0) {
-            // O_t holds the sum over blocks 0..j-1 (their P V completed before this block's scores)
-            const float alpha = m_new == m_ref ? 1.0f : ex2_approx(m_ref - m_new);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint32_t ov[32];
-              tc_ld_32x32b_x32(tmem_o + c * 32, ov);
-              tc_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-              tc_st_32x32b_x32(tmem_o + c * 32, ov);
-            }
-            tc_wait_st();
-            l *= alpha;
-          }
-          m_ref = m_new;
-        }
-        const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-        // P = exp2(s * scale - m_ref) as bf16, two per 32-bit column, over the first 64 columns of S_t
-        // pass 2: scores are read again from TMEM (cheaper than holding 128 of them in registers);
-        // P of columns [64 h, 64 h + 64) lands on columns [32 h, 32 h + 32), all of them already read
-        float sum0 = 0.0f, sum1 = 0.0f;
-        auto half = [&](auto masked, int h) {
-          uint32_t a[32], b[32], pk[32];
-          tc_ld_32x32b_x32(tmem_s + h * 64, a);
-          tc_ld_32x32b_x32(tmem_s + h * 64 + 32, b);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float a0, a1, c0, c1;
-            if (kSoftcap) {
-              a0 = ex2_approx(score_log2<true>(__uint_as_float(a[i]), p) - m_use);
-              a1 = ex2_approx(score_log2<true>(__uint_as_float(a[i + 1]), p) - m_use);
-              c0 = ex2_approx(score_log2<true>(__uint_as_float(b[i]), p) - m_use);
-              c1 = ex2_approx(score_log2<true>(__uint_as_float(b[i + 1]), p) - m_use);
-            } else {
-              a0 = ex2_approx(fmaf(__uint_as_float(a[i]), scale, -m_use));
-              a1 = ex2_approx(fmaf(__uint_as_float(a[i + 1]), scale, -m_use));
-              c0 = ex2_approx(fmaf(__uint_as_float(b[i]), scale, -m_use));
-              c1 = ex2_approx(fmaf(__uint_as_float(b[i + 1]), scale, -m_use));
-            }
-            if (decltype(masked)::value) {
-              if (h * 64 + i >= valid || h * 64 + i < lo) a0 = 0.0f;
-              if (h * 64 + i + 1 >= valid || h * 64 + i + 1 < lo) a1 = 0.0f;
-              if (h * 64 + 32 + i >= valid || h * 64 + 32 + i < lo) c0 = 0.0f;
-              if (h * 64 + 32 + i + 1 >= valid || h * 64 + 32 + i + 1 < lo) c1 = 0.0f;
-            }
-            sum0 += a0 + a1;
-            sum1 += c0 + c1;
-            __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pc = __floats2bfloat162_rn(c0, c1);
-            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&pa);
-            pk[16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&pc);
-          }
-          tc_st_32x32b_x32(tmem_s + h * 32, pk);
-        };
-        if (diag) {
-          half(TrueTag{}, 0);
-          half(TrueTag{}, 1);
-        } else {
-          half(FalseTag{}, 0);
-          half(FalseTag{}, 1);
-        }
-        tc_wait_st();
-        l += sum0 + sum1;
-        tc_fence_before();
-        mbar_arrive(smem_u32(&bars->p_full[t]));
-        ++blk_it;
-      }
-      if (!ok) break;
-      // epilogue: O_t / l as bf16 and the natural-log LSE
-      if (!mbar_wait(smem_u32(&bars->o_full[t]), item_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, 32)) ok = false;
-      ok = __all_sync(0xFFFFFFFFu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      const size_t out_row = static_cast<size_t>(wk.q_row0 + row);
-      uint4* dst = reinterpret_cast<uint4*>(p.out + (out_row * p.q_heads + head) * kD);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t ov[32];
-        tc_ld_32x32b_x32(tmem_o + c * 32, ov);
-        tc_wait_ld();
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint32_t wv[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 tt = __floats2bfloat162_rn(__uint_as_float(ov[g * 8 + e * 2]) * inv,
-                                                      __uint_as_float(ov[g * 8 + e * 2 + 1]) * inv);
-            wv[e] = *reinterpret_cast<uint32_t*>(&tt);
-          }
-          dst[c * 4 + g] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&bars->o_free[t]));
-      ++item_it;
-      p.lse[(static_cast<size_t>(wk.batch) * p.q_heads + head) * p.seq_q + (wk.q_row0 - wk.batch * p.seq_q) + row] =
-          l > 0.0f ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
-    }
+    softmax_role<L, kSoftcap>(p, sb, tmem);
   }
   tc_fence_before();
   __syncthreads();

@@ -953,6 +953,34 @@ int plb_tensor_map_2d_u8(void* out128, const void* base, uint64_t rows, uint64_t
   return PLB_OK;
 }
 
+int plb_tensor_map_2d_bf16(void* out128, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                           uint32_t box_cols, int swizzle128) {
+  if (!out128 || !base || rows == 0 || cols == 0 || cols % 8 || box_cols > 256 || box_rows > 256 || box_cols == 0 ||
+      box_rows == 0 || (swizzle128 && box_cols != 64))
+    return PLB_E_ARGUMENT;
+  typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                         const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                         CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                         CUtensorMapFloatOOBfill);
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return PLB_E_RESOURCE;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult rc = reinterpret_cast<Fn>(sym)(
+      &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return PLB_E_BUILD;
+  memcpy(out128, &map, sizeof(map));
+  return PLB_OK;
+}
+
 int plb_tensor_map_2d_u32(void* out128, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
                           uint32_t box_cols) {
   if (!out128 || !base || rows == 0 || cols == 0 || cols % 4 || box_cols > 256 || box_rows > 256 || box_cols == 0 ||

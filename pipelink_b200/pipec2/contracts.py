@@ -284,9 +284,11 @@ def expand_protocols(channels, manifests, cluster_size: int = 1) -> list[dict]:
                 if by not in warps:
                     failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.{side}.arrive.by", f"unknown role {by!r}"))
                     continue
-                legal = {1, warps[by], 32 * warps[by]}
+                # one elected thread, or one lane / every thread of some of the role's warps (a role may split
+                # its warps over the slots of a channel: four softmax warps per head arrive 128 strong)
+                legal = {1} | {n * w for w in range(1, warps[by] + 1) for n in (1, 32)}
                 if pe.get("scope") == "cluster":
-                    legal |= {cluster_size * n for n in (1, warps[by], 32 * warps[by])}
+                    legal |= {cluster_size * n for n in legal}
                 if count not in legal:
                     failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.{side}.arrive.count",
                                                   f"{s['arrive']['count']} arrivals cannot come from role {by!r} ({warps[by]} warps)",

@@ -79,16 +79,38 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         if name in forced:
             add(b == forced[name], "L-HANDLE", f"pipeline.forced_bindings.{name}")
 
-    # non-overlap inside every physical resource (kernel-lifetime claims only in this build)
+    # non-overlap inside every physical resource (kernel-lifetime claims only in this build). Shared
+    # memory holds the many small claims (every barrier slot array is one): there the claims that
+    # nothing pins are laid out in one fixed order, strictest alignment first, each behind the last,
+    # which needs no disjunctions and packs as tightly as any order does when alignments decrease;
+    # pinned claims (a forced or absolute base) and the small domains keep pairwise exclusion.
     names = sorted(claims)
-    for i, a in enumerate(names):
-        for bname in names[i + 1:]:
-            da, db = domains[claims[a]["domain"]], domains[claims[bname]["domain"]]
-            if da.physical != db.physical:
-                continue
-            lo_a, hi_a = base_vars[a] * da.scale, (base_vars[a] + ext_exprs[a]) * da.scale
-            lo_b, hi_b = base_vars[bname] * db.scale, (base_vars[bname] + ext_exprs[bname]) * db.scale
-            add(z3.Or(hi_a <= lo_b, hi_b <= lo_a), "L-OVERLAP", f"claims.{a}~{bname}")
+
+    def span(n):
+        d = domains[claims[n]["domain"]]
+        return base_vars[n] * d.scale, (base_vars[n] + ext_exprs[n]) * d.scale
+
+    def exclude(a, bname):
+        (lo_a, hi_a), (lo_b, hi_b) = span(a), span(bname)
+        add(z3.Or(hi_a <= lo_b, hi_b <= lo_a), "L-OVERLAP", f"claims.{a}~{bname}")
+
+    for phys in sorted({d.physical for d in domains.values()}):
+        members = [n for n in names if domains[claims[n]["domain"]].physical == phys]
+        pinned = [n for n in members if n in forced or "absolute_base" in claims[n]]
+        free = [n for n in members if n not in pinned]
+        if phys == "smem" and len(free) > 2:
+            byte_align = lambda n: max(claims[n].get("align", 1), 1) * domains[claims[n]["domain"]].scale
+            free.sort(key=lambda n: (-byte_align(n), n))
+            for prev, nxt in zip(free, free[1:]):
+                add(span(prev)[1] <= span(nxt)[0], "L-OVERLAP", f"claims.{prev}~{nxt}")
+            for a in pinned:
+                for bname in members:
+                    if bname != a and (bname not in pinned or a < bname):
+                        exclude(a, bname)
+        else:
+            for i, a in enumerate(members):
+                for bname in members[i + 1:]:
+                    exclude(a, bname)
 
     # warp claims tile [0, total) exactly
     warp_claims = [n for n in names if claims[n]["domain"] == "warp"]
@@ -176,9 +198,11 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         highwater[phys] = hw
         opt.minimize(hw)
         tiers.append({"name": f"min high-water {phys}"})
-    # finally prefer low bases so layouts are deterministic
-    for n in names:
-        opt.minimize(base_vars[n])
+    # finally prefer low bases so layouts are deterministic (PLB_SOLVE_TIEBREAK=0 to time the solve without it)
+    import os
+    if os.environ.get("PLB_SOLVE_TIEBREAK", "1") == "1":
+        for n in names:
+            opt.minimize(base_vars[n])
 
     if opt.check() != z3.sat:
         _diagnose(cons)
