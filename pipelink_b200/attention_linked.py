@@ -48,7 +48,7 @@ class LinkedAttention:
     def __init__(self, out_dir=None, image: str = "pipeline.cubin"):
         """image: "pipeline.cubin" (linked) or "one_tu.cubin" (the single-unit build of the same sources)."""
         out = Path(out_dir or ensure_built())
-        self.sessions = {c: Session(out / c, image) for c in ("prefill", "prefill_softcap")}
+        self.sessions = {c: Session(out / c, image) for c in COMPOSITIONS}
 
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, window: int = 0, softcap: float = 0.0,
                 check: bool = True):
@@ -80,6 +80,33 @@ class LinkedAttention:
         if check:
             status.check("linked attention")
         return out, lse
+
+    def attend_and_push(self, rank, q_local: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor):
+        """``CpRank.attend_and_push`` through the `prefill_cp` image: the gather owner's two warps push this
+        rank's K/V blocks to the ranks that need them while the load owner acquires each key block's
+        readiness counter. `rank` is an ``attention.CpRank`` (it owns the gathered buffers, counters,
+        peers tables, ticket and work list); one launch, every CTA resident."""
+        r = rank
+        if r.step_heads != 2:
+            raise ValueError("the linked images are the head-pair kernel")
+        r.generation += r.PARTS
+        r.ticket.zero_()
+        f32 = np.float32
+        block_bytes = attention.BLK * r.kv_heads * attention.D * 2
+        s = self.sessions["prefill_cp"]
+        p = struct.pack(PARAMS, r.work.data_ptr(), r.work.shape[0], r.q_heads, r.q_heads // r.kv_heads, 2 * r.C, r.out.data_ptr(),
+                        r.lse.data_ptr(), float(f32(1.0 / math.sqrt(attention.D)) * f32(1.4426950408889634)), 0.0, 0.0, 0,
+                        r.generation, r.ready.data_ptr(), r.status.buf.data_ptr(), k_local.data_ptr(), v_local.data_ptr(),
+                        r.k_peers.data_ptr(), r.v_peers.data_ptr(), r.ready_peers.data_ptr(), r.ticket.data_ptr(),
+                        r.C // attention.BLK, (block_bytes // r.PARTS) >> 4, r.PARTS, r.rank, r.world)
+        for stage_id in s.offsets:
+            if stage_id.startswith("attn.load"):
+                s.set_params(stage_id, _map(q_local) + _map(r.k_gather) + _map(r.v_gather) + p)
+            else:
+                s.set_params(stage_id, p)
+        sms = torch.cuda.get_device_properties(q_local.device).multi_processor_count
+        s.launch((min(sms, r.work.shape[0]), 1, 1), torch.cuda.current_stream().cuda_stream)
+        return r.out, r.lse
 
     def close(self):
         for s in self.sessions.values():

@@ -42,3 +42,31 @@ def test_linked_attention_wants_head_pairs(images):
     k = torch.zeros(1, 128, 3, 128, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(ValueError, match="head-pair"):
         images[0].forward(q, k, k)
+
+
+def test_linked_context_parallel_image_on_a_group_of_one(images):
+    """The `prefill_cp` composition (load owner behind readiness counters + the gather owner's ticketed
+    K/V push) on one rank: the gather warps move this rank's K/V from its local tensors into its own
+    gathered buffers while the load owner waits for the counts; the plain kernel's bits, three steps."""
+    from pipelink_b200 import _lib, attention as att, ep
+    S, Hq, Hkv = 2048, 8, 2
+    g = torch.Generator(device="cuda").manual_seed(99)
+    mk = lambda h: (torch.randn(S, h, 128, generator=g, device="cuda") * 0.8).to(torch.bfloat16)
+    q, k, v = mk(Hq), mk(Hkv), mk(Hkv)
+    want_o, want_lse = att.attention_fwd(q[None], k[None], v[None])
+    layout = att.CpRank.slab_layout(S, Hkv)
+    slab = ep.sym_alloc(layout["nbytes"])
+    try:
+        rnk = att.CpRank(S, Hq, Hkv, 0, 1, [slab], layout, "cuda", fused_push=True)
+        rnk.k_gather.fill_(float("nan"))
+        rnk.v_gather.fill_(float("nan"))
+        for step in range(3):
+            o, lse = images[0].attend_and_push(rnk, q, k, v)
+            torch.cuda.synchronize()
+            rnk.status.check(f"linked context-parallel image, step {step}")
+            assert torch.equal(o.view(torch.int16), want_o[0].view(torch.int16)), step
+            assert torch.equal(lse, want_lse), step
+            assert (rnk.ready.cpu().numpy() == (step + 1) * att.CpRank.PARTS).all()
+    finally:
+        torch.cuda.synchronize()
+        _lib.call("plb_sym_free", slab)
