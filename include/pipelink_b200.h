@@ -362,6 +362,9 @@ int plb_moe_swiglu_bwd_bf16(const void* gate_bf16, const void* up_bf16, const vo
                             const int32_t* num_tokens, int64_t capacity, int inter, void* d_gate_up_bf16, void* stream);
 /* dst [cols, rows] = src [rows, cols]^T, bf16, rows and cols multiples of 64. */
 int plb_bf16_transpose(const void* src_bf16, int64_t rows, int64_t cols, void* dst_bf16, void* stream);
+/* plb_bf16_transpose for a routed buffer sized for the worst case: only the 64-row tiles below *live_rows_dev move. */
+int plb_bf16_transpose_live(const void* src_bf16, int64_t rows, int64_t cols, const int32_t* live_rows_dev, void* dst_bf16,
+                            void* stream);
 
 /* ops.fwd_epilogue (campaigns/mok/host/mok_port_host.py:204):
  * out[t] = y_shared[t] + sum_j router_weights[t, j] * combine[t * topk + j], j ascending,

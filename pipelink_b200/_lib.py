@@ -65,6 +65,7 @@ PROTOTYPES = {
     "plb_moe_gemm_wgrad_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "plb_moe_swiglu_bwd_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "plb_bf16_transpose": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "plb_bf16_transpose_live": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "plb_moe_gemm_down_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                        c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "plb_ep_pull_rows_bulk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

@@ -201,9 +201,17 @@ swiglu_bwd_bf16_kernel(const uint4* __restrict__ gate, const uint4* __restrict__
 // shared memory, 128-byte segments on both sides. The bf16 weight-gradient GEMMs contract over the
 // schedule rows, so their operands are the transposes of the row-major activations.
 __global__ void __launch_bounds__(256)
-transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, int64_t rows, int64_t cols, __nv_bfloat16* __restrict__ out) {
+transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, int64_t rows, int64_t cols, const int* __restrict__ live_rows_dev,
+                      __nv_bfloat16* __restrict__ out) {
   __shared__ __nv_bfloat16 tile[64][66];
-  const int64_t tiles_c = cols >> 6, total = (rows >> 6) * tiles_c;
+  // a routed buffer is sized for the worst case: only the 64-row tiles in use are moved (`rows` stays
+  // the leading dimension of the transpose)
+  int64_t row_tiles = rows >> 6;
+  if (live_rows_dev != nullptr) {
+    const int64_t live = (static_cast<int64_t>(*live_rows_dev) + 63) >> 6;
+    if (live < row_tiles) row_tiles = live < 0 ? 0 : live;
+  }
+  const int64_t tiles_c = cols >> 6, total = row_tiles * tiles_c;
   for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
     const int64_t r0 = (t / tiles_c) << 6, c0 = (t % tiles_c) << 6;
     for (int i = threadIdx.x; i < 64 * 32; i += 256) {       // 32 pairs per row
@@ -332,9 +340,10 @@ cudaError_t launch_swiglu_bwd_bf16(const void* gate, const void* up, const void*
   return cudaGetLastError();
 }
 
-cudaError_t launch_transpose_bf16(const void* in, int64_t rows, int64_t cols, void* out, cudaStream_t stream) {
+cudaError_t launch_transpose_bf16(const void* in, int64_t rows, int64_t cols, const int* live_rows_dev, void* out,
+                                  cudaStream_t stream) {
   if (rows == 0 || cols == 0) return cudaSuccess;
-  transpose_bf16_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), rows, cols,
+  transpose_bf16_kernel<<<sm_grid(8), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), rows, cols, live_rows_dev,
                                                         static_cast<__nv_bfloat16*>(out));
   return cudaGetLastError();
 }

@@ -572,8 +572,13 @@ int plb_moe_swiglu_bwd_bf16(const void* gate_bf16, const void* up_bf16, const vo
 }
 
 int plb_bf16_transpose(const void* src_bf16, int64_t rows, int64_t cols, void* dst_bf16, void* stream) {
+  return plb_bf16_transpose_live(src_bf16, rows, cols, nullptr, dst_bf16, stream);
+}
+
+int plb_bf16_transpose_live(const void* src_bf16, int64_t rows, int64_t cols, const int* live_rows_dev, void* dst_bf16,
+                            void* stream) {
   if (!src_bf16 || !dst_bf16 || rows < 0 || cols < 0 || rows % 64 || cols % 64) return PLB_E_ARGUMENT;
-  return from_cuda(plb::launch_transpose_bf16(src_bf16, rows, cols, dst_bf16, static_cast<cudaStream_t>(stream)));
+  return from_cuda(plb::launch_transpose_bf16(src_bf16, rows, cols, live_rows_dev, dst_bf16, static_cast<cudaStream_t>(stream)));
 }
 
 int plb_moe_gemm_down_bf16(const void* hidden_bf16, const void* w2_bf16, const int32_t* block_expert,

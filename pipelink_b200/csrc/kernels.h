@@ -127,7 +127,8 @@ cudaError_t launch_swiglu_bwd(const void* gate, const void* gate_sc, const void*
                               float limit, void* dgu, cudaStream_t stream);
 cudaError_t launch_swiglu_bwd_bf16(const void* gate, const void* up, const void* d_hidden, const int* num_rows_dev,
                                    int64_t capacity, int inter, float limit, void* dgu, cudaStream_t stream);
-cudaError_t launch_transpose_bf16(const void* in, int64_t rows, int64_t cols, void* out, cudaStream_t stream);
+cudaError_t launch_transpose_bf16(const void* in, int64_t rows, int64_t cols, const int* live_rows_dev, void* out,
+                                  cudaStream_t stream);
 cudaError_t launch_ep_pull_rows_bulk(const void* const* xq_peers, const void* const* xsc_peers, const int* peer_rank,
                                      const int* peer_token_idx, const int* num_rows_dev, int64_t capacity, int hidden,
                                      void* x_routed_fp8, void* x_routed_sc, int scale_rows, Status* status,

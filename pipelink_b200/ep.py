@@ -426,6 +426,10 @@ class EpMoKHost(mok.MoKHost):
         """Down projection: data gradient d_hidden, then the weight gradient over each expert's rows."""
         b, w, sh = self.buffers, self.weights, self.shape
         H, I = sh.hidden, sh.intermediate
+        if self.precision == "bf16":
+            self._rows_gemm_bf16(b["d_y_routed"], w["w_down_t_bf16"], H, I, b["d_hidden_routed"], self._identity_rows)
+            self._wgrad_bf16(b["d_y_routed"], b["t_rows_h"], b["hidden_routed_bf16"], b["t_rows_i"], b["d_w_routed_down"])
+            return
         dy_q, dy_sc, dy_t, dy_t_sc = mok.mxfp8_quantize(b["d_y_routed"], True, True, self.schedule.num_tokens)
         self._gemm_rows(dy_q, dy_sc, w["w_down_t_fp8"], w["w_down_t_sc"], H, I, b["d_hidden_routed"], self._identity_rows)
         _, _, h_t, h_t_sc = mok.mxfp8_quantize(b["hidden_routed_bf16"], False, True, self.schedule.num_tokens)
@@ -434,6 +438,11 @@ class EpMoKHost(mok.MoKHost):
     def bwd_activation(self):
         s, b, sh = self.schedule, self.buffers, self.shape
         self.select_activation()
+        if self.precision == "bf16":
+            _lib.call("plb_moe_swiglu_bwd_bf16", b["gate_routed_bf16"].data_ptr(), b["up_routed_bf16"].data_ptr(),
+                      b["d_hidden_routed"].data_ptr(), s.num_tokens.data_ptr(), self.capacity, sh.intermediate,
+                      b["d_gate_up_routed"].data_ptr(), mok._stream())
+            return
         _lib.call("plb_moe_swiglu_bwd", b["gate_routed_fp8"].data_ptr(), b["gate_routed_sc"].data_ptr(),
                   b["up_routed_fp8"].data_ptr(), b["up_routed_sc"].data_ptr(), b["d_hidden_routed"].data_ptr(),
                   s.num_tokens.data_ptr(), self.capacity, sh.intermediate, b["d_gate_up_routed"].data_ptr(), mok._stream())
@@ -443,6 +452,13 @@ class EpMoKHost(mok.MoKHost):
         """Gate/up data gradient: d_x rows leave the GEMM epilogue straight into the home rank's
         [tokens * topk, H] buffer."""
         s, w, sh = self.schedule, self.weights, self.shape
+        if self.precision == "bf16":
+            # the bf16 GEMM's epilogue pushes to [token * topk + slot] of the home rank (no receive streams)
+            _lib.call("plb_moe_gemm_down_bf16", self.buffers["d_gate_up_routed"].data_ptr(), w["w_cat_t_bf16"].data_ptr(),
+                      s.block_expert.data_ptr(), s.num_tokens.data_ptr(), s.dest_row.data_ptr(), s.peer_rank.data_ptr(),
+                      self.capacity, self.num_local_experts, 2 * sh.intermediate, sh.hidden, self.push_rotation, None,
+                      self.d_x_rows_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
+            return
         dgu_q, dgu_sc, _, _ = self._dgu
         # with receive streams the rows take the positions the forward's combine rows took (same schedule)
         dest, peers = (self.stream_row, self.d_x_recv_peers) if self._streamed else (s.dest_row, self.d_x_rows_peers)
@@ -454,6 +470,10 @@ class EpMoKHost(mok.MoKHost):
     def bwd_gate_up_wgrad(self):
         """Gate/up weight gradient: the bf16 token rows pulled from their home ranks, quantised along the rows."""
         s, b, sh = self.schedule, self.buffers, self.shape
+        if self.precision == "bf16":
+            # the bf16 rows the forward's dispatch gathered are still in place
+            self._wgrad_bf16(b["d_gate_up_routed"], b["t_rows_2i"], b["x_routed_bf16"], b["t_rows_h2"], b["d_w_routed_gate_up"])
+            return
         _, _, dgu_t, dgu_t_sc = self._dgu
         # rows come from the copies the forward made of every rank's tokens (local reads); without a
         # training forward in front (a LocalGroup stepping phases by hand) they are pulled from the peers
@@ -511,8 +531,6 @@ class EpMoKHost(mok.MoKHost):
 
     def backward(self, d_out: torch.Tensor, *, check: bool = True):
         """Backward of the last ``forward(train=True)`` of a distributed group."""
-        if self.precision == "bf16":
-            raise ValueError("the backward cells of the bf16 routed precision are single-rank (mok.MoKHost)")
         if not self.group.distributed:
             raise ValueError("ranks of a LocalGroup are stepped together: use backward_local_group()")
         self.d_out_buffer.copy_(d_out)

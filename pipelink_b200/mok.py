@@ -472,8 +472,9 @@ class MoKHost:
     def _wgrad_bf16(self, a_rows, a_t, b_rows, b_t, out):
         """out[e] = A_e^T . B_e over each expert's rows of the schedule: A [P, M], B [P, N] row-major."""
         P, M, N = self.capacity, a_rows.shape[1], b_rows.shape[1]
-        _lib.call("plb_bf16_transpose", a_rows.data_ptr(), P, M, a_t.data_ptr(), _stream())
-        _lib.call("plb_bf16_transpose", b_rows.data_ptr(), P, N, b_t.data_ptr(), _stream())
+        live = self.schedule.num_tokens.data_ptr()       # only the rows in use are transposed
+        _lib.call("plb_bf16_transpose_live", a_rows.data_ptr(), P, M, live, a_t.data_ptr(), _stream())
+        _lib.call("plb_bf16_transpose_live", b_rows.data_ptr(), P, N, live, b_t.data_ptr(), _stream())
         _lib.call("plb_moe_gemm_wgrad_bf16", a_t.data_ptr(), b_t.data_ptr(), self.schedule.expert_offsets.data_ptr(), P,
                   self.num_local_experts, M, N, out.data_ptr(), self.status.buf.data_ptr(), _stream())
 

@@ -140,6 +140,33 @@ def main():
         torch.cuda.synchronize()
         dist.barrier()
         group.close()
+    # ---- the bf16 routed precision: forward + backward across the group == the single-rank bf16 pass
+    single_bf = mok.MoKHost(whole, device=dev, precision="bf16")
+    single_bf.load_weights(wg * 2.5, wu * 2.5, wd * 2.5, train=True)
+    group = ep.IpcGroup(shape, rank, world, dev, train=True)
+    host = ep.EpMoKHost(shape, rank, group, precision="bf16")
+    host.load_weights(wg[rank * El:(rank + 1) * El] * 2.5, wu[rank * El:(rank + 1) * El] * 2.5, wd[rank * El:(rank + 1) * El] * 2.5, train=True)
+    for generation in (1, 3):
+        inputs = [mok.MoKHost.new_inputs(shape, generation, dev, rank=r, world=world) for r in range(world)]
+        gen = torch.Generator(device=dev).manual_seed(177 + generation)
+        d_outs = [torch.randn(L, H, generator=gen, device=dev).to(torch.bfloat16) for _ in range(world)]
+        joined = mok.Inputs(torch.cat([i.x for i in inputs]), torch.cat([i.experts for i in inputs]), torch.cat([i.router for i in inputs]))
+        out_single = single_bf.forward(joined, train=True)["output"].clone()
+        want = {k: v.clone() for k, v in single_bf.backward(torch.cat(d_outs)).items()}
+        host.buffers["d_x_routed_buffer"].fill_(float("nan"))
+        out = host.forward(inputs[rank], train=True)["output"]
+        g = host.backward(d_outs[rank])
+        torch.cuda.synchronize()
+        tag = (rank, generation, "bf16")
+        assert eq(out, out_single[rank * L:(rank + 1) * L]), (tag, "output")
+        assert torch.isfinite(g["d_x"].float()).all()
+        assert eq(g["d_x"], want["d_x"][rank * L:(rank + 1) * L]), (tag, "d_x")
+        assert eq(g["d_router_weights"], want["d_router_weights"][rank * L:(rank + 1) * L]), (tag, "d_router_weights")
+        for name in ("d_w_routed_gate", "d_w_routed_up", "d_w_routed_down"):
+            assert eq(g[name], want[name][rank * El:(rank + 1) * El]), (tag, name)
+    torch.cuda.synchronize()
+    dist.barrier()
+    group.close()
     dist.destroy_process_group()
     if rank == 0:
         print("EP CHILD OK")
