@@ -16,6 +16,7 @@ import z3
 
 from .model import ClauseFailure, PipeLinkError
 
+SOLVE_TIMEOUT_MS = 120000
 PRECEDENCE = ("L-BUDGET", "L-OVERLAP", "L-HANDLE", "L-TOPO", "L-ALIGN", "L-REGS")
 
 
@@ -198,13 +199,16 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         highwater[phys] = hw
         opt.minimize(hw)
         tiers.append({"name": f"min high-water {phys}"})
-    # finally prefer low bases so layouts are deterministic (PLB_SOLVE_TIEBREAK=0 to time the solve without it)
-    import os
-    if os.environ.get("PLB_SOLVE_TIEBREAK", "1") == "1":
-        for n in names:
-            opt.minimize(base_vars[n])
+    # finally prefer low bases so layouts are deterministic
+    for n in names:
+        opt.minimize(base_vars[n])
 
-    if opt.check() != z3.sat:
+    opt.set("timeout", SOLVE_TIMEOUT_MS)
+    verdict = opt.check()
+    if verdict == z3.unknown:       # a link must end: say so instead of searching on
+        raise PipeLinkError(ClauseFailure("L-BUDGET", "solve", f"the solver gave up after {SOLVE_TIMEOUT_MS // 1000} s "
+                                          f"({opt.reason_unknown()}); pin some bases in forced_bindings or declare fewer claims"))
+    if verdict != z3.sat:
         _diagnose(cons)
     model = opt.model()
     val = lambda e: e if isinstance(e, int) else model.eval(e, model_completion=True).as_long()
