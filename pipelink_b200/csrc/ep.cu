@@ -23,16 +23,10 @@ namespace plb {
 
 namespace {
 
-__device__ __forceinline__ void red_release_sys_add(unsigned* addr, unsigned v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* addr) {
   unsigned v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
   return v;
-}
-__device__ __forceinline__ void fence_acq_rel_sys() {
-  asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
 
 // One CTA. Thread i < world signals peer i's flag[rank] and waits for its own flag[i].

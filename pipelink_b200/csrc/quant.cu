@@ -18,8 +18,6 @@ namespace {
 
 constexpr int kThreads = 256;
 
-__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
 // One thread owns 8 consecutive elements; 4 adjacent lanes own one 32-element block.
 template <bool GATHER>

@@ -202,7 +202,7 @@ class EpMoKHost(mok.MoKHost):
                 nbytes = _lib.load().plb_moe_schedule_streams_scratch_bytes(W, L, k, self.num_local_experts)
                 self.stream_scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.int32, device=dev)
         self._streamed = False
-        self.linked, self.one_launch = None, False      # attach_linked(): the FFN as one launch of the linked forward image
+        self.linked, self.one_launch, self.one_launch_full = None, False, False   # attach_linked()
         me = ptrs[rank]
         self.xq = tensor_from_ptr(me + lay.xq, (L, H), torch.uint8, dev)
         self.xsc = tensor_from_ptr(me + lay.xsc, (L // 128, H // 128, 32, 16), torch.uint8, dev)
@@ -317,23 +317,32 @@ class EpMoKHost(mok.MoKHost):
                   s.peer_rank.data_ptr(), self.capacity, self.num_local_experts, sh.intermediate, sh.hidden,
                   self.push_rotation, self.push_stride, self.combine_peers.data_ptr(), self.status.buf.data_ptr(), mok._stream())
 
-    def attach_linked(self, linked):
+    def attach_linked(self, linked, full: bool = False):
         """Run the inference forward's expert FFN through the linked forward image (moe_linked.LinkedMoE on
-        this host): dispatch warps, both projections and the combine push in ONE launch."""
-        self.linked, self.one_launch = linked, linked is not None
+        this host): dispatch warps, both projections and the combine push in ONE launch. With `full` the same
+        launch also holds the group barrier and the weighted epilogue: everything after the schedule."""
+        self.linked, self.one_launch, self.one_launch_full = linked, linked is not None, linked is not None and full
 
     def ffn_one_launch(self):
-        """pull() + gemm_gate_up() + gemm_down_push() as one launch of the linked forward image."""
+        """pull() + gemm_gate_up() + gemm_down_push() as one launch of the linked forward image; with the
+        full image also barrier() + fwd_epilogue(), and the output is returned."""
         s = self.schedule
         self._streamed = self.stream_push
         if self._streamed and not self.schedule_writes_streams:
             self.stream_rows()
         if not self.fused_dispatch:
             self.pull()
-        self.linked.forward_ffn(dispatch=self.fused_dispatch,
-                                dest_rows=self.stream_row if self._streamed else s.dest_row,
-                                out_peers=self.recv_peers if self._streamed else self.combine_peers,
-                                rotation=self.push_rotation, stride=self.push_stride)
+        kw = dict(dispatch=self.fused_dispatch, dest_rows=self.stream_row if self._streamed else s.dest_row,
+                  out_peers=self.recv_peers if self._streamed else self.combine_peers,
+                  rotation=self.push_rotation, stride=self.push_stride)
+        if not self.one_launch_full:
+            self.linked.forward_ffn(**kw)
+            return None
+        if not self.group.distributed:
+            raise ValueError("the full forward image waits for the other ranks inside the launch: real GPUs only")
+        return self.linked.forward_full(combine=self.recv if self._streamed else self.buffers["combine_buffer"],
+                                        index=self.recv_index if self._streamed else None, flags_peers=self.flags_peers,
+                                        barrier_state=self.barrier_state, rank=self.rank, world=self.world, **kw)
 
     def fwd_epilogue(self, y_shared=None):
         if not self._streamed:
@@ -374,7 +383,9 @@ class EpMoKHost(mok.MoKHost):
         self.barrier()          # routes gathered, every rank's quantised tokens readable
         self.build_schedule()
         if self.one_launch and not train:
-            self.ffn_one_launch()
+            out = self.ffn_one_launch()
+            if out is not None:
+                return out          # the launch held the barrier and the epilogue too
         else:
             self.pull()
             if train:
@@ -640,9 +651,9 @@ class BenchSession:
         h.barrier()
         h.build_schedule()
         if h.one_launch and not self.train:
-            h.ffn_one_launch()
-            h.barrier()
-            h.fwd_epilogue()
+            if h.ffn_one_launch() is None:
+                h.barrier()
+                h.fwd_epilogue()
             return
         h.pull()
         gate_up = h.gemm_gate_up_train if self.train else h.gemm_gate_up
@@ -682,11 +693,12 @@ class BenchSession:
             from . import moe_linked
             linked = moe_linked.LinkedMoE(h)
             forms.append(("one launch (linked image)", True, True))
+            forms.append(("whole forward in one launch (linked image)", True, "full"))
         except Exception:  # noqa: BLE001 - images absent: the library's launches are timed alone
             linked = None
         for name, fused, one in forms:
             h.fused_dispatch = fused
-            h.attach_linked(linked if one else None)
+            h.attach_linked(linked if one else None, full=one == "full")
             for _ in range(2):
                 self.step()
             torch.cuda.synchronize()
@@ -715,7 +727,7 @@ class BenchSession:
         chosen = min(times, key=times.get)
         _, fused, one = next(f for f in forms if f[0] == chosen)
         h.fused_dispatch = fused
-        h.attach_linked(linked if one else None)
+        h.attach_linked(linked if one else None, full=one == "full")
         if linked is not None and not one:
             linked.close()
         out = {"ms_per_step": times, "chosen": chosen}

@@ -27,7 +27,7 @@ from . import _lib, mok
 from .pipec2.launcher import Session
 
 OUT_DIR = Path(__file__).resolve().parent / "stages" / "moe" / "out"
-COMPOSITIONS = ("gate_up", "gate_up_dispatch", "down", "fwd", "fwd_dispatch")
+COMPOSITIONS = ("gate_up", "gate_up_dispatch", "down", "fwd", "fwd_dispatch", "fwd_full", "fwd_full_dispatch")
 
 
 def ensure_built() -> Path:
@@ -118,12 +118,14 @@ class LinkedMoE:
                                                                 dest.data_ptr(), sched.peer_rank.data_ptr(), sh.hidden, 0))
         self._launch("down")
 
-    def forward_ffn(self, dispatch: bool = False, dest_rows=None, out=None, out_peers=None, rotation: int = 0, stride: int = 1):
+    def forward_ffn(self, dispatch: bool = False, dest_rows=None, out=None, out_peers=None, rotation: int = 0, stride: int = 1,
+                    tail=None):
         """Gate/up projection + SwiGLU + requantise, then the down projection with its row placement (or
         combine push), in ONE launch of a linked image: the work of gemm_gate_up() followed by gemm_down().
-        With dispatch, the comm owner also pulls the routed rows from the home ranks under the mainloop."""
+        With dispatch, the comm owner also pulls the routed rows from the home ranks under the mainloop.
+        With `tail` (see forward_full) the same launch ends with the group barrier and the weighted epilogue."""
         h, b, w, sh = self.host, self.host.buffers, self.host.weights, self.host.shape
-        name = "fwd_dispatch" if dispatch else "fwd"
+        name = ("fwd_full" if tail is not None else "fwd") + ("_dispatch" if dispatch else "")
         s = self.sessions[name]
         if h.capacity // 256 > 4096 or sh.hidden > 4096:
             raise ValueError("the forward image counts at most 4096 row tiles of rows up to 4096 bytes")
@@ -146,11 +148,31 @@ class LinkedMoE:
         dest = sched.dest_row if dest_rows is None else dest_rows
         out = b["combine_buffer"] if out is None else out
         limit = h.swiglu_limit if h.swiglu_limit > 0 else self.inf
-        s.set_params("moe.fwd.epilogue", g1 + g2 + struct.pack(
+        epilogue = g1 + g2 + struct.pack(
             "<QQQQQQQiifi", b["hidden_routed_fp8"].data_ptr(), b["hidden_routed_sc"].data_ptr(), out.data_ptr(),
             0 if out_peers is None else out_peers.data_ptr(), dest.data_ptr(), sched.peer_rank.data_ptr(), counters,
-            sh.intermediate, sh.hidden, limit, 0))
+            sh.intermediate, sh.hidden, limit, 0)
+        if tail is None:
+            s.set_params("moe.fwd.epilogue", epilogue)
+        else:
+            # MoeFwdCombineParams = {MoeFwdEpilogueParams (176 bytes with its tail padding), MoeFwdTailParams}
+            s.set_params("moe.fwd.epilogue.combine", epilogue.ljust(176, b"\0") + tail)
         self._launch(name)
+
+    def forward_full(self, dispatch: bool = False, *, dest_rows=None, out_peers=None, rotation: int = 0, stride: int = 1,
+                     combine=None, index=None, flags_peers=None, barrier_state=None, rank: int = 0, world: int = 1):
+        """The whole forward after the schedule in ONE launch: forward_ffn() followed, inside the same launch,
+        by the group barrier (every rank's rows have landed; one rank: every CTA is done) and the weighted
+        epilogue into the session's output. `combine` / `index`: where the epilogue reads a (token, slot)
+        row (default: the session's combine buffer at token * topk + slot)."""
+        h, b, sh = self.host, self.host.buffers, self.host.shape
+        combine = b["combine_buffer"] if combine is None else combine
+        tail = struct.pack("<QQQQQQqiiii", combine.data_ptr(), 0 if index is None else index.data_ptr(),
+                           h.router_weight_buffer.data_ptr(), b["output"].data_ptr(),
+                           0 if flags_peers is None else flags_peers.data_ptr(),
+                           0 if barrier_state is None else barrier_state.data_ptr(), sh.tokens, sh.topk, sh.hidden, rank, world)
+        self.forward_ffn(dispatch, dest_rows=dest_rows, out_peers=out_peers, rotation=rotation, stride=stride, tail=tail)
+        return b["output"]
 
     def close(self):
         for s in self.sessions.values():

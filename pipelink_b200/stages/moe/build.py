@@ -11,6 +11,8 @@ campaigns/mok/README.md:80-118):
     down               load + mma + comm.none     + epilogue.rows-bf16      (placement or combine push)
     fwd                fwd.load + fwd.mma + comm.none     + fwd.epilogue    (both projections, one launch)
     fwd_dispatch       fwd.load + fwd.mma + comm.dispatch + fwd.epilogue    (dispatch, both projections, combine push)
+    fwd_full           fwd.load + fwd.mma + comm.none     + fwd.epilogue.combine   (+ group barrier and weighted epilogue)
+    fwd_full_dispatch  fwd.load + fwd.mma + comm.dispatch + fwd.epilogue.combine   (the whole forward after the schedule)
 
 The link solves the ring depth of the ``operands`` channel, every shared-memory / barrier /
 tensor-memory / counter base, the warp tiling and the two register groups. Runs without a GPU.
@@ -38,7 +40,8 @@ ABI = {"schema": "3.0", "target": {"profile": "sm_100a", "lto_arch": "lto_100a",
                                    "math": {"ftz": False, "prec_div": True, "prec_sqrt": True, "fmad": True}}}
 HELPERS = ("pipelink_moe_regs_helpers", "helpers", 56)     # load + mma + comm: one warpgroup
 EPILOGUE = ("pipelink_moe_regs_epilogue", "epilogue", 224)  # two warpgroups
-STAGES = ("load", "mma", "comm_none", "comm_dispatch", "epilogue_swiglu", "epilogue_rows", "fwd_load", "fwd_mma", "fwd_epilogue")
+STAGES = ("load", "mma", "comm_none", "comm_dispatch", "epilogue_swiglu", "epilogue_rows", "fwd_load", "fwd_mma", "fwd_epilogue",
+          "fwd_epilogue_combine")
 _manifests = None
 
 
@@ -67,9 +70,12 @@ COMPOSITIONS = {
     "down": ["load", "mma", "comm_none", "epilogue_rows"],
     "fwd": ["fwd_load", "fwd_mma", "comm_none", "fwd_epilogue"],
     "fwd_dispatch": ["fwd_load", "fwd_mma", "comm_dispatch", "fwd_epilogue"],
+    "fwd_full": ["fwd_load", "fwd_mma", "comm_none", "fwd_epilogue_combine"],
+    "fwd_full_dispatch": ["fwd_load", "fwd_mma", "comm_dispatch", "fwd_epilogue_combine"],
 }
 BASE_DOMAINS = {"pipelink_moe_operands": "smem", "pipelink_moe_staging": "smem", "pipelink_moe_dispatch_ring": "smem",
-                "pipelink_moe_hidden_ready": "gmem_counter", "pipelink_moe_full": "mbarrier",
+                "pipelink_moe_hidden_ready": "gmem_counter", "pipelink_moe_ctas_done": "gmem_counter",
+                "pipelink_moe_tail_barrier": "named_barrier", "pipelink_moe_full": "mbarrier",
                 "pipelink_moe_empty": "mbarrier", "pipelink_moe_acc_full": "mbarrier", "pipelink_moe_acc_empty": "mbarrier",
                 "pipelink_moe_drain": "mbarrier", "pipelink_moe_acc": "tmem", "pipelink_moe_sfcols": "tmem",
                 "pipelink_moe_warp_load": "warp", "pipelink_moe_warp_mma": "warp", "pipelink_moe_warp_comm": "warp",

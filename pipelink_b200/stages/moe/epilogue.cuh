@@ -118,4 +118,122 @@ __device__ __forceinline__ void rows_tile(const EpilogueWarp& e, const Tile& t, 
     __syncwarp();
   }
 }
+
+// The tile loop of the one-launch forward's epilogue: pass-1 tiles through the SwiGLU body (then the
+// row tile's hidden_ready count), pass-2 tiles through the row-store body. False when a wait ran out.
+__device__ __forceinline__ bool fwd_epilogue_tiles(const MoeFwdEpilogueParams& p, const EpilogueWarp& e, uint32_t smem) {
+  const FwdWalk f = make_fwd_walk(p.g1, p.g2, e.lane, false);
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  uint32_t acc_phase = 0;
+  bool ok = true;
+  for (int tile = pair_id; tile < f.total && ok; tile += num_pairs) {
+    const bool second = tile >= f.tiles1;
+    const Tile t = decode(second ? p.g2 : p.g1, second ? f.w2 : f.w1, second ? tile - f.tiles1 : tile, static_cast<int>(e.cta_rank));
+    if (!plb::mbar_wait(bar(smem, pipelink_moe_acc_full()), acc_phase, p.g1.status, plb::ST_TIMEOUT_TMEM_FULL, 0)) ok = false;
+    ok = __all_sync(0xFFFFFFFFu, ok);
+    if (!ok) break;
+    plb::tc_fence_after();
+    if (!second) {
+      swiglu_tile(e, t, p.hidden, p.hidden_sc, p.hidden_cols, p.limit);
+      // the warp's stores first, then its count: the load owner acquires the count before it reads the rows
+      __threadfence();
+      __syncwarp();
+      if (e.lane == 0) plb::red_release_gpu_add(p.counters + pipelink_moe_hidden_ready() + (t.a_blk >> 1), 1u);
+    } else {
+      rows_tile(e, t, p.out, p.out_peers, p.dest_row, p.peer_rank, p.out_cols);
+    }
+    acc_phase ^= 1u;
+  }
+  return ok;
+}
+
+__device__ __forceinline__ void tail_sync() {   // the eight epilogue warps of this CTA
+  asm volatile("bar.sync %0, %1;" ::"r"(pipelink_moe_tail_barrier()), "r"(EpilogueWarps * 32) : "memory");
+}
+
+// The forward's tail (see MoeFwdTailParams). Every CTA counts itself done; the CTA that completes the
+// count tells the group (one release per rank, as plb_ep_barrier does) and advances this rank's barrier
+// generation; every CTA then waits, bounded, for all ranks' flags (one rank: for the count) and takes
+// its share of the weighted sums. Arithmetic and order of weighted_combine_kernel: the same bits.
+__device__ __forceinline__ void fwd_tail(const MoeFwdTailParams& t, unsigned* counters, plb::Status* status, bool ok) {
+  const int tid = static_cast<int>(threadIdx.x) - 32 * pipelink_moe_warp_epilogue();      // 0 .. 255
+  __shared__ int tail_failed;
+  unsigned target = 0;
+  if (t.flags_peers != nullptr) target = plb::ld_volatile_u32(t.barrier_state) + 1u;      // read before anyone can advance it
+  if (tid == 0) tail_failed = 0;
+  tail_sync();
+  if (!ok) tail_failed = 1;        // a warp whose wait ran out: the CTA still counts itself done, then leaves
+  __threadfence_system();          // this thread's row stores (local and to peers) before its CTA is counted done
+  tail_sync();
+  unsigned* done = counters + pipelink_moe_ctas_done();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned before = atomicAdd(done, 1u);
+    __threadfence();
+    if (before + 1u == gridDim.x && t.flags_peers != nullptr) {
+      // every CTA of this GPU has pushed its rows: one release per rank, then this rank's generation
+      plb::fence_acq_rel_sys();
+      for (int r = 0; r < t.world; ++r) plb::red_release_sys_add(t.flags_peers[r] + t.rank, 1u);
+      *reinterpret_cast<volatile unsigned*>(t.barrier_state) = target;
+      __threadfence();
+    }
+  }
+  // wait: thread i < world for rank i's flag here; one rank: thread 0 for the count
+  const int waiters = t.flags_peers != nullptr ? t.world : 1;
+  if (tid < waiters) {
+    const unsigned* flag = t.flags_peers != nullptr ? t.flags_peers[t.rank] + tid : done;
+    const unsigned want = t.flags_peers != nullptr ? target : gridDim.x;
+    const long long t0 = clock64();
+    for (unsigned it = 0;; ++it) {
+      const unsigned v = t.flags_peers != nullptr ? plb::ld_acquire_sys_u32(flag) : plb::ld_acquire_gpu_u32(flag);
+      if (static_cast<int>(v - want) >= 0) break;
+      if ((it & 63u) == 63u) {
+        if (clock64() - t0 > plb::kWaitBudgetCycles || plb::ld_volatile_i32(&status->code) != 0) {
+          plb::report_failure(status, plb::ST_TIMEOUT_COUNTER, 330 + tid, v, want);
+          tail_failed = 1;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+  }
+  tail_sync();
+  if (*reinterpret_cast<volatile int*>(&tail_failed) != 0) return;
+  const uint4* combine = reinterpret_cast<const uint4*>(t.combine);
+  uint4* out = reinterpret_cast<uint4*>(t.output);
+  const long long vec_per_row = t.hidden >> 3, total = t.tokens * vec_per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * (EpilogueWarps * 32);
+  for (long long v = static_cast<long long>(blockIdx.x) * (EpilogueWarps * 32) + tid; v < total; v += stride) {
+    const long long tok = v / vec_per_row, j = v - tok * vec_per_row;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s0 = 0; s0 < t.topk; s0 += 8) {          // eight rows in flight
+      uint4 c[8];
+      float ws[8];
+      const int n = t.topk - s0 < 8 ? t.topk - s0 : 8;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        if (s < n) {
+          const long long slot = tok * t.topk + s0 + s;
+          ws[s] = t.router_w[slot];
+          c[s] = combine[(t.index != nullptr ? static_cast<long long>(t.index[slot]) : slot) * vec_per_row + j];
+        }
+      }
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        if (s < n) {
+          const float f[8] = {plb::bf16_lo(c[s].x), plb::bf16_hi(c[s].x), plb::bf16_lo(c[s].y), plb::bf16_hi(c[s].y),
+                              plb::bf16_lo(c[s].z), plb::bf16_hi(c[s].z), plb::bf16_lo(c[s].w), plb::bf16_hi(c[s].w)};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(ws[s], f[i]));
+        }
+      }
+    }
+    uint4 o;
+    o.x = plb::pack_bf16(__float_as_uint(acc[0]), __float_as_uint(acc[1]));
+    o.y = plb::pack_bf16(__float_as_uint(acc[2]), __float_as_uint(acc[3]));
+    o.z = plb::pack_bf16(__float_as_uint(acc[4]), __float_as_uint(acc[5]));
+    o.w = plb::pack_bf16(__float_as_uint(acc[6]), __float_as_uint(acc[7]));
+    out[v] = o;
+  }
+}
 }  // namespace moe

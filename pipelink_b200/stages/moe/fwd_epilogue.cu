@@ -28,27 +28,6 @@ extern "C" __device__ void moe_fwd_epilogue_role(const void* raw_params, unsigne
   extern __shared__ __align__(1024) unsigned char pl_smem[];
   const uint32_t smem = plb::smem_u32(pl_smem);
   const EpilogueWarp e = epilogue_warp(smem, pl_smem, true);
-  const FwdWalk f = make_fwd_walk(p.g1, p.g2, e.lane, false);
-  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  uint32_t acc_phase = 0;
-  bool ok = true;
-  for (int tile = pair_id; tile < f.total && ok; tile += num_pairs) {
-    const bool second = tile >= f.tiles1;
-    const Tile t = decode(second ? p.g2 : p.g1, second ? f.w2 : f.w1, second ? tile - f.tiles1 : tile, static_cast<int>(e.cta_rank));
-    if (!plb::mbar_wait(bar(smem, pipelink_moe_acc_full()), acc_phase, p.g1.status, plb::ST_TIMEOUT_TMEM_FULL, 0)) ok = false;
-    ok = __all_sync(0xFFFFFFFFu, ok);
-    if (!ok) break;
-    plb::tc_fence_after();
-    if (!second) {
-      swiglu_tile(e, t, p.hidden, p.hidden_sc, p.hidden_cols, p.limit);
-      // the warp's stores first, then its count: the load owner acquires the count before it reads the rows
-      __threadfence();
-      __syncwarp();
-      if (e.lane == 0) plb::red_release_gpu_add(p.counters + pipelink_moe_hidden_ready() + (t.a_blk >> 1), 1u);
-    } else {
-      rows_tile(e, t, p.out, p.out_peers, p.dest_row, p.peer_rank, p.out_cols);
-    }
-    acc_phase ^= 1u;
-  }
+  fwd_epilogue_tiles(p, e, smem);
 }
 #endif  // !PIPELINK_EMIT

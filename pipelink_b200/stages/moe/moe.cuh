@@ -121,6 +121,24 @@ struct alignas(16) MoeFwdEpilogueParams {
   int pad;
 };
 
+// The forward's tail inside the same launch: once every CTA of this GPU has finished its down-projection
+// tiles (and, in a group, every rank has said so through the group's flags), the epilogue warps sum
+// each token's top-k rows with its router weights.
+struct alignas(16) MoeFwdTailParams {
+  const uint8_t* combine;          // bf16 rows: the [tokens * topk, H] slots, or the receive streams
+  const int* index;                // row of (token, slot) in `combine`, or null for token * topk + slot
+  const float* router_w;           // [tokens, topk]
+  uint8_t* output;                 // bf16 [tokens, H]
+  unsigned* const* flags_peers;    // the group barrier's flags (per rank: u32 [world]), or null for one rank
+  unsigned* barrier_state;         // [0]: this rank's barrier generation, advanced here
+  long long tokens;
+  int topk, hidden, rank, world;
+};
+struct alignas(16) MoeFwdCombineParams {
+  MoeFwdEpilogueParams e;
+  MoeFwdTailParams t;
+};
+
 extern "C" __device__ int pipelink_moe_depth();
 extern "C" __device__ int pipelink_moe_operands();     // smem byte offset of the ring
 extern "C" __device__ int pipelink_moe_full();         // first mbarrier slot (16 bytes each)
@@ -137,6 +155,8 @@ extern "C" __device__ int pipelink_moe_rows_ready();   // first counter slot of 
 extern "C" __device__ int pipelink_moe_ticket();       // counter slot of the dispatch ticket
 extern "C" __device__ int pipelink_moe_hidden_ready(); // first counter slot of the per-row-tile pass-1 completion counts
 extern "C" __device__ int pipelink_moe_dispatch_ring();// smem byte offset: 8 KiB per dispatch warp
+extern "C" __device__ int pipelink_moe_ctas_done();    // counter slot: CTAs of this launch that finished their tiles
+extern "C" __device__ int pipelink_moe_tail_barrier(); // named barrier of the eight epilogue warps
 extern "C" __device__ int pipelink_tmem_slot();        // smem byte offset where dispatch put the TMEM base
 
 #ifndef PIPELINK_EMIT
@@ -278,5 +298,6 @@ inline pl::endpoint hidden_ready(const char* direction, const char* role) {
 
 static_assert(sizeof(MoeGeometry) == 48 && sizeof(MoeLoadParams) == 576 && sizeof(MoeMmaParams) == 48 &&
               sizeof(MoeCommParams) == 112 && sizeof(MoeSwigluParams) == 80 && sizeof(MoeRowsParams) == 96 &&
-              sizeof(MoeFwdLoadParams) == 1152 && sizeof(MoeFwdMmaParams) == 96 && sizeof(MoeFwdEpilogueParams) == 176,
+              sizeof(MoeFwdLoadParams) == 1152 && sizeof(MoeFwdMmaParams) == 96 && sizeof(MoeFwdEpilogueParams) == 176 &&
+              sizeof(MoeFwdTailParams) == 80 && sizeof(MoeFwdCombineParams) == 256,
               "parameter blocks: the manifests and the host image state these sizes");

@@ -52,12 +52,13 @@ def main():
     # ---- the FFN as ONE launch of the linked forward image (dispatch warps, both projections, combine push)
     from pipelink_b200 import moe_linked
     linked = moe_linked.LinkedMoE(host)
-    host.attach_linked(linked)
-    for fused in (True, False):
-        host.fused_dispatch = fused
-        for b, w in zip(batches, want):
-            got = host.forward(b)["output"].cpu()
-            assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "one-launch forward", fused)
+    for full in (False, True):      # full: the group barrier and the weighted epilogue inside the launch too
+        host.attach_linked(linked, full=full)
+        for fused in (True, False):
+            host.fused_dispatch = fused
+            for b, w in zip(batches, want):
+                got = host.forward(b)["output"].cpu()
+                assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "one-launch forward", fused, full)
     host.attach_linked(None)
     host.fused_dispatch = False
     torch.cuda.synchronize()
@@ -85,11 +86,12 @@ def main():
         got = host.forward(b)["output"].cpu()
         assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "receive streams")
     linked = moe_linked.LinkedMoE(host)
-    host.attach_linked(linked)
     host.fused_dispatch = True
-    for b, w in zip(batches, want):
-        got = host.forward(b)["output"].cpu()
-        assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "one-launch forward, receive streams")
+    for full in (False, True):
+        host.attach_linked(linked, full=full)
+        for b, w in zip(batches, want):
+            got = host.forward(b)["output"].cpu()
+            assert torch.equal(got.view(torch.int16), w.view(torch.int16)), (rank, "one-launch forward, receive streams", full)
     host.attach_linked(None)
     host.fused_dispatch = False
     torch.cuda.synchronize()

@@ -32,7 +32,7 @@ def test_linked_images_equal_the_library_kernels(linked_dir, shape_args, generat
         for step in range(2):
             inputs = mok.MoKHost.new_inputs(shape, generation + step, "cuda")
             want = lib.forward(inputs)
-            for dispatch, one_launch in ((False, False), (True, False), (False, True), (True, True)):
+            for dispatch, one_launch in ((False, False), (True, False), (False, True), (True, True), (False, "full"), (True, "full")):
                 lnk.status.reset()
                 lnk.fused_dispatch = dispatch               # quantise_tokens then also writes the scale rows
                 for name in ("x_routed_fp8", "hidden_routed_fp8"):
@@ -42,12 +42,16 @@ def test_linked_images_equal_the_library_kernels(linked_dir, shape_args, generat
                 lnk.x_buffer.copy_(inputs.x)
                 lnk.router_weight_buffer.copy_(inputs.router)
                 lnk.dispatch()                              # with dispatch: quantise only, the image pulls
-                if one_launch:                              # both projections in one launch of the fwd image
+                if one_launch == "full":                    # ... and the weighted epilogue in the same launch
+                    lnk.buffers["output"].fill_(float("nan"))
+                    out = linked.forward_full(dispatch=dispatch)
+                elif one_launch:                            # both projections in one launch of the fwd image
                     linked.forward_ffn(dispatch=dispatch)
+                    out = lnk.fwd_epilogue()
                 else:
                     linked.gemm_gate_up(dispatch=dispatch)
                     linked.gemm_down()
-                out = lnk.fwd_epilogue()
+                    out = lnk.fwd_epilogue()
                 torch.cuda.synchronize()
                 lnk.status.check("linked forward")
                 total = int(lib.schedule.num_tokens.item())

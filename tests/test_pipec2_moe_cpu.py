@@ -170,9 +170,9 @@ def linked(tmp_path_factory):
     return out, mb.build(out, one_tu=False)      # the one-unit control builds are for timing on a GPU
 
 
-def test_five_compositions_link_from_one_set_of_packages(linked):
+def test_seven_compositions_link_from_one_set_of_packages(linked):
     out, results = linked
-    assert set(results) == {"gate_up", "gate_up_dispatch", "down", "fwd", "fwd_dispatch"}
+    assert set(results) == {"gate_up", "gate_up_dispatch", "down", "fwd", "fwd_dispatch", "fwd_full", "fwd_full_dispatch"}
     for comp, r in results.items():
         assert (r.threads, tuple(r.cluster), r.tmem_columns, r.regs_cap) == (384, (2, 1, 1), 512, 168)
         assert r.observed[0] <= 168 and r.observed[2] == 0          # register audit: fits the solved launch allocation, no spills
@@ -180,7 +180,7 @@ def test_five_compositions_link_from_one_set_of_packages(linked):
         receipt = json.loads((out / comp / "link.json").read_text())
         # the one-launch forward with dispatch holds the operands ring, the row-store staging and the dispatch
         # ring at once: the solve gives the ring one stage less
-        assert receipt["bindings"]["pipelink_moe_depth"] == [5 if comp == "fwd_dispatch" else 6, "solved"]
+        assert receipt["bindings"]["pipelink_moe_depth"] == [5 if comp in ("fwd_dispatch", "fwd_full_dispatch") else 6, "solved"]
         text = (out / comp / "generated" / "dispatch.cu").read_text()
         assert "__cluster_dims__(2, 1, 1)" in text and "tcgen05.alloc.cta_group::2" in text
         assert "setmaxnreg.dec.sync.aligned.u32 56" in text and "setmaxnreg.inc.sync.aligned.u32 224" in text
@@ -195,3 +195,7 @@ def test_five_compositions_link_from_one_set_of_packages(linked):
     b = results["fwd_dispatch"].bindings
     slots = sorted((b[h][0], h) for h in ("pipelink_moe_hidden_ready", "pipelink_moe_rows_ready", "pipelink_moe_ticket"))
     assert [s for s, _ in slots] == [0, 4096, 8192]                 # disjoint intervals of the counter workspace
+    # the whole forward in one launch: the tail's done-count slot and its named barrier are link-time facts too
+    full = results["fwd_full_dispatch"].bindings
+    assert full["pipelink_moe_tail_barrier"][0] >= 1 and full["pipelink_moe_ctas_done"][0] == 0
+    assert sorted(full[h][0] for h in ("pipelink_moe_hidden_ready", "pipelink_moe_rows_ready", "pipelink_moe_ticket")) == [1, 4097, 8193]
