@@ -202,38 +202,59 @@ __device__ __forceinline__ void fwd_tail(const MoeFwdTailParams& t, unsigned* co
   const uint4* combine = reinterpret_cast<const uint4*>(t.combine);
   uint4* out = reinterpret_cast<uint4*>(t.output);
   const long long vec_per_row = t.hidden >> 3, total = t.tokens * vec_per_row;
+  // two output vectors per thread and pass: sixteen row loads in flight (a CTA runs 256 threads here, not
+  // the thousands a launch of its own would, so each thread keeps more of HBM's latency covered)
   const long long stride = static_cast<long long>(gridDim.x) * (EpilogueWarps * 32);
-  for (long long v = static_cast<long long>(blockIdx.x) * (EpilogueWarps * 32) + tid; v < total; v += stride) {
-    const long long tok = v / vec_per_row, j = v - tok * vec_per_row;
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int s0 = 0; s0 < t.topk; s0 += 8) {          // eight rows in flight
-      uint4 c[8];
-      float ws[8];
+  const long long first = static_cast<long long>(blockIdx.x) * (EpilogueWarps * 32) + tid;
+  for (long long v0 = first; v0 < total; v0 += 2 * stride) {
+    const long long vs[2] = {v0, v0 + stride};
+    float acc[2][8];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+    for (int s0 = 0; s0 < t.topk; s0 += 8) {
+      uint4 c[2][8];
+      float ws[2][8];
       const int n = t.topk - s0 < 8 ? t.topk - s0 : 8;
 #pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        if (s < n) {
-          const long long slot = tok * t.topk + s0 + s;
-          ws[s] = t.router_w[slot];
-          c[s] = combine[(t.index != nullptr ? static_cast<long long>(t.index[slot]) : slot) * vec_per_row + j];
+      for (int u = 0; u < 2; ++u) {
+        if (vs[u] >= total) continue;
+        const long long tok = vs[u] / vec_per_row, j = vs[u] - tok * vec_per_row;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          if (s < n) {
+            const long long slot = tok * t.topk + s0 + s;
+            ws[u][s] = t.router_w[slot];
+            c[u][s] = combine[(t.index != nullptr ? static_cast<long long>(t.index[slot]) : slot) * vec_per_row + j];
+          }
         }
       }
 #pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        if (s < n) {
-          const float f[8] = {plb::bf16_lo(c[s].x), plb::bf16_hi(c[s].x), plb::bf16_lo(c[s].y), plb::bf16_hi(c[s].y),
-                              plb::bf16_lo(c[s].z), plb::bf16_hi(c[s].z), plb::bf16_lo(c[s].w), plb::bf16_hi(c[s].w)};
+      for (int u = 0; u < 2; ++u) {
+        if (vs[u] >= total) continue;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(ws[s], f[i]));
+        for (int s = 0; s < 8; ++s) {
+          if (s < n) {
+            const uint4 cc = c[u][s];
+            const float f[8] = {plb::bf16_lo(cc.x), plb::bf16_hi(cc.x), plb::bf16_lo(cc.y), plb::bf16_hi(cc.y),
+                                plb::bf16_lo(cc.z), plb::bf16_hi(cc.z), plb::bf16_lo(cc.w), plb::bf16_hi(cc.w)};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[u][i] = __fadd_rn(acc[u][i], __fmul_rn(ws[u][s], f[i]));
+          }
         }
       }
     }
-    uint4 o;
-    o.x = plb::pack_bf16(__float_as_uint(acc[0]), __float_as_uint(acc[1]));
-    o.y = plb::pack_bf16(__float_as_uint(acc[2]), __float_as_uint(acc[3]));
-    o.z = plb::pack_bf16(__float_as_uint(acc[4]), __float_as_uint(acc[5]));
-    o.w = plb::pack_bf16(__float_as_uint(acc[6]), __float_as_uint(acc[7]));
-    out[v] = o;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (vs[u] >= total) continue;
+      uint4 o;
+      o.x = plb::pack_bf16(__float_as_uint(acc[u][0]), __float_as_uint(acc[u][1]));
+      o.y = plb::pack_bf16(__float_as_uint(acc[u][2]), __float_as_uint(acc[u][3]));
+      o.z = plb::pack_bf16(__float_as_uint(acc[u][4]), __float_as_uint(acc[u][5]));
+      o.w = plb::pack_bf16(__float_as_uint(acc[u][6]), __float_as_uint(acc[u][7]));
+      out[vs[u]] = o;
+    }
   }
 }
 }  // namespace moe
