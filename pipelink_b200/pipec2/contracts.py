@@ -321,9 +321,16 @@ def expand_protocols(channels, manifests, cluster_size: int = 1) -> list[dict]:
             rec["init"] = init
         elif proto["kind"] == "call":
             rec["callable"] = [proto["export"], proto.get("decl", "")]
+            # what the generated trampoline needs: the caller's symbol, the provider's, and the C signature
+            provider = (exports.get(cs, {}).get((ce.get("protocol") or {}).get("export")) or {}).get("symbol")
+            if "symbol" in proto and provider is not None and proto.get("signature"):
+                rec["trampoline"] = {"caller": proto["symbol"], "provider": provider, "signature": proto["signature"]}
             # the provided side restates its stage's export record: declaration text and its digest
             cproto = ce.get("protocol") or {}
             record = exports.get(cs, {}).get(cproto.get("export"))
+            if record is None:
+                failures.append(ClauseFailure("L-SYM", f"channels.{name}.protocol.export",
+                                              f"stage {cs!r} provides the channel but exports no {cproto.get('export')!r}"))
             if record is not None and "decl" in record and (
                     (cproto.get("decl"), cproto.get("decl_sha256")) != (record.get("decl"), record.get("decl_sha256"))):
                 failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol",

@@ -26,6 +26,7 @@
 #define PL_NO_PARAMS() static_assert(true, "")
 #define PL_ROLE(name, fn, warps) static_assert(true, "")
 #define PL_EXPORT(name, fn) static_assert(true, "")
+#define PL_CALL(channel, fn, direction, ...) static_assert(true, "")
 #define PL_ENDPOINT(name, ...) static_assert(true, "")
 #define PL_CLAIM(domain, handle, extent, align) static_assert(true, "")
 #define PL_CLAIM_EX(domain, handle, extent, align, key, value) static_assert(true, "")
@@ -465,6 +466,55 @@ inline int emit_main() {
   return 0;
 }
 
+// C spellings of the types a call channel may carry (scalars, pointers to them, const): the link
+// generates the trampoline from them, so the set is closed
+template <class T> struct type_name;
+#define PL_TYPE_NAME(T) template <> struct type_name<T> { static std::string get() { return #T; } }
+PL_TYPE_NAME(void); PL_TYPE_NAME(bool); PL_TYPE_NAME(char); PL_TYPE_NAME(signed char); PL_TYPE_NAME(unsigned char);
+PL_TYPE_NAME(short); PL_TYPE_NAME(unsigned short); PL_TYPE_NAME(int); PL_TYPE_NAME(unsigned); PL_TYPE_NAME(long);
+PL_TYPE_NAME(unsigned long); PL_TYPE_NAME(long long); PL_TYPE_NAME(unsigned long long); PL_TYPE_NAME(float); PL_TYPE_NAME(double);
+#undef PL_TYPE_NAME
+template <class T> struct type_name<const T> { static std::string get() { return "const " + type_name<T>::get(); } };
+template <class T> struct type_name<T*> { static std::string get() { return type_name<T>::get() + "*"; } };
+
+template <class F> struct signature;
+template <class R, class... A>
+struct signature<R(A...)> {
+  static std::string get() {
+    std::string args;
+    const std::string names[] = {type_name<A>::get()..., ""};
+    for (size_t i = 0; i < sizeof...(A); ++i) args += (i ? ", " : "") + names[i];
+    return type_name<R>::get() + "(" + args + ")";
+  }
+};
+
+// one side of a call channel: the caller's trampoline (produce, from a role) or the provided function (consume)
+struct reg_call {
+  reg_call(const char* channel, const char* fn, const std::string& sig, const char* direction, const char* who,
+           const char* export_name = nullptr) {
+    const bool caller = std::string(direction) == produce;
+    json proto = json::object();
+    proto["kind"] = json("call");
+    proto["export"] = json(caller ? (export_name ? export_name : channel) : who);
+    proto["signature"] = json(sig);
+    proto["symbol"] = json(fn);
+    json e = json::object();
+    e["name"] = json(channel);
+    e["direction"] = json(direction);
+    e["owner_role"] = caller ? json(who) : json();
+    e["space"] = json("reg");
+    e["scope"] = json("cta");
+    e["proxy"] = json("generic");
+    json tile = json::object();
+    tile["dtype"] = json("s32");
+    tile["shape"] = json::list({1});
+    e["tile"] = tile;
+    e["protocol"] = proto;
+    e["binds"] = json::object();
+    registry::get().endpoints.push(e);
+  }
+};
+
 // the entry signature every role has (docs/reference/annotations.md "Parameters and types")
 template <class F>
 constexpr bool is_role_entry = std::is_same<F, void(const void*, unsigned)>::value;
@@ -508,6 +558,10 @@ constexpr bool is_role_entry = std::is_same<F, void(const void*, unsigned)>::val
   static_assert(::pl::is_role_entry<decltype(fn)>, "PL_ROLE: void(const void* params, unsigned variant)"); \
   PL_REG(reg_role)(#name, #fn, warps)
 #define PL_EXPORT(name, fn) PL_REG(reg_export)(#name, #fn)
+// PL_CALL(channel, trampoline, pl::produce, "caller_role"[, "export_name"]) at the call site;
+// PL_CALL(channel, implementation, pl::consume, "export_name") beside the provided function
+#define PL_CALL(channel, fn, direction, ...) \
+  PL_REG(reg_call)(#channel, #fn, ::pl::signature<decltype(fn)>::get(), direction, __VA_ARGS__)
 #define PL_ENDPOINT(name, ...) PL_REG(reg_endpoint){#name, __VA_ARGS__}
 #define PL_CLAIM(domain, handle, extent, align) PL_REG(reg_claim)(#domain, #handle, extent, align)
 #define PL_CLAIM_EX(domain, handle, extent, align, key, value) \

@@ -170,7 +170,7 @@ def front_end(manifests, pipe):
                                         regs_priority=pipe.get("regs_priority", []),
                                         reg_claims=_reg_claims(manifests, handles), role_warps=role_warps,
                                         pipeline_domains=pipe.get("domains", {}))
-    _check_symbols(manifests, bindings)
+    _check_symbols(manifests, {**bindings, **{e["trampoline"]["caller"]: None for e in expansions if "trampoline" in e}})
     return {"profile": profile, "handles": handles, "cta_group": cta_group, "cluster": cluster, "expansions": expansions,
             "claims": claims, "uses_tmem": uses_tmem, "params": params, "role_warps": role_warps, "bindings": bindings,
             "intervals": intervals, "solver": solver}
@@ -216,16 +216,28 @@ def link(pipeline_path, out_dir, *, device_link=True):
 
     # roles: warp interval from the role's warp claim, params offset from the layout
     offsets = {e[0]: e[1] for e in params["entries"]}
-    roles, covered = [], 0
+    # a role without a warp claim takes the next warps behind the claimed ones, in declaration order
+    # (the smallest images, one role and nothing to solve, carry no claim at all)
+    roles, covered, unplaced = [], 0, []
     for m in manifests:
         for rname, r in m["stage"]["roles"].items():
-            if rname not in fe["role_warps"]:
-                raise PipeLinkError(ClauseFailure("L-TOPO", f"{m['stage']['id']}.roles.{rname}", "a role needs exactly one warp claim"))
-            handle, warps, inside = fe["role_warps"][rname]
-            lo = bindings[handle][0] + inside
-            roles.append({"stage": m["stage"]["id"], "role": rname, "entry": r["entry"], "warp_lo": lo,
-                          "warp_hi": lo + r["warps"], "params_offset": offsets[m["stage"]["id"]], "variant": 0})
+            rec = {"stage": m["stage"]["id"], "role": rname, "entry": r["entry"], "warps": r["warps"],
+                   "params_offset": offsets[m["stage"]["id"]], "variant": 0}
+            if rname in fe["role_warps"]:
+                handle, warps, inside = fe["role_warps"][rname]
+                rec["warp_lo"] = bindings[handle][0] + inside
+                roles.append(rec)
+            else:
+                unplaced.append(rec)
             covered += r["warps"]
+    next_warp = max((r["warp_lo"] + r["warps"] for r in roles), default=0)
+    for rec in unplaced:
+        rec["warp_lo"], next_warp = next_warp, next_warp + rec["warps"]
+        roles.append(rec)
+    for rec in roles:
+        rec["warp_hi"] = rec["warp_lo"] + rec.pop("warps")
+    if not roles:
+        raise PipeLinkError(ClauseFailure("L-TOPO", "pipeline.stages", "an image needs at least one role"))
     roles.sort(key=lambda r: r["warp_lo"])
     threads = 32 * covered
     tmem_cols = 0
@@ -236,7 +248,7 @@ def link(pipeline_path, out_dir, *, device_link=True):
             tmem_cols *= 2
     smem_hw = solver["high_water"].get("smem", 0)
     generated = {
-        "binding_stub.cu": codegen.binding_stub(bindings),
+        "binding_stub.cu": codegen.binding_stub(bindings, [e["trampoline"] for e in expansions if "trampoline" in e]),
         "dispatch.cu": codegen.dispatch(threads=threads, params_total=params["total_bytes"], roles=roles,
                                         expansions=expansions, bindings=bindings, tmem_columns=tmem_cols,
                                         tmem_slot=bindings.get(TMEM_SLOT_HANDLE, [0])[0], tmem_warp=roles[0]["warp_lo"],

@@ -79,7 +79,7 @@ def test_moe_units_state_the_sizes_their_structs_have():
     sizes = {name: (m["params"]["bytes"], m["params"]["align"]) for name, m in ms.items()}
     assert sizes == {"load": (576, 64), "mma": (48, 16), "comm_none": (0, 1), "comm_dispatch": (112, 16),
                      "epilogue_swiglu": (80, 16), "epilogue_rows": (96, 16), "fwd_load": (1152, 64),
-                     "fwd_mma": (96, 16), "fwd_epilogue": (176, 16)}
+                     "fwd_mma": (96, 16), "fwd_epilogue": (176, 16), "fwd_epilogue_combine": (256, 16)}
     # the members an owner reads cover its block up to tail padding
     for m in ms.values():
         if m["params"]["bytes"]:
