@@ -27,6 +27,7 @@
 #define PL_ROLE(name, fn, warps) static_assert(true, "")
 #define PL_EXPORT(name, fn) static_assert(true, "")
 #define PL_CALL(channel, fn, direction, ...) static_assert(true, "")
+#define PL_TYPE(T) static_assert(true, "")
 #define PL_ENDPOINT(name, ...) static_assert(true, "")
 #define PL_CLAIM(domain, handle, extent, align) static_assert(true, "")
 #define PL_CLAIM_EX(domain, handle, extent, align, key, value) static_assert(true, "")
@@ -47,6 +48,7 @@
 #define __forceinline__ inline
 #endif
 
+#include "tensor_source.h"
 #include <cstddef>
 #include <cstdio>
 #include <initializer_list>
@@ -473,6 +475,7 @@ template <class T> struct type_name;
 PL_TYPE_NAME(void); PL_TYPE_NAME(bool); PL_TYPE_NAME(char); PL_TYPE_NAME(signed char); PL_TYPE_NAME(unsigned char);
 PL_TYPE_NAME(short); PL_TYPE_NAME(unsigned short); PL_TYPE_NAME(int); PL_TYPE_NAME(unsigned); PL_TYPE_NAME(long);
 PL_TYPE_NAME(unsigned long); PL_TYPE_NAME(long long); PL_TYPE_NAME(unsigned long long); PL_TYPE_NAME(float); PL_TYPE_NAME(double);
+PL_TYPE_NAME(pipelink_tensor_source);
 #undef PL_TYPE_NAME
 template <class T> struct type_name<const T> { static std::string get() { return "const " + type_name<T>::get(); } };
 template <class T> struct type_name<T*> { static std::string get() { return type_name<T>::get() + "*"; } };
@@ -558,6 +561,10 @@ constexpr bool is_role_entry = std::is_same<F, void(const void*, unsigned)>::val
   static_assert(::pl::is_role_entry<decltype(fn)>, "PL_ROLE: void(const void* params, unsigned variant)"); \
   PL_REG(reg_role)(#name, #fn, warps)
 #define PL_EXPORT(name, fn) PL_REG(reg_export)(#name, #fn)
+// PL_TYPE(T): a struct that call channels pass by pointer; the generated trampoline forward-declares it
+#define PL_TYPE(T) \
+  namespace pl { template <> struct type_name<T> { static std::string get() { return "struct " #T; } }; } \
+  static_assert(true, "")
 // PL_CALL(channel, trampoline, pl::produce, "caller_role"[, "export_name"]) at the call site;
 // PL_CALL(channel, implementation, pl::consume, "export_name") beside the provided function
 #define PL_CALL(channel, fn, direction, ...) \

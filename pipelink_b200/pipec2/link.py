@@ -11,10 +11,12 @@ import json
 import tempfile
 from pathlib import Path
 
-from . import canonjson, codegen, container, contracts, jitlink, schema
+from . import canonjson, codegen, container, contracts, jitlink, schema, tensor_plan
 from .model import ClauseFailure, LinkResult, PipeLinkError
 from .profile import PROFILES
 from .solve import solve
+
+INCLUDE = Path(__file__).resolve().parent / "include"      # <pipelink/...> headers of generated units
 
 TMEM_SLOT_HANDLE = "pipelink_tmem_slot"
 
@@ -156,6 +158,15 @@ def front_end(manifests, pipe):
         if isinstance(d, dict) and "handle" in d and handles.get(d["handle"], {}).get("class") != "depth":
             raise PipeLinkError(ClauseFailure("L-HANDLE", f"channels.{e['channel']}.ring.depth", "ring depth handle is not declared"))
 
+    # tensor connections: plan each (route, certificate, reservations) and merge what the certified
+    # programs reserve into their consumers' claims, so the solve places scratch and barriers too
+    tensor_records = tensor_plan.plan_pipeline(manifests, pipe)
+    if tensor_records:
+        manifests = [json.loads(json.dumps(m)) for m in manifests]
+        for rec in tensor_records:
+            consumer = next(m for m in manifests if m["stage"]["id"] == rec["consumer"])
+            have = {c["handle"] for c in consumer.get("claims", [])}
+            consumer.setdefault("claims", []).extend(dict(c, lifetime="kernel", roles=[]) for c in rec["claims"] if c["handle"] not in have)
     claims = _unify_claims(manifests, handles)
     uses_tmem = any(c["rec"]["domain"] == "tmem" for c in claims.values())
     if uses_tmem:  # the dispatch kernel owns the slot it publishes the allocation base through
@@ -170,8 +181,14 @@ def front_end(manifests, pipe):
                                         regs_priority=pipe.get("regs_priority", []),
                                         reg_claims=_reg_claims(manifests, handles), role_warps=role_warps,
                                         pipeline_domains=pipe.get("domains", {}))
-    _check_symbols(manifests, {**bindings, **{e["trampoline"]["caller"]: None for e in expansions if "trampoline" in e}})
-    return {"profile": profile, "handles": handles, "cta_group": cta_group, "cluster": cluster, "expansions": expansions,
+    for rec in tensor_records:       # a lend no certified program touches claims nothing: its handle resolves to 0
+        for h in rec["unused_handles"]:
+            bindings.setdefault(h, [0, "unused"])
+    generated_symbols = {e["trampoline"]["caller"]: None for e in expansions if "trampoline" in e}
+    for rec in tensor_records:
+        generated_symbols.update({rec["callable"] + suffix: None for suffix in ("", "_ready", "_done")})
+    _check_symbols(manifests, {**bindings, **generated_symbols})
+    return {"tensor": tensor_records, "profile": profile, "handles": handles, "cta_group": cta_group, "cluster": cluster, "expansions": expansions,
             "claims": claims, "uses_tmem": uses_tmem, "params": params, "role_warps": role_warps, "bindings": bindings,
             "intervals": intervals, "solver": solver}
 
@@ -257,6 +274,9 @@ def link(pipeline_path, out_dir, *, device_link=True):
                                         extra_barriers={h: c["rec"]["init_count"] for h, c in claims.items()
                                                         if c["rec"]["domain"] == "mbarrier" and "init_count" in c["rec"]}),
     }
+    if fe["tensor"]:
+        by_role = {r["role"]: (r["warp_lo"], r["warp_hi"] - r["warp_lo"]) for r in roles}
+        generated["tensor_adapters.cu"] = tensor_plan.adapters_unit(fe["tensor"], by_role)
     out_dir.mkdir(parents=True, exist_ok=True)
     gen_dir = out_dir / "generated"
     gen_dir.mkdir(exist_ok=True)
@@ -268,7 +288,7 @@ def link(pipeline_path, out_dir, *, device_link=True):
         with tempfile.TemporaryDirectory() as tmp:
             for name in generated:
                 obj = Path(tmp) / (name + ".o")
-                jitlink.compile_lto(str(gen_dir / name), str(obj), profile)
+                jitlink.compile_lto(str(gen_dir / name), str(obj), profile, [INCLUDE])
                 objects.append((name, obj.read_bytes()))
         cubin, info = jitlink.link(objects, profile["sm"], extra=["-Xptxas=-v"])
         (out_dir / "pipeline.cubin").write_bytes(cubin)
@@ -280,6 +300,6 @@ def link(pipeline_path, out_dir, *, device_link=True):
         dyn_smem_bytes=smem_hw, cluster=tuple(cluster), params=params, bindings=bindings, variants={},
         intervals=intervals, protocol_expansions=expansions, observed=observed, input_hashes=input_hashes,
         generated_hashes={k: hashlib.sha256(v.encode()).hexdigest() for k, v in generated.items()},
-        solver=solver, roles=roles, tmem_columns=tmem_cols)
+        solver=solver, roles=roles, tmem_columns=tmem_cols, tensor=fe["tensor"] or None)
     (out_dir / "link.json").write_text(canonjson.dumps(result.to_json_obj()))
     return result

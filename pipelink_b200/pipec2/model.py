@@ -22,6 +22,11 @@ CLAUSES = {
     "L-TOPO": "stage topology constraints have a legal intersection",
     "L8": "paired endpoints describe the identical physical layout",
     "T-CONTRACT": "a stage's tensor import / export section is well formed",
+    "T-MODEL": "a tensor connection stays inside the modelled vocabulary",
+    "T-PLAN": "a route for the tensor connection is certified within the import's lends",
+    "T-PLAN-RENDEZVOUS": "a tensor import declares its outer ready and done events",
+    "T-PLAN-FRAME": "a register export is given one frame lend with enough positions",
+    "T-LOWER": "the certified program lowers to an adapter for the site it runs at",
     "P-ANNOTATION": "a unit's annotations state exactly one stage, one parameter block and at most one topology",
     "P-COMPILE": "the stage payload compiles for the target profile",
     "P-CONTAINER": "the package container is well formed",
@@ -74,6 +79,7 @@ class LinkResult:
     solver: dict | None = None
     roles: list | None = None         # [{stage, role, entry, warp_lo, warp_hi, params_offset}]
     tmem_columns: int = 0
+    tensor: list | None = None        # one record per tensor connection: routes tried, certified program, reservations
 
     def to_json_obj(self):
         return asdict(self)

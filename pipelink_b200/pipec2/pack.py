@@ -67,7 +67,7 @@ def undefined_symbols(source, profile: dict, includes=(), defines=()) -> dict:
     return {name: "function" for name in sorted(set(re.findall(r"^\.extern \.func[^;]*?\b(\w+)\s*(?:\(|;)", text, re.M)))}
 
 
-def pack_cu(source, manifest_path=None, out=None, profile="sm_100a", includes=(), defines=()):
+def pack_cu(source, manifest_path=None, out=None, profile="sm_100a", includes=(), defines=(), sections=None):
     source = Path(source)
     prof = PROFILES[profile]
     includes = [str(INCLUDE), *includes]
@@ -82,6 +82,9 @@ def pack_cu(source, manifest_path=None, out=None, profile="sm_100a", includes=()
             inputs = {"tu": hashlib.sha256(source.read_bytes()).hexdigest(),
                       "annotations": hashlib.sha256((INCLUDE / "pipelink" / "stage.hpp").read_bytes()).hexdigest()}
             mechanism = "annotations"
+            # sections a frontend derives in Python rather than from annotations (the tensor contracts)
+            for key, value in (sections or {}).items():
+                manifest[key] = json.loads(json.dumps(value))
         else:
             manifest_path = Path(manifest_path)
             manifest = json.loads(manifest_path.read_text())

@@ -9,8 +9,8 @@ coordinates, placements as expressions over coordinates and bindings, readiness)
 site gives) and ``bindings`` (link-time quantities a placement may depend on: a base column, a
 slot). This module is the loading half of the reference's tensor-import planner
 (pipec/src/pipec2/tensor/contracts.py, expr.py): it validates a section, evaluates its
-expressions and checks an import against the export it names; fitting placements and generating
-adapters between them is not part of this build.
+expressions and checks an import against the export it names. Routing a connection, certifying the
+program and generating the adapter is ``tensor_plan``.
 
 Expressions are JSON lists ``[op, args...]`` over three sorts, ``int``, ``pred`` and
 ``bits[n]``: ``const coord bind add sub mulc divc modc eq lt le not pand por select cbits band bor
