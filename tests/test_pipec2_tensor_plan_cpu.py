@@ -66,6 +66,25 @@ def test_staging_picks_the_conflict_free_shear():
     assert tp._bank_score(words) == 4 * 32
 
 
+@pytest.mark.parametrize("cell", ["tmem_transposed", "tmem_by_column"])
+def test_staging_rounds_are_conflict_free_and_cover_the_scratch_exactly(cell):
+    """The property the reference holds its staged routes to (pipec/tests/pipec2/test_tensor_construct.py:
+    test_matrix_staging_is_conflict_free_without_changing_extent): per warp and per round every bank
+    is hit once, and stores and loads visit exactly the words of the 64 KB scratch."""
+    (rec,) = _plan(cell)
+    store, load = rec["program"][1], rec["program"][3]
+    visited = {}
+    for step, var in ((store, "i"), (load, "p")):
+        seen = set()
+        for k in range(step["count"]):
+            for warp in range(4):
+                words = {tensor.evaluate(step["word"], {"t": 32 * warp + lane, var: k}) for lane in range(32)}
+                assert len(words) == 32 and len({w % 32 for w in words}) == 32
+                seen |= words
+        visited[step["op"]] = seen
+    assert visited["smem_store"] == visited["smem_load"] == set(range(65536 // 4))
+
+
 def test_the_checker_replays_the_program_and_catches_a_wrong_one():
     ms = _members("tmem_transposed")
     pipe = _pipe("tmem_transposed")
