@@ -326,6 +326,13 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   return r;
 }
 // Address of the same shared-memory offset in CTA `rank` of this cluster.
+// One lane of a converged warp. Code under it is single-lane, but operands computed before it, in convergent
+// code, stay warp-uniform: that is what the tensor, copy and commit instructions want their operands to be.
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
   uint32_t out;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));

@@ -227,7 +227,9 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t smem_base = raw_addr + pad;
   Barriers2* bars = reinterpret_cast<Barriers2*>(smem + kOffBars);
 
-  const int warp = threadIdx.x >> 5;
+  // warp-uniform by construction, and said so to the compiler: the operands of the tensor and copy
+  // instructions below are then computed once per warp, in convergent code
+  const int warp = __shfl_sync(0xFFFFFFFFu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const uint32_t cta_rank = cluster_ctarank();
   const bool leader = cta_rank == 0;
@@ -286,7 +288,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
   cluster_arrive();
   cluster_wait();
   tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base), 0);
   if (bad_schedule) {   // both CTAs of every pair see the same schedule and agree
     if (threadIdx.x == 0) report_failure(p.status, ST_BAD_ARGUMENT, 320, static_cast<unsigned>(rows_in_use), 256u);
     total_tiles = 0;
@@ -295,67 +297,82 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (warp < 4) {
     setmaxnreg_dec<kRegsHelpers>();
-    if (warp == 0 && lane == 0) {
+    if (warp == 0) {
       // ---------------------------------------------------------- TMA producer (both CTAs)
-      int stage = 0;
-      uint32_t phase = 0;
+      // Like the MMA issuer below, the whole warp walks the loop with warp-uniform coordinates and barrier
+      // addresses, and one elected lane issues the copies.
+      uint32_t stage = 0, phase = 0;
       bool ok = true;
+      const uint32_t empty0 = smem_u32(&bars->empty[0]);
+      const uint32_t full0_leader = mapa_shared(smem_u32(&bars->full[0]), 0);
+      const int tiles_u = __shfl_sync(0xFFFFFFFFu, total_tiles, 0);
       PROF_DECL(t_empty);
       PROF_T0(t_begin);
-      for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
+      for (int tile = pair_id; tile < tiles_u && ok; tile += num_pairs) {
         const Tile t = decode_tile<MODE>(p, tile, static_cast<int>(cta_rank), m_tiles_live, m_rot, m_stride);
-        const int a_blk = t.a_blk, b_blk0 = t.b_blk0;
+        const int a_blk = __shfl_sync(0xFFFFFFFFu, t.a_blk, 0), b_blk0 = __shfl_sync(0xFFFFFFFFu, t.b_blk0, 0);
+        const int k_steps = __shfl_sync(0xFFFFFFFFu, t.k_steps, 0), k_blk0 = __shfl_sync(0xFFFFFFFFu, t.k_blk0, 0);
+        const int k_pitch = __shfl_sync(0xFFFFFFFFu, t.k_pitch, 0);
         const int b_blk = b_blk0 + static_cast<int>(cta_rank);
         if (MODE == 0 && p.pull_xq != nullptr) {
-          const unsigned* flag = p.pull_ready + (a_blk >> 1);
-          const long long t0 = clock64();
-          while (ld_acquire_gpu_u32(flag) < 256u) {
-            if (clock64() - t0 > kWaitBudgetCycles / 2 || ld_volatile_i32(&p.status->code) != 0) {
-              report_failure(p.status, ST_TIMEOUT_COUNTER, 311, ld_acquire_gpu_u32(flag), 256u);
-              ok = false;
-              break;
+          if (lane == 0) {
+            const unsigned* flag = p.pull_ready + (a_blk >> 1);
+            const long long t0 = clock64();
+            while (ld_acquire_gpu_u32(flag) < 256u) {
+              if (clock64() - t0 > kWaitBudgetCycles / 2 || ld_volatile_i32(&p.status->code) != 0) {
+                report_failure(p.status, ST_TIMEOUT_COUNTER, 311, ld_acquire_gpu_u32(flag), 256u);
+                ok = false;
+                break;
+              }
             }
+            asm volatile("fence.proxy.async.global;" ::: "memory");
           }
+          ok = __all_sync(0xFFFFFFFFu, ok);
           if (!ok) break;
-          asm volatile("fence.proxy.async.global;" ::: "memory");
         }
         if (MODE == 1 && p.ready != nullptr) {
           // rows pushed by a peer are usable once its counter increment (a release at system scope,
           // examples/comm-overlap README "AllGather protocol") is observed; then order the TMA reads after it
-          const unsigned* flag = p.ready + (a_blk >> 1);
-          const long long t0 = clock64();
-          while (static_cast<int>(ld_acquire_sys_u32(flag) - p.ready_target) < 0) {
-            // half the budget of the barrier waits downstream, so the record names the cause
-            if (clock64() - t0 > kWaitBudgetCycles / 2 || ld_volatile_i32(&p.status->code) != 0) {
-              report_failure(p.status, ST_TIMEOUT_COUNTER, 310, ld_acquire_sys_u32(flag), p.ready_target);
-              ok = false;
-              break;
+          if (lane == 0) {
+            const unsigned* flag = p.ready + (a_blk >> 1);
+            const long long t0 = clock64();
+            while (static_cast<int>(ld_acquire_sys_u32(flag) - p.ready_target) < 0) {
+              // half the budget of the barrier waits downstream, so the record names the cause
+              if (clock64() - t0 > kWaitBudgetCycles / 2 || ld_volatile_i32(&p.status->code) != 0) {
+                report_failure(p.status, ST_TIMEOUT_COUNTER, 310, ld_acquire_sys_u32(flag), p.ready_target);
+                ok = false;
+                break;
+              }
             }
+            asm volatile("fence.proxy.async.global;" ::: "memory");
           }
+          ok = __all_sync(0xFFFFFFFFu, ok);
           if (!ok) break;
-          asm volatile("fence.proxy.async.global;" ::: "memory");
         }
-        for (int kb = 0; kb < t.k_steps; ++kb) {
+        for (int kb = 0; kb < k_steps; ++kb) {
           PROF_T0(t0);
-          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY,
-                         stage)) {
-            ok = false;
-            break;
-          }
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait(empty0 + 8u * stage, phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, static_cast<int>(stage)));
+          if (!ok) break;
           PROF_ADD(t_empty, t0);
-          const uint32_t full = mapa_shared(smem_u32(&bars->full[stage]), 0);
-          mbar_arrive_expect_tx_cluster(full, BF16 ? 2u * kTileBytes : kStageTx);
+          const uint32_t full = full0_leader + 8u * stage;
           const uint32_t sf = smem_base + kOffSf + stage * kSfStageBytes;
-          const int kk = t.k_blk0 + kb;
+          const uint32_t dst_a = smem_base + kOffA + stage * kTileBytes, dst_b = smem_base + kOffB + stage * kTileBytes;
+          const int kk = k_blk0 + kb;
           // the x coordinate counts elements: 128 E4M3 or 64 bf16 per 128-byte K step
           const int kx = kk * (BF16 ? 64 : 128);
-          tma_load_2d_pair(smem_base + kOffA + stage * kTileBytes, &map_a, full, kx, a_blk * 128);
-          tma_load_2d_pair(smem_base + kOffB + stage * kTileBytes, &map_b, full, kx, b_blk * 128);
-          if (!BF16) {
-            tma_load_2d_pair(sf, &map_sfa, full, 0, a_blk * t.k_pitch + kk);
-            tma_load_2d_pair(sf + kSfBytes, &map_sfb, full, 0, b_blk0 * t.k_pitch + kk);
-            tma_load_2d_pair(sf + 2 * kSfBytes, &map_sfb, full, 0, (b_blk0 + 1) * t.k_pitch + kk);
+          const int row_a = a_blk * 128, row_b = b_blk * 128;
+          const int sf_a = a_blk * k_pitch + kk, sf_b0 = b_blk0 * k_pitch + kk, sf_b1 = (b_blk0 + 1) * k_pitch + kk;
+          if (elect_one_sync()) {
+            mbar_arrive_expect_tx_cluster(full, BF16 ? 2u * kTileBytes : kStageTx);
+            tma_load_2d_pair(dst_a, &map_a, full, kx, row_a);
+            tma_load_2d_pair(dst_b, &map_b, full, kx, row_b);
+            if (!BF16) {
+              tma_load_2d_pair(sf, &map_sfa, full, 0, sf_a);
+              tma_load_2d_pair(sf + kSfBytes, &map_sfb, full, 0, sf_b0);
+              tma_load_2d_pair(sf + 2 * kSfBytes, &map_sfb, full, 0, sf_b1);
+            }
           }
+          __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -367,75 +384,89 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         while (clock64() - t0 < 200000LL) {
         }
       }
-    } else if (warp == 1 && lane == 0 && leader) {
+    } else if (warp == 1 && leader) {
       // ---------------------------------------------------------- MMA issuer (leader CTA)
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
+      // The whole warp walks the loop and every operand of the tensor instructions (descriptors, tensor-memory
+      // addresses, barrier addresses) is computed in convergent code; one elected lane issues them. Computed by a
+      // single lane in a divergent branch the same operands sit in per-thread registers and each instruction pays
+      // for moving them (60 - 77 cycles per tcgen05 instruction measured, nine per K step: the issuing thread, not
+      // the tensor pipe, then bounds the kernel).
+      const uint32_t full0 = smem_u32(&bars->full[0]);
+      const uint32_t empty0 = smem_u32(&bars->empty[0]);
+      const uint32_t empty0_peer = mapa_shared(empty0, 1);
       const uint32_t acc_full_own = smem_u32(&bars->acc_full);
       const uint32_t acc_full_peer = mapa_shared(acc_full_own, 1);
+      const uint32_t acc_empty = smem_u32(&bars->acc_empty);
+      const int tiles_u = __shfl_sync(0xFFFFFFFFu, total_tiles, 0);
+      uint32_t stage = 0, phase = 0, acc_phase = 0;
+      bool ok = true;
       PROF_DECL(t_acc);
       PROF_DECL(t_full);
       PROF_T0(t_begin);
-      for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
+      for (int tile = pair_id; tile < tiles_u && ok; tile += num_pairs) {
         const Tile t = decode_tile<MODE>(p, tile, 0, m_tiles_live, m_rot, m_stride);
-        if (t.k_steps == 0) continue;  // empty expert: the epilogue writes zeros on its own
+        const int k_steps = __shfl_sync(0xFFFFFFFFu, t.k_steps, 0);
+        if (k_steps == 0) continue;  // empty expert: the epilogue writes zeros on its own
         PROF_T0(ta);
-        if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY,
-                       0)) {
-          ok = false;
-          break;
-        }
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(acc_empty, acc_phase ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, 0));
+        if (!ok) break;
         PROF_ADD(t_acc, ta);
         tc_fence_after();
-        for (int kb = 0; kb < t.k_steps; ++kb) {
+        for (int kb = 0; kb < k_steps; ++kb) {
           PROF_T0(tf);
-          if (!mbar_wait(smem_u32(&bars->full[stage]), phase, p.status, ST_TIMEOUT_FULL, stage)) {
-            ok = false;
-            break;
-          }
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait(full0 + 8u * stage, phase, p.status, ST_TIMEOUT_FULL, static_cast<int>(stage)));
+          if (!ok) break;
           PROF_ADD(t_full, tf);
           tc_fence_after();
           const uint32_t sf = smem_base + kOffSf + stage * kSfStageBytes;
           const uint32_t sfa_t = tmem_base + kSfColBase + stage * kSfColsPerStage;
           const uint32_t sfb_t = sfa_t + 4;
-          if (!BF16) {
-            tc_cp_32x128b_warpx4_pair(sfa_t, smem_desc(sf, kDescScale));
-            tc_cp_32x128b_warpx4_pair(sfb_t, smem_desc(sf + kSfBytes, kDescScale));
-            tc_cp_32x128b_warpx4_pair(sfb_t + 4, smem_desc(sf + 2 * kSfBytes, kDescScale));
-          }
+          const uint64_t sfd_a = smem_desc(sf, kDescScale), sfd_b0 = smem_desc(sf + kSfBytes, kDescScale),
+                         sfd_b1 = smem_desc(sf + 2 * kSfBytes, kDescScale);
           const uint64_t adesc = smem_desc(smem_base + kOffA + stage * kTileBytes, kDescSw128KMajor);
           const uint64_t bdesc = smem_desc(smem_base + kOffB + stage * kTileBytes, kDescSw128KMajor);
+          const uint32_t first = kb != 0 ? 1u : 0u;
+          const uint32_t empty_own = empty0 + 8u * stage, empty_peer = empty0_peer + 8u * stage;
+          if (elect_one_sync()) {
+            if (!BF16) {
+              tc_cp_32x128b_warpx4_pair(sfa_t, sfd_a);
+              tc_cp_32x128b_warpx4_pair(sfb_t, sfd_b0);
+              tc_cp_32x128b_warpx4_pair(sfb_t + 4, sfd_b1);
+            }
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // 32 bytes further along K per MMA: 32 E4M3 or 16 bf16 elements
-            if (BF16)
-              tc_mma_f16_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, kIdescPairBf16, (kb | k) != 0 ? 1u : 0u);
-            else
-              tc_mma_mxf8_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(kIdescPair, k),
-                               sfa_t, sfb_t, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < 4; ++k) {
+              // 32 bytes further along K per MMA: 32 E4M3 or 16 bf16 elements
+              if (BF16)
+                tc_mma_f16_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, kIdescPairBf16, k != 0 ? 1u : first);
+              else
+                tc_mma_mxf8_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(kIdescPair, k), sfa_t, sfb_t,
+                                 k != 0 ? 1u : first);
+            }
+            tc_commit_pair(empty_own);
+            tc_commit_pair(empty_peer);
           }
-          const uint32_t empty_own = smem_u32(&bars->empty[stage]);
-          tc_commit_pair(empty_own);
-          tc_commit_pair(mapa_shared(empty_own, 1));
+          __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit_pair(acc_full_own);
-        tc_commit_pair(acc_full_peer);
+        if (elect_one_sync()) {
+          tc_commit_pair(acc_full_own);
+          tc_commit_pair(acc_full_peer);
+        }
+        __syncwarp();
         acc_phase ^= 1u;
       }
       PROF_WRITE(2, t_acc);
       PROF_WRITE(3, t_full);
       PROF_WRITE(4, clock64() - t_begin);
-      if (!ok) {
+      if (!ok && lane == 0) {
         tc_commit_pair(smem_u32(&bars->drain));
         const long long t0 = clock64();
         while (!mbar_try_wait(smem_u32(&bars->drain), 0)) {
           if (clock64() - t0 > 20000000LL) break;
         }
       }
+      __syncwarp();
     } else if (MODE == 0 && warp >= 2 && p.pull_xq != nullptr) {
       // ---------------------------------------------------------- dispatch warps (two per CTA)
       // A ticket is two consecutive rows. Their bytes cross as 16-byte asynchronous copies
