@@ -390,7 +390,7 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   uint8_t* smem = smem_raw + pad;
   const uint32_t sb = raw_addr + pad;
   PairBars* bars = reinterpret_cast<PairBars*>(smem + kPOffBar);
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xFFFFFFFFu, static_cast<int>(threadIdx.x >> 5), 0);   // warp-uniform, and said so to the compiler
   using L = LibPairLayout;
 
   if (threadIdx.x == 0) {

@@ -63,27 +63,40 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // ------------------------------------------------------------------ TMA producer (one warp)
 // Both Q tiles once per record; K and V blocks through two rings of L::kv_depth() stages. With
 // kUseCounters a key block's readiness counter is acquired before its first read (context parallel).
+// The whole warp walks the loop, so coordinates and barrier addresses are warp-uniform, and one
+// elected lane issues the copies (see mma_role).
 template <class L, bool kUseCounters>
 __device__ __forceinline__ void load_role(const CUtensorMap* map_q, const CUtensorMap* map_k, const CUtensorMap* map_v,
                                           const AttnParams& p, uint32_t sb) {
   const int lane = threadIdx.x & 31;
-  if (lane == 0) {
-    uint32_t q_phase = 0, k_it = 0, v_it = 0;
-    bool ok = true;
-    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
-      const AttnWork wk = p.work[w];
-      const int col = wk.head * kD;
-      const int kv_col = (wk.head / p.q_per_kv) * kD;
-      if (!mbar_wait(L::q_empty(sb), q_phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, 10)) { ok = false; break; }
-      mbar_arrive_expect_tx(L::q_full(sb), 2 * kTileBytes);
+  uint32_t q_phase = 0, k_it = 0, v_it = 0;
+  bool ok = true;
+  auto wait = [&](uint32_t bar, uint32_t parity, int code, int what) {
+    return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, p.status, code, what)) != 0;
+  };
+  for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+    const AttnWork wk = p.work[w];
+    const int head = __shfl_sync(0xFFFFFFFFu, wk.head, 0), q_row0 = __shfl_sync(0xFFFFFFFFu, wk.q_row0, 0);
+    const int kv_row0 = __shfl_sync(0xFFFFFFFFu, wk.kv_row0, 0), kv_blocks = __shfl_sync(0xFFFFFFFFu, wk.kv_blocks, 0);
+    const int col = head * kD;
+    const int kv_col = (head / p.q_per_kv) * kD;
+    if (!wait(L::q_empty(sb), q_phase ^ 1u, ST_TIMEOUT_EMPTY, 10)) { ok = false; break; }
+    {
+      const uint32_t q_full = L::q_full(sb), q_dst = sb + L::q();
+      if (elect_one_sync()) {
+        mbar_arrive_expect_tx(q_full, 2 * kTileBytes);
 #pragma unroll
-      for (int a = 0; a < 4; ++a)  // tile t = a / 2 (head + t), 64-column half a % 2
-        tma_load_2d(sb + L::q() + a * kAtomBytes, map_q, L::q_full(sb), col + a * 64, wk.q_row0);
-      q_phase ^= 1u;
-      for (int j = 0; j < wk.kv_blocks && ok; ++j) {
-        const int kv_row = wk.kv_row0 + j * kBlk;
-        if (kUseCounters && p.ready != nullptr) {
-          const unsigned* flag = p.ready + (wk.kv_row0 / kBlk + j);
+        for (int a = 0; a < 4; ++a)  // tile t = a / 2 (head + t), 64-column half a % 2
+          tma_load_2d(q_dst + a * kAtomBytes, map_q, q_full, col + a * 64, q_row0);
+      }
+      __syncwarp();
+    }
+    q_phase ^= 1u;
+    for (int j = 0; j < kv_blocks && ok; ++j) {
+      const int kv_row = kv_row0 + j * kBlk;
+      if (kUseCounters && p.ready != nullptr) {
+        if (lane == 0) {
+          const unsigned* flag = p.ready + (kv_row0 / kBlk + j);
           const long long t0 = clock64();
           while (static_cast<int>(ld_acquire_sys_u32(flag) - p.ready_target) < 0) {
             if (clock64() - t0 > kWaitBudgetCycles || ld_volatile_i32(&p.status->code) != 0) {
@@ -92,110 +105,135 @@ __device__ __forceinline__ void load_role(const CUtensorMap* map_q, const CUtens
               break;
             }
           }
-          if (!ok) break;
           asm volatile("fence.proxy.async.global;" ::: "memory");
         }
-        {
-          const int s = k_it % L::kv_depth();
-          if (!mbar_wait(L::k_empty(sb, s), ((k_it / L::kv_depth()) & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, 11)) { ok = false; break; }
-          const uint32_t full = L::k_full(sb, s);
+        ok = __all_sync(0xFFFFFFFFu, ok) != 0;
+        if (!ok) break;
+      }
+      {
+        const uint32_t s = k_it % L::kv_depth();
+        if (!wait(L::k_empty(sb, s), ((k_it / L::kv_depth()) & 1u) ^ 1u, ST_TIMEOUT_EMPTY, 11)) { ok = false; break; }
+        const uint32_t full = L::k_full(sb, s), dst = sb + L::k() + s * kTileBytes;
+        if (elect_one_sync()) {
           mbar_arrive_expect_tx(full, kTileBytes);
-          tma_load_2d(sb + L::k() + s * kTileBytes, map_k, full, kv_col, kv_row);
-          tma_load_2d(sb + L::k() + s * kTileBytes + kAtomBytes, map_k, full, kv_col + 64, kv_row);
-          ++k_it;
+          tma_load_2d(dst, map_k, full, kv_col, kv_row);
+          tma_load_2d(dst + kAtomBytes, map_k, full, kv_col + 64, kv_row);
         }
-        {
-          const int s = v_it % L::kv_depth();
-          if (!mbar_wait(L::v_empty(sb, s), ((v_it / L::kv_depth()) & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, 12)) { ok = false; break; }
-          const uint32_t full = L::v_full(sb, s);
+        __syncwarp();
+        ++k_it;
+      }
+      {
+        const uint32_t s = v_it % L::kv_depth();
+        if (!wait(L::v_empty(sb, s), ((v_it / L::kv_depth()) & 1u) ^ 1u, ST_TIMEOUT_EMPTY, 12)) { ok = false; break; }
+        const uint32_t full = L::v_full(sb, s), dst = sb + L::v() + s * kTileBytes;
+        if (elect_one_sync()) {
           mbar_arrive_expect_tx(full, kTileBytes);
-          tma_load_2d(sb + L::v() + s * kTileBytes, map_v, full, kv_col, kv_row);
-          tma_load_2d(sb + L::v() + s * kTileBytes + kAtomBytes, map_v, full, kv_col + 64, kv_row);
-          ++v_it;
+          tma_load_2d(dst, map_v, full, kv_col, kv_row);
+          tma_load_2d(dst + kAtomBytes, map_v, full, kv_col + 64, kv_row);
         }
+        __syncwarp();
+        ++v_it;
       }
     }
-    if (!ok) {
-      const long long t0 = clock64();
-      while (clock64() - t0 < 200000LL) {
-      }
+  }
+  if (!ok) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000LL) {
     }
   }
 }
 
 // ------------------------------------------------------------------ MMA issuer (one warp)
+// The whole warp walks the loop: ring positions, descriptors, tensor-memory and barrier addresses are
+// computed in convergent code, so they are warp-uniform, and one elected lane issues the tensor
+// instructions and commits. Computed by one lane in a divergent branch the operands sit in per-thread
+// registers and every instruction pays for moving them: with 32 small MMAs per key block the issuing
+// thread, not the tensor pipe, then bounds the kernel.
 template <class L>
-__device__ __forceinline__ void mma_role(const AttnParams& p, uint32_t sb, uint32_t tmem) {
+__device__ __forceinline__ void mma_role(const AttnParams& p, uint32_t sb, uint32_t tmem_in) {
   const int lane = threadIdx.x & 31;
-  if (lane == 0) {
-    uint32_t q_phase = 0, k_it = 0, v_it = 0, blk_it = 0, item_it = 0;
-    bool ok = true;
-    auto issue_qk = [&](int t, int ks) {
-      const uint32_t qa = sb + L::q() + t * kTileBytes, ka = sb + L::k() + ks * kTileBytes;
+  const uint32_t tmem = __shfl_sync(0xFFFFFFFFu, tmem_in, 0);
+  uint32_t q_phase = 0, k_it = 0, v_it = 0, blk_it = 0, item_it = 0;
+  bool ok = true;
+  auto wait = [&](uint32_t bar, uint32_t parity, int code, int what) {
+    return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, p.status, code, what)) != 0;
+  };
+  // the eight K16 steps of S_t = Q_t K^T into tile t's score columns, then the score barrier
+  auto issue_qk = [&](int t, uint32_t ks) {
+    const uint64_t qd = smem_desc(sb + L::q() + t * kTileBytes, kDescSw128KMajor), kd = smem_desc(sb + L::k() + ks * kTileBytes, kDescSw128KMajor);
+    const uint32_t s_t = tmem + L::s_col() + t * 128, s_full = L::s_full(sb, t);
+    if (elect_one_sync()) {
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
-        tc_mma_f16(tmem + L::s_col() + t * 128, smem_desc(qa + off, kDescSw128KMajor), smem_desc(ka + off, kDescSw128KMajor),
-                   kIdescQK, k != 0 ? 1u : 0u);
+        const uint32_t off = ((k >> 2) * kAtomBytes + (k & 3) * 32) >> 4;      // descriptor address units of 16 bytes
+        tc_mma_f16(s_t, qd + off, kd + off, kIdescQK, k != 0 ? 1u : 0u);
       }
-      tc_commit(L::s_full(sb, t));
-    };
-    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
-      const AttnWork wk = p.work[w];
-      const int n = wk.kv_blocks;
-      if (!mbar_wait(L::q_full(sb), q_phase, p.status, ST_TIMEOUT_FULL, 22)) { ok = false; break; }
-      {
-        const int ks = k_it % L::kv_depth();
-        if (!mbar_wait(L::k_full(sb, ks), (k_it / L::kv_depth()) & 1u, p.status, ST_TIMEOUT_FULL, 20)) { ok = false; break; }
-        tc_fence_after();
-        issue_qk(0, ks);
-        issue_qk(1, ks);
-        tc_commit(L::k_empty(sb, ks));
-        ++k_it;
-      }
-      for (int j = 0; j < n && ok; ++j) {
-        const bool have_next = j + 1 < n;
-        const int vs = v_it % L::kv_depth(), ks = k_it % L::kv_depth();
-        if (!mbar_wait(L::v_full(sb, vs), (v_it / L::kv_depth()) & 1u, p.status, ST_TIMEOUT_FULL, 23)) { ok = false; break; }
-        if (have_next &&
-            !mbar_wait(L::k_full(sb, ks), (k_it / L::kv_depth()) & 1u, p.status, ST_TIMEOUT_FULL, 26)) { ok = false; break; }
-        const uint32_t va = sb + L::v() + vs * kTileBytes;
+      tc_commit(s_full);
+    }
+    __syncwarp();
+  };
+  auto commit = [&](uint32_t bar) {
+    if (elect_one_sync()) tc_commit(bar);
+    __syncwarp();
+  };
+  const int num_work = p.num_work;
+  for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    const int n = __shfl_sync(0xFFFFFFFFu, p.work[w].kv_blocks, 0);
+    if (!wait(L::q_full(sb), q_phase, ST_TIMEOUT_FULL, 22)) { ok = false; break; }
+    {
+      const uint32_t ks = k_it % L::kv_depth();
+      if (!wait(L::k_full(sb, ks), (k_it / L::kv_depth()) & 1u, ST_TIMEOUT_FULL, 20)) { ok = false; break; }
+      tc_fence_after();
+      issue_qk(0, ks);
+      issue_qk(1, ks);
+      commit(L::k_empty(sb, ks));
+      ++k_it;
+    }
+    for (int j = 0; j < n && ok; ++j) {
+      const bool have_next = j + 1 < n;
+      const uint32_t vs = v_it % L::kv_depth(), ks = k_it % L::kv_depth();
+      if (!wait(L::v_full(sb, vs), (v_it / L::kv_depth()) & 1u, ST_TIMEOUT_FULL, 23)) { ok = false; break; }
+      if (have_next && !wait(L::k_full(sb, ks), (k_it / L::kv_depth()) & 1u, ST_TIMEOUT_FULL, 26)) { ok = false; break; }
+      const uint64_t vd = smem_desc(sb + L::v() + vs * kTileBytes, kDescVMn);
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (!mbar_wait(L::p_full(sb, t), blk_it & 1u, p.status, ST_TIMEOUT_FULL, 24)) { ok = false; break; }
-          // the first P V of a record overwrites O_t: the previous record's epilogue must have read it
-          if (j == 0 &&
-              !mbar_wait(L::o_free(sb, t), (item_it & 1u) ^ 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, 25)) { ok = false; break; }
-          tc_fence_after();
+      for (int t = 0; t < 2; ++t) {
+        if (!wait(L::p_full(sb, t), blk_it & 1u, ST_TIMEOUT_FULL, 24)) { ok = false; break; }
+        // the first P V of a record overwrites O_t: the previous record's epilogue must have read it
+        if (j == 0 && !wait(L::o_free(sb, t), (item_it & 1u) ^ 1u, ST_TIMEOUT_TMEM_EMPTY, 25)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t o_t = tmem + L::o_col() + t * 128, p_t = tmem + L::s_col() + t * 128, o_full = L::o_full(sb, t);
+        const uint32_t first = j != 0 ? 1u : 0u;
+        if (elect_one_sync()) {
 #pragma unroll
           for (int k = 0; k < 8; ++k)  // 16 keys per step: 8 packed columns of P, 16 rows x 128 B of V
-            tc_mma_f16_ts(tmem + L::o_col() + t * 128, tmem + L::s_col() + t * 128 + k * 8, smem_desc(va + k * 2048, kDescVMn), kIdescPV,
-                          (j != 0 || k != 0) ? 1u : 0u);
-          if (!have_next) tc_commit(L::o_full(sb, t));
-          if (have_next) issue_qk(t, ks);
+            tc_mma_f16_ts(o_t, p_t + k * 8, vd + ((k * 2048) >> 4), kIdescPV, k != 0 ? 1u : first);
+          if (!have_next) tc_commit(o_full);
         }
-        if (!ok) break;
-        tc_commit(L::v_empty(sb, vs));
-        ++v_it;
-        if (have_next) {
-          tc_commit(L::k_empty(sb, ks));
-          ++k_it;
-        }
-        ++blk_it;
+        __syncwarp();
+        if (have_next) issue_qk(t, ks);
       }
       if (!ok) break;
-      tc_commit(L::q_empty(sb));
-      q_phase ^= 1u;
-      ++item_it;
-    }
-    if (!ok) {
-      tc_commit(L::drain(sb));
-      const long long t0 = clock64();
-      while (!mbar_try_wait(L::drain(sb), 0)) {
-        if (clock64() - t0 > 20000000LL) break;
+      commit(L::v_empty(sb, vs));
+      ++v_it;
+      if (have_next) {
+        commit(L::k_empty(sb, ks));
+        ++k_it;
       }
+      ++blk_it;
+    }
+    if (!ok) break;
+    commit(L::q_empty(sb));
+    q_phase ^= 1u;
+    ++item_it;
+  }
+  if (!ok && lane == 0) {
+    tc_commit(L::drain(sb));
+    const long long t0 = clock64();
+    while (!mbar_try_wait(L::drain(sb), 0)) {
+      if (clock64() - t0 > 20000000LL) break;
     }
   }
+  __syncwarp();
 }
 
 // ------------------------------------------------------------------ K/V gather warps (two warps)

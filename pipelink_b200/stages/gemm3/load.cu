@@ -15,7 +15,7 @@ extern "C" __device__ void gemm_load_role(const void* raw_params, unsigned) {
   using namespace gemm3;
   const Gemm3LoadParams& p = *static_cast<const Gemm3LoadParams*>(raw_params);
   extern __shared__ __align__(1024) unsigned char pl_smem[];
-  if ((threadIdx.x & 31) != 0) return;
+  // the whole warp walks the loop (coordinates and addresses warp-uniform); one elected lane issues the copies
   const uint32_t smem = plb::smem_u32(pl_smem);
   const int depth = pipelink_gemm_depth();
   const int k_steps = p.K / TileK;
@@ -24,13 +24,18 @@ extern "C" __device__ void gemm_load_role(const void* raw_params, unsigned) {
     const int slot = k % depth;
     const uint32_t full = barrier_addr(smem, pipelink_gemm_full(), slot);
     const uint32_t empty = barrier_addr(smem, pipelink_gemm_empty(), slot);
-    if (!wait(empty, ((k / depth) & 1) ^ 1)) return;
-    plb::mbar_arrive_expect_tx(full, SlotBytes);
+    if (!__all_sync(0xFFFFFFFFu, wait(empty, ((k / depth) & 1) ^ 1))) return;
     const uint32_t dst = smem + pipelink_gemm_operands() + slot * SlotBytes;
-    plb::tma_load_2d(dst, &p.a, full, k * TileK, m_blk * TileM);
-    plb::tma_load_2d(dst + OperandBytes, &p.b, full, k * TileK, n_blk * TileN);
-    plb::bulk_load(dst + 2 * OperandBytes, p.a_sc + (static_cast<size_t>(m_blk) * k_steps + k) * ScaleBytes, ScaleBytes, full);
-    plb::bulk_load(dst + 2 * OperandBytes + ScaleBytes, p.b_sc + (static_cast<size_t>(n_blk) * k_steps + k) * ScaleBytes, ScaleBytes, full);
+    const uint8_t* const sc_a = p.a_sc + (static_cast<size_t>(m_blk) * k_steps + k) * ScaleBytes;
+    const uint8_t* const sc_b = p.b_sc + (static_cast<size_t>(n_blk) * k_steps + k) * ScaleBytes;
+    if (plb::elect_one_sync()) {
+      plb::mbar_arrive_expect_tx(full, SlotBytes);
+      plb::tma_load_2d(dst, &p.a, full, k * TileK, m_blk * TileM);
+      plb::tma_load_2d(dst + OperandBytes, &p.b, full, k * TileK, n_blk * TileN);
+      plb::bulk_load(dst + 2 * OperandBytes, sc_a, ScaleBytes, full);
+      plb::bulk_load(dst + 2 * OperandBytes + ScaleBytes, sc_b, ScaleBytes, full);
+    }
+    __syncwarp();
   }
 }
 #endif  // !PIPELINK_EMIT

@@ -23,21 +23,6 @@ MOE_CLAIM_ROWS_READY();
 MOE_CLAIM_HIDDEN_READY();
 
 #ifndef PIPELINK_EMIT
-namespace {
-// wait (bounded) until a grid-scoped counter reaches `target`, then order TMA reads after it
-__device__ __forceinline__ bool wait_count(const unsigned* flag, unsigned target, plb::Status* status, int where) {
-  const long long t0 = clock64();
-  while (plb::ld_acquire_gpu_u32(flag) < target) {
-    if (clock64() - t0 > plb::kWaitBudgetCycles / 2 || plb::ld_volatile_i32(&status->code) != 0) {
-      plb::report_failure(status, plb::ST_TIMEOUT_COUNTER, where, plb::ld_acquire_gpu_u32(flag), target);
-      return false;
-    }
-  }
-  asm volatile("fence.proxy.async.global;" ::: "memory");
-  return true;
-}
-}  // namespace
-
 extern "C" __device__ void moe_fwd_load_role(const void* raw_params, unsigned) {
   using namespace moe;
   const MoeFwdLoadParams& p = *static_cast<const MoeFwdLoadParams*>(raw_params);
@@ -48,50 +33,38 @@ extern "C" __device__ void moe_fwd_load_role(const void* raw_params, unsigned) {
   extern __shared__ __align__(1024) unsigned char pl_smem[];
   const int lane = threadIdx.x & 31;
   const FwdWalk f = make_fwd_walk(g1, g2, lane, blockIdx.x == 0);
-  if (lane != 0) return;
   const uint32_t smem = plb::smem_u32(pl_smem);
   const uint32_t cta_rank = plb::cluster_ctarank();
-  const int depth = pipelink_moe_depth();
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  plb::prefetch_tensormap(&p.a1);
-  plb::prefetch_tensormap(&p.b1);
-  plb::prefetch_tensormap(&p.sfa1);
-  plb::prefetch_tensormap(&p.sfb1);
+  if (lane == 0) {
+    plb::prefetch_tensormap(&p.a1);
+    plb::prefetch_tensormap(&p.b1);
+    plb::prefetch_tensormap(&p.sfa1);
+    plb::prefetch_tensormap(&p.sfb1);
+  }
   // every epilogue warp of the pair (16) counts once per pass-1 column tile
   const unsigned hidden_target = 16u * static_cast<unsigned>(g1.n_tiles);
-  int stage = 0;
-  uint32_t phase = 0;
+  Ring ring;
+  ring.init(smem);
+  const uint32_t leader_delta = plb::mapa_shared(ring.full0, 0) - ring.full0;   // the leader CTA's copy of a barrier
+  const int total = __shfl_sync(0xFFFFFFFFu, f.total, 0), tiles1 = __shfl_sync(0xFFFFFFFFu, f.tiles1, 0);
   bool ok = true;
-  for (int tile = pair_id; tile < f.total && ok; tile += num_pairs) {
-    const bool second = tile >= f.tiles1;
+  for (int tile = pair_id; tile < total && ok; tile += num_pairs) {
+    const bool second = tile >= tiles1;
     const MoeGeometry& g = second ? g2 : g1;
-    const Tile t = decode(g, second ? f.w2 : f.w1, second ? tile - f.tiles1 : tile, static_cast<int>(cta_rank));
-    const int b_blk = t.b_blk0 + static_cast<int>(cta_rank);
+    const Tile t = decode(g, second ? f.w2 : f.w1, second ? tile - tiles1 : tile, static_cast<int>(cta_rank));
+    const int a_blk = __shfl_sync(0xFFFFFFFFu, t.a_blk, 0), b_blk0 = __shfl_sync(0xFFFFFFFFu, t.b_blk0, 0);
+    const int b_blk = b_blk0 + static_cast<int>(cta_rank);
     const CUtensorMap* const ma = second ? &p.a2 : &p.a1;
     const CUtensorMap* const mb = second ? &p.b2 : &p.b1;
     const CUtensorMap* const msa = second ? &p.sfa2 : &p.sfa1;
     const CUtensorMap* const msb = second ? &p.sfb2 : &p.sfb1;
     if (second)
-      ok = wait_count(counters + pipelink_moe_hidden_ready() + (t.a_blk >> 1), hidden_target, g.status, 312);
+      ok = wait_count_warp(counters + pipelink_moe_hidden_ready() + (a_blk >> 1), hidden_target, g.status, 312, lane);
     else if (wait_rows)
-      ok = wait_count(counters + pipelink_moe_rows_ready() + (t.a_blk >> 1), 256u, g.status, 311);
+      ok = wait_count_warp(counters + pipelink_moe_rows_ready() + (a_blk >> 1), 256u, g.status, 311, lane);
     if (!ok) break;
-    const int k_steps = g.k_steps;
-    for (int kb = 0; kb < k_steps; ++kb) {
-      if (!plb::mbar_wait(bar(smem, pipelink_moe_empty(), stage), phase ^ 1u, g.status, plb::ST_TIMEOUT_EMPTY, stage)) {
-        ok = false;
-        break;
-      }
-      const uint32_t full = plb::mapa_shared(bar(smem, pipelink_moe_full(), stage), 0);
-      plb::mbar_arrive_expect_tx_cluster(full, SlotTx);
-      const uint32_t slot = smem + pipelink_moe_operands() + stage * SlotBytes;
-      plb::tma_load_2d_pair(slot + OffA, ma, full, kb * 128, t.a_blk * 128);
-      plb::tma_load_2d_pair(slot + OffB, mb, full, kb * 128, b_blk * 128);
-      plb::tma_load_2d_pair(slot + OffSf, msa, full, 0, t.a_blk * k_steps + kb);
-      plb::tma_load_2d_pair(slot + OffSf + SfBytes, msb, full, 0, t.b_blk0 * k_steps + kb);
-      plb::tma_load_2d_pair(slot + OffSf + 2 * SfBytes, msb, full, 0, (t.b_blk0 + 1) * k_steps + kb);
-      if (++stage == depth) { stage = 0; phase ^= 1u; }
-    }
+    ok = load_k_loop(ring, g.k_steps, leader_delta, ma, mb, msa, msb, a_blk, b_blk, b_blk0, g.status);
   }
   if (!ok) {
     // give copies already in flight time to land before this CTA can exit

@@ -28,51 +28,31 @@ extern "C" __device__ void moe_load_role(const void* raw_params, unsigned) {
   extern __shared__ __align__(1024) unsigned char pl_smem[];
   const int lane = threadIdx.x & 31;
   const Walk w = make_walk(g, lane, blockIdx.x == 0);
-  if (lane != 0) return;
   const uint32_t smem = plb::smem_u32(pl_smem);
   const uint32_t cta_rank = plb::cluster_ctarank();
-  const int depth = pipelink_moe_depth();
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  plb::prefetch_tensormap(&p.a);
-  plb::prefetch_tensormap(&p.b);
-  plb::prefetch_tensormap(&p.sfa);
-  plb::prefetch_tensormap(&p.sfb);
-  int stage = 0;
-  uint32_t phase = 0;
+  if (lane == 0) {
+    plb::prefetch_tensormap(&p.a);
+    plb::prefetch_tensormap(&p.b);
+    plb::prefetch_tensormap(&p.sfa);
+    plb::prefetch_tensormap(&p.sfb);
+  }
+  Ring ring;
+  ring.init(smem);
+  const uint32_t leader_delta = plb::mapa_shared(ring.full0, 0) - ring.full0;   // the leader CTA's copy of a barrier
+  const int total_tiles = __shfl_sync(0xFFFFFFFFu, w.total_tiles, 0);
   bool ok = true;
-  for (int tile = pair_id; tile < w.total_tiles && ok; tile += num_pairs) {
+  for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
     const Tile t = decode(g, w, tile, static_cast<int>(cta_rank));
-    const int b_blk = t.b_blk0 + static_cast<int>(cta_rank);
+    const int a_blk = __shfl_sync(0xFFFFFFFFu, t.a_blk, 0), b_blk0 = __shfl_sync(0xFFFFFFFFu, t.b_blk0, 0);
+    const int b_blk = b_blk0 + static_cast<int>(cta_rank);
     if (counters != nullptr) {
       // rows pulled by the comm owner are usable once their tile's count is complete; then order
       // the TMA reads after the count was observed
-      const unsigned* flag = counters + pipelink_moe_rows_ready() + (t.a_blk >> 1);
-      const long long t0 = clock64();
-      while (plb::ld_acquire_gpu_u32(flag) < 256u) {
-        if (clock64() - t0 > plb::kWaitBudgetCycles / 2 || plb::ld_volatile_i32(&g.status->code) != 0) {
-          plb::report_failure(g.status, plb::ST_TIMEOUT_COUNTER, 311, plb::ld_acquire_gpu_u32(flag), 256u);
-          ok = false;
-          break;
-        }
-      }
+      ok = wait_count_warp(counters + pipelink_moe_rows_ready() + (a_blk >> 1), 256u, g.status, 311, lane);
       if (!ok) break;
-      asm volatile("fence.proxy.async.global;" ::: "memory");
     }
-    for (int kb = 0; kb < g.k_steps; ++kb) {
-      if (!plb::mbar_wait(bar(smem, pipelink_moe_empty(), stage), phase ^ 1u, g.status, plb::ST_TIMEOUT_EMPTY, stage)) {
-        ok = false;
-        break;
-      }
-      const uint32_t full = plb::mapa_shared(bar(smem, pipelink_moe_full(), stage), 0);
-      plb::mbar_arrive_expect_tx_cluster(full, SlotTx);
-      const uint32_t slot = smem + pipelink_moe_operands() + stage * SlotBytes;
-      plb::tma_load_2d_pair(slot + OffA, &p.a, full, kb * 128, t.a_blk * 128);
-      plb::tma_load_2d_pair(slot + OffB, &p.b, full, kb * 128, b_blk * 128);
-      plb::tma_load_2d_pair(slot + OffSf, &p.sfa, full, 0, t.a_blk * g.k_steps + kb);
-      plb::tma_load_2d_pair(slot + OffSf + SfBytes, &p.sfb, full, 0, t.b_blk0 * g.k_steps + kb);
-      plb::tma_load_2d_pair(slot + OffSf + 2 * SfBytes, &p.sfb, full, 0, (t.b_blk0 + 1) * g.k_steps + kb);
-      if (++stage == depth) { stage = 0; phase ^= 1u; }
-    }
+    ok = load_k_loop(ring, g.k_steps, leader_delta, &p.a, &p.b, &p.sfa, &p.sfb, a_blk, b_blk, b_blk0, g.status);
   }
   if (!ok) {
     // give copies already in flight time to land before this CTA can exit

@@ -222,6 +222,103 @@ __device__ __forceinline__ FwdWalk make_fwd_walk(const MoeGeometry& g1, const Mo
   return f;
 }
 
+// ---- the two issue loops, shared by the GEMM owners and the one-launch forward owners.
+// A whole warp walks each loop: ring position, descriptors, tensor-memory and barrier addresses are
+// computed in convergent code, so they are warp-uniform, and one elected lane issues the copies, the
+// tensor instructions and the commits. (Computed by one lane in a divergent branch the operands sit in
+// per-thread registers and every such instruction pays for moving them: the issuing thread, not the
+// tensor pipe, then bounds the kernel.)
+struct Ring {
+  uint32_t smem, operands, full0, empty0, stage, phase;
+  int depth;
+  __device__ __forceinline__ void init(uint32_t smem_base) {
+    smem = smem_base;
+    operands = smem_base + static_cast<uint32_t>(pipelink_moe_operands());
+    full0 = bar(smem_base, pipelink_moe_full());
+    empty0 = bar(smem_base, pipelink_moe_empty());
+    depth = pipelink_moe_depth();
+    stage = 0;
+    phase = 0;
+  }
+  __device__ __forceinline__ void advance() {
+    if (++stage == static_cast<uint32_t>(depth)) { stage = 0; phase ^= 1u; }
+  }
+};
+
+// K steps of one tile, MMA side: scale blocks -> tensor memory, four K32 MMAs, the slot back to both CTAs.
+__device__ __forceinline__ bool mma_k_loop(Ring& r, int k_steps, uint32_t tmem, uint32_t d_tmem, uint32_t empty_peer_delta,
+                                           plb::Status* status) {
+  constexpr uint32_t idesc = plb::idesc_mxf8(256, 256);
+  const uint32_t sfcols0 = tmem + static_cast<uint32_t>(pipelink_moe_sfcols());
+  for (int kb = 0; kb < k_steps; ++kb) {
+    if (!__all_sync(0xFFFFFFFFu, plb::mbar_wait(r.full0 + 16u * r.stage, r.phase, status, plb::ST_TIMEOUT_FULL, static_cast<int>(r.stage))))
+      return false;
+    plb::tc_fence_after();
+    const uint32_t slot = r.operands + r.stage * SlotBytes;
+    const uint32_t sfa_t = sfcols0 + r.stage * SfColsPerSlot, sfb_t = sfa_t + 4;
+    const uint64_t sfd_a = plb::smem_desc(slot + OffSf, plb::kDescScale), sfd_b0 = plb::smem_desc(slot + OffSf + SfBytes, plb::kDescScale),
+                   sfd_b1 = plb::smem_desc(slot + OffSf + 2 * SfBytes, plb::kDescScale);
+    const uint64_t adesc = plb::smem_desc(slot + OffA, plb::kDescSw128KMajor), bdesc = plb::smem_desc(slot + OffB, plb::kDescSw128KMajor);
+    const uint32_t first = kb != 0 ? 1u : 0u;
+    const uint32_t empty_own = r.empty0 + 16u * r.stage, empty_peer = empty_own + empty_peer_delta;
+    if (plb::elect_one_sync()) {
+      plb::tc_cp_32x128b_warpx4_pair(sfa_t, sfd_a);
+      plb::tc_cp_32x128b_warpx4_pair(sfb_t, sfd_b0);
+      plb::tc_cp_32x128b_warpx4_pair(sfb_t + 4, sfd_b1);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        plb::tc_mma_mxf8_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, plb::idesc_with_sf(idesc, k), sfa_t, sfb_t, k != 0 ? 1u : first);
+      plb::tc_commit_pair(empty_own);
+      plb::tc_commit_pair(empty_peer);
+    }
+    __syncwarp();
+    r.advance();
+  }
+  return true;
+}
+
+// K steps of one tile, load side: this CTA's half of A and B and the scale blocks of every K step.
+__device__ __forceinline__ bool load_k_loop(Ring& r, int k_steps, uint32_t full_leader_delta, const CUtensorMap* ma, const CUtensorMap* mb,
+                                            const CUtensorMap* msa, const CUtensorMap* msb, int a_blk, int b_blk, int b_blk0,
+                                            plb::Status* status) {
+  for (int kb = 0; kb < k_steps; ++kb) {
+    if (!__all_sync(0xFFFFFFFFu, plb::mbar_wait(r.empty0 + 16u * r.stage, r.phase ^ 1u, status, plb::ST_TIMEOUT_EMPTY, static_cast<int>(r.stage))))
+      return false;
+    const uint32_t full = r.full0 + 16u * r.stage + full_leader_delta;
+    const uint32_t slot = r.operands + r.stage * SlotBytes;
+    const int kx = kb * 128, row_a = a_blk * 128, row_b = b_blk * 128;
+    const int sf_a = a_blk * k_steps + kb, sf_b0 = b_blk0 * k_steps + kb, sf_b1 = (b_blk0 + 1) * k_steps + kb;
+    if (plb::elect_one_sync()) {
+      plb::mbar_arrive_expect_tx_cluster(full, SlotTx);
+      plb::tma_load_2d_pair(slot + OffA, ma, full, kx, row_a);
+      plb::tma_load_2d_pair(slot + OffB, mb, full, kx, row_b);
+      plb::tma_load_2d_pair(slot + OffSf, msa, full, 0, sf_a);
+      plb::tma_load_2d_pair(slot + OffSf + SfBytes, msb, full, 0, sf_b0);
+      plb::tma_load_2d_pair(slot + OffSf + 2 * SfBytes, msb, full, 0, sf_b1);
+    }
+    __syncwarp();
+    r.advance();
+  }
+  return true;
+}
+
+// One lane waits (bounded) until a grid-scoped counter reaches `target` and orders TMA reads after it; the warp learns the outcome.
+__device__ __forceinline__ bool wait_count_warp(const unsigned* flag, unsigned target, plb::Status* status, int where, int lane) {
+  bool ok = true;
+  if (lane == 0) {
+    const long long t0 = clock64();
+    while (plb::ld_acquire_gpu_u32(flag) < target) {
+      if (clock64() - t0 > plb::kWaitBudgetCycles / 2 || plb::ld_volatile_i32(&status->code) != 0) {
+        plb::report_failure(status, plb::ST_TIMEOUT_COUNTER, where, plb::ld_acquire_gpu_u32(flag), target);
+        ok = false;
+        break;
+      }
+    }
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+  }
+  return __all_sync(0xFFFFFFFFu, ok);
+}
+
 __device__ __forceinline__ Tile decode(const MoeGeometry& g, const Walk& w, int tile, int cta_rank) {
   Tile t;
   int m_tile = tile / g.n_tiles;
