@@ -575,7 +575,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_leader);
         PROF_ADD(t_drain, td);
         PROF_T0(tm);
         if (BF16) {
@@ -656,7 +656,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a,
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_leader);
         PROF_ADD(t_drain, td);
         PROF_T0(tm);
         // 128 fp32 -> 64 packed bf16 pairs = 16 chunks of 16 bytes

@@ -43,7 +43,7 @@ __device__ __forceinline__ void swiglu_tile(const EpilogueWarp& e, const Tile& t
   plb::tc_wait_ld();
   plb::tc_fence_before();
   __syncwarp();
-  if (e.lane == 0) plb::mbar_arrive_cluster(e.acc_empty_leader);
+  if (e.lane == 0) plb::mbar_arrive_cluster_relaxed(e.acc_empty_leader);
   uint4 q0, q1, q2, q3;
   const uint32_t e0 = plb::swiglu_quant32(g0, u0, limit, q0, q1);
   const uint32_t e1 = plb::swiglu_quant32(g1, u1, limit, q2, q3);
@@ -72,7 +72,7 @@ __device__ __forceinline__ void rows_tile(const EpilogueWarp& e, const Tile& t, 
   plb::tc_wait_ld();
   plb::tc_fence_before();
   __syncwarp();
-  if (lane == 0) plb::mbar_arrive_cluster(e.acc_empty_leader);
+  if (lane == 0) plb::mbar_arrive_cluster_relaxed(e.acc_empty_leader);
   uint32_t wv[64];                      // 128 fp32 -> 64 packed bf16 pairs = 16 chunks of 16 bytes
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
