@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(kDecThreads, 1)
 decode_kernel(const DecodeGlobals g, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) uint8_t dsm_raw[];
   const uint32_t smem = smem_u32(dsm_raw);
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xFFFFFFFFu, static_cast<int>(threadIdx.x >> 5), 0);   // warp-uniform, and said so to the compiler
   const int pos = *g.pos_dev;
   int istride;
   const int* my = stage_instructions(g, reinterpret_cast<int*>(dsm_raw + LibLayout::inst()), threadIdx.x, kDecThreads, istride);
