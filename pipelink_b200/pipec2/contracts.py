@@ -109,10 +109,17 @@ def expand_counters(counters, handles) -> list[dict]:
     return out
 
 
-def check_topology(manifests, profile):
-    """All stages of one image agree on the CTA group and on the compiled cluster shape
+def check_topology(manifests, profile, pipeline_topology=None):
+    """All stages of one image agree on the CTA group and on the compiled cluster shape, and with the
+    pipeline on whether the kernel is persistent and who schedules it
     (clause L-TOPO; the reference intersects the same declarations, pipec/src/pipec2/link.py:1040-1100)."""
     failures = []
+    for m in manifests:
+        for key in ("persistent", "scheduler"):
+            mine, theirs = m.get("topology", {}).get(key), (pipeline_topology or {}).get(key)
+            if mine is not None and theirs is not None and mine != theirs:
+                failures.append(ClauseFailure("L-TOPO", f"stages.{m['stage']['id']}.topology.{key}",
+                                              f"the stage was written for {key} = {mine!r}, the pipeline states {theirs!r}"))
     groups = {m["stage"]["id"]: (m.get("topology", {}).get("cta_group") or {}).get("fixed", 1) for m in manifests}
     clusters = {m["stage"]["id"]: tuple((m.get("topology", {}).get("cluster") or {}).get("compiled", [1, 1, 1])) for m in manifests}
     if len(set(groups.values())) > 1:

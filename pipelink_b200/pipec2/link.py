@@ -144,7 +144,26 @@ def front_end(manifests, pipe):
     profile = PROFILES[profiles.pop()]
     handles = dict(pipe.get("handles", {}))
 
-    cta_group, cluster = contracts.check_topology(manifests, profile)
+    # the assembly: every handle an endpoint names is one the pipeline declares, before anything is paired
+    # (the reference validates the same at pipec/src/pipec2/link.py:125-139, schema.validate_assembly)
+    failures = []
+    for m in manifests:
+        for ep in m.get("endpoints", []):
+            depth = (ep.get("ring") or {}).get("depth")
+            if isinstance(depth, dict) and "handle" in depth and handles.get(depth["handle"], {}).get("class") != "depth":
+                failures.append(ClauseFailure("L-HANDLE", f"stages.{m['stage']['id']}.endpoints.{ep['name']}.ring.depth.handle",
+                                              f"ring depth handle {depth['handle']!r} is not a depth handle of the pipeline"))
+        # a claim lives for the kernel, for a phase the pipeline declares, or for a tensor-event interval (a
+        # record, not a string; placed like a kernel-lived claim here, which is always safe)
+        for cl in m.get("claims", []):
+            life = cl.get("lifetime", "kernel")
+            if isinstance(life, str) and life != "kernel" and not (
+                    life.startswith("phase:") and life[len("phase:"):] in pipe.get("phases", [])):
+                failures.append(ClauseFailure("L-PHASE", f"stages.{m['stage']['id']}.claims.{cl.get('domain')}.{cl.get('handle')}.lifetime",
+                                              f"lifetime {life!r} names no phase of the pipeline"))
+    if failures:
+        raise PipeLinkError(failures)
+    cta_group, cluster = contracts.check_topology(manifests, profile, pipe.get("topology"))
     cluster_size = cluster[0] * cluster[1] * cluster[2]
     channels = contracts.pair_channels(manifests)
     contracts.check_compatibility(channels)

@@ -37,3 +37,49 @@ def test_ring_pipeline_solves_as_the_reference_solves_it(name):
     exp = next(e for e in fe["expansions"] if e["channel"] == "tile_ring")
     assert (exp["full"]["count"], exp["empty"]["count"], exp["full"]["tx_bytes"]) == (
         want["arrive_full"], want["arrive_empty"], want["tx_bytes"])
+
+
+# ---------------------------------------------------------------- examples/contract-gallery
+GALLERY = json.loads((Path(__file__).parent / "golden" / "reference_contract_gallery.json").read_text())
+
+
+def _this_driver(case):
+    """The clause(s) this driver raises for a gallery case, or "OK" with the solved launch shape."""
+    from pipelink_b200.pipec2.model import PipeLinkError
+    manifests = [copy.deepcopy(GALLERY["producer"]), copy.deepcopy(case["manifest"])]
+    doc = copy.deepcopy(case["pipeline"])
+    try:
+        for m in manifests:
+            schema.validate_manifest(m)
+        schema.validate_pipeline(doc)
+        fe = linker.front_end(manifests, doc["pipeline"])
+    except PipeLinkError as err:
+        return sorted({f.clause_id for f in err.failures}), None
+    return "OK", {"threads": 32 * sum(w for _, w, _ in fe["role_warps"].values()), "dyn_smem_bytes": fe["solver"]["high_water"]["smem"]}
+
+
+@pytest.mark.parametrize("name", sorted(n for n, c in GALLERY["cases"].items() if c["phase"] == "link"))
+def test_contract_gallery_cases_end_as_the_reference_ends_them(name):
+    """One unchanged producer package against the original consumer, a replacement, and consumers
+    with one wrong contract each (the reference's third tutorial): the documents its annotation pass
+    emitted must link here where they link there (same launch shape) and fail with the same clause
+    where they fail there (recorded by tests/golden/make_reference_contract_gallery.py, which runs
+    the reference itself)."""
+    case = GALLERY["cases"][name]
+    got, launch = _this_driver(case)
+    if case["reference"] == "OK":
+        assert case["expected_clause"] is None and got == "OK" and launch == case["launch"]
+    else:
+        want = sorted({f["clause"] for f in case["reference"]})
+        assert want == [case["expected_clause"]]          # the reference's own table agrees with what it did here
+        assert got == want
+
+
+def test_contract_gallery_pack_time_case_is_recorded():
+    """`init.cu` names a consumer warp as the barrier initialiser although the dispatch kernel
+    materialises the ring: the reference refuses it while packing (P-INIT), so there is no
+    manifest to link. This driver's annotation pass has no producer/consumer init-warp field to get
+    wrong; the case is kept as a record of the reference's behaviour."""
+    case = GALLERY["cases"]["init"]
+    assert case["phase"] == "pack" and case["manifest"] is None
+    assert [f["clause"] for f in case["reference"]] == ["P-INIT"]
