@@ -222,6 +222,14 @@ def _protocol_differences(name, pp, cp):
     return out
 
 
+def _declared_name(decl):
+    """The function a C declaration declares: the identifier in front of its parameter list."""
+    if not isinstance(decl, str) or "(" not in decl:
+        return None
+    head = decl.split("(", 1)[0].replace("*", " ").split()
+    return head[-1] if head else None
+
+
 DTYPE_BITS = {"bf16": 16, "f16": 16, "fp16": 16, "f32": 32, "fp32": 32, "s32": 32, "u32": 32, "s8": 8, "u8": 8, "e4m3": 8,
               "e5m2": 8, "e4m3+ue8m0": 8}
 
@@ -329,9 +337,14 @@ def expand_protocols(channels, manifests, cluster_size: int = 1) -> list[dict]:
         elif proto["kind"] == "call":
             rec["callable"] = [proto["export"], proto.get("decl", "")]
             # what the generated trampoline needs: the caller's symbol, the provider's, and the C signature
-            provider = (exports.get(cs, {}).get((ce.get("protocol") or {}).get("export")) or {}).get("symbol")
-            if "symbol" in proto and provider is not None and proto.get("signature"):
-                rec["trampoline"] = {"caller": proto["symbol"], "provider": provider, "signature": proto["signature"]}
+            # (an endpoint names its function as `symbol`, or spells the whole declaration as `decl`, the
+            # reference's form: extern "C" __device__ float pipelink_call_scale(float);)
+            cproto0 = ce.get("protocol") or {}
+            caller = proto.get("symbol") or _declared_name(proto.get("decl"))
+            provider = ((exports.get(cs, {}).get(cproto0.get("export")) or {}).get("symbol") or cproto0.get("symbol")
+                        or _declared_name(cproto0.get("decl")))
+            if caller is not None and provider is not None and proto.get("signature"):
+                rec["trampoline"] = {"caller": caller, "provider": provider, "signature": proto["signature"]}
             # the provided side restates its stage's export record: declaration text and its digest
             cproto = ce.get("protocol") or {}
             record = exports.get(cs, {}).get(cproto.get("export"))

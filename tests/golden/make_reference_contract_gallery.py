@@ -7,7 +7,10 @@ Run in the build container, where the reference tree is mounted (it does not tra
 
     python tests/golden/make_reference_contract_gallery.py <path to a checkout of the reference>
 
-writes tests/golden/reference_contract_gallery.json.
+writes tests/golden/reference_contract_gallery.json, and tests/golden/reference_hello_callable.json: the
+two manifests of `examples/hello-callable` (a role-less provider and a caller joined by a call channel),
+the pipeline description its build.py writes, and the launch shape and parameter layout the reference's
+front end derives.
 """
 import json
 import os
@@ -115,3 +118,25 @@ dst.write_text(json.dumps(out, indent=1, sort_keys=True) + "\n")
 print(dst)
 for name, case in out["cases"].items():
     print(name, case["expected_clause"], case["phase"], case["reference"], case.get("launch"))
+
+
+# ---------------------------------------------------------------- examples/hello-callable
+HELLO = REFERENCE / "examples" / "hello-callable" / "src"
+hello = [emit(HELLO / "provider.cu"), emit(HELLO / "caller.cu")]
+hello_doc = {"pipelink_abi": hello[1]["pipelink_abi"],
+             "pipeline": {"name": "hello-callable",       # examples/hello-callable/build.py:56-70, restated as data
+                          "stages": [{"stage_id": m["stage"]["id"], "artifact_path": f"{n}.plink"} for m, n in zip(hello, ("provider", "caller"))],
+                          "handles": {"pipelink_call_warps": {"class": "base", "binding": "bind", "domain": "warp", "owner": "claim:call"}},
+                          "phases": ["call"], "exclusive": [], "domains": {}, "depth_priority": [], "regs_priority": [],
+                          "forced_bindings": {}, "topology": {"persistent": False, "scheduler": "static"}}}
+hello_stages = [rschema.load_stage_manifest(m) for m in hello]
+hello_pipe = rschema.load_pipeline(hello_doc)
+solution = front_end(hello_pipe, hello_stages)
+layout = rlink._params_layout(hello_stages, rlink.get_profile(hello_pipe.target.profile))
+record = {"source": "examples/hello-callable (src/provider.cu, src/caller.cu, build.py)", "manifests": hello, "pipeline": hello_doc,
+          "reference": {"threads": solution.launch.threads, "dyn_smem_bytes": solution.launch.dyn_smem_bytes,
+                        "warp_map": {k: list(v) for k, v in solution.warp_map.items()},
+                        "params": {"total_bytes": layout.total_bytes, "entries": [list(e) for e in layout.entries]}}}
+dst = ROOT / "tests" / "golden" / "reference_hello_callable.json"
+dst.write_text(json.dumps(record, indent=1, sort_keys=True) + "\n")
+print(dst, json.dumps(record["reference"]))

@@ -83,3 +83,32 @@ def test_contract_gallery_pack_time_case_is_recorded():
     case = GALLERY["cases"]["init"]
     assert case["phase"] == "pack" and case["manifest"] is None
     assert [f["clause"] for f in case["reference"]] == ["P-INIT"]
+
+
+# ---------------------------------------------------------------- examples/hello-callable
+HELLO = json.loads((Path(__file__).parent / "golden" / "reference_hello_callable.json").read_text())
+
+
+def test_hello_callable_links_as_the_reference_links_it():
+    """The reference's first tutorial: a role-less provider and a caller joined by a call channel.
+    Its own annotation pass emitted the manifests (call endpoints spell whole C declarations there);
+    this driver pairs the ends, derives the reference's launch shape and parameter total, and plans the
+    trampoline between the two declared functions."""
+    manifests, doc = copy.deepcopy(HELLO["manifests"]), copy.deepcopy(HELLO["pipeline"])
+    for m in manifests:
+        schema.validate_manifest(m)
+    schema.validate_pipeline(doc)
+    fe = linker.front_end(manifests, doc["pipeline"])
+    want = HELLO["reference"]
+    warp_map = {role: [fe["bindings"][h][0] + off, fe["bindings"][h][0] + off + warps] for role, (h, warps, off) in fe["role_warps"].items()}
+    assert warp_map == want["warp_map"]
+    assert 32 * sum(w for _, w, _ in fe["role_warps"].values()) == want["threads"] == 128
+    assert fe["solver"]["high_water"].get("smem", 0) == want["dyn_smem_bytes"] == 0
+    assert fe["params"]["total_bytes"] == want["params"]["total_bytes"]
+    mine = {e[0]: (e[2], e[3]) for e in fe["params"]["entries"]}
+    assert mine == {e[0]: (e[2], e[3]) for e in want["params"]["entries"]}            # bytes and alignment per stage
+    (call,) = [e for e in fe["expansions"] if e["kind"] == "call"]
+    assert call["trampoline"] == {"caller": "pipelink_call_scale", "provider": "hello_scale", "signature": "float(float)"}
+    from pipelink_b200.pipec2 import codegen
+    stub = codegen.binding_stub(fe["bindings"], [call["trampoline"]])
+    assert 'extern "C" __device__ float pipelink_call_scale(float a0) { return hello_scale(a0); }' in stub
