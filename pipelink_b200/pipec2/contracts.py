@@ -75,7 +75,14 @@ def expand_counters(counters, handles) -> list[dict]:
     for name, (prod, cons) in sorted(counters.items()):
         path = f"channels.{name}.protocol"
         eps = [e for _, e in prod + cons]
-        decls = [(e.get("protocol") or {}).get("counter") for e in eps]
+        # the declaration sits in `protocol.counter`, or flat in the protocol (the form the reference's annotation pass emits)
+        def declaration(e):
+            proto = e.get("protocol") or {}
+            if proto.get("counter") is not None:
+                return proto["counter"]
+            return {k: proto[k] for k in ("slot", "release", "acquire") if k in proto} if "slot" in proto else None
+
+        decls = [declaration(e) for e in eps]
         if any(e.get("protocol", {}).get("kind") != "counter" or d is None for e, d in zip(eps, decls)):
             failures.append(ClauseFailure("L-PROTO", path, "counter channel needs a counter declaration on every endpoint"))
             continue
@@ -121,7 +128,12 @@ def check_topology(manifests, profile, pipeline_topology=None):
                 failures.append(ClauseFailure("L-TOPO", f"stages.{m['stage']['id']}.topology.{key}",
                                               f"the stage was written for {key} = {mine!r}, the pipeline states {theirs!r}"))
     groups = {m["stage"]["id"]: (m.get("topology", {}).get("cta_group") or {}).get("fixed", 1) for m in manifests}
-    clusters = {m["stage"]["id"]: tuple((m.get("topology", {}).get("cluster") or {}).get("compiled", [1, 1, 1])) for m in manifests}
+    def compiled(m):
+        # "dynamic": the stage was compiled without a cluster attribute; the launch chooses (one CTA here)
+        c = (m.get("topology", {}).get("cluster") or {}).get("compiled", [1, 1, 1])
+        return (1, 1, 1) if c == "dynamic" else tuple(c)
+
+    clusters = {m["stage"]["id"]: compiled(m) for m in manifests}
     if len(set(groups.values())) > 1:
         failures.append(ClauseFailure("L-TOPO", "stages.topology.cta_group", "stages were compiled for different CTA groups", {"stages": groups}))
     if len(set(clusters.values())) > 1:
@@ -178,7 +190,12 @@ def check_compatibility(channels) -> None:
                                                   "TMEM lane/column shape is not congruent with tile.shape", {"stage": stage}))
         if failures:
             continue
+        handoff = (pe.get("protocol") or {}).get("kind") == "named_barrier"
         for f in COMPAT_FIELDS:
+            # the two ends of a named-barrier hand-off may hold the handed-over storage under claims of
+            # their own (one per phase); that the claims are the same place is checked once they are solved
+            if handoff and f == "binds":
+                continue
             if pe.get(f) != ce.get(f):
                 failures.append(ClauseFailure("L-PAIR", f"channels.{name}.endpoint.{f}",
                                               f"endpoint compatibility field {f} differs",
@@ -200,6 +217,11 @@ def _protocol_differences(name, pp, cp):
     path = f"channels.{name}.protocol"
     if pp.get("kind") != cp.get("kind"):
         return [ClauseFailure("L-PROTO", f"{path}.kind", "endpoint protocol kinds differ")]
+    if pp.get("kind") == "named_barrier":
+        # a hardware named barrier both roles reach: the ends name the same id handle and thread count
+        if (pp.get("id"), pp.get("count")) != (cp.get("id"), cp.get("count")):
+            return [ClauseFailure("L-PROTO", path, "named-barrier id handle or thread count disagrees")]
+        return []
     if pp.get("kind") == "call":
         # the two ends declare different functions by design (trampoline / implementation); they agree on
         # the export they mean and on its signature
@@ -261,7 +283,7 @@ def _role_sizes(manifests):
     return sizes
 
 
-def expand_protocols(channels, manifests, cluster_size: int = 1) -> list[dict]:
+def expand_protocols(channels, manifests, cluster_size: int = 1, handles=None) -> list[dict]:
     """One expansion record per channel: barrier slot handles, arrival counts, tx bytes, depth.
     A cluster-scoped channel may collect its arrivals from the role's warps in every CTA of the
     cluster (the reference's example: pl::side{..., {"producer", 2}, 0} under .scope("cluster"),
@@ -355,6 +377,13 @@ def expand_protocols(channels, manifests, cluster_size: int = 1) -> list[dict]:
                     (cproto.get("decl"), cproto.get("decl_sha256")) != (record.get("decl"), record.get("decl_sha256"))):
                 failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol",
                                               "consumer export declaration or hash disagrees with the channel"))
+        elif proto["kind"] == "named_barrier":
+            # pipec/src/pipec2/protocol.py:803-815: the id is a base handle of the named_barrier domain
+            decl = (handles or {}).get(proto.get("id"))
+            if handles is not None and (decl is None or decl.get("class") != "base" or decl.get("domain") != "named_barrier"):
+                failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol",
+                                              "named-barrier id handle is not declared in the named_barrier domain"))
+            rec["named_barrier"] = [proto.get("id"), proto.get("count")]
         else:
             failures.append(ClauseFailure("L-PROTO", f"channels.{name}.protocol.kind", f"unsupported protocol kind {proto['kind']!r}"))
         out.append(rec)

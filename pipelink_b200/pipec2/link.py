@@ -117,6 +117,12 @@ def _check_symbols(manifests, bindings):
         raise PipeLinkError(failures)
 
 
+def profile_scale(profile, pipe, domain):
+    """Physical units per unit of a domain (an mbarrier slot is 16 bytes, a page what the pipeline states)."""
+    stated = (pipe.get("domains", {}).get(domain) or {}).get("page_bytes")
+    return int(stated) if stated else profile["domains"][domain].scale
+
+
 def _params_layout(manifests, profile):
     entries, off = [], 0
     for m in manifests:
@@ -167,7 +173,7 @@ def front_end(manifests, pipe):
     cluster_size = cluster[0] * cluster[1] * cluster[2]
     channels = contracts.pair_channels(manifests)
     contracts.check_compatibility(channels)
-    expansions = contracts.expand_protocols(channels, manifests, cluster_size)
+    expansions = contracts.expand_protocols(channels, manifests, cluster_size, handles)
     expansions += contracts.expand_counters(contracts.counter_channels(manifests), handles)
     for e in expansions:
         if e.get("kind") == "mbarrier" and (e.get("init") or {}).get("materializer", "dispatch") != "dispatch":
@@ -199,7 +205,19 @@ def front_end(manifests, pipe):
                                         forced=pipe.get("forced_bindings", {}),
                                         regs_priority=pipe.get("regs_priority", []),
                                         reg_claims=_reg_claims(manifests, handles), role_warps=role_warps,
-                                        pipeline_domains=pipe.get("domains", {}))
+                                        pipeline_domains=pipe.get("domains", {}), exclusive=[tuple(e) for e in pipe.get("exclusive", [])])
+    # a named-barrier hand-off: both ends' storage claims must have been solved to the same bytes
+    for name, ((ps, pe), (cs, ce)) in channels.items():
+        if (pe.get("protocol") or {}).get("kind") != "named_barrier":
+            continue
+        places = []
+        for ep in (pe, ce):
+            h = (ep.get("binds") or {}).get("base")
+            if h in bindings and h in claims:
+                places.append(bindings[h][0] * profile_scale(profile, pipe, claims[h]["rec"]["domain"]))
+        if len(places) == 2 and places[0] != places[1]:
+            raise PipeLinkError(ClauseFailure("L8", f"channels.{name}.endpoint.physical_identity",
+                                              "the two ends of the hand-off hold different storage", {"bytes": places}))
     for rec in tensor_records:       # a lend no certified program touches claims nothing: its handle resolves to 0
         for h in rec["unused_handles"]:
             bindings.setdefault(h, [0, "unused"])

@@ -21,6 +21,9 @@ SM_100A = {
         "mbarrier": Domain("16-byte slots", 232448 // 16, 0, 1, "smem", 16),
         "tmem": Domain("columns", 512, 0, 32, "tmem", 1),
         "named_barrier": Domain("IDs", 16, 1, 1, "named_barrier", 1),
+        # pages of shared memory whose number and size the pipeline states (`domains.smem_page`:
+        # capacity, page_bytes); page p is bytes [p * page_bytes, (p + 1) * page_bytes)
+        "smem_page": Domain("pages", "pipeline", 0, 1, "smem", 1),
         "warp": Domain("launch warps", 32, 0, 1, "warp", 1),
         "regs": Domain("per-thread registers", 256, 24, 8, "regs", 1),
         "gmem_counter": Domain("4-byte slots", "pipeline", 0, 1, "gmem_counter", 1),

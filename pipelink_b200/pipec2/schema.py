@@ -142,12 +142,27 @@ def validate_pipeline(p: dict) -> None:
     for name in pipe.get("regs_priority", []):
         if pipe.get("handles", {}).get(name, {}).get("class") != "regs":
             c.add("L-HANDLE", f"pipeline.regs_priority.{name}", "not a regs handle")
+    # an exclusive entry is a pair of phase selectors: a declared phase, or `instr_*`, every phase whose name
+    # starts with instr_ (two of them in one entry: every pair of different instruction phases); nothing else
+    # is a pattern (the reference's rules, pipec/src/pipec2/schema.py:1285-1327)
     phases = pipe.get("phases", ["steady"])
     for i, pair in enumerate(pipe.get("exclusive", [])):
+        if not isinstance(pair, list) or len(pair) != 2:
+            c.add("L-PHASE", f"$.pipeline.exclusive[{i}]", "exclusive entry must contain exactly two phase selectors")
+            continue
         for j, name in enumerate(pair):
-            if name not in phases:
+            if name == "instr_*":
+                if not any(ph.startswith("instr_") for ph in phases):
+                    c.add("L-PHASE", f"$.pipeline.exclusive[{i}][{j}]", "instr_* matches no declared phase")
+            elif isinstance(name, str) and "*" in name:
+                c.add("L-PHASE", f"$.pipeline.exclusive[{i}][{j}]", "only the instr_* phase pattern is supported")
+            elif name not in phases:
                 c.add("L-PHASE", f"$.pipeline.exclusive[{i}][{j}]", f"unknown phase {name!r}")
+        if pair[0] == pair[1] and pair[0] != "instr_*":
+            c.add("L-PHASE", f"$.pipeline.exclusive[{i}]", "exclusive self-pair is invalid")
     for dom, d in pipe.get("domains", {}).items():
         if not isinstance(d.get("capacity"), int) or d["capacity"] < 0:
             c.add("L-BUDGET", f"pipeline.domains.{dom}.capacity", "a pipeline domain needs a non-negative capacity")
+        if dom == "smem_page" and (not isinstance(d.get("page_bytes"), int) or d["page_bytes"] < 1):
+            c.add("L-HANDLE", f"pipeline.domains.{dom}.page_bytes", "the page domain states the size of a page")
     c.raise_if_any()

@@ -28,7 +28,7 @@ def _extent_expr(extent, depth_vars):
 
 
 def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forced=None, total_warps=None,
-          regs_priority=(), reg_claims=(), role_warps=None, pipeline_domains=None):
+          regs_priority=(), reg_claims=(), role_warps=None, pipeline_domains=None, exclusive=()):
     """claims: handle -> unified claim record (every domain but `regs`). reg_claims: the register
     claims ({handle, roles, values, reg_group?}); role_warps: role -> (warp claim handle, warps[, offset inside the claim]).
     Returns (bindings, intervals, tiers)."""
@@ -58,8 +58,9 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
     domains = dict(profile["domains"])
     for dname, dom in list(domains.items()):
         if dom.capacity == "pipeline":      # the pipeline description sizes this domain (0 when it does not)
-            cap = int((pipeline_domains.get(dname) or {}).get("capacity", 0))
-            domains[dname] = type(dom)(dom.unit, cap, dom.lowest, dom.granularity, dom.physical, dom.scale)
+            stated = pipeline_domains.get(dname) or {}
+            cap = int(stated.get("capacity", 0))
+            domains[dname] = type(dom)(dom.unit, cap, dom.lowest, dom.granularity, dom.physical, int(stated.get("page_bytes", dom.scale)))
     for name, cl in claims.items():
         dom = domains[cl["domain"]]
         b = z3.Int(name)
@@ -70,8 +71,11 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         # reference places 24 scale columns at [128, 152), pipec/src/pipec2/solve.py)
         ext_g = ext
         ext_exprs[name] = ext_g
-        add(b >= dom.lowest, "L-BUDGET", f"claims.{name}.base")
-        add(b + ext_g <= dom.capacity + dom.lowest, "L-BUDGET", f"claims.{name}.extent")
+        # a claim that cannot be placed inside its domain is a placement failure like any other: the reference
+        # tracks the capacity of a domain under L-OVERLAP, path solve.capacity.<domain> (pipec/src/pipec2/solve.py);
+        # L-BUDGET is kept for a solve that runs out of its allowance
+        add(b >= dom.lowest, "L-OVERLAP", f"solve.capacity.{dom.physical}")
+        add(b + ext_g <= dom.capacity + dom.lowest, "L-OVERLAP", f"solve.capacity.{dom.physical}")
         align = max(cl.get("align", 1), gran)
         if align > 1:
             add(b % align == 0, "L-ALIGN", f"claims.{name}.align")
@@ -87,6 +91,17 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
     # pinned claims (a forced or absolute base) and the small domains keep pairwise exclusion.
     names = sorted(claims)
 
+    def may_share(a, bname):
+        """Two claims that live in phases the pipeline declares exclusive are never live together: they
+        may occupy the same space (the reference's phase lifetimes, docs/reference/annotations.md:294-300)."""
+        la, lb = claims[a].get("lifetime", "kernel"), claims[bname].get("lifetime", "kernel")
+        if not (isinstance(la, str) and isinstance(lb, str) and la.startswith("phase:") and lb.startswith("phase:")):
+            return False
+        x, y = la[len("phase:"):], lb[len("phase:"):]
+        from fnmatch import fnmatchcase
+        return x != y and any((fnmatchcase(x, p) and fnmatchcase(y, q)) or (fnmatchcase(x, q) and fnmatchcase(y, p))
+                              for p, q in exclusive)
+
     def span(n):
         d = domains[claims[n]["domain"]]
         return base_vars[n] * d.scale, (base_vars[n] + ext_exprs[n]) * d.scale
@@ -97,7 +112,8 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
 
     for phys in sorted({d.physical for d in domains.values()}):
         members = [n for n in names if domains[claims[n]["domain"]].physical == phys]
-        pinned = [n for n in members if n in forced or "absolute_base" in claims[n]]
+        pinned = [n for n in members if n in forced or "absolute_base" in claims[n] or
+                  str(claims[n].get("lifetime", "kernel")).startswith("phase:")]
         free = [n for n in members if n not in pinned]
         if phys == "smem" and len(free) > 2:
             byte_align = lambda n: max(claims[n].get("align", 1), 1) * domains[claims[n]["domain"]].scale
@@ -106,12 +122,13 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
                 add(span(prev)[1] <= span(nxt)[0], "L-OVERLAP", f"claims.{prev}~{nxt}")
             for a in pinned:
                 for bname in members:
-                    if bname != a and (bname not in pinned or a < bname):
+                    if bname != a and (bname not in pinned or a < bname) and not may_share(a, bname):
                         exclude(a, bname)
         else:
             for i, a in enumerate(members):
                 for bname in members[i + 1:]:
-                    exclude(a, bname)
+                    if not may_share(a, bname):
+                        exclude(a, bname)
 
     # warp claims tile [0, total) exactly
     warp_claims = [n for n in names if claims[n]["domain"] == "warp"]

@@ -112,3 +112,44 @@ def test_hello_callable_links_as_the_reference_links_it():
     from pipelink_b200.pipec2 import codegen
     stub = codegen.binding_stub(fe["bindings"], [call["trampoline"]])
     assert 'extern "C" __device__ float pipelink_call_scale(float a0) { return hello_scale(a0); }' in stub
+
+
+# ---------------------------------------------------------------- examples/profile-consumer
+PROFILE_CONSUMER = json.loads((Path(__file__).parent / "golden" / "reference_profile_consumer.json").read_text())
+
+
+@pytest.mark.parametrize("name", sorted(PROFILE_CONSUMER["cases"]))
+def test_profile_consumer_ends_as_the_reference_ends_it(name):
+    """Three stages (a scheduler and two instructions) that hand a shared-memory page over through a
+    named barrier and a grid-scoped counter; the pages are claims of a pipeline-defined page domain
+    living in mutually exclusive phases, so they may share page 1. The manifests come from the
+    reference's annotation pass; tests/golden/make_reference_profile_consumer.py recorded what the
+    reference's front end does with the shipped pipeline description and with four one-line changes."""
+    from pipelink_b200.pipec2.model import PipeLinkError
+    case = PROFILE_CONSUMER["cases"][name]
+    manifests, doc, want = copy.deepcopy(PROFILE_CONSUMER["manifests"]), copy.deepcopy(case["pipeline"]), case["reference"]
+    try:
+        for m in manifests:
+            schema.validate_manifest(m)
+        schema.validate_pipeline(doc)
+        fe = linker.front_end(manifests, doc["pipeline"])
+    except PipeLinkError as err:
+        assert "failures" in want, f"the reference links this; here: {err}"
+        assert sorted({f.clause_id for f in err.failures}) == sorted({f["clause"] for f in want["failures"]})
+        return
+    assert "failures" not in want
+    assert 32 * sum(w for _, w, _ in fe["role_warps"].values()) == want["threads"]
+    assert fe["solver"]["high_water"]["smem"] == want["dyn_smem_bytes"]
+    warp_map = {role: [fe["bindings"][h][0] + off, fe["bindings"][h][0] + off + warps] for role, (h, warps, off) in fe["role_warps"].items()}
+    assert warp_map == want["warp_map"]
+    # every claim where the reference puts it, in the reference's units (pages and barrier slots in bytes)
+    placed = {}
+    for domain, ivs in fe["intervals"].items():
+        scale = linker.profile_scale(fe["profile"], doc["pipeline"], domain)
+        for iv in ivs:
+            placed[iv["handle"]] = [iv["lo"] * scale, iv["hi"] * scale]
+    for ivs in want["intervals"].values():
+        for handle, lo, hi in ivs:
+            assert placed[handle] == [lo, hi], handle
+    assert [e["named_barrier"] for e in fe["expansions"] if e["kind"] == "named_barrier"] == want["named_barrier"]
+    assert [e["counter"] for e in fe["expansions"] if e["kind"] == "counter"] == want["counter"]
