@@ -124,17 +124,24 @@ def profile_scale(profile, pipe, domain):
 
 
 def _params_layout(manifests, profile):
-    entries, off = [], 0
-    for m in manifests:
+    """Where each stage's parameter block sits in the kernel's parameter bytes: stages in the order of
+    their ids, each block on max(target alignment, its own alignment), the total rounded up to the
+    largest alignment seen (the reference's rule, pipec/src/pipec2/dispatchgen.py:75-108, so the same
+    packages give the same layout under either driver)."""
+    base = profile["param_align"]
+    entries, cursor, aggregate = [], 0, base
+    for m in sorted(manifests, key=lambda m: m["stage"]["id"]):
         p = m.get("params", {"bytes": 0, "align": 1})
         align = max(p.get("align", 1), 1)
-        off = (off + align - 1) // align * align
+        effective = max(base, align)
+        off = (cursor + effective - 1) // effective * effective
         entries.append([m["stage"]["id"], off, p.get("bytes", 0), align])
-        off += p.get("bytes", 0)
-    total = (off + profile["param_align"] - 1) // profile["param_align"] * profile["param_align"]
+        cursor = off + p.get("bytes", 0)
+        aggregate = max(aggregate, align)
+    total = (cursor + aggregate - 1) // aggregate * aggregate if entries else 0
     if total > profile["param_limit_bytes"]:
         raise PipeLinkError(ClauseFailure("L-PARAMS", "params.total_bytes", f"{total} bytes exceed the {profile['param_limit_bytes']}-byte limit"))
-    return {"total_bytes": total, "align": profile["param_align"], "entries": entries}
+    return {"total_bytes": total, "align": aggregate, "entries": entries}
 
 
 def front_end(manifests, pipe):
@@ -303,7 +310,7 @@ def link(pipeline_path, out_dir, *, device_link=True):
     smem_hw = solver["high_water"].get("smem", 0)
     generated = {
         "binding_stub.cu": codegen.binding_stub(bindings, [e["trampoline"] for e in expansions if "trampoline" in e]),
-        "dispatch.cu": codegen.dispatch(threads=threads, params_total=params["total_bytes"], roles=roles,
+        "dispatch.cu": codegen.dispatch(threads=threads, params_total=params["total_bytes"], params_align=params["align"], roles=roles,
                                         expansions=expansions, bindings=bindings, tmem_columns=tmem_cols,
                                         tmem_slot=bindings.get(TMEM_SLOT_HANDLE, [0])[0], tmem_warp=roles[0]["warp_lo"],
                                         cta_group=cta_group, cluster=cluster, reg_groups=solver.get("reg_groups", []),

@@ -36,4 +36,9 @@ SM_100A = {
 # B300's profile: the same capacities (pipec/src/pipec2/profile.py:141-149). Packages stamped for it are
 # checked and solved here like any other; their device link needs a toolkit that knows the architecture.
 SM_103A = dict(SM_100A, name="sm_103a", lto_arch="lto_103", gencode=("compute_103a", "lto_103a"), sm="sm_103a")
-PROFILES = {"sm_100a": SM_100A, "sm_103a": SM_103A}
+# Hopper: no tensor memory, no CTA pairs (pipec/src/pipec2/profile.py, SM_90A). Kept so that the reference's Hopper
+# packages can be CHECKED and SOLVED by this driver (its `examples/hopper-gemm-split`); nothing is built for it.
+SM_90A = dict(SM_100A, name="sm_90a", lto_arch="lto_90a", gencode=("compute_90a", "lto_90a"), sm="sm_90a",
+              domains={k: v for k, v in SM_100A["domains"].items() if k != "tmem"},
+              caps=dict(SM_100A["caps"], cta_group_legal=(1,)))
+PROFILES = {"sm_100a": SM_100A, "sm_103a": SM_103A, "sm_90a": SM_90A}

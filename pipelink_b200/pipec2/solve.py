@@ -184,7 +184,21 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
                    launch_regs * launch_threads <= caps.get("regs_per_sm", 65536), pool <= launch_regs * launch_threads),
             "L-REGS", path)
     elif any(h.get("class") == "regs" for h in handles.values()):
-        add(z3.BoolVal(False), "L-REGS", "solve.register_groups")
+        # no role asks for registers of its own: the one register handle an image may then carry is the
+        # launch allocation itself (owner reg_group:launch): one count for every thread, taken from the
+        # handle's values, as large as the register file allows for the launch's threads
+        launch = [n for n, h in handles.items() if h.get("class") == "regs"]
+        h = handles[launch[0]]
+        launch_threads = 32 * sum(rw[1] for rw in (role_warps or {}).values())
+        if len(launch) != 1 or h.get("owner") != "reg_group:launch" or h.get("domain") != "regs" or not launch_threads:
+            add(z3.BoolVal(False), "L-REGS", "solve.register_groups")
+        else:
+            v = z3.Int(launch[0])
+            regs_vars[launch[0]] = v
+            values = [forced[launch[0]]] if launch[0] in forced else sorted(h["values"])
+            add(z3.Or([v == x for x in values]), "L-REGS", "solve.register_groups")
+            add(z3.And(v >= caps.get("regs_min", 24), v <= caps.get("regs_max", 255),
+                       v * launch_threads <= caps.get("regs_per_sm", 65536)), "L-REGS", "solve.register_groups")
 
     for expr, _, _ in cons:
         opt.add(expr)
@@ -241,6 +255,10 @@ def solve(claims: dict, handles: dict, profile: dict, *, depth_priority=(), forc
         tier["status"] = "optimal"
     hw_vals = {phys: val(hw) for phys, hw in highwater.items()}
     info = {"tiers": tiers, "high_water": hw_vals, "engine": f"z3 {z3.get_version_string()} Optimize(lex)"}
+    if not reg_claims and regs_vars:
+        (n, v), = regs_vars.items()
+        bindings[n] = [val(v), "forced" if n in forced else "solved"]
+        info["launch_regs"] = val(v)
     if reg_claims:
         for n, v in regs_vars.items():
             bindings[n] = [val(v), "forced" if n in forced else "solved"]

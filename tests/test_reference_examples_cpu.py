@@ -153,3 +153,40 @@ def test_profile_consumer_ends_as_the_reference_ends_it(name):
             assert placed[handle] == [lo, hi], handle
     assert [e["named_barrier"] for e in fe["expansions"] if e["kind"] == "named_barrier"] == want["named_barrier"]
     assert [e["counter"] for e in fe["expansions"] if e["kind"] == "counter"] == want["counter"]
+
+
+# ---------------------------------------------------------------- examples/hopper-gemm-split
+HOPPER = json.loads((Path(__file__).parent / "golden" / "reference_hopper_gemm_split.json").read_text())
+
+
+@pytest.mark.parametrize("cell", sorted(HOPPER["cells"]))
+def test_hopper_gemm_split_solves_as_the_reference_solves_it(cell):
+    """The reference's split GEMM (load, MMA and one of three epilogue owners; Hopper device code that
+    this library does not build): its manifests, emitted by its annotation pass, and the four pipeline
+    descriptions of its build.py are CHECKED and SOLVED here, to the reference's ring depth, launch
+    shape, register allocation, warp map, barrier arrival counts and the high-water mark of shared
+    memory (tests/golden/make_reference_hopper_gemm_split.py recorded both sides of the comparison)."""
+    rec = HOPPER["cells"][cell]
+    manifests = [copy.deepcopy(HOPPER["manifests"][n]) for n in rec["members"]]
+    doc, want = copy.deepcopy(rec["pipeline"]), rec["reference"]
+    for m in manifests:
+        schema.validate_manifest(m)
+    schema.validate_pipeline(doc)
+    fe = linker.front_end(manifests, doc["pipeline"])
+    assert {h: fe["bindings"][h][0] for h in want["depths"]} == want["depths"]
+    warp_map = {role: [fe["bindings"][h][0] + off, fe["bindings"][h][0] + off + warps] for role, (h, warps, off) in fe["role_warps"].items()}
+    assert warp_map == want["warp_map"]
+    assert 32 * sum(w for _, w, _ in fe["role_warps"].values()) == want["threads"]
+    assert fe["solver"]["high_water"]["smem"] == want["dyn_smem_bytes"]
+    assert fe["solver"].get("launch_regs") == want["regs_cap"]
+    assert fe["params"]["total_bytes"] == want["params_total_bytes"]
+    # every claim as large as the reference makes it (where inside shared memory is the solver's choice
+    # among equally good layouts); barrier claims are counted in slots here and in bytes there
+    mine = {iv["handle"]: (iv["hi"] - iv["lo"]) * linker.profile_scale(fe["profile"], doc["pipeline"], d)
+            for d, ivs in fe["intervals"].items() for iv in ivs}
+    for ivs in want["intervals"].values():
+        for handle, lo, hi in ivs:
+            assert mine[handle] == hi - lo, handle
+    for e in fe["expansions"]:
+        ch = want["channels"][e["channel"]]
+        assert (e["full"]["count"], e["empty"]["count"], e["full"]["tx_bytes"]) == (ch["arrive_full"], ch["arrive_empty"], ch["tx_bytes"])
