@@ -163,6 +163,20 @@ def test_cli_verbs(linked, capsys):
     assert "L-PROTO" in capsys.readouterr().out
     assert cli.main(["inspect", str(out / "mma.plink")]) == 0
     assert "gemm.mma" in capsys.readouterr().out
+    # the flags the reference's example scripts pass (examples/contract-gallery/check.py:57-90)
+    assert cli.main(["clauses", "--json"]) == 0
+    assert set(json.loads(capsys.readouterr().out)) >= {"L-PROTO", "L-TOPO", "L-HANDLE", "L-PARAMS", "L-PHASE"}
+    assert cli.main(["inspect", str(out / "mma.plink"), "--json"]) == 0
+    assert json.loads(capsys.readouterr().out)["stage"]["id"] == "gemm.mma"
+    assert cli.main(["link", str(out / "pipeline.json"), "--out-dir", str(out / "cli_link"), "--no-device-link"]) == 0
+    assert json.loads(capsys.readouterr().out)["threads"] == 192
+    broken = json.loads((out / "pipeline.json").read_text())
+    broken["pipeline"]["topology"]["persistent"] = not broken["pipeline"]["topology"].get("persistent", False)
+    (out / "broken.json").write_text(json.dumps(broken))
+    assert cli.main(["link", str(out / "broken.json"), "--out-dir", str(out / "cli_broken"), "--no-device-link"]) == 1
+    import re
+    # the structured prefix their checker reads clause tokens from, never the prose
+    assert re.findall(r"(?:^pipec2: |; )\[([A-Z][A-Z0-9]*(?:-[A-Z0-9]+)*)\] ", capsys.readouterr().err, re.M) == ["L-TOPO"] * 3
 
 
 def test_config0_oracle_is_finite_and_shaped():
