@@ -29,8 +29,8 @@
 #define PL_CALL(channel, fn, direction, ...) static_assert(true, "")
 #define PL_TYPE(T) static_assert(true, "")
 #define PL_ENDPOINT(name, ...) static_assert(true, "")
-#define PL_CLAIM(domain, handle, extent, align) static_assert(true, "")
-#define PL_CLAIM_EX(domain, handle, extent, align, key, value) static_assert(true, "")
+#define PL_CLAIM(...) static_assert(true, "")
+#define PL_CLAIM_EX(...) static_assert(true, "")
 #define PL_CLAIM_WARPS(handle, role, warps, align) static_assert(true, "")
 #define PL_CLAIM_REGS(handle, role, group, regs) static_assert(true, "")
 #define PL_TOPOLOGY(...) static_assert(true, "")
@@ -49,6 +49,7 @@
 #endif
 
 #include "tensor_source.h"
+#include <array>
 #include <cstddef>
 #include <cstdio>
 #include <initializer_list>
@@ -170,12 +171,139 @@ struct arrivals {
   }
 };
 
-// PL_ENDPOINT's builder: one end of a channel (mbarrier ring or grid-scoped counter)
+// ---- the reference's spelling of the same declarations (docs/reference/annotations.md "Endpoints and
+// protocols", "Topology and scheduling", "Resource claims"): a stage source written against its header
+// packs here unchanged. Each type only gathers what it is given; the manifest text is made by to_json().
+struct handle { const char* name; explicit handle(const char* n) : name(n) {} };
+struct fixed { int n; explicit fixed(int value) : n(value) {} };
+
+struct affine {          // pl::affine{shape, stride, elem_bits}[.swizzle(B, M, S)]
+  std::vector<int> shape, stride;
+  int elem_bits, sw_b = 0, sw_m = 0, sw_s = 0;
+  affine(std::initializer_list<int> sh, std::initializer_list<int> st, int bits) : shape(sh), stride(st), elem_bits(bits) {}
+  affine& swizzle(int b, int m, int s_) { sw_b = b; sw_m = m; sw_s = s_; return *this; }
+  json to_json() const {
+    json l = json::object();
+    l["encoding"] = json("pl-layout-v2");
+    l["elem_bits"] = json(elem_bits);
+    json sh = json::array(), st = json::array();
+    for (int v : shape) sh.push(json(v));
+    for (int v : stride) st.push(json(v));
+    l["shape"] = sh;
+    l["stride"] = st;
+    if (sw_b != 0) {
+      json sw = json::object();
+      sw["B"] = json(sw_b);
+      sw["M"] = json(sw_m);
+      sw["S"] = json(sw_s);
+      l["swizzle"] = sw;
+    }
+    return l;
+  }
+};
+struct tmem { int lanes_lo, lanes_hi, cols, elem_bits; };   // pl::tmem{lanes_lo, lanes_hi, cols, elem_bits}
+
+struct arrive {          // pl::arrive{"role", 2} or pl::arrive{"role", "threads(role)"}
+  std::string by;
+  json count;
+  arrive(const char* role, int n) : by(role), count(n) {}
+  arrive(const char* role, const char* expression) : by(role), count(expression) {}
+};
+struct side {            // pl::side{slots handle, arrive, tx_bytes}
+  std::string slots;
+  arrive who;
+  long long tx_bytes;
+  side(const char* slots_handle, const arrive& a, long long tx) : slots(slots_handle), who(a), tx_bytes(tx) {}
+  json to_json() const {
+    json a = json::object();
+    a["by"] = json(who.by);
+    a["count"] = who.count;
+    json j = json::object();
+    j["slots"] = json(slots);
+    j["arrive"] = a;
+    j["tx_bytes"] = json(tx_bytes);
+    return j;
+  }
+};
+struct init {            // pl::init{owner, phase, materializer[, warp]}
+  const char* owner;
+  int phase;
+  const char* materializer;
+  int warp;
+  init(const char* o, int ph, const char* m, int w = -1) : owner(o), phase(ph), materializer(m), warp(w) {}
+};
+struct mbarrier {        // pl::mbarrier{full, empty, init}
+  side full, empty;
+  init start;
+  mbarrier(const side& f, const side& e, const init& i) : full(f), empty(e), start(i) {}
+  json to_json() const {
+    json i = json::object();
+    if (start.owner != nullptr) i["owner"] = json(start.owner);
+    i["phase"] = json(start.phase);
+    i["materializer"] = json(start.materializer);
+    if (start.warp >= 0) i["warp"] = json(start.warp);
+    json p = json::object();
+    p["kind"] = json("mbarrier");
+    p["full"] = full.to_json();
+    p["empty"] = empty.to_json();
+    p["init"] = i;
+    p["release"] = json("once-per-acquire");
+    return p;
+  }
+};
+struct named_barrier { const char* id; int count; };        // pl::named_barrier{id handle, threads}
+struct counter {                                             // pl::counter{slot[, release, acquire]}: grid scope
+  const char* slot;
+  const char* release;
+  const char* acquire;
+  counter(const char* s, const char* r = "red.release.gpu", const char* a = "ld.acquire.gpu") : slot(s), release(r), acquire(a) {}
+};
+struct counter_sys : counter {                               // the same at system scope
+  counter_sys(const char* s, const char* r = "red.release.sys", const char* a = "ld.acquire.sys") : counter(s, r, a) {}
+};
+
+// PL_ENDPOINT's builder: one end of a channel (mbarrier ring, named barrier or counter)
 class endpoint {
  public:
-  endpoint(const char* direction, const char* owner_role) {
-    j_["direction"] = json(direction);
-    j_["owner_role"] = owner_role ? json(owner_role) : json();
+  // (direction, role): this header's own spelling; ("name", direction[, "role"]): the reference's
+  endpoint(const char* first, const char* second, const char* role = nullptr) {
+    const std::string a = first;
+    if (a == produce || a == consume) {
+      j_["direction"] = json(first);
+      j_["owner_role"] = second ? json(second) : json();
+    } else {
+      j_["direction"] = json(second);
+      j_["owner_role"] = role ? json(role) : json();
+    }
+    j_["binds"] = json::object();
+  }
+  endpoint& layout(const affine& a) { j_["layout"] = a.to_json(); return *this; }
+  endpoint& layout(const tmem& t) { return layout_tmem(t.elem_bits, t.lanes_lo, t.lanes_hi, t.cols); }
+  endpoint& ring(const handle& h, long long stage_stride_bytes) { return ring(depth::handle(h.name), stage_stride_bytes); }
+  endpoint& ring(const fixed& f, long long stage_stride_bytes) { return ring(depth::fixed(f.n), stage_stride_bytes); }
+  endpoint& protocol(const ::pl::mbarrier& m) { j_["protocol"] = m.to_json(); return *this; }
+  endpoint& protocol(const named_barrier& b) {
+    json p = json::object();
+    p["kind"] = json("named_barrier");
+    p["id"] = json(b.id);
+    p["count"] = json(b.count);
+    j_["protocol"] = p;
+    return *this;
+  }
+  endpoint& protocol(const ::pl::counter& c) {
+    json p = json::object();
+    p["kind"] = json("counter");
+    p["slot"] = json(c.slot);
+    p["release"] = json(c.release);
+    p["acquire"] = json(c.acquire);
+    j_["protocol"] = p;
+    return *this;
+  }
+  endpoint& exports(std::initializer_list<const char*> fns) {
+    json e = json::array();
+    for (const char* f : fns) e.push(json(f));
+    j_["exports"] = e;
+    return *this;
   }
   endpoint& space(const char* s) { j_["space"] = json(s); return *this; }
   endpoint& scope(const char* s) { j_["scope"] = json(s); return *this; }
@@ -280,12 +408,45 @@ class endpoint {
   json j_ = json::object();
 };
 
+struct launch {          // pl::launch{x_multiple_of, {max x, y, z}}
+  int x_multiple_of;
+  std::array<int, 3> max;
+  launch(int multiple = 1, std::array<int, 3> m = {1, 1, 1}) : x_multiple_of(multiple), max(m) {}
+};
+struct dynamic_t {};
+constexpr dynamic_t dynamic{};
+struct cluster {         // pl::cluster{{x, y, z} | pl::dynamic, pl::launch{...}}
+  bool is_dynamic;
+  std::array<int, 3> compiled;
+  launch at_launch;
+  cluster(std::array<int, 3> c, const launch& l) : is_dynamic(false), compiled(c), at_launch(l) {}
+  cluster(dynamic_t, const launch& l) : is_dynamic(true), compiled{1, 1, 1}, at_launch(l) {}
+};
+
 class topology {
  public:
+  // pl::topology{cta_group, cluster, persistent, scheduler, multicast}: the reference's spelling
+  topology(int group, const ::pl::cluster& c, bool is_persistent, const char* sched, std::initializer_list<const char*> multicast) {
+    json mc = json::array();
+    for (const char* m : multicast) mc.push(json(m));
+    j_["multicast"] = mc;
+    j_["persistent"] = json(is_persistent);
+    j_["scheduler"] = json(sched);
+    cta_group(group);
+    json l = json::object();
+    l["x_multiple_of"] = json(c.at_launch.x_multiple_of);
+    l["max"] = json::list({c.at_launch.max[0], c.at_launch.max[1], c.at_launch.max[2]});
+    json cl = json::object();
+    cl["compiled"] = c.is_dynamic ? json("dynamic") : json::list({c.compiled[0], c.compiled[1], c.compiled[2]});
+    cl["launch"] = l;
+    j_["cluster"] = cl;
+  }
   topology() {
     j_["multicast"] = json::array();
     j_["persistent"] = json(false);
     j_["scheduler"] = json("static");
+    cta_group(1);
+    cluster(1, 1, 1);
   }
   topology& cta_group(int n) {
     json g = json::object();
@@ -317,6 +478,8 @@ struct registry {
   json endpoints = json::array(), claims = json::array(), variants = json::array();
   json topology, params, hints = json::object();
   json strong = json::array();
+  std::vector<std::pair<std::string, int>> role_warps;   // every PL_ROLE, in order
+  std::vector<std::string> warp_claimed;                // roles some warp claim names
   int errors = 0;
   static registry& get() { static registry r; return r; }
   void fail(const std::string& what) { std::fprintf(stderr, "stage.hpp: %s\n", what.c_str()); ++errors; }
@@ -365,6 +528,7 @@ struct reg_role {
     role["warps"] = json(warps);
     r.roles[name] = role;
     r.strong.push(json(entry));
+    r.role_warps.push_back({name, warps});
   }
 };
 
@@ -395,6 +559,67 @@ struct reg_claim {
   }
 };
 
+// pl::claim(handle, domain).extent(...).align(...).lifetime(...).at(...).roles({...}): the reference's builder
+class claim {
+ public:
+  claim(const char* handle, const char* domain) : domain_(domain) {
+    j_["handle"] = json(handle);
+    j_["domain"] = json(domain);
+    j_["extent"] = units(0).to_json();
+    j_["align"] = json(1);
+    j_["lifetime"] = json("kernel");
+  }
+  claim& extent(long long constant, std::initializer_list<std::pair<const char*, long long>> per_handle = {}) {
+    ::pl::extent e = units(constant);
+    for (const auto& kv : per_handle) e.per_handle[kv.first] += kv.second;
+    j_["extent"] = e.to_json();
+    return *this;
+  }
+  claim& align(int a) { j_["align"] = json(a); return *this; }
+  claim& lifetime(const char* l) { j_["lifetime"] = json(l); return *this; }
+  claim& at(long long base) { j_["absolute_base"] = json(base); return *this; }
+  claim& roles(std::initializer_list<const char*> names) {
+    json r = json::array();
+    for (const char* n : names) { r.push(json(n)); roles_.push_back(n); }
+    j_["roles"] = r;
+    return *this;
+  }
+  const json& to_json() const { return j_; }
+  void note_warps() const {          // a warp claim places the roles it names
+    if (domain_ == "warp") for (const std::string& n : roles_) registry::get().warp_claimed.push_back(n);
+  }
+
+ private:
+  json j_ = json::object();
+  std::string domain_;
+  std::vector<std::string> roles_;
+};
+
+struct reg_claim_any {
+  static std::string bare(const char* token) {     // a stringified macro argument: quotes stay when the author wrote them
+    std::string t = token;
+    if (t.size() >= 2 && t.front() == '"' && t.back() == '"') t = t.substr(1, t.size() - 2);
+    return t;
+  }
+  // PL_CLAIM(domain, handle, pl::units(n) | pl::per(...), align): this header's own spelling
+  reg_claim_any(const char* domain, const char* handle, const ::pl::extent& e, int align) {
+    reg_claim(bare(domain).c_str(), bare(handle).c_str(), e, align);
+  }
+  // PL_CLAIM("handle", "domain", extent, align[, lifetime[, role...]]): the reference's
+  template <class... Roles>
+  reg_claim_any(const char* handle, const char* domain, long long n, int align, const char* lifetime = "kernel", Roles... role_names) {
+    claim c(bare(handle).c_str(), bare(domain).c_str());
+    c.extent(n).align(align).lifetime(lifetime);
+    if (sizeof...(Roles) > 0) c.roles({role_names...});
+    c.note_warps();
+    registry::get().claims.push(c.to_json());
+  }
+  explicit reg_claim_any(const claim& c) {   // PL_CLAIM_EX(pl::claim(...)...)
+    c.note_warps();
+    registry::get().claims.push(c.to_json());
+  }
+};
+
 struct reg_warps {
   reg_warps(const char* handle, const char* role, int warps, int align) {
     json c = json::object();
@@ -404,6 +629,7 @@ struct reg_warps {
     c["align"] = json(align);
     c["lifetime"] = json("kernel");
     c["roles"] = json::list({role});
+    registry::get().warp_claimed.push_back(role);
     registry::get().claims.push(c);
   }
 };
@@ -447,6 +673,24 @@ inline int emit_main() {
   if (r.params.is_null()) r.fail("no PL_PARAMS / PL_NO_PARAMS / PL_PARAMS_OPAQUE");
   if (r.topology.is_null()) r.topology = topology().to_json();
   if (r.errors != 0) return 1;
+  // a role no claim places gets a warp claim of its own, handle pipelink_<role>_warps (what the reference's
+  // pass adds: its hello-callable pipeline declares pipelink_call_warps for the role `call`)
+  for (const auto& role : r.role_warps) {
+    bool claimed = false;
+    for (const std::string& who : r.warp_claimed) claimed = claimed || who == role.first;
+    if (!claimed) {
+      json c = json::object();
+      c["domain"] = json("warp");
+      c["handle"] = json("pipelink_" + role.first + "_warps");
+      c["extent"] = units(role.second).to_json();
+      c["align"] = json(1);
+      c["lifetime"] = json("kernel");
+      json roles = json::array();
+      roles.push(json(role.first));
+      c["roles"] = roles;
+      r.claims.push(c);
+    }
+  }
   if (r.variants.dump() == "[]") reg_variant(0, json::object());
   json stage = r.stage;
   stage["entry_abi"] = json("v2");
@@ -493,14 +737,18 @@ struct signature<R(A...)> {
 
 // one side of a call channel: the caller's trampoline (produce, from a role) or the provided function (consume)
 struct reg_call {
+  // one side of a call channel. The protocol carries the C declaration of this side's function, spelled
+  // from its type: extern "C" __device__ float hello_scale(float);  (the digest is added by the packer)
   reg_call(const char* channel, const char* fn, const std::string& sig, const char* direction, const char* who,
            const char* export_name = nullptr) {
     const bool caller = std::string(direction) == produce;
+    const size_t paren = sig.find('(');
+    const std::string decl = "extern \"C\" __device__ " + sig.substr(0, paren) + " " + fn + sig.substr(paren) + ";";
     json proto = json::object();
     proto["kind"] = json("call");
     proto["export"] = json(caller ? (export_name ? export_name : channel) : who);
     proto["signature"] = json(sig);
-    proto["symbol"] = json(fn);
+    proto["decl"] = json(decl);
     json e = json::object();
     e["name"] = json(channel);
     e["direction"] = json(direction);
@@ -509,12 +757,26 @@ struct reg_call {
     e["scope"] = json("cta");
     e["proxy"] = json("generic");
     json tile = json::object();
-    tile["dtype"] = json("s32");
+    tile["dtype"] = json("u64");
     tile["shape"] = json::list({1});
     e["tile"] = tile;
+    json layout = json::object();
+    layout["encoding"] = json("pl-layout-v2");
+    layout["elem_bits"] = json(64);
+    json one = json::array();
+    one.push(json::list({1}));
+    layout["shape"] = one;
+    layout["stride"] = one;
+    e["layout"] = layout;
     e["protocol"] = proto;
     e["binds"] = json::object();
-    registry::get().endpoints.push(e);
+    registry& r = registry::get();
+    r.endpoints.push(e);
+    if (!caller) {      // the provided side restates its declaration in the stage's export record
+      if (r.exports[who].is_null()) r.exports[who] = json::object();
+      r.exports[who]["symbol"] = json(fn);
+      r.exports[who]["decl"] = json(decl);
+    }
   }
 };
 
@@ -570,9 +832,13 @@ constexpr bool is_role_entry = std::is_same<F, void(const void*, unsigned)>::val
 #define PL_CALL(channel, fn, direction, ...) \
   PL_REG(reg_call)(#channel, #fn, ::pl::signature<decltype(fn)>::get(), direction, __VA_ARGS__)
 #define PL_ENDPOINT(name, ...) PL_REG(reg_endpoint){#name, __VA_ARGS__}
-#define PL_CLAIM(domain, handle, extent, align) PL_REG(reg_claim)(#domain, #handle, extent, align)
-#define PL_CLAIM_EX(domain, handle, extent, align, key, value) \
+#define PL_CLAIM(a, b, ...) PL_REG(reg_claim_any)(#a, #b, __VA_ARGS__)
+// six arguments: (domain, handle, extent, align, key, value), this header's own form; one: a pl::claim builder
+#define PL_CLAIM_EX6(domain, handle, extent, align, key, value) \
   PL_REG(reg_claim)(#domain, #handle, extent, align, key, ::pl::json(value))
+#define PL_CLAIM_EX1(builder) PL_REG(reg_claim_any)(builder)
+#define PL_CLAIM_EX_PICK(a1, a2, a3, a4, a5, a6, which, ...) which
+#define PL_CLAIM_EX(...) PL_CLAIM_EX_PICK(__VA_ARGS__, PL_CLAIM_EX6, x, x, x, x, PL_CLAIM_EX1, x)(__VA_ARGS__)
 #define PL_CLAIM_WARPS(handle, role, warps, align) PL_REG(reg_warps)(#handle, #role, warps, align)
 #define PL_CLAIM_REGS(handle, role, group, regs) PL_REG(reg_regs)(#handle, #role, #group, regs)
 #define PL_TOPOLOGY(...) PL_REG(reg_topology){__VA_ARGS__}   // braces: no vexing parse of pl::topology()

@@ -29,6 +29,7 @@ CLAUSES = {
     "T-LOWER": "the certified program lowers to an adapter for the site it runs at",
     "P-ANNOTATION": "a unit's annotations state exactly one stage, one parameter block and at most one topology",
     "P-COMPILE": "the stage payload compiles for the target profile",
+    "P-INIT": "a barrier ring's declared initialising warp belongs to its owner role",
     "P-CONTAINER": "the package container is well formed",
     "P-SYM": "stage symbols carry the stage's symbol prefix",
 }

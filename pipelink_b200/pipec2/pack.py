@@ -32,25 +32,55 @@ ABI = {"schema": "3.0", "target": {"toolkit": "cuda-12.9", "math": {"ftz": False
 
 
 def emit_manifest(source, includes=(), defines=()) -> dict:
-    """Run the unit's host projection: g++ -DPIPELINK_EMIT, execute, parse what it prints."""
+    """Run the unit's host projection: compile with -DPIPELINK_EMIT, execute, parse what it prints.
+    Units of this repo keep their device code behind #ifndef PIPELINK_EMIT and compile as plain C++ in
+    a second; a unit that does not (one written for the reference's toolchain, device bodies in the
+    open) is compiled as CUDA by nvcc instead."""
     source = Path(source)
     with tempfile.TemporaryDirectory() as tmp:
         exe = Path(tmp) / "emit"
-        cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-x", "c++", "-DPIPELINK_EMIT", "-I", str(INCLUDE),
-               "-I", str(CUDA_INCLUDE), *[f"-I{i}" for i in includes], *[f"-D{d}" for d in defines], str(source), "-o", str(exe)]
+        common = ["-DPIPELINK_EMIT", "-I", str(INCLUDE), *[f"-I{i}" for i in includes], *[f"-D{d}" for d in defines]]
+        cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-x", "c++", "-I", str(CUDA_INCLUDE), *common, str(source), "-o", str(exe)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
-            fail("P-COMPILE", f"{source}:emit", proc.stderr[-2000:])
+            cuda = [jitlink.nvcc(), "-std=c++17", "-x", "cu", "-gencode", "arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr",
+                    *common, str(source), "-o", str(exe)]
+            second = subprocess.run(cuda, capture_output=True, text=True)
+            if second.returncode != 0:
+                fail("P-COMPILE", f"{source}:emit", (proc.stderr[-1500:] + "\n--- as CUDA ---\n" + second.stderr[-1500:]))
         run = subprocess.run([str(exe)], capture_output=True, text=True)
         if run.returncode != 0:
             fail("P-ANNOTATION", str(source), run.stderr.strip() or "the manifest pass failed")
     m = json.loads(run.stdout)
+    m["claims"].sort(key=lambda c: (c.get("handle", ""), c.get("domain", "")))     # claims in the order of their handles, as the reference writes them
+    _check_init_warps(m, source)
+    # a declaration travels with its digest (call protocols and the export records they restate)
+    for rec in [ep.get("protocol") or {} for ep in m.get("endpoints", [])] + list(m["stage"].get("exports", {}).values()):
+        if isinstance(rec.get("decl"), str):
+            rec["decl_sha256"] = hashlib.sha256(rec["decl"].encode()).hexdigest()
     params = m["params"]
     # the layout probe: what the compiler says about the block, member by member
     probe = json.dumps([params["type"], params["bytes"], params["align"],
                         [[x["name"], x["offset"], x["bytes"]] for x in params["members"]]])
     params["sha256_of_layout_probe"] = hashlib.sha256(probe.encode()).hexdigest()
     return m
+
+
+def _check_init_warps(m, source):
+    """P-INIT: a barrier ring whose `init` names the physical initialising warp must name one inside its
+    owner's warp claim, when that claim sits at an absolute base (docs/reference/annotations.md, pl::init)."""
+    placed = {}
+    for cl in m.get("claims", []):
+        if cl.get("domain") == "warp" and "absolute_base" in cl:
+            for role in cl.get("roles", []):
+                placed[role] = (cl["absolute_base"], cl["absolute_base"] + cl["extent"]["const"])
+    for i, ep in enumerate(m.get("endpoints", [])):
+        init = (ep.get("protocol") or {}).get("init") or {}
+        if "warp" in init and init.get("owner") in placed:
+            lo, hi = placed[init["owner"]]
+            if not lo <= init["warp"] < hi:
+                fail("P-INIT", f"$.endpoints[{i}].protocol.init.warp",
+                     f"warp {init['warp']} lies outside role {init['owner']!r}'s claim [{lo}, {hi})")
 
 
 def undefined_symbols(source, profile: dict, includes=(), defines=()) -> dict:

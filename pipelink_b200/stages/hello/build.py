@@ -38,7 +38,10 @@ def manifests() -> dict:
 
 def pipeline_spec(stages):
     return {"pipelink_abi": ABI,
-            "pipeline": {"name": "hello-callable", "stages": stages, "handles": {}, "phases": ["steady"], "exclusive": [],
+            # the caller's role claims its warps under the handle the annotation pass derives for it
+            "pipeline": {"name": "hello-callable", "stages": stages,
+                         "handles": {"pipelink_call_warps": {"class": "base", "binding": "bind", "domain": "warp", "owner": "claim:call"}},
+                         "phases": ["steady"], "exclusive": [],
                          "domains": {}, "depth_priority": [], "regs_priority": [], "forced_bindings": {},
                          "topology": {"persistent": False, "scheduler": "static"}}}
 

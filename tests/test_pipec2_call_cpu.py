@@ -24,12 +24,17 @@ def test_annotations_state_both_ends_of_the_call():
     ms = hb.manifests()
     provider, caller = ms["provider"], ms["caller"]
     assert provider["stage"]["roles"] == {} and provider["params"]["bytes"] == 0
-    assert provider["stage"]["exports"] == {"scale": {"symbol": "hello_scale"}}
+    assert provider["stage"]["exports"]["scale"]["symbol"] == "hello_scale"
     (pe,), (ce,) = provider["endpoints"], caller["endpoints"]
     assert pe["owner_role"] is None and pe["direction"] == "consume"      # a callee never names its caller's role
     assert ce["owner_role"] == "call" and ce["direction"] == "produce"
+    import hashlib
     for ep, symbol in ((pe, "hello_scale"), (ce, "pipelink_call_scale")):
-        assert ep["protocol"] == {"kind": "call", "export": "scale", "signature": "float(float)", "symbol": symbol}
+        decl = f'extern "C" __device__ float {symbol}(float);'       # the declaration, spelled from the function's type
+        assert ep["protocol"] == {"kind": "call", "export": "scale", "signature": "float(float)", "decl": decl,
+                                  "decl_sha256": hashlib.sha256(decl.encode()).hexdigest()}
+    assert provider["stage"]["exports"]["scale"]["decl"] == pe["protocol"]["decl"]
+    assert [c["handle"] for c in caller["claims"]] == ["pipelink_call_warps"]      # the role's own warp claim, derived
     assert caller["stage"]["roles"]["call"]["warps"] == 4
     assert caller["params"]["bytes"] == 24 and [m["name"] for m in caller["params"]["members"]] == ["input", "output", "count"]
 
@@ -48,7 +53,7 @@ def test_link_generates_the_trampoline_and_an_image(tmp_path):
     assert 'extern "C" __device__ float hello_scale(float);' in stub
     assert 'extern "C" __device__ float pipelink_call_scale(float a0) { return hello_scale(a0); }' in stub
     dispatch = (tmp_path / "link" / "generated" / "dispatch.cu").read_text()
-    assert "if (warp >= 0 && warp < 4) hello_call(p.bytes + 0, 0u);" in dispatch   # no warp claim: declaration order from warp 0
+    assert "if (warp >= 0 && warp < 4) hello_call(p.bytes + 0, 0u);" in dispatch
     assert r.threads == 128 and r.dyn_smem_bytes == 0
     regs, stack, spill = r.observed
     assert 0 < regs <= 64 and stack == 0 and spill == 0          # the call was inlined: no frame
