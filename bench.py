@@ -71,7 +71,7 @@ class ClockSampler:
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_power_cap,power.draw,enforced.power.limit,clocks_event_reasons.active")
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []
@@ -107,27 +107,51 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        mhz, mx, reasons = [], None, set()
+        mhz, mx, reasons, nearby, watts, limit, mask = [], None, set(), set(), [], None, 0
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         lines = self.lines
+        inside_times = None
         if self.t_begin is not None and self.t_end is not None:
             # samples taken while the timed steps ran; one sampling interval of slack on both sides
             inside = [l for l in lines if self.t_begin - 0.03 <= l[0] <= self.t_end + 0.03]
-            lines = inside or lines[-3:]
-        for _, line in lines:
+            inside_times = {l[0] for l in (inside or lines[-3:])}
+        for t, line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
+            timed = inside_times is None or t in inside_times
+            # the warm-up steps run the same load right before the timed ones: a reason active there explains
+            # a clock below the maximum even when the few samples inside a short timed region miss the flag
+            near = timed or (self.t_begin is not None and self.t_begin - 1.0 <= t <= self.t_end + 0.3)
             try:
-                mhz.append(float(parts[0]))
-                mx = float(parts[1])
+                if timed:
+                    mhz.append(float(parts[0]))
+                    mx = float(parts[1])
             except ValueError:
                 continue
             for n, v in zip(names, parts[2:6]):
                 if v.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx,
-                "reasons": sorted(reasons), "samples": len(mhz)}
+                    if timed:
+                        reasons.add(n)
+                    if near:
+                        nearby.add(n)
+            if timed and len(parts) >= 8:
+                try:
+                    watts.append(float(parts[6]))
+                    limit = float(parts[7])
+                except ValueError:
+                    pass
+            if timed and len(parts) >= 9:
+                try:
+                    mask |= int(parts[8], 16)       # every reason bit the driver reports, named or not
+                except ValueError:
+                    pass
+        out = {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx,
+               "reasons": sorted(reasons), "samples": len(mhz), "reasons_within_1s": sorted(nearby)}
+        if watts:
+            out.update(power_w=statistics.median(watts), power_limit_w=limit)
+        out["reasons_mask"] = hex(mask)
+        return out
 
 
 # ---------------------------------------------------------------------------------------------
