@@ -31,7 +31,7 @@ ABI = {"schema": "3.0", "target": {"toolkit": "cuda-12.9", "math": {"ftz": False
                                                                    "fmad": True}}}
 
 
-def emit_manifest(source, includes=(), defines=()) -> dict:
+def emit_manifest(source, includes=(), defines=(), profile="sm_100a") -> dict:
     """Run the unit's host projection: compile with -DPIPELINK_EMIT, execute, parse what it prints.
     Units of this repo keep their device code behind #ifndef PIPELINK_EMIT and compile as plain C++ in
     a second; a unit that does not (one written for the reference's toolchain, device bodies in the
@@ -43,7 +43,8 @@ def emit_manifest(source, includes=(), defines=()) -> dict:
         cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-x", "c++", "-I", str(CUDA_INCLUDE), *common, str(source), "-o", str(exe)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
-            cuda = [jitlink.nvcc(), "-std=c++17", "-x", "cu", "-gencode", "arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr",
+            arch = PROFILES[profile]["gencode"][0]           # the unit may insist on its target (a Hopper unit on sm_90a)
+            cuda = [jitlink.nvcc(), "-std=c++17", "-x", "cu", "-gencode", f"arch={arch},code={arch.replace('compute', 'sm')}", "--expt-relaxed-constexpr",
                     *common, str(source), "-o", str(exe)]
             second = subprocess.run(cuda, capture_output=True, text=True)
             if second.returncode != 0:
@@ -53,6 +54,7 @@ def emit_manifest(source, includes=(), defines=()) -> dict:
             fail("P-ANNOTATION", str(source), run.stderr.strip() or "the manifest pass failed")
     m = json.loads(run.stdout)
     m["claims"].sort(key=lambda c: (c.get("handle", ""), c.get("domain", "")))     # claims in the order of their handles, as the reference writes them
+    m["endpoints"].sort(key=lambda e: (e.get("name", ""), e.get("direction", "")))   # and endpoints in the order of their names
     _check_init_warps(m, source)
     # a declaration travels with its digest (call protocols and the export records they restate)
     for rec in [ep.get("protocol") or {} for ep in m.get("endpoints", [])] + list(m["stage"].get("exports", {}).values()):
@@ -106,7 +108,7 @@ def pack_cu(source, manifest_path=None, out=None, profile="sm_100a", includes=()
         payload_job = pool.submit(jitlink.compile_lto, str(source), str(obj), prof, includes, defines)
         if manifest_path is None:
             undefined_job = pool.submit(undefined_symbols, source, prof, includes[1:], defines)
-            manifest = emit_manifest(source, includes[1:], defines)
+            manifest = emit_manifest(source, includes[1:], defines, profile)
             manifest["symbols"].update(mechanism="ptx-extern", defined_weak=[], undefined=undefined_job.result())
             manifest["payload"] = {"file": "stage.o"}
             inputs = {"tu": hashlib.sha256(source.read_bytes()).hexdigest(),

@@ -14,36 +14,30 @@ SOLVE_CASES = {
 }
 
 
-def _set(path, value):
+def _endpoint(m, name):
+    """Endpoints are selected by name: their order in a manifest is the packer's (by name), not the source's."""
+    return next(e for e in m["endpoints"] if e["name"] == name)
+
+
+def _set(stage, endpoint, path, value):
     def mutate(ms):
-        node = ms
+        node = _endpoint(ms[stage], endpoint)
         for key in path[:-1]:
             node = node[key]
         node[path[-1]] = value
     return mutate
 
 
-def _both_operand_sides(path, value):
-    """The same edit on the producer (load) and consumer (mma) endpoint of `operands`."""
-    def mutate(ms):
-        for stage in (0, 1):
-            node = ms[stage]["endpoints"][0]
-            for key in path[:-1]:
-                node = node[key]
-            node[path[-1]] = value
-    return mutate
-
-
 # name -> mutation of [load, mma, epilogue] manifest dicts (deep copies)
 NEGATIVE_CASES = {
-    "missing-consumer": lambda ms: ms[1]["endpoints"].pop(0),
-    "scope-differs": _set((1, "endpoints", 0, "scope"), "cluster"),
-    "layout-stride-differs": _set((1, "endpoints", 0, "layout", "stride"), [[16384], [256], [1]]),
-    "swizzle-differs": _set((1, "endpoints", 0, "layout", "swizzle"), {"B": 2, "M": 4, "S": 3}),
-    "tmem-columns-differ": _set((2, "endpoints", 0, "layout", "cols"), 64),
-    "tile-differs": _set((2, "endpoints", 0, "tile"), {"dtype": "f32", "shape": [128, 64]}),
-    "empty-arrive-count-differs": _set((1, "endpoints", 0, "protocol", "empty", "arrive", "count"), 32),
-    "ring-stride-differs": _set((1, "endpoints", 0, "ring", "stage_stride_bytes"), 16384),
+    "missing-consumer": lambda ms: ms[1]["endpoints"].remove(_endpoint(ms[1], "operands")),
+    "scope-differs": _set(1, "operands", ("scope",), "cluster"),
+    "layout-stride-differs": _set(1, "operands", ("layout", "stride"), [[16384], [256], [1]]),
+    "swizzle-differs": _set(1, "operands", ("layout", "swizzle"), {"B": 2, "M": 4, "S": 3}),
+    "tmem-columns-differ": _set(2, "accumulator", ("layout", "cols"), 64),
+    "tile-differs": _set(2, "accumulator", ("tile",), {"dtype": "f32", "shape": [128, 64]}),
+    "empty-arrive-count-differs": _set(1, "operands", ("protocol", "empty", "arrive", "count"), 32),
+    "ring-stride-differs": _set(1, "operands", ("ring", "stage_stride_bytes"), 16384),
 }
 
 

@@ -45,16 +45,21 @@ def _channels(ms):
     return ch
 
 
+def _ep(m, name):
+    return next(e for e in m["endpoints"] if e["name"] == name)
+
+
 # negative corpus in the style of pipec/tests/pipec2/fixtures/negative: one mutation, one clause
+# (ms[0] = load, ms[1] = mma; both hold an end of `operands`)
 NEGATIVE = [
-    ("missing consumer", lambda ms: ms[1]["endpoints"].pop(0), "L-PAIR", "channels.operands"),
-    ("scope differs", lambda ms: ms[1]["endpoints"][0].__setitem__("scope", "cluster"), "L-PAIR", "channels.operands.endpoint.scope"),
-    ("layout differs", lambda ms: ms[1]["endpoints"][0]["layout"]["stride"].__setitem__(1, [256]), "L8", "channels.operands.layout"),
-    ("swizzle differs", lambda ms: ms[1]["endpoints"][0]["layout"].__setitem__("swizzle", {"B": 2, "M": 4, "S": 3}), "L8", "channels.operands.layout"),
-    ("tx bytes differ", lambda ms: ms[1]["endpoints"][0]["protocol"]["full"].__setitem__("tx_bytes", 1024), "L-PROTO", "channels.operands.protocol"),
-    ("arrive count impossible", lambda ms: [m["endpoints"][i]["protocol"]["empty"]["arrive"].__setitem__("count", 7)
-                                             for m, i in ((ms[0], 0), (ms[1], 0))], "L-PROTO", "channels.operands.protocol.empty.arrive.count"),
-    ("two materializers", lambda ms: ms[0]["endpoints"][0]["protocol"]["init"].__setitem__("materializer", "load"),
+    ("missing consumer", lambda ms: ms[1]["endpoints"].remove(_ep(ms[1], "operands")), "L-PAIR", "channels.operands"),
+    ("scope differs", lambda ms: _ep(ms[1], "operands").__setitem__("scope", "cluster"), "L-PAIR", "channels.operands.endpoint.scope"),
+    ("layout differs", lambda ms: _ep(ms[1], "operands")["layout"]["stride"].__setitem__(1, [256]), "L8", "channels.operands.layout"),
+    ("swizzle differs", lambda ms: _ep(ms[1], "operands")["layout"].__setitem__("swizzle", {"B": 2, "M": 4, "S": 3}), "L8", "channels.operands.layout"),
+    ("tx bytes differ", lambda ms: _ep(ms[1], "operands")["protocol"]["full"].__setitem__("tx_bytes", 1024), "L-PROTO", "channels.operands.protocol"),
+    ("arrive count impossible", lambda ms: [_ep(m, "operands")["protocol"]["empty"]["arrive"].__setitem__("count", 7) for m in ms[:2]],
+     "L-PROTO", "channels.operands.protocol.empty.arrive.count"),
+    ("two materializers", lambda ms: _ep(ms[0], "operands")["protocol"]["init"].__setitem__("materializer", "load"),
      "L-PROTO", "channels.operands.protocol.init"),
 ]
 

@@ -80,3 +80,32 @@ def test_ring_pipeline_sources_pack_and_link_into_an_image(tmp_path):
     assert (tmp_path / "link" / "pipeline.cubin").stat().st_size > 0
     dispatch = (tmp_path / "link" / "generated" / "dispatch.cu").read_text()
     assert "ring_producer(p.bytes" in dispatch and "ring_consumer(p.bytes" in dispatch
+
+
+HOPPER = json.loads((GOLDEN / "reference_hopper_gemm_split.json").read_text())
+
+
+def _cutlass_include():
+    """Any recent CUTLASS include tree (the example's own is a submodule that is not checked out): only
+    declarations are needed for the manifest pass."""
+    for module in ("flashinfer", "tilelang"):
+        import importlib.util
+        spec = importlib.util.find_spec(module)      # located, not imported
+        if spec is None or not spec.origin:
+            continue
+        root = Path(spec.origin).parent
+        for sub in ("data/cutlass/include", "3rdparty/cutlass/include"):
+            if (root / sub / "cutlass" / "arch" / "barrier.h").exists():
+                return root / sub
+    return None
+
+
+@pytest.mark.parametrize("name", sorted(HOPPER["manifests"]))
+def test_hopper_gemm_split_sources_emit_the_reference_manifests(name):
+    """Hopper units: only their host projection is compiled (as CUDA for sm_90a where a unit insists on it)."""
+    cutlass = _cutlass_include()
+    if cutlass is None:
+        pytest.skip("no CUTLASS include tree on this machine")
+    example = REFERENCE / "examples" / "hopper-gemm-split"
+    _same(pack.emit_manifest(example / "src" / f"{name}.cu", includes=(str(cutlass), str(example / "src")), profile="sm_90a"),
+          HOPPER["manifests"][name])
