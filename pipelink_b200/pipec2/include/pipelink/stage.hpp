@@ -28,6 +28,7 @@
 #define PL_EXPORT(name, fn) static_assert(true, "")
 #define PL_CALL(channel, fn, direction, ...) static_assert(true, "")
 #define PL_TYPE(T) static_assert(true, "")
+#define PL_DESCRIPTOR(T) static_assert(true, "")
 #define PL_ENDPOINT(name, ...) static_assert(true, "")
 #define PL_CLAIM(...) static_assert(true, "")
 #define PL_CLAIM_EX(...) static_assert(true, "")
@@ -177,20 +178,31 @@ struct arrivals {
 struct handle { const char* name; explicit handle(const char* n) : name(n) {} };
 struct fixed { int n; explicit fixed(int value) : n(value) {} };
 
+struct tree {            // a shape or stride tree: {128, 64} is [128, 64], {{64}} is [[64]]
+  bool leaf;
+  long long value = 0;
+  std::vector<tree> kids;
+  template <class I, typename std::enable_if<std::is_integral<I>::value, int>::type = 0>
+  tree(I v) : leaf(true), value(static_cast<long long>(v)) {}
+  tree(std::initializer_list<tree> k) : leaf(false), kids(k) {}
+  json to_json() const {
+    if (leaf) return json(value);
+    json a = json::array();
+    for (const tree& k : kids) a.push(k.to_json());
+    return a;
+  }
+};
 struct affine {          // pl::affine{shape, stride, elem_bits}[.swizzle(B, M, S)]
-  std::vector<int> shape, stride;
+  tree shape, stride;
   int elem_bits, sw_b = 0, sw_m = 0, sw_s = 0;
-  affine(std::initializer_list<int> sh, std::initializer_list<int> st, int bits) : shape(sh), stride(st), elem_bits(bits) {}
+  affine(std::initializer_list<tree> sh, std::initializer_list<tree> st, long long bits) : shape(sh), stride(st), elem_bits(static_cast<int>(bits)) {}
   affine& swizzle(int b, int m, int s_) { sw_b = b; sw_m = m; sw_s = s_; return *this; }
   json to_json() const {
     json l = json::object();
     l["encoding"] = json("pl-layout-v2");
     l["elem_bits"] = json(elem_bits);
-    json sh = json::array(), st = json::array();
-    for (int v : shape) sh.push(json(v));
-    for (int v : stride) st.push(json(v));
-    l["shape"] = sh;
-    l["stride"] = st;
+    l["shape"] = shape.to_json();
+    l["stride"] = stride.to_json();
     if (sw_b != 0) {
       json sw = json::object();
       sw["B"] = json(sw_b);
@@ -476,7 +488,7 @@ class topology {
 struct registry {
   json stage = json::object(), roles = json::object(), exports = json::object();
   json endpoints = json::array(), claims = json::array(), variants = json::array();
-  json topology, params, hints = json::object();
+  json topology, params, descriptor, hints = json::object();
   json strong = json::array();
   std::vector<std::pair<std::string, int>> role_warps;   // every PL_ROLE, in order
   std::vector<std::string> warp_claimed;                // roles some warp claim names
@@ -498,6 +510,25 @@ struct reg_stage {
 };
 
 struct member { const char* name; size_t offset, size; };
+// the name of a type as the compiler knows it, namespaces included ("pipelink_profile_consumer::InstructionParams")
+template <class T>
+std::string qualified_name(const char* as_written) {
+  const std::string pretty = __PRETTY_FUNCTION__;       // "... [with T = ns::Type; ...]"
+  const size_t at = pretty.find("T = ");
+  if (at == std::string::npos) return as_written;
+  size_t end = pretty.find_first_of(";]", at);
+  return pretty.substr(at + 4, end - at - 4);
+}
+
+struct reg_descriptor {      // PL_DESCRIPTOR(T): the size and alignment of the stage's descriptor record
+  reg_descriptor(size_t bytes, size_t align) {
+    json d = json::object();
+    d["bytes"] = json(static_cast<long long>(bytes));
+    d["align"] = json(static_cast<long long>(align));
+    registry::get().descriptor = d;
+  }
+};
+
 struct reg_params {
   reg_params(const char* type, size_t bytes, size_t align, bool opaque, std::initializer_list<member> members) {
     registry& r = registry::get();
@@ -698,6 +729,7 @@ inline int emit_main() {
   stage["roles"] = r.roles;
   stage["exports"] = r.exports;
   stage["variants"] = r.variants;
+  if (!r.descriptor.is_null()) stage["descriptor"] = r.descriptor;
   json symbols = json::object();
   symbols["defined_strong"] = r.strong;
   json out = json::object();
@@ -816,8 +848,9 @@ constexpr bool is_role_entry = std::is_same<F, void(const void*, unsigned)>::val
 #define PL_PARAMS(T, ...)                                                                                      \
   static_assert(std::is_standard_layout<T>::value && std::is_trivially_copyable<T>::value,                    \
                 "PL_PARAMS: a standard-layout, trivially copyable type");                                     \
-  PL_REG(reg_params)(#T, sizeof(T), alignof(T), false, {PL_FOR_EACH_MEMBER(T, __VA_ARGS__)})
-#define PL_PARAMS_OPAQUE(T) PL_REG(reg_params)(#T, sizeof(T), alignof(T), true, {})
+  PL_REG(reg_params)(::pl::qualified_name<T>(#T).c_str(), sizeof(T), alignof(T), false, {PL_FOR_EACH_MEMBER(T, __VA_ARGS__)})
+#define PL_PARAMS_OPAQUE(T) PL_REG(reg_params)(::pl::qualified_name<T>(#T).c_str(), sizeof(T), alignof(T), true, {})
+#define PL_DESCRIPTOR(T) PL_REG(reg_descriptor)(sizeof(T), alignof(T))
 #define PL_NO_PARAMS() PL_REG(reg_params)("void", 0, 1, false, {})
 #define PL_ROLE(name, fn, warps)                                                                  \
   static_assert(::pl::is_role_entry<decltype(fn)>, "PL_ROLE: void(const void* params, unsigned variant)"); \

@@ -109,3 +109,16 @@ def test_hopper_gemm_split_sources_emit_the_reference_manifests(name):
     example = REFERENCE / "examples" / "hopper-gemm-split"
     _same(pack.emit_manifest(example / "src" / f"{name}.cu", includes=(str(cutlass), str(example / "src")), profile="sm_90a"),
           HOPPER["manifests"][name])
+
+
+PROFILE_CONSUMER = json.loads((GOLDEN / "reference_profile_consumer.json").read_text())
+
+
+@pytest.mark.parametrize("index,name", [(1, "instruction1"), (2, "instruction2")])
+def test_profile_consumer_instruction_sources_emit_the_reference_manifests(index, name):
+    """Named-barrier and counter endpoints, nested layout trees, positional PL_CLAIM with a phase lifetime,
+    PL_DESCRIPTOR, a dynamic cluster, a namespace-qualified params type. (The third unit of the example, its
+    scheduler, declares a host owner with PL_HOST_* annotations this header does not have.)"""
+    example = REFERENCE / "examples" / "profile-consumer" / "src"
+    _same(pack.emit_manifest(example / f"{name}.cu", includes=(str(example), str(REFERENCE / "pipec/src/pipec2/host/include"))),
+          PROFILE_CONSUMER["manifests"][index])
