@@ -32,10 +32,12 @@
 #define PL_ENDPOINT(name, ...) static_assert(true, "")
 #define PL_CLAIM(...) static_assert(true, "")
 #define PL_CLAIM_EX(...) static_assert(true, "")
+#define PL_CLAIM_SMEM(...) static_assert(true, "")
 #define PL_CLAIM_WARPS(handle, role, warps, align) static_assert(true, "")
-#define PL_CLAIM_REGS(handle, role, group, regs) static_assert(true, "")
+#define PL_CLAIM_REGS(...) static_assert(true, "")
+#define PL_VARIANT_ENTRY(...) static_assert(true, "")
 #define PL_TOPOLOGY(...) static_assert(true, "")
-#define PL_VARIANT(index, key) static_assert(true, "")
+#define PL_VARIANT(...) static_assert(true, "")
 #define PL_HINT(key, value) static_assert(true, "")
 
 #else  // PIPELINK_EMIT: the host projection
@@ -51,6 +53,7 @@
 
 #include "tensor_source.h"
 #include <array>
+#include <optional>
 #include <cstddef>
 #include <cstdio>
 #include <initializer_list>
@@ -221,11 +224,14 @@ struct arrive {          // pl::arrive{"role", 2} or pl::arrive{"role", "threads
   arrive(const char* role, int n) : by(role), count(n) {}
   arrive(const char* role, const char* expression) : by(role), count(expression) {}
 };
-struct side {            // pl::side{slots handle, arrive, tx_bytes}
+struct tile_t {};
+constexpr tile_t tile{};      // pl::tile: the transaction bytes of a side are the bytes of the endpoint's tile
+struct side {            // pl::side{slots handle, arrive, tx_bytes | pl::tile}
   std::string slots;
   arrive who;
-  long long tx_bytes;
-  side(const char* slots_handle, const arrive& a, long long tx) : slots(slots_handle), who(a), tx_bytes(tx) {}
+  json tx;
+  side(const char* slots_handle, const arrive& a, long long tx_bytes) : slots(slots_handle), who(a), tx(tx_bytes) {}
+  side(const char* slots_handle, const arrive& a, tile_t) : slots(slots_handle), who(a), tx("tile") {}
   json to_json() const {
     json a = json::object();
     a["by"] = json(who.by);
@@ -233,7 +239,7 @@ struct side {            // pl::side{slots handle, arrive, tx_bytes}
     json j = json::object();
     j["slots"] = json(slots);
     j["arrive"] = a;
-    j["tx_bytes"] = json(tx_bytes);
+    j["tx_bytes"] = tx;
     return j;
   }
 };
@@ -244,10 +250,16 @@ struct init {            // pl::init{owner, phase, materializer[, warp]}
   int warp;
   init(const char* o, int ph, const char* m, int w = -1) : owner(o), phase(ph), materializer(m), warp(w) {}
 };
-struct mbarrier {        // pl::mbarrier{full, empty, init}
-  side full, empty;
+struct mbarrier {        // pl::mbarrier{full, empty | std::nullopt, init[, release]}
+  side full;
+  bool has_empty;
+  side empty;
   init start;
-  mbarrier(const side& f, const side& e, const init& i) : full(f), empty(e), start(i) {}
+  std::string release;
+  mbarrier(const side& f, const side& e, const init& i, const char* rel = "once-per-acquire")
+      : full(f), has_empty(true), empty(e), start(i), release(rel) {}
+  mbarrier(const side& f, std::nullopt_t, const init& i, const char* rel)
+      : full(f), has_empty(false), empty(f), start(i), release(rel) {}
   json to_json() const {
     json i = json::object();
     if (start.owner != nullptr) i["owner"] = json(start.owner);
@@ -257,9 +269,9 @@ struct mbarrier {        // pl::mbarrier{full, empty, init}
     json p = json::object();
     p["kind"] = json("mbarrier");
     p["full"] = full.to_json();
-    p["empty"] = empty.to_json();
+    if (has_empty) p["empty"] = empty.to_json();
     p["init"] = i;
-    p["release"] = json("once-per-acquire");
+    p["release"] = json(release);
     return p;
   }
 };
@@ -419,6 +431,13 @@ class endpoint {
  private:
   json j_ = json::object();
 };
+
+// pl::signal_endpoint(name, direction[, role]): a barrier channel that carries completion and no data
+inline endpoint signal_endpoint(const char* name, const char* direction, const char* role = nullptr) {
+  endpoint e(name, direction, role);
+  e.space("none").scope("cta").proxy("generic");
+  return e;
+}
 
 struct launch {          // pl::launch{x_multiple_of, {max x, y, z}}
   int x_multiple_of;
@@ -607,6 +626,7 @@ class claim {
     return *this;
   }
   claim& align(int a) { j_["align"] = json(a); return *this; }
+  claim& typed() { j_["_typed"] = json(true); return *this; }      // sized from a C++ type: the packer lists these last
   claim& lifetime(const char* l) { j_["lifetime"] = json(l); return *this; }
   claim& at(long long base) { j_["absolute_base"] = json(base); return *this; }
   claim& roles(std::initializer_list<const char*> names) {
@@ -665,14 +685,20 @@ struct reg_warps {
   }
 };
 
-struct reg_regs {
-  reg_regs(const char* handle, const char* role, const char* group, int regs) {
+struct reg_regs {          // PL_CLAIM_REGS("handle", "reg_group", {values...}, "role"...)
+  template <class... Roles>
+  reg_regs(const char* handle, const char* group, std::initializer_list<int> values, Roles... role_names) {
     json c = json::object();
     c["domain"] = json("regs");
     c["handle"] = json(handle);
-    c["roles"] = json::list({role});
-    c["values"] = json::list({regs});
     c["reg_group"] = json(group);
+    json roles = json::array();
+    const char* names[] = {role_names..., nullptr};
+    for (size_t i = 0; i < sizeof...(Roles); ++i) roles.push(json(names[i]));
+    c["roles"] = roles;
+    json vs = json::array();
+    for (int v : values) vs.push(json(v));
+    c["values"] = vs;
     registry::get().claims.push(c);
   }
 };
@@ -685,11 +711,28 @@ struct reg_topology {
   }
 };
 
-struct reg_variant {
-  reg_variant(int index, json key) {
+struct reg_variant {       // PL_VARIANT(index, {{handle, value}, ...}); PL_VARIANT_ENTRY(index, {{...}}, fn)
+  using key_list = std::initializer_list<std::pair<const char*, long long>>;
+  static json key_of(key_list key) {
+    json k = json::object();
+    for (const auto& kv : key) k[kv.first] = json(kv.second);
+    return k;
+  }
+  reg_variant(int index, json key) { push(index, key.is_null() ? json::object() : key, nullptr); }
+  reg_variant(int index, key_list key) { push(index, key_of(key), nullptr); }
+  // `text` is the stringified argument list: the entry's name is what follows its last comma
+  reg_variant(int index, const char* text, key_list key, void (*)(const void*, unsigned)) {
+    std::string t = text;
+    t = t.substr(t.rfind(',') + 1);
+    while (!t.empty() && t.front() == ' ') t.erase(0, 1);
+    push(index, key_of(key), t.c_str());
+    registry::get().strong.push(json(t));
+  }
+  static void push(int index, const json& key, const char* entry) {
     json v = json::object();
     v["index"] = json(index);
-    v["key"] = key.is_null() ? json::object() : key;
+    v["key"] = key;
+    if (entry != nullptr) v["entry"] = json(entry);
     registry::get().variants.push(v);
   }
 };
@@ -747,11 +790,12 @@ inline int emit_main() {
 // C spellings of the types a call channel may carry (scalars, pointers to them, const): the link
 // generates the trampoline from them, so the set is closed
 template <class T> struct type_name;
-#define PL_TYPE_NAME(T) template <> struct type_name<T> { static std::string get() { return #T; } }
-PL_TYPE_NAME(void); PL_TYPE_NAME(bool); PL_TYPE_NAME(char); PL_TYPE_NAME(signed char); PL_TYPE_NAME(unsigned char);
-PL_TYPE_NAME(short); PL_TYPE_NAME(unsigned short); PL_TYPE_NAME(int); PL_TYPE_NAME(unsigned); PL_TYPE_NAME(long);
-PL_TYPE_NAME(unsigned long); PL_TYPE_NAME(long long); PL_TYPE_NAME(unsigned long long); PL_TYPE_NAME(float); PL_TYPE_NAME(double);
-PL_TYPE_NAME(pipelink_tensor_source);
+#define PL_TYPE_NAME(T, spelled) template <> struct type_name<T> { static std::string get() { return spelled; } }
+PL_TYPE_NAME(void, "void"); PL_TYPE_NAME(bool, "bool"); PL_TYPE_NAME(char, "char"); PL_TYPE_NAME(float, "float"); PL_TYPE_NAME(double, "double");
+PL_TYPE_NAME(signed char, "int8_t"); PL_TYPE_NAME(unsigned char, "uint8_t"); PL_TYPE_NAME(short, "int16_t");
+PL_TYPE_NAME(unsigned short, "uint16_t"); PL_TYPE_NAME(int, "int32_t"); PL_TYPE_NAME(unsigned, "uint32_t");
+PL_TYPE_NAME(long, "int64_t"); PL_TYPE_NAME(unsigned long, "uint64_t"); PL_TYPE_NAME(long long, "int64_t");
+PL_TYPE_NAME(unsigned long long, "uint64_t"); PL_TYPE_NAME(pipelink_tensor_source, "pipelink_tensor_source");
 #undef PL_TYPE_NAME
 template <class T> struct type_name<const T> { static std::string get() { return "const " + type_name<T>::get(); } };
 template <class T> struct type_name<T*> { static std::string get() { return type_name<T>::get() + "*"; } };
@@ -872,10 +916,18 @@ constexpr bool is_role_entry = std::is_same<F, void(const void*, unsigned)>::val
 #define PL_CLAIM_EX1(builder) PL_REG(reg_claim_any)(builder)
 #define PL_CLAIM_EX_PICK(a1, a2, a3, a4, a5, a6, which, ...) which
 #define PL_CLAIM_EX(...) PL_CLAIM_EX_PICK(__VA_ARGS__, PL_CLAIM_EX6, x, x, x, x, PL_CLAIM_EX1, x)(__VA_ARGS__)
+// PL_CLAIM_SMEM("handle", T[, lifetime]): shared memory sized and aligned as T
+#define PL_CLAIM_SMEM(handle, T, ...) \
+  PL_REG(reg_claim_any)(::pl::claim(::pl::reg_claim_any::bare(#handle).c_str(), "smem").extent(sizeof(T)).align(alignof(T)).typed() PL_LIFETIME(__VA_ARGS__))
+#define PL_LIFETIME(...) PL_LIFETIME_PICK(_, ##__VA_ARGS__, PL_LIFETIME_1, PL_LIFETIME_0)(__VA_ARGS__)
+#define PL_LIFETIME_PICK(a, b, which, ...) which
+#define PL_LIFETIME_0()
+#define PL_LIFETIME_1(l) .lifetime(l)
 #define PL_CLAIM_WARPS(handle, role, warps, align) PL_REG(reg_warps)(#handle, #role, warps, align)
-#define PL_CLAIM_REGS(handle, role, group, regs) PL_REG(reg_regs)(#handle, #role, #group, regs)
+#define PL_CLAIM_REGS(handle, group, ...) PL_REG(reg_regs)(handle, group, __VA_ARGS__)
 #define PL_TOPOLOGY(...) PL_REG(reg_topology){__VA_ARGS__}   // braces: no vexing parse of pl::topology()
-#define PL_VARIANT(index, key) PL_REG(reg_variant)(index, key)
+#define PL_VARIANT(index, ...) PL_REG(reg_variant)(index, __VA_ARGS__)
+#define PL_VARIANT_ENTRY(index, ...) PL_REG(reg_variant)(index, #__VA_ARGS__, __VA_ARGS__)
 #define PL_HINT(key, value) PL_REG(reg_hint)(key, ::pl::json(value))
 
 #ifndef PIPELINK_EMIT_NO_MAIN

@@ -53,8 +53,15 @@ def emit_manifest(source, includes=(), defines=(), profile="sm_100a") -> dict:
         if run.returncode != 0:
             fail("P-ANNOTATION", str(source), run.stderr.strip() or "the manifest pass failed")
     m = json.loads(run.stdout)
-    m["claims"].sort(key=lambda c: (c.get("handle", ""), c.get("domain", "")))     # claims in the order of their handles, as the reference writes them
-    m["endpoints"].sort(key=lambda e: (e.get("name", ""), e.get("direction", "")))   # and endpoints in the order of their names
+    # claims in the order of their handles, those sized from a C++ type (PL_CLAIM_SMEM) behind the others and the
+    # register claims last: the order the reference writes
+    m["claims"].sort(key=lambda c: (2 if c.get("domain") == "regs" else int(bool(c.get("_typed"))), c.get("handle", ""), c.get("domain", "")))
+    for c in m["claims"]:
+        c.pop("_typed", None)
+    # and endpoints: call endpoints first, then the others, each group in the order of its names
+    m["endpoints"].sort(key=lambda e: ((e.get("protocol") or {}).get("kind") != "call", e.get("name", ""), e.get("direction", "")))
+    if not m.get("hints"):
+        m.pop("hints", None)                          # a section without entries is not written
     _check_init_warps(m, source)
     # a declaration travels with its digest (call protocols and the export records they restate)
     for rec in [ep.get("protocol") or {} for ep in m.get("endpoints", [])] + list(m["stage"].get("exports", {}).values()):

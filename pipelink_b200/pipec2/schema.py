@@ -70,7 +70,10 @@ def validate_manifest(m: dict, where: str = "manifest") -> None:
         if ep.get("direction") not in DIRECTIONS:
             c.add("L-PAIR", f"{p}.direction", "direction must be produce or consume")
         provided_call = (ep.get("protocol") or {}).get("kind") == "call" and ep.get("direction") == "consume"
-        if ep.get("owner_role") not in roles and not (provided_call and ep.get("owner_role") is None):
+        # an endpoint signalled or awaited inside an exported callable runs in its caller's role and names none;
+        # only register tiles depend on the owning role (pipec/src/pipec2/schema.py:670-679 of the reference)
+        in_callable = (ep.get("protocol") or {}).get("kind") != "call" and ep.get("space") != "reg"
+        if ep.get("owner_role") not in roles and not ((provided_call or in_callable) and ep.get("owner_role") is None):
             c.add("L-OWNER", f"{p}.owner_role", f"unknown role {ep.get('owner_role')!r}")
         # a shared-completion root lists each member of its transaction sum once
         for side in ("full", "empty"):

@@ -390,8 +390,8 @@ inline pl::endpoint hidden_ready(const char* direction, const char* role) {
 #define MOE_CLAIM_HIDDEN_READY() PL_CLAIM(gmem_counter, pipelink_moe_hidden_ready, pl::units(moe::MaxRowTiles), 1)
 #define MOE_CLAIM_ROWS_READY() PL_CLAIM(gmem_counter, pipelink_moe_rows_ready, pl::units(moe::MaxRowTiles), 1)
 // the two register groups of an image: load + MMA + comm warps give registers up, the epilogue takes them
-#define MOE_REGS_HELPER(role) PL_CLAIM_REGS(pipelink_moe_regs_helpers, role, helpers, 56)
-#define MOE_REGS_EPILOGUE(role) PL_CLAIM_REGS(pipelink_moe_regs_epilogue, role, epilogue, 224)
+#define MOE_REGS_HELPER(role) PL_CLAIM_REGS("pipelink_moe_regs_helpers", "helpers", {56}, #role)
+#define MOE_REGS_EPILOGUE(role) PL_CLAIM_REGS("pipelink_moe_regs_epilogue", "epilogue", {224}, #role)
 
 static_assert(sizeof(MoeGeometry) == 48 && sizeof(MoeLoadParams) == 576 && sizeof(MoeMmaParams) == 48 &&
               sizeof(MoeCommParams) == 112 && sizeof(MoeSwigluParams) == 80 && sizeof(MoeRowsParams) == 96 &&

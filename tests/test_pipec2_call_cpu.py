@@ -91,7 +91,8 @@ def test_a_provider_without_the_export_does_not_link():
 
 
 def test_signatures_are_spelled_from_the_declarations(tmp_path):
-    """The closed set of types a call may carry: scalars, pointers to them, const."""
+    """The closed set of types a call may carry: scalars, pointers to them, const; integers are spelled
+    by their fixed-width names, as the reference's pass spells them."""
     src = tmp_path / "sig.cu"
     src.write_text('#include <pipelink/stage.hpp>\n'
                    'extern "C" __device__ void f(const float* a, unsigned long long* b, int n, double s);\n'
@@ -101,7 +102,7 @@ def test_signatures_are_spelled_from_the_declarations(tmp_path):
     from pipelink_b200.pipec2 import codegen, pack
     m = pack.emit_manifest(src)
     proto = m["endpoints"][0]["protocol"]
-    assert proto["signature"] == "void(const float*, unsigned long long*, int, double)" and proto["export"] == "impl"
+    assert proto["signature"] == "void(const float*, uint64_t*, int32_t, double)" and proto["export"] == "impl"
     text = codegen.binding_stub({}, [{"caller": "f", "provider": "g", "signature": proto["signature"]}])
-    assert ('extern "C" __device__ void f(const float* a0, unsigned long long* a1, int a2, double a3) { g(a0, a1, a2, a3); }'
+    assert ('extern "C" __device__ void f(const float* a0, uint64_t* a1, int32_t a2, double a3) { g(a0, a1, a2, a3); }'
             in text)
