@@ -27,7 +27,11 @@
 #define PL_ROLE(name, fn, warps) static_assert(true, "")
 #define PL_EXPORT(name, fn) static_assert(true, "")
 #define PL_CALL(channel, fn, direction, ...) static_assert(true, "")
-#define PL_TYPE(T) static_assert(true, "")
+#define PL_TYPE(...) static_assert(true, "")
+#define PL_BINDING(...) static_assert(true, "")
+#define PL_SITE(...) static_assert(true, "")
+#define PL_EXPORT_TENSOR(...) static_assert(true, "")
+#define PL_IMPORT_TENSOR(...) static_assert(true, "")
 #define PL_DESCRIPTOR(T) static_assert(true, "")
 #define PL_ENDPOINT(name, ...) static_assert(true, "")
 #define PL_CLAIM(...) static_assert(true, "")
@@ -52,10 +56,14 @@
 #endif
 
 #include "tensor_source.h"
+#include <algorithm>
 #include <array>
+#include <cctype>
 #include <optional>
 #include <cstddef>
 #include <cstdio>
+#include <functional>
+#include <tuple>
 #include <initializer_list>
 #include <map>
 #include <memory>
@@ -90,6 +98,9 @@ class json {
   json& operator[](const std::string& key) { kind_ = Obj; return o_[key]; }
   json& set(const std::string& key, json v) { (*this)[key] = std::move(v); return *this; }
   bool is_null() const { return kind_ == Null; }
+  size_t size() const { return kind_ == Arr ? a_.size() : o_.size(); }
+  json& at(size_t i) { return a_[i]; }
+  const std::string& str() const { return s_; }
   std::string dump() const {
     switch (kind_) {
       case Null: return "null";
@@ -509,6 +520,9 @@ struct registry {
   json endpoints = json::array(), claims = json::array(), variants = json::array();
   json topology, params, descriptor, hints = json::object();
   json strong = json::array();
+  json tensor_exports = json::array(), tensor_imports = json::array(), tensor_sites = json::array(), tensor_bindings = json::array();
+  std::vector<std::pair<std::string, std::vector<long long>>> binding_values;   // PL_BINDING domains, by name
+  std::vector<std::pair<std::string, std::string>> type_texts;                // PL_TYPE(T, members...): name -> definition
   std::vector<std::pair<std::string, int>> role_warps;   // every PL_ROLE, in order
   std::vector<std::string> warp_claimed;                // roles some warp claim names
   int errors = 0;
@@ -609,6 +623,7 @@ struct reg_claim {
   }
 };
 
+struct during { const char* tensor; const char* from; const char* to = nullptr; };
 // pl::claim(handle, domain).extent(...).align(...).lifetime(...).at(...).roles({...}): the reference's builder
 class claim {
  public:
@@ -628,6 +643,15 @@ class claim {
   claim& align(int a) { j_["align"] = json(a); return *this; }
   claim& typed() { j_["_typed"] = json(true); return *this; }      // sized from a C++ type: the packer lists these last
   claim& lifetime(const char* l) { j_["lifetime"] = json(l); return *this; }
+  claim& lifetime(const during& events) {       // held between two events of a tensor's life (pl::during{tensor, from, to})
+    json l = json::object();
+    l["tensor"] = json(events.tensor);
+    l["from"] = json(events.from);
+    l["to"] = events.to ? json(events.to) : json();
+    j_["lifetime"] = l;
+    return *this;
+  }
+  claim& lifetime() { return *this; }
   claim& at(long long base) { j_["absolute_base"] = json(base); return *this; }
   claim& roles(std::initializer_list<const char*> names) {
     json r = json::array();
@@ -783,6 +807,36 @@ inline int emit_main() {
   out["params"] = r.params;
   out["hints"] = r.hints;
   out["symbols"] = symbols;
+  if (r.tensor_exports.size() + r.tensor_imports.size() + r.tensor_sites.size() + r.tensor_bindings.size() != 0) {
+    // "all threads" of a site or a rendezvous: every thread of the site's role, 32 per warp
+    auto threads_of = [&r](const std::string& role) {
+      json set = json::array();
+      for (const auto& rw : r.role_warps)
+        if (rw.first == role)
+          for (int t = 0; t < rw.second * 32; ++t) set.push(json(t));
+      json who = json::object();
+      who["set"] = set;
+      return who;
+    };
+    for (size_t i = 0; i < r.tensor_sites.size(); ++i)
+      if (r.tensor_sites.at(i)["participants"].is_null())
+        r.tensor_sites.at(i)["participants"] = threads_of(r.tensor_sites.at(i)["role"].str());
+    for (size_t i = 0; i < r.tensor_imports.size(); ++i) {
+      json& imp = r.tensor_imports.at(i);
+      std::string role;
+      for (size_t k = 0; k < r.tensor_sites.size(); ++k)
+        if (imp["sites"].size() != 0 && r.tensor_sites.at(k)["name"].str() == imp["sites"].at(0).str()) role = r.tensor_sites.at(k)["role"].str();
+      for (size_t k = 0; k < imp["rendezvous"].size(); ++k)
+        if (imp["rendezvous"].at(k)["cohort"].is_null()) imp["rendezvous"].at(k)["cohort"] = threads_of(role);
+    }
+    json tensor = json::object();
+    tensor["version"] = json("tensor-v2");
+    tensor["exports"] = r.tensor_exports;
+    tensor["imports"] = r.tensor_imports;
+    tensor["sites"] = r.tensor_sites;
+    tensor["bindings"] = r.tensor_bindings;
+    out["tensor"] = tensor;
+  }
   std::puts(out.dump().c_str());
   return 0;
 }
@@ -812,6 +866,32 @@ struct signature<R(A...)> {
 };
 
 // one side of a call channel: the caller's trampoline (produce, from a role) or the provided function (consume)
+// PL_TYPE(T, members...): the definitions of the registered structs a signature names, each behind an include
+// guard of its own (<T IN CAPITALS>_DEFINED), in the order the signature names them
+inline std::string type_definitions(const std::string& sig) {
+  std::vector<std::pair<size_t, std::string>> found;
+  for (const auto& t : registry::get().type_texts) {
+    const size_t at = sig.find(t.first);
+    if (at != std::string::npos) found.push_back({at, t.second});
+  }
+  std::sort(found.begin(), found.end());
+  std::string out;
+  for (const auto& f : found) out += f.second;
+  return out;
+}
+struct reg_type {
+  reg_type(const char* name, const char* members) {
+    std::string guard;
+    for (const char* c = name; *c; ++c) guard += static_cast<char>(std::toupper(static_cast<unsigned char>(*c)));
+    guard += "_DEFINED";
+    registry::get().type_texts.push_back({name, "#ifndef " + guard + "\n#define " + guard + "\nstruct " + name + " { " + members + " };\n#endif\n"});
+  }
+};
+
+struct reg_type_if {   // registers the definition only when members were given
+  reg_type_if(const char* name, const char* members) { if (*members) reg_type(name, members); }
+};
+
 struct reg_call {
   // one side of a call channel. The protocol carries the C declaration of this side's function, spelled
   // from its type: extern "C" __device__ float hello_scale(float);  (the digest is added by the packer)
@@ -819,7 +899,7 @@ struct reg_call {
            const char* export_name = nullptr) {
     const bool caller = std::string(direction) == produce;
     const size_t paren = sig.find('(');
-    const std::string decl = "extern \"C\" __device__ " + sig.substr(0, paren) + " " + fn + sig.substr(paren) + ";";
+    const std::string decl = type_definitions(sig) + "extern \"C\" __device__ " + sig.substr(0, paren) + " " + fn + sig.substr(paren) + ";";
     json proto = json::object();
     proto["kind"] = json("call");
     proto["export"] = json(caller ? (export_name ? export_name : channel) : who);
@@ -853,6 +933,525 @@ struct reg_call {
       r.exports[who]["symbol"] = json(fn);
       r.exports[who]["decl"] = json(decl);
     }
+  }
+};
+
+// ---------------------------------------------------------------------------------------------------
+// Tensor annotations (docs/reference/tensor-imports.md): PL_BINDING, PL_SITE, PL_EXPORT_TENSOR,
+// PL_IMPORT_TENSOR. A map (where an export keeps each element; which thread wants which element) is
+// written as a C++ lambda over named coordinates and bound values. The projection finds its
+// integer-affine form from the origin of the domain and one step along every input and checks that form
+// at every point of the full domain; a map that is not affine (an address swizzle) is solved as XOR-linear
+// in the bits of its inputs. Either is printed in the manifest's expression language
+// (["add", ["coord", "n"], ["toint", ["bind", "tmem_base"]]]); a map of neither family is refused.
+struct all_threads_t {};
+constexpr all_threads_t all_threads{};
+struct coord { const char* name; int lo, hi; };
+struct bound {                      // the value of a binding inside a map
+  long long value;
+  operator long long() const { return value; }
+};
+struct bind {
+  const char* name; const char* sort;
+  bind(const char* n, const char* s) : name(n), sort(s) {}
+};
+struct values {
+  const char* name; const char* sort; std::vector<long long> items;
+  values(const char* n, const char* s, std::initializer_list<long long> v) : name(n), sort(s), items(v) {}
+};
+struct strings : std::vector<std::string> {
+  strings(std::initializer_list<const char*> v) { for (const char* x : v) push_back(x); }
+  json to_json() const { json a = json::array(); for (const auto& x : *this) a.push(json(x)); return a; }
+};
+using guarantees = strings;
+struct sync { int generations, capacity; };
+struct lend {                       // field order: the reference's aggregate (stage.hpp:65-70 there), which sources brace-initialise
+  const char* name; const char* domain; int extent, align;
+  const char* scope; const char* binding; const char* handle;
+  std::optional<int> base; const char* owner; const char* from; const char* to;
+  std::optional<::pl::sync> barrier_sync = std::nullopt;
+  json to_json() const {
+    json j = json::object(), life = json::object(), where = json::object();
+    life["from"] = json(from);
+    life["to"] = json(to);
+    where["base"] = base ? json(*base) : json();
+    where["handle"] = handle ? json(handle) : json();
+    j["name"] = json(name);
+    j["domain"] = json(domain);
+    j["extent"] = json(extent);
+    j["align"] = json(align);
+    j["scope"] = json(scope);
+    j["binding"] = json(binding);
+    j["owner"] = json(owner);
+    j["lifetime"] = life;
+    j["location"] = where;
+    if (barrier_sync) {
+      json sy = json::object();
+      sy["generations"] = json(barrier_sync->generations);
+      sy["capacity"] = json(barrier_sync->capacity);
+      j["sync"] = sy;
+    } else {
+      j["sync"] = json();
+    }
+    return j;
+  }
+};
+using lends = std::initializer_list<lend>;
+inline json lends_json(lends all) { json a = json::array(); for (const lend& l : all) a.push(l.to_json()); return a; }
+// the common lends by kind: shared-memory bytes at a link-time handle, registers of every thread, words of the
+// caller's register frame, per-warp metadata words, a CTA barrier id with the generations the hand-off may use
+constexpr lend smem(const char* name, int extent, int align, const char* handle, const char* owner, const char* from, const char* to) {
+  return {name, "smem", extent, align, "cta", "relocatable", handle, std::nullopt, owner, from, to};
+}
+constexpr lend regs(const char* name, int extent, const char* handle, const char* owner, const char* from, const char* to) {
+  return {name, "reg", extent, 1, "thread", "fixed", handle, std::nullopt, owner, from, to};
+}
+constexpr lend frame(const char* name, int words, const char* handle, const char* owner, const char* from, const char* to) {
+  return {name, "reg", words, 1, "thread", "caller_frame", handle, std::nullopt, owner, from, to};
+}
+constexpr lend metadata(const char* name, int extent, const char* handle, const char* owner, const char* from, const char* to) {
+  return {name, "metadata", extent, 1, "warp", "fixed", handle, std::nullopt, owner, from, to};
+}
+constexpr lend cta_barrier(const char* name, int base, const char* owner, const char* from, const char* to, ::pl::sync s) {
+  return {name, "barrier", 1, 1, "cta", "fixed", nullptr, base, owner, from, to, s};
+}
+struct arg { const char* name; const char* meaning; };
+using args = std::initializer_list<arg>;
+struct readiness { const char* after; const char* reuse_after; };
+struct fixed_bindings : std::vector<std::pair<std::string, long long>> {
+  fixed_bindings() {}
+  fixed_bindings(std::initializer_list<std::pair<const char*, long long>> v) { for (const auto& x : v) push_back({x.first, x.second}); }
+};
+struct calls { const char* produce; const char* release = nullptr; };
+struct rendezvous {
+  const char* event; const char* barrier;
+  rendezvous(const char* e, const char* b, all_threads_t) : event(e), barrier(b) {}
+};
+struct identity {
+  const char* result; const char* work; const char* version; const char* dtype; const char* interpretation;
+  std::vector<coord> coords;
+  identity(const char* r, const char* w, const char* v, const char* d, const char* i, std::initializer_list<coord> c)
+      : result(r), work(w), version(v), dtype(d), interpretation(i), coords(c) {}
+  json to_json() const {
+    json j = json::object(), cs = json::array();
+    for (const coord& c : coords) cs.push(coord_json(c));
+    j["result"] = json(result);
+    j["work"] = json(work);
+    j["version"] = json(version);
+    j["dtype"] = json(dtype);
+    j["interpretation"] = json(interpretation);
+    j["coords"] = cs;
+    return j;
+  }
+  static json coord_json(const coord& c) {
+    json j = json::object();
+    j["name"] = json(c.name);
+    j["lo"] = json(c.lo);
+    j["hi"] = json(c.hi);
+    j["sort"] = json("int");
+    return j;
+  }
+};
+
+// one input of a map: a coordinate (every integer of [lo, hi)) or a binding (the values its PL_BINDING lists)
+struct map_input {
+  std::string name, sort;
+  bool bound;
+  std::vector<long long> points;
+  json reference() const {
+    json ref = json::array();
+    ref.push(json(bound ? "bind" : "coord")).push(json(name));
+    if (!bound || sort == "int") return ref;
+    json as_int = json::array();
+    as_int.push(json("toint")).push(ref);
+    return as_int;
+  }
+};
+inline map_input input_of(const coord& c) {
+  map_input in{c.name, "int", false, {}};
+  for (int v = c.lo; v < c.hi; ++v) in.points.push_back(v);
+  return in;
+}
+inline map_input input_of(const bind& b) {
+  map_input in{b.name, b.sort, true, {}};
+  for (const auto& known : registry::get().binding_values)
+    if (known.first == b.name) in.points = known.second;
+  if (in.points.empty()) registry::get().fail(std::string("map input ") + b.name + " names no PL_BINDING declared before it");
+  return in;
+}
+template <class In> struct map_argument { static int of(long long v) { return static_cast<int>(v); } };
+template <> struct map_argument<bind> { static bound of(long long v) { return bound{v}; } };
+
+// the integer-affine form of output `which` of `eval` over the inputs, as an expression; null when there is none
+template <class Eval>
+json fit_affine(const std::vector<map_input>& inputs, size_t which, Eval eval) {
+  const size_t n = inputs.size();
+  std::vector<long long> at(n), coefficient(n, 0);
+  for (size_t i = 0; i < n; ++i) at[i] = inputs[i].points.empty() ? 0 : inputs[i].points[0];
+  const long long origin = eval(at)[which];
+  long long constant = origin;
+  for (size_t i = 0; i < n; ++i) {
+    if (inputs[i].points.size() < 2) continue;
+    std::vector<long long> stepped = at;
+    stepped[i] = inputs[i].points[1];
+    const long long rise = eval(stepped)[which] - origin, run = stepped[i] - at[i];
+    if (rise % run != 0) return json();
+    coefficient[i] = rise / run;
+    constant -= coefficient[i] * at[i];
+  }
+  // every point of the domain, odometer order
+  std::vector<size_t> index(n, 0);
+  for (bool more = true; more;) {
+    long long want = constant;
+    for (size_t i = 0; i < n; ++i) {
+      at[i] = inputs[i].points.empty() ? 0 : inputs[i].points[index[i]];
+      want += coefficient[i] * at[i];
+    }
+    if (eval(at)[which] != want) return json();
+    more = false;
+    for (size_t i = 0; i < n && !more; ++i) {
+      if (inputs[i].points.empty()) continue;
+      if (++index[i] < inputs[i].points.size()) more = true;
+      else index[i] = 0;
+    }
+  }
+  // terms in the order of the inputs' names, the constant last, sums nested to the left
+  std::vector<size_t> order;
+  for (size_t i = 0; i < n; ++i) if (coefficient[i] != 0) order.push_back(i);
+  std::sort(order.begin(), order.end(), [&](size_t a, size_t b) { return inputs[a].name < inputs[b].name; });
+  std::vector<json> terms;
+  for (size_t i : order) {
+    if (coefficient[i] == 1) { terms.push_back(inputs[i].reference()); continue; }
+    json scaled = json::array();
+    scaled.push(json("mulc")).push(json(coefficient[i])).push(inputs[i].reference());
+    terms.push_back(scaled);
+  }
+  if (constant != 0 || terms.empty()) {
+    json c = json::array();
+    c.push(json("const")).push(json(constant));
+    terms.push_back(c);
+  }
+  json sum = terms[0];
+  for (size_t i = 1; i < terms.size(); ++i) {
+    json next = json::array();
+    next.push(json("add")).push(sum).push(terms[i]);
+    sum = next;
+  }
+  return sum;
+}
+
+inline json node(const char* op, json a) { json j = json::array(); j.push(json(op)).push(std::move(a)); return j; }
+inline json node(const char* op, json a, json b) { json j = json::array(); j.push(json(op)).push(std::move(a)).push(std::move(b)); return j; }
+inline json fold(const char* op, const std::vector<json>& terms) {      // nested to the left
+  json all = terms[0];
+  for (size_t i = 1; i < terms.size(); ++i) all = node(op, all, terms[i]);
+  return all;
+}
+inline int bit_length(unsigned long long v) { int n = 0; while (v) { ++n; v >>= 1; } return n; }
+
+// The second family: every bit of the output is an XOR of input bits and a constant (address swizzles). The
+// inputs' bits are the unknowns of one linear system over GF(2) per output bit, all output bits solved at once
+// by carrying the whole output word as the right-hand side; a bit of an input that never varies gets no
+// image. Printed as integer fields when no output bit mixes two input bits (x / 2^s % 2^w * 2^t), otherwise
+// as masked shifts of the inputs XORed together. Inputs are taken in the order of their names.
+template <class Eval>
+json fit_xor_linear(const std::vector<map_input>& inputs, size_t which, Eval eval) {
+  const size_t n = inputs.size();
+  std::vector<size_t> order(n);
+  for (size_t i = 0; i < n; ++i) order[i] = i;
+  std::sort(order.begin(), order.end(), [&](size_t a, size_t b) { return inputs[a].name < inputs[b].name; });
+  std::vector<int> width(n), offset(n);
+  int unknowns = 1;
+  for (size_t i : order) {
+    long long top = 0;
+    for (long long v : inputs[i].points) { if (v < 0) return json(); top = std::max(top, v); }
+    width[i] = std::max(1, bit_length(static_cast<unsigned long long>(top)));
+    offset[i] = unknowns;
+    unknowns += width[i];
+  }
+  if (unknowns > 63) return json();
+  std::vector<unsigned long long> row(unknowns, 0), image(unknowns, 0), solved(unknowns, 0);
+  std::vector<bool> have(unknowns, false);
+  std::vector<long long> at(n);
+  std::vector<size_t> index(n, 0);
+  int out_bits = 1;
+  auto every_point = [&](auto&& visit) {
+    std::fill(index.begin(), index.end(), 0);
+    for (bool more = true; more;) {
+      for (size_t i = 0; i < n; ++i) at[i] = inputs[i].points.empty() ? 0 : inputs[i].points[index[i]];
+      if (!visit()) return false;
+      more = false;
+      for (size_t i = 0; i < n && !more; ++i) {
+        if (inputs[i].points.empty()) continue;
+        if (++index[i] < inputs[i].points.size()) more = true;
+        else index[i] = 0;
+      }
+    }
+    return true;
+  };
+  auto unknowns_of = [&]() {
+    unsigned long long bits = 1;
+    for (size_t i = 0; i < n; ++i) bits |= static_cast<unsigned long long>(at[i]) << offset[i];
+    return bits;
+  };
+  // elimination, pivot on the lowest unknown of a row
+  const bool consistent = every_point([&]() {
+    const long long value = eval(at)[which];
+    if (value < 0) return false;
+    out_bits = std::max(out_bits, bit_length(static_cast<unsigned long long>(value)));
+    unsigned long long bits = unknowns_of(), rhs = static_cast<unsigned long long>(value);
+    while (bits) {
+      const int pivot = bit_length(bits & (~bits + 1)) - 1;
+      if (!have[pivot]) { have[pivot] = true; row[pivot] = bits; image[pivot] = rhs; break; }
+      bits ^= row[pivot];
+      rhs ^= image[pivot];
+    }
+    return bits != 0 || rhs == 0;
+  });
+  if (!consistent) return json();
+  for (int pivot = unknowns - 1; pivot >= 0; --pivot) {
+    if (!have[pivot]) continue;
+    unsigned long long rhs = image[pivot];
+    for (int other = pivot + 1; other < unknowns; ++other)
+      if ((row[pivot] >> other) & 1) rhs ^= solved[other];
+    solved[pivot] = rhs;
+  }
+  // integer fields: possible when every output bit copies at most one input bit
+  struct origin { size_t input; int bit; };
+  std::map<int, origin> source;
+  bool mixing = false;
+  for (size_t i : order)
+    for (int b = 0; b < width[i] && !mixing; ++b)
+      for (int t = 0; t < 64; ++t)
+        if ((solved[offset[i] + b] >> t) & 1) {
+          if (source.count(t)) { mixing = true; break; }
+          source[t] = origin{i, b};
+        }
+  const unsigned long long constant = solved[0];
+  if (!mixing) {
+    std::vector<json> terms;
+    int end = 0;
+    for (const auto& entry : source) {
+      const int target = entry.first;
+      if (target < end) continue;
+      const origin from = entry.second;
+      const bool inverted = (constant >> target) & 1;
+      int run = 1;
+      for (auto next = source.find(target + run); next != source.end(); next = source.find(target + run)) {
+        if (next->second.input != from.input || next->second.bit != from.bit + run || (((constant >> (target + run)) & 1) != 0) != inverted) break;
+        ++run;
+      }
+      end = target + run;
+      json term = inputs[from.input].reference();
+      if (from.bit) term = node("divc", term, json(1LL << from.bit));
+      if (from.bit + run < width[from.input]) term = node("modc", term, json(1LL << run));
+      const long long scale = inverted ? -(1LL << target) : (1LL << target);      // c XOR x = c - x on a copied bit
+      if (scale != 1) term = node("mulc", json(scale), term);
+      terms.push_back(term);
+    }
+    if (constant != 0 || terms.empty()) terms.push_back(node("const", json(static_cast<long long>(constant))));
+    return fold("add", terms);
+  }
+  int word = std::max(1, out_bits);
+  for (size_t i = 0; i < n; ++i) word = std::max(word, width[i]);
+  auto cbits = [word](unsigned long long v) { json j = json::array(); j.push(json("cbits")).push(json(word)).push(json(static_cast<long long>(v))); return j; };
+  std::vector<json> terms;
+  if (constant) terms.push_back(cbits(constant));
+  for (size_t i : order) {
+    std::map<int, unsigned long long> by_shift;        // shift -> the input bits that move by it
+    for (int b = 0; b < width[i]; ++b)
+      for (int t = 0; t < 64; ++t)
+        if ((solved[offset[i] + b] >> t) & 1) by_shift[t - b] |= 1ULL << b;
+    json as_bits = json::array();
+    as_bits.push(json("tobits")).push(json(word)).push(inputs[i].reference());
+    for (const auto& moved : by_shift) {
+      json term = node("band", as_bits, cbits(moved.second));
+      if (moved.first != 0) term = node(moved.first > 0 ? "shlc" : "shrc", term, json(moved.first > 0 ? moved.first : -moved.first));
+      terms.push_back(term);
+    }
+  }
+  if (terms.empty()) return node("const", json(0));
+  return node("toint", fold("bxor", terms));
+}
+
+// a map's output as an expression: integer-affine if it is, else XOR-linear; null when it is neither
+template <class Eval>
+json fit_map(const std::vector<map_input>& inputs, size_t which, Eval eval) {
+  json e = fit_affine(inputs, which, eval);
+  return e.is_null() ? fit_xor_linear(inputs, which, eval) : e;
+}
+
+template <class Fn, class... In, size_t... I>
+std::vector<long long> call_map(const Fn& fn, const std::vector<long long>& at, std::index_sequence<I...>) {
+  const auto out = fn(map_argument<In>::of(at[I])...);
+  return std::vector<long long>(out.begin(), out.end());
+}
+
+// pl::placement{space, units, {component names}, map, inputs...}: where an export keeps element (coords...)
+struct placement {
+  json record;
+  template <class Fn, class... In>
+  placement(const char* space, const char* units, std::initializer_list<const char*> components, Fn fn, In... in) {
+    const std::vector<map_input> inputs = {input_of(in)...};
+    auto eval = [&fn](const std::vector<long long>& at) { return call_map<Fn, In...>(fn, at, std::index_sequence_for<In...>{}); };
+    json parts = json::object();
+    size_t which = 0;
+    for (const char* name : components) {
+      json e = fit_map(inputs, which++, eval);
+      if (e.is_null()) registry::get().fail(std::string("placement component ") + name + " is neither integer-affine nor XOR-linear in its inputs");
+      parts[name] = e;
+    }
+    record = json::object();
+    record["space"] = json(space);
+    record["units"] = json(units);
+    record["components"] = parts;
+    record["guard"] = json();
+  }
+};
+
+// pl::demand_positions{coords..., map}: thread `participant` wants element (identity coords...) at `position`
+// of its destination; the map returns {identity coordinates in their declared order, participant, position}
+struct demand_positions {
+  std::vector<coord> domain;
+  std::function<std::vector<long long>(const std::vector<long long>&)> eval;
+  template <class... A>
+  demand_positions(A... a) { split(std::make_tuple(a...), std::make_index_sequence<sizeof...(A) - 1>{}); }
+  template <class Tuple, size_t... I>
+  void split(const Tuple& t, std::index_sequence<I...>) {
+    domain = {std::get<I>(t)...};
+    auto fn = std::get<sizeof...(I)>(t);
+    eval = [fn](const std::vector<long long>& at) {
+      const auto out = fn(static_cast<int>(at[I])...);
+      return std::vector<long long>(out.begin(), out.end());
+    };
+  }
+  json to_json(const identity& id, const std::string& what) const {
+    std::vector<map_input> inputs;
+    json dom = json::array();
+    for (const coord& c : domain) { inputs.push_back(input_of(c)); dom.push(identity::coord_json(c)); }
+    auto fitted = [&](size_t which, const std::string& name) {
+      json e = fit_map(inputs, which, eval);
+      if (e.is_null()) registry::get().fail("demand of " + what + ": " + name + " is neither integer-affine nor XOR-linear in its inputs");
+      return e;
+    };
+    json d = json::object(), coords = json::object();
+    d["kind"] = json("positions");
+    d["domain"] = dom;
+    d["guard"] = json();
+    const size_t k = id.coords.size();
+    for (size_t i = 0; i < k; ++i) coords[id.coords[i].name] = fitted(i, id.coords[i].name);
+    d["participant"] = fitted(k, "participant");
+    d["position"] = fitted(k + 1, "position");
+    d["identity_coords"] = coords;
+    return d;
+  }
+};
+
+struct reg_binding {     // PL_BINDING(name, sort, pl::values{...}, owner, units, observation scope, lifetime)
+  reg_binding(const char* name, const char* sort, const values& domain, const char* owner, const char* units,
+              const char* observed_at, const char* lifetime) {
+    json dom = json::object(), vs = json::array();
+    for (long long v : domain.items) vs.push(json(v));
+    dom["name"] = json(domain.name);
+    dom["sort"] = json(domain.sort);
+    dom["values"] = vs;
+    json b = json::object();
+    b["name"] = json(name);
+    b["sort"] = json(sort);
+    b["domain"] = dom;
+    b["owner"] = json(owner);
+    b["units"] = json(units);
+    b["observation_scope"] = json(observed_at);
+    b["lifetime"] = json(lifetime);
+    registry::get().tensor_bindings.push(b);
+    registry::get().binding_values.push_back({name, domain.items});
+  }
+};
+
+struct reg_site {        // PL_SITE(name, role, pl::all_threads, invocation, guarantees, observed events)
+  reg_site(const char* name, const char* role, all_threads_t, const char* invocation, const guarantees& promised, const strings& observes) {
+    json s = json::object();
+    s["name"] = json(name);
+    s["role"] = json(role);
+    s["invocation"] = json(invocation);
+    s["guarantees"] = promised.to_json();
+    s["observes"] = observes.to_json();
+    s["participants"] = json();          // every thread of the role: filled in when the roles are known
+    registry::get().tensor_sites.push(s);
+  }
+};
+
+struct reg_export_tensor {
+  reg_export_tensor(const char* name, const identity& id, const placement& where, const strings& read_capabilities,
+                    const readiness& ready, const fixed_bindings& fixed, lends backing, const ::pl::calls& through) {
+    json e = json::object(), places = json::array(), rd = json::object(), fx = json::object(), cs = json::object();
+    places.push(where.record);
+    rd["after"] = json(ready.after);
+    rd["reuse_after"] = json(ready.reuse_after);
+    for (const auto& kv : fixed) fx[kv.first] = json(kv.second);
+    cs["produce"] = json(through.produce);
+    cs["release"] = through.release ? json(through.release) : json();
+    e["name"] = json(name);
+    e["identity"] = id.to_json();
+    e["placements"] = places;
+    e["read_capabilities"] = read_capabilities.to_json();
+    e["readiness"] = rd;
+    e["fixed_bindings"] = fx;
+    e["backing"] = lends_json(backing);
+    e["calls"] = cs;
+    registry::get().tensor_exports.push(e);
+  }
+};
+
+template <class F> struct argument_types;
+template <class R, class... A>
+struct argument_types<R(A...)> {
+  static std::vector<std::string> get() { return {type_name<A>::get()...}; }
+};
+
+struct reg_import_tensor {
+  // `fn` is the adapter the link generates for this import; <fn>_ready and <fn>_done are its two events
+  reg_import_tensor(const char* name, const char* fn, const std::string& sig, const std::vector<std::string>& ctypes,
+                    const identity& id, args meanings, const demand_positions& demand, const strings& sites,
+                    const char* completion, lends lent, std::initializer_list<rendezvous> meets) {
+    const size_t paren = sig.find('(');
+    json callable = json::object(), events = json::object(), params = json::array();
+    callable["symbol"] = json(fn);
+    callable["declaration"] = json("extern \"C\" __device__ " + sig.substr(0, paren) + " " + fn + sig.substr(paren) + ";");
+    events["ready"] = json(std::string(fn) + "_ready");
+    events["done"] = json(std::string(fn) + "_done");
+    callable["events"] = events;
+    size_t k = 0;
+    for (const arg& a : meanings) {
+      json prm = json::object();
+      prm["name"] = json(a.name);
+      prm["meaning"] = json(a.meaning);
+      prm["ctype"] = json(k < ctypes.size() ? ctypes[k] : std::string());
+      params.push(prm);
+      ++k;
+    }
+    if (k != ctypes.size()) registry::get().fail(std::string("import ") + name + ": pl::args names " + std::to_string(k) + " of the adapter's " + std::to_string(ctypes.size()) + " parameters");
+    callable["params"] = params;
+    json ms = json::array();
+    for (const rendezvous& m : meets) {
+      json one = json::object();
+      one["event"] = json(m.event);
+      one["barrier"] = json(m.barrier);
+      one["cohort"] = json();            // every thread of the site's role
+      ms.push(one);
+    }
+    json demands = json::array();
+    demands.push(demand.to_json(id, name));
+    json imp = json::object();
+    imp["name"] = json(name);
+    imp["callable"] = callable;
+    imp["identity"] = id.to_json();
+    imp["demands"] = demands;
+    imp["sites"] = sites.to_json();
+    imp["completion"] = json(completion);
+    imp["lends"] = lends_json(lent);
+    imp["rendezvous"] = ms;
+    registry::get().tensor_imports.push(imp);
   }
 };
 
@@ -901,13 +1500,24 @@ constexpr bool is_role_entry = std::is_same<F, void(const void*, unsigned)>::val
   PL_REG(reg_role)(#name, #fn, warps)
 #define PL_EXPORT(name, fn) PL_REG(reg_export)(#name, #fn)
 // PL_TYPE(T): a struct that call channels pass by pointer; the generated trampoline forward-declares it
-#define PL_TYPE(T) \
-  namespace pl { template <> struct type_name<T> { static std::string get() { return "struct " #T; } }; } \
-  static_assert(true, "")
+// PL_TYPE(T, members...): the same with the members restated, checked against T's layout; declarations that
+// name T then carry its definition, and a consumer needs no header of the provider's
+#define PL_TYPE(T, ...) \
+  namespace pl { template <> struct type_name<T> { \
+    static std::string get() { return sizeof(#__VA_ARGS__) == 1 ? "struct " #T : #T; } }; } \
+  struct PL_CAT(pl_type_shadow_, __LINE__) { __VA_ARGS__ }; \
+  static_assert(sizeof(#__VA_ARGS__) == 1 || (sizeof(PL_CAT(pl_type_shadow_, __LINE__)) == sizeof(T) && \
+                alignof(PL_CAT(pl_type_shadow_, __LINE__)) == alignof(T)), "PL_TYPE members do not restate the layout of " #T); \
+  static ::pl::reg_type_if PL_CAT(pl_reg_, __COUNTER__)(#T, #__VA_ARGS__)
 // PL_CALL(channel, trampoline, pl::produce, "caller_role"[, "export_name"]) at the call site;
 // PL_CALL(channel, implementation, pl::consume, "export_name") beside the provided function
 #define PL_CALL(channel, fn, direction, ...) \
   PL_REG(reg_call)(#channel, #fn, ::pl::signature<decltype(fn)>::get(), direction, __VA_ARGS__)
+#define PL_BINDING(...) PL_REG(reg_binding)(__VA_ARGS__)
+#define PL_SITE(name, ...) PL_REG(reg_site)(#name, __VA_ARGS__)
+#define PL_EXPORT_TENSOR(name, ...) PL_REG(reg_export_tensor)(#name, __VA_ARGS__)
+#define PL_IMPORT_TENSOR(name, fn, ...) \
+  PL_REG(reg_import_tensor)(#name, #fn, ::pl::signature<decltype(fn)>::get(), ::pl::argument_types<decltype(fn)>::get(), __VA_ARGS__)
 #define PL_ENDPOINT(name, ...) PL_REG(reg_endpoint){#name, __VA_ARGS__}
 #define PL_CLAIM(a, b, ...) PL_REG(reg_claim_any)(#a, #b, __VA_ARGS__)
 // six arguments: (domain, handle, extent, align, key, value), this header's own form; one: a pl::claim builder
@@ -918,11 +1528,7 @@ constexpr bool is_role_entry = std::is_same<F, void(const void*, unsigned)>::val
 #define PL_CLAIM_EX(...) PL_CLAIM_EX_PICK(__VA_ARGS__, PL_CLAIM_EX6, x, x, x, x, PL_CLAIM_EX1, x)(__VA_ARGS__)
 // PL_CLAIM_SMEM("handle", T[, lifetime]): shared memory sized and aligned as T
 #define PL_CLAIM_SMEM(handle, T, ...) \
-  PL_REG(reg_claim_any)(::pl::claim(::pl::reg_claim_any::bare(#handle).c_str(), "smem").extent(sizeof(T)).align(alignof(T)).typed() PL_LIFETIME(__VA_ARGS__))
-#define PL_LIFETIME(...) PL_LIFETIME_PICK(_, ##__VA_ARGS__, PL_LIFETIME_1, PL_LIFETIME_0)(__VA_ARGS__)
-#define PL_LIFETIME_PICK(a, b, which, ...) which
-#define PL_LIFETIME_0()
-#define PL_LIFETIME_1(l) .lifetime(l)
+  PL_REG(reg_claim_any)(::pl::claim(::pl::reg_claim_any::bare(#handle).c_str(), "smem").extent(sizeof(T)).align(alignof(T)).typed().lifetime(__VA_ARGS__))
 #define PL_CLAIM_WARPS(handle, role, warps, align) PL_REG(reg_warps)(#handle, #role, warps, align)
 #define PL_CLAIM_REGS(handle, group, ...) PL_REG(reg_regs)(handle, group, __VA_ARGS__)
 #define PL_TOPOLOGY(...) PL_REG(reg_topology){__VA_ARGS__}   // braces: no vexing parse of pl::topology()

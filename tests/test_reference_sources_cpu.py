@@ -122,3 +122,29 @@ def test_profile_consumer_instruction_sources_emit_the_reference_manifests(index
     example = REFERENCE / "examples" / "profile-consumer" / "src"
     _same(pack.emit_manifest(example / f"{name}.cu", includes=(str(example), str(REFERENCE / "pipec/src/pipec2/host/include"))),
           PROFILE_CONSUMER["manifests"][index])
+
+
+ONE_EPILOGUE = json.loads((GOLDEN / "reference_one_epilogue_units.json").read_text())["units"]
+
+
+def _one_epilogue_unit(name, cutlass):
+    unit = ONE_EPILOGUE[name]
+    mine = pack.emit_manifest(REFERENCE / unit["source"], includes=(str(cutlass),),
+                              defines=[f"{k}={v}" for k, v in unit["defines"].items()])
+    _same(mine, unit["manifest"])
+    assert mine["tensor"] == unit["manifest"]["tensor"], name
+
+
+def test_one_epilogue_sources_emit_the_reference_tensor_sections():
+    """The tensor annotations (PL_SITE, PL_IMPORT_TENSOR, PL_EXPORT_TENSOR, PL_BINDING, PL_TYPE with members):
+    the maps are C++ lambdas; this header finds their forms itself and must print the expressions the reference's
+    pass fitted: affine ones (the tensor-memory placement comes out of a CUTLASS tiled-MMA layout, offset by a
+    bound base column) and an XOR-linear one (the 128-byte-swizzled shared-memory tile of the second cell).
+    The units compile side by side: the providers' mainloops take most of a minute each."""
+    from concurrent.futures import ThreadPoolExecutor
+    cutlass = _cutlass_include()
+    if cutlass is None:
+        pytest.skip("no CUTLASS include tree on this machine")
+    with ThreadPoolExecutor(len(ONE_EPILOGUE)) as pool:
+        for job in [pool.submit(_one_epilogue_unit, name, cutlass) for name in sorted(ONE_EPILOGUE)]:
+            job.result()
