@@ -21,9 +21,9 @@ from __future__ import annotations
 
 import re
 
-SITE_GUARANTEES = ("enter_once", "converged", "full_warps", "no_early_return")
-LEND_DOMAINS = ("smem", "barrier", "reg", "tmem")
-LEND_BINDINGS = ("relocatable", "fixed")
+SITE_GUARANTEES = ("enter_once", "single_completion", "converged", "full_warps", "no_early_return")
+LEND_DOMAINS = ("smem", "barrier", "reg", "tmem", "metadata")
+LEND_BINDINGS = ("relocatable", "fixed", "caller_frame")      # caller_frame: words of the caller's register frame
 TENSOR_SCHEMAS = ("2.2", "3.0")
 VERSION = "tensor-v2"
 _BITS = re.compile(r"bits\[([1-9][0-9]*)\]\Z")

@@ -154,7 +154,13 @@ def _range(d):
 class Connection:
     """An export's placement and an import's demand over one finite space."""
 
-    def __init__(self, export, imp, site, bindings=None):
+    # component names of the reference's units ("dp/column", "byte" addresses) beside this build's own
+    ALIASES = {"dp": "lane", "address": "byte"}
+
+    def __init__(self, export, imp, site, bindings=None, runtime=None):
+        """bindings: {name: value} known at link time. runtime: {name: {"values": [...], "units": ...}}, bindings
+        whose value the producer publishes at run time; one whose unit is `column` is what the tensor-memory
+        source handle carries, so the placement's columns are planned relative to it (checked in every world)."""
         self.export, self.imp, self.site = export, imp, site
         failures = tensor.check_import(export, imp)
         if failures:
@@ -170,12 +176,37 @@ class Connection:
         fixed.update(export.get("fixed_bindings") or {})
         self.placement = export["placements"][0]
         self.space = self.placement.get("space")
-        self.components = {k: bind_values(e, fixed) for k, e in self.placement["components"].items()}
+        runtime = {k: v for k, v in (runtime or {}).items() if k not in fixed}
+        worlds = [dict(zip(runtime, vs)) for vs in itertools.product(*[r["values"] for r in runtime.values()])] or [{}]
+        if len(worlds) > 64:
+            raise Infeasible("UNSUPPORTED_MODEL", f"{len(worlds)} binding worlds", "T-MODEL")
+
+        def bias(world):
+            return sum(v for k, v in world.items() if runtime[k].get("units") == "column")
+
+        def in_world(world):
+            return {self.ALIASES.get(k, k): bind_values(e, {**fixed, **world}) for k, e in self.placement["components"].items()}
+
+        self.components = in_world(worlds[0])
+        if bias(worlds[0]) and "column" in self.components:
+            self.components["column"] = ["add", self.components["column"], ["const", -bias(worlds[0])]]
+        if len(worlds) > 1:
+            names = [c["name"] for c in ident["coords"]]
+            for world in worlds[1:]:
+                other = in_world(world)
+                for point in itertools.product(*[_range(c) for c in ident["coords"]]):
+                    e = dict(zip(names, point))
+                    for k, expr in other.items():
+                        shift = bias(world) if k == "column" else 0
+                        if tensor.evaluate(expr, e) - shift != tensor.evaluate(self.components[k], e):
+                            raise Infeasible("UNSUPPORTED_MODEL", f"placement component {k} depends on a run-time binding other than as the source's base column", "T-MODEL")
         self.guard = bind_values(self.placement["guard"], fixed) if self.placement.get("guard") is not None else None
         dem = imp["demands"][0]
         if dem.get("guard") is not None:
             raise Infeasible("UNSUPPORTED_MODEL", "guarded demands", "T-MODEL")
-        dom = dem.get("domain", [])
+        dom = list(dem.get("domain", []))
+        if len(dom) == 1:          # one element per participant: the position is the single point 0
+            dom.append({"name": "pl_position", "lo": 0, "hi": 1, "sort": "int"})
         if len(dom) != 2:
             raise Infeasible("UNSUPPORTED_MODEL", "a positions demand ranges over (participant, position)", "T-MODEL")
         self.t, self.p = dom[0], dom[1]
@@ -401,20 +432,27 @@ def certify(program, conn):
 # ---------------------------------------------------------------- planning one connection
 def _rendezvous_events(conn):
     events = [r.get("event") for r in conn.imp.get("rendezvous", [])]
-    missing = [e for e in ("ready", "done") if e not in events]
+    # the two outer events: by this build's names, or as the contracts name them (the export's readiness
+    # event and the import's completion event, as the reference's units do)
+    wanted = ("ready", "done")
+    readiness = conn.export.get("readiness")
+    named = (readiness.get("after") if isinstance(readiness, dict) else None, conn.imp.get("completion"))
+    if all(named) and all(e in events for e in named):
+        wanted = named
+    missing = [e for e in wanted if e not in events]
     if missing:
         raise PipeLinkError(ClauseFailure("T-PLAN-RENDEZVOUS", f"tensor.imports.{conn.imp.get('name')}.rendezvous",
                                           f"missing outer events: {missing}"))
     return {r["event"]: r for r in conn.imp["rendezvous"]}
 
 
-def plan_connection(name, export, imp, site, bindings=None):
+def plan_connection(name, export, imp, site, bindings=None, runtime=None):
     """-> the connection's record: routes tried in order with their outcomes, the certified
     program, what it reserves. Raises PipeLinkError (T-CONTRACT / T-MODEL / T-PLAN...) when no
     route is certified."""
     path = f"pipeline.tensor_connections.{name}"
     try:
-        conn = Connection(export, imp, site, bindings)
+        conn = Connection(export, imp, site, bindings, runtime)
     except Infeasible as why:
         raise PipeLinkError(ClauseFailure(why.clause, path, f"{why.outcome}: {why.reason}"))
     events = _rendezvous_events(conn)
@@ -455,14 +493,18 @@ def plan_connection(name, export, imp, site, bindings=None):
     if used["scratch_bytes"]:
         claims.append({"handle": scratch["location"]["handle"], "domain": "smem", "align": scratch.get("align", 16),
                        "extent": {"const": used["scratch_bytes"], "per": {}}})
-    claims.append({"handle": barrier["location"]["handle"], "domain": "named_barrier", "align": 1, "extent": {"const": 1, "per": {}}})
+    # a barrier lent at a link-time handle is claimed; one lent at a fixed id (location.base) is the consumer's own to keep free
+    if barrier["location"].get("handle") is not None:
+        claims.append({"handle": barrier["location"]["handle"], "domain": "named_barrier", "align": 1, "extent": {"const": 1, "per": {}}})
     text = json.dumps(program, sort_keys=True, separators=(",", ":"))
-    return {"name": name, "export": export["name"], "import": imp["name"], "callable": imp["callable"], "dtype": conn.dtype,
+    return {"name": name, "export": export["name"], "import": imp["name"],
+            # the adapter's symbol: a bare name, or the record {symbol, declaration, events, params} of the reference's units
+            "callable": imp["callable"]["symbol"] if isinstance(imp["callable"], dict) else imp["callable"], "dtype": conn.dtype,
             "space": conn.space, "participants": len(conn.participants), "positions": len(conn.positions),
             "route_order": list(ROUTE_ORDER), "tried": tried, "route": route, "outcome": "MODEL_SAT", "program": program,
             "plan_sha256": hashlib.sha256(text.encode()).hexdigest(), "used": used, "claims": claims,
             "unused_handles": [scratch["location"]["handle"]] if scratch is not None and not used["scratch_bytes"] else [],
-            "barrier_handle": barrier["location"]["handle"], "events": sorted(events),
+            "barrier_handle": barrier["location"].get("handle"), "barrier_id": barrier["location"].get("base"), "events": sorted(events),
             "coords": {"t": conn.t["name"], "p": conn.p["name"]}}
 
 
@@ -493,13 +535,14 @@ def lower(record, *, warp_lo, threads_in_role):
     fn, ctype = record["callable"], C_TYPES[record["dtype"]]
     names = {record["coords"]["t"]: "pl_t", record["coords"]["p"]: "p", "i": "i"}
     tmem = record["space"] == "tmem"
-    bar = f"{record['barrier_handle']}()"
+    by_handle = record.get("barrier_handle") is not None
+    bar = f"{record['barrier_handle']}()" if by_handle else f"{int(record.get('barrier_id') or 0)}"
     sync = [f'  asm volatile("bar.sync %0, %1;" :: "r"({bar}), "r"({threads_in_role}) : "memory");']
     if tmem:
         sync = ['  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");'] + sync + \
                ['  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");']
     L = [f"// connection {record['name']}: route {record['route']}, plan {record['plan_sha256'][:16]}",
-         f'extern "C" __device__ int {record["barrier_handle"]}();',
+         *([f'extern "C" __device__ int {record["barrier_handle"]}();'] if by_handle else []),
          f'extern "C" __device__ void {fn}_ready() {{', *sync, "}",
          f'extern "C" __device__ void {fn}_done() {{', *sync, "}",
          f'extern "C" __device__ void {fn}(pipelink_tensor_source source, {ctype}* dest, void* scratch) {{',
@@ -552,6 +595,10 @@ def plan_pipeline(manifests, pipe):
     records, fed = [], {}
     for c in pipe.get("tensor_connections", []):
         path = f"pipeline.tensor_connections.{c.get('name')}"
+        if "producer" not in c and "consumer" not in c:        # the reference's spelling: "stage id:export", "stage id:import"
+            c = dict(c)
+            c["producer"], _, c["export"] = str(c.get("export", "")).rpartition(":")
+            c["consumer"], _, c["import"] = str(c.get("import", "")).rpartition(":")
         prod, cons = by_id.get(c.get("producer")), by_id.get(c.get("consumer"))
         if prod is None or cons is None:
             raise PipeLinkError(ClauseFailure("T-CONTRACT", path, "producer or consumer is not a stage of the pipeline"))
@@ -571,9 +618,14 @@ def plan_pipeline(manifests, pipe):
         site["participants"] = 32 * cons["stage"]["roles"][role]["warps"]
         site["warpgroup_aligned"] = any(cl.get("domain") == "warp" and role in cl.get("roles", []) and cl.get("align", 1) % 4 == 0
                                         for cl in cons.get("claims", []))
-        binds = {b["name"]: b["domain"]["values"][0] for b in (prod.get("tensor") or {}).get("bindings", [])
-                 if len(b.get("domain", {}).get("values", [])) == 1}
-        rec = plan_connection(c["name"], export, imp, site, binds)
+        declared = (prod.get("tensor") or {}).get("bindings", [])
+        binds = {b["name"]: b["domain"]["values"][0] for b in declared if len(b.get("domain", {}).get("values", [])) == 1}
+        runtime = {b["name"]: {"values": list(b["domain"]["values"]), "units": b.get("units")} for b in declared
+                   if len(b.get("domain", {}).get("values", [])) > 1}
+        # the only role of the pipeline that owns warps starts at warp 0, whatever its claim's alignment
+        owners = [r for m in manifests for r, spec in m["stage"]["roles"].items() if spec.get("warps", 0) > 0]
+        site["warpgroup_aligned"] = site["warpgroup_aligned"] or owners == [role]
+        rec = plan_connection(c["name"], export, imp, site, binds, runtime)
         rec.update(producer=c["producer"], consumer=c["consumer"], site_role=role)
         records.append(rec)
     return records

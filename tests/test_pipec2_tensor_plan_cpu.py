@@ -181,16 +181,29 @@ def test_contract_and_model_failures():
 
 
 def test_tensor_memory_needs_a_warpgroup_aligned_role():
-    def unaligned(_prod, cons):
+    def unaligned(prod, cons):
         for c in cons["claims"]:
             if c["domain"] == "warp":
                 c["align"] = 1
+        # a second role that owns warps: the importing role is no longer known to start at warp 0
+        prod["stage"]["roles"]["feeder"] = {"entry": "feeder_role", "warps": 1}
     with pytest.raises(PipeLinkError) as err:
         _plan("tmem", unaligned)
     (f,) = err.value.failures
     assert f.clause_id == "T-PLAN" and f.detail["missing"] == {"role_warp_align": 4}
     (rec,) = _plan("smem", unaligned)            # shared memory has no such rule
     assert rec["route"] == "shared_direct"
+
+
+def test_the_only_warp_owner_starts_at_warp_zero():
+    """With one role in the whole pipeline its claim's alignment does not matter (the reference's
+    one-epilogue cells: a four-warp epilogue whose warp claim has alignment 1)."""
+    def unaligned(_prod, cons):
+        for c in cons["claims"]:
+            if c["domain"] == "warp":
+                c["align"] = 1
+    (rec,) = _plan("tmem", unaligned)
+    assert rec["outcome"] == "MODEL_SAT"
 
 
 def test_register_export_needs_a_frame():

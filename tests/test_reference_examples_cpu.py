@@ -190,3 +190,61 @@ def test_hopper_gemm_split_solves_as_the_reference_solves_it(cell):
     for e in fe["expansions"]:
         ch = want["channels"][e["channel"]]
         assert (e["full"]["count"], e["empty"]["count"], e["full"]["tx_bytes"]) == (ch["arrive_full"], ch["arrive_empty"], ch["tx_bytes"])
+
+
+# ---------------------------------------------------------------- examples/one-epilogue-many-producers
+ONE_EPILOGUE = json.loads((Path(__file__).parent / "golden" / "reference_one_epilogue_units.json").read_text())
+# the reference names a route by its path through storage; this planner by what the consumer executes
+ROUTE_NAMES = {"tmem>receipt>reg": "direct_receipt", "smem>load>reg": "shared_direct"}
+
+
+@pytest.mark.parametrize("cell", sorted(ONE_EPILOGUE["cells"]))
+def test_one_epilogue_cells_plan_and_solve_as_the_reference_does(cell, tmp_path):
+    """Tensor imports end to end on the reference's documents: three owners' manifests emitted by the reference's
+    annotation pass (an accumulator tile in tensor memory behind a run-time base column, or in 128-byte-swizzled
+    shared memory; a row-scale vector; an epilogue importing both) and the pipeline description its example
+    generates. This driver's planner must certify every connection on the route the reference's planner
+    certified, and the solve must reach the reference's launch shape, parameter layout and placements; the
+    adapters it generates for the connections must compile for the profile."""
+    case = ONE_EPILOGUE["cells"][cell]
+    manifests = [copy.deepcopy(ONE_EPILOGUE["units"][n]["manifest"]) for n in case["units"]]
+    for m in manifests:
+        schema.validate_manifest(m)
+    fe = linker.front_end(manifests, copy.deepcopy(case["pipeline"]["pipeline"]))
+    want = case["reference"]
+    records = {r["name"]: r for r in fe["tensor"]}
+    assert sorted(records) == sorted(want["connections"])
+    for name, theirs in want["connections"].items():
+        assert theirs["status"] == records[name]["outcome"] == "MODEL_SAT"
+        assert records[name]["route"] == ROUTE_NAMES[theirs["route"]["id"]], name
+        assert records[name]["used"]["scratch_bytes"] == 0          # a direct route stages nothing
+    solved = want["solved"]
+    assert 32 * sum(w for _, w, _ in fe["role_warps"].values()) == solved["threads"]
+    warp_map = {role: [fe["bindings"][h][0] + off, fe["bindings"][h][0] + off + warps] for role, (h, warps, off) in fe["role_warps"].items()}
+    assert warp_map == solved["warp_map"]
+    # this driver's dispatch kernel owns the tensor-memory allocation and keeps a 16-byte slot for its base among
+    # the stages' claims; the reference's stages allocate for themselves, so its total is the claims alone
+    slot = next(iv for iv in fe["intervals"]["smem"] if iv["handle"] == linker.TMEM_SLOT_HANDLE)
+    assert slot["hi"] - slot["lo"] == 16
+    assert fe["solver"]["high_water"]["smem"] == solved["dyn_smem_bytes"] + 16
+    assert fe["params"]["total_bytes"] == solved["params"]["total_bytes"] and fe["params"]["align"] == solved["params"]["align"]
+    assert [list(e) for e in fe["params"]["entries"]] == solved["params"]["entries"]
+    mine = {iv["handle"]: [iv["lo"], iv["hi"]] for ivs in fe["intervals"].values() for iv in ivs}
+    for ivs in solved["intervals"].values():
+        for handle, lo, hi in ivs:
+            assert mine[handle][1] - mine[handle][0] == hi - lo, handle
+            if lo < slot["lo"]:            # what lies behind the slot sits 16 bytes further on
+                assert mine[handle] == [lo, hi], handle
+            else:
+                assert mine[handle] == [lo + 16, hi + 16], handle
+    assert sorted(e["channel"] for e in fe["expansions"]) == solved["channels"]
+    # the generated adapters are CUDA this toolchain compiles
+    import subprocess
+    from pipelink_b200.pipec2 import jitlink, pack, tensor_plan
+    unit = tmp_path / "adapters.cu"
+    unit.write_text(tensor_plan.adapters_unit(fe["tensor"], {role: (lo, hi - lo) for role, (lo, hi) in warp_map.items()}))
+    done = subprocess.run([jitlink.nvcc(), "-dc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", str(pack.INCLUDE),
+                           "-o", str(tmp_path / "adapters.o"), str(unit)], capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-2000:]
+    text = unit.read_text()
+    assert ("tcgen05.ld" in text) == (cell == "tmem")
