@@ -44,24 +44,29 @@ TCGEN05 = {"PL_TILE_N": "128", "PL_MMA_M": "128"}          # the defines of the 
 UNITS = {"consumer": ("consumer/epilogue.cu", {}), "rowscale": ("providers/rowscale/rowscale.cu", {}),
          "producer_m128": ("providers/accumulator/producer_m128.cu", {}),
          "acc_tmem": ("providers/accumulator/producer_source.cu", {**TCGEN05, "PL_EXPORT_TMEM": "1"}),
-         "acc_smem": ("providers/accumulator/producer_source.cu", {**TCGEN05, "PL_EXPORT_SMEM": "1"})}
+         "acc_smem": ("providers/accumulator/producer_source.cu", {**TCGEN05, "PL_EXPORT_SMEM": "1"}),
+         # the Hopper provider that exports the accumulator from the warpgroup-MMA register fragment: only its host
+         # projection is compiled; its placement is a bit permutation of (m, n), printed as integer bit fields
+         "sm90_reg": ("providers/accumulator/producer_sm90.cu", {"PL_TILE_N": "128"}, "sm_90a")}
 
 
-def emit(source: Path, defines: dict) -> dict:
+def emit(source: Path, defines: dict, profile: str = PROFILE) -> dict:
     env = os.environ.copy()
     cuda = symbols.cuda_home(env)
     env["PATH"] = str(cuda / "bin") + os.pathsep + env.get("PATH", "")
     env["CUDA_VISIBLE_DEVICES"] = ""
     with tempfile.TemporaryDirectory() as tmp:
-        comp = compile_registry(source, Path(tmp), includes=(CUTLASS,), defines=tuple(f"{k}={v}" for k, v in defines.items()), nvcc_flags=(), profile=PROFILE,
+        comp = compile_registry(source, Path(tmp), includes=(CUTLASS,), defines=tuple(f"{k}={v}" for k, v in defines.items()), nvcc_flags=(), profile=profile,
                                 toolkit=TOOLKIT, env=env)
-        return assemble(comp.registry, profile=PROFILE, toolkit=TOOLKIT, provenance_inputs=comp.provenance_inputs,
+        return assemble(comp.registry, profile=profile, toolkit=TOOLKIT, provenance_inputs=comp.provenance_inputs,
                         math=comp.math)
 
 
-record = {"units": {name: {"source": "examples/one-epilogue-many-producers/" + rel, "defines": defines,
-                           "manifest": emit(EXAMPLE / rel, defines)}
-                    for name, (rel, defines) in UNITS.items()}}
+record = {"units": {}}
+for name, (rel, defines, *rest) in UNITS.items():
+    profile = rest[0] if rest else PROFILE
+    record["units"][name] = {"source": "examples/one-epilogue-many-producers/" + rel, "defines": defines, "profile": profile,
+                             "manifest": emit(EXAMPLE / rel, defines, profile)}
 
 
 def cell_document(cell: str, owners: list) -> dict:

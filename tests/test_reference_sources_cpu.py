@@ -130,7 +130,7 @@ ONE_EPILOGUE = json.loads((GOLDEN / "reference_one_epilogue_units.json").read_te
 def _one_epilogue_unit(name, cutlass):
     unit = ONE_EPILOGUE[name]
     mine = pack.emit_manifest(REFERENCE / unit["source"], includes=(str(cutlass),),
-                              defines=[f"{k}={v}" for k, v in unit["defines"].items()])
+                              defines=[f"{k}={v}" for k, v in unit["defines"].items()], profile=unit["profile"])
     _same(mine, unit["manifest"])
     assert mine["tensor"] == unit["manifest"]["tensor"], name
 
@@ -139,7 +139,8 @@ def test_one_epilogue_sources_emit_the_reference_tensor_sections():
     """The tensor annotations (PL_SITE, PL_IMPORT_TENSOR, PL_EXPORT_TENSOR, PL_BINDING, PL_TYPE with members):
     the maps are C++ lambdas; this header finds their forms itself and must print the expressions the reference's
     pass fitted: affine ones (the tensor-memory placement comes out of a CUTLASS tiled-MMA layout, offset by a
-    bound base column) and an XOR-linear one (the 128-byte-swizzled shared-memory tile of the second cell).
+    bound base column), an XOR-linear one (the 128-byte-swizzled shared-memory tile of the second cell) and a bit
+    permutation printed as integer fields (the Hopper provider's warpgroup-MMA register fragment).
     The units compile side by side: the providers' mainloops take most of a minute each."""
     from concurrent.futures import ThreadPoolExecutor
     cutlass = _cutlass_include()
