@@ -210,6 +210,7 @@ def test_one_epilogue_cells_plan_and_solve_as_the_reference_does(cell, tmp_path)
     manifests = [copy.deepcopy(ONE_EPILOGUE["units"][n]["manifest"]) for n in case["units"]]
     for m in manifests:
         schema.validate_manifest(m)
+    schema.validate_pipeline(copy.deepcopy(case["pipeline"]))
     fe = linker.front_end(manifests, copy.deepcopy(case["pipeline"]["pipeline"]))
     want = case["reference"]
     records = {r["name"]: r for r in fe["tensor"]}
