@@ -74,6 +74,39 @@ def test_malformed_units_fail_with_a_clause(tmp_path, extra, clause):
     assert err.value.failures[0].clause_id == clause
 
 
+TENSOR_EXPORT = '''PL_EXPORT_TENSOR(tile, pl::identity{"tile", "work", "done", "f32", "plain", {{"m", 0, 16}, {"n", 0, 8}}},
+    pl::placement{"smem", "byte", {"address"}, [](int m, int n) { return std::array<int, 1>{%s}; },
+                  pl::coord{"m", 0, 16}, pl::coord{"n", 0, 8}},
+    pl::strings{"smem_load_scalar"}, pl::readiness{"ready", "done"}, pl::fixed_bindings{},
+    pl::lends{pl::smem("store", 512, 16, "pipelink_demo_store", "scale", "work", "done")}, pl::calls{"produce", "release"});'''
+
+
+@pytest.mark.parametrize("body, address", [
+    ("4 * (8 * m + n) + 64", ["add", ["add", ["mulc", 32, ["coord", "m"]], ["mulc", 4, ["coord", "n"]]], ["const", 64]]),      # affine
+    ("4 * ((8 * m + n) ^ (m >> 1))", None),                                                                                   # XOR swizzle
+    ("4 * (8 * (m / 2) + 4 * (m % 2) + n / 2) + 256 * (n % 2)", None),                                                         # bit permutation
+])
+def test_a_placement_lambda_is_solved_to_an_expression(tmp_path, body, address):
+    """Whatever family the map falls in, the printed expression reproduces the lambda on its whole domain."""
+    from pipelink_b200.pipec2 import tensor
+    m = pack.emit_manifest(_unit(tmp_path, TENSOR_EXPORT % body))
+    expr = m["tensor"]["exports"][0]["placements"][0]["components"]["address"]
+    if address is not None:
+        assert expr == address
+    else:
+        assert expr[0] in ("toint", "add", "mulc", "modc", "divc")
+    for mm in range(16):
+        for nn in range(8):
+            want = eval(body.replace("/", "//"), {"m": mm, "n": nn})
+            assert tensor.evaluate(expr, {"m": mm, "n": nn}) == want, (mm, nn)
+
+
+def test_a_map_of_neither_family_is_refused(tmp_path):
+    with pytest.raises(PipeLinkError) as err:
+        pack.emit_manifest(_unit(tmp_path, TENSOR_EXPORT % "m * n"))
+    assert err.value.failures[0].clause_id == "P-ANNOTATION" and "neither integer-affine nor XOR-linear" in str(err.value)
+
+
 def test_moe_units_state_the_sizes_their_structs_have():
     ms = mb.manifests()
     sizes = {name: (m["params"]["bytes"], m["params"]["align"]) for name, m in ms.items()}
